@@ -1,0 +1,199 @@
+"""Deterministic synthetic checkpoints and prompts (numpy twin of include/nerva_synth.h).
+
+The reference's decode benchmarks run on random-init BF16 weights ~N(0, 0.02)
+(seed 0), unit norm weights, and uniform prompt ids (seed 1).  Values are a pure
+function of (seed, tensor id, element index), computed with integer arithmetic
+plus one float32 multiply, so this module, the C header and the CUDA fill kernel
+produce identical bits.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass, field
+
+import numpy as np
+
+GAMMA = np.uint64(0x9E3779B97F4A7C15)
+_M1 = np.uint64(0xBF58476D1CE4E5B9)
+_M2 = np.uint64(0x94D049BB133111EB)
+
+T_EMBEDDINGS = 1
+T_LM_HEAD = 2
+T_PROMPT = 3
+T_PAGE_TABLE = 4
+T_ACTIVATION = 5
+T_LAYER_BASE = 1000
+L_WQ, L_WK, L_WV, L_WO, L_WGATE, L_WUP, L_WDOWN = 0, 1, 2, 3, 4, 5, 6
+L_ROUTER, L_EXPERT_GATE_UP, L_EXPERT_DOWN = 7, 8, 9
+L_SHARED_GATE, L_SHARED_UP, L_SHARED_DOWN = 10, 11, 12
+L_Q_A, L_Q_B, L_KV_A, L_KV_B, L_K, L_V, L_Q = 13, 14, 15, 16, 17, 18, 19
+
+BF16_ONE = 0x3F80
+
+
+def layer_tensor_id(layer: int, slot: int) -> int:
+    return T_LAYER_BASE + layer * 64 + slot
+
+
+def _mix64(z: np.ndarray) -> np.ndarray:
+    z = (z ^ (z >> np.uint64(30))) * _M1
+    z = (z ^ (z >> np.uint64(27))) * _M2
+    return z ^ (z >> np.uint64(31))
+
+
+def key(seed: int, tensor_id: int) -> np.uint64:
+    with np.errstate(over="ignore"):
+        return _mix64(np.uint64(seed) * GAMMA + np.uint64(tensor_id))
+
+
+def u64(k: np.uint64, counter: np.ndarray) -> np.ndarray:
+    with np.errstate(over="ignore"):
+        return _mix64(k + (counter.astype(np.uint64) + np.uint64(1)) * GAMMA)
+
+
+def _fields16(h: np.ndarray) -> np.ndarray:
+    m = np.uint64(0xFFFF)
+    return ((h & m) + ((h >> np.uint64(16)) & m) + ((h >> np.uint64(32)) & m) + (h >> np.uint64(48))).astype(np.int64)
+
+
+def normal_i32(seed: int, tensor_id: int, count: int, start: int = 0) -> np.ndarray:
+    k = key(seed, tensor_id)
+    idx = np.arange(start, start + count, dtype=np.uint64) * np.uint64(3)
+    s = _fields16(u64(k, idx)) + _fields16(u64(k, idx + np.uint64(1))) + _fields16(u64(k, idx + np.uint64(2)))
+    return (s - 6 * 65535).astype(np.int32)
+
+
+def f32_to_bf16(values: np.ndarray) -> np.ndarray:
+    bits = np.ascontiguousarray(values, dtype=np.float32).view(np.uint32)
+    lsb = (bits >> np.uint32(16)) & np.uint32(1)
+    rounded = ((bits.astype(np.uint64) + np.uint64(0x7FFF) + lsb) >> np.uint64(16)).astype(np.uint16)
+    nan = ((bits & np.uint32(0x7F800000)) == np.uint32(0x7F800000)) & ((bits & np.uint32(0x007FFFFF)) != 0)
+    return np.where(nan, ((bits >> np.uint32(16)) | np.uint32(1)).astype(np.uint16), rounded)
+
+
+def bf16_to_f32(bits: np.ndarray) -> np.ndarray:
+    return (np.ascontiguousarray(bits, dtype=np.uint16).astype(np.uint32) << np.uint32(16)).view(np.float32)
+
+
+def normal_f32(seed: int, tensor_id: int, count: int, std: float, start: int = 0) -> np.ndarray:
+    scale = np.float32(np.float32(std) * np.float32(2.0 ** -16))
+    return normal_i32(seed, tensor_id, count, start).astype(np.float32) * scale
+
+
+def normal_bf16(seed: int, tensor_id: int, count: int, std: float, start: int = 0) -> np.ndarray:
+    out = np.empty(count, dtype=np.uint16)
+    chunk = 1 << 22
+    for lo in range(0, count, chunk):
+        n = min(chunk, count - lo)
+        out[lo:lo + n] = f32_to_bf16(normal_f32(seed, tensor_id, n, std, start + lo))
+    return out
+
+
+def uniform_u32(seed: int, tensor_id: int, count: int, bound: int) -> np.ndarray:
+    k = key(seed, tensor_id)
+    return (u64(k, np.arange(count, dtype=np.uint64)) % np.uint64(bound)).astype(np.uint32)
+
+
+def permutation(seed: int, tensor_id: int, count: int) -> np.ndarray:
+    """Seeded Fisher-Yates shuffle of 0..count-1 (physical KV page ids)."""
+    k = key(seed, tensor_id)
+    draws = u64(k, np.arange(count, dtype=np.uint64))
+    perm = list(range(count))
+    for i in range(count - 1, 0, -1):
+        j = int(draws[i] % np.uint64(i + 1))
+        perm[i], perm[j] = perm[j], perm[i]
+    return np.asarray(perm, dtype=np.uint32)
+
+
+@dataclass
+class DecoderConfig:
+    name: str
+    layers: int
+    hidden: int
+    heads: int
+    kv_heads: int
+    head_dim: int
+    intermediate: int
+    vocab: int
+    rms_eps: float = 1e-6
+    rope_theta: float = 1e6
+    qk_norm: bool = True
+    prompt_tokens: int = 64
+    decode_tokens: int = 32
+    # softmax top-k MoE (mlp_kind 1); zero experts = dense SwiGLU
+    num_experts: int = 0
+    top_k: int = 0
+    moe_intermediate: int = 0
+    shared_intermediate: int = 0
+    norm_topk_prob: bool = False
+
+    @property
+    def attention_hidden(self) -> int:
+        return self.heads * self.head_dim
+
+    @property
+    def kv_hidden(self) -> int:
+        return self.kv_heads * self.head_dim
+
+    def projection_bytes_per_token(self) -> int:
+        """Weight bytes one decoded token must stream (2*N*K per projection)."""
+        h = self.hidden
+        per_layer = (self.attention_hidden + 2 * self.kv_hidden) * h + h * self.attention_hidden
+        per_layer += 3 * self.intermediate * h
+        return 2 * (per_layer * self.layers + self.vocab * h)
+
+
+TINY_QWEN3 = DecoderConfig("tiny-qwen3", layers=4, hidden=512, heads=8, kv_heads=2, head_dim=64,
+                           intermediate=1536, vocab=32000, prompt_tokens=64, decode_tokens=32)
+QWEN3_8B = DecoderConfig("qwen3-8b", layers=36, hidden=4096, heads=32, kv_heads=8, head_dim=128,
+                         intermediate=12288, vocab=151936, prompt_tokens=512, decode_tokens=256)
+
+
+@dataclass
+class DenseCheckpoint:
+    config: DecoderConfig
+    embeddings: np.ndarray
+    final_norm: np.ndarray
+    lm_head: np.ndarray
+    layers: list = field(default_factory=list)  # dict name -> uint16 array
+
+
+def dense_checkpoint(cfg: DecoderConfig, seed: int = 0, std: float = 0.02, fill=None) -> DenseCheckpoint:
+    """Random-init BF16 checkpoint.  `fill(seed, tensor_id, count, std)` may be a
+    native generator (same bits, multi-threaded) for the full-size models."""
+    gen = fill or normal_bf16
+    ones_h = np.full(cfg.hidden, BF16_ONE, dtype=np.uint16)
+    ones_d = np.full(cfg.head_dim, BF16_ONE, dtype=np.uint16)
+    ck = DenseCheckpoint(
+        cfg,
+        embeddings=gen(seed, T_EMBEDDINGS, cfg.vocab * cfg.hidden, std),
+        final_norm=ones_h.copy(),
+        lm_head=gen(seed, T_LM_HEAD, cfg.vocab * cfg.hidden, std),
+    )
+    for layer in range(cfg.layers):
+        tid = lambda slot: layer_tensor_id(layer, slot)  # noqa: E731
+        entry = {
+            "rms_attn": ones_h.copy(),
+            "rms_mlp": ones_h.copy(),
+            "w_q": gen(seed, tid(L_WQ), cfg.attention_hidden * cfg.hidden, std),
+            "w_k": gen(seed, tid(L_WK), cfg.kv_hidden * cfg.hidden, std),
+            "w_v": gen(seed, tid(L_WV), cfg.kv_hidden * cfg.hidden, std),
+            "w_o": gen(seed, tid(L_WO), cfg.hidden * cfg.attention_hidden, std),
+        }
+        if cfg.qk_norm:
+            entry["q_norm"] = ones_d.copy()
+            entry["k_norm"] = ones_d.copy()
+        if cfg.num_experts == 0:
+            entry["w_gate"] = gen(seed, tid(L_WGATE), cfg.intermediate * cfg.hidden, std)
+            entry["w_up"] = gen(seed, tid(L_WUP), cfg.intermediate * cfg.hidden, std)
+            entry["w_down"] = gen(seed, tid(L_WDOWN), cfg.hidden * cfg.intermediate, std)
+        else:
+            mi, e = cfg.moe_intermediate, cfg.num_experts
+            entry["w_router"] = gen(seed, tid(L_ROUTER), e * cfg.hidden, std)
+            entry["w_expert_gate_up"] = gen(seed, tid(L_EXPERT_GATE_UP), e * 2 * mi * cfg.hidden, std)
+            entry["w_expert_down"] = gen(seed, tid(L_EXPERT_DOWN), e * cfg.hidden * mi, std)
+        ck.layers.append(entry)
+    return ck
+
+
+def prompt_ids(cfg: DecoderConfig, seed: int = 1, count: int | None = None) -> np.ndarray:
+    return uniform_u32(seed, T_PROMPT, cfg.prompt_tokens if count is None else count, cfg.vocab)

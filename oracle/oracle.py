@@ -1,0 +1,242 @@
+"""ctypes front-end of the CPU oracle.  TEST INFRASTRUCTURE — never imported by the product package.
+
+Only tests/, the smoke check and the CPU-baseline / reference arm of bench.py
+may import this module.
+"""
+from __future__ import annotations
+
+import ctypes as C
+import os
+import subprocess
+
+import numpy as np
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+_LIB_PATH = os.path.join(_HERE, "_build", "libnerva_oracle.so")
+
+MODE_CPU = 0
+MODE_CUDA = 1
+DTYPE_F16 = 0
+DTYPE_BF16 = 1
+
+_u16p = C.POINTER(C.c_uint16)
+_u32p = C.POINTER(C.c_uint32)
+_f32p = C.POINTER(C.c_float)
+
+
+class OracleLayer(C.Structure):
+    _fields_ = [(n, _u16p) for n in (
+        "rms_attn", "rms_mlp", "w_q", "w_k", "w_v", "w_o", "q_norm", "k_norm",
+        "q_bias", "k_bias", "v_bias", "o_bias", "w_gate", "w_up", "w_down")] + [
+        (n, C.c_uint32) for n in (
+            "mlp_kind", "moe_intermediate", "shared_intermediate", "num_experts", "top_k", "norm_topk_prob")] + [
+        (n, _u16p) for n in (
+            "w_router", "w_expert_gate_up", "w_expert_down",
+            "w_shared_gate", "w_shared_up", "w_shared_down", "w_shared_router")]
+
+
+class OracleModel(C.Structure):
+    _fields_ = [(n, C.c_uint32) for n in (
+        "dtype", "hidden", "heads", "kv_heads", "head_dim", "intermediate", "vocab", "layers")] + [
+        ("rms_eps", C.c_float), ("rope_theta", C.c_float),
+        ("embeddings", _u16p), ("final_norm", _u16p), ("lm_head", _u16p),
+        ("layer", C.POINTER(OracleLayer))]
+
+
+def build(force: bool = False) -> str:
+    """Compile the oracle with the Makefile beside this file."""
+    if force or not os.path.exists(_LIB_PATH):
+        subprocess.run(["make", "-C", _HERE], check=True, capture_output=True)
+    return _LIB_PATH
+
+
+_lib = None
+
+
+def lib() -> C.CDLL:
+    global _lib
+    if _lib is None:
+        build()
+        L = C.CDLL(_LIB_PATH)
+        L.oracle_bf16_to_f32.restype = C.c_float
+        L.oracle_bf16_to_f32.argtypes = [C.c_uint16]
+        L.oracle_f32_to_bf16.restype = C.c_uint16
+        L.oracle_f32_to_bf16.argtypes = [C.c_float]
+        L.oracle_f16_to_f32.restype = C.c_float
+        L.oracle_f16_to_f32.argtypes = [C.c_uint16]
+        L.oracle_f32_to_f16.restype = C.c_uint16
+        L.oracle_f32_to_f16.argtypes = [C.c_float]
+        L.oracle_silu.restype = C.c_float
+        L.oracle_silu.argtypes = [C.c_float]
+        L.oracle_rms_norm.argtypes = [C.c_uint32, _f32p, _u16p, C.c_uint32, C.c_float, _f32p]
+        L.oracle_per_head_rms_norm.argtypes = [C.c_uint32, _u16p, C.c_uint32, _f32p, C.c_uint32, C.c_float]
+        L.oracle_matvec.argtypes = [C.c_uint32, _u16p, _f32p, C.c_uint32, C.c_uint32, _f32p]
+        L.oracle_rope.argtypes = [_f32p, C.c_uint32, C.c_uint32, C.c_uint32, C.c_float]
+        L.oracle_attention.argtypes = [_f32p, _f32p, _f32p, C.c_uint32, C.c_uint32, C.c_uint32, C.c_uint32, _f32p]
+        L.oracle_attention_paged.argtypes = [C.c_uint32, _f32p, _u16p, _u16p, _u32p, C.c_uint32, C.c_uint32,
+                                             C.c_uint32, C.c_uint32, _f32p]
+        L.oracle_argmax.restype = C.c_int64
+        L.oracle_argmax.argtypes = [_f32p, C.c_uint32, C.c_int]
+        L.oracle_route_softmax_topk.argtypes = [_f32p, C.c_uint32, C.c_uint32, C.c_uint32, _u32p, _f32p]
+        L.oracle_create.restype = C.c_void_p
+        L.oracle_create.argtypes = [C.POINTER(OracleModel), C.c_uint32, C.c_int]
+        L.oracle_destroy.argtypes = [C.c_void_p]
+        L.oracle_reset.argtypes = [C.c_void_p]
+        L.oracle_position.restype = C.c_uint32
+        L.oracle_position.argtypes = [C.c_void_p]
+        L.oracle_step.argtypes = [C.c_void_p, C.c_uint32, _f32p]
+        L.oracle_decode_greedy.argtypes = [C.c_void_p, _u32p, C.c_uint32, C.c_uint32, _u32p, _f32p]
+        L.oracle_hidden_state.restype = _f32p
+        L.oracle_hidden_state.argtypes = [C.c_void_p]
+        L.oracle_hash_tokens.restype = C.c_uint64
+        L.oracle_hash_tokens.argtypes = [_u32p, C.c_uint32]
+        L.oracle_set_threads.argtypes = [C.c_int]
+        L.oracle_get_threads.restype = C.c_int
+        _lib = L
+    return _lib
+
+
+def _p16(a):
+    return None if a is None else a.ctypes.data_as(_u16p)
+
+
+def _pf(a):
+    return a.ctypes.data_as(_f32p)
+
+
+def _pu(a):
+    return a.ctypes.data_as(_u32p)
+
+
+def matvec(matrix_bits: np.ndarray, x: np.ndarray, rows: int, cols: int, dtype: int = DTYPE_BF16) -> np.ndarray:
+    x = np.ascontiguousarray(x, dtype=np.float32)
+    out = np.empty(rows, dtype=np.float32)
+    lib().oracle_matvec(dtype, _p16(matrix_bits), _pf(x), rows, cols, _pf(out))
+    return out
+
+
+def rms_norm(x: np.ndarray, weight_bits: np.ndarray, eps: float, dtype: int = DTYPE_BF16) -> np.ndarray:
+    x = np.ascontiguousarray(x, dtype=np.float32)
+    out = np.empty_like(x)
+    lib().oracle_rms_norm(dtype, _pf(x), _p16(weight_bits), x.size, eps, _pf(out))
+    return out
+
+
+def per_head_rms_norm(values: np.ndarray, weight_bits: np.ndarray, head_dim: int, eps: float,
+                      dtype: int = DTYPE_BF16) -> np.ndarray:
+    out = np.array(values, dtype=np.float32, copy=True)
+    lib().oracle_per_head_rms_norm(dtype, _p16(weight_bits), head_dim, _pf(out), out.size, eps)
+    return out
+
+
+def rope(values: np.ndarray, heads: int, head_dim: int, position: int, theta: float) -> np.ndarray:
+    out = np.array(values, dtype=np.float32, copy=True)
+    lib().oracle_rope(_pf(out), heads, head_dim, position, theta)
+    return out
+
+
+def attention(q, keys, values, tokens, heads, kv_heads, head_dim) -> np.ndarray:
+    q = np.ascontiguousarray(q, dtype=np.float32)
+    keys = np.ascontiguousarray(keys, dtype=np.float32)
+    values = np.ascontiguousarray(values, dtype=np.float32)
+    out = np.empty(heads * head_dim, dtype=np.float32)
+    rc = lib().oracle_attention(_pf(q), _pf(keys), _pf(values), tokens, heads, kv_heads, head_dim, _pf(out))
+    if rc != 0:
+        raise ValueError("oracle attention rejected its input")
+    return out
+
+
+def attention_paged(q, key_pages, value_pages, page_table, tokens, heads, kv_heads, head_dim,
+                    dtype: int = DTYPE_BF16) -> np.ndarray:
+    q = np.ascontiguousarray(q, dtype=np.float32)
+    page_table = np.ascontiguousarray(page_table, dtype=np.uint32)
+    out = np.empty(heads * head_dim, dtype=np.float32)
+    rc = lib().oracle_attention_paged(dtype, _pf(q), _p16(key_pages), _p16(value_pages), _pu(page_table),
+                                      tokens, heads, kv_heads, head_dim, _pf(out))
+    if rc != 0:
+        raise ValueError("oracle paged attention rejected its input")
+    return out
+
+
+def argmax(logits: np.ndarray, mode: int = MODE_CUDA) -> int:
+    logits = np.ascontiguousarray(logits, dtype=np.float32)
+    return int(lib().oracle_argmax(_pf(logits), logits.size, mode))
+
+
+def route_softmax_topk(router_logits, top_k: int, norm_topk_prob: bool):
+    logits = np.ascontiguousarray(router_logits, dtype=np.float32)
+    experts = np.zeros(top_k, dtype=np.uint32)
+    weights = np.zeros(top_k, dtype=np.float32)
+    lib().oracle_route_softmax_topk(_pf(logits), logits.size, top_k, int(norm_topk_prob), _pu(experts), _pf(weights))
+    return experts, weights
+
+
+def hash_tokens(tokens) -> int:
+    t = np.ascontiguousarray(tokens, dtype=np.uint32)
+    return int(lib().oracle_hash_tokens(_pu(t), t.size))
+
+
+class Decoder:
+    """CPU decoder over a checkpoint object exposing `.config`, `.embeddings`,
+    `.final_norm`, `.lm_head` and `.layers` (list of dict name -> uint16 array)."""
+
+    def __init__(self, checkpoint, max_context: int, mode: int = MODE_CPU, dtype: int = DTYPE_BF16):
+        cfg = checkpoint.config
+        self.cfg = cfg
+        self._keep = checkpoint
+        self._layers = (OracleLayer * cfg.layers)()
+        names = {"w_shared_gate": "w_shared_expert_gate", "w_shared_up": "w_shared_expert_up",
+                 "w_shared_down": "w_shared_expert_down", "w_shared_router": "w_shared_expert_router"}
+        for i, entry in enumerate(checkpoint.layers):
+            layer = self._layers[i]
+            for fname, ftype in OracleLayer._fields_:
+                if ftype is _u16p:
+                    setattr(layer, fname, _p16(entry.get(names.get(fname, fname))))
+            if cfg.num_experts:
+                layer.mlp_kind = 1
+                layer.moe_intermediate = cfg.moe_intermediate
+                layer.shared_intermediate = cfg.shared_intermediate
+                layer.num_experts = cfg.num_experts
+                layer.top_k = cfg.top_k
+                layer.norm_topk_prob = int(cfg.norm_topk_prob)
+        self._model = OracleModel(
+            dtype=dtype, hidden=cfg.hidden, heads=cfg.heads, kv_heads=cfg.kv_heads, head_dim=cfg.head_dim,
+            intermediate=cfg.intermediate, vocab=cfg.vocab, layers=cfg.layers, rms_eps=cfg.rms_eps,
+            rope_theta=cfg.rope_theta, embeddings=_p16(checkpoint.embeddings),
+            final_norm=_p16(checkpoint.final_norm), lm_head=_p16(checkpoint.lm_head),
+            layer=C.cast(self._layers, C.POINTER(OracleLayer)))
+        self._ctx = lib().oracle_create(C.byref(self._model), max_context, mode)
+        if not self._ctx:
+            raise ValueError("oracle rejected the model")
+        self.mode = mode
+
+    def close(self):
+        if self._ctx:
+            lib().oracle_destroy(self._ctx)
+            self._ctx = None
+
+    def __del__(self):
+        self.close()
+
+    def reset(self):
+        lib().oracle_reset(self._ctx)
+
+    def step(self, token: int, want_logits: bool = True):
+        logits = np.empty(self.cfg.vocab, dtype=np.float32) if want_logits else None
+        rc = lib().oracle_step(self._ctx, int(token), _pf(logits) if want_logits else None)
+        if rc != 0:
+            raise ValueError("oracle step failed")
+        return logits
+
+    def hidden_state(self) -> np.ndarray:
+        return np.ctypeslib.as_array(lib().oracle_hidden_state(self._ctx), shape=(self.cfg.hidden,)).copy()
+
+    def decode_greedy(self, prompt, steps: int, want_logits: bool = False):
+        prompt = np.ascontiguousarray(prompt, dtype=np.uint32)
+        tokens = np.zeros(steps, dtype=np.uint32)
+        logits = np.empty((steps, self.cfg.vocab), dtype=np.float32) if want_logits else None
+        n = lib().oracle_decode_greedy(self._ctx, _pu(prompt), prompt.size, steps, _pu(tokens),
+                                       _pf(logits) if want_logits else None)
+        if n < 0:
+            raise ValueError("oracle decode failed")
+        return (tokens[:n], logits[:n]) if want_logits else tokens[:n]
