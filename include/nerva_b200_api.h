@@ -1,0 +1,658 @@
+/*
+ * C ABI of the B200-native resident decode step.
+ *
+ * Every `nerva_cuda_*` entry point and every `NervaCuda*` struct below has the
+ * same name, field order, field types and error convention as its counterpart
+ * in the reference's native/cuda/nerva_cuda_api.h, so the reference's FFI crate
+ * (crates/nerva-cuda, `repr(C)` mirrors in src/decode/hf_sequence/session/ffi.rs)
+ * links against this library unchanged.  The citation after each declaration is
+ * the reference declaration it replaces.
+ *
+ * Error convention (reference: hf_decode_sequence/session_api_lifecycle.inc.cu):
+ * return 0 on success and -1 on failure; `out` is zero-filled first, then
+ * `status` (0 / -1) and `cuda_error` (a cudaError_t value) are set.  Invalid
+ * arguments are rejected before any device call.  Nothing here falls back to
+ * the CPU: without a CUDA device `cuda_error` is cudaErrorNoDevice.
+ *
+ * Entry points named `nerva_b200_*` are additive (no reference counterpart);
+ * each says so.
+ */
+#ifndef NERVA_B200_API_H_
+#define NERVA_B200_API_H_
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* dtype codes — hf_decode_sequence/types.cuh:9-11 */
+#define NERVA_DTYPE_F16 0u
+#define NERVA_DTYPE_BF16 1u
+#define NERVA_DTYPE_F32 2u
+/* hf_decode_sequence/types.cuh:12-16,37-38,64 */
+#define NERVA_MLP_KIND_DENSE 0u
+#define NERVA_MLP_KIND_SPARSE_MOE 1u
+#define NERVA_ATTENTION_KIND_FULL 0u
+#define NERVA_ATTENTION_KIND_LINEAR_GDN 1u
+#define NERVA_ATTENTION_KIND_DEEPSEEK_MLA 2u
+#define NERVA_WEIGHT_STRATEGY_GPU_RESIDENT 1u
+#define NERVA_WEIGHT_STRATEGY_GPU_STAGED 2u
+#define NERVA_KV_CACHE_BLOCK_TOKENS 16u
+
+/* nerva_cuda_api.h:29-37 — one entry of the device token ring (40 bytes). */
+typedef struct NervaCudaSyntheticTokenSlot {
+  uint32_t request_id;
+  uint32_t sequence_id;
+  uint64_t token_index;
+  uint32_t token;
+  uint64_t version;
+  uint32_t completion;
+  uint32_t host_copied;
+} NervaCudaSyntheticTokenSlot;
+
+/* nerva_cuda_api.h:255-332 */
+typedef struct NervaCudaHfDecodeChainLayer {
+  const uint16_t *rms_attn_weight;
+  const uint16_t *rms_mlp_weight;
+  const uint16_t *w_q;
+  const uint16_t *w_q_gate;
+  const uint16_t *w_k;
+  const uint16_t *q_norm_weight;
+  const uint16_t *k_norm_weight;
+  const uint16_t *w_v;
+  const uint16_t *w_o;
+  const uint16_t *q_bias;
+  const uint16_t *k_bias;
+  const uint16_t *v_bias;
+  const uint16_t *o_bias;
+  const uint16_t *w_gate;
+  const uint16_t *w_up;
+  const uint16_t *w_down;
+  const uint16_t *w_router;
+  const uint16_t *w_expert_gate_up;
+  const uint16_t *w_expert_down;
+  const uint16_t *w_shared_expert_gate;
+  const uint16_t *w_shared_expert_up;
+  const uint16_t *w_shared_expert_down;
+  const uint16_t *w_shared_expert_router;
+  uint32_t linear_key_heads;
+  uint32_t linear_value_heads;
+  uint32_t linear_key_head_dim;
+  uint32_t linear_value_head_dim;
+  uint32_t linear_conv_kernel;
+  const uint16_t *w_linear_conv;
+  const uint16_t *w_linear_qkv;
+  const uint16_t *w_linear_z;
+  const uint16_t *w_linear_b;
+  const uint16_t *w_linear_a;
+  const uint16_t *w_linear_dt_bias;
+  const float *w_linear_a_log;
+  const uint16_t *w_linear_norm;
+  const uint16_t *w_linear_out;
+  uint32_t mlp_kind;
+  uint32_t moe_intermediate;
+  uint32_t shared_expert_intermediate;
+  uint32_t num_experts;
+  uint32_t experts_per_token;
+  uint32_t norm_topk_prob;
+  uint32_t attention_kind;
+  uint32_t deepseek_mode;
+  uint32_t deepseek_flags;
+  uint32_t deepseek_storage;
+  uint32_t deepseek_hc_mult;
+  uint32_t deepseek_hc_sinkhorn_iters;
+  uint32_t deepseek_q_lora_rank;
+  uint32_t deepseek_kv_lora_rank;
+  uint32_t deepseek_o_lora_rank;
+  uint32_t deepseek_o_groups;
+  uint32_t deepseek_qk_nope_head_dim;
+  uint32_t deepseek_qk_rope_head_dim;
+  uint32_t deepseek_v_head_dim;
+  uint32_t deepseek_compress_ratio;
+  uint32_t deepseek_index_topk;
+  uint32_t deepseek_index_n_heads;
+  uint32_t deepseek_index_head_dim;
+  uint32_t deepseek_router_num_groups;
+  uint32_t deepseek_router_topk_groups;
+  float deepseek_routed_scaling_factor;
+  float deepseek_hc_eps;
+  float deepseek_hc_post_alpha;
+  uint32_t deepseek_rope_scaling_type;
+  uint32_t deepseek_rope_original_max_position;
+  float deepseek_rope_scaling_factor;
+  float deepseek_rope_extrapolation_factor;
+  float deepseek_rope_attn_factor;
+  float deepseek_rope_beta_fast;
+  float deepseek_rope_beta_slow;
+  float deepseek_rope_mscale;
+  float deepseek_rope_mscale_all_dim;
+  float deepseek_compress_rope_theta;
+  float deepseek_swiglu_limit;
+} NervaCudaHfDecodeChainLayer;
+
+/* nerva_cuda_api.h:380-391 */
+typedef struct NervaCudaHfDecodeSequenceWeightBlock {
+  const uint16_t *host_source;
+  const char *source_file;
+  uint64_t source_file_len;
+  uint64_t file_offset_begin;
+  uint64_t block_id;
+  uint64_t block_version;
+  uint64_t offset_bytes;
+  uint64_t bytes;
+  uint32_t strategy;
+  uint32_t reserved;
+} NervaCudaHfDecodeSequenceWeightBlock;
+
+/* nerva_cuda_api.h:393-399 */
+typedef struct NervaCudaHfDecodeSamplerConfig {
+  float temperature;
+  float top_p;
+  uint32_t top_k;
+  uint32_t reserved;
+  uint64_t seed;
+} NervaCudaHfDecodeSamplerConfig;
+
+/* nerva_cuda_api.h:401-434 */
+typedef struct NervaCudaHfDecodeSequenceRequest {
+  uint32_t dtype;
+  uint32_t hidden;
+  uint32_t heads;
+  uint32_t kv_heads;
+  uint32_t head_dim;
+  uint32_t intermediate;
+  uint32_t vocab_size;
+  uint32_t layer_count;
+  uint32_t steps;
+  uint32_t seed_token;
+  const uint32_t *prompt_tokens;
+  uint32_t prompt_token_count;
+  uint32_t has_eos_token;
+  uint32_t eos_token;
+  float rms_eps;
+  float rope_theta;
+  const uint16_t *embeddings;
+  const NervaCudaHfDecodeChainLayer *layers;
+  const uint16_t *final_norm_weight;
+  const uint16_t *lm_head;
+  uint32_t planned_weight_blocks;
+  uint32_t planned_gpu_resident_blocks;
+  uint32_t planned_gpu_staged_blocks;
+  uint64_t planned_weight_bytes;
+  uint64_t planned_gpu_resident_weight_bytes;
+  uint64_t planned_gpu_staged_weight_bytes;
+  const NervaCudaHfDecodeSequenceWeightBlock *planned_weight_descriptors;
+  uint32_t planned_weight_descriptor_count;
+  uint64_t planned_weight_descriptor_hash;
+  uint32_t *output_tokens;
+  uint32_t output_token_capacity;
+  NervaCudaHfDecodeSamplerConfig sampler;
+} NervaCudaHfDecodeSequenceRequest;
+
+/* nerva_cuda_api.h:436-513 */
+typedef struct NervaCudaHfDecodeSequenceResult {
+  int32_t status;
+  int32_t cuda_error;
+  int32_t device_count;
+  uint32_t dtype;
+  uint32_t hidden;
+  uint32_t heads;
+  uint32_t kv_heads;
+  uint32_t head_dim;
+  uint32_t intermediate;
+  uint32_t vocab_size;
+  uint32_t layer_count;
+  uint32_t steps;
+  uint32_t seed_token;
+  uint32_t observed_tokens;
+  uint32_t last_token;
+  uint64_t observed_token_hash;
+  uint64_t resident_weight_bytes;
+  uint32_t planned_weight_blocks;
+  uint32_t planned_gpu_resident_blocks;
+  uint32_t planned_gpu_staged_blocks;
+  uint64_t planned_weight_bytes;
+  uint64_t planned_gpu_resident_weight_bytes;
+  uint64_t planned_gpu_staged_weight_bytes;
+  uint64_t descriptor_gpu_resident_h2d_bytes;
+  uint64_t descriptor_gpu_staged_h2d_bytes;
+  uint32_t planned_weight_descriptor_count;
+  uint64_t planned_weight_descriptor_hash;
+  uint64_t resident_kv_bytes;
+  uint64_t deepseek_mhc_residual_bytes;
+  uint64_t deepseek_mhc_post_mix_bytes;
+  uint64_t deepseek_mhc_comb_mix_bytes;
+  uint64_t kv_tokens;
+  uint64_t device_arena_bytes;
+  uint64_t pinned_host_bytes;
+  uint64_t h2d_bytes;
+  uint64_t d2h_bytes;
+  uint64_t graph_replays;
+  uint64_t graph_nodes;
+  uint64_t graph_launches;
+  uint64_t graph_captures;
+  uint64_t graph_cache_hits;
+  uint64_t kernel_launches;
+  uint64_t experimental_rt_selector_launches;
+  uint32_t experimental_rt_sparse_attention_active;
+  uint32_t experimental_rt_dense_attention_chunks;
+  uint32_t experimental_rt_attention_chunks;
+  uint32_t experimental_rt_reserved;
+  uint64_t device_elapsed_ns;
+  uint64_t projection_ns;
+  uint64_t qkv_projection_ns;
+  uint64_t attention_output_projection_ns;
+  uint64_t gate_up_projection_ns;
+  uint64_t down_projection_ns;
+  uint64_t lm_head_projection_ns;
+  uint64_t attention_ns;
+  uint64_t mlp_ns;
+  uint64_t norm_ns;
+  uint64_t sampling_ns;
+  uint64_t sync_calls;
+  uint64_t host_causality_edges;
+  uint64_t hot_path_allocations;
+  uint64_t deepseek_compressor_state_writes;
+  uint64_t deepseek_compressed_kv_writes;
+  uint64_t deepseek_indexer_state_writes;
+  uint64_t deepseek_indexer_kv_writes;
+  uint64_t deepseek_compressed_kv_attention_reads;
+  uint64_t deepseek_compressed_kv_attention_slots_scanned;
+  uint64_t deepseek_sparse_topk_selections;
+  uint64_t deepseek_sparse_topk_slots_selected;
+  uint64_t deepseek_sparse_topk_candidates_scored;
+  uint64_t deepseek_sparse_topk_selection_hash;
+  uint64_t deepseek_v3_grouped_router_selections;
+  uint64_t deepseek_v4_bias_router_selections;
+  uint64_t deepseek_v4_hash_router_selections;
+  uint64_t deepseek_raw_attention_tokens_scanned;
+  uint64_t deepseek_sparse_attention_output_hash;
+} NervaCudaHfDecodeSequenceResult;
+
+/* nerva_cuda_api.h:515-525 */
+typedef struct NervaCudaHfDecodeSequenceLayoutPlanRequest {
+  uint32_t hidden;
+  uint32_t heads;
+  uint32_t kv_heads;
+  uint32_t head_dim;
+  uint32_t intermediate;
+  uint32_t vocab_size;
+  uint32_t layer_count;
+  uint32_t layer_index;
+  const NervaCudaHfDecodeChainLayer *layers;
+} NervaCudaHfDecodeSequenceLayoutPlanRequest;
+
+/* nerva_cuda_api.h:527-602.  Offsets are in 16-bit arena elements;
+ * UINT64_MAX marks a tensor the layer does not have. */
+typedef struct NervaCudaHfDecodeSequenceLayoutPlanResult {
+  int32_t status;
+  uint32_t hidden;
+  uint32_t heads;
+  uint32_t kv_heads;
+  uint32_t head_dim;
+  uint32_t intermediate;
+  uint32_t vocab_size;
+  uint32_t layer_count;
+  uint32_t layer_index;
+  uint32_t attention_kind;
+  uint32_t deepseek_mode;
+  uint32_t deepseek_flags;
+  uint32_t deepseek_hc_mult;
+  uint32_t deepseek_hc_sinkhorn_iters;
+  uint32_t deepseek_qk_head_dim;
+  uint32_t deepseek_q_rows;
+  uint32_t deepseek_kv_cache_width;
+  uint32_t deepseek_kv_b_rows;
+  uint32_t deepseek_value_rows;
+  uint64_t resident_weight_bytes;
+  uint64_t layout_bytes;
+  uint64_t final_norm;
+  uint64_t lm_head;
+  uint64_t rms_attn;
+  uint64_t rms_mlp;
+  uint64_t w_q;
+  uint64_t q_norm;
+  uint64_t w_k;
+  uint64_t k_norm;
+  uint64_t w_v;
+  uint64_t w_o;
+  uint64_t w_router;
+  uint64_t w_expert_gate_up;
+  uint64_t w_expert_down;
+  uint64_t w_shared_expert_gate;
+  uint64_t w_shared_expert_up;
+  uint64_t w_shared_expert_down;
+  uint64_t deepseek_q_a_scale;
+  uint64_t deepseek_q_b;
+  uint64_t deepseek_q_b_scale;
+  uint64_t deepseek_kv_a_scale;
+  uint64_t deepseek_kv_b_scale;
+  uint64_t deepseek_o_a_scale;
+  uint64_t deepseek_o_b;
+  uint64_t deepseek_o_b_scale;
+  uint64_t deepseek_attention_sink;
+  uint64_t deepseek_indexer_q;
+  uint64_t deepseek_indexer_q_scale;
+  uint64_t deepseek_indexer_k;
+  uint64_t deepseek_indexer_k_scale;
+  uint64_t deepseek_indexer_k_norm;
+  uint64_t deepseek_indexer_k_norm_bias;
+  uint64_t deepseek_indexer_weights;
+  uint64_t deepseek_compressor_ape;
+  uint64_t deepseek_compressor_wkv;
+  uint64_t deepseek_compressor_wgate;
+  uint64_t deepseek_compressor_norm;
+  uint64_t deepseek_indexer_compressor_ape;
+  uint64_t deepseek_indexer_compressor_wkv;
+  uint64_t deepseek_indexer_compressor_wgate;
+  uint64_t deepseek_indexer_compressor_norm;
+  uint64_t deepseek_hc_head_base;
+  uint64_t deepseek_hc_head_fn;
+  uint64_t deepseek_hc_head_scale;
+  uint64_t deepseek_hc_attn_base;
+  uint64_t deepseek_hc_attn_fn;
+  uint64_t deepseek_hc_attn_scale;
+  uint64_t deepseek_hc_ffn_base;
+  uint64_t deepseek_hc_ffn_fn;
+  uint64_t deepseek_hc_ffn_scale;
+  float deepseek_hc_eps;
+  float deepseek_hc_post_alpha;
+  float deepseek_compress_rope_theta;
+  float deepseek_swiglu_limit;
+} NervaCudaHfDecodeSequenceLayoutPlanResult;
+
+/* nerva_cuda_api.h:604 */
+typedef struct NervaCudaHfDecodeSequenceSession NervaCudaHfDecodeSequenceSession;
+
+/* nerva_cuda_api.h:606-638 */
+typedef struct NervaCudaHfDecodeSequenceSessionCreateRequest {
+  uint32_t dtype;
+  uint32_t hidden;
+  uint32_t heads;
+  uint32_t kv_heads;
+  uint32_t head_dim;
+  uint32_t intermediate;
+  uint32_t vocab_size;
+  uint32_t layer_count;
+  uint32_t max_context_tokens;
+  float rms_eps;
+  float rope_theta;
+  const uint16_t *embeddings;
+  const NervaCudaHfDecodeChainLayer *layers;
+  const uint16_t *final_norm_weight;
+  const uint16_t *lm_head;
+  uint32_t planned_weight_blocks;
+  uint32_t planned_gpu_resident_blocks;
+  uint32_t planned_gpu_staged_blocks;
+  uint64_t planned_weight_bytes;
+  uint64_t planned_gpu_resident_weight_bytes;
+  uint64_t planned_gpu_staged_weight_bytes;
+  const NervaCudaHfDecodeSequenceWeightBlock *planned_weight_descriptors;
+  uint32_t planned_weight_descriptor_count;
+  uint64_t planned_weight_descriptor_hash;
+  uint32_t detailed_profile;
+  uint32_t experimental_rt_decode;
+  uint32_t experimental_rt_mode;
+  uint32_t experimental_rt_page_tokens;
+  uint32_t experimental_rt_pages;
+  uint32_t experimental_rt_local_window_tokens;
+  uint32_t experimental_rt_sink_tokens;
+} NervaCudaHfDecodeSequenceSessionCreateRequest;
+
+/* nerva_cuda_api.h:640-687 */
+typedef struct NervaCudaHfDecodeSequenceSessionCreateResult {
+  int32_t status;
+  int32_t cuda_error;
+  int32_t failure_stage;
+  int32_t device_count;
+  uint32_t dtype;
+  uint32_t hidden;
+  uint32_t heads;
+  uint32_t kv_heads;
+  uint32_t head_dim;
+  uint32_t intermediate;
+  uint32_t vocab_size;
+  uint32_t layer_count;
+  uint32_t max_context_tokens;
+  uint32_t prefill_chunk_tokens;
+  uint32_t head_threads;
+  uint64_t resident_weight_bytes;
+  uint32_t planned_weight_blocks;
+  uint32_t planned_gpu_resident_blocks;
+  uint32_t planned_gpu_staged_blocks;
+  uint64_t planned_weight_bytes;
+  uint64_t planned_gpu_resident_weight_bytes;
+  uint64_t planned_gpu_staged_weight_bytes;
+  uint64_t descriptor_gpu_resident_h2d_bytes;
+  uint64_t descriptor_gpu_staged_h2d_bytes;
+  uint32_t planned_weight_descriptor_count;
+  uint64_t planned_weight_descriptor_hash;
+  uint32_t experimental_rt_decode_requested;
+  uint32_t experimental_rt_decode_enabled;
+  uint32_t experimental_rt_mode;
+  uint32_t experimental_rt_page_tokens;
+  uint32_t experimental_rt_pages;
+  uint32_t experimental_rt_local_window_tokens;
+  uint32_t experimental_rt_sink_tokens;
+  uint32_t deepseek_v4_attention_aux_streams;
+  uint32_t deepseek_v4_attention_events;
+  uint64_t deepseek_v4_swa_kv_bytes;
+  uint64_t deepseek_mhc_residual_bytes;
+  uint64_t deepseek_mhc_post_mix_bytes;
+  uint64_t deepseek_mhc_comb_mix_bytes;
+  uint64_t resident_kv_bytes;
+  uint64_t device_arena_bytes;
+  uint64_t pinned_host_bytes;
+  uint64_t h2d_bytes;
+  uint64_t sync_calls;
+  uint64_t hot_path_allocations;
+  uint64_t device_memory_bandwidth_bps;
+} NervaCudaHfDecodeSequenceSessionCreateResult;
+
+/* nerva_cuda_api.h:689-692 */
+typedef struct NervaCudaHfDecodeSequenceSessionForkSharedWeightsRequest {
+  NervaCudaHfDecodeSequenceSession *parent;
+  uint32_t detailed_profile;
+} NervaCudaHfDecodeSequenceSessionForkSharedWeightsRequest;
+
+/* nerva_cuda_api.h:694-705 */
+typedef struct NervaCudaHfDecodeSequenceSessionRunRequest {
+  NervaCudaHfDecodeSequenceSession *session;
+  uint32_t steps;
+  uint32_t seed_token;
+  const uint32_t *prompt_tokens;
+  uint32_t prompt_token_count;
+  uint32_t has_eos_token;
+  uint32_t eos_token;
+  uint32_t *output_tokens;
+  uint32_t output_token_capacity;
+  NervaCudaHfDecodeSamplerConfig sampler;
+} NervaCudaHfDecodeSequenceSessionRunRequest;
+
+/* nerva_cuda_api.h:707-714 */
+typedef struct NervaCudaHfDecodeSequenceSessionStartRequest {
+  NervaCudaHfDecodeSequenceSession *session;
+  const uint32_t *prompt_tokens;
+  uint32_t prompt_token_count;
+  uint32_t has_eos_token;
+  uint32_t eos_token;
+  NervaCudaHfDecodeSamplerConfig sampler;
+} NervaCudaHfDecodeSequenceSessionStartRequest;
+
+/* nerva_cuda_api.h:716-721 */
+typedef struct NervaCudaHfDecodeSequenceSessionAdvanceRequest {
+  NervaCudaHfDecodeSequenceSession *session;
+  uint32_t steps;
+  uint32_t *output_tokens;
+  uint32_t output_token_capacity;
+} NervaCudaHfDecodeSequenceSessionAdvanceRequest;
+
+/* nerva_cuda_api.h:1075-1082 */
+typedef struct NervaCudaProjectionBenchRequest {
+  uint32_t dtype;
+  uint32_t rows;
+  uint32_t cols;
+  uint32_t iterations;
+  uint32_t warmup_iterations;
+  uint32_t block_tokens;
+} NervaCudaProjectionBenchRequest;
+
+/* nerva_cuda_api.h:1084-1144.  The `cublaslt_*` fields stay zero: this library
+ * links no BLAS.  `custom_*` describe the hand-written projection kernel. */
+typedef struct NervaCudaProjectionBenchResult {
+  int32_t status;
+  int32_t cuda_error;
+  int32_t device_count;
+  int32_t device_ordinal;
+  int32_t compute_capability_major;
+  int32_t compute_capability_minor;
+  uint32_t dtype;
+  uint32_t rows;
+  uint32_t cols;
+  uint32_t block_tokens;
+  uint32_t iterations;
+  uint32_t warmup_iterations;
+  uint64_t matrix_bytes;
+  uint64_t input_bytes;
+  uint64_t output_bytes;
+  uint64_t cublaslt_total_ns;
+  uint64_t cublaslt_avg_ns;
+  uint64_t cublaslt_default_total_ns;
+  uint64_t cublaslt_default_avg_ns;
+  uint32_t cublaslt_heuristic_count;
+  uint32_t cublaslt_best_heuristic_index;
+  uint64_t cublaslt_best_heuristic_total_ns;
+  uint64_t cublaslt_best_heuristic_avg_ns;
+  uint64_t custom_total_ns;
+  uint64_t custom_avg_ns;
+  uint64_t cublaslt_graph_total_ns;
+  uint64_t cublaslt_graph_avg_ns;
+  uint64_t cublaslt_default_graph_total_ns;
+  uint64_t cublaslt_default_graph_avg_ns;
+  uint64_t cublaslt_best_heuristic_graph_total_ns;
+  uint64_t cublaslt_best_heuristic_graph_avg_ns;
+  uint64_t custom_graph_total_ns;
+  uint64_t custom_graph_avg_ns;
+  uint64_t cublaslt_graph_nodes;
+  uint64_t custom_graph_nodes;
+  uint64_t graph_replays;
+  uint64_t graph_captures;
+  uint32_t selected_graph_strategy;
+  uint64_t cublaslt_effective_bandwidth_bps;
+  uint64_t custom_effective_bandwidth_bps;
+  uint32_t selected_strategy;
+  uint32_t mismatch_count;
+  float max_abs_diff;
+  uint64_t kernel_launches;
+  uint64_t sync_calls;
+  uint64_t device_allocations;
+  uint64_t device_frees;
+  uint64_t device_arena_bytes;
+  uint64_t hot_path_allocations;
+  uint64_t block_cublaslt_total_ns;
+  uint64_t block_cublaslt_avg_ns;
+  uint64_t block_cublaslt_per_token_ns;
+  uint64_t block_cublaslt_graph_total_ns;
+  uint64_t block_cublaslt_graph_avg_ns;
+  uint64_t block_cublaslt_graph_per_token_ns;
+  uint64_t block_cublaslt_graph_nodes;
+  uint64_t block_cublaslt_speedup_x1000;
+  uint64_t block_cublaslt_graph_speedup_x1000;
+  uint64_t block_cublaslt_effective_bandwidth_bps;
+} NervaCudaProjectionBenchResult;
+
+/* ---- resident decode session (the hot path) ---- */
+
+/* nerva_cuda_api.h:2160 */
+int nerva_cuda_hf_decode_sequence_plan_layout(
+    const NervaCudaHfDecodeSequenceLayoutPlanRequest *request,
+    NervaCudaHfDecodeSequenceLayoutPlanResult *out);
+/* nerva_cuda_api.h:2163 */
+int nerva_cuda_hf_decode_sequence_session_create(
+    const NervaCudaHfDecodeSequenceSessionCreateRequest *request,
+    NervaCudaHfDecodeSequenceSession **session,
+    NervaCudaHfDecodeSequenceSessionCreateResult *out);
+/* nerva_cuda_api.h:2167 */
+int nerva_cuda_hf_decode_sequence_session_run(
+    const NervaCudaHfDecodeSequenceSessionRunRequest *request,
+    NervaCudaHfDecodeSequenceResult *out);
+/* nerva_cuda_api.h:2170 */
+int nerva_cuda_hf_decode_sequence_session_start(
+    const NervaCudaHfDecodeSequenceSessionStartRequest *request,
+    NervaCudaHfDecodeSequenceResult *out);
+/* nerva_cuda_api.h:2173 */
+int nerva_cuda_hf_decode_sequence_session_advance(
+    const NervaCudaHfDecodeSequenceSessionAdvanceRequest *request,
+    NervaCudaHfDecodeSequenceResult *out);
+/* nerva_cuda_api.h:2212 */
+int nerva_cuda_hf_decode_sequence_session_fork_shared_weights(
+    const NervaCudaHfDecodeSequenceSessionForkSharedWeightsRequest *request,
+    NervaCudaHfDecodeSequenceSession **session,
+    NervaCudaHfDecodeSequenceSessionCreateResult *out);
+/* nerva_cuda_api.h:2216 */
+int nerva_cuda_hf_decode_sequence_session_destroy(NervaCudaHfDecodeSequenceSession *session);
+/* nerva_cuda_api.h:2157 — one-shot: create, run, destroy. */
+int nerva_cuda_hf_decode_sequence_u16(const NervaCudaHfDecodeSequenceRequest *request,
+                                      NervaCudaHfDecodeSequenceResult *out);
+/* nerva_cuda_api.h:2227 */
+int nerva_cuda_projection_bench(const NervaCudaProjectionBenchRequest *request,
+                                NervaCudaProjectionBenchResult *out);
+
+/* ---- additive entry points (no counterpart in the reference) ---- */
+
+/* Step engine of a session: 0 = one kernel per operator captured in a CUDA
+ * graph, 1 = the persistent whole-step kernel.  Must be called before
+ * session_start.  Returns 0, or -1 when the engine cannot run the model. */
+int nerva_b200_session_set_engine(NervaCudaHfDecodeSequenceSession *session, uint32_t engine);
+/* Copies the f32 logits of the most recent sampled step (vocab_size floats) to
+ * host memory.  Synchronises the session stream. */
+int nerva_b200_session_read_logits(NervaCudaHfDecodeSequenceSession *session, float *logits,
+                                   uint32_t capacity);
+/* Replaces the logical->physical KV page table (one uint32 per 16-token page,
+ * a permutation of 0..page_count-1).  Only legal before session_start. */
+int nerva_b200_session_set_kv_block_table(NervaCudaHfDecodeSequenceSession *session,
+                                          const uint32_t *table, uint32_t page_count);
+/* Reads the page table back (for page-table parity checks). */
+int nerva_b200_session_get_kv_block_table(NervaCudaHfDecodeSequenceSession *session,
+                                          uint32_t *table, uint32_t capacity);
+/* Copies one token's K or V row (kv_heads*head_dim 16-bit values) of one layer
+ * out of the paged cache. which: 0 = K, 1 = V. */
+int nerva_b200_session_read_kv_row(NervaCudaHfDecodeSequenceSession *session, uint32_t layer,
+                                   uint32_t token, uint32_t which, uint16_t *row,
+                                   uint32_t capacity);
+
+/* Isolated projection: y[m][n] = sum_k W[n][k] * x[m][k], bf16 in, fp32
+ * accumulate and out.  All pointers are HOST memory; the call copies in, runs
+ * `iterations` launches after `warmup` untimed ones, and copies y back.
+ * avg_ns (nullable) receives the mean device time per launch. */
+int nerva_b200_projection(const uint16_t *weight, const uint16_t *x, float *y, uint32_t rows,
+                          uint32_t cols, uint32_t tokens, uint32_t warmup, uint32_t iterations,
+                          uint64_t *avg_ns);
+
+/* Isolated GQA paged decode attention for `batch` sequences of `context`
+ * tokens each: q f32 [batch][heads*head_dim]; K/V pages bf16
+ * [batch][pages][16][kv_heads*head_dim]; page_table uint32 [batch][pages];
+ * out f32 [batch][heads*head_dim].  Host pointers. */
+int nerva_b200_gqa_decode_attention(const float *q, const uint16_t *key_pages,
+                                    const uint16_t *value_pages, const uint32_t *page_table,
+                                    float *out, uint32_t batch, uint32_t context, uint32_t heads,
+                                    uint32_t kv_heads, uint32_t head_dim, uint32_t warmup,
+                                    uint32_t iterations, uint64_t *avg_ns);
+
+/* Greedy argmax over f32 logits with the sampler's tie rule (lowest index,
+ * non-finite values skipped).  Host pointers. */
+int nerva_b200_greedy_argmax(const float *logits, uint32_t count, uint32_t *token);
+
+/* Fills host memory with the synthetic checkpoint generator of
+ * include/nerva_synth.h (multi-threaded; same bits as the header). */
+void nerva_b200_synth_normal_bf16(uint64_t seed, uint64_t tensor_id, uint64_t count, float std,
+                                  uint16_t *out);
+
+/* Last error text of the calling thread ("" when none). */
+const char *nerva_b200_last_error(void);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* NERVA_B200_API_H_ */

@@ -1,0 +1,118 @@
+// Host-callable launchers of the decode-step kernels.  All pointers are device
+// pointers; every launcher only enqueues work on `stream` (graph-capturable) and
+// returns cudaGetLastError().
+#pragma once
+
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "../../include/nerva_b200_api.h"
+
+namespace nb {
+
+// ---- projection (weight-streaming GEMV) ----
+enum ProjectionPrologue : uint32_t {
+  kProloguePlain = 0,     // x_bf16 is the activation vector
+  kPrologueAddNorm = 1,   // r = add_a + add_b + add_bias; x = bf16(rmsnorm(r) * norm_weight);
+                          // block 0 stores r to resid_out
+};
+enum ProjectionEpilogue : uint32_t {
+  kEpilogueStore = 0,     // out_f32[row] = y
+  kEpilogueSwiglu = 1,    // rows interleaved (gate, up): out_bf16[row/2] = bf16(silu(gate) * up)
+  kEpilogueArgmax = 2,    // out_f32[row] = y and per-block (best value, lowest index)
+};
+
+struct ProjectionParams {
+  const uint16_t *weight;  // [rows][cols] bf16 row-major
+  uint32_t rows, cols;
+  uint32_t prologue;
+  const uint16_t *x_bf16;       // kProloguePlain: the vector.  kPrologueAddNorm: `cols`
+                                // writable bf16 elements of scratch (used by the toy-shape path)
+  const float *add_a;           // kPrologueAddNorm (required)
+  const float *add_b;           // optional
+  const uint16_t *add_bias;     // optional bf16 vector
+  const uint16_t *norm_weight;  // bf16 [cols]
+  float eps;
+  float *resid_out;             // optional
+  uint32_t epilogue;
+  float *out_f32;
+  uint16_t *out_bf16;
+  float *best_value;     // [blocks] kEpilogueArgmax
+  uint32_t *best_index;  // [blocks]
+  uint32_t *error_word;
+};
+
+// Number of blocks launch_projection will use (= number of arg-max partials).
+uint32_t projection_blocks(const ProjectionParams &p, uint32_t sm_count);
+cudaError_t launch_projection(cudaStream_t stream, const ProjectionParams &p, uint32_t sm_count);
+cudaError_t configure_projection_kernels();
+
+// ---- token / position bookkeeping ----
+struct StepState {
+  uint32_t *cursor;                       // device step cursor (= position of the token being run)
+  const uint32_t *prompt;                 // device prompt ids
+  uint32_t prompt_count;
+  NervaCudaSyntheticTokenSlot *slots;     // device token ring
+  uint32_t max_context;
+  uint32_t vocab;
+  uint32_t *error_word;
+};
+
+// input[h] = embedding[token(cursor)][h] as f32.
+cudaError_t launch_embed(cudaStream_t stream, const StepState &st, const uint16_t *embeddings,
+                         uint32_t hidden, float *input);
+
+struct QkvPrepareParams {
+  float *qkv;  // [heads*d | kv_heads*d | kv_heads*d] f32, q is normalised/rotated in place
+  const uint16_t *q_bias, *k_bias, *v_bias;  // optional bf16
+  const uint16_t *q_norm, *k_norm;           // optional bf16 [head_dim]
+  uint32_t heads, kv_heads, head_dim;
+  float eps, rope_theta;
+  uint16_t *key_pages, *value_pages;  // this layer's pages: [pages][16][kv_hidden] bf16
+  const uint32_t *page_table;
+  uint32_t page_count;
+};
+cudaError_t launch_qkv_prepare(cudaStream_t stream, const StepState &st, const QkvPrepareParams &p);
+
+// ---- GQA paged split-KV decode attention ----
+struct AttentionParams {
+  const float *q;              // [batch][heads*d] f32 (already normalised / rotated)
+  const uint16_t *key_pages;   // [batch][pages][16][kv_hidden] bf16
+  const uint16_t *value_pages;
+  const uint32_t *page_table;  // [batch][pages]
+  uint32_t batch, heads, kv_heads, head_dim, page_count;
+  const uint32_t *cursor;      // context = *cursor + 1 when non-null ...
+  uint32_t context;            // ... else this
+  uint32_t splits;
+  float *partial_acc;          // [batch][heads][splits][d]
+  float *partial_m;            // [batch][heads][splits]
+  float *partial_l;
+  float *out_f32;              // [batch][heads*d] optional
+  uint16_t *out_bf16;          // optional
+  uint32_t *error_word;
+};
+cudaError_t launch_attention(cudaStream_t stream, const AttentionParams &p);
+cudaError_t configure_attention_kernels();
+uint32_t attention_default_splits(uint32_t context, uint32_t batch, uint32_t kv_heads,
+                                  uint32_t sm_count);
+
+// ---- greedy sampling ----
+// Reduces per-block (value, index) partials, writes the token slot at the
+// cursor and advances the cursor.  sample == 0: only advances the cursor.
+cudaError_t launch_sample_greedy(cudaStream_t stream, const StepState &st, const float *best_value,
+                                 const uint32_t *best_index, uint32_t partials, uint32_t sample);
+// Stand-alone argmax over logits (used by the per-op entry point).
+cudaError_t launch_argmax(cudaStream_t stream, const float *logits, uint32_t count,
+                          uint32_t *token_out);
+
+// ---- helpers ----
+cudaError_t launch_pack_qkv(cudaStream_t stream, const uint16_t *wq, const uint16_t *wk,
+                            const uint16_t *wv, uint16_t *packed, uint64_t q_elems,
+                            uint64_t kv_elems);
+cudaError_t launch_pack_gate_up(cudaStream_t stream, const uint16_t *gate, const uint16_t *up,
+                                uint16_t *packed, uint32_t intermediate, uint32_t hidden);
+cudaError_t launch_identity_table(cudaStream_t stream, uint32_t *table, uint32_t count);
+cudaError_t launch_fill_normal_bf16(cudaStream_t stream, uint16_t *out, uint64_t count,
+                                    uint64_t seed, uint64_t tensor_id, float std);
+
+}  // namespace nb

@@ -1,0 +1,380 @@
+// Per-operator C ABI: isolated projection (and the reference's projection bench
+// entry point), isolated GQA decode attention, greedy arg-max, and the host
+// synthetic-checkpoint generator.  Host pointers in, host pointers out.
+#include <math.h>
+#include <string.h>
+
+#include <vector>
+
+#include "../../include/nerva_synth.h"
+#include "kernels.cuh"
+#include "session.h"
+
+using namespace nb;
+
+namespace {
+
+struct DeviceBuffers {
+  std::vector<void *> ptrs;
+  ~DeviceBuffers() {
+    for (void *p : ptrs) cudaFree(p);
+  }
+  template <class T>
+  cudaError_t alloc(T **out, uint64_t count) {
+    void *p = nullptr;
+    const cudaError_t err = cudaMalloc(&p, (count == 0 ? 1 : count) * sizeof(T));
+    if (err == cudaSuccess) ptrs.push_back(p);
+    *out = static_cast<T *>(p);
+    return err;
+  }
+};
+
+struct Timing {
+  cudaEvent_t a = nullptr, b = nullptr;
+  ~Timing() {
+    if (a != nullptr) cudaEventDestroy(a);
+    if (b != nullptr) cudaEventDestroy(b);
+  }
+  cudaError_t init() {
+    cudaError_t err = cudaEventCreate(&a);
+    if (err == cudaSuccess) err = cudaEventCreate(&b);
+    return err;
+  }
+};
+
+cudaError_t device_sm_count(uint32_t *sms, int *major, int *minor, int *ordinal) {
+  int device = 0;
+  cudaError_t err = cudaGetDevice(&device);
+  cudaDeviceProp prop{};
+  if (err == cudaSuccess) err = cudaGetDeviceProperties(&prop, device);
+  if (err == cudaSuccess) {
+    *sms = static_cast<uint32_t>(prop.multiProcessorCount);
+    if (major != nullptr) *major = prop.major;
+    if (minor != nullptr) *minor = prop.minor;
+    if (ordinal != nullptr) *ordinal = device;
+  }
+  return err;
+}
+
+// L2 flush between timed launches: a write larger than the 126 MB L2.
+constexpr uint64_t kFlushBytes = 192ull << 20;
+
+}  // namespace
+
+extern "C" int nerva_b200_projection(const uint16_t *weight, const uint16_t *x, float *y,
+                                     uint32_t rows, uint32_t cols, uint32_t tokens,
+                                     uint32_t warmup, uint32_t iterations, uint64_t *avg_ns) {
+  set_last_error("");
+  if (weight == nullptr || x == nullptr || y == nullptr || rows == 0 || cols == 0 || tokens == 0) return -1;
+  uint32_t sms = 0;
+  cudaError_t err = device_sm_count(&sms, nullptr, nullptr, nullptr);
+  if (err == cudaSuccess) err = configure_projection_kernels();
+  DeviceBuffers buf;
+  Timing t;
+  uint16_t *d_w = nullptr, *d_x = nullptr;
+  float *d_y = nullptr;
+  uint8_t *d_flush = nullptr;
+  const uint64_t w_elems = static_cast<uint64_t>(rows) * cols;
+  if (err == cudaSuccess) err = buf.alloc(&d_w, w_elems);
+  if (err == cudaSuccess) err = buf.alloc(&d_x, static_cast<uint64_t>(tokens) * cols);
+  if (err == cudaSuccess) err = buf.alloc(&d_y, static_cast<uint64_t>(tokens) * rows);
+  if (err == cudaSuccess && iterations > 1) err = buf.alloc(&d_flush, kFlushBytes);
+  if (err == cudaSuccess) err = t.init();
+  if (err == cudaSuccess) err = cudaMemcpy(d_w, weight, w_elems * 2u, cudaMemcpyHostToDevice);
+  if (err == cudaSuccess)
+    err = cudaMemcpy(d_x, x, static_cast<uint64_t>(tokens) * cols * 2u, cudaMemcpyHostToDevice);
+  double total_ms = 0.0;
+  for (uint32_t it = 0; err == cudaSuccess && it < warmup + iterations; ++it) {
+    if (d_flush != nullptr) err = cudaMemsetAsync(d_flush, it & 0xff, kFlushBytes, nullptr);
+    if (err == cudaSuccess) err = cudaEventRecord(t.a, nullptr);
+    for (uint32_t m = 0; err == cudaSuccess && m < tokens; ++m) {
+      ProjectionParams p{};
+      p.weight = d_w;
+      p.rows = rows;
+      p.cols = cols;
+      p.prologue = kProloguePlain;
+      p.x_bf16 = d_x + static_cast<uint64_t>(m) * cols;
+      p.epilogue = kEpilogueStore;
+      p.out_f32 = d_y + static_cast<uint64_t>(m) * rows;
+      err = launch_projection(nullptr, p, sms);
+    }
+    if (err == cudaSuccess) err = cudaEventRecord(t.b, nullptr);
+    if (err == cudaSuccess) err = cudaEventSynchronize(t.b);
+    float ms = 0.0f;
+    if (err == cudaSuccess) err = cudaEventElapsedTime(&ms, t.a, t.b);
+    if (it >= warmup) total_ms += ms;
+  }
+  if (err == cudaSuccess)
+    err = cudaMemcpy(y, d_y, static_cast<uint64_t>(tokens) * rows * 4u, cudaMemcpyDeviceToHost);
+  if (err != cudaSuccess) {
+    set_last_error(cudaGetErrorString(err));
+    return -1;
+  }
+  if (avg_ns != nullptr) *avg_ns = iterations == 0 ? 0 : static_cast<uint64_t>(total_ms * 1.0e6 / iterations);
+  return 0;
+}
+
+// Reference: native/cuda/nerva_cuda_projection_bench.cu.  Same deterministic
+// inputs (((17 i + 13) mod 127) - 63) / 128 for the matrix and the vector
+// (:38-41,84-101).  `custom_*` time this library's projection kernel as single
+// launches and as graph replays; the `cublaslt_*` fields stay zero.
+extern "C" int nerva_cuda_projection_bench(const NervaCudaProjectionBenchRequest *request,
+                                           NervaCudaProjectionBenchResult *out) {
+  if (out == nullptr) return -1;
+  memset(out, 0, sizeof(*out));
+  out->status = -1;
+  if (request == nullptr || request->rows == 0 || request->cols == 0 || request->iterations == 0 ||
+      request->dtype > NERVA_DTYPE_BF16)
+    return -1;
+  set_last_error("");
+  int count = 0;
+  cudaError_t err = cudaGetDeviceCount(&count);
+  if (err != cudaSuccess || count == 0) {
+    out->cuda_error = static_cast<int32_t>(err != cudaSuccess ? err : cudaErrorNoDevice);
+    cudaGetLastError();
+    return -1;
+  }
+  out->device_count = count;
+  if (request->dtype != NERVA_DTYPE_BF16) {
+    out->cuda_error = static_cast<int32_t>(cudaErrorNotSupported);
+    return -1;
+  }
+  uint32_t sms = 0;
+  err = device_sm_count(&sms, &out->compute_capability_major, &out->compute_capability_minor,
+                        &out->device_ordinal);
+  if (err == cudaSuccess) err = configure_projection_kernels();
+  const uint32_t rows = request->rows, cols = request->cols;
+  const uint32_t tokens = request->block_tokens == 0 ? 1u : request->block_tokens;
+  out->dtype = request->dtype;
+  out->rows = rows;
+  out->cols = cols;
+  out->block_tokens = request->block_tokens;
+  out->iterations = request->iterations;
+  out->warmup_iterations = request->warmup_iterations;
+  const uint64_t w_elems = static_cast<uint64_t>(rows) * cols;
+  out->matrix_bytes = w_elems * 2u;
+  out->input_bytes = static_cast<uint64_t>(cols) * 2u;
+  out->output_bytes = static_cast<uint64_t>(rows) * 4u;
+
+  auto value_at = [](uint64_t i) { return (static_cast<float>((17u * i + 13u) % 127u) - 63.0f) / 128.0f; };
+  std::vector<uint16_t> h_w(w_elems), h_x(cols);
+  for (uint64_t i = 0; i < w_elems; ++i) h_w[i] = nerva_synth_f32_to_bf16(value_at(i));
+  for (uint32_t i = 0; i < cols; ++i) h_x[i] = nerva_synth_f32_to_bf16(value_at(i));
+
+  DeviceBuffers buf;
+  Timing t;
+  uint16_t *d_w = nullptr, *d_x = nullptr;
+  float *d_y = nullptr;
+  if (err == cudaSuccess) err = buf.alloc(&d_w, w_elems);
+  if (err == cudaSuccess) err = buf.alloc(&d_x, static_cast<uint64_t>(cols));
+  if (err == cudaSuccess) err = buf.alloc(&d_y, static_cast<uint64_t>(rows));
+  out->device_allocations = 3;
+  out->device_arena_bytes = w_elems * 2u + cols * 2u + rows * 4u;
+  if (err == cudaSuccess) err = t.init();
+  cudaStream_t stream = nullptr;
+  if (err == cudaSuccess) err = cudaStreamCreateWithFlags(&stream, cudaStreamNonBlocking);
+  if (err == cudaSuccess) err = cudaMemcpy(d_w, h_w.data(), w_elems * 2u, cudaMemcpyHostToDevice);
+  if (err == cudaSuccess) err = cudaMemcpy(d_x, h_x.data(), cols * 2u, cudaMemcpyHostToDevice);
+  ProjectionParams p{};
+  p.weight = d_w;
+  p.rows = rows;
+  p.cols = cols;
+  p.prologue = kProloguePlain;
+  p.x_bf16 = d_x;
+  p.epilogue = kEpilogueStore;
+  p.out_f32 = d_y;
+  // stream launches
+  for (uint32_t i = 0; err == cudaSuccess && i < request->warmup_iterations; ++i)
+    err = launch_projection(stream, p, sms);
+  if (err == cudaSuccess) err = cudaEventRecord(t.a, stream);
+  for (uint32_t i = 0; err == cudaSuccess && i < request->iterations * tokens; ++i) {
+    err = launch_projection(stream, p, sms);
+    out->kernel_launches += 1;
+  }
+  if (err == cudaSuccess) err = cudaEventRecord(t.b, stream);
+  if (err == cudaSuccess) err = cudaEventSynchronize(t.b);
+  out->sync_calls += 1;
+  float ms = 0.0f;
+  if (err == cudaSuccess) err = cudaEventElapsedTime(&ms, t.a, t.b);
+  out->custom_total_ns = static_cast<uint64_t>(ms * 1.0e6f);
+  out->custom_avg_ns = out->custom_total_ns / (static_cast<uint64_t>(request->iterations) * tokens);
+  // graph replays
+  cudaGraph_t graph = nullptr;
+  cudaGraphExec_t exec = nullptr;
+  if (err == cudaSuccess) err = cudaStreamBeginCapture(stream, cudaStreamCaptureModeThreadLocal);
+  if (err == cudaSuccess) {
+    for (uint32_t m = 0; err == cudaSuccess && m < tokens; ++m) err = launch_projection(stream, p, sms);
+    const cudaError_t end_err = cudaStreamEndCapture(stream, &graph);
+    if (err == cudaSuccess) err = end_err;
+  }
+  if (err == cudaSuccess) err = cudaGraphInstantiate(&exec, graph, 0);
+  if (err == cudaSuccess) {
+    size_t nodes = 0;
+    cudaGraphGetNodes(graph, nullptr, &nodes);
+    out->custom_graph_nodes = nodes;
+    out->graph_captures = 1;
+  }
+  for (uint32_t i = 0; err == cudaSuccess && i < request->warmup_iterations; ++i)
+    err = cudaGraphLaunch(exec, stream);
+  if (err == cudaSuccess) err = cudaEventRecord(t.a, stream);
+  for (uint32_t i = 0; err == cudaSuccess && i < request->iterations; ++i) {
+    err = cudaGraphLaunch(exec, stream);
+    out->graph_replays += 1;
+  }
+  if (err == cudaSuccess) err = cudaEventRecord(t.b, stream);
+  if (err == cudaSuccess) err = cudaEventSynchronize(t.b);
+  out->sync_calls += 1;
+  if (err == cudaSuccess) err = cudaEventElapsedTime(&ms, t.a, t.b);
+  out->custom_graph_total_ns = static_cast<uint64_t>(ms * 1.0e6f);
+  out->custom_graph_avg_ns = out->custom_graph_total_ns / request->iterations;
+  if (out->custom_graph_avg_ns != 0) {
+    const uint64_t bytes = tokens * (out->matrix_bytes + out->input_bytes + out->output_bytes);
+    out->custom_effective_bandwidth_bps = bytes * 1000000000ull / out->custom_graph_avg_ns;
+  }
+  // check against an fp64 host dot product of the same bf16 inputs on a row sample
+  std::vector<float> h_y(rows);
+  if (err == cudaSuccess) err = cudaMemcpy(h_y.data(), d_y, rows * 4u, cudaMemcpyDeviceToHost);
+  if (err == cudaSuccess) {
+    const uint32_t stride = rows > 4096 ? rows / 4096 : 1;
+    for (uint32_t r = 0; r < rows; r += stride) {
+      double acc = 0.0;
+      for (uint32_t k = 0; k < cols; ++k) {
+        const float w = __builtin_bit_cast(float, static_cast<uint32_t>(h_w[static_cast<uint64_t>(r) * cols + k]) << 16);
+        const float xv = __builtin_bit_cast(float, static_cast<uint32_t>(h_x[k]) << 16);
+        acc += static_cast<double>(w) * xv;
+      }
+      const float diff = fabsf(h_y[r] - static_cast<float>(acc));
+      if (diff > out->max_abs_diff) out->max_abs_diff = diff;
+      if (diff > 0.25f) out->mismatch_count += 1;  // the reference's tolerance (:843-845)
+    }
+  }
+  if (exec != nullptr) cudaGraphExecDestroy(exec);
+  if (graph != nullptr) cudaGraphDestroy(graph);
+  if (stream != nullptr) cudaStreamDestroy(stream);
+  out->device_frees = 3;
+  out->selected_strategy = 1;        // custom kernel
+  out->selected_graph_strategy = 1;
+  out->hot_path_allocations = 0;
+  if (err != cudaSuccess) {
+    out->cuda_error = static_cast<int32_t>(err);
+    set_last_error(cudaGetErrorString(err));
+    return -1;
+  }
+  out->status = out->mismatch_count == 0 ? 0 : -1;
+  return out->status;
+}
+
+extern "C" int nerva_b200_gqa_decode_attention(const float *q, const uint16_t *key_pages,
+                                               const uint16_t *value_pages,
+                                               const uint32_t *page_table, float *out,
+                                               uint32_t batch, uint32_t context, uint32_t heads,
+                                               uint32_t kv_heads, uint32_t head_dim,
+                                               uint32_t warmup, uint32_t iterations,
+                                               uint64_t *avg_ns) {
+  set_last_error("");
+  if (q == nullptr || key_pages == nullptr || value_pages == nullptr || page_table == nullptr ||
+      out == nullptr || batch == 0 || context == 0 || heads == 0 || kv_heads == 0 ||
+      heads % kv_heads != 0 || head_dim == 0 || head_dim > 256)
+    return -1;
+  uint32_t sms = 0;
+  cudaError_t err = device_sm_count(&sms, nullptr, nullptr, nullptr);
+  if (err == cudaSuccess) err = configure_attention_kernels();
+  const uint32_t pages = (context + NERVA_KV_CACHE_BLOCK_TOKENS - 1) / NERVA_KV_CACHE_BLOCK_TOKENS;
+  const uint64_t kv_hidden = static_cast<uint64_t>(kv_heads) * head_dim;
+  const uint64_t kv_elems = static_cast<uint64_t>(batch) * pages * NERVA_KV_CACHE_BLOCK_TOKENS * kv_hidden;
+  const uint64_t q_elems = static_cast<uint64_t>(batch) * heads * head_dim;
+  const uint32_t splits = attention_default_splits(context, batch, kv_heads, sms);
+  DeviceBuffers buf;
+  Timing t;
+  AttentionParams p{};
+  float *d_q = nullptr, *d_out = nullptr, *d_acc = nullptr, *d_m = nullptr, *d_l = nullptr;
+  uint16_t *d_k = nullptr, *d_v = nullptr;
+  uint32_t *d_table = nullptr, *d_err = nullptr;
+  uint8_t *d_flush = nullptr;
+  if (err == cudaSuccess) err = buf.alloc(&d_q, q_elems);
+  if (err == cudaSuccess) err = buf.alloc(&d_out, q_elems);
+  if (err == cudaSuccess) err = buf.alloc(&d_k, kv_elems);
+  if (err == cudaSuccess) err = buf.alloc(&d_v, kv_elems);
+  if (err == cudaSuccess) err = buf.alloc(&d_table, static_cast<uint64_t>(batch) * pages);
+  if (err == cudaSuccess) err = buf.alloc(&d_acc, q_elems * splits);
+  if (err == cudaSuccess) err = buf.alloc(&d_m, static_cast<uint64_t>(batch) * heads * splits);
+  if (err == cudaSuccess) err = buf.alloc(&d_l, static_cast<uint64_t>(batch) * heads * splits);
+  if (err == cudaSuccess) err = buf.alloc(&d_err, uint64_t{1});
+  if (err == cudaSuccess && iterations > 1) err = buf.alloc(&d_flush, kFlushBytes);
+  if (err == cudaSuccess) err = t.init();
+  if (err == cudaSuccess) err = cudaMemset(d_err, 0, 4);
+  if (err == cudaSuccess) err = cudaMemcpy(d_q, q, q_elems * 4u, cudaMemcpyHostToDevice);
+  if (err == cudaSuccess) err = cudaMemcpy(d_k, key_pages, kv_elems * 2u, cudaMemcpyHostToDevice);
+  if (err == cudaSuccess) err = cudaMemcpy(d_v, value_pages, kv_elems * 2u, cudaMemcpyHostToDevice);
+  if (err == cudaSuccess)
+    err = cudaMemcpy(d_table, page_table, static_cast<uint64_t>(batch) * pages * 4u, cudaMemcpyHostToDevice);
+  p.q = d_q;
+  p.key_pages = d_k;
+  p.value_pages = d_v;
+  p.page_table = d_table;
+  p.batch = batch;
+  p.heads = heads;
+  p.kv_heads = kv_heads;
+  p.head_dim = head_dim;
+  p.page_count = pages;
+  p.cursor = nullptr;
+  p.context = context;
+  p.splits = splits;
+  p.partial_acc = d_acc;
+  p.partial_m = d_m;
+  p.partial_l = d_l;
+  p.out_f32 = d_out;
+  p.error_word = d_err;
+  double total_ms = 0.0;
+  for (uint32_t it = 0; err == cudaSuccess && it < warmup + iterations; ++it) {
+    if (d_flush != nullptr) err = cudaMemsetAsync(d_flush, it & 0xff, kFlushBytes, nullptr);
+    if (err == cudaSuccess) err = cudaEventRecord(t.a, nullptr);
+    if (err == cudaSuccess) err = launch_attention(nullptr, p);
+    if (err == cudaSuccess) err = cudaEventRecord(t.b, nullptr);
+    if (err == cudaSuccess) err = cudaEventSynchronize(t.b);
+    float ms = 0.0f;
+    if (err == cudaSuccess) err = cudaEventElapsedTime(&ms, t.a, t.b);
+    if (it >= warmup) total_ms += ms;
+  }
+  uint32_t device_error = 0;
+  if (err == cudaSuccess) err = cudaMemcpy(&device_error, d_err, 4, cudaMemcpyDeviceToHost);
+  if (err == cudaSuccess) err = cudaMemcpy(out, d_out, q_elems * 4u, cudaMemcpyDeviceToHost);
+  if (err != cudaSuccess) {
+    set_last_error(cudaGetErrorString(err));
+    return -1;
+  }
+  if (device_error != 0) {
+    set_last_error("attention kernel reported a page index outside the page table");
+    return -1;
+  }
+  if (avg_ns != nullptr) *avg_ns = iterations == 0 ? 0 : static_cast<uint64_t>(total_ms * 1.0e6 / iterations);
+  return 0;
+}
+
+extern "C" int nerva_b200_greedy_argmax(const float *logits, uint32_t count, uint32_t *token) {
+  set_last_error("");
+  if (logits == nullptr || token == nullptr || count == 0) return -1;
+  DeviceBuffers buf;
+  float *d_logits = nullptr;
+  uint32_t *d_token = nullptr;
+  cudaError_t err = buf.alloc(&d_logits, static_cast<uint64_t>(count));
+  if (err == cudaSuccess) err = buf.alloc(&d_token, uint64_t{1});
+  if (err == cudaSuccess) err = cudaMemcpy(d_logits, logits, static_cast<uint64_t>(count) * 4u, cudaMemcpyHostToDevice);
+  if (err == cudaSuccess) err = launch_argmax(nullptr, d_logits, count, d_token);
+  if (err == cudaSuccess) err = cudaMemcpy(token, d_token, 4, cudaMemcpyDeviceToHost);
+  if (err != cudaSuccess) {
+    set_last_error(cudaGetErrorString(err));
+    return -1;
+  }
+  return 0;
+}
+
+extern "C" void nerva_b200_synth_normal_bf16(uint64_t seed, uint64_t tensor_id, uint64_t count,
+                                             float std, uint16_t *out) {
+  const uint64_t key = nerva_synth_key(seed, tensor_id);
+  const float scale = std * (1.0f / 65536.0f);
+#pragma omp parallel for schedule(static)
+  for (int64_t i = 0; i < static_cast<int64_t>(count); ++i) {
+    out[i] = nerva_synth_normal_bf16(key, static_cast<uint64_t>(i), scale);
+  }
+}

@@ -1,0 +1,1494 @@
+// C ABI of the resident decode session: create / start / advance / run / fork /
+// destroy / plan_layout / one-shot.  Entry-point names, argument structs,
+// validation rules and result accounting follow the reference
+// (hf_decode_sequence/session_api_lifecycle.inc.cu, weights.cu); the engine
+// underneath is this library's own.
+#include "session.h"
+
+#include <math.h>
+#include <stdio.h>
+#include <string.h>
+
+#include <algorithm>
+#include <new>
+
+namespace nb {
+
+// ---------------------------------------------------------------- errors ----
+static thread_local std::string g_last_error;
+void set_last_error(const std::string &text) { g_last_error = text; }
+
+// Reference create-failure stages that still apply
+// (hf_decode_sequence/session_prelude.inc.cu:1-40).
+enum CreateStage : int32_t {
+  kStageNone = 0,
+  kStageInvalidRequest = 1,
+  kStageGetDeviceCount = 2,
+  kStageSetDevice = 3,
+  kStageSessionAlloc = 4,
+  kStageHostSlotsAlloc = 6,
+  kStageDeviceArenaAlloc = 7,
+  kStageDeviceScratchAlloc = 9,
+  kStageStreamCreate = 19,
+  kStageStartEventCreate = 23,
+  kStageStopEventCreate = 24,
+  kStageDescriptorCopy = 25,
+  kStagePackReplicas = 27,
+  kStageSetupSynchronize = 29,
+};
+
+// ------------------------------------------------------------ validation ----
+// hf_decode_sequence/weights.cu:168-230.
+bool valid_layer(const NervaCudaHfDecodeChainLayer &layer, bool require_sources) {
+  const bool dense = layer.mlp_kind == NERVA_MLP_KIND_DENSE;
+  const bool sparse = layer.mlp_kind == NERVA_MLP_KIND_SPARSE_MOE;
+  if (!dense && !sparse) return false;
+  if (layer.attention_kind == NERVA_ATTENTION_KIND_LINEAR_GDN) {
+    if (layer.linear_key_heads == 0 || layer.linear_value_heads == 0 ||
+        layer.linear_key_head_dim == 0 || layer.linear_value_head_dim == 0 ||
+        layer.linear_conv_kernel == 0)
+      return false;
+  } else if (layer.attention_kind == NERVA_ATTENTION_KIND_DEEPSEEK_MLA) {
+    if (layer.deepseek_kv_lora_rank == 0 || layer.deepseek_qk_rope_head_dim == 0) return false;
+  } else if (layer.attention_kind != NERVA_ATTENTION_KIND_FULL) {
+    return false;
+  }
+  if (sparse && (layer.moe_intermediate == 0 || layer.num_experts == 0 ||
+                 layer.experts_per_token == 0 || layer.experts_per_token > layer.num_experts ||
+                 layer.num_experts > 256u || layer.experts_per_token > 16u))
+    return false;
+  if (!require_sources) return true;
+  if (layer.rms_attn_weight == nullptr || layer.rms_mlp_weight == nullptr) return false;
+  if (layer.attention_kind != NERVA_ATTENTION_KIND_FULL) return false;
+  if (layer.w_q == nullptr || layer.w_k == nullptr || layer.w_v == nullptr || layer.w_o == nullptr)
+    return false;
+  if (dense) return layer.w_gate != nullptr && layer.w_up != nullptr && layer.w_down != nullptr;
+  if (layer.w_router == nullptr || layer.w_expert_gate_up == nullptr ||
+      layer.w_expert_down == nullptr)
+    return false;
+  if (layer.shared_expert_intermediate != 0 &&
+      (layer.w_shared_expert_gate == nullptr || layer.w_shared_expert_up == nullptr ||
+       layer.w_shared_expert_down == nullptr || layer.w_shared_expert_router == nullptr))
+    return false;
+  return true;
+}
+
+// What this library's kernels run: full attention, no query gate, dense SwiGLU.
+bool layer_supported(const NervaCudaHfDecodeChainLayer &layer) {
+  return layer.attention_kind == NERVA_ATTENTION_KIND_FULL && layer.w_q_gate == nullptr &&
+         layer.mlp_kind == NERVA_MLP_KIND_DENSE;
+}
+
+static bool sampler_valid(const NervaCudaHfDecodeSamplerConfig &s) {
+  return isfinite(s.temperature) && s.temperature >= 0.0f && isfinite(s.top_p) && s.top_p > 0.0f &&
+         s.top_p <= 1.0f;
+}
+static bool sampler_greedy(const NervaCudaHfDecodeSamplerConfig &s) {
+  return !(s.temperature > 0.0f) || s.top_k == 1;  // sampler.cu:88
+}
+
+// ---------------------------------------------------------------- layout ----
+static uint64_t push(uint64_t &cursor, uint64_t len) {
+  const uint64_t offset = cursor;
+  cursor += len;
+  return offset;
+}
+static uint64_t push_optional(uint64_t &cursor, uint64_t len, const void *ptr) {
+  return ptr == nullptr ? kMissingOffset : push(cursor, len);
+}
+
+// hf_decode_sequence/weights.cu:487-591 (full-attention layers) and
+// session_api_lifecycle.inc.cu:124-146 (arena order).
+ArenaLayout compute_arena_layout(const ModelDims &d, const NervaCudaHfDecodeChainLayer *layers) {
+  ArenaLayout out;
+  const uint64_t hidden = d.hidden, ah = d.attention_hidden(), kvh = d.kv_hidden();
+  const uint64_t inter = d.intermediate;
+  uint64_t c = 0;
+  out.embeddings = push(c, static_cast<uint64_t>(d.vocab) * hidden);
+  out.input = push(c, hidden);
+  out.scratch = push(c, hidden);
+  out.layers.resize(d.layers);
+  for (uint32_t i = 0; i < d.layers; ++i) {
+    const NervaCudaHfDecodeChainLayer &layer = layers[i];
+    LayerLayout &l = out.layers[i];
+    l.mlp_kind = layer.mlp_kind;
+    l.moe_intermediate = layer.moe_intermediate;
+    l.shared_intermediate = layer.shared_expert_intermediate;
+    l.num_experts = layer.num_experts;
+    l.top_k = layer.experts_per_token;
+    l.norm_topk_prob = layer.norm_topk_prob == 0 ? 0u : 1u;
+    l.rms_attn = push(c, hidden);
+    l.w_q = push(c, ah * hidden);
+    l.w_q_gate = push_optional(c, ah * hidden, layer.w_q_gate);
+    l.q_norm = push_optional(c, d.head_dim, layer.q_norm_weight);
+    l.w_k = push(c, kvh * hidden);
+    l.k_norm = push_optional(c, d.head_dim, layer.k_norm_weight);
+    l.w_v = push(c, kvh * hidden);
+    l.w_o = push(c, hidden * ah);
+    l.rms_mlp = push(c, hidden);
+    if (layer.mlp_kind == NERVA_MLP_KIND_SPARSE_MOE) {
+      const uint64_t mi = layer.moe_intermediate, e = layer.num_experts;
+      const uint64_t si = layer.shared_expert_intermediate;
+      l.w_router = push(c, e * hidden);
+      l.w_expert_gate_up = push(c, e * mi * 2u * hidden);
+      l.w_expert_down = push(c, e * hidden * mi);
+      if (si != 0) {
+        l.w_shared_gate = push(c, si * hidden);
+        l.w_shared_up = push(c, si * hidden);
+        l.w_shared_down = push(c, hidden * si);
+        l.w_shared_router = push(c, hidden);
+      }
+    } else {
+      l.w_gate = push(c, inter * hidden);
+      l.w_up = push(c, inter * hidden);
+      l.w_down = push(c, hidden * inter);
+    }
+    l.q_bias = push_optional(c, ah, layer.q_bias);
+    l.k_bias = push_optional(c, kvh, layer.k_bias);
+    l.v_bias = push_optional(c, kvh, layer.v_bias);
+    l.o_bias = push_optional(c, hidden, layer.o_bias);
+  }
+  out.final_norm = push(c, hidden);
+  out.lm_head = push(c, static_cast<uint64_t>(d.vocab) * hidden);
+  out.elements = c;
+  return out;
+}
+
+// ---------------------------------------------------------------- hashes ----
+constexpr uint64_t kFnvOffset = 0xcbf29ce484222325ull;
+constexpr uint64_t kFnvPrime = 0x00000100000001b3ull;
+static void fnv_bytes(uint64_t &h, uint64_t v, uint32_t n) {
+  for (uint32_t b = 0; b < n; ++b) {
+    h ^= (v >> (8u * b)) & 0xffu;
+    h *= kFnvPrime;
+  }
+}
+// hf_decode_sequence/weights.cu:78-88
+uint64_t hash_tokens(const uint32_t *tokens, uint32_t count) {
+  uint64_t h = kFnvOffset;
+  for (uint32_t i = 0; i < count; ++i) fnv_bytes(h, tokens[i], 4);
+  return h;
+}
+// hf_decode_sequence/weights.cu:104-111
+uint64_t hash_weight_descriptors(const NervaCudaHfDecodeSequenceWeightBlock *blocks, uint32_t n) {
+  uint64_t h = kFnvOffset;
+  for (uint32_t i = 0; i < n; ++i) {
+    fnv_bytes(h, blocks[i].block_id, 8);
+    fnv_bytes(h, blocks[i].block_version, 8);
+    fnv_bytes(h, blocks[i].offset_bytes, 8);
+    fnv_bytes(h, blocks[i].bytes, 8);
+    fnv_bytes(h, blocks[i].strategy, 4);
+  }
+  return h;
+}
+
+}  // namespace nb
+
+using namespace nb;
+typedef NervaCudaHfDecodeSequenceSession Session;
+
+namespace {
+
+template <class T>
+bool carve(StaticArena &arena, void *base, uint64_t count, T **out) {
+  ArenaRegion region;
+  if (!arena.reserve(count * sizeof(T), 256, AllocationPhase::Initialization, &region)) return false;
+  if (base != nullptr) *out = reinterpret_cast<T *>(static_cast<uint8_t *>(base) + region.offset);
+  return true;
+}
+
+// Carves the shared weight block.  base == nullptr: sizing pass.
+bool plan_weights(Session *s, StaticArena &arena, void *base, SharedWeights *w) {
+  const ModelDims &d = s->dims;
+  const uint64_t qkv_rows = d.attention_hidden() + 2 * d.kv_hidden();
+  uint16_t *arena_ptr = nullptr, *qkv = nullptr, *gu = nullptr;
+  bool ok = carve(arena, base, s->layout.elements, &arena_ptr);
+  ok = ok && carve(arena, base, static_cast<uint64_t>(d.layers) * qkv_rows * d.hidden, &qkv);
+  ok = ok && carve(arena, base, static_cast<uint64_t>(d.layers) * 2u * d.intermediate * d.hidden, &gu);
+  if (ok && w != nullptr) {
+    w->arena = arena_ptr;
+    w->qkv_packed = qkv;
+    w->gate_up_packed = gu;
+  }
+  return ok;
+}
+
+// Carves the private state block.  base == nullptr: sizing pass.
+bool plan_state(Session *s, StaticArena &arena, void *base) {
+  const ModelDims &d = s->dims;
+  const uint64_t ah = d.attention_hidden(), kvh = d.kv_hidden();
+  s->kv_pages = (s->max_context + NERVA_KV_CACHE_BLOCK_TOKENS - 1) / NERVA_KV_CACHE_BLOCK_TOKENS;
+  s->kv_layer_elems = static_cast<uint64_t>(s->kv_pages) * NERVA_KV_CACHE_BLOCK_TOKENS * kvh;
+  s->max_splits = attention_default_splits(s->max_context, 1, d.kv_heads, s->sm_count);
+  const uint64_t max_x = std::max<uint64_t>(std::max<uint64_t>(d.hidden, d.intermediate), ah);
+  bool ok = carve(arena, base, d.layers * s->kv_layer_elems, &s->kv_keys);
+  ok = ok && carve(arena, base, d.layers * s->kv_layer_elems, &s->kv_values);
+  ok = ok && carve(arena, base, static_cast<uint64_t>(s->kv_pages), &s->page_table);
+  ok = ok && carve(arena, base, static_cast<uint64_t>(d.hidden), &s->h_a);
+  ok = ok && carve(arena, base, static_cast<uint64_t>(d.hidden), &s->h_b);
+  ok = ok && carve(arena, base, ah + 2 * kvh, &s->qkv);
+  ok = ok && carve(arena, base, static_cast<uint64_t>(d.hidden), &s->o_out);
+  ok = ok && carve(arena, base, static_cast<uint64_t>(d.hidden), &s->down);
+  ok = ok && carve(arena, base, static_cast<uint64_t>(d.vocab), &s->logits);
+  ok = ok && carve(arena, base, static_cast<uint64_t>(d.heads) * s->max_splits * d.head_dim, &s->partial_acc);
+  ok = ok && carve(arena, base, static_cast<uint64_t>(d.heads) * s->max_splits, &s->partial_m);
+  ok = ok && carve(arena, base, static_cast<uint64_t>(d.heads) * s->max_splits, &s->partial_l);
+  ok = ok && carve(arena, base, ah, &s->attn_bf16);
+  ok = ok && carve(arena, base, static_cast<uint64_t>(d.intermediate), &s->ff_bf16);
+  ok = ok && carve(arena, base, max_x, &s->x_scratch);
+  ok = ok && carve(arena, base, static_cast<uint64_t>(s->sm_count), &s->best_value);
+  ok = ok && carve(arena, base, static_cast<uint64_t>(s->sm_count), &s->best_index);
+  ok = ok && carve(arena, base, static_cast<uint64_t>(s->max_context), &s->device_slots);
+  ok = ok && carve(arena, base, static_cast<uint64_t>(s->max_context), &s->device_prompt);
+  ok = ok && carve(arena, base, uint64_t{4}, &s->device_cursor);
+  ok = ok && carve(arena, base, uint64_t{4}, &s->device_error);
+  return ok;
+}
+
+void destroy_graphs(Session *s) {
+  for (GraphEntry &g : s->graphs) {
+    if (g.exec != nullptr) cudaGraphExecDestroy(g.exec);
+    if (g.graph != nullptr) cudaGraphDestroy(g.graph);
+  }
+  s->graphs.clear();
+}
+
+void destroy_session(Session *s) {
+  if (s == nullptr) return;
+  if (s->stream != nullptr) cudaStreamSynchronize(s->stream);
+  destroy_graphs(s);
+  if (s->ev_start != nullptr) cudaEventDestroy(s->ev_start);
+  if (s->ev_stop != nullptr) cudaEventDestroy(s->ev_stop);
+  if (s->stream != nullptr) cudaStreamDestroy(s->stream);
+  if (s->host_slots != nullptr) cudaFreeHost(s->host_slots);
+  if (s->host_error != nullptr) cudaFreeHost(s->host_error);
+  if (s->state_block != nullptr) cudaFree(s->state_block);
+  delete s;
+}
+
+StepState step_state(Session *s) {
+  StepState st;
+  st.cursor = s->device_cursor;
+  st.prompt = s->device_prompt;
+  st.prompt_count = s->prompt_count;
+  st.slots = s->device_slots;
+  st.max_context = s->max_context;
+  st.vocab = s->dims.vocab;
+  st.error_word = s->device_error;
+  return st;
+}
+
+const uint16_t *arena_at(Session *s, uint64_t offset) {
+  return offset == kMissingOffset ? nullptr : s->weights->arena + offset;
+}
+
+// One decode step as a sequence of kernels (engine 0).  Per layer:
+//   QKV projection (residual add + RMSNorm fused in front)
+//   q/k norm + RoPE + KV append, split-KV attention, merge
+//   O projection
+//   gate/up projection (residual add + RMSNorm in front, SwiGLU behind)
+//   down projection
+// then lm_head (final norm in front, arg-max partials behind) and the sampler.
+// Same operator order as the reference step
+// (hf_decode_sequence/session_decode_prefill.inc.cu:74-372).
+cudaError_t enqueue_step(Session *s, uint32_t splits, uint32_t sample, uint64_t *launches) {
+  const ModelDims &d = s->dims;
+  const StepState st = step_state(s);
+  const uint64_t ah = d.attention_hidden(), kvh = d.kv_hidden();
+  const uint64_t qkv_rows = ah + 2 * kvh;
+  uint64_t n = 0;
+  cudaError_t err = launch_embed(s->stream, st, arena_at(s, s->layout.embeddings), d.hidden, s->h_b);
+  n += 1;
+  for (uint32_t l = 0; err == cudaSuccess && l < d.layers; ++l) {
+    const LayerLayout &L = s->layout.layers[l];
+    ProjectionParams p{};
+    p.error_word = s->device_error;
+    p.eps = s->rms_eps;
+    // QKV
+    p.weight = s->weights->qkv_packed + static_cast<uint64_t>(l) * qkv_rows * d.hidden;
+    p.rows = static_cast<uint32_t>(qkv_rows);
+    p.cols = d.hidden;
+    p.prologue = kPrologueAddNorm;
+    p.x_bf16 = s->x_scratch;
+    p.add_a = s->h_b;
+    p.add_b = l == 0 ? nullptr : s->down;
+    p.norm_weight = arena_at(s, L.rms_attn);
+    p.resid_out = s->h_a;
+    p.epilogue = kEpilogueStore;
+    p.out_f32 = s->qkv;
+    err = launch_projection(s->stream, p, s->sm_count);
+    n += 1;
+    if (err != cudaSuccess) break;
+
+    QkvPrepareParams qp{};
+    qp.qkv = s->qkv;
+    qp.q_bias = arena_at(s, L.q_bias);
+    qp.k_bias = arena_at(s, L.k_bias);
+    qp.v_bias = arena_at(s, L.v_bias);
+    qp.q_norm = arena_at(s, L.q_norm);
+    qp.k_norm = arena_at(s, L.k_norm);
+    qp.heads = d.heads;
+    qp.kv_heads = d.kv_heads;
+    qp.head_dim = d.head_dim;
+    qp.eps = s->rms_eps;
+    qp.rope_theta = s->rope_theta;
+    qp.key_pages = s->kv_keys + l * s->kv_layer_elems;
+    qp.value_pages = s->kv_values + l * s->kv_layer_elems;
+    qp.page_table = s->page_table;
+    qp.page_count = s->kv_pages;
+    err = launch_qkv_prepare(s->stream, st, qp);
+    n += 1;
+    if (err != cudaSuccess) break;
+
+    AttentionParams ap{};
+    ap.q = s->qkv;
+    ap.key_pages = qp.key_pages;
+    ap.value_pages = qp.value_pages;
+    ap.page_table = s->page_table;
+    ap.batch = 1;
+    ap.heads = d.heads;
+    ap.kv_heads = d.kv_heads;
+    ap.head_dim = d.head_dim;
+    ap.page_count = s->kv_pages;
+    ap.cursor = s->device_cursor;
+    ap.splits = splits;
+    ap.partial_acc = s->partial_acc;
+    ap.partial_m = s->partial_m;
+    ap.partial_l = s->partial_l;
+    ap.out_bf16 = s->attn_bf16;
+    ap.error_word = s->device_error;
+    err = launch_attention(s->stream, ap);
+    n += 2;
+    if (err != cudaSuccess) break;
+
+    // O
+    p = ProjectionParams{};
+    p.error_word = s->device_error;
+    p.eps = s->rms_eps;
+    p.weight = arena_at(s, L.w_o);
+    p.rows = d.hidden;
+    p.cols = static_cast<uint32_t>(ah);
+    p.prologue = kProloguePlain;
+    p.x_bf16 = s->attn_bf16;
+    p.epilogue = kEpilogueStore;
+    p.out_f32 = s->o_out;
+    err = launch_projection(s->stream, p, s->sm_count);
+    n += 1;
+    if (err != cudaSuccess) break;
+
+    // gate/up + SwiGLU
+    p = ProjectionParams{};
+    p.error_word = s->device_error;
+    p.eps = s->rms_eps;
+    p.weight = s->weights->gate_up_packed + static_cast<uint64_t>(l) * 2u * d.intermediate * d.hidden;
+    p.rows = 2u * d.intermediate;
+    p.cols = d.hidden;
+    p.prologue = kPrologueAddNorm;
+    p.x_bf16 = s->x_scratch;
+    p.add_a = s->h_a;
+    p.add_b = s->o_out;
+    p.add_bias = arena_at(s, L.o_bias);
+    p.norm_weight = arena_at(s, L.rms_mlp);
+    p.resid_out = s->h_b;
+    p.epilogue = kEpilogueSwiglu;
+    p.out_bf16 = s->ff_bf16;
+    err = launch_projection(s->stream, p, s->sm_count);
+    n += 1;
+    if (err != cudaSuccess) break;
+
+    // down
+    p = ProjectionParams{};
+    p.error_word = s->device_error;
+    p.eps = s->rms_eps;
+    p.weight = arena_at(s, L.w_down);
+    p.rows = d.hidden;
+    p.cols = d.intermediate;
+    p.prologue = kProloguePlain;
+    p.x_bf16 = s->ff_bf16;
+    p.epilogue = kEpilogueStore;
+    p.out_f32 = s->down;
+    err = launch_projection(s->stream, p, s->sm_count);
+    n += 1;
+  }
+  uint32_t partials = 0;
+  if (err == cudaSuccess && sample != 0) {
+    ProjectionParams p{};
+    p.error_word = s->device_error;
+    p.eps = s->rms_eps;
+    p.weight = arena_at(s, s->layout.lm_head);
+    p.rows = d.vocab;
+    p.cols = d.hidden;
+    p.prologue = kPrologueAddNorm;
+    p.x_bf16 = s->x_scratch;
+    p.add_a = s->h_b;
+    p.add_b = s->down;
+    p.norm_weight = arena_at(s, s->layout.final_norm);
+    p.resid_out = s->h_a;
+    p.epilogue = kEpilogueArgmax;
+    p.out_f32 = s->logits;
+    p.best_value = s->best_value;
+    p.best_index = s->best_index;
+    partials = projection_blocks(p, s->sm_count);
+    err = launch_projection(s->stream, p, s->sm_count);
+    n += 1;
+  }
+  if (err == cudaSuccess) {
+    err = launch_sample_greedy(s->stream, st, s->best_value, s->best_index, partials, sample);
+    n += 1;
+  }
+  if (launches != nullptr) *launches = n;
+  return err;
+}
+
+// Graph cache: one instantiated graph per (prompt length, attention split
+// count, sampling on/off, engine), like the reference's cached graph key
+// (hf_decode_sequence/session_graph_result.inc.cu:87-209).
+cudaError_t ensure_graph(Session *s, uint32_t splits, uint32_t sample, GraphEntry **out,
+                         NervaCudaHfDecodeSequenceResult *res) {
+  for (GraphEntry &g : s->graphs) {
+    if (g.prompt_count == s->prompt_count && g.splits == splits && g.sample == sample &&
+        g.engine == s->engine) {
+      *out = &g;
+      if (res != nullptr) {
+        res->graph_cache_hits += 1;
+        res->graph_nodes = g.nodes;
+      }
+      return cudaSuccess;
+    }
+  }
+  GraphEntry entry;
+  entry.prompt_count = s->prompt_count;
+  entry.splits = splits;
+  entry.sample = sample;
+  entry.engine = s->engine;
+  cudaError_t err = cudaStreamBeginCapture(s->stream, cudaStreamCaptureModeThreadLocal);
+  if (err != cudaSuccess) return err;
+  uint64_t launches = 0;
+  err = enqueue_step(s, splits, sample, &launches);
+  cudaGraph_t graph = nullptr;
+  const cudaError_t end_err = cudaStreamEndCapture(s->stream, &graph);
+  if (err == cudaSuccess) err = end_err;
+  if (err != cudaSuccess) {
+    if (graph != nullptr) cudaGraphDestroy(graph);
+    return err;
+  }
+  size_t nodes = 0;
+  err = cudaGraphGetNodes(graph, nullptr, &nodes);
+  cudaGraphExec_t exec = nullptr;
+  if (err == cudaSuccess) err = cudaGraphInstantiate(&exec, graph, 0);
+  if (err != cudaSuccess) {
+    cudaGraphDestroy(graph);
+    return err;
+  }
+  entry.graph = graph;
+  entry.exec = exec;
+  entry.nodes = nodes;
+  s->graphs.push_back(entry);
+  *out = &s->graphs.back();
+  if (res != nullptr) {
+    res->graph_captures += 1;
+    res->graph_nodes = nodes;
+  }
+  return cudaSuccess;
+}
+
+// Attention split count for a launch that will see contexts up to `target`:
+// bucketed to a power of two so that a growing context re-uses the graph.
+uint32_t splits_for(Session *s, uint32_t target_context) {
+  uint32_t want = attention_default_splits(target_context, 1, s->dims.kv_heads, s->sm_count);
+  uint32_t bucket = 1;
+  while (bucket < want) bucket <<= 1;
+  if (bucket > s->max_splits) bucket = s->max_splits;
+  return bucket == 0 ? 1 : bucket;
+}
+
+void fill_header(const Session *s, NervaCudaHfDecodeSequenceResult *out, uint32_t steps,
+                 uint32_t seed_token) {
+  out->device_count = 1;
+  out->dtype = s->dims.dtype;
+  out->hidden = s->dims.hidden;
+  out->heads = s->dims.heads;
+  out->kv_heads = s->dims.kv_heads;
+  out->head_dim = s->dims.head_dim;
+  out->intermediate = s->dims.intermediate;
+  out->vocab_size = s->dims.vocab;
+  out->layer_count = s->dims.layers;
+  out->steps = steps;
+  out->seed_token = seed_token;
+  out->resident_weight_bytes = s->resident_weight_bytes;
+  out->planned_weight_blocks = s->planned_weight_blocks;
+  out->planned_gpu_resident_blocks = s->planned_gpu_resident_blocks;
+  out->planned_gpu_staged_blocks = s->planned_gpu_staged_blocks;
+  out->planned_weight_bytes = s->planned_weight_bytes;
+  out->planned_gpu_resident_weight_bytes = s->planned_gpu_resident_weight_bytes;
+  out->planned_gpu_staged_weight_bytes = s->planned_gpu_staged_weight_bytes;
+  out->planned_weight_descriptor_count = s->planned_weight_descriptor_count;
+  out->planned_weight_descriptor_hash = s->planned_weight_descriptor_hash;
+}
+
+uint64_t resident_kv_bytes(const Session *s) {
+  return 2ull * s->dims.layers * s->kv_layer_elems * sizeof(uint16_t);
+}
+uint64_t device_footprint(const Session *s) {
+  return s->state_bytes + (s->weights ? s->weights->block_bytes : 0);
+}
+
+int fail(NervaCudaHfDecodeSequenceResult *out, cudaError_t err) {
+  out->status = -1;
+  out->cuda_error = static_cast<int32_t>(err);
+  set_last_error(cudaGetErrorString(err));
+  return -1;
+}
+
+// Reads the device error word (after a synchronise).  Non-zero fails the call.
+bool device_error_set(Session *s, NervaCudaHfDecodeSequenceResult *out) {
+  if (*s->host_error == 0) return false;
+  char text[96];
+  snprintf(text, sizeof(text), "device kernel reported error code %u", *s->host_error);
+  set_last_error(text);
+  out->status = -1;
+  out->cuda_error = static_cast<int32_t>(cudaErrorLaunchFailure);
+  return true;
+}
+
+uint32_t observed_from_slots(uint32_t steps, uint32_t has_eos, uint32_t eos,
+                             const NervaCudaSyntheticTokenSlot *slots) {
+  for (uint32_t i = 0; i < steps; ++i) {
+    if (slots[i].completion != 1u) return i;
+    if (has_eos != 0 && slots[i].token == eos) return i + 1;
+  }
+  return steps;
+}
+
+bool slots_valid(const NervaCudaSyntheticTokenSlot *slots, uint32_t count, uint32_t first_index) {
+  for (uint32_t i = 0; i < count; ++i) {
+    if (slots[i].request_id != 1u || slots[i].sequence_id != 1u || slots[i].completion != 1u ||
+        slots[i].token_index != static_cast<uint64_t>(first_index) + i)
+      return false;
+  }
+  return true;
+}
+
+cudaError_t reset_request_state(Session *s, const uint32_t *prompt, uint32_t count,
+                                NervaCudaHfDecodeSequenceResult *out) {
+  cudaError_t err = cudaMemsetAsync(s->device_slots, 0, s->slots_bytes, s->stream);
+  if (err == cudaSuccess) err = cudaMemsetAsync(s->device_cursor, 0, sizeof(uint32_t), s->stream);
+  if (err == cudaSuccess) err = cudaMemsetAsync(s->device_error, 0, sizeof(uint32_t), s->stream);
+  const uint64_t bytes = static_cast<uint64_t>(count) * sizeof(uint32_t);
+  if (err == cudaSuccess)
+    err = cudaMemcpyAsync(s->device_prompt, prompt, bytes, cudaMemcpyHostToDevice, s->stream);
+  out->h2d_bytes = bytes;
+  s->logits_valid = false;
+  return err;
+}
+
+}  // namespace
+
+// ============================================================ C ABI ========
+
+extern "C" const char *nerva_b200_last_error(void) { return g_last_error.c_str(); }
+
+extern "C" int nerva_cuda_hf_decode_sequence_plan_layout(
+    const NervaCudaHfDecodeSequenceLayoutPlanRequest *request,
+    NervaCudaHfDecodeSequenceLayoutPlanResult *out) {
+  if (out == nullptr) return -1;
+  memset(out, 0, sizeof(*out));
+  out->status = -1;
+  if (request == nullptr || request->layers == nullptr || request->layer_count == 0 ||
+      request->layer_index >= request->layer_count || request->hidden == 0 ||
+      request->heads == 0 || request->kv_heads == 0 || request->head_dim == 0 ||
+      request->intermediate == 0 || request->vocab_size == 0 ||
+      request->kv_heads > request->heads || request->heads % request->kv_heads != 0)
+    return -1;
+  for (uint32_t i = 0; i < request->layer_count; ++i) {
+    if (!valid_layer(request->layers[i], false)) return -1;
+    if (request->layers[i].attention_kind != NERVA_ATTENTION_KIND_FULL) return -1;
+  }
+  ModelDims d;
+  d.dtype = NERVA_DTYPE_BF16;
+  d.hidden = request->hidden;
+  d.heads = request->heads;
+  d.kv_heads = request->kv_heads;
+  d.head_dim = request->head_dim;
+  d.intermediate = request->intermediate;
+  d.vocab = request->vocab_size;
+  d.layers = request->layer_count;
+  const ArenaLayout layout = compute_arena_layout(d, request->layers);
+  const LayerLayout &l = layout.layers[request->layer_index];
+  out->status = 0;
+  out->hidden = d.hidden;
+  out->heads = d.heads;
+  out->kv_heads = d.kv_heads;
+  out->head_dim = d.head_dim;
+  out->intermediate = d.intermediate;
+  out->vocab_size = d.vocab;
+  out->layer_count = d.layers;
+  out->layer_index = request->layer_index;
+  out->attention_kind = NERVA_ATTENTION_KIND_FULL;
+  out->resident_weight_bytes = layout.elements * 2u - static_cast<uint64_t>(d.hidden) * 2u * 2u;
+  out->layout_bytes = static_cast<uint64_t>(d.layers) * 688u;  // sizeof the reference's per-layer layout record
+  out->final_norm = layout.final_norm;
+  out->lm_head = layout.lm_head;
+  out->rms_attn = l.rms_attn;
+  out->rms_mlp = l.rms_mlp;
+  out->w_q = l.w_q;
+  out->q_norm = l.q_norm;
+  out->w_k = l.w_k;
+  out->k_norm = l.k_norm;
+  out->w_v = l.w_v;
+  out->w_o = l.w_o;
+  out->w_router = l.w_router;
+  out->w_expert_gate_up = l.w_expert_gate_up;
+  out->w_expert_down = l.w_expert_down;
+  out->w_shared_expert_gate = l.w_shared_gate;
+  out->w_shared_expert_up = l.w_shared_up;
+  out->w_shared_expert_down = l.w_shared_down;
+  // The reference leaves every DeepSeek offset of a full-attention layer "missing".
+  uint64_t *ds = &out->deepseek_q_a_scale;
+  for (uint64_t *p = ds; p <= &out->deepseek_hc_ffn_scale; ++p) *p = kMissingOffset;
+  return 0;
+}
+
+namespace {
+
+struct UploadCounters {
+  uint64_t h2d = 0, resident = 0, staged = 0;
+};
+
+cudaError_t copy_tensor(Session *s, uint64_t offset, const uint16_t *src, uint64_t elems,
+                        UploadCounters *c) {
+  if (offset == kMissingOffset || src == nullptr) return cudaSuccess;
+  c->h2d += elems * 2u;
+  return cudaMemcpyAsync(s->weights->arena + offset, src, elems * 2u, cudaMemcpyHostToDevice,
+                         s->stream);
+}
+
+// Pointer mode: every tensor comes from a host pointer in the request
+// (hf_decode_sequence/weights.cu:650-726).
+cudaError_t upload_from_pointers(Session *s, const NervaCudaHfDecodeSequenceSessionCreateRequest *r,
+                                 UploadCounters *c) {
+  const ModelDims &d = s->dims;
+  const uint64_t hidden = d.hidden, ah = d.attention_hidden(), kvh = d.kv_hidden();
+  const uint64_t inter = d.intermediate;
+  cudaError_t err = copy_tensor(s, s->layout.embeddings, r->embeddings, d.vocab * hidden, c);
+  for (uint32_t i = 0; err == cudaSuccess && i < d.layers; ++i) {
+    const NervaCudaHfDecodeChainLayer &L = r->layers[i];
+    const LayerLayout &o = s->layout.layers[i];
+    struct Item { uint64_t off; const uint16_t *src; uint64_t n; } items[] = {
+        {o.rms_attn, L.rms_attn_weight, hidden}, {o.w_q, L.w_q, ah * hidden},
+        {o.q_norm, L.q_norm_weight, d.head_dim}, {o.w_k, L.w_k, kvh * hidden},
+        {o.k_norm, L.k_norm_weight, d.head_dim}, {o.w_v, L.w_v, kvh * hidden},
+        {o.w_o, L.w_o, hidden * ah},             {o.rms_mlp, L.rms_mlp_weight, hidden},
+        {o.w_gate, L.w_gate, inter * hidden},    {o.w_up, L.w_up, inter * hidden},
+        {o.w_down, L.w_down, hidden * inter},    {o.q_bias, L.q_bias, ah},
+        {o.k_bias, L.k_bias, kvh},               {o.v_bias, L.v_bias, kvh},
+        {o.o_bias, L.o_bias, hidden}};
+    for (const Item &it : items) {
+      if (err == cudaSuccess) err = copy_tensor(s, it.off, it.src, it.n, c);
+    }
+  }
+  if (err == cudaSuccess) err = copy_tensor(s, s->layout.final_norm, r->final_norm_weight, hidden, c);
+  if (err == cudaSuccess) err = copy_tensor(s, s->layout.lm_head, r->lm_head, d.vocab * hidden, c);
+  return err;
+}
+
+// Descriptor mode: blocks are contiguous over the resident-weight byte space
+// (the arena minus its input|scratch gap); each comes from host memory or from
+// a byte range of a file, streamed through a pinned staging buffer
+// (hf_decode_sequence/weights.cu:728-745,797-908).
+cudaError_t upload_from_descriptors(Session *s,
+                                    const NervaCudaHfDecodeSequenceSessionCreateRequest *r,
+                                    UploadCounters *c) {
+  const uint64_t embedding_bytes = static_cast<uint64_t>(s->dims.vocab) * s->dims.hidden * 2u;
+  const uint64_t gap_bytes = static_cast<uint64_t>(s->dims.hidden) * 2u * 2u;
+  constexpr uint64_t kStagingBytes = 64ull << 20;
+  uint8_t *staging = nullptr;
+  cudaError_t err = cudaSuccess;
+  uint8_t *arena_bytes = reinterpret_cast<uint8_t *>(s->weights->arena);
+  for (uint32_t i = 0; err == cudaSuccess && i < r->planned_weight_descriptor_count; ++i) {
+    const NervaCudaHfDecodeSequenceWeightBlock &b = r->planned_weight_descriptors[i];
+    if (b.offset_bytes < embedding_bytes && b.offset_bytes + b.bytes > embedding_bytes) {
+      set_last_error("weight block straddles the embedding boundary");
+      err = cudaErrorInvalidValue;
+      break;
+    }
+    const uint64_t dst = b.offset_bytes >= embedding_bytes ? b.offset_bytes + gap_bytes : b.offset_bytes;
+    if (b.host_source != nullptr) {
+      err = cudaMemcpyAsync(arena_bytes + dst, b.host_source, b.bytes, cudaMemcpyHostToDevice, s->stream);
+    } else {
+      std::string path(b.source_file, b.source_file_len);
+      FILE *f = fopen(path.c_str(), "rb");
+      if (f == nullptr) {
+        set_last_error("cannot open weight file " + path);
+        err = cudaErrorInvalidValue;
+        break;
+      }
+      if (staging == nullptr) err = cudaMallocHost(&staging, kStagingBytes);
+      uint64_t done = 0;
+      if (err == cudaSuccess && fseek(f, static_cast<long>(b.file_offset_begin), SEEK_SET) != 0)
+        err = cudaErrorInvalidValue;
+      while (err == cudaSuccess && done < b.bytes) {
+        const uint64_t n = std::min<uint64_t>(kStagingBytes, b.bytes - done);
+        if (fread(staging, 1, n, f) != n) {
+          set_last_error("short read from weight file " + path);
+          err = cudaErrorInvalidValue;
+          break;
+        }
+        err = cudaMemcpyAsync(arena_bytes + dst + done, staging, n, cudaMemcpyHostToDevice, s->stream);
+        if (err == cudaSuccess) err = cudaStreamSynchronize(s->stream);  // staging is reused
+        done += n;
+      }
+      fclose(f);
+    }
+    c->h2d += b.bytes;
+    if (b.strategy == NERVA_WEIGHT_STRATEGY_GPU_RESIDENT) c->resident += b.bytes;
+    else c->staged += b.bytes;
+  }
+  if (staging != nullptr) {
+    cudaStreamSynchronize(s->stream);
+    cudaFreeHost(staging);
+  }
+  return err;
+}
+
+// hf_decode_sequence/weights.cu:412-467
+bool validate_descriptors(const NervaCudaHfDecodeSequenceSessionCreateRequest *r,
+                          uint64_t resident_weight_bytes) {
+  uint64_t cursor = 0, resident = 0, staged = 0;
+  uint32_t resident_blocks = 0, staged_blocks = 0;
+  for (uint32_t i = 0; i < r->planned_weight_descriptor_count; ++i) {
+    const NervaCudaHfDecodeSequenceWeightBlock &b = r->planned_weight_descriptors[i];
+    const bool has_source = b.host_source != nullptr || (b.source_file != nullptr && b.source_file_len != 0);
+    if (b.bytes == 0 || b.reserved != 0 || !has_source || b.offset_bytes != cursor ||
+        b.offset_bytes % 2u != 0 || b.bytes % 2u != 0)
+      return false;
+    if (cursor + b.bytes < cursor) return false;
+    cursor += b.bytes;
+    if (b.strategy == NERVA_WEIGHT_STRATEGY_GPU_RESIDENT) {
+      resident_blocks += 1;
+      resident += b.bytes;
+    } else if (b.strategy == NERVA_WEIGHT_STRATEGY_GPU_STAGED) {
+      staged_blocks += 1;
+      staged += b.bytes;
+    } else {
+      return false;
+    }
+  }
+  return cursor == resident_weight_bytes && cursor == r->planned_weight_bytes &&
+         hash_weight_descriptors(r->planned_weight_descriptors, r->planned_weight_descriptor_count) ==
+             r->planned_weight_descriptor_hash &&
+         resident_blocks == r->planned_gpu_resident_blocks &&
+         staged_blocks == r->planned_gpu_staged_blocks &&
+         resident == r->planned_gpu_resident_weight_bytes &&
+         staged == r->planned_gpu_staged_weight_bytes;
+}
+
+void fill_create_header(const NervaCudaHfDecodeSequenceSessionCreateRequest *r,
+                        NervaCudaHfDecodeSequenceSessionCreateResult *out) {
+  out->dtype = r->dtype;
+  out->hidden = r->hidden;
+  out->heads = r->heads;
+  out->kv_heads = r->kv_heads;
+  out->head_dim = r->head_dim;
+  out->intermediate = r->intermediate;
+  out->vocab_size = r->vocab_size;
+  out->layer_count = r->layer_count;
+  out->max_context_tokens = r->max_context_tokens;
+  out->planned_weight_blocks = r->planned_weight_blocks;
+  out->planned_gpu_resident_blocks = r->planned_gpu_resident_blocks;
+  out->planned_gpu_staged_blocks = r->planned_gpu_staged_blocks;
+  out->planned_weight_bytes = r->planned_weight_bytes;
+  out->planned_gpu_resident_weight_bytes = r->planned_gpu_resident_weight_bytes;
+  out->planned_gpu_staged_weight_bytes = r->planned_gpu_staged_weight_bytes;
+  out->planned_weight_descriptor_count = r->planned_weight_descriptor_count;
+  out->experimental_rt_decode_requested = r->experimental_rt_decode == 0 ? 0u : 1u;
+  out->experimental_rt_mode = r->experimental_rt_mode;
+  out->experimental_rt_page_tokens = r->experimental_rt_page_tokens;
+  out->experimental_rt_pages = r->experimental_rt_pages;
+  out->experimental_rt_local_window_tokens = r->experimental_rt_local_window_tokens;
+  out->experimental_rt_sink_tokens = r->experimental_rt_sink_tokens;
+}
+
+int create_fail(Session *s, NervaCudaHfDecodeSequenceSessionCreateResult *out, cudaError_t err,
+                int32_t stage) {
+  out->status = -1;
+  out->cuda_error = static_cast<int32_t>(err);
+  out->failure_stage = stage;
+  if (err != cudaSuccess) set_last_error(cudaGetErrorString(err));
+  destroy_session(s);
+  return -1;
+}
+
+// Allocates and carves the private state of a session whose dims, max_context
+// and sm_count are set.
+cudaError_t allocate_state(Session *s, int32_t *stage) {
+  StaticArena sizing(UINT64_MAX / 2);
+  if (!plan_state(s, sizing, nullptr)) return cudaErrorMemoryAllocation;
+  s->state_bytes = sizing.used();
+  *stage = kStageDeviceScratchAlloc;
+  cudaError_t err = cudaMalloc(&s->state_block, s->state_bytes);
+  if (err != cudaSuccess) return err;
+  s->state_arena = StaticArena(s->state_bytes);
+  if (!plan_state(s, s->state_arena, s->state_block)) return cudaErrorMemoryAllocation;
+  s->slots_bytes = static_cast<uint64_t>(s->max_context) * sizeof(NervaCudaSyntheticTokenSlot);
+  *stage = kStageHostSlotsAlloc;
+  err = cudaMallocHost(&s->host_slots, s->slots_bytes);
+  if (err == cudaSuccess) err = cudaMallocHost(&s->host_error, sizeof(uint32_t));
+  if (err != cudaSuccess) return err;
+  *s->host_error = 0;
+  *stage = kStageStreamCreate;
+  err = cudaStreamCreateWithFlags(&s->stream, cudaStreamNonBlocking);
+  if (err != cudaSuccess) return err;
+  *stage = kStageStartEventCreate;
+  err = cudaEventCreate(&s->ev_start);
+  if (err != cudaSuccess) return err;
+  *stage = kStageStopEventCreate;
+  err = cudaEventCreate(&s->ev_stop);
+  if (err != cudaSuccess) return err;
+  // KV pages come out of the pool in FIFO order, which makes the initial
+  // logical->physical table the identity, as the reference initialises it
+  // (hf_decode_sequence/kernels.cu:732-739).
+  StaticArena page_space(2ull * s->dims.layers * s->kv_layer_elems * 2u);
+  const uint64_t page_bytes = NERVA_KV_CACHE_BLOCK_TOKENS * s->dims.kv_hidden() * 2u;
+  if (!s->kv_pool.preallocate(page_space, s->kv_pages, NERVA_KV_CACHE_BLOCK_TOKENS, page_bytes, 16))
+    return cudaErrorMemoryAllocation;
+  std::vector<uint32_t> table(s->kv_pages);
+  for (uint32_t i = 0; i < s->kv_pages; ++i) {
+    const int64_t page = s->kv_pool.allocate_page(i * NERVA_KV_CACHE_BLOCK_TOKENS, 0, 0);
+    if (page < 0) return cudaErrorMemoryAllocation;
+    table[i] = static_cast<uint32_t>(page);
+  }
+  err = cudaMemcpyAsync(s->page_table, table.data(), table.size() * sizeof(uint32_t),
+                        cudaMemcpyHostToDevice, s->stream);
+  if (err == cudaSuccess) err = cudaMemsetAsync(s->device_error, 0, sizeof(uint32_t), s->stream);
+  if (err == cudaSuccess) err = cudaMemsetAsync(s->device_cursor, 0, sizeof(uint32_t), s->stream);
+  if (err == cudaSuccess) err = cudaStreamSynchronize(s->stream);
+  return err;
+}
+
+}  // namespace
+
+extern "C" int nerva_cuda_hf_decode_sequence_session_create(
+    const NervaCudaHfDecodeSequenceSessionCreateRequest *request,
+    NervaCudaHfDecodeSequenceSession **session_out,
+    NervaCudaHfDecodeSequenceSessionCreateResult *out) {
+  if (out == nullptr) return -1;
+  memset(out, 0, sizeof(*out));
+  out->status = -1;
+  if (session_out == nullptr) return -1;
+  *session_out = nullptr;
+  set_last_error("");
+  // session_api_lifecycle.inc.cu:15-55 and weights.cu:232-340
+  if (request == nullptr || request->layers == nullptr || request->layer_count == 0 ||
+      request->hidden == 0 || request->heads == 0 || request->kv_heads == 0 ||
+      request->head_dim == 0 || request->intermediate == 0 || request->vocab_size == 0 ||
+      request->max_context_tokens == 0 || request->kv_heads > request->heads ||
+      request->heads % request->kv_heads != 0 || request->dtype > NERVA_DTYPE_BF16 ||
+      (request->rope_theta > 0.0f && request->head_dim % 2 != 0)) {
+    out->failure_stage = kStageInvalidRequest;
+    return -1;
+  }
+  const bool declared_plan = request->planned_weight_blocks != 0;
+  if (!declared_plan && (request->embeddings == nullptr || request->final_norm_weight == nullptr ||
+                         request->lm_head == nullptr)) {
+    out->failure_stage = kStageInvalidRequest;
+    return -1;
+  }
+  for (uint32_t i = 0; i < request->layer_count; ++i) {
+    const NervaCudaHfDecodeChainLayer &layer = request->layers[i];
+    if (!valid_layer(layer, !declared_plan) ||
+        (layer.mlp_kind == NERVA_MLP_KIND_SPARSE_MOE &&
+         (layer.moe_intermediate > request->intermediate ||
+          layer.shared_expert_intermediate > request->intermediate))) {
+      out->failure_stage = kStageInvalidRequest;
+      return -1;
+    }
+  }
+  if (declared_plan &&
+      (request->planned_weight_bytes == 0 || request->planned_weight_descriptors == nullptr ||
+       request->planned_weight_descriptor_count != request->planned_weight_blocks ||
+       request->planned_weight_descriptor_hash == 0 ||
+       request->planned_gpu_resident_blocks > request->planned_weight_blocks ||
+       request->planned_gpu_staged_blocks >
+           request->planned_weight_blocks - request->planned_gpu_resident_blocks ||
+       request->planned_gpu_resident_weight_bytes > request->planned_weight_bytes ||
+       request->planned_gpu_staged_weight_bytes >
+           request->planned_weight_bytes - request->planned_gpu_resident_weight_bytes)) {
+    out->failure_stage = kStageInvalidRequest;
+    return -1;
+  }
+  fill_create_header(request, out);
+
+  ModelDims d;
+  d.dtype = request->dtype;
+  d.hidden = request->hidden;
+  d.heads = request->heads;
+  d.kv_heads = request->kv_heads;
+  d.head_dim = request->head_dim;
+  d.intermediate = request->intermediate;
+  d.vocab = request->vocab_size;
+  d.layers = request->layer_count;
+  ArenaLayout layout = compute_arena_layout(d, request->layers);
+  const uint64_t resident_weight_bytes = layout.elements * 2u - static_cast<uint64_t>(d.hidden) * 4u;
+  out->resident_weight_bytes = resident_weight_bytes;
+  if (declared_plan && (request->planned_weight_bytes != resident_weight_bytes ||
+                        !validate_descriptors(request, resident_weight_bytes))) {
+    out->failure_stage = kStageInvalidRequest;
+    return -1;
+  }
+  if (declared_plan) out->planned_weight_descriptor_hash = request->planned_weight_descriptor_hash;
+
+  // Device work starts here.
+  int device_count = 0;
+  cudaError_t err = cudaGetDeviceCount(&device_count);
+  if (err != cudaSuccess || device_count == 0) {
+    out->cuda_error = static_cast<int32_t>(err != cudaSuccess ? err : cudaErrorNoDevice);
+    out->failure_stage = kStageGetDeviceCount;
+    set_last_error("no CUDA device");
+    cudaGetLastError();
+    return -1;
+  }
+  out->device_count = device_count;
+  // Shapes this library does not run are refused, never emulated.
+  bool supported = request->dtype == NERVA_DTYPE_BF16 && request->head_dim <= 256;
+  for (uint32_t i = 0; supported && i < request->layer_count; ++i)
+    supported = layer_supported(request->layers[i]);
+  if (!supported) {
+    out->cuda_error = static_cast<int32_t>(cudaErrorNotSupported);
+    out->failure_stage = kStageInvalidRequest;
+    set_last_error("model not supported: needs bf16, full attention, dense SwiGLU, head_dim <= 256");
+    return -1;
+  }
+
+  Session *s = new (std::nothrow) Session();
+  if (s == nullptr) {
+    out->cuda_error = static_cast<int32_t>(cudaErrorMemoryAllocation);
+    out->failure_stage = kStageSessionAlloc;
+    return -1;
+  }
+  s->dims = d;
+  s->max_context = request->max_context_tokens;
+  s->rms_eps = request->rms_eps;
+  s->rope_theta = request->rope_theta;
+  s->detailed_profile = request->detailed_profile;
+  s->layout = layout;
+  s->resident_weight_bytes = resident_weight_bytes;
+  s->planned_weight_blocks = request->planned_weight_blocks;
+  s->planned_gpu_resident_blocks = request->planned_gpu_resident_blocks;
+  s->planned_gpu_staged_blocks = request->planned_gpu_staged_blocks;
+  s->planned_weight_bytes = request->planned_weight_bytes;
+  s->planned_gpu_resident_weight_bytes = request->planned_gpu_resident_weight_bytes;
+  s->planned_gpu_staged_weight_bytes = request->planned_gpu_staged_weight_bytes;
+  s->planned_weight_descriptor_count = request->planned_weight_descriptor_count;
+  s->planned_weight_descriptor_hash = declared_plan ? request->planned_weight_descriptor_hash : 0;
+  s->layer_meta.assign(request->layers, request->layers + request->layer_count);
+
+  int device = 0;
+  err = cudaGetDevice(&device);
+  cudaDeviceProp prop{};
+  if (err == cudaSuccess) err = cudaGetDeviceProperties(&prop, device);
+  if (err != cudaSuccess) return create_fail(s, out, err, kStageSetDevice);
+  s->sm_count = static_cast<uint32_t>(prop.multiProcessorCount);
+  out->device_memory_bandwidth_bps =
+      static_cast<uint64_t>(prop.memoryClockRate) * 1000ull * (static_cast<uint64_t>(prop.memoryBusWidth) / 8ull);
+  err = configure_projection_kernels();
+  if (err == cudaSuccess) err = configure_attention_kernels();
+  if (err != cudaSuccess) return create_fail(s, out, err, kStageSetDevice);
+
+  // shared weights: one allocation
+  s->weights = std::make_shared<SharedWeights>();
+  {
+    StaticArena sizing(UINT64_MAX / 2);
+    plan_weights(s, sizing, nullptr, nullptr);
+    s->weights->block_bytes = sizing.used();
+    err = cudaMalloc(&s->weights->block, s->weights->block_bytes);
+    if (err != cudaSuccess) return create_fail(s, out, err, kStageDeviceArenaAlloc);
+    s->weight_arena = StaticArena(s->weights->block_bytes);
+    plan_weights(s, s->weight_arena, s->weights->block, s->weights.get());
+  }
+  int32_t stage = kStageDeviceScratchAlloc;
+  err = allocate_state(s, &stage);
+  if (err != cudaSuccess) return create_fail(s, out, err, stage);
+
+  UploadCounters counters;
+  err = declared_plan ? upload_from_descriptors(s, request, &counters)
+                      : upload_from_pointers(s, request, &counters);
+  if (err != cudaSuccess) return create_fail(s, out, err, kStageDescriptorCopy);
+  // packed replicas
+  const uint64_t ah = d.attention_hidden(), kvh = d.kv_hidden();
+  const uint64_t qkv_rows = ah + 2 * kvh;
+  for (uint32_t l = 0; err == cudaSuccess && l < d.layers; ++l) {
+    const LayerLayout &L = s->layout.layers[l];
+    err = launch_pack_qkv(s->stream, arena_at(s, L.w_q), arena_at(s, L.w_k), arena_at(s, L.w_v),
+                          s->weights->qkv_packed + l * qkv_rows * d.hidden, ah * d.hidden,
+                          kvh * d.hidden);
+    if (err == cudaSuccess)
+      err = launch_pack_gate_up(s->stream, arena_at(s, L.w_gate), arena_at(s, L.w_up),
+                                s->weights->gate_up_packed + static_cast<uint64_t>(l) * 2u * d.intermediate * d.hidden,
+                                d.intermediate, d.hidden);
+  }
+  if (err != cudaSuccess) return create_fail(s, out, err, kStagePackReplicas);
+  err = cudaStreamSynchronize(s->stream);
+  if (err != cudaSuccess) return create_fail(s, out, err, kStageSetupSynchronize);
+
+  out->descriptor_gpu_resident_h2d_bytes = counters.resident;
+  out->descriptor_gpu_staged_h2d_bytes = counters.staged;
+  out->h2d_bytes = counters.h2d;
+  out->sync_calls = 2;
+  out->resident_kv_bytes = resident_kv_bytes(s);
+  out->device_arena_bytes = device_footprint(s);
+  out->pinned_host_bytes = s->slots_bytes;
+  out->head_threads = 128;
+  out->prefill_chunk_tokens = 1;  // the prompt is pushed through the decode step token by token
+  out->hot_path_allocations = 0;
+  out->status = 0;
+  *session_out = s;
+  return 0;
+}
+
+extern "C" int nerva_cuda_hf_decode_sequence_session_destroy(Session *session) {
+  if (session == nullptr) return -1;
+  destroy_session(session);
+  return 0;
+}
+
+extern "C" int nerva_b200_session_set_engine(Session *s, uint32_t engine) {
+  if (s == nullptr || engine > 0 || s->started) return -1;
+  s->engine = engine;
+  return 0;
+}
+
+extern "C" int nerva_cuda_hf_decode_sequence_session_start(
+    const NervaCudaHfDecodeSequenceSessionStartRequest *request,
+    NervaCudaHfDecodeSequenceResult *out) {
+  if (out == nullptr) return -1;
+  memset(out, 0, sizeof(*out));
+  out->status = -1;
+  if (request == nullptr || request->session == nullptr || request->prompt_tokens == nullptr ||
+      request->prompt_token_count == 0 || !sampler_valid(request->sampler))
+    return -1;
+  Session *s = request->session;
+  if (request->prompt_token_count > s->max_context) return -1;
+  for (uint32_t i = 0; i < request->prompt_token_count; ++i) {
+    if (request->prompt_tokens[i] >= s->dims.vocab) return -1;
+  }
+  fill_header(s, out, 0, request->prompt_tokens[request->prompt_token_count - 1u]);
+  if (!sampler_greedy(request->sampler)) {
+    set_last_error("only greedy sampling is implemented");
+    out->cuda_error = static_cast<int32_t>(cudaErrorNotSupported);
+    return -1;
+  }
+  s->prompt_count = request->prompt_token_count;
+  s->started = false;
+  cudaError_t err = reset_request_state(s, request->prompt_tokens, request->prompt_token_count, out);
+  // Prefill by decode: prompt_count - 1 steps without sampling, then one with
+  // (the reference's serial prefill, session_decode_prefill.inc.cu:2245-2297).
+  const uint32_t splits = splits_for(s, s->prompt_count);
+  GraphEntry *quiet = nullptr, *sampled = nullptr;
+  if (err == cudaSuccess && s->prompt_count > 1) err = ensure_graph(s, splits, 0, &quiet, out);
+  if (err == cudaSuccess) err = ensure_graph(s, splits, 1, &sampled, out);
+  if (err == cudaSuccess) err = cudaEventRecord(s->ev_start, s->stream);
+  for (uint32_t i = 0; err == cudaSuccess && i + 1 < s->prompt_count; ++i) {
+    err = cudaGraphLaunch(quiet->exec, s->stream);
+    out->graph_replays += 1;
+    out->graph_launches += 1;
+    out->kernel_launches += quiet->nodes;
+  }
+  if (err == cudaSuccess) {
+    err = cudaGraphLaunch(sampled->exec, s->stream);
+    out->graph_replays += 1;
+    out->graph_launches += 1;
+    out->kernel_launches += sampled->nodes;
+  }
+  if (err == cudaSuccess) err = cudaEventRecord(s->ev_stop, s->stream);
+  if (err == cudaSuccess)
+    err = cudaMemcpyAsync(s->host_error, s->device_error, sizeof(uint32_t), cudaMemcpyDeviceToHost, s->stream);
+  if (err == cudaSuccess) {
+    err = cudaStreamSynchronize(s->stream);
+    out->sync_calls += 1;
+    out->d2h_bytes += sizeof(uint32_t);
+  }
+  if (err != cudaSuccess) return fail(out, err);
+  if (device_error_set(s, out)) return -1;
+  float ms = 0.0f;
+  if (cudaEventElapsedTime(&ms, s->ev_start, s->ev_stop) == cudaSuccess && ms > 0.0f)
+    out->device_elapsed_ns = static_cast<uint64_t>(ms * 1.0e6f);
+  s->has_eos = request->has_eos_token;
+  s->eos_token = request->eos_token;
+  s->seed_token = request->prompt_tokens[request->prompt_token_count - 1u];
+  s->observed = 0;
+  s->cursor = s->prompt_count;
+  s->started = true;
+  s->finished = false;
+  s->logits_valid = true;
+  out->resident_kv_bytes = resident_kv_bytes(s);
+  out->kv_tokens = s->prompt_count;
+  out->device_arena_bytes = device_footprint(s);
+  out->pinned_host_bytes = s->slots_bytes;
+  out->hot_path_allocations = s->hot_path_allocations;
+  out->status = 0;
+  return 0;
+}
+
+extern "C" int nerva_cuda_hf_decode_sequence_session_advance(
+    const NervaCudaHfDecodeSequenceSessionAdvanceRequest *request,
+    NervaCudaHfDecodeSequenceResult *out) {
+  if (out == nullptr) return -1;
+  memset(out, 0, sizeof(*out));
+  out->status = -1;
+  if (request == nullptr || request->session == nullptr || request->output_tokens == nullptr ||
+      request->steps == 0 || request->output_token_capacity < request->steps)
+    return -1;
+  Session *s = request->session;
+  if (!s->started || s->finished || s->prompt_count == 0) return -1;
+  // session_api_lifecycle.inc.cu:1137-1153
+  const uint32_t slot_start = s->prompt_count - 1u + s->observed;
+  const uint64_t target64 = static_cast<uint64_t>(s->prompt_count) + s->observed + request->steps - 1u;
+  if (target64 > s->max_context || target64 < s->cursor) return -1;
+  const uint32_t target = static_cast<uint32_t>(target64);
+  const uint32_t run_count = target - s->cursor;
+  const uint32_t seed = s->observed == 0 ? s->seed_token : s->host_slots[slot_start - 1u].token;
+  fill_header(s, out, request->steps, seed);
+
+  cudaError_t err = cudaSuccess;
+  GraphEntry *graph = nullptr;
+  if (run_count != 0) err = ensure_graph(s, splits_for(s, target), 1, &graph, out);
+  if (err == cudaSuccess && run_count != 0) err = cudaEventRecord(s->ev_start, s->stream);
+  for (uint32_t step = 0; err == cudaSuccess && step < run_count; ++step) {
+    err = cudaGraphLaunch(graph->exec, s->stream);  // the hot loop: nothing else per token
+    if (err != cudaSuccess) break;
+    out->graph_replays += 1;
+    out->graph_launches += 1;
+    out->kernel_launches += graph->nodes;
+    if (s->has_eos != 0) {
+      // Stop launching once the stop token has been produced
+      // (session_api_lifecycle.inc.cu:1217-1234).
+      const uint32_t position = s->cursor + step;
+      err = cudaStreamSynchronize(s->stream);
+      out->sync_calls += 1;
+      if (err == cudaSuccess)
+        err = cudaMemcpy(&s->host_slots[position], &s->device_slots[position],
+                         sizeof(NervaCudaSyntheticTokenSlot), cudaMemcpyDeviceToHost);
+      out->d2h_bytes += sizeof(NervaCudaSyntheticTokenSlot);
+      if (err == cudaSuccess && s->host_slots[position].completion == 1u &&
+          s->host_slots[position].token == s->eos_token)
+        break;
+    }
+  }
+  if (err == cudaSuccess && run_count != 0) err = cudaEventRecord(s->ev_stop, s->stream);
+  const uint64_t bytes = static_cast<uint64_t>(request->steps) * sizeof(NervaCudaSyntheticTokenSlot);
+  if (err == cudaSuccess)
+    err = cudaMemcpyAsync(s->host_slots + slot_start, s->device_slots + slot_start, bytes,
+                          cudaMemcpyDeviceToHost, s->stream);
+  if (err == cudaSuccess)
+    err = cudaMemcpyAsync(s->host_error, s->device_error, sizeof(uint32_t), cudaMemcpyDeviceToHost, s->stream);
+  out->d2h_bytes += bytes + sizeof(uint32_t);
+  if (err == cudaSuccess) {
+    err = cudaStreamSynchronize(s->stream);
+    out->sync_calls += 1;
+  }
+  if (err != cudaSuccess) return fail(out, err);
+  if (device_error_set(s, out)) return -1;
+  if (run_count != 0) {
+    float ms = 0.0f;
+    if (cudaEventElapsedTime(&ms, s->ev_start, s->ev_stop) == cudaSuccess && ms > 0.0f) {
+      out->device_elapsed_ns = static_cast<uint64_t>(ms * 1.0e6f);
+      if (out->device_elapsed_ns == 0) out->device_elapsed_ns = 1;
+    }
+    s->logits_valid = true;
+  }
+  const NervaCudaSyntheticTokenSlot *slots = s->host_slots + slot_start;
+  out->observed_tokens = observed_from_slots(request->steps, s->has_eos, s->eos_token, slots);
+  for (uint32_t i = 0; i < out->observed_tokens; ++i) request->output_tokens[i] = slots[i].token;
+  out->last_token = out->observed_tokens == 0 ? 0 : request->output_tokens[out->observed_tokens - 1];
+  out->observed_token_hash = hash_tokens(request->output_tokens, out->observed_tokens);
+  out->resident_kv_bytes = resident_kv_bytes(s);
+  out->kv_tokens = static_cast<uint64_t>(slot_start) + out->observed_tokens;
+  out->device_arena_bytes = device_footprint(s);
+  out->pinned_host_bytes = s->slots_bytes;
+  out->host_causality_edges = 0;
+  out->hot_path_allocations = s->hot_path_allocations;
+  out->status = out->observed_tokens > 0 && slots_valid(slots, out->observed_tokens, slot_start) ? 0 : -1;
+  if (out->status == 0) {
+    s->observed += out->observed_tokens;
+    s->cursor = out->observed_tokens < request->steps ? s->max_context : target;
+    s->finished = out->observed_tokens < request->steps || out->kv_tokens >= s->max_context;
+  }
+  return out->status == 0 ? 0 : -1;
+}
+
+extern "C" int nerva_cuda_hf_decode_sequence_session_run(
+    const NervaCudaHfDecodeSequenceSessionRunRequest *request,
+    NervaCudaHfDecodeSequenceResult *out) {
+  if (out == nullptr) return -1;
+  memset(out, 0, sizeof(*out));
+  out->status = -1;
+  if (request == nullptr || request->session == nullptr || request->prompt_tokens == nullptr ||
+      request->output_tokens == nullptr || request->steps == 0 ||
+      request->prompt_token_count == 0 || request->output_token_capacity < request->steps ||
+      request->prompt_tokens[request->prompt_token_count - 1u] != request->seed_token ||
+      !sampler_valid(request->sampler) ||
+      request->prompt_token_count > UINT32_MAX - request->steps + 1u)
+    return -1;
+  Session *s = request->session;
+  const uint32_t context_steps = request->prompt_token_count + request->steps - 1u;
+  if (context_steps > s->max_context) return -1;
+  for (uint32_t i = 0; i < request->prompt_token_count; ++i) {
+    if (request->prompt_tokens[i] >= s->dims.vocab) return -1;
+  }
+  fill_header(s, out, request->steps, request->seed_token);
+  if (!sampler_greedy(request->sampler)) {
+    set_last_error("only greedy sampling is implemented");
+    out->cuda_error = static_cast<int32_t>(cudaErrorNotSupported);
+    return -1;
+  }
+  s->prompt_count = request->prompt_token_count;
+  s->started = false;
+  cudaError_t err = reset_request_state(s, request->prompt_tokens, request->prompt_token_count, out);
+  // One sampling graph replayed for every position, prompt included; samples at
+  // prompt positions are never read (session_api_lifecycle.inc.cu:849-920).
+  GraphEntry *graph = nullptr;
+  if (err == cudaSuccess) err = ensure_graph(s, splits_for(s, context_steps), 1, &graph, out);
+  if (err == cudaSuccess) err = cudaEventRecord(s->ev_start, s->stream);
+  for (uint32_t step = 0; err == cudaSuccess && step < context_steps; ++step) {
+    err = cudaGraphLaunch(graph->exec, s->stream);
+    if (err == cudaSuccess) {
+      out->graph_replays += 1;
+      out->graph_launches += 1;
+      out->kernel_launches += graph->nodes;
+    }
+  }
+  if (err == cudaSuccess) err = cudaEventRecord(s->ev_stop, s->stream);
+  const uint64_t bytes = static_cast<uint64_t>(context_steps) * sizeof(NervaCudaSyntheticTokenSlot);
+  if (err == cudaSuccess)
+    err = cudaMemcpyAsync(s->host_slots, s->device_slots, bytes, cudaMemcpyDeviceToHost, s->stream);
+  if (err == cudaSuccess)
+    err = cudaMemcpyAsync(s->host_error, s->device_error, sizeof(uint32_t), cudaMemcpyDeviceToHost, s->stream);
+  out->d2h_bytes = bytes + sizeof(uint32_t);
+  if (err == cudaSuccess) {
+    err = cudaStreamSynchronize(s->stream);
+    out->sync_calls += 1;
+  }
+  if (err != cudaSuccess) return fail(out, err);
+  if (device_error_set(s, out)) return -1;
+  float ms = 0.0f;
+  if (cudaEventElapsedTime(&ms, s->ev_start, s->ev_stop) == cudaSuccess && ms > 0.0f)
+    out->device_elapsed_ns = static_cast<uint64_t>(ms * 1.0e6f);
+  s->logits_valid = true;
+  const uint32_t output_start = request->prompt_token_count - 1u;
+  const NervaCudaSyntheticTokenSlot *slots = s->host_slots + output_start;
+  out->observed_tokens = observed_from_slots(request->steps, request->has_eos_token, request->eos_token, slots);
+  for (uint32_t i = 0; i < out->observed_tokens; ++i) request->output_tokens[i] = slots[i].token;
+  out->last_token = out->observed_tokens == 0 ? 0 : request->output_tokens[out->observed_tokens - 1];
+  out->observed_token_hash = hash_tokens(request->output_tokens, out->observed_tokens);
+  out->resident_kv_bytes = resident_kv_bytes(s);
+  out->kv_tokens = static_cast<uint64_t>(output_start) + out->observed_tokens;
+  out->device_arena_bytes = device_footprint(s);
+  out->pinned_host_bytes = s->slots_bytes;
+  out->hot_path_allocations = s->hot_path_allocations;
+  out->status = out->observed_tokens > 0 && slots_valid(slots, out->observed_tokens, output_start) ? 0 : -1;
+  return out->status == 0 ? 0 : -1;
+}
+
+// Clones an active session's KV cache, token ring, cursor and request state;
+// the device weights are shared (session_api_batch_fork_destroy.inc.cu:311+).
+extern "C" int nerva_cuda_hf_decode_sequence_session_fork_shared_weights(
+    const NervaCudaHfDecodeSequenceSessionForkSharedWeightsRequest *request,
+    NervaCudaHfDecodeSequenceSession **session_out,
+    NervaCudaHfDecodeSequenceSessionCreateResult *out) {
+  if (out == nullptr) return -1;
+  memset(out, 0, sizeof(*out));
+  out->status = -1;
+  if (session_out == nullptr) return -1;
+  *session_out = nullptr;
+  if (request == nullptr || request->parent == nullptr) {
+    out->failure_stage = kStageInvalidRequest;
+    return -1;
+  }
+  Session *parent = request->parent;
+  Session *s = new (std::nothrow) Session();
+  if (s == nullptr) {
+    out->cuda_error = static_cast<int32_t>(cudaErrorMemoryAllocation);
+    out->failure_stage = kStageSessionAlloc;
+    return -1;
+  }
+  s->dims = parent->dims;
+  s->max_context = parent->max_context;
+  s->rms_eps = parent->rms_eps;
+  s->rope_theta = parent->rope_theta;
+  s->sm_count = parent->sm_count;
+  s->engine = parent->engine;
+  s->detailed_profile = request->detailed_profile;
+  s->layout = parent->layout;
+  s->layer_meta = parent->layer_meta;
+  s->resident_weight_bytes = parent->resident_weight_bytes;
+  s->planned_weight_blocks = parent->planned_weight_blocks;
+  s->planned_gpu_resident_blocks = parent->planned_gpu_resident_blocks;
+  s->planned_gpu_staged_blocks = parent->planned_gpu_staged_blocks;
+  s->planned_weight_bytes = parent->planned_weight_bytes;
+  s->planned_gpu_resident_weight_bytes = parent->planned_gpu_resident_weight_bytes;
+  s->planned_gpu_staged_weight_bytes = parent->planned_gpu_staged_weight_bytes;
+  s->planned_weight_descriptor_count = parent->planned_weight_descriptor_count;
+  s->planned_weight_descriptor_hash = parent->planned_weight_descriptor_hash;
+  s->weights = parent->weights;
+  int32_t stage = kStageDeviceScratchAlloc;
+  cudaError_t err = allocate_state(s, &stage);
+  if (err != cudaSuccess) return create_fail(s, out, err, stage);
+  // The two state blocks have the same carve-up, so one copy clones KV, page
+  // table, ring, prompt and cursor.
+  err = cudaStreamSynchronize(parent->stream);
+  if (err == cudaSuccess)
+    err = cudaMemcpyAsync(s->state_block, parent->state_block, s->state_bytes, cudaMemcpyDeviceToDevice, s->stream);
+  if (err == cudaSuccess) err = cudaStreamSynchronize(s->stream);
+  if (err != cudaSuccess) return create_fail(s, out, err, kStageSetupSynchronize);
+  memcpy(s->host_slots, parent->host_slots, s->slots_bytes);
+  s->started = parent->started;
+  s->finished = parent->finished;
+  s->prompt_count = parent->prompt_count;
+  s->has_eos = parent->has_eos;
+  s->eos_token = parent->eos_token;
+  s->seed_token = parent->seed_token;
+  s->observed = parent->observed;
+  s->cursor = parent->cursor;
+  s->logits_valid = parent->logits_valid;
+  out->device_count = 1;
+  out->dtype = s->dims.dtype;
+  out->hidden = s->dims.hidden;
+  out->heads = s->dims.heads;
+  out->kv_heads = s->dims.kv_heads;
+  out->head_dim = s->dims.head_dim;
+  out->intermediate = s->dims.intermediate;
+  out->vocab_size = s->dims.vocab;
+  out->layer_count = s->dims.layers;
+  out->max_context_tokens = s->max_context;
+  out->resident_weight_bytes = s->resident_weight_bytes;
+  out->resident_kv_bytes = resident_kv_bytes(s);
+  out->device_arena_bytes = device_footprint(s);
+  out->pinned_host_bytes = s->slots_bytes;
+  out->head_threads = 128;
+  out->prefill_chunk_tokens = 1;
+  out->sync_calls = 2;
+  out->status = 0;
+  *session_out = s;
+  return 0;
+}
+
+// One-shot: create, run, destroy (session_api_oneshot.inc.cu).
+extern "C" int nerva_cuda_hf_decode_sequence_u16(const NervaCudaHfDecodeSequenceRequest *request,
+                                                 NervaCudaHfDecodeSequenceResult *out) {
+  if (out == nullptr) return -1;
+  memset(out, 0, sizeof(*out));
+  out->status = -1;
+  // weights.cu:232-262
+  if (request == nullptr || request->layers == nullptr || request->output_tokens == nullptr ||
+      request->prompt_tokens == nullptr || request->output_token_capacity < request->steps ||
+      request->layer_count == 0 || request->steps == 0 || request->prompt_token_count == 0 ||
+      request->vocab_size == 0 || request->seed_token >= request->vocab_size ||
+      !sampler_valid(request->sampler) ||
+      request->prompt_token_count > UINT32_MAX - request->steps + 1u)
+    return -1;
+  for (uint32_t i = 0; i < request->prompt_token_count; ++i) {
+    if (request->prompt_tokens[i] >= request->vocab_size) return -1;
+  }
+  if (request->prompt_tokens[request->prompt_token_count - 1u] != request->seed_token) return -1;
+  NervaCudaHfDecodeSequenceSessionCreateRequest create{};
+  create.dtype = request->dtype;
+  create.hidden = request->hidden;
+  create.heads = request->heads;
+  create.kv_heads = request->kv_heads;
+  create.head_dim = request->head_dim;
+  create.intermediate = request->intermediate;
+  create.vocab_size = request->vocab_size;
+  create.layer_count = request->layer_count;
+  create.max_context_tokens = request->prompt_token_count + request->steps - 1u;
+  create.rms_eps = request->rms_eps;
+  create.rope_theta = request->rope_theta;
+  create.embeddings = request->embeddings;
+  create.layers = request->layers;
+  create.final_norm_weight = request->final_norm_weight;
+  create.lm_head = request->lm_head;
+  create.planned_weight_blocks = request->planned_weight_blocks;
+  create.planned_gpu_resident_blocks = request->planned_gpu_resident_blocks;
+  create.planned_gpu_staged_blocks = request->planned_gpu_staged_blocks;
+  create.planned_weight_bytes = request->planned_weight_bytes;
+  create.planned_gpu_resident_weight_bytes = request->planned_gpu_resident_weight_bytes;
+  create.planned_gpu_staged_weight_bytes = request->planned_gpu_staged_weight_bytes;
+  create.planned_weight_descriptors = request->planned_weight_descriptors;
+  create.planned_weight_descriptor_count = request->planned_weight_descriptor_count;
+  create.planned_weight_descriptor_hash = request->planned_weight_descriptor_hash;
+  Session *s = nullptr;
+  NervaCudaHfDecodeSequenceSessionCreateResult created{};
+  if (nerva_cuda_hf_decode_sequence_session_create(&create, &s, &created) != 0) {
+    out->cuda_error = created.cuda_error;
+    out->device_count = created.device_count;
+    return -1;
+  }
+  NervaCudaHfDecodeSequenceSessionRunRequest run{};
+  run.session = s;
+  run.steps = request->steps;
+  run.seed_token = request->seed_token;
+  run.prompt_tokens = request->prompt_tokens;
+  run.prompt_token_count = request->prompt_token_count;
+  run.has_eos_token = request->has_eos_token;
+  run.eos_token = request->eos_token;
+  run.output_tokens = request->output_tokens;
+  run.output_token_capacity = request->output_token_capacity;
+  run.sampler = request->sampler;
+  const int rc = nerva_cuda_hf_decode_sequence_session_run(&run, out);
+  out->h2d_bytes += created.h2d_bytes;
+  out->descriptor_gpu_resident_h2d_bytes = created.descriptor_gpu_resident_h2d_bytes;
+  out->descriptor_gpu_staged_h2d_bytes = created.descriptor_gpu_staged_h2d_bytes;
+  destroy_session(s);
+  return rc;
+}
+
+// ------------------------------------------------------- additive exports ----
+
+extern "C" int nerva_b200_session_read_logits(Session *s, float *logits, uint32_t capacity) {
+  if (s == nullptr || logits == nullptr || capacity < s->dims.vocab || !s->logits_valid) return -1;
+  if (cudaStreamSynchronize(s->stream) != cudaSuccess) return -1;
+  return cudaMemcpy(logits, s->logits, static_cast<uint64_t>(s->dims.vocab) * 4u, cudaMemcpyDeviceToHost) ==
+                 cudaSuccess
+             ? 0
+             : -1;
+}
+
+extern "C" int nerva_b200_session_set_kv_block_table(Session *s, const uint32_t *table,
+                                                     uint32_t page_count) {
+  if (s == nullptr || table == nullptr || page_count != s->kv_pages || s->started) return -1;
+  std::vector<uint8_t> seen(page_count, 0);
+  for (uint32_t i = 0; i < page_count; ++i) {
+    if (table[i] >= page_count || seen[table[i]]) return -1;  // must be a permutation
+    seen[table[i]] = 1;
+  }
+  if (cudaMemcpy(s->page_table, table, static_cast<uint64_t>(page_count) * 4u, cudaMemcpyHostToDevice) !=
+      cudaSuccess)
+    return -1;
+  return 0;
+}
+
+extern "C" int nerva_b200_session_get_kv_block_table(Session *s, uint32_t *table, uint32_t capacity) {
+  if (s == nullptr || table == nullptr || capacity < s->kv_pages) return -1;
+  if (cudaStreamSynchronize(s->stream) != cudaSuccess) return -1;
+  return cudaMemcpy(table, s->page_table, static_cast<uint64_t>(s->kv_pages) * 4u, cudaMemcpyDeviceToHost) ==
+                 cudaSuccess
+             ? static_cast<int>(s->kv_pages)
+             : -1;
+}
+
+extern "C" int nerva_b200_session_read_kv_row(Session *s, uint32_t layer, uint32_t token,
+                                              uint32_t which, uint16_t *row, uint32_t capacity) {
+  if (s == nullptr || row == nullptr || layer >= s->dims.layers || token >= s->max_context ||
+      which > 1 || capacity < s->dims.kv_hidden())
+    return -1;
+  if (cudaStreamSynchronize(s->stream) != cudaSuccess) return -1;
+  uint32_t physical = 0;
+  if (cudaMemcpy(&physical, s->page_table + token / NERVA_KV_CACHE_BLOCK_TOKENS, 4, cudaMemcpyDeviceToHost) !=
+      cudaSuccess)
+    return -1;
+  // hf_decode_sequence/types.cuh:328-337
+  const uint64_t offset = ((static_cast<uint64_t>(layer) * s->kv_pages + physical) * NERVA_KV_CACHE_BLOCK_TOKENS +
+                           token % NERVA_KV_CACHE_BLOCK_TOKENS) * s->dims.kv_hidden();
+  const uint16_t *src = (which == 0 ? s->kv_keys : s->kv_values) + offset;
+  return cudaMemcpy(row, src, s->dims.kv_hidden() * 2u, cudaMemcpyDeviceToHost) == cudaSuccess ? 0 : -1;
+}

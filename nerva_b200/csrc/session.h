@@ -1,0 +1,137 @@
+// Resident decode session: everything a session owns on the host and on the
+// device.  Mirrors the role of the reference's
+// hf_decode_sequence/session_state.cuh:1-222 (device pointers, cached graphs,
+// cursor, token ring) with a different memory plan: two device allocations per
+// session (shared weights, private state), each carved by a StaticArena, and
+// nothing allocated after create.
+#pragma once
+
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include <memory>
+#include <string>
+#include <vector>
+
+#include "../../include/nerva_b200_api.h"
+#include "host_memory.h"
+#include "kernels.cuh"
+
+namespace nb {
+
+constexpr uint64_t kMissingOffset = UINT64_MAX;
+
+// Offsets (16-bit elements) of one layer's tensors in the upload arena; the
+// order is the reference's pack_layer (hf_decode_sequence/weights.cu:487-591).
+struct LayerLayout {
+  uint64_t rms_attn = kMissingOffset, rms_mlp = kMissingOffset;
+  uint64_t w_q = kMissingOffset, w_q_gate = kMissingOffset, q_norm = kMissingOffset;
+  uint64_t w_k = kMissingOffset, k_norm = kMissingOffset, w_v = kMissingOffset;
+  uint64_t w_o = kMissingOffset;
+  uint64_t w_gate = kMissingOffset, w_up = kMissingOffset, w_down = kMissingOffset;
+  uint64_t w_router = kMissingOffset, w_expert_gate_up = kMissingOffset;
+  uint64_t w_expert_down = kMissingOffset;
+  uint64_t w_shared_gate = kMissingOffset, w_shared_up = kMissingOffset;
+  uint64_t w_shared_down = kMissingOffset, w_shared_router = kMissingOffset;
+  uint64_t q_bias = kMissingOffset, k_bias = kMissingOffset, v_bias = kMissingOffset;
+  uint64_t o_bias = kMissingOffset;
+  uint32_t mlp_kind = 0, moe_intermediate = 0, shared_intermediate = 0;
+  uint32_t num_experts = 0, top_k = 0, norm_topk_prob = 0;
+};
+
+struct ArenaLayout {
+  uint64_t embeddings = 0, input = 0, scratch = 0, final_norm = 0, lm_head = 0;
+  uint64_t elements = 0;
+  std::vector<LayerLayout> layers;
+};
+
+struct ModelDims {
+  uint32_t dtype = 0, hidden = 0, heads = 0, kv_heads = 0, head_dim = 0;
+  uint32_t intermediate = 0, vocab = 0, layers = 0;
+  uint64_t attention_hidden() const { return static_cast<uint64_t>(heads) * head_dim; }
+  uint64_t kv_hidden() const { return static_cast<uint64_t>(kv_heads) * head_dim; }
+};
+
+bool valid_layer(const NervaCudaHfDecodeChainLayer &layer, bool require_sources);
+bool layer_supported(const NervaCudaHfDecodeChainLayer &layer);
+ArenaLayout compute_arena_layout(const ModelDims &dims, const NervaCudaHfDecodeChainLayer *layers);
+uint64_t hash_tokens(const uint32_t *tokens, uint32_t count);
+uint64_t hash_weight_descriptors(const NervaCudaHfDecodeSequenceWeightBlock *blocks, uint32_t count);
+void set_last_error(const std::string &text);
+
+// Device weights shared between a session and its forks.
+struct SharedWeights {
+  void *block = nullptr;  // one allocation
+  uint64_t block_bytes = 0;
+  uint16_t *arena = nullptr;          // upload arena (reference layout)
+  uint16_t *qkv_packed = nullptr;     // [layers][(A + 2 KV) x H]
+  uint16_t *gate_up_packed = nullptr; // [layers][2 I x H], rows interleaved gate/up
+  ~SharedWeights() {
+    if (block != nullptr) cudaFree(block);
+  }
+};
+
+struct GraphEntry {
+  uint32_t prompt_count = 0, splits = 0, sample = 0, engine = 0;
+  cudaGraph_t graph = nullptr;
+  cudaGraphExec_t exec = nullptr;
+  uint64_t nodes = 0;
+};
+
+}  // namespace nb
+
+// The opaque handle of the C ABI.
+struct NervaCudaHfDecodeSequenceSession {
+  nb::ModelDims dims;
+  uint32_t max_context = 0;
+  float rms_eps = 0.0f, rope_theta = 0.0f;
+  uint32_t sm_count = 0;
+  uint32_t engine = 0;
+  uint32_t detailed_profile = 0;
+  nb::ArenaLayout layout;
+  std::vector<NervaCudaHfDecodeChainLayer> layer_meta;  // scalars only; pointers cleared
+
+  // planned-weight echo
+  uint64_t resident_weight_bytes = 0;
+  uint32_t planned_weight_blocks = 0, planned_gpu_resident_blocks = 0, planned_gpu_staged_blocks = 0;
+  uint64_t planned_weight_bytes = 0, planned_gpu_resident_weight_bytes = 0;
+  uint64_t planned_gpu_staged_weight_bytes = 0;
+  uint32_t planned_weight_descriptor_count = 0;
+  uint64_t planned_weight_descriptor_hash = 0;
+
+  std::shared_ptr<nb::SharedWeights> weights;
+  nb::StaticArena weight_arena, state_arena;
+  nb::KvPagePool kv_pool;
+
+  // private device state (one allocation)
+  void *state_block = nullptr;
+  uint64_t state_bytes = 0;
+  uint16_t *kv_keys = nullptr, *kv_values = nullptr;  // [layers][pages][16][kv_hidden]
+  uint64_t kv_layer_elems = 0;
+  uint32_t kv_pages = 0;
+  uint32_t *page_table = nullptr;
+  float *h_a = nullptr, *h_b = nullptr, *qkv = nullptr, *o_out = nullptr, *down = nullptr;
+  float *logits = nullptr;
+  float *partial_acc = nullptr, *partial_m = nullptr, *partial_l = nullptr;
+  uint32_t max_splits = 1;
+  uint16_t *attn_bf16 = nullptr, *ff_bf16 = nullptr, *x_scratch = nullptr;
+  float *best_value = nullptr;
+  uint32_t *best_index = nullptr;
+  NervaCudaSyntheticTokenSlot *device_slots = nullptr;
+  uint32_t *device_cursor = nullptr, *device_error = nullptr, *device_prompt = nullptr;
+  uint64_t slots_bytes = 0;
+
+  NervaCudaSyntheticTokenSlot *host_slots = nullptr;  // pinned
+  uint32_t *host_error = nullptr;                     // pinned, 1 word
+
+  cudaStream_t stream = nullptr;
+  cudaEvent_t ev_start = nullptr, ev_stop = nullptr;
+  std::vector<nb::GraphEntry> graphs;
+
+  // active request
+  bool started = false, finished = false;
+  uint32_t prompt_count = 0, has_eos = 0, eos_token = 0, seed_token = 0;
+  uint32_t observed = 0, cursor = 0;
+  bool logits_valid = false;
+  uint64_t hot_path_allocations = 0;
+};
