@@ -1,0 +1,309 @@
+"""Decode benchmark of the resident decode step.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--config qwen3-8b|tiny]
+
+Workload (N = 1): Qwen3-8B architecture, random-init BF16 weights ~N(0, 0.02) seed 0,
+512-token seeded prompt, batch 1 greedy decode.  A "step" is one decoded token
+(one replay of the resident step).  Prints ONE JSON line on rank 0.
+
+  value     decode tok/s from CUDA events on the session stream around K graph replays,
+            inputs (weights, KV, previous token) resident in HBM
+  e2e       the same metric through the C ABI the way a streaming server calls it:
+            one session_advance(steps=1) per token, host wall clock, device->host copy
+            of the token slot and a stream synchronise inside every step
+  roofline  the projection kernel (all five shapes): algorithmic weight+vector bytes
+            per token / its summed device time per token, from an event-per-launch
+            pass run after the timed region
+  cpu_baseline / --impl reference: the CPU restatement of the reference decoder on
+            the host cores (bounded sample)
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+import numpy as np  # noqa: E402
+
+METRIC = "Qwen3-8B-arch BF16 batch-1 decode tok/s"
+UNIT = "tok/s"
+
+
+def measured_peaks() -> dict:
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        with open(path) as f:
+            peaks = json.load(f)
+        return {"hbm_gbs": float(peaks["hbm_gbs"]), "source": "measured"}
+    return {"hbm_gbs": 6650.0, "source": "fallback"}
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
+
+    QUERY = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+             "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+             "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index: int = 0):
+        self.gpu_index = gpu_index
+        self.lines: list[str] = []
+        self.proc = None
+        self.thread = None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--id={self.gpu_index}", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits",
+                 "-lms", "100"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+        except OSError:
+            self.proc = None
+            return
+        self.thread = threading.Thread(target=self._pump, daemon=True)
+        self.thread.start()
+
+    def _pump(self):
+        for line in self.proc.stdout:
+            self.lines.append(line.strip())
+
+    def stop(self) -> dict:
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+        sm, sm_max, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for line in self.lines:
+            parts = [p.strip() for p in line.split(",")]
+            if len(parts) < 9:
+                continue
+            try:
+                sm.append(float(parts[1]))
+                sm_max.append(float(parts[2]))
+            except ValueError:
+                continue
+            for name, flag in zip(names, parts[5:9]):
+                if flag.lower().startswith("active"):
+                    reasons.add(name)
+        return {"sm_mhz": float(np.median(sm)) if sm else None, "sm_max_mhz": max(sm_max) if sm_max else None,
+                "samples": len(sm), "reasons": sorted(reasons)}
+
+
+def workload(name: str):
+    from nerva_b200 import synth
+    if name == "tiny":
+        return synth.TINY_QWEN3
+    return synth.QWEN3_8B
+
+
+def config_block(cfg, gpus: int, extra: dict | None = None) -> dict:
+    block = {
+        "workload": f"{cfg.name}: {cfg.layers} layers, hidden {cfg.hidden}, {cfg.heads}q/{cfg.kv_heads}kv heads, "
+                    f"head_dim {cfg.head_dim}, intermediate {cfg.intermediate}, vocab {cfg.vocab}; batch 1, "
+                    f"{cfg.prompt_tokens}-token seeded prompt, greedy decode",
+        "weights": "random-init bf16 ~N(0,0.02) seed 0, unit norm weights, untied lm_head (synthetic)",
+        "bytes_per_token": cfg.projection_bytes_per_token(),
+        "l2": "each step streams the full weight set (far larger than the 126 MB L2); no flush needed",
+        "parallelism": "single GPU" if gpus == 1 else f"{gpus} independent replicas (no tensor parallel engine yet)",
+    }
+    if extra:
+        block.update(extra)
+    return block
+
+
+def cpu_decode_sample(ck, cfg, budget_s: float, max_tokens: int, prompt_len: int = 2):
+    """Times the CPU restatement of the reference decoder (oracle, CPU contract) on a
+    short prompt: returns (tok/s over the decode tokens, tokens timed, threads)."""
+    from nerva_b200 import synth
+    from oracle import oracle as O
+    dec = O.Decoder(ck, prompt_len + max_tokens + 1, mode=O.MODE_CPU)
+    prompt = synth.prompt_ids(cfg, count=prompt_len)
+    for t in prompt[:-1]:
+        dec.step(int(t), want_logits=False)
+    token = int(prompt[-1])
+    done, elapsed = 0, 0.0
+    while done < max_tokens and (done == 0 or elapsed + elapsed / done < budget_s):
+        t0 = time.perf_counter()
+        logits = dec.step(token)
+        token = O.argmax(logits, O.MODE_CPU)
+        elapsed += time.perf_counter() - t0
+        done += 1
+    threads = O.lib().oracle_get_threads()
+    dec.close()
+    return done / elapsed, done, threads
+
+
+def run_reference(args, cfg) -> dict:
+    """The reference's own CPU implementation of the path (the C restatement of its
+    Rust decoder; the Rust original cannot be compiled on this image), on all host
+    threads.  Each step is one decoded token of the same model; steps stop early
+    when the wall-clock budget is spent."""
+    from nerva_b200 import ops, synth
+    ck = synth.dense_checkpoint(cfg, fill=ops.synth_normal_bf16)
+    budget = float(os.environ.get("NERVA_REFERENCE_BUDGET_S", "150"))
+    warm_rate, _, threads = cpu_decode_sample(ck, cfg, budget_s=0.0, max_tokens=max(1, min(args.warmup, 1)))
+    rate, done, threads = cpu_decode_sample(ck, cfg, budget_s=budget, max_tokens=args.steps)
+    sample = (f"{done} of {args.steps} requested decode steps of the full model after a 2-token prompt "
+              f"(stops at a {budget:.0f} s budget), {threads} threads")
+    return {
+        "impl": "reference", "metric": METRIC, "value": rate, "unit": UNIT, "n_gpus": args.gpus,
+        "steps": done, "warmup": 1, "ms_per_step": 1000.0 / rate, "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "bf16", "data": "synthetic", "config": config_block(cfg, 1),
+        "cpu_baseline": {"value": rate, "unit": UNIT, "cores": threads, "kind": "port", "sample": sample},
+        "e2e": {"value": rate, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+
+
+def run_ours(args, cfg, rank: int, world: int) -> dict:
+    from nerva_b200 import build, ops, synth
+    from nerva_b200.session import CudaHfDecodeSequenceLoop, CudaHfDecodeSequenceSession, SmokeStatus
+    build.build()
+    t0 = time.perf_counter()
+    ck = synth.dense_checkpoint(cfg, fill=ops.synth_normal_bf16)
+    gen_s = time.perf_counter() - t0
+    prompt = synth.prompt_ids(cfg)
+    profile_steps = 4
+    max_context = cfg.prompt_tokens + 1 + args.warmup + 2 * args.steps + profile_steps + 8
+    t0 = time.perf_counter()
+    session = CudaHfDecodeSequenceSession(ck, max_context)
+    if session.status != SmokeStatus.OK:
+        raise RuntimeError(f"session create failed: {session.status} {session.error}")
+    create_s = time.perf_counter() - t0
+    t0 = time.perf_counter()
+    start, loop = CudaHfDecodeSequenceLoop.start(session, prompt)
+    if start.status != SmokeStatus.OK:
+        raise RuntimeError(f"session start failed: {start.error}")
+    prefill_s = time.perf_counter() - t0
+    first = loop.advance(1)                      # the token the prefill produced (no replay)
+    warm = loop.advance(max(args.warmup, 3))     # untimed warm-up replays
+    if warm.status != SmokeStatus.OK:
+        raise RuntimeError(f"warm-up failed: {warm.error}")
+
+    sync = _barrier_fn(world)
+    clocks = ClockSampler(int(os.environ.get("NERVA_GPU_INDEX", "0")))
+    clocks.start()
+    sync()
+    timed = loop.advance(args.steps)             # K graph replays, timed by CUDA events on the session stream
+    sync()
+    if timed.status != SmokeStatus.OK or len(timed.tokens) != args.steps:
+        raise RuntimeError(f"timed advance failed: {timed.error}")
+    device_s = timed.device_elapsed_ns * 1e-9
+    # end to end: one C-ABI call per token, host clock, D2H of the slot + synchronise each step
+    t0 = time.perf_counter()
+    e2e_tokens = 0
+    for _ in range(args.steps):
+        out = loop.advance(1)
+        e2e_tokens += len(out.tokens)
+    e2e_s = time.perf_counter() - t0
+    clock_info = clocks.stop()
+    # per-kernel pass: events between launch groups, un-captured
+    prof = session.profile_steps(profile_steps)
+    session.destroy()
+
+    device_s = _max_over_ranks(device_s, world)
+    e2e_s = _max_over_ranks(e2e_s, world)
+    proj_ns = sum(prof[k]["ns"] for k in ("qkv", "o", "gate_up", "down", "lm_head")) / profile_steps
+    proj_launches = sum(prof[k]["launches_per_step"] for k in ("qkv", "o", "gate_up", "down", "lm_head"))
+    bytes_per_token = cfg.projection_bytes_per_token() + 2 * cfg.hidden * (3 * cfg.layers + 1)  # + bf16 vectors
+    peaks = measured_peaks()
+    achieved = bytes_per_token / (proj_ns * 1e-9) / 1e9
+    value = world * args.steps / device_s
+    result = {
+        "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
+        "warmup": max(args.warmup, 3), "ms_per_step": 1000.0 * device_s / args.steps, "higher_is_better": True,
+        "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+        "config": config_block(cfg, world, {"timed_context": f"{cfg.prompt_tokens + 1 + max(args.warmup, 3)}.."
+                                                              f"{cfg.prompt_tokens + 1 + max(args.warmup, 3) + args.steps}"}),
+        "clocks": clock_info,
+        "e2e": {"value": world * e2e_tokens / e2e_s, "unit": UNIT, "h2d_bytes_per_step": 0,
+                "d2h_bytes_per_step": 44,
+                "note": "session_advance(steps=1) per token with host buffers; the ABI keeps the previous token on "
+                        "the device, so a step has no host input; the prompt (4 B/token) is copied once in "
+                        "session_start"},
+        "gpu_launches": int(timed.kernel_launches),
+        "roofline": {
+            "bound": "hbm", "kernel": "projection_stream_kernel (QKV, O, gate-up, down, lm_head)",
+            "achieved": achieved, "peak": peaks["hbm_gbs"], "unit": "GB/s", "frac": achieved / peaks["hbm_gbs"],
+            "peak_source": peaks["source"], "traffic": None,
+            "launches_per_token": proj_launches, "bytes_per_token": bytes_per_token,
+            "us_per_token": proj_ns / 1e3,
+            "whole_step_frac": (bytes_per_token * args.steps / device_s / 1e9) / peaks["hbm_gbs"],
+        },
+        "profile_us_per_token": {k: v["ns"] / profile_steps / 1e3 for k, v in prof.items()},
+        "setup_s": {"generate_weights": gen_s, "session_create": create_s, "prefill_by_decode": prefill_s},
+        "graph_nodes": int(timed.graph_nodes),
+        "token_hash": f"{timed.observed_token_hash:016x}",
+    }
+    if rank == 0 and world == 1 and not args.no_cpu_baseline:
+        rate, done, threads = cpu_decode_sample(ck, cfg, budget_s=float(os.environ.get("NERVA_CPU_BUDGET_S", "20")),
+                                                max_tokens=8)
+        result["cpu_baseline"] = {
+            "value": rate, "unit": UNIT, "cores": threads, "kind": "port",
+            "sample": f"{done} decode steps of the full model after a 2-token prompt (CPU restatement of the "
+                      f"reference decoder, row-parallel mat-vec)"}
+    return result
+
+
+def _barrier_fn(world: int):
+    if world == 1:
+        return lambda: None
+    import torch.distributed as dist
+    return dist.barrier
+
+
+def _max_over_ranks(value: float, world: int) -> float:
+    if world == 1:
+        return value
+    import torch
+    import torch.distributed as dist
+    t = torch.tensor([value], dtype=torch.float64)
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    return float(t.item())
+
+
+def main() -> None:
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=128)
+    ap.add_argument("--warmup", type=int, default=8)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--config", default="qwen3-8b", choices=["qwen3-8b", "tiny"])
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    args = ap.parse_args()
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    cfg = workload(args.config)
+    if args.impl == "reference":
+        if rank == 0:
+            print(json.dumps(run_reference(args, cfg)), flush=True)
+        return
+    if world > 1:
+        # one process per GPU: this rank sees only its own device
+        os.environ["NERVA_GPU_INDEX"] = os.environ.get("CUDA_VISIBLE_DEVICES", ",".join(map(str, range(world)))).split(",")[local]
+        os.environ["CUDA_VISIBLE_DEVICES"] = os.environ["NERVA_GPU_INDEX"]
+        import torch.distributed as dist
+        dist.init_process_group("gloo")
+    result = run_ours(args, cfg, rank, world)
+    if world > 1:
+        import torch.distributed as dist
+        dist.barrier()
+        dist.destroy_process_group()
+    if rank == 0:
+        print(json.dumps(result), flush=True)
+
+
+if __name__ == "__main__":
+    main()

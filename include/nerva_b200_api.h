@@ -622,6 +622,16 @@ int nerva_b200_session_read_kv_row(NervaCudaHfDecodeSequenceSession *session, ui
                                    uint32_t token, uint32_t which, uint16_t *row,
                                    uint32_t capacity);
 
+/* Runs `steps` further decode steps of the active request un-captured, with a
+ * CUDA event between operator groups, and returns summed device nanoseconds per
+ * bucket: 0 embedding, 1 QKV projection, 2 attention (q/k norm + RoPE + KV
+ * append + split-KV + merge), 3 O projection, 4 gate/up projection, 5 down
+ * projection, 6 lm_head projection, 7 sampling.  bucket_launches (nullable)
+ * receives kernel launches per bucket per step.  The sequence advances. */
+int nerva_b200_session_profile_steps(NervaCudaHfDecodeSequenceSession *session, uint32_t steps,
+                                     uint64_t *bucket_ns, uint32_t *bucket_launches,
+                                     uint32_t bucket_capacity);
+
 /* Isolated projection: y[m][n] = sum_k W[n][k] * x[m][k], bf16 in, fp32
  * accumulate and out.  All pointers are HOST memory; the call copies in, runs
  * `iterations` launches after `warmup` untimed ones, and copies y back.

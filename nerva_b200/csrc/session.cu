@@ -291,14 +291,31 @@ const uint16_t *arena_at(Session *s, uint64_t offset) {
 // then lm_head (final norm in front, arg-max partials behind) and the sampler.
 // Same operator order as the reference step
 // (hf_decode_sequence/session_decode_prefill.inc.cu:74-372).
-cudaError_t enqueue_step(Session *s, uint32_t splits, uint32_t sample, uint64_t *launches) {
+// Records the next profile event; the interval that ends here gets `bucket`.
+static void profile_mark(Session *s, StepProfile *prof, uint32_t bucket) {
+  if (prof == nullptr) return;
+  if (prof->used >= prof->events.size()) {
+    cudaEvent_t e = nullptr;
+    if (cudaEventCreate(&e) != cudaSuccess) return;
+    prof->events.push_back(e);
+    prof->bucket.push_back(0);
+  }
+  cudaEventRecord(prof->events[prof->used], s->stream);
+  if (prof->used > 0) prof->bucket[prof->used - 1] = bucket;
+  prof->used += 1;
+}
+
+cudaError_t enqueue_step(Session *s, uint32_t splits, uint32_t sample, uint64_t *launches,
+                         StepProfile *prof = nullptr) {
   const ModelDims &d = s->dims;
   const StepState st = step_state(s);
   const uint64_t ah = d.attention_hidden(), kvh = d.kv_hidden();
   const uint64_t qkv_rows = ah + 2 * kvh;
   uint64_t n = 0;
+  profile_mark(s, prof, kBucketEmbed);
   cudaError_t err = launch_embed(s->stream, st, arena_at(s, s->layout.embeddings), d.hidden, s->h_b);
   n += 1;
+  profile_mark(s, prof, kBucketEmbed);
   for (uint32_t l = 0; err == cudaSuccess && l < d.layers; ++l) {
     const LayerLayout &L = s->layout.layers[l];
     ProjectionParams p{};
@@ -318,6 +335,7 @@ cudaError_t enqueue_step(Session *s, uint32_t splits, uint32_t sample, uint64_t 
     p.out_f32 = s->qkv;
     err = launch_projection(s->stream, p, s->sm_count);
     n += 1;
+    profile_mark(s, prof, kBucketQkv);
     if (err != cudaSuccess) break;
 
     QkvPrepareParams qp{};
@@ -359,6 +377,7 @@ cudaError_t enqueue_step(Session *s, uint32_t splits, uint32_t sample, uint64_t 
     ap.error_word = s->device_error;
     err = launch_attention(s->stream, ap);
     n += 2;
+    profile_mark(s, prof, kBucketAttention);
     if (err != cudaSuccess) break;
 
     // O
@@ -374,6 +393,7 @@ cudaError_t enqueue_step(Session *s, uint32_t splits, uint32_t sample, uint64_t 
     p.out_f32 = s->o_out;
     err = launch_projection(s->stream, p, s->sm_count);
     n += 1;
+    profile_mark(s, prof, kBucketO);
     if (err != cudaSuccess) break;
 
     // gate/up + SwiGLU
@@ -394,6 +414,7 @@ cudaError_t enqueue_step(Session *s, uint32_t splits, uint32_t sample, uint64_t 
     p.out_bf16 = s->ff_bf16;
     err = launch_projection(s->stream, p, s->sm_count);
     n += 1;
+    profile_mark(s, prof, kBucketGateUp);
     if (err != cudaSuccess) break;
 
     // down
@@ -409,6 +430,7 @@ cudaError_t enqueue_step(Session *s, uint32_t splits, uint32_t sample, uint64_t 
     p.out_f32 = s->down;
     err = launch_projection(s->stream, p, s->sm_count);
     n += 1;
+    profile_mark(s, prof, kBucketDown);
   }
   uint32_t partials = 0;
   if (err == cudaSuccess && sample != 0) {
@@ -431,10 +453,12 @@ cudaError_t enqueue_step(Session *s, uint32_t splits, uint32_t sample, uint64_t 
     partials = projection_blocks(p, s->sm_count);
     err = launch_projection(s->stream, p, s->sm_count);
     n += 1;
+    profile_mark(s, prof, kBucketLmHead);
   }
   if (err == cudaSuccess) {
     err = launch_sample_greedy(s->stream, st, s->best_value, s->best_index, partials, sample);
     n += 1;
+    profile_mark(s, prof, kBucketSampling);
   }
   if (launches != nullptr) *launches = n;
   return err;
@@ -1491,4 +1515,50 @@ extern "C" int nerva_b200_session_read_kv_row(Session *s, uint32_t layer, uint32
                            token % NERVA_KV_CACHE_BLOCK_TOKENS) * s->dims.kv_hidden();
   const uint16_t *src = (which == 0 ? s->kv_keys : s->kv_values) + offset;
   return cudaMemcpy(row, src, s->dims.kv_hidden() * 2u, cudaMemcpyDeviceToHost) == cudaSuccess ? 0 : -1;
+}
+
+// Runs `steps` further decode steps of the active request outside any graph,
+// with a CUDA event between launch groups, and sums the device time per
+// operator bucket (the reference's detailed_profile path,
+// session_decode_prefill.inc.cu:374-810, fills the same buckets).  The steps are
+// real: the sequence advances by `steps` tokens.
+extern "C" int nerva_b200_session_profile_steps(Session *s, uint32_t steps, uint64_t *bucket_ns,
+                                                uint32_t *bucket_launches, uint32_t bucket_capacity) {
+  if (s == nullptr || bucket_ns == nullptr || bucket_capacity < kBucketCount || steps == 0) return -1;
+  if (!s->started || s->finished) return -1;
+  const uint64_t target = static_cast<uint64_t>(s->cursor) + steps;
+  if (target > s->max_context) return -1;
+  for (uint32_t b = 0; b < bucket_capacity; ++b) {
+    bucket_ns[b] = 0;
+    if (bucket_launches != nullptr) bucket_launches[b] = 0;
+  }
+  static const uint32_t kLaunchesPerMark[kBucketCount] = {1, 1, 3, 1, 1, 1, 1, 1};
+  StepProfile prof;
+  const uint32_t splits = splits_for(s, static_cast<uint32_t>(target));
+  cudaError_t err = cudaSuccess;
+  for (uint32_t step = 0; err == cudaSuccess && step < steps; ++step) {
+    prof.used = 0;
+    uint64_t launches = 0;
+    err = enqueue_step(s, splits, 1, &launches, &prof);
+    if (err == cudaSuccess) err = cudaStreamSynchronize(s->stream);
+    for (uint32_t i = 0; err == cudaSuccess && i + 1 < prof.used; ++i) {
+      float ms = 0.0f;
+      if (cudaEventElapsedTime(&ms, prof.events[i], prof.events[i + 1]) != cudaSuccess) continue;
+      const uint32_t b = prof.bucket[i];
+      bucket_ns[b] += static_cast<uint64_t>(ms * 1.0e6f);
+      if (bucket_launches != nullptr && step == 0) bucket_launches[b] += kLaunchesPerMark[b];
+    }
+  }
+  for (cudaEvent_t e : prof.events) cudaEventDestroy(e);
+  if (err == cudaSuccess)
+    err = cudaMemcpy(s->host_slots + s->cursor - 0, s->device_slots + s->cursor,
+                     static_cast<uint64_t>(steps) * sizeof(NervaCudaSyntheticTokenSlot), cudaMemcpyDeviceToHost);
+  if (err != cudaSuccess) {
+    set_last_error(cudaGetErrorString(err));
+    return -1;
+  }
+  s->observed += steps;
+  s->cursor = static_cast<uint32_t>(target);
+  s->logits_valid = true;
+  return 0;
 }

@@ -71,6 +71,18 @@ struct SharedWeights {
   }
 };
 
+// Event-per-launch-group timing of un-captured steps (the reference's
+// detailed_profile path, hf_decode_sequence/session_decode_prefill.inc.cu:374-810).
+enum ProfileBucket : uint32_t {
+  kBucketEmbed = 0, kBucketQkv, kBucketAttention, kBucketO, kBucketGateUp, kBucketDown,
+  kBucketLmHead, kBucketSampling, kBucketCount
+};
+struct StepProfile {
+  std::vector<cudaEvent_t> events;
+  std::vector<uint32_t> bucket;  // bucket[i] labels the interval events[i] -> events[i+1]
+  uint32_t used = 0;
+};
+
 struct GraphEntry {
   uint32_t prompt_count = 0, splits = 0, sample = 0, engine = 0;
   cudaGraph_t graph = nullptr;

@@ -1,0 +1,77 @@
+"""Per-operator entry points of libnerva_b200.so (host buffers in, host buffers out)."""
+from __future__ import annotations
+
+import ctypes as C
+
+import numpy as np
+
+from . import ffi
+
+
+def _check(rc: int, what: str) -> None:
+    if rc != 0:
+        raise RuntimeError(f"{what} failed: {ffi.last_error() or 'rejected arguments'}")
+
+
+def projection(weight_bits: np.ndarray, x_bits: np.ndarray, rows: int, cols: int, tokens: int = 1,
+               warmup: int = 0, iterations: int = 1):
+    """y[m][n] = sum_k W[n][k] x[m][k]; bf16 bits in, fp32 out.  Returns (y, avg_ns)."""
+    w = np.ascontiguousarray(weight_bits, dtype=np.uint16)
+    x = np.ascontiguousarray(x_bits, dtype=np.uint16)
+    assert w.size == rows * cols and x.size == tokens * cols
+    y = np.empty((tokens, rows), dtype=np.float32)
+    ns = C.c_uint64(0)
+    _check(ffi.lib().nerva_b200_projection(w.ctypes.data, x.ctypes.data, y.ctypes.data, rows, cols, tokens,
+                                           warmup, iterations, C.byref(ns)), "projection")
+    return y, ns.value
+
+
+def gqa_decode_attention(q: np.ndarray, key_pages: np.ndarray, value_pages: np.ndarray, page_table: np.ndarray,
+                         batch: int, context: int, heads: int, kv_heads: int, head_dim: int,
+                         warmup: int = 0, iterations: int = 1):
+    """Paged GQA decode attention for `batch` sequences.  Returns (out f32 [batch, heads*d], avg_ns)."""
+    q = np.ascontiguousarray(q, dtype=np.float32)
+    k = np.ascontiguousarray(key_pages, dtype=np.uint16)
+    v = np.ascontiguousarray(value_pages, dtype=np.uint16)
+    t = np.ascontiguousarray(page_table, dtype=np.uint32)
+    pages = (context + 15) // 16
+    assert q.size == batch * heads * head_dim
+    assert k.size == v.size == batch * pages * 16 * kv_heads * head_dim and t.size == batch * pages
+    out = np.empty((batch, heads * head_dim), dtype=np.float32)
+    ns = C.c_uint64(0)
+    _check(ffi.lib().nerva_b200_gqa_decode_attention(q.ctypes.data, k.ctypes.data, v.ctypes.data, t.ctypes.data,
+                                                     out.ctypes.data, batch, context, heads, kv_heads, head_dim,
+                                                     warmup, iterations, C.byref(ns)), "gqa_decode_attention")
+    return out, ns.value
+
+
+def greedy_argmax(logits: np.ndarray) -> int:
+    logits = np.ascontiguousarray(logits, dtype=np.float32)
+    token = C.c_uint32(0)
+    _check(ffi.lib().nerva_b200_greedy_argmax(logits.ctypes.data, logits.size, C.byref(token)), "greedy_argmax")
+    return token.value
+
+
+def projection_bench(rows: int, cols: int, iterations: int = 20, warmup: int = 5, block_tokens: int = 0,
+                     dtype: int = 1):
+    req = ffi.ProjectionBenchRequest(dtype=dtype, rows=rows, cols=cols, iterations=iterations,
+                                     warmup_iterations=warmup, block_tokens=block_tokens)
+    out = ffi.ProjectionBenchResult()
+    rc = ffi.lib().nerva_cuda_projection_bench(C.byref(req), C.byref(out))
+    return rc, out
+
+
+def synth_normal_bf16(seed: int, tensor_id: int, count: int, std: float) -> np.ndarray:
+    """Multi-threaded native twin of nerva_b200.synth.normal_bf16 (same bits)."""
+    out = np.empty(count, dtype=np.uint16)
+    ffi.lib().nerva_b200_synth_normal_bf16(seed, tensor_id, count, std, out.ctypes.data)
+    return out
+
+
+def plan_layout(cfg, layers, layer_index: int = 0):
+    req = ffi.LayoutPlanRequest(hidden=cfg.hidden, heads=cfg.heads, kv_heads=cfg.kv_heads, head_dim=cfg.head_dim,
+                                intermediate=cfg.intermediate, vocab_size=cfg.vocab, layer_count=cfg.layers,
+                                layer_index=layer_index, layers=C.cast(layers, C.c_void_p))
+    out = ffi.LayoutPlanResult()
+    rc = ffi.lib().nerva_cuda_hf_decode_sequence_plan_layout(C.byref(req), C.byref(out))
+    return rc, out
