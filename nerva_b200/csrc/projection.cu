@@ -6,6 +6,7 @@
 //   epilogue  SwiGLU -> bf16                    (kernels.cu:597-612)
 //             per-block greedy arg-max partials (sampler.cu:89-119)
 #include "kernels.cuh"
+#include "step_device.cuh"
 #include "weight_stream.cuh"
 
 namespace nb {
@@ -87,22 +88,8 @@ __global__ void __launch_bounds__(kStreamThreads, 1) projection_stream_kernel(Pr
     uint4 *dst = reinterpret_cast<uint4 *>(x);
     for (uint32_t i = threadIdx.x; i < p.cols / 8u; i += blockDim.x) dst[i] = src[i];
   } else {
-    float sumsq = 0.0f;
-    for (uint32_t i = threadIdx.x; i < p.cols; i += blockDim.x) {
-      float r = p.add_a[i];
-      if (p.add_b != nullptr) r += p.add_b[i];
-      if (p.add_bias != nullptr) r += bf16_bits_to_f32(p.add_bias[i]);
-      sumsq += r * r;
-    }
-    const float total = block_sum(sumsq, scratch);
-    const float scale = rsqrtf(total / static_cast<float>(p.cols) + p.eps);
-    for (uint32_t i = threadIdx.x; i < p.cols; i += blockDim.x) {
-      float r = p.add_a[i];
-      if (p.add_b != nullptr) r += p.add_b[i];
-      if (p.add_bias != nullptr) r += bf16_bits_to_f32(p.add_bias[i]);
-      if (blockIdx.x == 0 && p.resid_out != nullptr) p.resid_out[i] = r;
-      x[i] = f32_to_bf16_bits(r * scale * bf16_bits_to_f32(p.norm_weight[i]));
-    }
+    add_norm_to_smem(x, p.add_a, p.add_b, p.add_bias, p.norm_weight, p.eps, p.cols,
+                     blockIdx.x == 0 ? p.resid_out : nullptr, scratch);
   }
   __syncthreads();
 

@@ -4,6 +4,7 @@
 // (hf_decode_sequence/session_api_lifecycle.inc.cu, weights.cu); the engine
 // underneath is this library's own.
 #include "session.h"
+#include "step_kernel.cuh"
 
 #include <math.h>
 #include <stdio.h>
@@ -230,9 +231,14 @@ bool plan_state(Session *s, StaticArena &arena, void *base) {
   ok = ok && carve(arena, base, static_cast<uint64_t>(d.hidden), &s->o_out);
   ok = ok && carve(arena, base, static_cast<uint64_t>(d.hidden), &s->down);
   ok = ok && carve(arena, base, static_cast<uint64_t>(d.vocab), &s->logits);
-  ok = ok && carve(arena, base, static_cast<uint64_t>(d.heads) * s->max_splits * d.head_dim, &s->partial_acc);
-  ok = ok && carve(arena, base, static_cast<uint64_t>(d.heads) * s->max_splits, &s->partial_m);
-  ok = ok && carve(arena, base, static_cast<uint64_t>(d.heads) * s->max_splits, &s->partial_l);
+  const uint64_t split_slots = std::max<uint32_t>(s->max_splits, kStepMaxSplits);
+  s->x_elems = static_cast<uint32_t>(max_x);
+  ok = ok && carve(arena, base, static_cast<uint64_t>(d.heads) * split_slots * d.head_dim, &s->partial_acc);
+  ok = ok && carve(arena, base, static_cast<uint64_t>(d.heads) * split_slots, &s->partial_m);
+  ok = ok && carve(arena, base, static_cast<uint64_t>(d.heads) * split_slots, &s->partial_l);
+  ok = ok && carve(arena, base, static_cast<uint64_t>(d.layers), &s->step_layers);
+  ok = ok && carve(arena, base, static_cast<uint64_t>(d.layers) * 4u + 1u, &s->step_jobs);
+  ok = ok && carve(arena, base, uint64_t{4}, &s->barrier_counter);
   ok = ok && carve(arena, base, ah, &s->attn_bf16);
   ok = ok && carve(arena, base, static_cast<uint64_t>(d.intermediate), &s->ff_bf16);
   ok = ok && carve(arena, base, max_x, &s->x_scratch);
@@ -291,6 +297,99 @@ const uint16_t *arena_at(Session *s, uint64_t offset) {
 // then lm_head (final norm in front, arg-max partials behind) and the sampler.
 // Same operator order as the reference step
 // (hf_decode_sequence/session_decode_prefill.inc.cu:74-372).
+// Fills the device tables of the whole-step kernel: one StepLayerDev per layer
+// and the projection job list (QKV, O, gate/up, down per layer, then lm_head).
+cudaError_t setup_step_kernel(Session *s) {
+  const ModelDims &d = s->dims;
+  s->step_kernel_ok = step_kernel_supported(d.hidden, d.heads, d.kv_heads, d.head_dim, d.intermediate, s->x_elems);
+  if (!s->step_kernel_ok) return cudaSuccess;
+  cudaError_t err = configure_step_kernel();
+  if (err != cudaSuccess) return err;
+  const uint64_t ah = d.attention_hidden(), kvh = d.kv_hidden(), qkv_rows = ah + 2 * kvh;
+  std::vector<StepLayerDev> layers(d.layers);
+  std::vector<JobDesc> jobs(static_cast<size_t>(d.layers) * 4u + 1u);
+  for (uint32_t l = 0; l < d.layers; ++l) {
+    const LayerLayout &L = s->layout.layers[l];
+    StepLayerDev &o = layers[l];
+    o.rms_attn = arena_at(s, L.rms_attn);
+    o.rms_mlp = arena_at(s, L.rms_mlp);
+    o.q_norm = arena_at(s, L.q_norm);
+    o.k_norm = arena_at(s, L.k_norm);
+    o.q_bias = arena_at(s, L.q_bias);
+    o.k_bias = arena_at(s, L.k_bias);
+    o.v_bias = arena_at(s, L.v_bias);
+    o.o_bias = arena_at(s, L.o_bias);
+    o.key_pages = s->kv_keys + l * s->kv_layer_elems;
+    o.value_pages = s->kv_values + l * s->kv_layer_elems;
+    jobs[4 * l + 0] = JobDesc{s->weights->qkv_packed + static_cast<uint64_t>(l) * qkv_rows * d.hidden,
+                              static_cast<uint32_t>(qkv_rows), d.hidden, 0, 0};
+    jobs[4 * l + 1] = JobDesc{arena_at(s, L.w_o), d.hidden, static_cast<uint32_t>(ah), 0, 0};
+    jobs[4 * l + 2] = JobDesc{s->weights->gate_up_packed + static_cast<uint64_t>(l) * 2u * d.intermediate * d.hidden,
+                              2u * d.intermediate, d.hidden, 1, 0};
+    jobs[4 * l + 3] = JobDesc{arena_at(s, L.w_down), d.hidden, d.intermediate, 0, 0};
+  }
+  jobs[4 * d.layers] = JobDesc{arena_at(s, s->layout.lm_head), d.vocab, d.hidden, 0, 0};
+  for (const JobDesc &j : jobs) {
+    if ((reinterpret_cast<uintptr_t>(j.weight) & 15u) != 0) s->step_kernel_ok = false;  // TMA source alignment
+  }
+  if (!s->step_kernel_ok) return cudaSuccess;
+  err = cudaMemcpyAsync(s->step_layers, layers.data(), layers.size() * sizeof(StepLayerDev),
+                        cudaMemcpyHostToDevice, s->stream);
+  if (err == cudaSuccess)
+    err = cudaMemcpyAsync(s->step_jobs, jobs.data(), jobs.size() * sizeof(JobDesc), cudaMemcpyHostToDevice,
+                          s->stream);
+  if (err == cudaSuccess) err = cudaStreamSynchronize(s->stream);  // the host vectors go out of scope
+  return err;
+}
+
+// Attention items per query head in the whole-step kernel: about 256 cached
+// tokens (one 32-token tile per warp) per item, at most kStepMaxSplits.
+uint32_t step_kernel_splits(uint32_t target_context) {
+  uint32_t s = (target_context + 255u) / 256u;
+  if (s < 1) s = 1;
+  if (s > kStepMaxSplits) s = kStepMaxSplits;
+  return s;
+}
+
+cudaError_t enqueue_step_kernel(Session *s, uint32_t splits, uint32_t sample) {
+  const ModelDims &d = s->dims;
+  StepKernelParams p{};
+  p.st = step_state(s);
+  p.embeddings = arena_at(s, s->layout.embeddings);
+  p.final_norm = arena_at(s, s->layout.final_norm);
+  p.layers = s->step_layers;
+  p.jobs = s->step_jobs;
+  p.layer_count = d.layers;
+  p.job_count = sample != 0 ? d.layers * 4u + 1u : d.layers * 4u;
+  p.hidden = d.hidden;
+  p.heads = d.heads;
+  p.kv_heads = d.kv_heads;
+  p.head_dim = d.head_dim;
+  p.intermediate = d.intermediate;
+  p.vocab = d.vocab;
+  p.eps = s->rms_eps;
+  p.rope_theta = s->rope_theta;
+  p.page_table = s->page_table;
+  p.page_count = s->kv_pages;
+  p.h_a = s->h_a;
+  p.h_b = s->h_b;
+  p.qkv = s->qkv;
+  p.o_out = s->o_out;
+  p.down = s->down;
+  p.logits = s->logits;
+  p.ff_bf16 = s->ff_bf16;
+  p.partial_acc = s->partial_acc;
+  p.partial_m = s->partial_m;
+  p.partial_l = s->partial_l;
+  p.attn_splits = splits;
+  p.best_value = s->best_value;
+  p.best_index = s->best_index;
+  p.barrier_counter = s->barrier_counter;
+  p.sample = sample;
+  p.x_elems = s->x_elems;
+  return launch_step_kernel(s->stream, p, s->sm_count);
+}
+
 // Records the next profile event; the interval that ends here gets `bucket`.
 static void profile_mark(Session *s, StepProfile *prof, uint32_t bucket) {
   if (prof == nullptr) return;
@@ -312,6 +411,10 @@ cudaError_t enqueue_step(Session *s, uint32_t splits, uint32_t sample, uint64_t 
   const uint64_t ah = d.attention_hidden(), kvh = d.kv_hidden();
   const uint64_t qkv_rows = ah + 2 * kvh;
   uint64_t n = 0;
+  if (s->engine == 1 && prof == nullptr) {
+    if (launches != nullptr) *launches = 1;
+    return enqueue_step_kernel(s, splits, sample);
+  }
   profile_mark(s, prof, kBucketEmbed);
   cudaError_t err = launch_embed(s->stream, st, arena_at(s, s->layout.embeddings), d.hidden, s->h_b);
   n += 1;
@@ -492,17 +595,19 @@ cudaError_t ensure_graph(Session *s, uint32_t splits, uint32_t sample, GraphEntr
   cudaGraph_t graph = nullptr;
   const cudaError_t end_err = cudaStreamEndCapture(s->stream, &graph);
   if (err == cudaSuccess) err = end_err;
-  if (err != cudaSuccess) {
-    if (graph != nullptr) cudaGraphDestroy(graph);
-    return err;
-  }
   size_t nodes = 0;
-  err = cudaGraphGetNodes(graph, nullptr, &nodes);
   cudaGraphExec_t exec = nullptr;
+  if (err == cudaSuccess) err = cudaGraphGetNodes(graph, nullptr, &nodes);
   if (err == cudaSuccess) err = cudaGraphInstantiate(&exec, graph, 0);
   if (err != cudaSuccess) {
-    cudaGraphDestroy(graph);
-    return err;
+    if (graph != nullptr) cudaGraphDestroy(graph);
+    graph = nullptr;
+    if (s->engine != 1) return err;
+    // The whole-step kernel is a cooperative launch; where the runtime will not
+    // put one into a graph the step is launched directly (one launch per token).
+    cudaGetLastError();
+    exec = nullptr;
+    nodes = 2;
   }
   entry.graph = graph;
   entry.exec = exec;
@@ -518,7 +623,13 @@ cudaError_t ensure_graph(Session *s, uint32_t splits, uint32_t sample, GraphEntr
 
 // Attention split count for a launch that will see contexts up to `target`:
 // bucketed to a power of two so that a growing context re-uses the graph.
+cudaError_t replay(Session *s, GraphEntry *g) {
+  if (g->exec != nullptr) return cudaGraphLaunch(g->exec, s->stream);
+  return enqueue_step(s, g->splits, g->sample, nullptr);
+}
+
 uint32_t splits_for(Session *s, uint32_t target_context) {
+  if (s->engine == 1) return step_kernel_splits(target_context);
   uint32_t want = attention_default_splits(target_context, 1, s->dims.kv_heads, s->sm_count);
   uint32_t bucket = 1;
   while (bucket < want) bucket <<= 1;
@@ -1051,6 +1162,7 @@ extern "C" int nerva_cuda_hf_decode_sequence_session_create(
                                 s->weights->gate_up_packed + static_cast<uint64_t>(l) * 2u * d.intermediate * d.hidden,
                                 d.intermediate, d.hidden);
   }
+  if (err == cudaSuccess) err = setup_step_kernel(s);
   if (err != cudaSuccess) return create_fail(s, out, err, kStagePackReplicas);
   err = cudaStreamSynchronize(s->stream);
   if (err != cudaSuccess) return create_fail(s, out, err, kStageSetupSynchronize);
@@ -1077,7 +1189,12 @@ extern "C" int nerva_cuda_hf_decode_sequence_session_destroy(Session *session) {
 }
 
 extern "C" int nerva_b200_session_set_engine(Session *s, uint32_t engine) {
-  if (s == nullptr || engine > 0 || s->started) return -1;
+  if (s == nullptr || engine > 1 || s->started) return -1;
+  if (engine == 1 && !s->step_kernel_ok) {
+    set_last_error("whole-step kernel needs head_dim 64 or 128, dims that are multiples of 8, and "
+                   "an activation vector that fits beside the weight ring in shared memory");
+    return -1;
+  }
   s->engine = engine;
   return 0;
 }
@@ -1113,13 +1230,13 @@ extern "C" int nerva_cuda_hf_decode_sequence_session_start(
   if (err == cudaSuccess) err = ensure_graph(s, splits, 1, &sampled, out);
   if (err == cudaSuccess) err = cudaEventRecord(s->ev_start, s->stream);
   for (uint32_t i = 0; err == cudaSuccess && i + 1 < s->prompt_count; ++i) {
-    err = cudaGraphLaunch(quiet->exec, s->stream);
+    err = replay(s, quiet);
     out->graph_replays += 1;
     out->graph_launches += 1;
     out->kernel_launches += quiet->nodes;
   }
   if (err == cudaSuccess) {
-    err = cudaGraphLaunch(sampled->exec, s->stream);
+    err = replay(s, sampled);
     out->graph_replays += 1;
     out->graph_launches += 1;
     out->kernel_launches += sampled->nodes;
@@ -1179,7 +1296,7 @@ extern "C" int nerva_cuda_hf_decode_sequence_session_advance(
   if (run_count != 0) err = ensure_graph(s, splits_for(s, target), 1, &graph, out);
   if (err == cudaSuccess && run_count != 0) err = cudaEventRecord(s->ev_start, s->stream);
   for (uint32_t step = 0; err == cudaSuccess && step < run_count; ++step) {
-    err = cudaGraphLaunch(graph->exec, s->stream);  // the hot loop: nothing else per token
+    err = replay(s, graph);  // the hot loop: one graph launch per token, nothing else
     if (err != cudaSuccess) break;
     out->graph_replays += 1;
     out->graph_launches += 1;
@@ -1275,7 +1392,7 @@ extern "C" int nerva_cuda_hf_decode_sequence_session_run(
   if (err == cudaSuccess) err = ensure_graph(s, splits_for(s, context_steps), 1, &graph, out);
   if (err == cudaSuccess) err = cudaEventRecord(s->ev_start, s->stream);
   for (uint32_t step = 0; err == cudaSuccess && step < context_steps; ++step) {
-    err = cudaGraphLaunch(graph->exec, s->stream);
+    err = replay(s, graph);
     if (err == cudaSuccess) {
       out->graph_replays += 1;
       out->graph_launches += 1;
@@ -1364,6 +1481,9 @@ extern "C" int nerva_cuda_hf_decode_sequence_session_fork_shared_weights(
   if (err == cudaSuccess)
     err = cudaMemcpyAsync(s->state_block, parent->state_block, s->state_bytes, cudaMemcpyDeviceToDevice, s->stream);
   if (err == cudaSuccess) err = cudaStreamSynchronize(s->stream);
+  if (err != cudaSuccess) return create_fail(s, out, err, kStageSetupSynchronize);
+  // the copied layer table points at the parent's KV pages: rebuild it for this session
+  err = setup_step_kernel(s);
   if (err != cudaSuccess) return create_fail(s, out, err, kStageSetupSynchronize);
   memcpy(s->host_slots, parent->host_slots, s->slots_bytes);
   s->started = parent->started;

@@ -86,9 +86,18 @@ struct StepProfile {
 struct GraphEntry {
   uint32_t prompt_count = 0, splits = 0, sample = 0, engine = 0;
   cudaGraph_t graph = nullptr;
-  cudaGraphExec_t exec = nullptr;
+  cudaGraphExec_t exec = nullptr;  // null: the step is launched directly (capture was refused)
   uint64_t nodes = 0;
 };
+
+struct StepLayerDev;
+struct JobDesc;
+struct StepKernelParams;
+uint32_t step_kernel_smem_bytes(uint32_t x_elems);
+bool step_kernel_supported(uint32_t hidden, uint32_t heads, uint32_t kv_heads, uint32_t head_dim,
+                           uint32_t intermediate, uint32_t x_elems);
+cudaError_t configure_step_kernel();
+cudaError_t launch_step_kernel(cudaStream_t stream, const StepKernelParams &p, uint32_t blocks);
 
 }  // namespace nb
 
@@ -129,6 +138,12 @@ struct NervaCudaHfDecodeSequenceSession {
   uint16_t *attn_bf16 = nullptr, *ff_bf16 = nullptr, *x_scratch = nullptr;
   float *best_value = nullptr;
   uint32_t *best_index = nullptr;
+  // whole-step kernel (engine 1)
+  nb::StepLayerDev *step_layers = nullptr;
+  nb::JobDesc *step_jobs = nullptr;
+  uint32_t *barrier_counter = nullptr;
+  uint32_t x_elems = 0;
+  bool step_kernel_ok = false;
   NervaCudaSyntheticTokenSlot *device_slots = nullptr;
   uint32_t *device_cursor = nullptr, *device_error = nullptr, *device_prompt = nullptr;
   uint64_t slots_bytes = 0;

@@ -158,10 +158,40 @@ void oracle_per_head_rms_norm(uint32_t dtype, const uint16_t *weight, uint32_t h
 
 /* precision/block/ops.rs:78-93: one serial ascending f32 sum per row.  Rows are
  * independent, so distributing them over threads does not change any bit. */
+/* Summation-order probe (NOT the reference order): with lanes > 1 every row is
+ * summed in `lanes` interleaved fp32 partial sums that are added at the end.
+ * Tests use it to measure how far two equally valid fp32 evaluations of the
+ * same contract drift apart (the floor under any logit tolerance). */
+static int g_sum_lanes = 1;
+void oracle_set_sum_lanes(int lanes) { g_sum_lanes = lanes < 1 ? 1 : (lanes > 16 ? 16 : lanes); }
+
+static void matvec_lanes(uint32_t dtype, const uint16_t *matrix, const float *input,
+                         uint32_t rows, uint32_t cols, float *output, int lanes) {
+  const int threads = oracle_get_threads();
+  (void)threads;
+#pragma omp parallel for schedule(static) num_threads(threads) if (rows >= 64)
+  for (int64_t row = 0; row < (int64_t)rows; ++row) {
+    const uint16_t *w = matrix + (uint64_t)row * cols;
+    float part[16] = {0};
+    for (uint32_t col = 0; col < cols; ++col) {
+      part[col % (uint32_t)lanes] += decode(dtype, w[col]) * input[col];
+    }
+    float sum = 0.0f;
+    for (int l = 0; l < lanes; ++l) {
+      sum += part[l];
+    }
+    output[row] = sum;
+  }
+}
+
 void oracle_matvec(uint32_t dtype, const uint16_t *matrix, const float *input,
                    uint32_t rows, uint32_t cols, float *output) {
   const int threads = oracle_get_threads();
   (void)threads;
+  if (g_sum_lanes > 1) {
+    matvec_lanes(dtype, matrix, input, rows, cols, output, g_sum_lanes);
+    return;
+  }
   /* Eight rows advance together so that their eight independent add chains
    * overlap in the pipeline; each row's own sum is still col = 0, 1, 2, ... */
   const int64_t blocks = ((int64_t)rows + 7) / 8;
@@ -617,7 +647,7 @@ static int layer_forward(OracleCtx *ctx, uint32_t layer_index, uint32_t position
   if (m->rope_theta > 0.0f) {
     oracle_rope(ctx->k, m->kv_heads, m->head_dim, position, m->rope_theta);
   }
-  if (cuda) {
+  if (cuda || ctx->mode == ORACLE_MODE_CPU_KV16) {
     round_vec(dtype, ctx->k, kv_hidden);
     round_vec(dtype, ctx->v, kv_hidden);
   }

@@ -28,7 +28,11 @@ enum { ORACLE_DTYPE_F16 = 0, ORACLE_DTYPE_BF16 = 1 };
  *                    to the model dtype, residual stream kept in f32 across
  *                    layers (hf_decode_sequence/kernels.cu:182-217,434-492,
  *                    577-612,651-687). */
-enum { ORACLE_MODE_CPU = 0, ORACLE_MODE_CUDA = 1 };
+/* ORACLE_MODE_CPU_KV16: the CPU contract with K and V rounded to the model dtype
+ * when they enter the cache (the paged cache of the C ABI holds 16-bit values,
+ * hf_decode_sequence/types.cuh:328-337).  Used to study contracts; not a
+ * reference path by itself. */
+enum { ORACLE_MODE_CPU = 0, ORACLE_MODE_CUDA = 1, ORACLE_MODE_CPU_KV16 = 2 };
 
 typedef struct OracleLayer {
   const uint16_t *rms_attn, *rms_mlp;
@@ -113,6 +117,9 @@ const float *oracle_hidden_state(const OracleCtx *ctx);
 uint64_t oracle_hash_tokens(const uint32_t *tokens, uint32_t count);
 
 /* Host thread count used by the row-parallel mat-vec (results do not depend on it). */
+/* Summation-order probe for tolerance-floor measurements: 1 = the reference's
+ * serial order (default); n > 1 = n interleaved partial sums per row. */
+void oracle_set_sum_lanes(int lanes);
 void oracle_set_threads(int threads);
 int oracle_get_threads(void);
 

@@ -91,6 +91,7 @@ def lib() -> C.CDLL:
         L.oracle_hash_tokens.restype = C.c_uint64
         L.oracle_hash_tokens.argtypes = [_u32p, C.c_uint32]
         L.oracle_set_threads.argtypes = [C.c_int]
+        L.oracle_set_sum_lanes.argtypes = [C.c_int]
         L.oracle_get_threads.restype = C.c_int
         _lib = L
     return _lib
@@ -169,6 +170,11 @@ def route_softmax_topk(router_logits, top_k: int, norm_topk_prob: bool):
     weights = np.zeros(top_k, dtype=np.float32)
     lib().oracle_route_softmax_topk(_pf(logits), logits.size, top_k, int(norm_topk_prob), _pu(experts), _pf(weights))
     return experts, weights
+
+
+def set_sum_lanes(lanes: int) -> None:
+    """1 = reference serial summation; n > 1 = a different, equally valid fp32 order."""
+    lib().oracle_set_sum_lanes(lanes)
 
 
 def hash_tokens(tokens) -> int:

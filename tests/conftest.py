@@ -68,6 +68,20 @@ def tiny_golden():
         return json.load(f)
 
 
+def contract_self_distance(oracle_mod, checkpoint, max_context, prompt, steps, ref_logits) -> float:
+    """max |logit difference| between two exact restatements of the same numeric
+    contract that differ only in fp32 summation order (serial vs 8 interleaved
+    partial sums per row).  Rounding projection inputs to bf16 makes deep/wide
+    models sensitive to that order, so this is the floor under any logit bound."""
+    oracle_mod.set_sum_lanes(8)
+    try:
+        dec = oracle_mod.Decoder(checkpoint, max_context, mode=oracle_mod.MODE_CUDA)
+        _, alt = dec.decode_greedy(prompt, steps, want_logits=True)
+    finally:
+        oracle_mod.set_sum_lanes(1)
+    return float(np.abs(alt[-1] - ref_logits[-1]).max())
+
+
 def bf16_bits(values) -> np.ndarray:
     from nerva_b200 import synth
     return synth.f32_to_bf16(np.asarray(values, dtype=np.float32))
