@@ -632,6 +632,14 @@ int nerva_b200_session_profile_steps(NervaCudaHfDecodeSequenceSession *session, 
                                      uint64_t *bucket_ns, uint32_t *bucket_launches,
                                      uint32_t bucket_capacity);
 
+/* Tuning aid of the whole-step kernel: reads and clears 16 counters of SM cycles
+ * that block 0 spent per phase (QKV prologue, QKV, barrier, attention, barrier,
+ * O prologue, O, barrier, gate/up prologue, gate/up, barrier, down prologue,
+ * down, barrier, lm_head, tail).  Only filled when the session was created with
+ * the environment variable NERVA_B200_PHASE_PROFILE=1.  Returns the count. */
+int nerva_b200_session_read_phase_cycles(NervaCudaHfDecodeSequenceSession *session,
+                                         uint64_t *cycles, uint32_t capacity);
+
 /* Isolated projection: y[m][n] = sum_k W[n][k] * x[m][k], bf16 in, fp32
  * accumulate and out.  All pointers are HOST memory; the call copies in, runs
  * `iterations` launches after `warmup` untimed ones, and copies y back.

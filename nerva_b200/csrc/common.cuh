@@ -129,6 +129,18 @@ __device__ __forceinline__ void tma_load_1d(void *smem_dst, const void *gmem_src
       : "memory");
 }
 
+// ---- programmatic dependent launch ----
+// A kernel launched with the programmatic-serialization attribute may start
+// while its predecessor in the stream is still running.  Everything it does
+// before pdl_wait() must be independent of the predecessor (set-up, weight
+// prefetch); pdl_wait() returns once the predecessor has completed and its
+// writes are visible.  pdl_trigger() lets the successor start launching.  Both
+// are no-ops for a kernel launched the ordinary way.
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void pdl_trigger() {
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+}
+
 __device__ __forceinline__ void report_error(uint32_t *error_word, uint32_t code) {
   if (error_word != nullptr) atomicMax(error_word, code);
 }

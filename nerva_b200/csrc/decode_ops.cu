@@ -22,6 +22,7 @@ __device__ __forceinline__ uint32_t current_token(const StepState &st, uint32_t 
 
 __global__ void embed_kernel(StepState st, const uint16_t *embeddings, uint32_t hidden,
                              float *input) {
+  pdl_trigger();  // the first projection may start prefetching its weights now
   const uint32_t position = *st.cursor;
   if (position >= st.max_context) {
     if (threadIdx.x == 0) report_error(st.error_word, kErrCursorOutOfRange);
@@ -118,6 +119,7 @@ __global__ void sample_greedy_kernel(StepState st, const float *best_value,
                                      uint32_t sample) {
   __shared__ float sv[32];
   __shared__ uint32_t si[32];
+  pdl_wait();  // the arg-max partials come from the lm_head projection
   const uint32_t position = *st.cursor;
   if (position >= st.max_context) return;
   float bv = -INFINITY;
@@ -264,9 +266,10 @@ cudaError_t launch_qkv_prepare(cudaStream_t stream, const StepState &st,
 }
 
 cudaError_t launch_sample_greedy(cudaStream_t stream, const StepState &st, const float *best_value,
-                                 const uint32_t *best_index, uint32_t partials, uint32_t sample) {
-  sample_greedy_kernel<<<1, 256, 0, stream>>>(st, best_value, best_index, partials, sample);
-  return cudaGetLastError();
+                                 const uint32_t *best_index, uint32_t partials, uint32_t sample,
+                                 bool pdl) {
+  return launch_with_pdl(sample_greedy_kernel, dim3(1), dim3(256), 0, stream, pdl, st, best_value,
+                         best_index, partials, sample);
 }
 
 cudaError_t launch_argmax(cudaStream_t stream, const float *logits, uint32_t count,

@@ -10,6 +10,28 @@
 
 namespace nb {
 
+// Launches `kernel`; with pdl set the launch carries the programmatic
+// stream-serialization attribute, so the kernel may begin (up to its
+// griddepcontrol.wait) while its predecessor in the stream drains.  Works under
+// stream capture (the edge becomes a programmatic graph dependency).
+template <class... KernelArgs, class... Args>
+cudaError_t launch_with_pdl(void (*kernel)(KernelArgs...), dim3 grid, dim3 block, size_t smem,
+                            cudaStream_t stream, bool pdl, Args &&...args) {
+  cudaLaunchConfig_t config{};
+  config.gridDim = grid;
+  config.blockDim = block;
+  config.dynamicSmemBytes = smem;
+  config.stream = stream;
+  cudaLaunchAttribute attribute{};
+  if (pdl) {
+    attribute.id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attribute.val.programmaticStreamSerializationAllowed = 1;
+    config.attrs = &attribute;
+    config.numAttrs = 1;
+  }
+  return cudaLaunchKernelEx(&config, kernel, static_cast<KernelArgs>(args)...);
+}
+
 // ---- projection (weight-streaming GEMV) ----
 enum ProjectionPrologue : uint32_t {
   kProloguePlain = 0,     // x_bf16 is the activation vector
@@ -40,6 +62,7 @@ struct ProjectionParams {
   float *best_value;     // [blocks] kEpilogueArgmax
   uint32_t *best_index;  // [blocks]
   uint32_t *error_word;
+  uint32_t pdl;          // launch with programmatic dependent launch (see launch_with_pdl)
 };
 
 // Number of blocks launch_projection will use (= number of arg-max partials).
@@ -96,11 +119,34 @@ cudaError_t configure_attention_kernels();
 uint32_t attention_default_splits(uint32_t context, uint32_t batch, uint32_t kv_heads,
                                   uint32_t sm_count);
 
+// ---- fused decode attention of the session (one launch per layer) ----
+struct FusedAttentionParams {
+  const uint32_t *cursor;  // position of the token being decoded
+  uint32_t max_context;
+  const float *qkv;        // [heads*d | kv_heads*d | kv_heads*d] f32 projection output
+  const uint16_t *q_bias, *k_bias, *v_bias, *q_norm, *k_norm;  // optional
+  uint16_t *key_pages, *value_pages;  // this layer's pages
+  const uint32_t *page_table;
+  uint32_t page_count;
+  uint32_t heads, kv_heads, head_dim;
+  float eps, rope_theta;
+  uint32_t splits;
+  float *partial_acc, *partial_m, *partial_l;  // [heads][splits][...]
+  uint32_t *tickets;                           // [heads], zero between launches
+  uint16_t *out_bf16;                          // [heads*d]
+  uint32_t *error_word;
+  uint32_t pdl;
+};
+bool fused_attention_supported(uint32_t heads, uint32_t kv_heads, uint32_t head_dim);
+uint32_t fused_attention_splits(uint32_t target_context);
+cudaError_t launch_fused_attention(cudaStream_t stream, const FusedAttentionParams &p);
+
 // ---- greedy sampling ----
 // Reduces per-block (value, index) partials, writes the token slot at the
 // cursor and advances the cursor.  sample == 0: only advances the cursor.
 cudaError_t launch_sample_greedy(cudaStream_t stream, const StepState &st, const float *best_value,
-                                 const uint32_t *best_index, uint32_t partials, uint32_t sample);
+                                 const uint32_t *best_index, uint32_t partials, uint32_t sample,
+                                 bool pdl = false);
 // Stand-alone argmax over logits (used by the per-op entry point).
 cudaError_t launch_argmax(cudaStream_t stream, const float *logits, uint32_t count,
                           uint32_t *token_out);

@@ -6,31 +6,13 @@
 //   epilogue  SwiGLU -> bf16                    (kernels.cu:597-612)
 //             per-block greedy arg-max partials (sampler.cu:89-119)
 #include "kernels.cuh"
+#include "row_stream.cuh"
 #include "step_device.cuh"
-#include "weight_stream.cuh"
 
 namespace nb {
 namespace {
 
-struct StoreEpilogue {
-  float *out;
-  __device__ __forceinline__ void row(uint32_t r, float v) {
-    if ((threadIdx.x & 31u) == 0) out[r] = v;
-  }
-};
-
-// Rows come as (gate_i, up_i) pairs; a warp always owns whole pairs.
-struct SwigluEpilogue {
-  uint16_t *out;
-  float gate;
-  __device__ __forceinline__ void row(uint32_t r, float v) {
-    if ((r & 1u) == 0) {
-      gate = v;
-    } else if ((threadIdx.x & 31u) == 0) {
-      out[r >> 1] = f32_to_bf16_bits(silu(gate) * v);
-    }
-  }
-};
+constexpr uint32_t kNoIndex = 0xffffffffu;
 
 // Tie rule of the reference sampler: larger value, then lower index; non-finite
 // logits never win (sampler.cu:35-40).
@@ -39,89 +21,105 @@ __device__ __forceinline__ bool candidate_better(float v, uint32_t i, float best
   return v > best_v || (v == best_v && i < best_i);
 }
 
-struct ArgmaxEpilogue {
-  float *out;
-  float best_v;
-  uint32_t best_i;
-  __device__ __forceinline__ void row(uint32_t r, float v) {
-    if ((threadIdx.x & 31u) == 0) out[r] = v;
-    if (isfinite(v) && candidate_better(v, r, best_v, best_i)) {
-      best_v = v;
-      best_i = r;
-    }
-  }
+struct ProjectionShared {
+  StreamShared stream;
+  JobDesc job;
+  float scratch[40];
+  float best_v[kStreamWarps];
+  uint32_t best_i[kStreamWarps];
 };
 
-constexpr uint32_t kNoIndex = 0xffffffffu;
+__host__ __device__ inline uint32_t round128(uint32_t v) { return (v + 127u) & ~127u; }
 
-// Shared memory map of the streaming kernel (dynamic):
-//   [0, kRingBytes)                     weight ring
-//   [kRingBytes, +cols*2 rounded 16)    activation vector, bf16
-//   then 24 mbarriers, 40 floats of reduction scratch, 8+8 arg-max words
-__device__ __forceinline__ uint32_t round16(uint32_t v) { return (v + 15u) & ~15u; }
-
+// Shared memory map (dynamic): weight ring | activation vector (bf16) |
+// ProjectionShared | row totals (one float per row of the block).
 template <uint32_t EPI>
 __global__ void __launch_bounds__(kStreamThreads, 1) projection_stream_kernel(ProjectionParams p) {
   extern __shared__ __align__(128) uint8_t smem[];
   uint8_t *ring = smem;
   uint16_t *x = reinterpret_cast<uint16_t *>(smem + kRingBytes);
-  uint8_t *tail = smem + kRingBytes + round16(p.cols * 2u);
-  uint64_t *bars = reinterpret_cast<uint64_t *>(tail);
-  float *scratch = reinterpret_cast<float *>(tail + kStreamWarps * kStreamSlots * 8u);
-  float *warp_best_v = scratch + 40;
-  uint32_t *warp_best_i = reinterpret_cast<uint32_t *>(scratch + 48);
+  ProjectionShared &sh = *reinterpret_cast<ProjectionShared *>(smem + kRingBytes + round128(p.cols * 2u));
+  float *row_total = reinterpret_cast<float *>(smem + kRingBytes + round128(p.cols * 2u) +
+                                               round128(sizeof(ProjectionShared)));
+  const uint32_t unit = EPI == kEpilogueSwiglu ? 2u : 1u;
+  pdl_trigger();
+  if (threadIdx.x == 0) sh.job = JobDesc{p.weight, p.rows, p.cols, unit, 0};
+  __syncthreads();
 
-  WarpStream ws;
-  stream_init(ws, ring, bars);
-
-  const bool pairs = EPI == kEpilogueSwiglu;
-  const StreamShape shape = make_stream_shape(p.cols, pairs);
-  uint32_t row_begin, row_end;
-  block_row_range(p.rows, pairs ? 2u : 1u, blockIdx.x, gridDim.x, &row_begin, &row_end);
-  const StreamJob job = make_stream_job(p.weight, shape, row_begin, row_end);
-  uint32_t next = 0;
+  RowStream rs;
+  stream_init(rs, ring, sh.stream, &sh.job, 1);
   // Weights do not depend on the activations: start streaming before the prologue.
-  stream_fill(ws, job, &next);
+  stream_fill(rs);
 
+  uint32_t row_begin, row_end;
+  block_row_range(p.rows, unit, blockIdx.x, gridDim.x, &row_begin, &row_end);
+  const uint32_t rows_local = row_end - row_begin;
+  for (uint32_t r = threadIdx.x; r < rows_local; r += blockDim.x) row_total[r] = 0.0f;
+
+  // Everything above is independent of the previous kernel; its output is read below.
+  pdl_wait();
   if (p.prologue == kProloguePlain) {
     const uint4 *src = reinterpret_cast<const uint4 *>(p.x_bf16);
     uint4 *dst = reinterpret_cast<uint4 *>(x);
     for (uint32_t i = threadIdx.x; i < p.cols / 8u; i += blockDim.x) dst[i] = src[i];
   } else {
     add_norm_to_smem(x, p.add_a, p.add_b, p.add_bias, p.norm_weight, p.eps, p.cols,
-                     blockIdx.x == 0 ? p.resid_out : nullptr, scratch);
+                     blockIdx.x == 0 ? p.resid_out : nullptr, sh.scratch);
   }
   __syncthreads();
 
+  stream_consume(rs, sh.stream, 0, x, row_total, p.error_word);
+  __syncthreads();
+
+  // Epilogue over the block's rows, coalesced.
   if (EPI == kEpilogueStore) {
-    StoreEpilogue epi{p.out_f32};
-    stream_consume(ws, job, &next, x, epi, p.error_word);
+    for (uint32_t r = threadIdx.x; r < rows_local; r += blockDim.x) {
+      p.out_f32[row_begin + r] = stream_row_total(sh.stream, row_total, r);
+    }
   } else if (EPI == kEpilogueSwiglu) {
-    SwigluEpilogue epi{p.out_bf16, 0.0f};
-    stream_consume(ws, job, &next, x, epi, p.error_word);
+    for (uint32_t i = threadIdx.x; i < rows_local / 2u; i += blockDim.x) {
+      const float gate = stream_row_total(sh.stream, row_total, 2u * i);
+      const float up = stream_row_total(sh.stream, row_total, 2u * i + 1u);
+      p.out_bf16[row_begin / 2u + i] = f32_to_bf16_bits(silu(gate) * up);
+    }
   } else {
-    ArgmaxEpilogue epi{p.out_f32, -INFINITY, kNoIndex};
-    stream_consume(ws, job, &next, x, epi, p.error_word);
-    const uint32_t warp = threadIdx.x >> 5;
+    float bv = -INFINITY;
+    uint32_t bi = kNoIndex;
+    for (uint32_t r = threadIdx.x; r < rows_local; r += blockDim.x) {
+      const float v = stream_row_total(sh.stream, row_total, r);
+      p.out_f32[row_begin + r] = v;
+      if (isfinite(v) && candidate_better(v, row_begin + r, bv, bi)) {
+        bv = v;
+        bi = row_begin + r;
+      }
+    }
+    for (int offset = 16; offset > 0; offset >>= 1) {
+      const float ov = __shfl_xor_sync(0xffffffffu, bv, offset);
+      const uint32_t oi = __shfl_xor_sync(0xffffffffu, bi, offset);
+      if (oi != kNoIndex && candidate_better(ov, oi, bv, bi)) {
+        bv = ov;
+        bi = oi;
+      }
+    }
     if ((threadIdx.x & 31u) == 0) {
-      warp_best_v[warp] = epi.best_v;
-      warp_best_i[warp] = epi.best_i;
+      sh.best_v[threadIdx.x >> 5] = bv;
+      sh.best_i[threadIdx.x >> 5] = bi;
     }
     __syncthreads();
     if (threadIdx.x == 0) {
-      float bv = -INFINITY;
-      uint32_t bi = kNoIndex;
+      bv = -INFINITY;
+      bi = kNoIndex;
       for (uint32_t w = 0; w < kStreamWarps; ++w) {
-        if (warp_best_i[w] != kNoIndex && candidate_better(warp_best_v[w], warp_best_i[w], bv, bi)) {
-          bv = warp_best_v[w];
-          bi = warp_best_i[w];
+        if (sh.best_i[w] != kNoIndex && candidate_better(sh.best_v[w], sh.best_i[w], bv, bi)) {
+          bv = sh.best_v[w];
+          bi = sh.best_i[w];
         }
       }
       p.best_value[blockIdx.x] = bv;
       p.best_index[blockIdx.x] = bi;
     }
   }
-  stream_drain(ws);
+  stream_drain(rs);
 }
 
 // Any-shape path (cols not a multiple of 8, or an unaligned matrix): one warp
@@ -130,17 +128,17 @@ __global__ void projection_generic_prologue_kernel(ProjectionParams p, uint16_t 
   __shared__ float scratch[40];
   float sumsq = 0.0f;
   for (uint32_t i = threadIdx.x; i < p.cols; i += blockDim.x) {
-    float r = p.add_a[i];
-    if (p.add_b != nullptr) r += p.add_b[i];
+    float r = p.add_b != nullptr ? p.add_b[i] : p.add_a[i];
     if (p.add_bias != nullptr) r += bf16_bits_to_f32(p.add_bias[i]);
+    if (p.add_b != nullptr) r += p.add_a[i];
     sumsq += r * r;
   }
   const float total = block_sum(sumsq, scratch);
   const float scale = rsqrtf(total / static_cast<float>(p.cols) + p.eps);
   for (uint32_t i = threadIdx.x; i < p.cols; i += blockDim.x) {
-    float r = p.add_a[i];
-    if (p.add_b != nullptr) r += p.add_b[i];
+    float r = p.add_b != nullptr ? p.add_b[i] : p.add_a[i];
     if (p.add_bias != nullptr) r += bf16_bits_to_f32(p.add_bias[i]);
+    if (p.add_b != nullptr) r += p.add_a[i];
     if (p.resid_out != nullptr) p.resid_out[i] = r;
     x_out[i] = f32_to_bf16_bits(r * scale * bf16_bits_to_f32(p.norm_weight[i]));
   }
@@ -156,7 +154,7 @@ __global__ void projection_generic_kernel(ProjectionParams p, const uint16_t *x)
   const uint32_t unit = p.epilogue == kEpilogueSwiglu ? 2u : 1u;
   float best_v = -INFINITY;
   uint32_t best_i = kNoIndex;
-  for (uint32_t base = warp * unit; base < p.rows; base += warps * unit) {
+  for (uint32_t base = warp * unit; base + unit <= p.rows; base += warps * unit) {
     float gate = 0.0f;
     for (uint32_t u = 0; u < unit; ++u) {
       const uint32_t r = base + u;
@@ -202,16 +200,30 @@ __global__ void projection_generic_kernel(ProjectionParams p, const uint16_t *x)
   }
 }
 
-uint32_t stream_smem_bytes(uint32_t cols) {
-  return kRingBytes + ((cols * 2u + 15u) & ~15u) + kStreamWarps * kStreamSlots * 8u + 64u * 4u;
+uint32_t blocks_for(const ProjectionParams &p, uint32_t sm_count) {
+  // One block per SM; fewer when the matrix is too small to give every warp of
+  // every block 4 KiB (toy shapes).
+  const uint64_t bytes = static_cast<uint64_t>(p.rows) * p.cols * 2u;
+  uint64_t blocks = bytes / (static_cast<uint64_t>(kStreamWarps) * 4096u);
+  const uint32_t unit = p.epilogue == kEpilogueSwiglu ? 2u : 1u;
+  if (blocks > p.rows / unit) blocks = p.rows / unit;
+  if (blocks > sm_count) blocks = sm_count;
+  if (blocks == 0) blocks = 1;
+  return static_cast<uint32_t>(blocks);
 }
 
-bool stream_eligible(const ProjectionParams &p) {
-  if (p.cols % 8u != 0 || p.cols == 0) return false;
+uint32_t stream_smem_bytes(const ProjectionParams &p, uint32_t blocks) {
+  const uint32_t unit = p.epilogue == kEpilogueSwiglu ? 2u : 1u;
+  return kRingBytes + round128(p.cols * 2u) + round128(sizeof(ProjectionShared)) +
+         round128(max_rows_per_block(p.rows, unit, blocks) * 4u + 16u);
+}
+
+bool stream_eligible(const ProjectionParams &p, uint32_t sm_count) {
+  if (p.cols % 8u != 0 || p.cols == 0 || p.rows == 0) return false;
   if (reinterpret_cast<uintptr_t>(p.weight) % 16u != 0) return false;
   if (p.prologue == kProloguePlain && reinterpret_cast<uintptr_t>(p.x_bf16) % 16u != 0) return false;
   if (p.epilogue == kEpilogueSwiglu && p.rows % 2u != 0) return false;
-  return stream_smem_bytes(p.cols) <= 227u * 1024u;
+  return stream_smem_bytes(p, blocks_for(p, sm_count)) <= 227u * 1024u;
 }
 
 }  // namespace
@@ -230,29 +242,24 @@ cudaError_t configure_projection_kernels() {
 }
 
 uint32_t projection_blocks(const ProjectionParams &p, uint32_t sm_count) {
-  if (!stream_eligible(p)) return 1;
-  // One block per SM; fewer when the matrix is too small to give every warp a
-  // chunk (toy shapes).
-  const StreamShape shape = make_stream_shape(p.cols, p.epilogue == kEpilogueSwiglu);
-  const uint32_t items = (p.rows + shape.rows_per_item - 1) / shape.rows_per_item;
-  uint32_t blocks = (items + kStreamWarps - 1) / kStreamWarps;
-  if (blocks > sm_count) blocks = sm_count;
-  if (blocks == 0) blocks = 1;
-  return blocks;
+  return stream_eligible(p, sm_count) ? blocks_for(p, sm_count) : 1u;
 }
 
 cudaError_t launch_projection(cudaStream_t stream, const ProjectionParams &p, uint32_t sm_count) {
-  if (stream_eligible(p)) {
-    const uint32_t blocks = projection_blocks(p, sm_count);
-    const uint32_t smem = stream_smem_bytes(p.cols);
+  if (stream_eligible(p, sm_count)) {
+    const uint32_t blocks = blocks_for(p, sm_count);
+    const uint32_t smem = stream_smem_bytes(p, blocks);
+    const bool pdl = p.pdl != 0;
     if (p.epilogue == kEpilogueStore) {
-      projection_stream_kernel<kEpilogueStore><<<blocks, kStreamThreads, smem, stream>>>(p);
-    } else if (p.epilogue == kEpilogueSwiglu) {
-      projection_stream_kernel<kEpilogueSwiglu><<<blocks, kStreamThreads, smem, stream>>>(p);
-    } else {
-      projection_stream_kernel<kEpilogueArgmax><<<blocks, kStreamThreads, smem, stream>>>(p);
+      return launch_with_pdl(projection_stream_kernel<kEpilogueStore>, dim3(blocks), dim3(kStreamThreads),
+                             smem, stream, pdl, p);
     }
-    return cudaGetLastError();
+    if (p.epilogue == kEpilogueSwiglu) {
+      return launch_with_pdl(projection_stream_kernel<kEpilogueSwiglu>, dim3(blocks), dim3(kStreamThreads),
+                             smem, stream, pdl, p);
+    }
+    return launch_with_pdl(projection_stream_kernel<kEpilogueArgmax>, dim3(blocks), dim3(kStreamThreads),
+                           smem, stream, pdl, p);
   }
   // Toy-shape path.  With a fused prologue the caller passes `cols` writable
   // bf16 elements in x_bf16; the normalised vector goes through them.

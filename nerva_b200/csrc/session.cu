@@ -231,7 +231,8 @@ bool plan_state(Session *s, StaticArena &arena, void *base) {
   ok = ok && carve(arena, base, static_cast<uint64_t>(d.hidden), &s->o_out);
   ok = ok && carve(arena, base, static_cast<uint64_t>(d.hidden), &s->down);
   ok = ok && carve(arena, base, static_cast<uint64_t>(d.vocab), &s->logits);
-  const uint64_t split_slots = std::max<uint32_t>(s->max_splits, kStepMaxSplits);
+  const uint64_t split_slots = std::max<uint32_t>(s->max_splits, 8u);  // fused attention uses up to 8
+  ok = ok && carve(arena, base, static_cast<uint64_t>(d.heads), &s->attn_tickets);
   s->x_elems = static_cast<uint32_t>(max_x);
   ok = ok && carve(arena, base, static_cast<uint64_t>(d.heads) * split_slots * d.head_dim, &s->partial_acc);
   ok = ok && carve(arena, base, static_cast<uint64_t>(d.heads) * split_slots, &s->partial_m);
@@ -239,6 +240,7 @@ bool plan_state(Session *s, StaticArena &arena, void *base) {
   ok = ok && carve(arena, base, static_cast<uint64_t>(d.layers), &s->step_layers);
   ok = ok && carve(arena, base, static_cast<uint64_t>(d.layers) * 4u + 1u, &s->step_jobs);
   ok = ok && carve(arena, base, uint64_t{4}, &s->barrier_counter);
+  ok = ok && carve(arena, base, static_cast<uint64_t>(kPhaseCount), &s->phase_cycles);
   ok = ok && carve(arena, base, ah, &s->attn_bf16);
   ok = ok && carve(arena, base, static_cast<uint64_t>(d.intermediate), &s->ff_bf16);
   ok = ok && carve(arena, base, max_x, &s->x_scratch);
@@ -301,9 +303,19 @@ const uint16_t *arena_at(Session *s, uint64_t offset) {
 // and the projection job list (QKV, O, gate/up, down per layer, then lm_head).
 cudaError_t setup_step_kernel(Session *s) {
   const ModelDims &d = s->dims;
-  s->step_kernel_ok = step_kernel_supported(d.hidden, d.heads, d.kv_heads, d.head_dim, d.intermediate, s->x_elems);
+  const uint32_t qkv_rows32 = static_cast<uint32_t>(d.attention_hidden() + 2 * d.kv_hidden());
+  s->row_elems = std::max(std::max(max_rows_per_block(qkv_rows32, 1, s->sm_count),
+                                   max_rows_per_block(2u * d.intermediate, 2, s->sm_count)),
+                          std::max(max_rows_per_block(d.hidden, 1, s->sm_count),
+                                   max_rows_per_block(d.vocab, 1, s->sm_count)));
+  s->step_kernel_ok = step_kernel_supported(d.hidden, d.heads, d.kv_heads, d.head_dim, d.intermediate,
+                                            s->x_elems, s->row_elems);
   if (!s->step_kernel_ok) return cudaSuccess;
   cudaError_t err = configure_step_kernel();
+  if (err != cudaSuccess) return err;
+  const char *profile = getenv("NERVA_B200_PHASE_PROFILE");
+  s->phase_profile = profile != nullptr && profile[0] == '1';
+  err = cudaMemsetAsync(s->phase_cycles, 0, kPhaseCount * sizeof(unsigned long long), s->stream);
   if (err != cudaSuccess) return err;
   const uint64_t ah = d.attention_hidden(), kvh = d.kv_hidden(), qkv_rows = ah + 2 * kvh;
   std::vector<StepLayerDev> layers(d.layers);
@@ -322,13 +334,13 @@ cudaError_t setup_step_kernel(Session *s) {
     o.key_pages = s->kv_keys + l * s->kv_layer_elems;
     o.value_pages = s->kv_values + l * s->kv_layer_elems;
     jobs[4 * l + 0] = JobDesc{s->weights->qkv_packed + static_cast<uint64_t>(l) * qkv_rows * d.hidden,
-                              static_cast<uint32_t>(qkv_rows), d.hidden, 0, 0};
-    jobs[4 * l + 1] = JobDesc{arena_at(s, L.w_o), d.hidden, static_cast<uint32_t>(ah), 0, 0};
+                              static_cast<uint32_t>(qkv_rows), d.hidden, 1, 0};
+    jobs[4 * l + 1] = JobDesc{arena_at(s, L.w_o), d.hidden, static_cast<uint32_t>(ah), 1, 0};
     jobs[4 * l + 2] = JobDesc{s->weights->gate_up_packed + static_cast<uint64_t>(l) * 2u * d.intermediate * d.hidden,
-                              2u * d.intermediate, d.hidden, 1, 0};
-    jobs[4 * l + 3] = JobDesc{arena_at(s, L.w_down), d.hidden, d.intermediate, 0, 0};
+                              2u * d.intermediate, d.hidden, 2, 0};
+    jobs[4 * l + 3] = JobDesc{arena_at(s, L.w_down), d.hidden, d.intermediate, 1, 0};
   }
-  jobs[4 * d.layers] = JobDesc{arena_at(s, s->layout.lm_head), d.vocab, d.hidden, 0, 0};
+  jobs[4 * d.layers] = JobDesc{arena_at(s, s->layout.lm_head), d.vocab, d.hidden, 1, 0};
   for (const JobDesc &j : jobs) {
     if ((reinterpret_cast<uintptr_t>(j.weight) & 15u) != 0) s->step_kernel_ok = false;  // TMA source alignment
   }
@@ -342,10 +354,11 @@ cudaError_t setup_step_kernel(Session *s) {
   return err;
 }
 
-// Attention items per query head in the whole-step kernel: about 256 cached
-// tokens (one 32-token tile per warp) per item, at most kStepMaxSplits.
+// Attention items per query head in the whole-step kernel: one 32-token tile
+// per warp per item where possible, at most kStepMaxSplits items.
 uint32_t step_kernel_splits(uint32_t target_context) {
-  uint32_t s = (target_context + 255u) / 256u;
+  const uint32_t per_item = kStreamWarps * kStepAttnTile;
+  uint32_t s = (target_context + per_item - 1u) / per_item;
   if (s < 1) s = 1;
   if (s > kStepMaxSplits) s = kStepMaxSplits;
   return s;
@@ -387,6 +400,8 @@ cudaError_t enqueue_step_kernel(Session *s, uint32_t splits, uint32_t sample) {
   p.barrier_counter = s->barrier_counter;
   p.sample = sample;
   p.x_elems = s->x_elems;
+  p.row_elems = s->row_elems;
+  p.phase_cycles = s->phase_profile ? s->phase_cycles : nullptr;
   return launch_step_kernel(s->stream, p, s->sm_count);
 }
 
@@ -423,6 +438,7 @@ cudaError_t enqueue_step(Session *s, uint32_t splits, uint32_t sample, uint64_t 
     const LayerLayout &L = s->layout.layers[l];
     ProjectionParams p{};
     p.error_word = s->device_error;
+    p.pdl = s->use_pdl ? 1u : 0u;
     p.eps = s->rms_eps;
     // QKV
     p.weight = s->weights->qkv_packed + static_cast<uint64_t>(l) * qkv_rows * d.hidden;
@@ -457,6 +473,39 @@ cudaError_t enqueue_step(Session *s, uint32_t splits, uint32_t sample, uint64_t 
     qp.value_pages = s->kv_values + l * s->kv_layer_elems;
     qp.page_table = s->page_table;
     qp.page_count = s->kv_pages;
+    if (s->fused_attention) {
+      // q/k norm + RoPE + KV append + split attention + merge in one launch
+      FusedAttentionParams fp{};
+      fp.cursor = s->device_cursor;
+      fp.max_context = s->max_context;
+      fp.qkv = s->qkv;
+      fp.q_bias = qp.q_bias;
+      fp.k_bias = qp.k_bias;
+      fp.v_bias = qp.v_bias;
+      fp.q_norm = qp.q_norm;
+      fp.k_norm = qp.k_norm;
+      fp.key_pages = qp.key_pages;
+      fp.value_pages = qp.value_pages;
+      fp.page_table = s->page_table;
+      fp.page_count = s->kv_pages;
+      fp.heads = d.heads;
+      fp.kv_heads = d.kv_heads;
+      fp.head_dim = d.head_dim;
+      fp.eps = s->rms_eps;
+      fp.rope_theta = s->rope_theta;
+      fp.splits = splits;
+      fp.partial_acc = s->partial_acc;
+      fp.partial_m = s->partial_m;
+      fp.partial_l = s->partial_l;
+      fp.tickets = s->attn_tickets;
+      fp.out_bf16 = s->attn_bf16;
+      fp.error_word = s->device_error;
+      fp.pdl = s->use_pdl ? 1u : 0u;
+      err = launch_fused_attention(s->stream, fp);
+      n += 1;
+      profile_mark(s, prof, kBucketAttention);
+      if (err != cudaSuccess) break;
+    } else {
     err = launch_qkv_prepare(s->stream, st, qp);
     n += 1;
     if (err != cudaSuccess) break;
@@ -482,10 +531,12 @@ cudaError_t enqueue_step(Session *s, uint32_t splits, uint32_t sample, uint64_t 
     n += 2;
     profile_mark(s, prof, kBucketAttention);
     if (err != cudaSuccess) break;
+    }
 
     // O
     p = ProjectionParams{};
     p.error_word = s->device_error;
+    p.pdl = s->use_pdl ? 1u : 0u;
     p.eps = s->rms_eps;
     p.weight = arena_at(s, L.w_o);
     p.rows = d.hidden;
@@ -502,6 +553,7 @@ cudaError_t enqueue_step(Session *s, uint32_t splits, uint32_t sample, uint64_t 
     // gate/up + SwiGLU
     p = ProjectionParams{};
     p.error_word = s->device_error;
+    p.pdl = s->use_pdl ? 1u : 0u;
     p.eps = s->rms_eps;
     p.weight = s->weights->gate_up_packed + static_cast<uint64_t>(l) * 2u * d.intermediate * d.hidden;
     p.rows = 2u * d.intermediate;
@@ -523,6 +575,7 @@ cudaError_t enqueue_step(Session *s, uint32_t splits, uint32_t sample, uint64_t 
     // down
     p = ProjectionParams{};
     p.error_word = s->device_error;
+    p.pdl = s->use_pdl ? 1u : 0u;
     p.eps = s->rms_eps;
     p.weight = arena_at(s, L.w_down);
     p.rows = d.hidden;
@@ -539,6 +592,7 @@ cudaError_t enqueue_step(Session *s, uint32_t splits, uint32_t sample, uint64_t 
   if (err == cudaSuccess && sample != 0) {
     ProjectionParams p{};
     p.error_word = s->device_error;
+    p.pdl = s->use_pdl ? 1u : 0u;
     p.eps = s->rms_eps;
     p.weight = arena_at(s, s->layout.lm_head);
     p.rows = d.vocab;
@@ -559,7 +613,7 @@ cudaError_t enqueue_step(Session *s, uint32_t splits, uint32_t sample, uint64_t 
     profile_mark(s, prof, kBucketLmHead);
   }
   if (err == cudaSuccess) {
-    err = launch_sample_greedy(s->stream, st, s->best_value, s->best_index, partials, sample);
+    err = launch_sample_greedy(s->stream, st, s->best_value, s->best_index, partials, sample, s->use_pdl);
     n += 1;
     profile_mark(s, prof, kBucketSampling);
   }
@@ -588,6 +642,14 @@ cudaError_t ensure_graph(Session *s, uint32_t splits, uint32_t sample, GraphEntr
   entry.splits = splits;
   entry.sample = sample;
   entry.engine = s->engine;
+  const char *no_graph = getenv("NERVA_B200_NO_GRAPH");
+  if (no_graph != nullptr && no_graph[0] == '1') {
+    // Profiling aid: replay the step as direct launches instead of a graph.
+    entry.nodes = 0;
+    s->graphs.push_back(entry);
+    *out = &s->graphs.back();
+    return cudaSuccess;
+  }
   cudaError_t err = cudaStreamBeginCapture(s->stream, cudaStreamCaptureModeThreadLocal);
   if (err != cudaSuccess) return err;
   uint64_t launches = 0;
@@ -630,6 +692,7 @@ cudaError_t replay(Session *s, GraphEntry *g) {
 
 uint32_t splits_for(Session *s, uint32_t target_context) {
   if (s->engine == 1) return step_kernel_splits(target_context);
+  if (s->fused_attention) return fused_attention_splits(target_context);
   uint32_t want = attention_default_splits(target_context, 1, s->dims.kv_heads, s->sm_count);
   uint32_t bucket = 1;
   while (bucket < want) bucket <<= 1;
@@ -997,6 +1060,11 @@ cudaError_t allocate_state(Session *s, int32_t *stage) {
                         cudaMemcpyHostToDevice, s->stream);
   if (err == cudaSuccess) err = cudaMemsetAsync(s->device_error, 0, sizeof(uint32_t), s->stream);
   if (err == cudaSuccess) err = cudaMemsetAsync(s->device_cursor, 0, sizeof(uint32_t), s->stream);
+  if (err == cudaSuccess)
+    err = cudaMemsetAsync(s->attn_tickets, 0, s->dims.heads * sizeof(uint32_t), s->stream);
+  s->fused_attention = fused_attention_supported(s->dims.heads, s->dims.kv_heads, s->dims.head_dim);
+  const char *pdl_env = getenv("NERVA_B200_PDL");
+  s->use_pdl = !(pdl_env != nullptr && pdl_env[0] == '0');
   if (err == cudaSuccess) err = cudaStreamSynchronize(s->stream);
   return err;
 }
@@ -1652,7 +1720,7 @@ extern "C" int nerva_b200_session_profile_steps(Session *s, uint32_t steps, uint
     bucket_ns[b] = 0;
     if (bucket_launches != nullptr) bucket_launches[b] = 0;
   }
-  static const uint32_t kLaunchesPerMark[kBucketCount] = {1, 1, 3, 1, 1, 1, 1, 1};
+  const uint32_t kLaunchesPerMark[kBucketCount] = {1, 1, s->fused_attention ? 1u : 3u, 1, 1, 1, 1, 1};
   StepProfile prof;
   const uint32_t splits = splits_for(s, static_cast<uint32_t>(target));
   cudaError_t err = cudaSuccess;
@@ -1681,4 +1749,15 @@ extern "C" int nerva_b200_session_profile_steps(Session *s, uint32_t steps, uint
   s->cursor = static_cast<uint32_t>(target);
   s->logits_valid = true;
   return 0;
+}
+
+// Reads and clears the per-phase cycle counters of the whole-step kernel (only
+// filled when the session was created with NERVA_B200_PHASE_PROFILE=1).
+extern "C" int nerva_b200_session_read_phase_cycles(Session *s, uint64_t *cycles, uint32_t capacity) {
+  if (s == nullptr || cycles == nullptr || capacity < kPhaseCount || s->phase_cycles == nullptr) return -1;
+  if (cudaStreamSynchronize(s->stream) != cudaSuccess) return -1;
+  if (cudaMemcpy(cycles, s->phase_cycles, kPhaseCount * sizeof(uint64_t), cudaMemcpyDeviceToHost) != cudaSuccess)
+    return -1;
+  if (cudaMemset(s->phase_cycles, 0, kPhaseCount * sizeof(uint64_t)) != cudaSuccess) return -1;
+  return static_cast<int>(kPhaseCount);
 }

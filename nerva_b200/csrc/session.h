@@ -11,6 +11,7 @@
 
 #include <memory>
 #include <string>
+#include <deque>
 #include <vector>
 
 #include "../../include/nerva_b200_api.h"
@@ -93,9 +94,9 @@ struct GraphEntry {
 struct StepLayerDev;
 struct JobDesc;
 struct StepKernelParams;
-uint32_t step_kernel_smem_bytes(uint32_t x_elems);
+uint32_t step_kernel_smem_bytes(uint32_t x_elems, uint32_t row_elems);
 bool step_kernel_supported(uint32_t hidden, uint32_t heads, uint32_t kv_heads, uint32_t head_dim,
-                           uint32_t intermediate, uint32_t x_elems);
+                           uint32_t intermediate, uint32_t x_elems, uint32_t row_elems);
 cudaError_t configure_step_kernel();
 cudaError_t launch_step_kernel(cudaStream_t stream, const StepKernelParams &p, uint32_t blocks);
 
@@ -135,6 +136,10 @@ struct NervaCudaHfDecodeSequenceSession {
   float *logits = nullptr;
   float *partial_acc = nullptr, *partial_m = nullptr, *partial_l = nullptr;
   uint32_t max_splits = 1;
+  uint32_t *attn_tickets = nullptr;  // per-head completion tickets of the fused attention kernel
+  bool fused_attention = false;      // head_dim 64/128: one attention launch per layer
+  bool use_pdl = true;               // programmatic dependent launch between the step's kernels
+                                     // (NERVA_B200_PDL=0 at create turns it off)
   uint16_t *attn_bf16 = nullptr, *ff_bf16 = nullptr, *x_scratch = nullptr;
   float *best_value = nullptr;
   uint32_t *best_index = nullptr;
@@ -142,7 +147,10 @@ struct NervaCudaHfDecodeSequenceSession {
   nb::StepLayerDev *step_layers = nullptr;
   nb::JobDesc *step_jobs = nullptr;
   uint32_t *barrier_counter = nullptr;
+  unsigned long long *phase_cycles = nullptr;  // per-phase SM cycles of block 0 (tuning aid)
+  bool phase_profile = false;                  // NERVA_B200_PHASE_PROFILE=1 at create
   uint32_t x_elems = 0;
+  uint32_t row_elems = 0;  // rows of the largest per-block row range of any projection
   bool step_kernel_ok = false;
   NervaCudaSyntheticTokenSlot *device_slots = nullptr;
   uint32_t *device_cursor = nullptr, *device_error = nullptr, *device_prompt = nullptr;
@@ -153,7 +161,7 @@ struct NervaCudaHfDecodeSequenceSession {
 
   cudaStream_t stream = nullptr;
   cudaEvent_t ev_start = nullptr, ev_stop = nullptr;
-  std::vector<nb::GraphEntry> graphs;
+  std::deque<nb::GraphEntry> graphs;  // deque: entries keep their address when more are cached
 
   // active request
   bool started = false, finished = false;

@@ -30,6 +30,7 @@ __device__ __forceinline__ void add_norm_to_smem(uint16_t *x, const float *a, co
                     (reinterpret_cast<uintptr_t>(w) & 7u) == 0;
   if (fast) {
     float4 r[kNormRegIters];
+    uint2 wk[kNormRegIters];
     float sumsq = 0.0f;
 #pragma unroll
     for (uint32_t k = 0; k < kNormRegIters; ++k) {
@@ -45,6 +46,7 @@ __device__ __forceinline__ void add_norm_to_smem(uint16_t *x, const float *a, co
           v.w = t.w + v.w;
         }
         r[k] = v;
+        wk[k] = reinterpret_cast<const uint2 *>(w)[i];  // in flight together with a and b
         sumsq += v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w;
       }
     }
@@ -56,7 +58,7 @@ __device__ __forceinline__ void add_norm_to_smem(uint16_t *x, const float *a, co
       if (i < vecs) {
         const float4 v = r[k];
         if (resid_out != nullptr) reinterpret_cast<float4 *>(resid_out)[i] = v;
-        const uint2 wb = reinterpret_cast<const uint2 *>(w)[i];
+        const uint2 wb = wk[k];
         uint2 out;
         out.x = static_cast<uint32_t>(f32_to_bf16_bits(v.x * scale * bf16x2_lo(wb.x))) |
                 (static_cast<uint32_t>(f32_to_bf16_bits(v.y * scale * bf16x2_hi(wb.x))) << 16);

@@ -1,9 +1,10 @@
 // Parameters and device helpers of the whole-step kernel (engine 1).
 #pragma once
 
+#include "attention_device.cuh"
 #include "kernels.cuh"
+#include "row_stream.cuh"
 #include "step_device.cuh"
-#include "weight_stream_multi.cuh"
 
 namespace nb {
 
@@ -31,24 +32,44 @@ struct StepKernelParams {
   uint32_t *best_index;
   uint32_t *barrier_counter;  // zeroed before every launch
   uint32_t sample;
-  uint32_t x_elems;  // capacity of the shared activation vector (bf16 elements)
+  uint32_t x_elems;    // capacity of the shared activation vector (bf16 elements)
+  uint32_t row_elems;  // capacity of the shared row-total buffer (floats)
+  // Optional: block 0 adds the SM cycles it spent in each phase of the step
+  // (kPhase* slots), for tuning.  Null in normal operation.
+  unsigned long long *phase_cycles;
+};
+
+enum StepPhase : uint32_t {
+  kPhaseQkvPrologue = 0, kPhaseQkv, kPhaseBarrierQkv, kPhaseAttention, kPhaseBarrierAttention,
+  kPhaseOPrologue, kPhaseO, kPhaseBarrierO, kPhaseGateUpPrologue, kPhaseGateUp, kPhaseBarrierGateUp,
+  kPhaseDownPrologue, kPhaseDown, kPhaseBarrierDown, kPhaseLmHead, kPhaseTail, kPhaseCount
 };
 
 constexpr uint32_t kStepMaxSplits = 4;  // attention items per query head
 constexpr uint32_t kStepAttnTile = 32;
 constexpr uint32_t kStepMaxHeadDim = 128;
+constexpr uint32_t kStepMaxHeads = 64;
 
-// Shared memory beyond the ring and the activation vector.
+// Shared memory beyond the ring, the activation vector and the row totals.
 struct StepShared {
-  uint64_t bars[kStreamWarps * kStreamSlots];
+  StreamShared stream;
   float scratch[64];
   uint32_t dead;                                   // a grid barrier timed out
-  alignas(16) float q[kStepMaxHeadDim];            // this item's query, pre-scaled (read as float4)
-  alignas(16) float k_new[kStepMaxHeadDim];        // current token's K and V, bf16-rounded
-  alignas(16) float v_new[kStepMaxHeadDim];
-  alignas(16) float p[kStreamWarps][kStepAttnTile];
-  alignas(16) float merge[kStreamWarps][kStepMaxHeadDim + 2];
+  AttnItemShared<kStreamWarps> attn;
+  alignas(16) float weights[kStepMaxHeads * kStepMaxSplits];  // merge weights per (head, item)
 };
+// The per-warp merge records of the attention phase ([warps][head_dim + 2]
+// floats) overlay the activation vector, which is dead between the QKV
+// projection and the O prologue.
+constexpr uint32_t kStepMergeStride = kAttnMergeStride;
+constexpr uint32_t kStepMergeBytes = kStreamWarps * kStepMergeStride * 4u;
+__host__ __device__ inline uint32_t step_round128(uint32_t v) { return (v + 127u) & ~127u; }
+// Bytes reserved for the activation vector (and the merge records that overlay it).
+__host__ __device__ inline uint32_t step_x_bytes(uint32_t x_elems) {
+  const uint32_t x = step_round128(x_elems * 2u);
+  const uint32_t m = step_round128(kStepMergeBytes);
+  return x > m ? x : m;
+}
 
 // Grid-wide barrier number `index` (1-based) of this launch.  All threads of
 // all blocks call it.  A block that waits longer than the cycle limit records
@@ -75,39 +96,6 @@ __device__ __forceinline__ void grid_barrier(const StepKernelParams &p, StepShar
     __threadfence();
   }
   __syncthreads();
-}
-
-// Per-head RMSNorm + RoPE of one head held four-elements-per-lane by one warp
-// (element e = lane + 32 k).  head_dim is a multiple of 64, so both members of
-// every rotary pair (e, e + d/2) live in the same lane.
-template <uint32_t PER>  // elements per lane; head_dim = 32 * PER
-__device__ __forceinline__ void head_norm_rope(float (&v)[PER], const uint16_t *norm, float eps,
-                                               float theta, uint32_t position) {
-  constexpr uint32_t D = PER * 32u;
-  constexpr uint32_t HALF = PER / 2u;  // v[k] pairs with v[k + HALF]
-  const uint32_t lane = threadIdx.x & 31u;
-  if (norm != nullptr) {
-    float ss = 0.0f;
-#pragma unroll
-    for (uint32_t k = 0; k < PER; ++k) ss += v[k] * v[k];
-    ss = warp_sum(ss);
-    const float scale = rsqrtf(ss / static_cast<float>(D) + eps);
-#pragma unroll
-    for (uint32_t k = 0; k < PER; ++k) v[k] *= scale * bf16_bits_to_f32(norm[lane + 32u * k]);
-  }
-  if (theta > 0.0f) {
-#pragma unroll
-    for (uint32_t k = 0; k < HALF; ++k) {
-      const uint32_t i = lane + 32u * k;
-      const float exponent = static_cast<float>(2u * i) / static_cast<float>(D);
-      const float angle = static_cast<float>(position) / powf(theta, exponent);
-      float s, c;
-      sincosf(angle, &s, &c);
-      const float left = v[k], right = v[k + HALF];
-      v[k] = left * c - right * s;
-      v[k + HALF] = right * c + left * s;
-    }
-  }
 }
 
 }  // namespace nb

@@ -12,7 +12,7 @@ import re
 
 _HERE = os.path.dirname(os.path.abspath(__file__))
 HEADER = os.path.join(_HERE, "..", "include", "nerva_b200_api.h")
-LIB_PATH = os.path.join(_HERE, "_lib", "libnerva_b200.so")
+LIB_PATH = os.environ.get("NERVA_B200_LIB") or os.path.join(_HERE, "_lib", "libnerva_b200.so")
 
 _SCALARS = {
     "uint8_t": C.c_uint8, "uint16_t": C.c_uint16, "uint32_t": C.c_uint32, "uint64_t": C.c_uint64,
@@ -107,6 +107,7 @@ def lib() -> C.CDLL:
         "nerva_b200_session_get_kv_block_table": [vp, vp, C.c_uint32],
         "nerva_b200_session_read_kv_row": [vp, C.c_uint32, C.c_uint32, C.c_uint32, vp, C.c_uint32],
         "nerva_b200_session_profile_steps": [vp, C.c_uint32, vp, vp, C.c_uint32],
+        "nerva_b200_session_read_phase_cycles": [vp, vp, C.c_uint32],
         "nerva_b200_projection": [vp, vp, vp, C.c_uint32, C.c_uint32, C.c_uint32, C.c_uint32, C.c_uint32,
                                   P(C.c_uint64)],
         "nerva_b200_gqa_decode_attention": [vp, vp, vp, vp, vp, C.c_uint32, C.c_uint32, C.c_uint32, C.c_uint32,

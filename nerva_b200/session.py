@@ -225,6 +225,18 @@ class CudaHfDecodeSequenceSession:
         return {name: {"ns": int(ns[i]), "launches_per_step": int(launches[i])}
                 for i, name in enumerate(self.PROFILE_BUCKETS)}
 
+    PHASES = ("qkv_prologue", "qkv", "barrier_qkv", "attention", "barrier_attention", "o_prologue", "o",
+              "barrier_o", "gate_up_prologue", "gate_up", "barrier_gate_up", "down_prologue", "down",
+              "barrier_down", "lm_head", "tail")
+
+    def read_phase_cycles(self) -> dict:
+        """Per-phase SM cycles of block 0 of the whole-step kernel since the last read
+        (needs NERVA_B200_PHASE_PROFILE=1 in the environment when the session is created)."""
+        cycles = np.zeros(16, dtype=np.uint64)
+        if ffi.lib().nerva_b200_session_read_phase_cycles(self._handle, _ptr(cycles), 16) < 0:
+            raise RuntimeError("phase cycles unavailable")
+        return {name: int(c) for name, c in zip(self.PHASES, cycles)}
+
     def destroy(self) -> None:
         if self._handle:
             ffi.lib().nerva_cuda_hf_decode_sequence_session_destroy(self._handle)

@@ -183,7 +183,7 @@ def test_qwen3_8b_shapes_logits(built_lib, oracle_mod, layers):
     ref_tokens, ref_logits = dec.decode_greedy(prompt, 4, want_logits=True)
     bound = LOGIT_ATOL
     if layers > 1:
-        bound = max(LOGIT_ATOL, 1.5 * contract_self_distance(oracle_mod, ck, 32, prompt, 4, ref_logits))
+        bound = max(LOGIT_ATOL, 2.0 * contract_self_distance(oracle_mod, ck, 32, prompt, 4, ref_logits))
     srt = np.sort(ref_logits, axis=1)
     margins = srt[:, -1] - srt[:, -2]
     for step, (a, b) in enumerate(zip(out.tokens, ref_tokens.tolist())):

@@ -93,7 +93,7 @@ def test_whole_step_kernel_qwen3_8b_layer_shapes(built_lib, oracle_mod):
     ref_tokens, ref_logits = dec.decode_greedy(prompt, 4, want_logits=True)
     assert out.tokens == ref_tokens.tolist()
     # at these widths the contract's own summation-order sensitivity can exceed 2e-2
-    bound = max(LOGIT_ATOL, 1.5 * contract_self_distance(oracle_mod, ck, 64, prompt, 4, ref_logits))
+    bound = max(LOGIT_ATOL, 2.0 * contract_self_distance(oracle_mod, ck, 64, prompt, 4, ref_logits))
     assert np.abs(got - ref_logits[-1]).max() <= bound
 
 
