@@ -293,7 +293,7 @@ def main() -> None:
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--config", default="qwen3-8b", choices=["qwen3-8b", "tiny"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
-    ap.add_argument("--engine", type=int, default=1, choices=[0, 1],
+    ap.add_argument("--engine", type=int, default=0, choices=[0, 1],
                     help="0: one kernel per operator in a CUDA graph; 1: the whole-step kernel")
     args = ap.parse_args()
     rank = int(os.environ.get("RANK", "0"))

@@ -128,6 +128,23 @@ __device__ __forceinline__ void tma_load_1d(void *smem_dst, const void *gmem_src
       "l"(gmem_src), "r"(bytes), "r"(smem_addr(bar))
       : "memory");
 }
+// L2 policy for data that is read once per step (the weights): first in line for
+// eviction, so that 15 GB of weight traffic per token does not push the small
+// per-token working set (KV pages, norm weights, page table, activations) out
+// of the 126 MB L2.
+__device__ __forceinline__ uint64_t l2_evict_first_policy() {
+  uint64_t policy;
+  asm volatile("createpolicy.fractional.L2::evict_first.b64 %0, 1.0;" : "=l"(policy));
+  return policy;
+}
+__device__ __forceinline__ void tma_load_1d_hint(void *smem_dst, const void *gmem_src, uint32_t bytes,
+                                                 uint64_t *bar, uint64_t policy) {
+  asm volatile(
+      "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes.L2::cache_hint "
+      "[%0], [%1], %2, [%3], %4;" ::"r"(smem_addr(smem_dst)),
+      "l"(gmem_src), "r"(bytes), "r"(smem_addr(bar)), "l"(policy)
+      : "memory");
+}
 
 // ---- programmatic dependent launch ----
 // A kernel launched with the programmatic-serialization attribute may start

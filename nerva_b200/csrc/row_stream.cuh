@@ -141,6 +141,7 @@ struct RowStream {
   uint32_t issue_job;
   WarpJob issue;
   StreamCursor issue_cursor;
+  uint64_t policy;  // L2 evict-first: weights are read once per step
 };
 
 __device__ inline void stream_init(RowStream &rs, uint8_t *ring_base, StreamShared &sh,
@@ -153,6 +154,7 @@ __device__ inline void stream_init(RowStream &rs, uint8_t *ring_base, StreamShar
   rs.issued = rs.consumed = 0;
   rs.dead = false;
   rs.drain_from = rs.drain_to = 0;
+  rs.policy = l2_evict_first_policy();
   rs.issue_job = 0;
   if (job_count != 0) {
     rs.issue = warp_job(jobs[0]);
@@ -182,7 +184,7 @@ __device__ __forceinline__ void stream_fill(RowStream &rs) {
     const uint32_t slot = rs.issued % kStreamSlots;
     if ((threadIdx.x & 31u) == 0) {
       mbar_arrive_expect_tx(&rs.bars[slot], len);
-      tma_load_1d(rs.ring + slot * kChunkBytes, rs.issue.base + pos, len, &rs.bars[slot]);
+      tma_load_1d_hint(rs.ring + slot * kChunkBytes, rs.issue.base + pos, len, &rs.bars[slot], rs.policy);
     }
     rs.issued += 1;
   }

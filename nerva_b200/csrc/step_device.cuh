@@ -87,4 +87,70 @@ __device__ __forceinline__ void add_norm_to_smem(uint16_t *x, const float *a, co
   }
 }
 
+// Prologue of the O projection: merges the split-attention partials of every
+// head into the bf16 activation vector,
+//   x[h*D + d] = bf16( sum_s acc[h][s][d] w[h][s] ),
+//   w[h][s] = 2^{m_s - M} / sum_s l_s 2^{m_s - M}
+// (the algebra of hf_decode_sequence/kernels.cu:494-555, base 2).  Two round
+// trips to L2 per block: first the (m, l) pairs become normalised weights in
+// shared memory (`weights`, heads * S floats), then every thread issues all of
+// its partial-accumulator loads before it uses any of them.
+constexpr uint32_t kMergeMaxSplits = 8;
+
+__device__ __forceinline__ void merge_attention_to_smem(uint16_t *x, float *weights,
+                                                        const float *partial_acc,
+                                                        const float *partial_m,
+                                                        const float *partial_l, uint32_t heads,
+                                                        uint32_t D, uint32_t S) {
+  for (uint32_t h = threadIdx.x; h < heads; h += blockDim.x) {
+    float ms[kMergeMaxSplits], ls[kMergeMaxSplits];
+#pragma unroll
+    for (uint32_t s = 0; s < kMergeMaxSplits; ++s) {
+      ms[s] = s < S ? __ldcg(partial_m + h * S + s) : -INFINITY;
+      ls[s] = s < S ? __ldcg(partial_l + h * S + s) : 0.0f;
+    }
+    float m = -INFINITY;
+#pragma unroll
+    for (uint32_t s = 0; s < kMergeMaxSplits; ++s)
+      if (ls[s] > 0.0f) m = fmaxf(m, ms[s]);
+    float l = 0.0f;
+#pragma unroll
+    for (uint32_t s = 0; s < kMergeMaxSplits; ++s)
+      if (ls[s] > 0.0f) l = fmaf(ls[s], exp2f(ms[s] - m), l);
+    const float inv = l > 0.0f ? 1.0f / l : 0.0f;
+#pragma unroll
+    for (uint32_t s = 0; s < kMergeMaxSplits; ++s)
+      if (s < S) weights[h * S + s] = ls[s] > 0.0f ? exp2f(ms[s] - m) * inv : 0.0f;
+  }
+  __syncthreads();
+  constexpr uint32_t kBatch = 4;
+  const uint32_t total = heads * D;
+  for (uint32_t base = 0; base < total; base += kBatch * blockDim.x) {
+    float v[kBatch][kMergeMaxSplits];
+#pragma unroll
+    for (uint32_t k = 0; k < kBatch; ++k) {
+      const uint32_t idx = base + k * blockDim.x + threadIdx.x;
+      const uint32_t h = idx / D, d = idx - h * D;
+#pragma unroll
+      for (uint32_t s = 0; s < kMergeMaxSplits; ++s) {
+        v[k][s] = (idx < total && s < S)
+                      ? __ldcg(partial_acc + (static_cast<uint64_t>(h) * S + s) * D + d)
+                      : 0.0f;
+      }
+    }
+#pragma unroll
+    for (uint32_t k = 0; k < kBatch; ++k) {
+      const uint32_t idx = base + k * blockDim.x + threadIdx.x;
+      if (idx < total) {
+        const uint32_t h = idx / D;
+        float a = 0.0f;
+#pragma unroll
+        for (uint32_t s = 0; s < kMergeMaxSplits; ++s)
+          if (s < S) a = fmaf(v[k][s], weights[h * S + s], a);
+        x[idx] = f32_to_bf16_bits(a);
+      }
+    }
+  }
+}
+
 }  // namespace nb

@@ -56,64 +56,6 @@ __device__ void attention_phase(const StepKernelParams &p, StepShared &sh, float
   }
 }
 
-// x[h*D + d] = bf16( sum_s acc_s w_s ),  w_s = 2^{m_s - M} / sum_s l_s 2^{m_s - M}.
-// Two round trips to L2 per block: first the (m, l) pairs of every (head, split)
-// become normalised weights in shared memory, then every thread issues all of its
-// partial-accumulator loads before it uses any of them.
-__device__ void merge_attention_to_smem(const StepKernelParams &p, StepShared &sh, uint16_t *x) {
-  const uint32_t D = p.head_dim, S = p.attn_splits;
-  float *weights = sh.weights;  // [heads][S]
-  for (uint32_t h = threadIdx.x; h < p.heads; h += blockDim.x) {
-    float ms[kStepMaxSplits], ls[kStepMaxSplits];
-#pragma unroll
-    for (uint32_t s = 0; s < kStepMaxSplits; ++s) {
-      ms[s] = s < S ? __ldcg(p.partial_m + h * S + s) : -INFINITY;
-      ls[s] = s < S ? __ldcg(p.partial_l + h * S + s) : 0.0f;
-    }
-    float m = -INFINITY;
-#pragma unroll
-    for (uint32_t s = 0; s < kStepMaxSplits; ++s)
-      if (ls[s] > 0.0f) m = fmaxf(m, ms[s]);
-    float l = 0.0f;
-#pragma unroll
-    for (uint32_t s = 0; s < kStepMaxSplits; ++s)
-      if (ls[s] > 0.0f) l = fmaf(ls[s], exp2f(ms[s] - m), l);
-    const float inv = l > 0.0f ? 1.0f / l : 0.0f;
-#pragma unroll
-    for (uint32_t s = 0; s < kStepMaxSplits; ++s)
-      if (s < S) weights[h * S + s] = ls[s] > 0.0f ? exp2f(ms[s] - m) * inv : 0.0f;
-  }
-  __syncthreads();
-  constexpr uint32_t kBatch = 8;
-  const uint32_t total = p.heads * D;
-  for (uint32_t base = 0; base < total; base += kBatch * blockDim.x) {
-    float v[kBatch][kStepMaxSplits];
-#pragma unroll
-    for (uint32_t k = 0; k < kBatch; ++k) {
-      const uint32_t idx = base + k * blockDim.x + threadIdx.x;
-      const uint32_t h = idx / D, d = idx - h * D;
-#pragma unroll
-      for (uint32_t s = 0; s < kStepMaxSplits; ++s) {
-        v[k][s] = (idx < total && s < S)
-                      ? __ldcg(p.partial_acc + (static_cast<uint64_t>(h) * S + s) * D + d)
-                      : 0.0f;
-      }
-    }
-#pragma unroll
-    for (uint32_t k = 0; k < kBatch; ++k) {
-      const uint32_t idx = base + k * blockDim.x + threadIdx.x;
-      if (idx < total) {
-        const uint32_t h = idx / D;
-        float a = 0.0f;
-#pragma unroll
-        for (uint32_t s = 0; s < kStepMaxSplits; ++s)
-          if (s < S) a = fmaf(v[k][s], weights[h * S + s], a);
-        x[idx] = f32_to_bf16_bits(a);
-      }
-    }
-  }
-}
-
 }  // namespace
 }  // namespace nb
 

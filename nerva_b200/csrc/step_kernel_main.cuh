@@ -100,7 +100,8 @@ __global__ void __launch_bounds__(kStreamThreads, 1) decode_step_kernel(StepKern
     mark(kPhaseBarrierAttention);
     // ---- O ----
     clear_rows(4u * l + 1u);
-    merge_attention_to_smem(p, sh, x);
+    merge_attention_to_smem(x, sh.weights, p.partial_acc, p.partial_m, p.partial_l, p.heads, p.head_dim,
+                            p.attn_splits);
     __syncthreads();
     mark(kPhaseOPrologue);
     stream_consume(rs, sh.stream, 4u * l + 1u, x, row_total, p.st.error_word);
