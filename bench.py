@@ -100,11 +100,15 @@ class ClockSampler:
                 "samples": len(sm), "reasons": sorted(reasons)}
 
 
-def workload(name: str):
+def workload(name: str, layers: int = 0, prompt_tokens: int = 0):
+    import dataclasses
     from nerva_b200 import synth
-    if name == "tiny":
-        return synth.TINY_QWEN3
-    return synth.QWEN3_8B
+    cfg = synth.TINY_QWEN3 if name == "tiny" else synth.QWEN3_8B
+    if layers > 0:       # profiler captures: same kernels and shapes, fewer layers resident
+        cfg = dataclasses.replace(cfg, layers=layers, name=f"{cfg.name} cut to {layers} layers")
+    if prompt_tokens > 0:
+        cfg = dataclasses.replace(cfg, prompt_tokens=prompt_tokens)
+    return cfg
 
 
 def config_block(cfg, gpus: int, extra: dict | None = None) -> dict:
@@ -295,11 +299,14 @@ def main() -> None:
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--engine", type=int, default=0, choices=[0, 1],
                     help="0: one kernel per operator in a CUDA graph; 1: the whole-step kernel")
+    ap.add_argument("--layers", type=int, default=0,
+                    help="cut the model to this many layers (profiler captures only; not a bench line)")
+    ap.add_argument("--prompt-tokens", type=int, default=0, help="override the prompt length")
     args = ap.parse_args()
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
     local = int(os.environ.get("LOCAL_RANK", "0"))
-    cfg = workload(args.config)
+    cfg = workload(args.config, args.layers, args.prompt_tokens)
     if args.impl == "reference":
         if rank == 0:
             print(json.dumps(run_reference(args, cfg)), flush=True)
