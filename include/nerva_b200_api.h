@@ -658,6 +658,22 @@ int nerva_b200_gqa_decode_attention(const float *q, const uint16_t *key_pages,
                                     uint32_t kv_heads, uint32_t head_dim, uint32_t warmup,
                                     uint32_t iterations, uint64_t *avg_ns);
 
+/* The same attention with DEVICE pointers (layouts as above) and no allocation:
+ * the split partials live in a fixed 4 MiB device array inside the library, so
+ * the call needs batch*heads*splits*(head_dim+2) <= 1048576 floats (the split
+ * count is lowered to fit; a shape that does not fit unsplit returns -1 with
+ * the limit in nerva_b200_last_error()).  `stream` is a cudaStream_t (NULL: the
+ * default stream); the call returns once the stream has finished the work.
+ * Calls on one device share the array, so overlapping calls race: serialise
+ * them.  The first call on each device performs the set-up and should be made
+ * before any stream capture begins.  No counterpart in the reference: it is
+ * for callers whose arena already owns the device memory, or whose decode loop
+ * must report zero hot-path allocations. */
+int nerva_b200_gqa_decode_attention_static_scratch(
+    const float *q, const uint16_t *key_pages, const uint16_t *value_pages,
+    const uint32_t *page_table, float *out, uint32_t batch, uint32_t context, uint32_t heads,
+    uint32_t kv_heads, uint32_t head_dim, void *stream);
+
 /* Greedy argmax over f32 logits with the sampler's tie rule (lowest index,
  * non-finite values skipped).  Host pointers. */
 int nerva_b200_greedy_argmax(const float *logits, uint32_t count, uint32_t *token);

@@ -112,6 +112,8 @@ def lib() -> C.CDLL:
                                   P(C.c_uint64)],
         "nerva_b200_gqa_decode_attention": [vp, vp, vp, vp, vp, C.c_uint32, C.c_uint32, C.c_uint32, C.c_uint32,
                                             C.c_uint32, C.c_uint32, C.c_uint32, P(C.c_uint64)],
+        "nerva_b200_gqa_decode_attention_static_scratch": [vp, vp, vp, vp, vp, C.c_uint32, C.c_uint32,
+                                                           C.c_uint32, C.c_uint32, C.c_uint32, vp],
         "nerva_b200_greedy_argmax": [vp, C.c_uint32, P(C.c_uint32)],
         "nerva_b200_synth_normal_bf16": [C.c_uint64, C.c_uint64, C.c_uint64, C.c_float, vp],
     }

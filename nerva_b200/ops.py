@@ -45,6 +45,17 @@ def gqa_decode_attention(q: np.ndarray, key_pages: np.ndarray, value_pages: np.n
     return out, ns.value
 
 
+def gqa_decode_attention_static_scratch(q_ptr: int, key_pages_ptr: int, value_pages_ptr: int, page_table_ptr: int,
+                                        out_ptr: int, batch: int, context: int, heads: int, kv_heads: int,
+                                        head_dim: int, stream: int = 0) -> None:
+    """The same attention on DEVICE addresses, with the split partials in the library's fixed
+    device array: the call allocates nothing and returns when `stream` has finished the work.
+    Calls on one device share that array; do not overlap them."""
+    _check(ffi.lib().nerva_b200_gqa_decode_attention_static_scratch(
+        q_ptr, key_pages_ptr, value_pages_ptr, page_table_ptr, out_ptr, batch, context, heads, kv_heads,
+        head_dim, stream), "gqa_decode_attention_static_scratch")
+
+
 def greedy_argmax(logits: np.ndarray) -> int:
     logits = np.ascontiguousarray(logits, dtype=np.float32)
     token = C.c_uint32(0)
