@@ -571,8 +571,8 @@ int nerva_cuda_hf_decode_sequence_plan_layout(
 /* nerva_cuda_api.h:2163 */
 int nerva_cuda_hf_decode_sequence_session_create(
     const NervaCudaHfDecodeSequenceSessionCreateRequest *request,
-    NervaCudaHfDecodeSequenceSession **session,
-    NervaCudaHfDecodeSequenceSessionCreateResult *out);
+    NervaCudaHfDecodeSequenceSessionCreateResult *out,
+    NervaCudaHfDecodeSequenceSession **session);
 /* nerva_cuda_api.h:2167 */
 int nerva_cuda_hf_decode_sequence_session_run(
     const NervaCudaHfDecodeSequenceSessionRunRequest *request,
@@ -588,10 +588,12 @@ int nerva_cuda_hf_decode_sequence_session_advance(
 /* nerva_cuda_api.h:2212 */
 int nerva_cuda_hf_decode_sequence_session_fork_shared_weights(
     const NervaCudaHfDecodeSequenceSessionForkSharedWeightsRequest *request,
-    NervaCudaHfDecodeSequenceSession **session,
-    NervaCudaHfDecodeSequenceSessionCreateResult *out);
+    NervaCudaHfDecodeSequenceSessionCreateResult *out,
+    NervaCudaHfDecodeSequenceSession **session_out);
 /* nerva_cuda_api.h:2216 */
-int nerva_cuda_hf_decode_sequence_session_destroy(NervaCudaHfDecodeSequenceSession *session);
+int nerva_cuda_hf_decode_sequence_session_destroy(
+    NervaCudaHfDecodeSequenceSession *session,
+    NervaCudaHfDecodeSequenceSessionCreateResult *out /* nullable */);
 /* nerva_cuda_api.h:2157 — one-shot: create, run, destroy. */
 int nerva_cuda_hf_decode_sequence_u16(const NervaCudaHfDecodeSequenceRequest *request,
                                       NervaCudaHfDecodeSequenceResult *out);
@@ -640,6 +642,15 @@ int nerva_b200_session_profile_steps(NervaCudaHfDecodeSequenceSession *session, 
 int nerva_b200_session_read_phase_cycles(NervaCudaHfDecodeSequenceSession *session,
                                          uint64_t *cycles, uint32_t capacity);
 
+/* Tuning aid of the per-operator engine: nanosecond stamps (%globaltimer) of the
+ * last step, 8 per launch, launches ordered [layer][QKV, attention, O, gate/up,
+ * down] then lm_head.  Slots 0..3: first block at kernel entry, after the wait
+ * for the previous kernel, after the prologue, before exit; slots 4..7: the same
+ * for the last block.  Only filled when the session was created with the
+ * environment variable NERVA_B200_TIMELINE=1.  Returns the number of values. */
+int nerva_b200_session_read_timeline(NervaCudaHfDecodeSequenceSession *session, uint64_t *stamps,
+                                     uint32_t capacity);
+
 /* Isolated projection: y[m][n] = sum_k W[n][k] * x[m][k], bf16 in, fp32
  * accumulate and out.  All pointers are HOST memory; the call copies in, runs
  * `iterations` launches after `warmup` untimed ones, and copies y back.
@@ -682,6 +693,56 @@ int nerva_b200_greedy_argmax(const float *logits, uint32_t count, uint32_t *toke
  * include/nerva_synth.h (multi-threaded; same bits as the header). */
 void nerva_b200_synth_normal_bf16(uint64_t seed, uint64_t tensor_id, uint64_t count, float std,
                                   uint16_t *out);
+
+/* ---- host-side memory bookkeeping (no device call) ----
+ * C++ restatements, used by the session, of the reference's
+ * crates/nerva-memory StaticArena (arena/static_arena.rs:71-112: bump offsets
+ * rounded up to `align`, requests in the hot-path phase refused) and KvPagePool
+ * (kv/pool/{preallocate,allocation,cache}.rs: FIFO free list, reference counts,
+ * prefix-key cache).  phase: 0 initialization, 1 warm-up, 2 hot path. */
+typedef struct NervaB200StaticArena NervaB200StaticArena;
+typedef struct NervaB200KvPagePool NervaB200KvPagePool;
+typedef struct NervaB200KvPageInfo {
+  uint64_t arena_offset;
+  uint64_t page_bytes;
+  uint64_t last_use;
+  uint32_t token_start;
+  uint32_t token_count;
+  uint32_t ref_count;
+  uint32_t prefix_tokens;
+  uint32_t is_free;
+  uint32_t has_prefix;
+} NervaB200KvPageInfo;
+
+NervaB200StaticArena *nerva_b200_static_arena_new(uint64_t capacity_bytes);
+void nerva_b200_static_arena_free(NervaB200StaticArena *arena);
+int nerva_b200_static_arena_reserve(NervaB200StaticArena *arena, uint64_t bytes, uint64_t align,
+                                    uint32_t phase, uint64_t *offset_out);
+uint64_t nerva_b200_static_arena_used(const NervaB200StaticArena *arena);
+uint64_t nerva_b200_static_arena_remaining(const NervaB200StaticArena *arena);
+int nerva_b200_static_arena_restore(NervaB200StaticArena *arena, uint64_t cursor);
+
+NervaB200KvPagePool *nerva_b200_kv_page_pool_new(NervaB200StaticArena *arena, uint32_t num_pages,
+                                                 uint32_t block_size_tokens, uint64_t page_bytes,
+                                                 uint64_t align);
+void nerva_b200_kv_page_pool_free(NervaB200KvPagePool *pool);
+uint32_t nerva_b200_kv_page_pool_len(const NervaB200KvPagePool *pool);
+uint32_t nerva_b200_kv_page_pool_free_pages(const NervaB200KvPagePool *pool);
+/* page index, -1 pool exhausted, -2 token_count larger than a page */
+int64_t nerva_b200_kv_page_pool_allocate(NervaB200KvPagePool *pool, uint32_t token_start,
+                                         uint32_t token_count, uint64_t step);
+int nerva_b200_kv_page_pool_retain(NervaB200KvPagePool *pool, uint32_t page, uint64_t step);
+int nerva_b200_kv_page_pool_release(NervaB200KvPagePool *pool, uint32_t page, uint64_t step);
+int nerva_b200_kv_page_pool_cache(NervaB200KvPagePool *pool, uint32_t page, const uint8_t *hash32,
+                                  uint32_t group_id, uint32_t prefix_tokens);
+int64_t nerva_b200_kv_page_pool_lookup_cached(const NervaB200KvPagePool *pool,
+                                              const uint8_t *hash32, uint32_t group_id);
+int64_t nerva_b200_kv_page_pool_retain_cached(NervaB200KvPagePool *pool, const uint8_t *hash32,
+                                              uint32_t group_id, uint64_t step);
+/* 1 a key was evicted, 0 the page had none, -1 bad index */
+int nerva_b200_kv_page_pool_evict_cached(NervaB200KvPagePool *pool, uint32_t page);
+int nerva_b200_kv_page_pool_page(const NervaB200KvPagePool *pool, uint32_t page,
+                                 NervaB200KvPageInfo *out);
 
 /* Last error text of the calling thread ("" when none). */
 const char *nerva_b200_last_error(void);

@@ -36,6 +36,7 @@ struct AttnItemCtx {
   // tiles (written by earlier steps) are put in flight first, then the item
   // waits for the QKV projection before it touches `qkv`.
   bool wait_dependency;
+  unsigned long long *stamps = nullptr;  // optional timeline stamps (common.cuh: stamp)
 };
 
 template <uint32_t WARPS>
@@ -76,6 +77,55 @@ __device__ __forceinline__ void head_norm_rope(float (&v)[PER], const uint16_t *
       const float left = v[k], right = v[k + HALF];
       v[k] = left * c - right * s;
       v[k + HALF] = right * c + left * s;
+    }
+  }
+}
+
+// The same in two steps, for kernels that know the position before their input
+// arrives: rope_factors() needs only the position; head_norm_rope_pre() then
+// applies norm weights already held in registers and the prepared rotation.
+template <uint32_t PER>
+struct RopeFactors {
+  float c[PER / 2u], s[PER / 2u];
+  bool on;
+};
+template <uint32_t PER>
+__device__ __forceinline__ void rope_factors(RopeFactors<PER> &f, float theta, uint32_t position) {
+  constexpr uint32_t D = PER * 32u;
+  const uint32_t lane = threadIdx.x & 31u;
+  f.on = theta > 0.0f;
+#pragma unroll
+  for (uint32_t k = 0; k < PER / 2u; ++k) {
+    f.c[k] = 1.0f;
+    f.s[k] = 0.0f;
+    if (f.on) {
+      const uint32_t i = lane + 32u * k;
+      const float exponent = static_cast<float>(2u * i) / static_cast<float>(D);
+      const float angle = static_cast<float>(position) / powf(theta, exponent);
+      sincosf(angle, &f.s[k], &f.c[k]);
+    }
+  }
+}
+template <uint32_t PER>
+__device__ __forceinline__ void head_norm_rope_pre(float (&v)[PER], bool has_norm, const float (&w)[PER],
+                                                   float eps, const RopeFactors<PER> &f) {
+  constexpr uint32_t D = PER * 32u;
+  constexpr uint32_t HALF = PER / 2u;
+  if (has_norm) {
+    float ss = 0.0f;
+#pragma unroll
+    for (uint32_t k = 0; k < PER; ++k) ss += v[k] * v[k];
+    ss = warp_sum(ss);
+    const float scale = rsqrtf(ss / static_cast<float>(D) + eps);
+#pragma unroll
+    for (uint32_t k = 0; k < PER; ++k) v[k] *= scale * w[k];
+  }
+  if (f.on) {
+#pragma unroll
+    for (uint32_t k = 0; k < HALF; ++k) {
+      const float left = v[k], right = v[k + HALF];
+      v[k] = left * f.c[k] - right * f.s[k];
+      v[k + HALF] = right * f.c[k] + left * f.s[k];
     }
   }
 }
@@ -138,7 +188,9 @@ __device__ __forceinline__ void attention_item(const AttnItemCtx &c, AttnItemSha
   };
   uint32_t tile = tile_begin + warp;
   if (tile < tile_end) load_tile(tile);
+  stamp(c.stamps, kStampAfterWait);      // attention: cached K/V tile loads issued
   if (c.wait_dependency) pdl_wait();
+  stamp(c.stamps, kStampAfterPrologue);  // attention: the QKV projection has completed
 
   if (warp == 0) {
     float v[PER];

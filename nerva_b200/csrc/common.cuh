@@ -158,6 +158,22 @@ __device__ __forceinline__ void pdl_trigger() {
   asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
 }
 
+// Timeline stamps of one launch (tuning aid, off unless the session asks for it):
+// the first block writes slots 0..3, the last block slots 4..7, of
+//   +0 kernel entry   +1 after pdl_wait   +2 after the prologue   +3 before exit
+// in nanoseconds of %globaltimer.
+constexpr uint32_t kStampEntry = 0, kStampAfterWait = 1, kStampAfterPrologue = 2, kStampExit = 3;
+__device__ __forceinline__ void stamp(unsigned long long *stamps, uint32_t slot) {
+  if (stamps == nullptr || threadIdx.x != 0) return;
+  const uint32_t last = gridDim.x * gridDim.y * gridDim.z - 1u;
+  const uint32_t block = blockIdx.x + gridDim.x * (blockIdx.y + gridDim.y * blockIdx.z);
+  if (block != 0 && block != last) return;
+  unsigned long long now;
+  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(now));
+  if (block == 0) stamps[slot] = now;
+  if (block == last) stamps[4u + slot] = now;
+}
+
 __device__ __forceinline__ void report_error(uint32_t *error_word, uint32_t code) {
   if (error_word != nullptr) atomicMax(error_word, code);
 }

@@ -63,7 +63,10 @@ struct ProjectionParams {
   uint32_t *best_index;  // [blocks]
   uint32_t *error_word;
   uint32_t pdl;          // launch with programmatic dependent launch (see launch_with_pdl)
+  unsigned long long *stamps;  // optional kTimelineSlots timeline stamps (common.cuh: stamp)
 };
+
+constexpr uint32_t kTimelineSlots = 8;
 
 // Number of blocks launch_projection will use (= number of arg-max partials).
 uint32_t projection_blocks(const ProjectionParams &p, uint32_t sm_count);
@@ -132,14 +135,16 @@ struct FusedAttentionParams {
   float eps, rope_theta;
   uint32_t splits;
   float *partial_acc, *partial_m, *partial_l;  // [heads][splits][...]
-  uint32_t *tickets;                           // [heads], zero between launches
+  uint32_t *tickets;                           // [kv_heads], zero between launches
   uint16_t *out_bf16;                          // [heads*d]
   uint32_t *error_word;
   uint32_t pdl;
+  unsigned long long *stamps;  // optional timeline stamps
 };
 bool fused_attention_supported(uint32_t heads, uint32_t kv_heads, uint32_t head_dim);
 uint32_t fused_attention_splits(uint32_t target_context);
 cudaError_t launch_fused_attention(cudaStream_t stream, const FusedAttentionParams &p);
+cudaError_t configure_fused_attention_kernel();
 
 // ---- greedy sampling ----
 // Reduces per-block (value, index) partials, writes the token slot at the

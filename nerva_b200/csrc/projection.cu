@@ -43,6 +43,7 @@ __global__ void __launch_bounds__(kStreamThreads, 1) projection_stream_kernel(Pr
                                                round128(sizeof(ProjectionShared)));
   const uint32_t unit = EPI == kEpilogueSwiglu ? 2u : 1u;
   pdl_trigger();
+  stamp(p.stamps, kStampEntry);
   if (threadIdx.x == 0) sh.job = JobDesc{p.weight, p.rows, p.cols, unit, 0};
   __syncthreads();
 
@@ -58,6 +59,7 @@ __global__ void __launch_bounds__(kStreamThreads, 1) projection_stream_kernel(Pr
 
   // Everything above is independent of the previous kernel; its output is read below.
   pdl_wait();
+  stamp(p.stamps, kStampAfterWait);
   if (p.prologue == kProloguePlain) {
     const uint4 *src = reinterpret_cast<const uint4 *>(p.x_bf16);
     uint4 *dst = reinterpret_cast<uint4 *>(x);
@@ -67,6 +69,7 @@ __global__ void __launch_bounds__(kStreamThreads, 1) projection_stream_kernel(Pr
                      blockIdx.x == 0 ? p.resid_out : nullptr, sh.scratch);
   }
   __syncthreads();
+  stamp(p.stamps, kStampAfterPrologue);
 
   stream_consume(rs, sh.stream, 0, x, row_total, p.error_word);
   __syncthreads();
@@ -120,6 +123,7 @@ __global__ void __launch_bounds__(kStreamThreads, 1) projection_stream_kernel(Pr
     }
   }
   stream_drain(rs);
+  stamp(p.stamps, kStampExit);
 }
 
 // Any-shape path (cols not a multiple of 8, or an unaligned matrix): one warp

@@ -231,7 +231,7 @@ bool plan_state(Session *s, StaticArena &arena, void *base) {
   ok = ok && carve(arena, base, static_cast<uint64_t>(d.hidden), &s->o_out);
   ok = ok && carve(arena, base, static_cast<uint64_t>(d.hidden), &s->down);
   ok = ok && carve(arena, base, static_cast<uint64_t>(d.vocab), &s->logits);
-  const uint64_t split_slots = std::max<uint32_t>(s->max_splits, 8u);  // fused attention uses up to 8
+  const uint64_t split_slots = std::max<uint32_t>(s->max_splits, 16u);  // fused attention uses up to 16
   ok = ok && carve(arena, base, static_cast<uint64_t>(d.heads), &s->attn_tickets);
   s->x_elems = static_cast<uint32_t>(max_x);
   ok = ok && carve(arena, base, static_cast<uint64_t>(d.heads) * split_slots * d.head_dim, &s->partial_acc);
@@ -250,6 +250,8 @@ bool plan_state(Session *s, StaticArena &arena, void *base) {
   ok = ok && carve(arena, base, static_cast<uint64_t>(s->max_context), &s->device_prompt);
   ok = ok && carve(arena, base, uint64_t{4}, &s->device_cursor);
   ok = ok && carve(arena, base, uint64_t{4}, &s->device_error);
+  s->timeline_nodes = 5u * d.layers + 1u;
+  ok = ok && carve(arena, base, static_cast<uint64_t>(s->timeline_nodes) * kTimelineSlots, &s->timeline);
   return ok;
 }
 
@@ -426,6 +428,9 @@ cudaError_t enqueue_step(Session *s, uint32_t splits, uint32_t sample, uint64_t 
   const uint64_t ah = d.attention_hidden(), kvh = d.kv_hidden();
   const uint64_t qkv_rows = ah + 2 * kvh;
   uint64_t n = 0;
+  auto stamps_for = [s](uint32_t node) -> unsigned long long * {
+    return s->timeline_on && node < s->timeline_nodes ? s->timeline + node * kTimelineSlots : nullptr;
+  };
   if (s->engine == 1 && prof == nullptr) {
     if (launches != nullptr) *launches = 1;
     return enqueue_step_kernel(s, splits, sample);
@@ -452,6 +457,7 @@ cudaError_t enqueue_step(Session *s, uint32_t splits, uint32_t sample, uint64_t 
     p.resid_out = s->h_a;
     p.epilogue = kEpilogueStore;
     p.out_f32 = s->qkv;
+    p.stamps = stamps_for(5u * l);
     err = launch_projection(s->stream, p, s->sm_count);
     n += 1;
     profile_mark(s, prof, kBucketQkv);
@@ -501,6 +507,7 @@ cudaError_t enqueue_step(Session *s, uint32_t splits, uint32_t sample, uint64_t 
       fp.out_bf16 = s->attn_bf16;
       fp.error_word = s->device_error;
       fp.pdl = s->use_pdl ? 1u : 0u;
+      fp.stamps = stamps_for(5u * l + 1u);
       err = launch_fused_attention(s->stream, fp);
       n += 1;
       profile_mark(s, prof, kBucketAttention);
@@ -545,6 +552,7 @@ cudaError_t enqueue_step(Session *s, uint32_t splits, uint32_t sample, uint64_t 
     p.x_bf16 = s->attn_bf16;
     p.epilogue = kEpilogueStore;
     p.out_f32 = s->o_out;
+    p.stamps = stamps_for(5u * l + 2u);
     err = launch_projection(s->stream, p, s->sm_count);
     n += 1;
     profile_mark(s, prof, kBucketO);
@@ -567,6 +575,7 @@ cudaError_t enqueue_step(Session *s, uint32_t splits, uint32_t sample, uint64_t 
     p.resid_out = s->h_b;
     p.epilogue = kEpilogueSwiglu;
     p.out_bf16 = s->ff_bf16;
+    p.stamps = stamps_for(5u * l + 3u);
     err = launch_projection(s->stream, p, s->sm_count);
     n += 1;
     profile_mark(s, prof, kBucketGateUp);
@@ -584,6 +593,7 @@ cudaError_t enqueue_step(Session *s, uint32_t splits, uint32_t sample, uint64_t 
     p.x_bf16 = s->ff_bf16;
     p.epilogue = kEpilogueStore;
     p.out_f32 = s->down;
+    p.stamps = stamps_for(5u * l + 4u);
     err = launch_projection(s->stream, p, s->sm_count);
     n += 1;
     profile_mark(s, prof, kBucketDown);
@@ -607,6 +617,7 @@ cudaError_t enqueue_step(Session *s, uint32_t splits, uint32_t sample, uint64_t 
     p.out_f32 = s->logits;
     p.best_value = s->best_value;
     p.best_index = s->best_index;
+    p.stamps = stamps_for(5u * d.layers);
     partials = projection_blocks(p, s->sm_count);
     err = launch_projection(s->stream, p, s->sm_count);
     n += 1;
@@ -1063,6 +1074,10 @@ cudaError_t allocate_state(Session *s, int32_t *stage) {
   if (err == cudaSuccess)
     err = cudaMemsetAsync(s->attn_tickets, 0, s->dims.heads * sizeof(uint32_t), s->stream);
   s->fused_attention = fused_attention_supported(s->dims.heads, s->dims.kv_heads, s->dims.head_dim);
+  const char *timeline_env = getenv("NERVA_B200_TIMELINE");
+  s->timeline_on = timeline_env != nullptr && timeline_env[0] == '1';
+  if (err == cudaSuccess)
+    err = cudaMemsetAsync(s->timeline, 0, static_cast<size_t>(s->timeline_nodes) * kTimelineSlots * 8u, s->stream);
   const char *pdl_env = getenv("NERVA_B200_PDL");
   s->use_pdl = !(pdl_env != nullptr && pdl_env[0] == '0');
   if (err == cudaSuccess) err = cudaStreamSynchronize(s->stream);
@@ -1073,8 +1088,8 @@ cudaError_t allocate_state(Session *s, int32_t *stage) {
 
 extern "C" int nerva_cuda_hf_decode_sequence_session_create(
     const NervaCudaHfDecodeSequenceSessionCreateRequest *request,
-    NervaCudaHfDecodeSequenceSession **session_out,
-    NervaCudaHfDecodeSequenceSessionCreateResult *out) {
+    NervaCudaHfDecodeSequenceSessionCreateResult *out,
+    NervaCudaHfDecodeSequenceSession **session_out) {
   if (out == nullptr) return -1;
   memset(out, 0, sizeof(*out));
   out->status = -1;
@@ -1196,6 +1211,7 @@ extern "C" int nerva_cuda_hf_decode_sequence_session_create(
       static_cast<uint64_t>(prop.memoryClockRate) * 1000ull * (static_cast<uint64_t>(prop.memoryBusWidth) / 8ull);
   err = configure_projection_kernels();
   if (err == cudaSuccess) err = configure_attention_kernels();
+  if (err == cudaSuccess) err = configure_fused_attention_kernel();
   if (err != cudaSuccess) return create_fail(s, out, err, kStageSetDevice);
 
   // shared weights: one allocation
@@ -1250,10 +1266,47 @@ extern "C" int nerva_cuda_hf_decode_sequence_session_create(
   return 0;
 }
 
-extern "C" int nerva_cuda_hf_decode_sequence_session_destroy(Session *session) {
+// session_api_batch_fork_destroy.inc.cu:716-732: `out` (nullable) receives the
+// session's identity one last time.
+extern "C" int nerva_cuda_hf_decode_sequence_session_destroy(
+    Session *session, NervaCudaHfDecodeSequenceSessionCreateResult *out) {
+  if (out != nullptr) {
+    memset(out, 0, sizeof(*out));
+    out->status = -1;
+  }
   if (session == nullptr) return -1;
+  if (out != nullptr) {
+    out->device_count = 1;
+    out->dtype = session->dims.dtype;
+    out->hidden = session->dims.hidden;
+    out->heads = session->dims.heads;
+    out->kv_heads = session->dims.kv_heads;
+    out->head_dim = session->dims.head_dim;
+    out->intermediate = session->dims.intermediate;
+    out->vocab_size = session->dims.vocab;
+    out->layer_count = session->dims.layers;
+    out->max_context_tokens = session->max_context;
+    out->resident_weight_bytes = session->resident_weight_bytes;
+    out->resident_kv_bytes = resident_kv_bytes(session);
+    out->device_arena_bytes = device_footprint(session);
+    out->pinned_host_bytes = session->slots_bytes;
+    out->status = 0;
+  }
   destroy_session(session);
   return 0;
+}
+
+extern "C" int nerva_b200_session_read_timeline(Session *s, uint64_t *stamps, uint32_t capacity) {
+  if (s == nullptr || stamps == nullptr || !s->timeline_on) return -1;
+  const uint32_t count = s->timeline_nodes * kTimelineSlots;
+  if (capacity < count) return -1;
+  cudaError_t err = cudaStreamSynchronize(s->stream);
+  if (err == cudaSuccess) err = cudaMemcpy(stamps, s->timeline, static_cast<size_t>(count) * 8u, cudaMemcpyDeviceToHost);
+  if (err != cudaSuccess) {
+    set_last_error(cudaGetErrorString(err));
+    return -1;
+  }
+  return static_cast<int>(count);
 }
 
 extern "C" int nerva_b200_session_set_engine(Session *s, uint32_t engine) {
@@ -1503,8 +1556,8 @@ extern "C" int nerva_cuda_hf_decode_sequence_session_run(
 // the device weights are shared (session_api_batch_fork_destroy.inc.cu:311+).
 extern "C" int nerva_cuda_hf_decode_sequence_session_fork_shared_weights(
     const NervaCudaHfDecodeSequenceSessionForkSharedWeightsRequest *request,
-    NervaCudaHfDecodeSequenceSession **session_out,
-    NervaCudaHfDecodeSequenceSessionCreateResult *out) {
+    NervaCudaHfDecodeSequenceSessionCreateResult *out,
+    NervaCudaHfDecodeSequenceSession **session_out) {
   if (out == nullptr) return -1;
   memset(out, 0, sizeof(*out));
   out->status = -1;
@@ -1630,7 +1683,7 @@ extern "C" int nerva_cuda_hf_decode_sequence_u16(const NervaCudaHfDecodeSequence
   create.planned_weight_descriptor_hash = request->planned_weight_descriptor_hash;
   Session *s = nullptr;
   NervaCudaHfDecodeSequenceSessionCreateResult created{};
-  if (nerva_cuda_hf_decode_sequence_session_create(&create, &s, &created) != 0) {
+  if (nerva_cuda_hf_decode_sequence_session_create(&create, &created, &s) != 0) {
     out->cuda_error = created.cuda_error;
     out->device_count = created.device_count;
     return -1;

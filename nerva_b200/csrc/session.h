@@ -149,6 +149,11 @@ struct NervaCudaHfDecodeSequenceSession {
   uint32_t *barrier_counter = nullptr;
   unsigned long long *phase_cycles = nullptr;  // per-phase SM cycles of block 0 (tuning aid)
   bool phase_profile = false;                  // NERVA_B200_PHASE_PROFILE=1 at create
+  // Tuning aid (NERVA_B200_TIMELINE=1 at create): per launch of a step, %globaltimer
+  // stamps of the first and the last block (see kTimelineSlots in kernels.cuh).
+  unsigned long long *timeline = nullptr;
+  uint32_t timeline_nodes = 0;
+  bool timeline_on = false;
   uint32_t x_elems = 0;
   uint32_t row_elems = 0;  // rows of the largest per-block row range of any projection
   bool step_kernel_ok = false;

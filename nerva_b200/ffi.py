@@ -93,12 +93,12 @@ def lib() -> C.CDLL:
     vp = C.c_void_p
     sigs = {
         "nerva_cuda_hf_decode_sequence_plan_layout": [P(LayoutPlanRequest), P(LayoutPlanResult)],
-        "nerva_cuda_hf_decode_sequence_session_create": [P(CreateRequest), P(vp), P(CreateResult)],
+        "nerva_cuda_hf_decode_sequence_session_create": [P(CreateRequest), P(CreateResult), P(vp)],
         "nerva_cuda_hf_decode_sequence_session_run": [P(RunRequest), P(SequenceResult)],
         "nerva_cuda_hf_decode_sequence_session_start": [P(StartRequest), P(SequenceResult)],
         "nerva_cuda_hf_decode_sequence_session_advance": [P(AdvanceRequest), P(SequenceResult)],
-        "nerva_cuda_hf_decode_sequence_session_fork_shared_weights": [P(ForkRequest), P(vp), P(CreateResult)],
-        "nerva_cuda_hf_decode_sequence_session_destroy": [vp],
+        "nerva_cuda_hf_decode_sequence_session_fork_shared_weights": [P(ForkRequest), P(CreateResult), P(vp)],
+        "nerva_cuda_hf_decode_sequence_session_destroy": [vp, P(CreateResult)],
         "nerva_cuda_hf_decode_sequence_u16": [P(SequenceRequest), P(SequenceResult)],
         "nerva_cuda_projection_bench": [P(ProjectionBenchRequest), P(ProjectionBenchResult)],
         "nerva_b200_session_set_engine": [vp, C.c_uint32],
@@ -108,6 +108,7 @@ def lib() -> C.CDLL:
         "nerva_b200_session_read_kv_row": [vp, C.c_uint32, C.c_uint32, C.c_uint32, vp, C.c_uint32],
         "nerva_b200_session_profile_steps": [vp, C.c_uint32, vp, vp, C.c_uint32],
         "nerva_b200_session_read_phase_cycles": [vp, vp, C.c_uint32],
+        "nerva_b200_session_read_timeline": [vp, vp, C.c_uint32],
         "nerva_b200_projection": [vp, vp, vp, C.c_uint32, C.c_uint32, C.c_uint32, C.c_uint32, C.c_uint32,
                                   P(C.c_uint64)],
         "nerva_b200_gqa_decode_attention": [vp, vp, vp, vp, vp, C.c_uint32, C.c_uint32, C.c_uint32, C.c_uint32,
@@ -121,6 +122,31 @@ def lib() -> C.CDLL:
         fn = getattr(L, name)
         fn.argtypes = argtypes
         fn.restype = None if name == "nerva_b200_synth_normal_bf16" else C.c_int
+    u32, u64, i64 = C.c_uint32, C.c_uint64, C.c_int64
+    host = {  # host-side memory bookkeeping: name -> (restype, argtypes)
+        "nerva_b200_static_arena_new": (vp, [u64]),
+        "nerva_b200_static_arena_free": (None, [vp]),
+        "nerva_b200_static_arena_reserve": (C.c_int, [vp, u64, u64, u32, P(u64)]),
+        "nerva_b200_static_arena_used": (u64, [vp]),
+        "nerva_b200_static_arena_remaining": (u64, [vp]),
+        "nerva_b200_static_arena_restore": (C.c_int, [vp, u64]),
+        "nerva_b200_kv_page_pool_new": (vp, [vp, u32, u32, u64, u64]),
+        "nerva_b200_kv_page_pool_free": (None, [vp]),
+        "nerva_b200_kv_page_pool_len": (u32, [vp]),
+        "nerva_b200_kv_page_pool_free_pages": (u32, [vp]),
+        "nerva_b200_kv_page_pool_allocate": (i64, [vp, u32, u32, u64]),
+        "nerva_b200_kv_page_pool_retain": (C.c_int, [vp, u32, u64]),
+        "nerva_b200_kv_page_pool_release": (C.c_int, [vp, u32, u64]),
+        "nerva_b200_kv_page_pool_cache": (C.c_int, [vp, u32, C.c_char_p, u32, u32]),
+        "nerva_b200_kv_page_pool_lookup_cached": (i64, [vp, C.c_char_p, u32]),
+        "nerva_b200_kv_page_pool_retain_cached": (i64, [vp, C.c_char_p, u32, u64]),
+        "nerva_b200_kv_page_pool_evict_cached": (C.c_int, [vp, u32]),
+        "nerva_b200_kv_page_pool_page": (C.c_int, [vp, u32, P(structs["NervaB200KvPageInfo"])]),
+    }
+    for name, (restype, argtypes) in host.items():
+        fn = getattr(L, name)
+        fn.restype = restype
+        fn.argtypes = argtypes
     L.nerva_b200_last_error.restype = C.c_char_p
     L.nerva_b200_last_error.argtypes = []
     _lib = L

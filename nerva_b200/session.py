@@ -145,8 +145,8 @@ class CudaHfDecodeSequenceSession:
         self.request = req
         self._handle = C.c_void_p()
         self.create_result = ffi.CreateResult()
-        rc = ffi.lib().nerva_cuda_hf_decode_sequence_session_create(C.byref(req), C.byref(self._handle),
-                                                                    C.byref(self.create_result))
+        rc = ffi.lib().nerva_cuda_hf_decode_sequence_session_create(C.byref(req), C.byref(self.create_result),
+                                                                    C.byref(self._handle))
         r = self.create_result
         self.status = _status(rc, r.status, r.cuda_error, r.device_count)
         self.error = ffi.last_error()
@@ -174,8 +174,8 @@ class CudaHfDecodeSequenceSession:
     def fork_shared_weights(self) -> "CudaHfDecodeSequenceSession":
         req = ffi.ForkRequest(parent=self._handle, detailed_profile=0)
         handle, res = C.c_void_p(), ffi.CreateResult()
-        rc = ffi.lib().nerva_cuda_hf_decode_sequence_session_fork_shared_weights(C.byref(req), C.byref(handle),
-                                                                                 C.byref(res))
+        rc = ffi.lib().nerva_cuda_hf_decode_sequence_session_fork_shared_weights(C.byref(req), C.byref(res),
+                                                                                 C.byref(handle))
         return self._from_handle(self, handle, res, _status(rc, res.status, res.cuda_error, res.device_count))
 
     def run(self, prompt_tokens, steps: int, eos_token=None) -> Summary:
@@ -237,9 +237,19 @@ class CudaHfDecodeSequenceSession:
             raise RuntimeError("phase cycles unavailable")
         return {name: int(c) for name, c in zip(self.PHASES, cycles)}
 
+    def read_timeline(self) -> np.ndarray:
+        """%globaltimer stamps of the last step, shape [5 * layers + 1, 8] (launch order QKV, attention,
+        O, gate/up, down per layer, then lm_head; columns: entry / after wait / after prologue / exit of
+        the first block, then of the last block).  Needs NERVA_B200_TIMELINE=1 at create."""
+        nodes = 5 * self.config.layers + 1
+        stamps = np.zeros(nodes * 8, dtype=np.uint64)
+        if ffi.lib().nerva_b200_session_read_timeline(self._handle, _ptr(stamps), stamps.size) < 0:
+            raise RuntimeError("timeline unavailable")
+        return stamps.reshape(nodes, 8)
+
     def destroy(self) -> None:
         if self._handle:
-            ffi.lib().nerva_cuda_hf_decode_sequence_session_destroy(self._handle)
+            ffi.lib().nerva_cuda_hf_decode_sequence_session_destroy(self._handle, None)
             self._handle = C.c_void_p()
 
     def __del__(self):

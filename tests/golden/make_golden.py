@@ -54,6 +54,8 @@ def tiny_golden() -> dict:
 def layout_probe_source(header: str) -> str:
     lines = ["#include <stddef.h>", "#include <stdio.h>", f'#include "{header}"', "int main(void) {"]
     for name, cls in ffi.structs.items():
+        if not name.startswith("NervaCuda"):
+            continue  # additive structs of this library have no counterpart in the reference header
         lines.append(f'  printf("{name} %zu\\n", sizeof({name}));')
         for fname, _ in cls._fields_:
             lines.append(f'  printf("{name}.{fname} %zu\\n", offsetof({name}, {fname}));')
@@ -71,11 +73,40 @@ def measure_layout(header: str) -> str:
         return subprocess.run([exe], check=True, capture_output=True, text=True).stdout
 
 
+def prototypes(header_text: str, prefix: str = "nerva_cuda_") -> dict:
+    """name -> 'return_type(param_type, ...)' with parameter names and comments removed."""
+    import re
+    text = re.sub(r"/\*.*?\*/", "", header_text, flags=re.S)
+    text = re.sub(r"//[^\n]*", "", text)
+    found = {}
+    for m in re.finditer(r"([A-Za-z_][\w \*]*?)\b(" + prefix + r"\w+)\s*\(([^)]*)\)\s*;", text):
+        ret, name, params = m.group(1), m.group(2), m.group(3)
+        types = []
+        for p in params.split(","):
+            p = " ".join(p.split())
+            p = re.sub(r"\b\w+$", "", p).strip() if p != "void" else p   # drop the parameter name
+            types.append(re.sub(r"\s*\*\s*", "*", p))
+        found[name] = f"{' '.join(ret.split())}({', '.join(types)})"
+    return found
+
+
+def reference_prototypes() -> str:
+    """Prototypes, as the reference header declares them, of every nerva_cuda_* function that
+    this repository's header declares."""
+    with open(REFERENCE_HEADER) as f:
+        ref = prototypes(f.read())
+    with open(ffi.HEADER) as f:
+        ours = prototypes(f.read())
+    return "".join(f"{name} {ref[name]}\n" for name in sorted(ours))
+
+
 if __name__ == "__main__":
     with open(os.path.join(HERE, "tiny_qwen3.json"), "w") as f:
         json.dump(tiny_golden(), f, indent=1)
     if os.path.exists(REFERENCE_HEADER):
         with open(os.path.join(HERE, "abi_layout.txt"), "w") as f:
             f.write(measure_layout(REFERENCE_HEADER))
+        with open(os.path.join(HERE, "abi_prototypes.txt"), "w") as f:
+            f.write(reference_prototypes())
     else:
         print("reference header not present: abi_layout.txt left untouched")
