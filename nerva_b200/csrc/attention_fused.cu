@@ -86,11 +86,7 @@ __global__ void fused_decode_attention_kernel(FusedAttentionParams p) {
   // the 16-byte pieces of the K row, the other half those of the V row, so every
   // request covers complete 128-byte lines.  The chunk's four page-table entries
   // are read once per warp, before the loop, and handed out by shuffle.
-  auto issue = [&](uint32_t chunk, uint32_t stage) {
-    uint8_t *k_stage = smem + stage * Layout::kStageBytes;
-    uint8_t *v_stage = k_stage + kChunkTokens * Layout::kRowK;
-    constexpr uint32_t kLanesPerToken = 2u * Layout::kPieces;          // 32 (D = 128) or 16 (D = 64)
-    constexpr uint32_t kTokensPerIter = 32u / kLanesPerToken;
+  auto chunk_pages = [&](uint32_t chunk) -> uint32_t {
     constexpr uint32_t kPagesPerChunk = kChunkTokens / NERVA_KV_CACHE_BLOCK_TOKENS;
     const uint32_t first = chunk * kChunkTokens;
     uint32_t my_page = 0;
@@ -101,6 +97,14 @@ __global__ void fused_decode_attention_kernel(FusedAttentionParams p) {
         my_page = 0;
       }
     }
+    return my_page;
+  };
+  auto issue = [&](uint32_t chunk, uint32_t stage, uint32_t my_page) {
+    uint8_t *k_stage = smem + stage * Layout::kStageBytes;
+    uint8_t *v_stage = k_stage + kChunkTokens * Layout::kRowK;
+    constexpr uint32_t kLanesPerToken = 2u * Layout::kPieces;          // 32 (D = 128) or 16 (D = 64)
+    constexpr uint32_t kTokensPerIter = 32u / kLanesPerToken;
+    const uint32_t first = chunk * kChunkTokens;
     const uint32_t sub = lane / kLanesPerToken, r = lane % kLanesPerToken;
     const bool is_v = r >= Layout::kPieces;
     const uint32_t piece = is_v ? r - Layout::kPieces : r;
@@ -119,18 +123,21 @@ __global__ void fused_decode_attention_kernel(FusedAttentionParams p) {
     }
     cp_async_commit();
   };
-  if (chunk_begin < chunk_end) issue(chunk_begin, 0);
-  if (chunk_begin + 1u < chunk_end) issue(chunk_begin + 1u, 1);
-  // Everything that depends only on the position is computed before the wait.
+  // Everything that depends only on the position happens before the wait; the
+  // page-table and norm-weight loads are in flight while the rotation is computed.
+  const uint32_t pages0 = chunk_begin < chunk_end ? chunk_pages(chunk_begin) : 0u;
+  const uint32_t pages1 = chunk_begin + 1u < chunk_end ? chunk_pages(chunk_begin + 1u) : 0u;
   const uint32_t h = kvh * group + warp;  // query head of this warp (warp < group)
   const float qscale = kAttnLog2e * rsqrtf(static_cast<float>(D));
-  RopeFactors<PER> rope;
-  rope_factors<PER>(rope, p.rope_theta, position);
   const uint16_t *norm_ptr = warp < group ? p.q_norm : p.k_norm;
   float norm_w[PER];
 #pragma unroll
   for (uint32_t k = 0; k < PER; ++k)
     norm_w[k] = norm_ptr != nullptr ? bf16_bits_to_f32(norm_ptr[lane + 32u * k]) : 1.0f;
+  if (chunk_begin < chunk_end) issue(chunk_begin, 0, pages0);
+  if (chunk_begin + 1u < chunk_end) issue(chunk_begin + 1u, 1, pages1);
+  RopeFactors<PER> rope;
+  rope_factors<PER>(rope, p.rope_theta, position);
   stamp(p.stamps, kStampAfterWait);      // cached K/V copies issued
   pdl_wait();
   stamp(p.stamps, kStampAfterPrologue);  // the QKV projection has completed
@@ -243,7 +250,7 @@ __global__ void fused_decode_attention_kernel(FusedAttentionParams p) {
       }
     }
     __syncthreads();  // the stage is free again
-    if (chunk + kStages < chunk_end) issue(chunk + kStages, stage);
+    if (chunk + kStages < chunk_end) issue(chunk + kStages, stage, chunk_pages(chunk + kStages));
   }
   if (chunk_begin >= chunk_end) __syncthreads();  // q, k_new, v_new visible when no chunk ran
 
