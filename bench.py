@@ -119,7 +119,9 @@ def config_block(cfg, gpus: int, extra: dict | None = None) -> dict:
         "weights": "random-init bf16 ~N(0,0.02) seed 0, unit norm weights, untied lm_head (synthetic)",
         "bytes_per_token": cfg.projection_bytes_per_token(),
         "l2": "each step streams the full weight set (far larger than the 126 MB L2); no flush needed",
-        "parallelism": "single GPU" if gpus == 1 else f"{gpus} independent replicas (no tensor parallel engine yet)",
+        "parallelism": "single GPU" if gpus == 1 else
+                       f"tp{gpus}: QKV, gate/up, lm_head split by rows, O and down by columns; partial sums "
+                       f"exchanged inside the projection kernels over NVLink peer memory",
     }
     if extra:
         block.update(extra)
@@ -175,7 +177,12 @@ def run_ours(args, cfg, rank: int, world: int) -> dict:
     from nerva_b200.session import CudaHfDecodeSequenceLoop, CudaHfDecodeSequenceSession, SmokeStatus
     build.build()
     t0 = time.perf_counter()
-    ck = synth.dense_checkpoint(cfg, fill=ops.synth_normal_bf16)
+    if world > 1:
+        # tensor parallel: this rank generates and holds only its slices of the model
+        ck = synth.dense_checkpoint_shard(cfg, rank, world, block_fill=ops.synth_normal_bf16_block,
+                                          fill=ops.synth_normal_bf16)
+    else:
+        ck = synth.dense_checkpoint(cfg, fill=ops.synth_normal_bf16)
     gen_s = time.perf_counter() - t0
     prompt = synth.prompt_ids(cfg)
     profile_steps = 4
@@ -184,6 +191,9 @@ def run_ours(args, cfg, rank: int, world: int) -> dict:
     session = CudaHfDecodeSequenceSession(ck, max_context, engine=args.engine)
     if session.status != SmokeStatus.OK:
         raise RuntimeError(f"session create failed: {session.status} {session.error}")
+    if world > 1:
+        from nerva_b200 import tp
+        tp.connect(session)
     create_s = time.perf_counter() - t0
     t0 = time.perf_counter()
     start, loop = CudaHfDecodeSequenceLoop.start(session, prompt)
@@ -220,7 +230,8 @@ def run_ours(args, cfg, rank: int, world: int) -> dict:
     e2e_s = _max_over_ranks(e2e_s, world)
     proj_ns = sum(prof[k]["ns"] for k in ("qkv", "o", "gate_up", "down", "lm_head")) / profile_steps
     proj_launches = sum(prof[k]["launches_per_step"] for k in ("qkv", "o", "gate_up", "down", "lm_head"))
-    bytes_per_token = cfg.projection_bytes_per_token() + 2 * cfg.hidden * (3 * cfg.layers + 1)  # + bf16 vectors
+    # per GPU: this rank's weight slices + bf16 vectors
+    bytes_per_token = ck.config.projection_bytes_per_token() + 2 * cfg.hidden * (3 * cfg.layers + 1)
     peaks = measured_peaks()
     achieved = bytes_per_token / (proj_ns * 1e-9) / 1e9
     kernel_name = "projection_stream_kernel (QKV, O, gate-up, down, lm_head)"
@@ -235,15 +246,15 @@ def run_ours(args, cfg, rank: int, world: int) -> dict:
         kernel_name = "decode_step_kernel (whole step: projections + attention + sampling)"
         kernel_us = 1e6 * device_s / args.steps
         achieved = bytes_per_token / (device_s / args.steps) / 1e9
-    value = world * args.steps / device_s
+    value = args.steps / device_s  # all ranks decode the same sequence together
     result = {
         "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
         "warmup": max(args.warmup, 3), "ms_per_step": 1000.0 * device_s / args.steps, "higher_is_better": True,
-        "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+        "scaling": "weak" if world == 1 else "strong", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
         "config": config_block(cfg, world, {"timed_context": f"{cfg.prompt_tokens + 1 + max(args.warmup, 3)}.."
                                                               f"{cfg.prompt_tokens + 1 + max(args.warmup, 3) + args.steps}"}),
         "clocks": clock_info,
-        "e2e": {"value": world * e2e_tokens / e2e_s, "unit": UNIT, "h2d_bytes_per_step": 0,
+        "e2e": {"value": e2e_tokens / e2e_s, "unit": UNIT, "h2d_bytes_per_step": 0,
                 "d2h_bytes_per_step": 44,
                 "note": "session_advance(steps=1) per token with host buffers; the ABI keeps the previous token on "
                         "the device, so a step has no host input; the prompt (4 B/token) is copied once in "
@@ -312,9 +323,11 @@ def main() -> None:
             print(json.dumps(run_reference(args, cfg)), flush=True)
         return
     if world > 1:
-        # one process per GPU: this rank sees only its own device
-        os.environ["NERVA_GPU_INDEX"] = os.environ.get("CUDA_VISIBLE_DEVICES", ",".join(map(str, range(world)))).split(",")[local]
-        os.environ["CUDA_VISIBLE_DEVICES"] = os.environ["NERVA_GPU_INDEX"]
+        # one process per GPU; every GPU stays visible (the ranks map each other's exchange buffers)
+        visible = os.environ.get("CUDA_VISIBLE_DEVICES", "")
+        os.environ["NERVA_GPU_INDEX"] = visible.split(",")[local] if visible else str(local)
+        from nerva_b200 import tp
+        tp.select_device(local)
         import torch.distributed as dist
         dist.init_process_group("gloo")
     result = run_ours(args, cfg, rank, world)

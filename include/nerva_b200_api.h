@@ -642,6 +642,42 @@ int nerva_b200_session_profile_steps(NervaCudaHfDecodeSequenceSession *session, 
 int nerva_b200_session_read_phase_cycles(NervaCudaHfDecodeSequenceSession *session,
                                          uint64_t *cycles, uint32_t capacity);
 
+/* ---- tensor parallel over the GPUs of one node (no counterpart in the reference, whose
+ * multi-GPU plan moves activations between layer islands only) ----
+ * One process per GPU.  Every rank creates a session over ITS SHARD of the model with the
+ * CUDA device it owns current: the request carries the full hidden size, the rank's share
+ * of the query heads, KV heads, intermediate size (rows of gate/up, columns of down) and
+ * lm_head rows, the matching slices of the weights, and the WHOLE embedding table
+ * (`full_vocab` rows).  QKV, gate/up and lm_head are split by output rows; O and down by
+ * input columns, and their partial sums travel between the GPUs inside the projection
+ * kernels: the epilogue stores each rank's partial rows into every rank's exchange buffer
+ * with plain peer stores, the prologue of the next projection waits (bounded, about a
+ * second, then the step fails) for all partials and adds them in rank order, so every rank
+ * holds the same residual stream bit for bit.  The arg-max candidates of the vocabulary
+ * shards are exchanged the same way by the sampler.  No collective library is involved on
+ * the data path.
+ *
+ * Set-up: create_sharded on every rank -> comm_handle -> exchange the 64-byte handles by
+ * any host channel -> attach_peers.  Afterwards start/advance/run are called on all ranks
+ * in lock-step with identical arguments.  Not available: planned weight descriptors,
+ * forks, the whole-step engine. */
+typedef struct NervaB200ShardInfo {
+  uint32_t rank;
+  uint32_t world;        /* 2, 4 or 8 (any value in 2..8 that divides the head counts) */
+  uint32_t full_vocab;   /* rows of the embedding table */
+  uint32_t vocab_offset; /* first lm_head row of this rank */
+} NervaB200ShardInfo;
+int nerva_b200_session_create_sharded(const NervaCudaHfDecodeSequenceSessionCreateRequest *request,
+                                      const NervaB200ShardInfo *shard,
+                                      NervaCudaHfDecodeSequenceSessionCreateResult *out,
+                                      NervaCudaHfDecodeSequenceSession **session);
+/* Writes the 64-byte inter-process handle of this rank's exchange buffer; returns 64. */
+int nerva_b200_session_comm_handle(NervaCudaHfDecodeSequenceSession *session, uint8_t *handle,
+                                   uint32_t capacity);
+/* handles: world x 64 bytes in rank order (the rank's own entry is ignored). */
+int nerva_b200_session_attach_peers(NervaCudaHfDecodeSequenceSession *session,
+                                    const uint8_t *handles, uint32_t world);
+
 /* Tuning aid of the per-operator engine: nanosecond stamps (%globaltimer) of the
  * last step, 8 per launch, launches ordered [layer][QKV, attention, O, gate/up,
  * down] then lm_head.  Slots 0..3: first block at kernel entry, after the wait
@@ -743,6 +779,12 @@ int64_t nerva_b200_kv_page_pool_retain_cached(NervaB200KvPagePool *pool, const u
 int nerva_b200_kv_page_pool_evict_cached(NervaB200KvPagePool *pool, uint32_t page);
 int nerva_b200_kv_page_pool_page(const NervaB200KvPagePool *pool, uint32_t page,
                                  NervaB200KvPageInfo *out);
+
+/* The block [row_begin, row_begin+rows) x [col_begin, col_begin+cols) of the same generator's
+ * row-major tensor with full_cols columns (what a tensor-parallel rank holds), rows*cols values. */
+void nerva_b200_synth_normal_bf16_block(uint64_t seed, uint64_t tensor_id, uint64_t full_cols,
+                                        uint64_t row_begin, uint64_t rows, uint64_t col_begin,
+                                        uint64_t cols, float std, uint16_t *out);
 
 /* Last error text of the calling thread ("" when none). */
 const char *nerva_b200_last_error(void);

@@ -19,6 +19,7 @@ enum DeviceError : uint32_t {
   kErrPageOutOfRange = 3,
   kErrTokenOutOfRange = 4,
   kErrCursorOutOfRange = 5,
+  kErrPeerWaitTimeout = 6,
 };
 
 // ---- bf16 ----
@@ -156,6 +157,26 @@ __device__ __forceinline__ void tma_load_1d_hint(void *smem_dst, const void *gme
 __device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
 __device__ __forceinline__ void pdl_trigger() {
   asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+}
+
+// ---- counters written by other GPUs (tensor-parallel exchange) ----
+__device__ __forceinline__ unsigned long long ld_acquire_sys(const unsigned long long *p) {
+  unsigned long long v;
+  asm volatile("ld.acquire.sys.global.u64 %0, [%1];" : "=l"(v) : "l"(p) : "memory");
+  return v;
+}
+// Bounded wait until *counter >= expected (a few seconds); false on timeout.
+__device__ __forceinline__ bool wait_counter_bounded(const unsigned long long *counter,
+                                                     unsigned long long expected) {
+  if (ld_acquire_sys(counter) >= expected) return true;
+  const long long start = clock64();
+  for (;;) {
+#pragma unroll 1
+    for (uint32_t spin = 0; spin < 32; ++spin) {
+      if (ld_acquire_sys(counter) >= expected) return true;
+    }
+    if (clock64() - start > 4 * kWaitCycleLimit) return false;  // another process: allow host jitter
+  }
 }
 
 // Timeline stamps of one launch (tuning aid, off unless the session asks for it):

@@ -114,9 +114,16 @@ __device__ __forceinline__ bool candidate_better(float v, uint32_t i, float best
 }
 
 // hf_decode_sequence/sampler.cu:394-407: slot fields and cursor advance.
+//
+// Tensor parallel (tp.world > 1): every rank holds the arg-max of its vocabulary
+// shard.  Thread 0 stores (value, global index) into slot `rank` of every rank's
+// candidate array, bumps the arrival counters, waits (bounded) for the other
+// ranks' candidates of this step and applies the same tie rule, so all ranks
+// write the same token.  Quiet steps exchange an empty candidate to keep the
+// counters equal to the number of completed steps.
 __global__ void sample_greedy_kernel(StepState st, const float *best_value,
                                      const uint32_t *best_index, uint32_t partials,
-                                     uint32_t sample) {
+                                     uint32_t sample, TpSample tp) {
   __shared__ float sv[32];
   __shared__ uint32_t si[32];
   pdl_wait();  // the arg-max partials come from the lm_head projection
@@ -156,6 +163,32 @@ __global__ void sample_greedy_kernel(StepState st, const float *best_value,
           bi = si[w];
         }
       }
+      if (bi != kNoIndex) bi += tp.vocab_offset;
+    }
+    if (tp.world > 1) {
+      const unsigned long long mine =
+          (static_cast<unsigned long long>(__float_as_uint(bv)) << 32) | (sample != 0 ? bi : kNoIndex);
+      for (uint32_t q = 0; q < tp.world; ++q) tp.recv[q][tp.rank] = mine;
+      __threadfence_system();
+      for (uint32_t q = 0; q < tp.world; ++q) atomicAdd_system(tp.arrivals[q] + tp.rank, 1ull);
+      const unsigned long long expected = *tp.epoch + 1ull;
+      bv = -INFINITY;
+      bi = kNoIndex;
+      for (uint32_t q = 0; q < tp.world; ++q) {
+        if (!wait_counter_bounded(tp.arrivals[tp.rank] + q, expected)) {
+          report_error(st.error_word, kErrPeerWaitTimeout);
+          continue;
+        }
+        const unsigned long long cand = ld_acquire_sys(tp.recv[tp.rank] + q);
+        const float cv = __uint_as_float(static_cast<uint32_t>(cand >> 32));
+        const uint32_t ci = static_cast<uint32_t>(cand & 0xffffffffull);
+        if (ci != kNoIndex && candidate_better(cv, ci, bv, bi)) {
+          bv = cv;
+          bi = ci;
+        }
+      }
+    }
+    if (sample != 0) {
       NervaCudaSyntheticTokenSlot *slot = st.slots + position;
       slot->request_id = kRequestId;
       slot->sequence_id = kSequenceId;
@@ -166,6 +199,7 @@ __global__ void sample_greedy_kernel(StepState st, const float *best_value,
       slot->host_copied = 0;
     }
     *st.cursor = position + 1;
+    if (tp.epoch != nullptr) *tp.epoch += 1ull;
   }
 }
 
@@ -267,9 +301,11 @@ cudaError_t launch_qkv_prepare(cudaStream_t stream, const StepState &st,
 
 cudaError_t launch_sample_greedy(cudaStream_t stream, const StepState &st, const float *best_value,
                                  const uint32_t *best_index, uint32_t partials, uint32_t sample,
-                                 bool pdl) {
+                                 bool pdl, const TpSample *tp) {
+  TpSample exchange{};
+  if (tp != nullptr) exchange = *tp;
   return launch_with_pdl(sample_greedy_kernel, dim3(1), dim3(256), 0, stream, pdl, st, best_value,
-                         best_index, partials, sample);
+                         best_index, partials, sample, exchange);
 }
 
 cudaError_t launch_argmax(cudaStream_t stream, const float *logits, uint32_t count,

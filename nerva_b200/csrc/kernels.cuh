@@ -44,6 +44,28 @@ enum ProjectionEpilogue : uint32_t {
   kEpilogueArgmax = 2,    // out_f32[row] = y and per-block (best value, lowest index)
 };
 
+// ---- tensor-parallel exchange of a row-parallel projection (O, down) ----
+// Every rank holds a receive buffer [world][rows] f32 and arrival counters
+// [world] per phase.  The writer's epilogue stores its rows of the partial
+// result into slot `rank` of EVERY rank's buffer (plain peer stores over
+// NVLink), fences, and adds 1 per block to slot `rank` of every rank's counters.
+// The next kernel's prologue waits (bounded) until each counter has reached the
+// value this step implies, then adds the partials in rank order.  Counters only
+// grow: expected = *epoch * per_epoch + offset, where *epoch counts the steps
+// this session has completed (the same on every rank).
+constexpr uint32_t kMaxTpWorld = 8;
+struct TpPush {
+  uint32_t world, rank;                       // world <= 1: off
+  float *recv[kMaxTpWorld];                   // rank q's receive buffer of this phase
+  unsigned long long *arrivals[kMaxTpWorld];  // rank q's arrival counters of this phase
+};
+struct TpGather {
+  uint32_t world;                             // world <= 1: off
+  const unsigned long long *arrivals;         // local counters of the phase [world]
+  const unsigned long long *epoch;
+  unsigned long long per_epoch, offset;
+};
+
 struct ProjectionParams {
   const uint16_t *weight;  // [rows][cols] bf16 row-major
   uint32_t rows, cols;
@@ -64,6 +86,8 @@ struct ProjectionParams {
   uint32_t *error_word;
   uint32_t pdl;          // launch with programmatic dependent launch (see launch_with_pdl)
   unsigned long long *stamps;  // optional kTimelineSlots timeline stamps (common.cuh: stamp)
+  TpGather gather;  // kPrologueAddNorm: add_b is [world][cols], complete once the counters say so
+  TpPush push;      // kEpilogueStore: results go to every rank's receive buffer instead of out_f32
 };
 
 constexpr uint32_t kTimelineSlots = 8;
@@ -149,9 +173,18 @@ cudaError_t configure_fused_attention_kernel();
 // ---- greedy sampling ----
 // Reduces per-block (value, index) partials, writes the token slot at the
 // cursor and advances the cursor.  sample == 0: only advances the cursor.
+// tp (nullable): the exchange of per-shard arg-max candidates between tensor-parallel ranks;
+// tp->epoch (nullable) is incremented at the end of every step.
+struct TpSample {
+  uint32_t world, rank;
+  uint32_t vocab_offset;                      // first vocabulary row of this rank's lm_head shard
+  unsigned long long *epoch;
+  unsigned long long *recv[kMaxTpWorld];      // rank q's candidates [world]: value bits << 32 | index
+  unsigned long long *arrivals[kMaxTpWorld];  // rank q's arrival counters [world]
+};
 cudaError_t launch_sample_greedy(cudaStream_t stream, const StepState &st, const float *best_value,
                                  const uint32_t *best_index, uint32_t partials, uint32_t sample,
-                                 bool pdl = false);
+                                 bool pdl = false, const TpSample *tp = nullptr);
 // Stand-alone argmax over logits (used by the per-op entry point).
 cudaError_t launch_argmax(cudaStream_t stream, const float *logits, uint32_t count,
                           uint32_t *token_out);

@@ -369,6 +369,21 @@ extern "C" int nerva_b200_greedy_argmax(const float *logits, uint32_t count, uin
   return 0;
 }
 
+// A rectangular block of a row-major tensor with `full_cols` columns: the shard
+// generator of the tensor-parallel tests and bench (same bits as the whole tensor).
+extern "C" void nerva_b200_synth_normal_bf16_block(uint64_t seed, uint64_t tensor_id, uint64_t full_cols,
+                                                   uint64_t row_begin, uint64_t rows, uint64_t col_begin,
+                                                   uint64_t cols, float std, uint16_t *out) {
+  const uint64_t key = nerva_synth_key(seed, tensor_id);
+  const float scale = std * (1.0f / 65536.0f);
+#pragma omp parallel for schedule(static)
+  for (int64_t r = 0; r < static_cast<int64_t>(rows); ++r) {
+    const uint64_t base = (row_begin + static_cast<uint64_t>(r)) * full_cols + col_begin;
+    uint16_t *dst = out + static_cast<uint64_t>(r) * cols;
+    for (uint64_t c = 0; c < cols; ++c) dst[c] = nerva_synth_normal_bf16(key, base + c, scale);
+  }
+}
+
 extern "C" void nerva_b200_synth_normal_bf16(uint64_t seed, uint64_t tensor_id, uint64_t count,
                                              float std, uint16_t *out) {
   const uint64_t key = nerva_synth_key(seed, tensor_id);

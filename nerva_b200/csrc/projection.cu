@@ -65,8 +65,19 @@ __global__ void __launch_bounds__(kStreamThreads, 1) projection_stream_kernel(Pr
     uint4 *dst = reinterpret_cast<uint4 *>(x);
     for (uint32_t i = threadIdx.x; i < p.cols / 8u; i += blockDim.x) dst[i] = src[i];
   } else {
+    uint32_t partials = 1;
+    if (p.gather.world > 1 && p.add_b != nullptr) {
+      // the partial sums of the other ranks arrive over NVLink
+      partials = p.gather.world;
+      if (threadIdx.x < partials) {
+        const unsigned long long expected = *p.gather.epoch * p.gather.per_epoch + p.gather.offset;
+        if (!wait_counter_bounded(p.gather.arrivals + threadIdx.x, expected))
+          report_error(p.error_word, kErrPeerWaitTimeout);
+      }
+      __syncthreads();
+    }
     add_norm_to_smem(x, p.add_a, p.add_b, p.add_bias, p.norm_weight, p.eps, p.cols,
-                     blockIdx.x == 0 ? p.resid_out : nullptr, sh.scratch);
+                     blockIdx.x == 0 ? p.resid_out : nullptr, sh.scratch, partials);
   }
   __syncthreads();
   stamp(p.stamps, kStampAfterPrologue);
@@ -76,8 +87,19 @@ __global__ void __launch_bounds__(kStreamThreads, 1) projection_stream_kernel(Pr
 
   // Epilogue over the block's rows, coalesced.
   if (EPI == kEpilogueStore) {
-    for (uint32_t r = threadIdx.x; r < rows_local; r += blockDim.x) {
-      p.out_f32[row_begin + r] = stream_row_total(sh.stream, row_total, r);
+    if (p.push.world > 1) {
+      for (uint32_t r = threadIdx.x; r < rows_local; r += blockDim.x) {
+        const float y = stream_row_total(sh.stream, row_total, r);
+        const uint64_t at = static_cast<uint64_t>(p.push.rank) * p.rows + row_begin + r;
+        for (uint32_t q = 0; q < p.push.world; ++q) p.push.recv[q][at] = y;
+      }
+      __threadfence_system();
+      __syncthreads();
+      if (threadIdx.x < p.push.world) atomicAdd_system(p.push.arrivals[threadIdx.x] + p.push.rank, 1ull);
+    } else {
+      for (uint32_t r = threadIdx.x; r < rows_local; r += blockDim.x) {
+        p.out_f32[row_begin + r] = stream_row_total(sh.stream, row_total, r);
+      }
     }
   } else if (EPI == kEpilogueSwiglu) {
     for (uint32_t i = threadIdx.x; i < rows_local / 2u; i += blockDim.x) {
@@ -265,6 +287,7 @@ cudaError_t launch_projection(cudaStream_t stream, const ProjectionParams &p, ui
     return launch_with_pdl(projection_stream_kernel<kEpilogueArgmax>, dim3(blocks), dim3(kStreamThreads),
                            smem, stream, pdl, p);
   }
+  if (p.push.world > 1 || p.gather.world > 1) return cudaErrorNotSupported;  // exchange: streaming path only
   // Toy-shape path.  With a fused prologue the caller passes `cols` writable
   // bf16 elements in x_bf16; the normalised vector goes through them.
   const uint16_t *x = p.x_bf16;

@@ -105,7 +105,7 @@ ArenaLayout compute_arena_layout(const ModelDims &d, const NervaCudaHfDecodeChai
   const uint64_t hidden = d.hidden, ah = d.attention_hidden(), kvh = d.kv_hidden();
   const uint64_t inter = d.intermediate;
   uint64_t c = 0;
-  out.embeddings = push(c, static_cast<uint64_t>(d.vocab) * hidden);
+  out.embeddings = push(c, static_cast<uint64_t>(d.embed_vocab != 0 ? d.embed_vocab : d.vocab) * hidden);
   out.input = push(c, hidden);
   out.scratch = push(c, hidden);
   out.layers.resize(d.layers);
@@ -255,6 +255,41 @@ bool plan_state(Session *s, StaticArena &arena, void *base) {
   return ok;
 }
 
+// Exchange buffer of a tensor-parallel rank (its own allocation, shared with the
+// other ranks through an inter-process handle).  Offsets are the same on every rank.
+struct CommLayout {
+  uint64_t recv_o, recv_d, arrivals_o, arrivals_d, arrivals_s, candidates, epoch, bytes;
+};
+CommLayout comm_layout(uint32_t world, uint32_t hidden) {
+  CommLayout c{};
+  uint64_t at = 0;
+  auto take = [&at](uint64_t bytes) {
+    const uint64_t begin = at;
+    at = (at + bytes + 255u) & ~uint64_t{255};
+    return begin;
+  };
+  c.recv_o = take(static_cast<uint64_t>(world) * hidden * 4u);
+  c.recv_d = take(static_cast<uint64_t>(world) * hidden * 4u);
+  c.arrivals_o = take(world * 8u);
+  c.arrivals_d = take(world * 8u);
+  c.arrivals_s = take(world * 8u);
+  c.candidates = take(world * 8u);
+  c.epoch = take(8u);
+  c.bytes = at;
+  return c;
+}
+template <class T>
+T *comm_at(void *base, uint64_t offset) {
+  return reinterpret_cast<T *>(static_cast<uint8_t *>(base) + offset);
+}
+cudaError_t allocate_comm(Session *s) {
+  const CommLayout c = comm_layout(s->tp_world, s->dims.hidden);
+  cudaError_t err = cudaMalloc(&s->comm_block, c.bytes);
+  if (err == cudaSuccess) err = cudaMemset(s->comm_block, 0, c.bytes);
+  s->comm_bytes = c.bytes;
+  return err;
+}
+
 void destroy_graphs(Session *s) {
   for (GraphEntry &g : s->graphs) {
     if (g.exec != nullptr) cudaGraphExecDestroy(g.exec);
@@ -273,6 +308,10 @@ void destroy_session(Session *s) {
   if (s->host_slots != nullptr) cudaFreeHost(s->host_slots);
   if (s->host_error != nullptr) cudaFreeHost(s->host_error);
   if (s->state_block != nullptr) cudaFree(s->state_block);
+  for (uint32_t q = 0; q < kMaxTpWorld; ++q) {
+    if (s->comm_peers[q] != nullptr && s->comm_peers[q] != s->comm_block) cudaIpcCloseMemHandle(s->comm_peers[q]);
+  }
+  if (s->comm_block != nullptr) cudaFree(s->comm_block);
   delete s;
 }
 
@@ -283,7 +322,7 @@ StepState step_state(Session *s) {
   st.prompt_count = s->prompt_count;
   st.slots = s->device_slots;
   st.max_context = s->max_context;
-  st.vocab = s->dims.vocab;
+  st.vocab = s->dims.embed_vocab;  // token ids index the (whole) embedding table
   st.error_word = s->device_error;
   return st;
 }
@@ -428,6 +467,42 @@ cudaError_t enqueue_step(Session *s, uint32_t splits, uint32_t sample, uint64_t 
   const uint64_t ah = d.attention_hidden(), kvh = d.kv_hidden();
   const uint64_t qkv_rows = ah + 2 * kvh;
   uint64_t n = 0;
+  // tensor parallel: where the partial sums of O and down travel (see kernels.cuh: TpPush)
+  const bool tp = s->tp_world > 1;
+  if (tp && (!s->tp_attached || s->engine != 0)) return cudaErrorNotReady;
+  const CommLayout comm = comm_layout(s->tp_world, d.hidden);
+  auto push_to = [&](uint64_t recv, uint64_t arrivals) {
+    TpPush push{};
+    push.world = s->tp_world;
+    push.rank = s->tp_rank;
+    for (uint32_t q = 0; q < s->tp_world; ++q) {
+      push.recv[q] = comm_at<float>(s->comm_peers[q], recv);
+      push.arrivals[q] = comm_at<unsigned long long>(s->comm_peers[q], arrivals);
+    }
+    return push;
+  };
+  auto gather_from = [&](uint64_t arrivals, uint64_t writer_blocks, uint64_t pushes_so_far) {
+    TpGather gather{};
+    gather.world = s->tp_world;
+    gather.arrivals = comm_at<unsigned long long>(s->comm_block, arrivals);
+    gather.epoch = comm_at<unsigned long long>(s->comm_block, comm.epoch);
+    gather.per_epoch = writer_blocks * d.layers;
+    gather.offset = writer_blocks * pushes_so_far;
+    return gather;
+  };
+  uint64_t o_blocks = 0, down_blocks = 0;
+  if (tp) {
+    ProjectionParams shape{};
+    shape.rows = d.hidden;
+    shape.cols = static_cast<uint32_t>(ah);
+    shape.weight = arena_at(s, s->layout.layers[0].w_o);
+    shape.x_bf16 = s->attn_bf16;
+    o_blocks = projection_blocks(shape, s->sm_count);
+    shape.cols = d.intermediate;
+    shape.weight = arena_at(s, s->layout.layers[0].w_down);
+    shape.x_bf16 = s->ff_bf16;
+    down_blocks = projection_blocks(shape, s->sm_count);
+  }
   auto stamps_for = [s](uint32_t node) -> unsigned long long * {
     return s->timeline_on && node < s->timeline_nodes ? s->timeline + node * kTimelineSlots : nullptr;
   };
@@ -453,6 +528,10 @@ cudaError_t enqueue_step(Session *s, uint32_t splits, uint32_t sample, uint64_t 
     p.x_bf16 = s->x_scratch;
     p.add_a = s->h_b;
     p.add_b = l == 0 ? nullptr : s->down;
+    if (tp && l != 0) {
+      p.add_b = comm_at<float>(s->comm_block, comm.recv_d);
+      p.gather = gather_from(comm.arrivals_d, down_blocks, l);
+    }
     p.norm_weight = arena_at(s, L.rms_attn);
     p.resid_out = s->h_a;
     p.epilogue = kEpilogueStore;
@@ -552,6 +631,7 @@ cudaError_t enqueue_step(Session *s, uint32_t splits, uint32_t sample, uint64_t 
     p.x_bf16 = s->attn_bf16;
     p.epilogue = kEpilogueStore;
     p.out_f32 = s->o_out;
+    if (tp) p.push = push_to(comm.recv_o, comm.arrivals_o);
     p.stamps = stamps_for(5u * l + 2u);
     err = launch_projection(s->stream, p, s->sm_count);
     n += 1;
@@ -570,6 +650,10 @@ cudaError_t enqueue_step(Session *s, uint32_t splits, uint32_t sample, uint64_t 
     p.x_bf16 = s->x_scratch;
     p.add_a = s->h_a;
     p.add_b = s->o_out;
+    if (tp) {
+      p.add_b = comm_at<float>(s->comm_block, comm.recv_o);
+      p.gather = gather_from(comm.arrivals_o, o_blocks, l + 1u);
+    }
     p.add_bias = arena_at(s, L.o_bias);
     p.norm_weight = arena_at(s, L.rms_mlp);
     p.resid_out = s->h_b;
@@ -593,6 +677,7 @@ cudaError_t enqueue_step(Session *s, uint32_t splits, uint32_t sample, uint64_t 
     p.x_bf16 = s->ff_bf16;
     p.epilogue = kEpilogueStore;
     p.out_f32 = s->down;
+    if (tp) p.push = push_to(comm.recv_d, comm.arrivals_d);
     p.stamps = stamps_for(5u * l + 4u);
     err = launch_projection(s->stream, p, s->sm_count);
     n += 1;
@@ -611,6 +696,10 @@ cudaError_t enqueue_step(Session *s, uint32_t splits, uint32_t sample, uint64_t 
     p.x_bf16 = s->x_scratch;
     p.add_a = s->h_b;
     p.add_b = s->down;
+    if (tp) {
+      p.add_b = comm_at<float>(s->comm_block, comm.recv_d);
+      p.gather = gather_from(comm.arrivals_d, down_blocks, d.layers);
+    }
     p.norm_weight = arena_at(s, s->layout.final_norm);
     p.resid_out = s->h_a;
     p.epilogue = kEpilogueArgmax;
@@ -624,7 +713,19 @@ cudaError_t enqueue_step(Session *s, uint32_t splits, uint32_t sample, uint64_t 
     profile_mark(s, prof, kBucketLmHead);
   }
   if (err == cudaSuccess) {
-    err = launch_sample_greedy(s->stream, st, s->best_value, s->best_index, partials, sample, s->use_pdl);
+    TpSample exchange{};
+    if (tp) {
+      exchange.world = s->tp_world;
+      exchange.rank = s->tp_rank;
+      exchange.vocab_offset = d.vocab_offset;
+      exchange.epoch = comm_at<unsigned long long>(s->comm_block, comm.epoch);
+      for (uint32_t q = 0; q < s->tp_world; ++q) {
+        exchange.recv[q] = comm_at<unsigned long long>(s->comm_peers[q], comm.candidates);
+        exchange.arrivals[q] = comm_at<unsigned long long>(s->comm_peers[q], comm.arrivals_s);
+      }
+    }
+    err = launch_sample_greedy(s->stream, st, s->best_value, s->best_index, partials, sample, s->use_pdl,
+                               tp ? &exchange : nullptr);
     n += 1;
     profile_mark(s, prof, kBucketSampling);
   }
@@ -879,7 +980,7 @@ cudaError_t upload_from_pointers(Session *s, const NervaCudaHfDecodeSequenceSess
   const ModelDims &d = s->dims;
   const uint64_t hidden = d.hidden, ah = d.attention_hidden(), kvh = d.kv_hidden();
   const uint64_t inter = d.intermediate;
-  cudaError_t err = copy_tensor(s, s->layout.embeddings, r->embeddings, d.vocab * hidden, c);
+  cudaError_t err = copy_tensor(s, s->layout.embeddings, r->embeddings, d.embed_vocab * hidden, c);
   for (uint32_t i = 0; err == cudaSuccess && i < d.layers; ++i) {
     const NervaCudaHfDecodeChainLayer &L = r->layers[i];
     const LayerLayout &o = s->layout.layers[i];
@@ -908,7 +1009,7 @@ cudaError_t upload_from_pointers(Session *s, const NervaCudaHfDecodeSequenceSess
 cudaError_t upload_from_descriptors(Session *s,
                                     const NervaCudaHfDecodeSequenceSessionCreateRequest *r,
                                     UploadCounters *c) {
-  const uint64_t embedding_bytes = static_cast<uint64_t>(s->dims.vocab) * s->dims.hidden * 2u;
+  const uint64_t embedding_bytes = static_cast<uint64_t>(s->dims.embed_vocab) * s->dims.hidden * 2u;
   const uint64_t gap_bytes = static_cast<uint64_t>(s->dims.hidden) * 2u * 2u;
   constexpr uint64_t kStagingBytes = 64ull << 20;
   uint8_t *staging = nullptr;
@@ -1086,10 +1187,10 @@ cudaError_t allocate_state(Session *s, int32_t *stage) {
 
 }  // namespace
 
-extern "C" int nerva_cuda_hf_decode_sequence_session_create(
-    const NervaCudaHfDecodeSequenceSessionCreateRequest *request,
-    NervaCudaHfDecodeSequenceSessionCreateResult *out,
-    NervaCudaHfDecodeSequenceSession **session_out) {
+static int create_session(const NervaCudaHfDecodeSequenceSessionCreateRequest *request,
+                          const NervaB200ShardInfo *shard,
+                          NervaCudaHfDecodeSequenceSessionCreateResult *out,
+                          NervaCudaHfDecodeSequenceSession **session_out) {
   if (out == nullptr) return -1;
   memset(out, 0, sizeof(*out));
   out->status = -1;
@@ -1146,6 +1247,20 @@ extern "C" int nerva_cuda_hf_decode_sequence_session_create(
   d.intermediate = request->intermediate;
   d.vocab = request->vocab_size;
   d.layers = request->layer_count;
+  d.embed_vocab = d.vocab;
+  if (shard != nullptr) {
+    // A tensor-parallel rank: the request describes this rank's shard (local heads,
+    // KV heads, intermediate size and lm_head rows); the embedding table is whole.
+    if (shard->world < 2 || shard->world > kMaxTpWorld || shard->rank >= shard->world ||
+        shard->full_vocab < request->vocab_size ||
+        static_cast<uint64_t>(shard->vocab_offset) + request->vocab_size > shard->full_vocab ||
+        request->planned_weight_blocks != 0) {
+      out->failure_stage = kStageInvalidRequest;
+      return -1;
+    }
+    d.embed_vocab = shard->full_vocab;
+    d.vocab_offset = shard->vocab_offset;
+  }
   ArenaLayout layout = compute_arena_layout(d, request->layers);
   const uint64_t resident_weight_bytes = layout.elements * 2u - static_cast<uint64_t>(d.hidden) * 4u;
   out->resident_weight_bytes = resident_weight_bytes;
@@ -1200,6 +1315,10 @@ extern "C" int nerva_cuda_hf_decode_sequence_session_create(
   s->planned_weight_descriptor_count = request->planned_weight_descriptor_count;
   s->planned_weight_descriptor_hash = declared_plan ? request->planned_weight_descriptor_hash : 0;
   s->layer_meta.assign(request->layers, request->layers + request->layer_count);
+  if (shard != nullptr) {
+    s->tp_world = shard->world;
+    s->tp_rank = shard->rank;
+  }
 
   int device = 0;
   err = cudaGetDevice(&device);
@@ -1228,6 +1347,10 @@ extern "C" int nerva_cuda_hf_decode_sequence_session_create(
   int32_t stage = kStageDeviceScratchAlloc;
   err = allocate_state(s, &stage);
   if (err != cudaSuccess) return create_fail(s, out, err, stage);
+  if (s->tp_world > 1) {
+    err = allocate_comm(s);
+    if (err != cudaSuccess) return create_fail(s, out, err, kStageDeviceScratchAlloc);
+  }
 
   UploadCounters counters;
   err = declared_plan ? upload_from_descriptors(s, request, &counters)
@@ -1263,6 +1386,64 @@ extern "C" int nerva_cuda_hf_decode_sequence_session_create(
   out->hot_path_allocations = 0;
   out->status = 0;
   *session_out = s;
+  return 0;
+}
+
+extern "C" int nerva_cuda_hf_decode_sequence_session_create(
+    const NervaCudaHfDecodeSequenceSessionCreateRequest *request,
+    NervaCudaHfDecodeSequenceSessionCreateResult *out,
+    NervaCudaHfDecodeSequenceSession **session_out) {
+  return create_session(request, nullptr, out, session_out);
+}
+
+extern "C" int nerva_b200_session_create_sharded(
+    const NervaCudaHfDecodeSequenceSessionCreateRequest *request, const NervaB200ShardInfo *shard,
+    NervaCudaHfDecodeSequenceSessionCreateResult *out, NervaCudaHfDecodeSequenceSession **session_out) {
+  if (shard == nullptr) {
+    if (out != nullptr) {
+      memset(out, 0, sizeof(*out));
+      out->status = -1;
+      out->failure_stage = kStageInvalidRequest;
+    }
+    return -1;
+  }
+  return create_session(request, shard, out, session_out);
+}
+
+// The 64-byte inter-process handle of this rank's exchange buffer.
+extern "C" int nerva_b200_session_comm_handle(Session *s, uint8_t *handle, uint32_t capacity) {
+  if (s == nullptr || handle == nullptr || capacity < sizeof(cudaIpcMemHandle_t) || s->comm_block == nullptr)
+    return -1;
+  cudaIpcMemHandle_t h;
+  const cudaError_t err = cudaIpcGetMemHandle(&h, s->comm_block);
+  if (err != cudaSuccess) {
+    set_last_error(cudaGetErrorString(err));
+    return -1;
+  }
+  memcpy(handle, &h, sizeof(h));
+  return static_cast<int>(sizeof(h));
+}
+
+// handles: world x 64 bytes, in rank order (this rank's own entry is ignored).
+extern "C" int nerva_b200_session_attach_peers(Session *s, const uint8_t *handles, uint32_t world) {
+  if (s == nullptr || handles == nullptr || world != s->tp_world || s->comm_block == nullptr || s->tp_attached)
+    return -1;
+  for (uint32_t q = 0; q < world; ++q) {
+    if (q == s->tp_rank) {
+      s->comm_peers[q] = s->comm_block;
+      continue;
+    }
+    cudaIpcMemHandle_t h;
+    memcpy(&h, handles + static_cast<size_t>(q) * sizeof(h), sizeof(h));
+    void *mapped = nullptr;
+    const cudaError_t err = cudaIpcOpenMemHandle(&mapped, h, cudaIpcMemLazyEnablePeerAccess);
+    if (err != cudaSuccess) {
+      set_last_error(std::string("cudaIpcOpenMemHandle: ") + cudaGetErrorString(err));
+      return -1;
+    }
+    s->comm_peers[q] = mapped;
+  }
+  s->tp_attached = true;
   return 0;
 }
 
@@ -1311,6 +1492,10 @@ extern "C" int nerva_b200_session_read_timeline(Session *s, uint64_t *stamps, ui
 
 extern "C" int nerva_b200_session_set_engine(Session *s, uint32_t engine) {
   if (s == nullptr || engine > 1 || s->started) return -1;
+  if (engine == 1 && s->tp_world > 1) {
+    set_last_error("the whole-step kernel has no tensor-parallel exchange");
+    return -1;
+  }
   if (engine == 1 && !s->step_kernel_ok) {
     set_last_error("whole-step kernel needs head_dim 64 or 128, dims that are multiples of 8, and "
                    "an activation vector that fits beside the weight ring in shared memory");
@@ -1332,7 +1517,7 @@ extern "C" int nerva_cuda_hf_decode_sequence_session_start(
   Session *s = request->session;
   if (request->prompt_token_count > s->max_context) return -1;
   for (uint32_t i = 0; i < request->prompt_token_count; ++i) {
-    if (request->prompt_tokens[i] >= s->dims.vocab) return -1;
+    if (request->prompt_tokens[i] >= s->dims.embed_vocab) return -1;
   }
   fill_header(s, out, 0, request->prompt_tokens[request->prompt_token_count - 1u]);
   if (!sampler_greedy(request->sampler)) {
@@ -1496,7 +1681,7 @@ extern "C" int nerva_cuda_hf_decode_sequence_session_run(
   const uint32_t context_steps = request->prompt_token_count + request->steps - 1u;
   if (context_steps > s->max_context) return -1;
   for (uint32_t i = 0; i < request->prompt_token_count; ++i) {
-    if (request->prompt_tokens[i] >= s->dims.vocab) return -1;
+    if (request->prompt_tokens[i] >= s->dims.embed_vocab) return -1;
   }
   fill_header(s, out, request->steps, request->seed_token);
   if (!sampler_greedy(request->sampler)) {

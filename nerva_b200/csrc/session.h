@@ -49,6 +49,9 @@ struct ArenaLayout {
 struct ModelDims {
   uint32_t dtype = 0, hidden = 0, heads = 0, kv_heads = 0, head_dim = 0;
   uint32_t intermediate = 0, vocab = 0, layers = 0;
+  // vocab = rows of lm_head held here; a tensor-parallel rank holds a shard of the
+  // rows starting at vocab_offset, while the embedding table keeps embed_vocab rows.
+  uint32_t embed_vocab = 0, vocab_offset = 0;
   uint64_t attention_hidden() const { return static_cast<uint64_t>(heads) * head_dim; }
   uint64_t kv_hidden() const { return static_cast<uint64_t>(kv_heads) * head_dim; }
 };
@@ -154,6 +157,12 @@ struct NervaCudaHfDecodeSequenceSession {
   unsigned long long *timeline = nullptr;
   uint32_t timeline_nodes = 0;
   bool timeline_on = false;
+  // tensor parallel (nerva_b200_session_create_sharded)
+  uint32_t tp_world = 1, tp_rank = 0;
+  void *comm_block = nullptr;  // this rank's exchange buffer (own allocation, exported to the peers)
+  uint64_t comm_bytes = 0;
+  void *comm_peers[nb::kMaxTpWorld] = {};  // every rank's exchange buffer as mapped here
+  bool tp_attached = false;
   uint32_t x_elems = 0;
   uint32_t row_elems = 0;  // rows of the largest per-block row range of any projection
   bool step_kernel_ok = false;

@@ -19,9 +19,14 @@ namespace nb {
 // prologue is one round trip to L2.
 constexpr uint32_t kNormRegIters = 8;  // float4 per thread held in registers
 
+//
+// b_count > 1 (tensor parallel): b holds b_count partial vectors of `cols`
+// floats, one per rank; they are added in rank order, so every rank computes
+// the same r bit for bit.
 __device__ __forceinline__ void add_norm_to_smem(uint16_t *x, const float *a, const float *b,
                                                  const uint16_t *bias, const uint16_t *w, float eps,
-                                                 uint32_t cols, float *resid_out, float *scratch) {
+                                                 uint32_t cols, float *resid_out, float *scratch,
+                                                 uint32_t b_count = 1) {
   const uint32_t vecs = cols / 4u;
   const bool fast = cols % 4u == 0 && bias == nullptr && vecs <= kNormRegIters * blockDim.x &&
                     (reinterpret_cast<uintptr_t>(a) & 15u) == 0 &&
@@ -39,7 +44,14 @@ __device__ __forceinline__ void add_norm_to_smem(uint16_t *x, const float *a, co
         // L2 loads: in the whole-step kernel these vectors were written by other blocks
         float4 v = __ldcg(reinterpret_cast<const float4 *>(a) + i);
         if (b != nullptr) {
-          const float4 t = __ldcg(reinterpret_cast<const float4 *>(b) + i);
+          float4 t = __ldcg(reinterpret_cast<const float4 *>(b) + i);
+          for (uint32_t q = 1; q < b_count; ++q) {
+            const float4 u = __ldcg(reinterpret_cast<const float4 *>(b + static_cast<uint64_t>(q) * cols) + i);
+            t.x += u.x;
+            t.y += u.y;
+            t.z += u.z;
+            t.w += u.w;
+          }
           v.x = t.x + v.x;
           v.y = t.y + v.y;
           v.z = t.z + v.z;
@@ -69,9 +81,14 @@ __device__ __forceinline__ void add_norm_to_smem(uint16_t *x, const float *a, co
     }
     return;
   }
+  auto b_sum = [&](uint32_t i) {
+    float t = __ldcg(b + i);
+    for (uint32_t q = 1; q < b_count; ++q) t += __ldcg(b + static_cast<uint64_t>(q) * cols + i);
+    return t;
+  };
   float sumsq = 0.0f;
   for (uint32_t i = threadIdx.x; i < cols; i += blockDim.x) {
-    float r = b != nullptr ? __ldcg(b + i) : __ldcg(a + i);
+    float r = b != nullptr ? b_sum(i) : __ldcg(a + i);
     if (bias != nullptr) r += bf16_bits_to_f32(bias[i]);
     if (b != nullptr) r += __ldcg(a + i);
     sumsq += r * r;
@@ -79,7 +96,7 @@ __device__ __forceinline__ void add_norm_to_smem(uint16_t *x, const float *a, co
   const float total = block_sum(sumsq, scratch);
   const float scale = rsqrtf(total / static_cast<float>(cols) + eps);
   for (uint32_t i = threadIdx.x; i < cols; i += blockDim.x) {
-    float r = b != nullptr ? __ldcg(b + i) : __ldcg(a + i);
+    float r = b != nullptr ? b_sum(i) : __ldcg(a + i);
     if (bias != nullptr) r += bf16_bits_to_f32(bias[i]);
     if (b != nullptr) r += __ldcg(a + i);
     if (resid_out != nullptr) resid_out[i] = r;

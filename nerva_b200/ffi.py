@@ -109,6 +109,10 @@ def lib() -> C.CDLL:
         "nerva_b200_session_profile_steps": [vp, C.c_uint32, vp, vp, C.c_uint32],
         "nerva_b200_session_read_phase_cycles": [vp, vp, C.c_uint32],
         "nerva_b200_session_read_timeline": [vp, vp, C.c_uint32],
+        "nerva_b200_session_create_sharded": [P(CreateRequest), P(structs["NervaB200ShardInfo"]), P(CreateResult),
+                                              P(vp)],
+        "nerva_b200_session_comm_handle": [vp, vp, C.c_uint32],
+        "nerva_b200_session_attach_peers": [vp, vp, C.c_uint32],
         "nerva_b200_projection": [vp, vp, vp, C.c_uint32, C.c_uint32, C.c_uint32, C.c_uint32, C.c_uint32,
                                   P(C.c_uint64)],
         "nerva_b200_gqa_decode_attention": [vp, vp, vp, vp, vp, C.c_uint32, C.c_uint32, C.c_uint32, C.c_uint32,
@@ -117,11 +121,12 @@ def lib() -> C.CDLL:
                                                            C.c_uint32, C.c_uint32, C.c_uint32, vp],
         "nerva_b200_greedy_argmax": [vp, C.c_uint32, P(C.c_uint32)],
         "nerva_b200_synth_normal_bf16": [C.c_uint64, C.c_uint64, C.c_uint64, C.c_float, vp],
+        "nerva_b200_synth_normal_bf16_block": [C.c_uint64] * 7 + [C.c_float, vp],
     }
     for name, argtypes in sigs.items():
         fn = getattr(L, name)
         fn.argtypes = argtypes
-        fn.restype = None if name == "nerva_b200_synth_normal_bf16" else C.c_int
+        fn.restype = None if name.startswith("nerva_b200_synth_normal_bf16") else C.c_int
     u32, u64, i64 = C.c_uint32, C.c_uint64, C.c_int64
     host = {  # host-side memory bookkeeping: name -> (restype, argtypes)
         "nerva_b200_static_arena_new": (vp, [u64]),

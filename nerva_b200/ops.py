@@ -79,6 +79,15 @@ def synth_normal_bf16(seed: int, tensor_id: int, count: int, std: float) -> np.n
     return out
 
 
+def synth_normal_bf16_block(seed: int, tensor_id: int, full_cols: int, row_begin: int, rows: int, col_begin: int,
+                            cols: int, std: float) -> np.ndarray:
+    """rows x cols block of the generator's row-major tensor with full_cols columns (flattened)."""
+    out = np.empty(rows * cols, dtype=np.uint16)
+    ffi.lib().nerva_b200_synth_normal_bf16_block(seed, tensor_id, full_cols, row_begin, rows, col_begin, cols, std,
+                                                 out.ctypes.data)
+    return out
+
+
 def plan_layout(cfg, layers, layer_index: int = 0):
     req = ffi.LayoutPlanRequest(hidden=cfg.hidden, heads=cfg.heads, kv_heads=cfg.kv_heads, head_dim=cfg.head_dim,
                                 intermediate=cfg.intermediate, vocab_size=cfg.vocab, layer_count=cfg.layers,

@@ -145,8 +145,17 @@ class CudaHfDecodeSequenceSession:
         self.request = req
         self._handle = C.c_void_p()
         self.create_result = ffi.CreateResult()
-        rc = ffi.lib().nerva_cuda_hf_decode_sequence_session_create(C.byref(req), C.byref(self.create_result),
-                                                                    C.byref(self._handle))
+        self.shard = getattr(checkpoint, "shard", None)
+        if self.shard is not None:
+            # a tensor-parallel rank: `checkpoint` holds this rank's slices (nerva_b200.synth.shard_checkpoint)
+            info = ffi.structs["NervaB200ShardInfo"](rank=self.shard.rank, world=self.shard.world,
+                                                     full_vocab=self.shard.full_vocab,
+                                                     vocab_offset=self.shard.vocab_offset)
+            rc = ffi.lib().nerva_b200_session_create_sharded(C.byref(req), C.byref(info),
+                                                             C.byref(self.create_result), C.byref(self._handle))
+        else:
+            rc = ffi.lib().nerva_cuda_hf_decode_sequence_session_create(C.byref(req), C.byref(self.create_result),
+                                                                        C.byref(self._handle))
         r = self.create_result
         self.status = _status(rc, r.status, r.cuda_error, r.device_count)
         self.error = ffi.last_error()
@@ -236,6 +245,20 @@ class CudaHfDecodeSequenceSession:
         if ffi.lib().nerva_b200_session_read_phase_cycles(self._handle, _ptr(cycles), 16) < 0:
             raise RuntimeError("phase cycles unavailable")
         return {name: int(c) for name, c in zip(self.PHASES, cycles)}
+
+    def comm_handle(self) -> bytes:
+        """64-byte inter-process handle of this tensor-parallel rank's exchange buffer."""
+        buf = (C.c_uint8 * 64)()
+        if ffi.lib().nerva_b200_session_comm_handle(self._handle, buf, 64) != 64:
+            raise RuntimeError("no exchange buffer: " + ffi.last_error())
+        return bytes(buf)
+
+    def attach_peers(self, handles) -> None:
+        """handles: the comm_handle() of every rank, in rank order."""
+        blob = b"".join(handles)
+        buf = (C.c_uint8 * len(blob)).from_buffer_copy(blob)
+        if ffi.lib().nerva_b200_session_attach_peers(self._handle, buf, len(handles)) != 0:
+            raise RuntimeError("attach_peers failed: " + ffi.last_error())
 
     def read_timeline(self) -> np.ndarray:
         """%globaltimer stamps of the last step, shape [5 * layers + 1, 8] (launch order QKV, attention,

@@ -195,5 +195,106 @@ def dense_checkpoint(cfg: DecoderConfig, seed: int = 0, std: float = 0.02, fill=
     return ck
 
 
+@dataclass
+class ShardInfo:
+    rank: int
+    world: int
+    full_vocab: int
+    vocab_offset: int
+
+
+def shard_config(cfg: DecoderConfig, world: int) -> DecoderConfig:
+    """Dimensions one tensor-parallel rank holds: its share of the query heads, KV heads,
+    intermediate size and lm_head rows; hidden size, head_dim and layer count stay."""
+    import dataclasses
+    if cfg.num_experts:
+        raise ValueError("tensor parallel sharding covers dense layers")
+    for name, value in (("heads", cfg.heads), ("kv_heads", cfg.kv_heads), ("intermediate", cfg.intermediate),
+                        ("vocab", cfg.vocab)):
+        if value % world:
+            raise ValueError(f"{name}={value} is not divisible by {world} ranks")
+    return dataclasses.replace(cfg, name=f"{cfg.name} shard 1/{world}", heads=cfg.heads // world,
+                               kv_heads=cfg.kv_heads // world, intermediate=cfg.intermediate // world,
+                               vocab=cfg.vocab // world)
+
+
+def _numpy_block(seed, tensor_id, full_cols, row_begin, rows, col_begin, cols, std):
+    full = normal_bf16(seed, tensor_id, (row_begin + rows) * full_cols, std).reshape(-1, full_cols)
+    return np.ascontiguousarray(full[row_begin:row_begin + rows, col_begin:col_begin + cols]).reshape(-1)
+
+
+def dense_checkpoint_shard(cfg: DecoderConfig, rank: int, world: int, seed: int = 0, std: float = 0.02,
+                           block_fill=None, fill=None) -> DenseCheckpoint:
+    """Rank `rank`'s slice of dense_checkpoint(cfg): QKV, gate/up and lm_head by rows, O and down
+    by columns, norms and the embedding table whole.  Generated directly (no full model in
+    memory) with the same bits as the slices of the full tensors.  The result carries
+    `.shard` (ShardInfo) and `.config` (the local dimensions)."""
+    local = shard_config(cfg, world)
+    block = block_fill or _numpy_block
+    gen = fill or normal_bf16
+    h, d = cfg.hidden, cfg.head_dim
+    ah, kvh, inter = cfg.attention_hidden, cfg.kv_hidden, cfg.intermediate
+    lah, lkvh, linter = local.attention_hidden, local.kv_hidden, local.intermediate
+    ones_h = np.full(h, BF16_ONE, dtype=np.uint16)
+    ones_d = np.full(d, BF16_ONE, dtype=np.uint16)
+    ck = DenseCheckpoint(
+        local,
+        embeddings=gen(seed, T_EMBEDDINGS, cfg.vocab * h, std),
+        final_norm=ones_h.copy(),
+        lm_head=block(seed, T_LM_HEAD, h, rank * local.vocab, local.vocab, 0, h, std),
+    )
+    ck.shard = ShardInfo(rank, world, cfg.vocab, rank * local.vocab)
+    for layer in range(cfg.layers):
+        tid = lambda slot: layer_tensor_id(layer, slot)  # noqa: E731
+        entry = {
+            "rms_attn": ones_h.copy(),
+            "rms_mlp": ones_h.copy(),
+            "w_q": block(seed, tid(L_WQ), h, rank * lah, lah, 0, h, std),
+            "w_k": block(seed, tid(L_WK), h, rank * lkvh, lkvh, 0, h, std),
+            "w_v": block(seed, tid(L_WV), h, rank * lkvh, lkvh, 0, h, std),
+            "w_o": block(seed, tid(L_WO), ah, 0, h, rank * lah, lah, std),
+            "w_gate": block(seed, tid(L_WGATE), h, rank * linter, linter, 0, h, std),
+            "w_up": block(seed, tid(L_WUP), h, rank * linter, linter, 0, h, std),
+            "w_down": block(seed, tid(L_WDOWN), inter, 0, h, rank * linter, linter, std),
+        }
+        if cfg.qk_norm:
+            entry["q_norm"] = ones_d.copy()
+            entry["k_norm"] = ones_d.copy()
+        ck.layers.append(entry)
+    return ck
+
+
+def shard_checkpoint(full: DenseCheckpoint, rank: int, world: int) -> DenseCheckpoint:
+    """The same slices cut out of a full checkpoint that is already in memory."""
+    cfg = full.config
+    local = shard_config(cfg, world)
+    h = cfg.hidden
+    lah, lkvh, linter = local.attention_hidden, local.kv_hidden, local.intermediate
+
+    def rows(t, cols, begin, count):
+        return np.ascontiguousarray(t.reshape(-1, cols)[begin:begin + count]).reshape(-1)
+
+    def cols_of(t, full_cols, begin, count):
+        return np.ascontiguousarray(t.reshape(-1, full_cols)[:, begin:begin + count]).reshape(-1)
+
+    ck = DenseCheckpoint(local, embeddings=full.embeddings, final_norm=full.final_norm,
+                         lm_head=rows(full.lm_head, h, rank * local.vocab, local.vocab))
+    ck.shard = ShardInfo(rank, world, cfg.vocab, rank * local.vocab)
+    for entry in full.layers:
+        out = {k: v for k, v in entry.items() if k in ("rms_attn", "rms_mlp", "q_norm", "k_norm", "o_bias")}
+        out["w_q"] = rows(entry["w_q"], h, rank * lah, lah)
+        out["w_k"] = rows(entry["w_k"], h, rank * lkvh, lkvh)
+        out["w_v"] = rows(entry["w_v"], h, rank * lkvh, lkvh)
+        out["w_o"] = cols_of(entry["w_o"], cfg.attention_hidden, rank * lah, lah)
+        out["w_gate"] = rows(entry["w_gate"], h, rank * linter, linter)
+        out["w_up"] = rows(entry["w_up"], h, rank * linter, linter)
+        out["w_down"] = cols_of(entry["w_down"], cfg.intermediate, rank * linter, linter)
+        for name, width in (("q_bias", lah), ("k_bias", lkvh), ("v_bias", lkvh)):
+            if name in entry:
+                out[name] = np.ascontiguousarray(entry[name][rank * width:(rank + 1) * width])
+        ck.layers.append(out)
+    return ck
+
+
 def prompt_ids(cfg: DecoderConfig, seed: int = 1, count: int | None = None) -> np.ndarray:
     return uniform_u32(seed, T_PROMPT, cfg.prompt_tokens if count is None else count, cfg.vocab)

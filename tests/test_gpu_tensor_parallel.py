@@ -1,0 +1,102 @@
+"""Tensor parallel over 2 GPUs: one process per GPU, the tiny Qwen3-architecture model cut in two,
+tokens and logits against the CPU oracle of the whole model.  Skipped on a single-GPU machine."""
+import ctypes
+import os
+import socket
+import sys
+
+import numpy as np
+import pytest
+
+pytestmark = pytest.mark.gpu
+
+ROOT = os.path.abspath(os.path.join(os.path.dirname(__file__), ".."))
+LOGIT_ATOL = 2e-2  # the stated end-to-end bound, met on this configuration
+
+
+def _gpu_count() -> int:
+    try:
+        cudart = ctypes.CDLL("libcudart.so")
+    except OSError:
+        try:
+            cudart = ctypes.CDLL("/usr/local/cuda/lib64/libcudart.so")
+        except OSError:
+            return 0
+    count = ctypes.c_int(0)
+    return count.value if cudart.cudaGetDeviceCount(ctypes.byref(count)) == 0 else 0
+
+
+def _free_port() -> int:
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        return s.getsockname()[1]
+
+
+def _rank_main(rank: int, world: int, port: int, steps: int, results) -> None:
+    sys.path.insert(0, ROOT)
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), RANK=str(rank), WORLD_SIZE=str(world))
+    import torch.distributed as dist
+    from nerva_b200 import ops, synth, tp
+    from nerva_b200.session import CudaHfDecodeSequenceLoop, SmokeStatus
+    tp.select_device(rank)
+    import datetime
+    dist.init_process_group("gloo", rank=rank, world_size=world, timeout=datetime.timedelta(seconds=180))
+    try:
+        cfg = synth.TINY_QWEN3
+        full = synth.dense_checkpoint(cfg, fill=ops.synth_normal_bf16)
+        session = tp.create_session(cfg, cfg.prompt_tokens + steps + 1, rank, world, full_checkpoint=full)
+        # the directly generated shard has the same bits as the slice of the full model
+        direct = synth.dense_checkpoint_shard(cfg, rank, world, block_fill=ops.synth_normal_bf16_block,
+                                              fill=ops.synth_normal_bf16)
+        cut = synth.shard_checkpoint(full, rank, world)
+        same = np.array_equal(direct.lm_head, cut.lm_head) and all(
+            np.array_equal(a[k], b[k]) for a, b in zip(direct.layers, cut.layers) for k in a)
+        start, loop = CudaHfDecodeSequenceLoop.start(session, synth.prompt_ids(cfg))
+        assert start.status == SmokeStatus.OK, start.error
+        tokens, logits = [], []
+        for _ in range(steps):
+            out = loop.advance(1)
+            assert out.status == SmokeStatus.OK, out.error
+            tokens += out.tokens
+            logits.append(session.read_logits())  # this rank's rows of the vocabulary
+        dist.barrier()
+        session.destroy()
+        results[rank] = {"tokens": tokens, "logits": np.stack(logits), "offset": session.shard.vocab_offset,
+                         "shards_equal": bool(same)}
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.skipif(_gpu_count() < 2, reason="needs two GPUs")
+def test_two_rank_tensor_parallel_matches_oracle(built_lib, oracle_mod, tiny_golden):
+    import torch.multiprocessing as mp
+    from nerva_b200 import synth
+    world, steps = 2, 32
+    ctx = mp.get_context("spawn")
+    results = ctx.Manager().dict()
+    port = _free_port()
+    procs = [ctx.Process(target=_rank_main, args=(r, world, port, steps, results)) for r in range(world)]
+    for p in procs:
+        p.start()
+    try:
+        for p in procs:
+            p.join(600)
+            assert p.exitcode == 0
+    finally:
+        for p in procs:
+            if p.is_alive():
+                p.terminate()
+    r0, r1 = results[0], results[1]
+    assert r0["shards_equal"] and r1["shards_equal"]
+    # every rank writes the same token stream, and it is the oracle's
+    assert r0["tokens"] == r1["tokens"]
+    assert r0["tokens"] == tiny_golden["cuda"]["tokens"]
+    # the vocabulary shards, put side by side, are the oracle's logits within the stated bound
+    cfg = synth.TINY_QWEN3
+    ck = synth.dense_checkpoint(cfg)
+    dec = oracle_mod.Decoder(ck, cfg.prompt_tokens + steps + 1, mode=oracle_mod.MODE_CUDA)
+    _, ref = dec.decode_greedy(synth.prompt_ids(cfg), steps, want_logits=True)
+    got = np.concatenate([r0["logits"], r1["logits"]], axis=1)
+    assert r0["offset"] == 0 and r1["offset"] == cfg.vocab // 2
+    assert got.shape == ref.shape
+    assert float(np.abs(got - ref).max()) <= LOGIT_ATOL
