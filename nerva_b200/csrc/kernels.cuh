@@ -45,25 +45,28 @@ enum ProjectionEpilogue : uint32_t {
 };
 
 // ---- tensor-parallel exchange of a row-parallel projection (O, down) ----
-// Every rank holds a receive buffer [world][rows] f32 and arrival counters
-// [world] per phase.  The writer's epilogue stores its rows of the partial
-// result into slot `rank` of EVERY rank's buffer (plain peer stores over
-// NVLink), fences, and adds 1 per block to slot `rank` of every rank's counters.
-// The next kernel's prologue waits (bounded) until each counter has reached the
-// value this step implies, then adds the partials in rank order.  Counters only
-// grow: expected = *epoch * per_epoch + offset, where *epoch counts the steps
-// this session has completed (the same on every rank).
+// Every rank holds, per phase, a receive buffer of [world][rows] 8-byte entries:
+// the f32 value in the low word, a tag in the high word.  The writer's epilogue
+// stores each of its result rows, tagged, into slot `rank` of EVERY rank's
+// buffer with one 8-byte store per entry (plain peer stores over NVLink; an
+// 8-byte store is single-copy atomic, so a matching tag proves the value).  The
+// prologue of the next projection polls (bounded) the entries it needs until
+// their tags match, and adds the partials in rank order.  Tags only grow:
+// tag = *epoch * per_epoch + offset, where *epoch counts the steps this session
+// has completed (the same on every rank) and offset numbers the exchange inside
+// a step from 1.
 constexpr uint32_t kMaxTpWorld = 8;
 struct TpPush {
-  uint32_t world, rank;                       // world <= 1: off
-  float *recv[kMaxTpWorld];                   // rank q's receive buffer of this phase
-  unsigned long long *arrivals[kMaxTpWorld];  // rank q's arrival counters of this phase
+  uint32_t world, rank;                   // world <= 1: off
+  unsigned long long *recv[kMaxTpWorld];  // rank q's receive buffer of this phase
+  const unsigned long long *epoch;
+  uint32_t per_epoch, offset;
 };
 struct TpGather {
-  uint32_t world;                             // world <= 1: off
-  const unsigned long long *arrivals;         // local counters of the phase [world]
+  uint32_t world;                         // world <= 1: off
+  const unsigned long long *recv;         // this rank's receive buffer of the phase
   const unsigned long long *epoch;
-  unsigned long long per_epoch, offset;
+  uint32_t per_epoch, offset;
 };
 
 struct ProjectionParams {
@@ -86,7 +89,7 @@ struct ProjectionParams {
   uint32_t *error_word;
   uint32_t pdl;          // launch with programmatic dependent launch (see launch_with_pdl)
   unsigned long long *stamps;  // optional kTimelineSlots timeline stamps (common.cuh: stamp)
-  TpGather gather;  // kPrologueAddNorm: add_b is [world][cols], complete once the counters say so
+  TpGather gather;  // kPrologueAddNorm: add_b is the sum of the partials arriving in gather.recv
   TpPush push;      // kEpilogueStore: results go to every rank's receive buffer instead of out_f32
 };
 

@@ -65,19 +65,24 @@ __global__ void __launch_bounds__(kStreamThreads, 1) projection_stream_kernel(Pr
     uint4 *dst = reinterpret_cast<uint4 *>(x);
     for (uint32_t i = threadIdx.x; i < p.cols / 8u; i += blockDim.x) dst[i] = src[i];
   } else {
-    uint32_t partials = 1;
     if (p.gather.world > 1 && p.add_b != nullptr) {
-      // the partial sums of the other ranks arrive over NVLink
-      partials = p.gather.world;
-      if (threadIdx.x < partials) {
-        const unsigned long long expected = *p.gather.epoch * p.gather.per_epoch + p.gather.offset;
-        if (!wait_counter_bounded(p.gather.arrivals + threadIdx.x, expected))
-          report_error(p.error_word, kErrPeerWaitTimeout);
+      // the partial sums of the ranks arrive over NVLink while this polls
+      const uint32_t tag = static_cast<uint32_t>(*p.gather.epoch) * p.gather.per_epoch + p.gather.offset;
+      float *resid = blockIdx.x == 0 ? p.resid_out : nullptr;
+      if (p.gather.world == 2) {
+        gather_norm_to_smem<2>(x, p.add_a, p.gather.recv, tag, p.add_bias, p.norm_weight, p.eps, p.cols, resid,
+                               sh.scratch, p.error_word);
+      } else if (p.gather.world == 4) {
+        gather_norm_to_smem<4>(x, p.add_a, p.gather.recv, tag, p.add_bias, p.norm_weight, p.eps, p.cols, resid,
+                               sh.scratch, p.error_word);
+      } else {
+        gather_norm_to_smem<8>(x, p.add_a, p.gather.recv, tag, p.add_bias, p.norm_weight, p.eps, p.cols, resid,
+                               sh.scratch, p.error_word);
       }
-      __syncthreads();
+    } else {
+      add_norm_to_smem(x, p.add_a, p.add_b, p.add_bias, p.norm_weight, p.eps, p.cols,
+                       blockIdx.x == 0 ? p.resid_out : nullptr, sh.scratch);
     }
-    add_norm_to_smem(x, p.add_a, p.add_b, p.add_bias, p.norm_weight, p.eps, p.cols,
-                     blockIdx.x == 0 ? p.resid_out : nullptr, sh.scratch, partials);
   }
   __syncthreads();
   stamp(p.stamps, kStampAfterPrologue);
@@ -88,14 +93,16 @@ __global__ void __launch_bounds__(kStreamThreads, 1) projection_stream_kernel(Pr
   // Epilogue over the block's rows, coalesced.
   if (EPI == kEpilogueStore) {
     if (p.push.world > 1) {
+      const unsigned long long tag =
+          static_cast<unsigned long long>(static_cast<uint32_t>(*p.push.epoch) * p.push.per_epoch + p.push.offset) << 32;
       for (uint32_t r = threadIdx.x; r < rows_local; r += blockDim.x) {
         const float y = stream_row_total(sh.stream, row_total, r);
+        const unsigned long long entry = tag | __float_as_uint(y);
         const uint64_t at = static_cast<uint64_t>(p.push.rank) * p.rows + row_begin + r;
-        for (uint32_t q = 0; q < p.push.world; ++q) p.push.recv[q][at] = y;
+        for (uint32_t q = 0; q < p.push.world; ++q) {
+          asm volatile("st.volatile.global.u64 [%0], %1;" ::"l"(p.push.recv[q] + at), "l"(entry) : "memory");
+        }
       }
-      __threadfence_system();
-      __syncthreads();
-      if (threadIdx.x < p.push.world) atomicAdd_system(p.push.arrivals[threadIdx.x] + p.push.rank, 1ull);
     } else {
       for (uint32_t r = threadIdx.x; r < rows_local; r += blockDim.x) {
         p.out_f32[row_begin + r] = stream_row_total(sh.stream, row_total, r);
@@ -272,6 +279,9 @@ uint32_t projection_blocks(const ProjectionParams &p, uint32_t sm_count) {
 }
 
 cudaError_t launch_projection(cudaStream_t stream, const ProjectionParams &p, uint32_t sm_count) {
+  if (p.gather.world > 1 && (p.cols % 4u != 0 || p.cols / 4u > kNormRegIters * kStreamThreads ||
+                             (p.gather.world != 2 && p.gather.world != 4 && p.gather.world != 8)))
+    return cudaErrorNotSupported;
   if (stream_eligible(p, sm_count)) {
     const uint32_t blocks = blocks_for(p, sm_count);
     const uint32_t smem = stream_smem_bytes(p, blocks);

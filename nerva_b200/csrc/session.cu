@@ -258,7 +258,7 @@ bool plan_state(Session *s, StaticArena &arena, void *base) {
 // Exchange buffer of a tensor-parallel rank (its own allocation, shared with the
 // other ranks through an inter-process handle).  Offsets are the same on every rank.
 struct CommLayout {
-  uint64_t recv_o, recv_d, arrivals_o, arrivals_d, arrivals_s, candidates, epoch, bytes;
+  uint64_t recv_o, recv_d, arrivals_s, candidates, epoch, bytes;
 };
 CommLayout comm_layout(uint32_t world, uint32_t hidden) {
   CommLayout c{};
@@ -268,10 +268,8 @@ CommLayout comm_layout(uint32_t world, uint32_t hidden) {
     at = (at + bytes + 255u) & ~uint64_t{255};
     return begin;
   };
-  c.recv_o = take(static_cast<uint64_t>(world) * hidden * 4u);
-  c.recv_d = take(static_cast<uint64_t>(world) * hidden * 4u);
-  c.arrivals_o = take(world * 8u);
-  c.arrivals_d = take(world * 8u);
+  c.recv_o = take(static_cast<uint64_t>(world) * hidden * 8u);  // tagged 8-byte entries
+  c.recv_d = take(static_cast<uint64_t>(world) * hidden * 8u);
   c.arrivals_s = take(world * 8u);
   c.candidates = take(world * 8u);
   c.epoch = take(8u);
@@ -471,38 +469,25 @@ cudaError_t enqueue_step(Session *s, uint32_t splits, uint32_t sample, uint64_t 
   const bool tp = s->tp_world > 1;
   if (tp && (!s->tp_attached || s->engine != 0)) return cudaErrorNotReady;
   const CommLayout comm = comm_layout(s->tp_world, d.hidden);
-  auto push_to = [&](uint64_t recv, uint64_t arrivals) {
+  auto push_to = [&](uint64_t recv, uint32_t exchange) {
     TpPush push{};
     push.world = s->tp_world;
     push.rank = s->tp_rank;
-    for (uint32_t q = 0; q < s->tp_world; ++q) {
-      push.recv[q] = comm_at<float>(s->comm_peers[q], recv);
-      push.arrivals[q] = comm_at<unsigned long long>(s->comm_peers[q], arrivals);
-    }
+    for (uint32_t q = 0; q < s->tp_world; ++q) push.recv[q] = comm_at<unsigned long long>(s->comm_peers[q], recv);
+    push.epoch = comm_at<unsigned long long>(s->comm_block, comm.epoch);
+    push.per_epoch = d.layers;
+    push.offset = exchange;
     return push;
   };
-  auto gather_from = [&](uint64_t arrivals, uint64_t writer_blocks, uint64_t pushes_so_far) {
+  auto gather_from = [&](uint64_t recv, uint32_t exchange) {
     TpGather gather{};
     gather.world = s->tp_world;
-    gather.arrivals = comm_at<unsigned long long>(s->comm_block, arrivals);
+    gather.recv = comm_at<unsigned long long>(s->comm_block, recv);
     gather.epoch = comm_at<unsigned long long>(s->comm_block, comm.epoch);
-    gather.per_epoch = writer_blocks * d.layers;
-    gather.offset = writer_blocks * pushes_so_far;
+    gather.per_epoch = d.layers;
+    gather.offset = exchange;
     return gather;
   };
-  uint64_t o_blocks = 0, down_blocks = 0;
-  if (tp) {
-    ProjectionParams shape{};
-    shape.rows = d.hidden;
-    shape.cols = static_cast<uint32_t>(ah);
-    shape.weight = arena_at(s, s->layout.layers[0].w_o);
-    shape.x_bf16 = s->attn_bf16;
-    o_blocks = projection_blocks(shape, s->sm_count);
-    shape.cols = d.intermediate;
-    shape.weight = arena_at(s, s->layout.layers[0].w_down);
-    shape.x_bf16 = s->ff_bf16;
-    down_blocks = projection_blocks(shape, s->sm_count);
-  }
   auto stamps_for = [s](uint32_t node) -> unsigned long long * {
     return s->timeline_on && node < s->timeline_nodes ? s->timeline + node * kTimelineSlots : nullptr;
   };
@@ -529,8 +514,8 @@ cudaError_t enqueue_step(Session *s, uint32_t splits, uint32_t sample, uint64_t 
     p.add_a = s->h_b;
     p.add_b = l == 0 ? nullptr : s->down;
     if (tp && l != 0) {
-      p.add_b = comm_at<float>(s->comm_block, comm.recv_d);
-      p.gather = gather_from(comm.arrivals_d, down_blocks, l);
+      p.add_b = s->down;  // placeholder: the sum arrives in the exchange buffer
+      p.gather = gather_from(comm.recv_d, l);  // down of layer l-1 was exchange number l
     }
     p.norm_weight = arena_at(s, L.rms_attn);
     p.resid_out = s->h_a;
@@ -631,7 +616,7 @@ cudaError_t enqueue_step(Session *s, uint32_t splits, uint32_t sample, uint64_t 
     p.x_bf16 = s->attn_bf16;
     p.epilogue = kEpilogueStore;
     p.out_f32 = s->o_out;
-    if (tp) p.push = push_to(comm.recv_o, comm.arrivals_o);
+    if (tp) p.push = push_to(comm.recv_o, l + 1u);
     p.stamps = stamps_for(5u * l + 2u);
     err = launch_projection(s->stream, p, s->sm_count);
     n += 1;
@@ -651,8 +636,7 @@ cudaError_t enqueue_step(Session *s, uint32_t splits, uint32_t sample, uint64_t 
     p.add_a = s->h_a;
     p.add_b = s->o_out;
     if (tp) {
-      p.add_b = comm_at<float>(s->comm_block, comm.recv_o);
-      p.gather = gather_from(comm.arrivals_o, o_blocks, l + 1u);
+      p.gather = gather_from(comm.recv_o, l + 1u);
     }
     p.add_bias = arena_at(s, L.o_bias);
     p.norm_weight = arena_at(s, L.rms_mlp);
@@ -677,7 +661,7 @@ cudaError_t enqueue_step(Session *s, uint32_t splits, uint32_t sample, uint64_t 
     p.x_bf16 = s->ff_bf16;
     p.epilogue = kEpilogueStore;
     p.out_f32 = s->down;
-    if (tp) p.push = push_to(comm.recv_d, comm.arrivals_d);
+    if (tp) p.push = push_to(comm.recv_d, l + 1u);
     p.stamps = stamps_for(5u * l + 4u);
     err = launch_projection(s->stream, p, s->sm_count);
     n += 1;
@@ -697,8 +681,7 @@ cudaError_t enqueue_step(Session *s, uint32_t splits, uint32_t sample, uint64_t 
     p.add_a = s->h_b;
     p.add_b = s->down;
     if (tp) {
-      p.add_b = comm_at<float>(s->comm_block, comm.recv_d);
-      p.gather = gather_from(comm.arrivals_d, down_blocks, d.layers);
+      p.gather = gather_from(comm.recv_d, d.layers);
     }
     p.norm_weight = arena_at(s, s->layout.final_norm);
     p.resid_out = s->h_a;
@@ -1251,7 +1234,7 @@ static int create_session(const NervaCudaHfDecodeSequenceSessionCreateRequest *r
   if (shard != nullptr) {
     // A tensor-parallel rank: the request describes this rank's shard (local heads,
     // KV heads, intermediate size and lm_head rows); the embedding table is whole.
-    if (shard->world < 2 || shard->world > kMaxTpWorld || shard->rank >= shard->world ||
+    if ((shard->world != 2 && shard->world != 4 && shard->world != 8) || shard->rank >= shard->world ||
         shard->full_vocab < request->vocab_size ||
         static_cast<uint64_t>(shard->vocab_offset) + request->vocab_size > shard->full_vocab ||
         request->planned_weight_blocks != 0) {

@@ -19,14 +19,9 @@ namespace nb {
 // prologue is one round trip to L2.
 constexpr uint32_t kNormRegIters = 8;  // float4 per thread held in registers
 
-//
-// b_count > 1 (tensor parallel): b holds b_count partial vectors of `cols`
-// floats, one per rank; they are added in rank order, so every rank computes
-// the same r bit for bit.
 __device__ __forceinline__ void add_norm_to_smem(uint16_t *x, const float *a, const float *b,
                                                  const uint16_t *bias, const uint16_t *w, float eps,
-                                                 uint32_t cols, float *resid_out, float *scratch,
-                                                 uint32_t b_count = 1) {
+                                                 uint32_t cols, float *resid_out, float *scratch) {
   const uint32_t vecs = cols / 4u;
   const bool fast = cols % 4u == 0 && bias == nullptr && vecs <= kNormRegIters * blockDim.x &&
                     (reinterpret_cast<uintptr_t>(a) & 15u) == 0 &&
@@ -44,14 +39,7 @@ __device__ __forceinline__ void add_norm_to_smem(uint16_t *x, const float *a, co
         // L2 loads: in the whole-step kernel these vectors were written by other blocks
         float4 v = __ldcg(reinterpret_cast<const float4 *>(a) + i);
         if (b != nullptr) {
-          float4 t = __ldcg(reinterpret_cast<const float4 *>(b) + i);
-          for (uint32_t q = 1; q < b_count; ++q) {
-            const float4 u = __ldcg(reinterpret_cast<const float4 *>(b + static_cast<uint64_t>(q) * cols) + i);
-            t.x += u.x;
-            t.y += u.y;
-            t.z += u.z;
-            t.w += u.w;
-          }
+          const float4 t = __ldcg(reinterpret_cast<const float4 *>(b) + i);
           v.x = t.x + v.x;
           v.y = t.y + v.y;
           v.z = t.z + v.z;
@@ -81,14 +69,9 @@ __device__ __forceinline__ void add_norm_to_smem(uint16_t *x, const float *a, co
     }
     return;
   }
-  auto b_sum = [&](uint32_t i) {
-    float t = __ldcg(b + i);
-    for (uint32_t q = 1; q < b_count; ++q) t += __ldcg(b + static_cast<uint64_t>(q) * cols + i);
-    return t;
-  };
   float sumsq = 0.0f;
   for (uint32_t i = threadIdx.x; i < cols; i += blockDim.x) {
-    float r = b != nullptr ? b_sum(i) : __ldcg(a + i);
+    float r = b != nullptr ? __ldcg(b + i) : __ldcg(a + i);
     if (bias != nullptr) r += bf16_bits_to_f32(bias[i]);
     if (b != nullptr) r += __ldcg(a + i);
     sumsq += r * r;
@@ -96,11 +79,149 @@ __device__ __forceinline__ void add_norm_to_smem(uint16_t *x, const float *a, co
   const float total = block_sum(sumsq, scratch);
   const float scale = rsqrtf(total / static_cast<float>(cols) + eps);
   for (uint32_t i = threadIdx.x; i < cols; i += blockDim.x) {
-    float r = b != nullptr ? b_sum(i) : __ldcg(a + i);
+    float r = b != nullptr ? __ldcg(b + i) : __ldcg(a + i);
     if (bias != nullptr) r += bf16_bits_to_f32(bias[i]);
     if (b != nullptr) r += __ldcg(a + i);
     if (resid_out != nullptr) resid_out[i] = r;
     x[i] = f32_to_bf16_bits(r * scale * bf16_bits_to_f32(w[i]));
+  }
+}
+
+// Tensor-parallel form of the same prologue: `b` is the sum over the ranks of
+// partial vectors that arrive from the other GPUs while this runs.  recv holds
+// [world][cols] 8-byte entries, value bits in the low word and a tag in the high
+// word; a writer stores an entry with ONE 8-byte store, so an entry whose tag is
+// the expected one carries its value (no fence, no separate flag).  Each thread
+// polls exactly the entries it needs (bounded; on expiry the error word is set
+// and the step fails) and adds the partials in rank order, so every rank
+// computes the same r bit for bit.  cols % 4 == 0 and cols <= 4 * kNormRegIters *
+// blockDim.x.
+constexpr uint32_t kMaxGatherWorld = 8;
+
+__device__ __forceinline__ ulonglong2 ld_volatile_16(const ulonglong2 *p) {
+  ulonglong2 v;
+  asm volatile("ld.volatile.global.v2.u64 {%0, %1}, [%2];" : "=l"(v.x), "=l"(v.y) : "l"(p) : "memory");
+  return v;
+}
+
+// WORLD is the number of ranks (compile time, so that the entries in flight live
+// in registers); a thread keeps BATCH of its float4 groups from all ranks in
+// flight at once, so the whole gather is one or two round trips to L2 once the
+// data has arrived.
+template <uint32_t WORLD>
+__device__ __forceinline__ void gather_norm_to_smem(uint16_t *x, const float *a,
+                                                    const unsigned long long *recv, uint32_t tag,
+                                                    const uint16_t *bias, const uint16_t *w, float eps,
+                                                    uint32_t cols, float *resid_out, float *scratch,
+                                                    uint32_t *error_word) {
+  constexpr uint32_t BATCH = WORLD <= 4 ? 4 : 2;
+  static_assert(kNormRegIters % BATCH == 0, "batches tile the register-resident groups");
+  const uint32_t vecs = cols / 4u;
+  float4 r[kNormRegIters];
+  uint2 wk[kNormRegIters];
+  float sumsq = 0.0f;
+  const long long start = clock64();
+  bool gave_up = false;
+#pragma unroll
+  for (uint32_t k0 = 0; k0 < kNormRegIters; k0 += BATCH) {
+    if (k0 * blockDim.x >= vecs) break;
+    float4 av[BATCH];
+#pragma unroll
+    for (uint32_t kb = 0; kb < BATCH; ++kb) {
+      const uint32_t i = threadIdx.x + (k0 + kb) * blockDim.x;
+      if (i < vecs) {
+        av[kb] = __ldcg(reinterpret_cast<const float4 *>(a) + i);
+        wk[k0 + kb] = reinterpret_cast<const uint2 *>(w)[i];
+      }
+    }
+    ulonglong2 lo[BATCH][WORLD], hi[BATCH][WORLD];
+    uint32_t polls = 0;
+    for (;;) {
+#pragma unroll
+      for (uint32_t kb = 0; kb < BATCH; ++kb) {
+        const uint32_t i = threadIdx.x + (k0 + kb) * blockDim.x;
+        if (i < vecs) {
+#pragma unroll
+          for (uint32_t q = 0; q < WORLD; ++q) {
+            const ulonglong2 *src =
+                reinterpret_cast<const ulonglong2 *>(recv + static_cast<uint64_t>(q) * cols + 4u * i);
+            lo[kb][q] = ld_volatile_16(src);
+            hi[kb][q] = ld_volatile_16(src + 1);
+          }
+        }
+      }
+      bool ok = true;
+#pragma unroll
+      for (uint32_t kb = 0; kb < BATCH; ++kb) {
+        const uint32_t i = threadIdx.x + (k0 + kb) * blockDim.x;
+        if (i < vecs) {
+#pragma unroll
+          for (uint32_t q = 0; q < WORLD; ++q) {
+            ok = ok && static_cast<uint32_t>(lo[kb][q].x >> 32) == tag &&
+                 static_cast<uint32_t>(lo[kb][q].y >> 32) == tag &&
+                 static_cast<uint32_t>(hi[kb][q].x >> 32) == tag &&
+                 static_cast<uint32_t>(hi[kb][q].y >> 32) == tag;
+          }
+        }
+      }
+      if (ok || gave_up) break;
+      if ((++polls & 63u) == 0 && clock64() - start > 4 * kWaitCycleLimit) {
+        gave_up = true;
+        report_error(error_word, kErrPeerWaitTimeout);
+      }
+    }
+#pragma unroll
+    for (uint32_t kb = 0; kb < BATCH; ++kb) {
+      const uint32_t i = threadIdx.x + (k0 + kb) * blockDim.x;
+      if (i < vecs) {
+        float4 t = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+#pragma unroll
+        for (uint32_t q = 0; q < WORLD; ++q) {
+          const float4 u = make_float4(__uint_as_float(static_cast<uint32_t>(lo[kb][q].x)),
+                                       __uint_as_float(static_cast<uint32_t>(lo[kb][q].y)),
+                                       __uint_as_float(static_cast<uint32_t>(hi[kb][q].x)),
+                                       __uint_as_float(static_cast<uint32_t>(hi[kb][q].y)));
+          if (q == 0) {
+            t = u;
+          } else {
+            t.x += u.x;
+            t.y += u.y;
+            t.z += u.z;
+            t.w += u.w;
+          }
+        }
+        if (bias != nullptr) {
+          t.x += bf16_bits_to_f32(bias[4u * i]);
+          t.y += bf16_bits_to_f32(bias[4u * i + 1u]);
+          t.z += bf16_bits_to_f32(bias[4u * i + 2u]);
+          t.w += bf16_bits_to_f32(bias[4u * i + 3u]);
+        }
+        float4 v = av[kb];
+        v.x = t.x + v.x;
+        v.y = t.y + v.y;
+        v.z = t.z + v.z;
+        v.w = t.w + v.w;
+        r[k0 + kb] = v;
+        sumsq += v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w;
+      }
+    }
+  }
+  const float total = block_sum(sumsq, scratch);
+  const float scale = rsqrtf(total / static_cast<float>(cols) + eps);
+#pragma unroll
+  for (uint32_t k = 0; k < kNormRegIters; ++k) {
+    const uint32_t i = threadIdx.x + k * blockDim.x;
+    if (i < vecs) {
+      const float4 v = r[k];
+      if (resid_out != nullptr) reinterpret_cast<float4 *>(resid_out)[i] = v;
+      const uint2 wb = wk[k];
+      uint2 out;
+      out.x = static_cast<uint32_t>(f32_to_bf16_bits(v.x * scale * bf16x2_lo(wb.x))) |
+              (static_cast<uint32_t>(f32_to_bf16_bits(v.y * scale * bf16x2_hi(wb.x))) << 16);
+      out.y = static_cast<uint32_t>(f32_to_bf16_bits(v.z * scale * bf16x2_lo(wb.y))) |
+              (static_cast<uint32_t>(f32_to_bf16_bits(v.w * scale * bf16x2_hi(wb.y))) << 16);
+      reinterpret_cast<uint2 *>(x)[i] = out;
+    }
   }
 }
 
