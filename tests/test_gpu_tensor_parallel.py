@@ -32,7 +32,21 @@ def _free_port() -> int:
         return s.getsockname()[1]
 
 
-def _rank_main(rank: int, world: int, port: int, steps: int, results) -> None:
+def _wide_config():
+    """Qwen3-8B layer shapes (32 query / 8 KV heads of 128, hidden 4096, intermediate 12288) cut to two
+    layers and a small vocabulary, so that it splits 2, 4 and 8 ways and the oracle stays quick."""
+    import dataclasses
+    from nerva_b200 import synth
+    return dataclasses.replace(synth.QWEN3_8B, name="qwen3-8b-shape-2-layers", layers=2, vocab=8192,
+                               prompt_tokens=24, decode_tokens=8)
+
+
+def _config(kind: str):
+    from nerva_b200 import synth
+    return synth.TINY_QWEN3 if kind == "tiny" else _wide_config()
+
+
+def _rank_main(rank: int, world: int, port: int, steps: int, kind: str, results) -> None:
     sys.path.insert(0, ROOT)
     os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), RANK=str(rank), WORLD_SIZE=str(world))
     import torch.distributed as dist
@@ -42,7 +56,7 @@ def _rank_main(rank: int, world: int, port: int, steps: int, results) -> None:
     import datetime
     dist.init_process_group("gloo", rank=rank, world_size=world, timeout=datetime.timedelta(seconds=180))
     try:
-        cfg = synth.TINY_QWEN3
+        cfg = _config(kind)
         full = synth.dense_checkpoint(cfg, fill=ops.synth_normal_bf16)
         session = tp.create_session(cfg, cfg.prompt_tokens + steps + 1, rank, world, full_checkpoint=full)
         # the directly generated shard has the same bits as the slice of the full model
@@ -67,15 +81,12 @@ def _rank_main(rank: int, world: int, port: int, steps: int, results) -> None:
         dist.destroy_process_group()
 
 
-@pytest.mark.skipif(_gpu_count() < 2, reason="needs two GPUs")
-def test_two_rank_tensor_parallel_matches_oracle(built_lib, oracle_mod, tiny_golden):
+def _run_ranks(world: int, steps: int, kind: str):
     import torch.multiprocessing as mp
-    from nerva_b200 import synth
-    world, steps = 2, 32
     ctx = mp.get_context("spawn")
     results = ctx.Manager().dict()
     port = _free_port()
-    procs = [ctx.Process(target=_rank_main, args=(r, world, port, steps, results)) for r in range(world)]
+    procs = [ctx.Process(target=_rank_main, args=(r, world, port, steps, kind, results)) for r in range(world)]
     for p in procs:
         p.start()
     try:
@@ -86,7 +97,14 @@ def test_two_rank_tensor_parallel_matches_oracle(built_lib, oracle_mod, tiny_gol
         for p in procs:
             if p.is_alive():
                 p.terminate()
-    r0, r1 = results[0], results[1]
+    return [results[r] for r in range(world)]
+
+
+@pytest.mark.skipif(_gpu_count() < 2, reason="needs two GPUs")
+def test_two_rank_tensor_parallel_matches_oracle(built_lib, oracle_mod, tiny_golden):
+    from nerva_b200 import synth
+    world, steps = 2, 32
+    r0, r1 = _run_ranks(world, steps, "tiny")
     assert r0["shards_equal"] and r1["shards_equal"]
     # every rank writes the same token stream, and it is the oracle's
     assert r0["tokens"] == r1["tokens"]
@@ -100,3 +118,31 @@ def test_two_rank_tensor_parallel_matches_oracle(built_lib, oracle_mod, tiny_gol
     assert r0["offset"] == 0 and r1["offset"] == cfg.vocab // 2
     assert got.shape == ref.shape
     assert float(np.abs(got - ref).max()) <= LOGIT_ATOL
+
+
+@pytest.mark.parametrize("world", [2, 4, 8])
+def test_tensor_parallel_on_qwen3_8b_layer_shapes(built_lib, oracle_mod, world):
+    """Every rank count the head counts allow: same tokens on every rank, the oracle's tokens, and
+    logits within max(2e-2, twice the oracle's own distance to itself under another fp32
+    summation order) on the 4096-wide, two-layer model."""
+    if _gpu_count() < world:
+        pytest.skip(f"needs {world} GPUs")
+    from nerva_b200 import synth
+    from tests.conftest import contract_self_distance
+    cfg = _wide_config()
+    steps = cfg.decode_tokens
+    ranks = _run_ranks(world, steps, "wide")
+    assert all(r["shards_equal"] for r in ranks)
+    assert all(r["tokens"] == ranks[0]["tokens"] for r in ranks)
+    ck = synth.dense_checkpoint(cfg, fill=__import__("nerva_b200.ops", fromlist=["ops"]).synth_normal_bf16)
+    prompt = synth.prompt_ids(cfg)
+    dec = oracle_mod.Decoder(ck, cfg.prompt_tokens + steps + 1, mode=oracle_mod.MODE_CUDA)
+    ref_tokens, ref = dec.decode_greedy(prompt, steps, want_logits=True)
+    got = np.concatenate([r["logits"] for r in ranks], axis=1)
+    assert [r["offset"] for r in ranks] == [q * (cfg.vocab // world) for q in range(world)]
+    floor = contract_self_distance(oracle_mod, ck, cfg.prompt_tokens + steps + 1, prompt, steps, ref)
+    bound = max(LOGIT_ATOL, 2.0 * floor)
+    worst = float(np.abs(got - ref).max())
+    assert worst <= bound, (worst, bound)
+    if worst <= LOGIT_ATOL / 4:  # far from any tie: the token streams must agree as well
+        assert ranks[0]["tokens"] == ref_tokens.tolist()
