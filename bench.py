@@ -176,6 +176,8 @@ def run_ours(args, cfg, rank: int, world: int) -> dict:
     from nerva_b200 import build, ops, synth
     from nerva_b200.session import CudaHfDecodeSequenceLoop, CudaHfDecodeSequenceSession, SmokeStatus
     build.build()
+    if args.timeline:
+        os.environ["NERVA_B200_TIMELINE"] = "1"  # read when the session is created
     t0 = time.perf_counter()
     if world > 1:
         # tensor parallel: this rank generates and holds only its slices of the model
@@ -186,7 +188,8 @@ def run_ours(args, cfg, rank: int, world: int) -> dict:
     gen_s = time.perf_counter() - t0
     prompt = synth.prompt_ids(cfg)
     profile_steps = 4
-    max_context = cfg.prompt_tokens + 1 + args.warmup + 2 * args.steps + profile_steps + 8
+    timeline_steps = 10 if args.timeline else 0
+    max_context = cfg.prompt_tokens + 1 + args.warmup + 2 * args.steps + profile_steps + timeline_steps + 8
     t0 = time.perf_counter()
     session = CudaHfDecodeSequenceSession(ck, max_context, engine=args.engine)
     if session.status != SmokeStatus.OK:
@@ -222,6 +225,22 @@ def run_ours(args, cfg, rank: int, world: int) -> dict:
         e2e_tokens += len(out.tokens)
     e2e_s = time.perf_counter() - t0
     clock_info = clocks.stop()
+    timeline = None
+    if args.timeline:
+        # %globaltimer stamps written by the kernels themselves during ordinary graph replays
+        acc = None
+        for _ in range(timeline_steps):
+            loop.advance(1)
+            t = session.read_timeline().astype(np.int64)[:5 * cfg.layers].reshape(cfg.layers, 5, 8)
+            rel = (t - t[:, 0, 0][:, None, None]).astype(np.float64)
+            acc = rel if acc is None else acc + rel
+            period = float((t[1:, 0, 0] - t[:-1, 0, 0]).mean()) / 1e3
+        mean = (acc / timeline_steps)[1:-1].mean(axis=0) / 1e3 if cfg.layers > 2 else (acc / timeline_steps).mean(axis=0) / 1e3
+        cols = ["entry", "after_wait", "after_prologue", "exit", "last_entry", "last_after_wait", "last_after_prologue",
+                "last_exit"]
+        timeline = {"layer_period_us": period, "columns": cols,
+                    "us_since_qkv_entry": {name: [round(float(v), 2) for v in mean[i]]
+                                           for i, name in enumerate(("qkv", "attention", "o", "gate_up", "down"))}}
     # per-kernel pass: events between launch groups, un-captured
     prof = session.profile_steps(profile_steps)
     session.destroy()
@@ -273,6 +292,8 @@ def run_ours(args, cfg, rank: int, world: int) -> dict:
         "graph_nodes": int(timed.graph_nodes),
         "token_hash": f"{timed.observed_token_hash:016x}",
     }
+    if timeline is not None:
+        result["timeline"] = timeline
     if rank == 0 and world == 1 and not args.no_cpu_baseline:
         rate, done, threads = cpu_decode_sample(ck, cfg, budget_s=float(os.environ.get("NERVA_CPU_BUDGET_S", "20")),
                                                 max_tokens=8)
@@ -313,6 +334,8 @@ def main() -> None:
     ap.add_argument("--layers", type=int, default=0,
                     help="cut the model to this many layers (profiler captures only; not a bench line)")
     ap.add_argument("--prompt-tokens", type=int, default=0, help="override the prompt length")
+    ap.add_argument("--timeline", action="store_true",
+                    help="add the in-graph timeline (kernel-written %%globaltimer stamps, mean over layers)")
     args = ap.parse_args()
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))

@@ -33,7 +33,9 @@ __host__ __device__ inline uint32_t round128(uint32_t v) { return (v + 127u) & ~
 
 // Shared memory map (dynamic): weight ring | activation vector (bf16) |
 // ProjectionShared | row totals (one float per row of the block).
-template <uint32_t EPI>
+// TP = true adds the tensor-parallel exchange (gather in the AddNorm prologue, push in the
+// Store epilogue); the single-GPU instantiations carry none of that code.
+template <uint32_t EPI, bool TP>
 __global__ void __launch_bounds__(kStreamThreads, 1) projection_stream_kernel(ProjectionParams p) {
   extern __shared__ __align__(128) uint8_t smem[];
   uint8_t *ring = smem;
@@ -65,7 +67,7 @@ __global__ void __launch_bounds__(kStreamThreads, 1) projection_stream_kernel(Pr
     uint4 *dst = reinterpret_cast<uint4 *>(x);
     for (uint32_t i = threadIdx.x; i < p.cols / 8u; i += blockDim.x) dst[i] = src[i];
   } else {
-    if (p.gather.world > 1 && p.add_b != nullptr) {
+    if (TP && p.gather.world > 1 && p.add_b != nullptr) {
       // the partial sums of the ranks arrive over NVLink while this polls
       const uint32_t tag = static_cast<uint32_t>(*p.gather.epoch) * p.gather.per_epoch + p.gather.offset;
       float *resid = blockIdx.x == 0 ? p.resid_out : nullptr;
@@ -92,7 +94,7 @@ __global__ void __launch_bounds__(kStreamThreads, 1) projection_stream_kernel(Pr
 
   // Epilogue over the block's rows, coalesced.
   if (EPI == kEpilogueStore) {
-    if (p.push.world > 1) {
+    if (TP && p.push.world > 1) {
       const unsigned long long tag =
           static_cast<unsigned long long>(static_cast<uint32_t>(*p.push.epoch) * p.push.per_epoch + p.push.offset) << 32;
       for (uint32_t r = threadIdx.x; r < rows_local; r += blockDim.x) {
@@ -263,14 +265,17 @@ bool stream_eligible(const ProjectionParams &p, uint32_t sm_count) {
 
 cudaError_t configure_projection_kernels() {
   const int max_smem = 227 * 1024;
-  cudaError_t err = cudaFuncSetAttribute(projection_stream_kernel<kEpilogueStore>,
-                                         cudaFuncAttributeMaxDynamicSharedMemorySize, max_smem);
-  if (err == cudaSuccess)
-    err = cudaFuncSetAttribute(projection_stream_kernel<kEpilogueSwiglu>,
-                               cudaFuncAttributeMaxDynamicSharedMemorySize, max_smem);
-  if (err == cudaSuccess)
-    err = cudaFuncSetAttribute(projection_stream_kernel<kEpilogueArgmax>,
-                               cudaFuncAttributeMaxDynamicSharedMemorySize, max_smem);
+  cudaError_t err = cudaSuccess;
+  auto set = [&](void (*kernel)(ProjectionParams)) {
+    if (err == cudaSuccess)
+      err = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, max_smem);
+  };
+  set(projection_stream_kernel<kEpilogueStore, false>);
+  set(projection_stream_kernel<kEpilogueSwiglu, false>);
+  set(projection_stream_kernel<kEpilogueArgmax, false>);
+  set(projection_stream_kernel<kEpilogueStore, true>);
+  set(projection_stream_kernel<kEpilogueSwiglu, true>);
+  set(projection_stream_kernel<kEpilogueArgmax, true>);
   return err;
 }
 
@@ -286,16 +291,16 @@ cudaError_t launch_projection(cudaStream_t stream, const ProjectionParams &p, ui
     const uint32_t blocks = blocks_for(p, sm_count);
     const uint32_t smem = stream_smem_bytes(p, blocks);
     const bool pdl = p.pdl != 0;
+    const bool tp = p.push.world > 1 || p.gather.world > 1;
+    void (*kernel)(ProjectionParams) = nullptr;
     if (p.epilogue == kEpilogueStore) {
-      return launch_with_pdl(projection_stream_kernel<kEpilogueStore>, dim3(blocks), dim3(kStreamThreads),
-                             smem, stream, pdl, p);
+      kernel = tp ? projection_stream_kernel<kEpilogueStore, true> : projection_stream_kernel<kEpilogueStore, false>;
+    } else if (p.epilogue == kEpilogueSwiglu) {
+      kernel = tp ? projection_stream_kernel<kEpilogueSwiglu, true> : projection_stream_kernel<kEpilogueSwiglu, false>;
+    } else {
+      kernel = tp ? projection_stream_kernel<kEpilogueArgmax, true> : projection_stream_kernel<kEpilogueArgmax, false>;
     }
-    if (p.epilogue == kEpilogueSwiglu) {
-      return launch_with_pdl(projection_stream_kernel<kEpilogueSwiglu>, dim3(blocks), dim3(kStreamThreads),
-                             smem, stream, pdl, p);
-    }
-    return launch_with_pdl(projection_stream_kernel<kEpilogueArgmax>, dim3(blocks), dim3(kStreamThreads),
-                           smem, stream, pdl, p);
+    return launch_with_pdl(kernel, dim3(blocks), dim3(kStreamThreads), smem, stream, pdl, p);
   }
   if (p.push.world > 1 || p.gather.world > 1) return cudaErrorNotSupported;  // exchange: streaming path only
   // Toy-shape path.  With a fused prologue the caller passes `cols` writable
