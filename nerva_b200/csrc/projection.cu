@@ -33,6 +33,23 @@ __host__ __device__ inline uint32_t round128(uint32_t v) { return (v + 127u) & ~
 
 // Shared memory map (dynamic): weight ring | activation vector (bf16) |
 // ProjectionShared | row totals (one float per row of the block).
+// The gather of the tensor-parallel prologue, out of line: its register-resident
+// batches must not shape the register allocation of the streaming loop.
+__device__ __noinline__ void gather_prologue(const ProjectionParams &p, uint16_t *x, float *scratch) {
+  const uint32_t tag = static_cast<uint32_t>(*p.gather.epoch) * p.gather.per_epoch + p.gather.offset;
+  float *resid = blockIdx.x == 0 ? p.resid_out : nullptr;
+  if (p.gather.world == 2) {
+    gather_norm_to_smem<2>(x, p.add_a, p.gather.recv, tag, p.add_bias, p.norm_weight, p.eps, p.cols, resid,
+                           scratch, p.error_word);
+  } else if (p.gather.world == 4) {
+    gather_norm_to_smem<4>(x, p.add_a, p.gather.recv, tag, p.add_bias, p.norm_weight, p.eps, p.cols, resid,
+                           scratch, p.error_word);
+  } else {
+    gather_norm_to_smem<8>(x, p.add_a, p.gather.recv, tag, p.add_bias, p.norm_weight, p.eps, p.cols, resid,
+                           scratch, p.error_word);
+  }
+}
+
 // TP = true adds the tensor-parallel exchange (gather in the AddNorm prologue, push in the
 // Store epilogue); the single-GPU instantiations carry none of that code.
 template <uint32_t EPI, bool TP>
@@ -69,18 +86,7 @@ __global__ void __launch_bounds__(kStreamThreads, 1) projection_stream_kernel(Pr
   } else {
     if (TP && p.gather.world > 1 && p.add_b != nullptr) {
       // the partial sums of the ranks arrive over NVLink while this polls
-      const uint32_t tag = static_cast<uint32_t>(*p.gather.epoch) * p.gather.per_epoch + p.gather.offset;
-      float *resid = blockIdx.x == 0 ? p.resid_out : nullptr;
-      if (p.gather.world == 2) {
-        gather_norm_to_smem<2>(x, p.add_a, p.gather.recv, tag, p.add_bias, p.norm_weight, p.eps, p.cols, resid,
-                               sh.scratch, p.error_word);
-      } else if (p.gather.world == 4) {
-        gather_norm_to_smem<4>(x, p.add_a, p.gather.recv, tag, p.add_bias, p.norm_weight, p.eps, p.cols, resid,
-                               sh.scratch, p.error_word);
-      } else {
-        gather_norm_to_smem<8>(x, p.add_a, p.gather.recv, tag, p.add_bias, p.norm_weight, p.eps, p.cols, resid,
-                               sh.scratch, p.error_word);
-      }
+      gather_prologue(p, x, sh.scratch);
     } else {
       add_norm_to_smem(x, p.add_a, p.add_b, p.add_bias, p.norm_weight, p.eps, p.cols,
                        blockIdx.x == 0 ? p.resid_out : nullptr, sh.scratch);
