@@ -34,6 +34,10 @@ if ROOT not in sys.path:
 import numpy as np  # noqa: E402
 
 METRIC = "Qwen3-8B-arch BF16 batch-1 decode tok/s"
+# DRAM bytes (read + write) of the projection kernel's launches of one Qwen3-8B token, from the ncu
+# capture summarised in profiles/projection_stream_kernel_qwen3_8b_shapes.md:
+# 36 x (QKV 50.45 + O 33.65 + gate/up 204.97 + down 103.99 MB) + lm_head 1248.52 MB.
+NCU_PROJECTION_TRAFFIC_PER_TOKEN = 36 * (50.45e6 + 33.65e6 + 204.97e6 + 103.99e6) + 1248.52e6
 UNIT = "tok/s"
 
 
@@ -282,7 +286,9 @@ def run_ours(args, cfg, rank: int, world: int) -> dict:
         "roofline": {
             "bound": "hbm", "kernel": kernel_name,
             "achieved": achieved, "peak": peaks["hbm_gbs"], "unit": "GB/s", "frac": achieved / peaks["hbm_gbs"],
-            "peak_source": peaks["source"], "traffic": None,
+            "peak_source": peaks["source"],
+            "traffic": NCU_PROJECTION_TRAFFIC_PER_TOKEN if (world == 1 and cfg.name == "qwen3-8b") else None,
+            "traffic_unit": "DRAM bytes per token over the same launches as bytes_per_token (ncu, see profiles/)",
             "launches_per_token": proj_launches, "bytes_per_token": bytes_per_token,
             "us_per_token": kernel_us, "engine": args.engine,
             "whole_step_frac": (bytes_per_token * args.steps / device_s / 1e9) / peaks["hbm_gbs"],

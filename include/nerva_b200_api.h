@@ -601,6 +601,50 @@ int nerva_cuda_hf_decode_sequence_u16(const NervaCudaHfDecodeSequenceRequest *re
 int nerva_cuda_projection_bench(const NervaCudaProjectionBenchRequest *request,
                                 NervaCudaProjectionBenchResult *out);
 
+/* nerva_cuda_api.h:1480-1495 — DeepSeek expert routing of one token.  router_kind: 1 = V3
+ * grouped sigmoid, 2 = V4 sqrt-softplus, 3 = V4 hash table.  Host pointers. */
+typedef struct NervaCudaDeepSeekRouterRouteRequest {
+  uint32_t router_kind;
+  uint32_t num_experts;
+  uint32_t num_groups;
+  uint32_t top_k_groups;
+  uint32_t top_k;
+  uint32_t norm_topk_prob;
+  uint32_t route_token;
+  float routed_scaling_factor;
+  const float *logits;
+  const float *correction_bias;
+  const uint32_t *hash_route_table;
+  uint32_t hash_route_table_len;
+  uint32_t *expert_ids;
+  float *weights;
+} NervaCudaDeepSeekRouterRouteRequest;
+
+/* nerva_cuda_api.h:1497-1515 */
+typedef struct NervaCudaDeepSeekRouterRouteResult {
+  int32_t status;
+  int32_t cuda_error;
+  int32_t device_count;
+  int32_t route_error;
+  uint32_t router_kind;
+  uint32_t num_experts;
+  uint32_t num_groups;
+  uint32_t top_k_groups;
+  uint32_t top_k;
+  uint64_t output_hash;
+  uint64_t device_arena_bytes;
+  uint64_t pinned_host_bytes;
+  uint64_t h2d_bytes;
+  uint64_t d2h_bytes;
+  uint64_t kernel_launches;
+  uint64_t sync_calls;
+  uint64_t hot_path_allocations;
+} NervaCudaDeepSeekRouterRouteResult;
+
+/* nerva_cuda_api.h:2258 */
+int nerva_cuda_deepseek_router_route(const NervaCudaDeepSeekRouterRouteRequest *request,
+                                     NervaCudaDeepSeekRouterRouteResult *out);
+
 /* ---- additive entry points (no counterpart in the reference) ---- */
 
 /* Step engine of a session: 0 = one kernel per operator captured in a CUDA

@@ -72,6 +72,31 @@ def projection_bench(rows: int, cols: int, iterations: int = 20, warmup: int = 5
     return rc, out
 
 
+ROUTER_V3_GROUPED_SIGMOID, ROUTER_V4_SQRTSOFTPLUS, ROUTER_V4_HASH = 1, 2, 3
+
+
+def deepseek_router_route(kind: int, logits, top_k: int, bias=None, num_groups: int = 0, top_k_groups: int = 0,
+                          norm_topk_prob: bool = True, routed_scaling_factor: float = 1.0, hash_route_table=None,
+                          route_token: int = 0):
+    """Expert ids and weights of one token (reference: deepseek_router_route_* of
+    crates/nerva-cuda/src/deepseek/router.rs).  Returns (return code, ids, weights, result struct)."""
+    logits = np.ascontiguousarray(logits, dtype=np.float32)
+    bias_arr = None if bias is None else np.ascontiguousarray(bias, dtype=np.float32)
+    table = None if hash_route_table is None else np.ascontiguousarray(hash_route_table, dtype=np.uint32)
+    ids = np.zeros(top_k, dtype=np.uint32)
+    weights = np.zeros(top_k, dtype=np.float32)
+    req = ffi.structs["NervaCudaDeepSeekRouterRouteRequest"](
+        router_kind=kind, num_experts=logits.size, num_groups=num_groups, top_k_groups=top_k_groups, top_k=top_k,
+        norm_topk_prob=int(norm_topk_prob), route_token=route_token, routed_scaling_factor=routed_scaling_factor,
+        logits=logits.ctypes.data, correction_bias=None if bias_arr is None else bias_arr.ctypes.data,
+        hash_route_table=None if table is None else table.ctypes.data,
+        hash_route_table_len=0 if table is None else table.size, expert_ids=ids.ctypes.data,
+        weights=weights.ctypes.data)
+    out = ffi.structs["NervaCudaDeepSeekRouterRouteResult"]()
+    rc = ffi.lib().nerva_cuda_deepseek_router_route(C.byref(req), C.byref(out))
+    return rc, ids, weights, out
+
+
 def synth_normal_bf16(seed: int, tensor_id: int, count: int, std: float) -> np.ndarray:
     """Multi-threaded native twin of nerva_b200.synth.normal_bf16 (same bits)."""
     out = np.empty(count, dtype=np.uint16)

@@ -246,3 +246,76 @@ class Decoder:
         if n < 0:
             raise ValueError("oracle decode failed")
         return (tokens[:n], logits[:n]) if want_logits else tokens[:n]
+
+
+# ---- DeepSeek expert routers (oracle/nerva_oracle_router.c) and the reference's own header ----
+
+_REF_ROUTER_PATH = os.path.join(_HERE, "_ref", "libnerva_ref_router.so")
+_REFERENCE_HEADER = "/root/reference/native/cuda/deepseek/deepseek_router.cuh"
+_ref_router = None
+
+
+def build_ref(force: bool = False):
+    """Compiles the reference's router header for the host (oracle/_ref/), where the reference
+    checkout exists.  Returns the library path, or None when neither checkout nor a prebuilt
+    library is there."""
+    if os.path.exists(_REFERENCE_HEADER) and (force or not os.path.exists(_REF_ROUTER_PATH)):
+        subprocess.run(["make", "-C", _HERE, "ref"], check=True, capture_output=True)
+    return _REF_ROUTER_PATH if os.path.exists(_REF_ROUTER_PATH) else None
+
+
+def ref_router_lib():
+    """The reference router compiled for the host, or None when it has not been built."""
+    global _ref_router
+    if _ref_router is None:
+        path = build_ref()
+        if path is None:
+            return None
+        _ref_router = C.CDLL(path)
+    return _ref_router
+
+
+def _route(fn, kind: str, logits, bias, top_k, norm_topk_prob, scaling, num_groups=0, top_k_groups=0, table=None,
+           route_token=0):
+    logits = np.ascontiguousarray(logits, dtype=np.float32)
+    bias_arr = None if bias is None else np.ascontiguousarray(bias, dtype=np.float32)
+    ids = np.zeros(top_k, dtype=np.uint32)
+    weights = np.zeros(top_k, dtype=np.float32)
+    f = C.c_float(scaling)
+    if kind == "v3":
+        rc = fn(_pf(logits), _pf(bias_arr) if bias_arr is not None else None, logits.size, num_groups, top_k_groups,
+                top_k, int(norm_topk_prob), f, _pu(ids), _pf(weights))
+    elif kind == "v4":
+        rc = fn(_pf(logits), _pf(bias_arr) if bias_arr is not None else None, logits.size, top_k,
+                int(norm_topk_prob), f, _pu(ids), _pf(weights))
+    else:
+        table = np.ascontiguousarray(table, dtype=np.uint32)
+        rc = fn(_pf(logits), _pu(table), table.size, route_token, logits.size, top_k, int(norm_topk_prob), f,
+                _pu(ids), _pf(weights))
+    return rc, ids, weights
+
+
+def _router_fn(library, prefix: str, kind: str):
+    name = {"v3": "route_v3_grouped_sigmoid", "v4": "route_v4_sqrtsoftplus", "hash": "route_v4_hash"}[kind]
+    fn = getattr(library, f"{prefix}_{name}")
+    fn.restype = C.c_int
+    fn.argtypes = None  # mixed pointer / scalar arguments are passed explicitly typed by _route
+    return fn
+
+
+def route_v3_grouped_sigmoid(logits, bias, num_groups, top_k_groups, top_k, norm_topk_prob, scaling, ref=False):
+    library = ref_router_lib() if ref else lib()
+    return _route(_router_fn(library, "ref" if ref else "oracle", "v3"), "v3", logits, bias, top_k, norm_topk_prob,
+                  scaling, num_groups=num_groups, top_k_groups=top_k_groups)
+
+
+def route_v4_sqrtsoftplus(logits, bias, top_k, norm_topk_prob, scaling, ref=False):
+    library = ref_router_lib() if ref else lib()
+    return _route(_router_fn(library, "ref" if ref else "oracle", "v4"), "v4", logits, bias, top_k, norm_topk_prob,
+                  scaling)
+
+
+def route_v4_hash(logits, table, route_token, top_k, norm_topk_prob, scaling, ref=False):
+    library = ref_router_lib() if ref else lib()
+    return _route(_router_fn(library, "ref" if ref else "oracle", "hash"), "hash", logits, None, top_k,
+                  norm_topk_prob, scaling, table=table, route_token=route_token)
