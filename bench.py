@@ -310,6 +310,48 @@ def run_ours(args, cfg, rank: int, world: int) -> dict:
     return result
 
 
+def run_operator_workloads(kind: str) -> None:
+    """Per-operator measurements of BASELINE configs 3 and 4 through the per-op C ABI (host buffers in,
+    device time per launch out, L2 flushed between launches).  One JSON line per case."""
+    from nerva_b200 import build, ops, synth
+    build.build()
+    peak = measured_peaks()
+    if kind == "linear":
+        shapes = [("qkv", 6144, 4096), ("o", 4096, 4096), ("gate_up", 24576, 4096), ("down", 4096, 12288),
+                  ("lm_head", 151936, 4096)]
+        for name, rows, cols in shapes:
+            w = ops.synth_normal_bf16(0, 77, rows * cols, 0.02)
+            for m in (1, 4, 16, 64):
+                x = ops.synth_normal_bf16(0, synth.T_ACTIVATION, m * cols, 1.0)
+                _, ns = ops.projection(w, x, rows, cols, tokens=m, warmup=3, iterations=10)
+                nbytes = 2 * rows * cols + 2 * m * cols + 4 * m * rows
+                gbs = nbytes / ns
+                print(json.dumps({"workload": "decode-linear", "shape": name, "N": rows, "K": cols, "M": m,
+                                  "us": ns / 1e3, "algorithmic_bytes": nbytes, "GB/s": gbs,
+                                  "frac_of_measured_hbm": gbs / peak["hbm_gbs"],
+                                  "note": "M > 1 re-streams the weights once per token (no skinny-GEMM kernel yet)"
+                                  if m > 1 else "weight-streaming GEMV"}), flush=True)
+        return
+    heads, kv_heads, d = 32, 8, 128
+    for batch in (1, 8):
+        for context in (8192, 32768, 131072):
+            pages = (context + 15) // 16
+            n = batch * pages * 16 * kv_heads * d
+            k = ops.synth_normal_bf16(0, synth.layer_tensor_id(0, synth.L_K), n, 1.0)
+            v = ops.synth_normal_bf16(0, synth.layer_tensor_id(0, synth.L_V), n, 1.0)
+            table = np.stack([synth.permutation(b, synth.T_PAGE_TABLE, pages) for b in range(batch)])
+            q = synth.normal_f32(0, synth.layer_tensor_id(0, synth.L_Q), batch * heads * d, 1.0)
+            _, ns = ops.gqa_decode_attention(q, k, v, table, batch, context, heads, kv_heads, d, warmup=3,
+                                             iterations=10)
+            nbytes = batch * (4096 * context + pages * 4 + heads * d * 4 * 2)
+            gbs = nbytes / ns
+            print(json.dumps({"workload": "long-context GQA decode attention", "batch": batch, "context": context,
+                              "heads": heads, "kv_heads": kv_heads, "head_dim": d, "us": ns / 1e3,
+                              "algorithmic_bytes": nbytes, "GB/s": gbs,
+                              "frac_of_measured_hbm": gbs / peak["hbm_gbs"],
+                              "pages": "16-token pages placed by a seeded Fisher-Yates permutation"}), flush=True)
+
+
 def _barrier_fn(world: int):
     if world == 1:
         return lambda: None
@@ -340,12 +382,19 @@ def main() -> None:
     ap.add_argument("--layers", type=int, default=0,
                     help="cut the model to this many layers (profiler captures only; not a bench line)")
     ap.add_argument("--prompt-tokens", type=int, default=0, help="override the prompt length")
+    ap.add_argument("--workload", default="decode", choices=["decode", "linear", "attention"],
+                    help="decode: the bench line; linear / attention: per-operator sweeps of the isolated "
+                         "projection shapes and of long-context attention (one JSON line per case)")
     ap.add_argument("--timeline", action="store_true",
                     help="add the in-graph timeline (kernel-written %%globaltimer stamps, mean over layers)")
     args = ap.parse_args()
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
     local = int(os.environ.get("LOCAL_RANK", "0"))
+    if args.workload != "decode":
+        if rank == 0:
+            run_operator_workloads(args.workload)
+        return
     cfg = workload(args.config, args.layers, args.prompt_tokens)
     if args.impl == "reference":
         if rank == 0:

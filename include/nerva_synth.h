@@ -112,7 +112,8 @@ enum {
   NERVA_SYNTH_L_KV_B = 16,
   NERVA_SYNTH_L_K = 17,
   NERVA_SYNTH_L_V = 18,
-  NERVA_SYNTH_L_Q = 19
+  NERVA_SYNTH_L_Q = 19,
+  NERVA_SYNTH_L_SHARED_ROUTER = 20
 };
 
 #endif /* NERVA_SYNTH_H_ */

@@ -173,6 +173,39 @@ uint32_t fused_attention_splits(uint32_t target_context);
 cudaError_t launch_fused_attention(cudaStream_t stream, const FusedAttentionParams &p);
 cudaError_t configure_fused_attention_kernel();
 
+// ---- softmax top-k sparse MoE MLP (moe.cu) ----
+struct MoeRouteParams {
+  const float *logits;   // [num_experts] router logits of this token
+  uint32_t num_experts, top_k, norm_topk_prob;
+  uint32_t *expert_ids;  // [top_k]
+  float *weights;        // [top_k]
+};
+struct MoeExpertParams {
+  // residual add + RMSNorm prologue (as ProjectionParams), fp32 result
+  const float *add_a, *add_b;
+  const uint16_t *add_bias, *norm_weight;
+  float eps;
+  uint32_t hidden, moe_intermediate, shared_intermediate, top_k;
+  const uint16_t *w_expert_gate_up;  // [E][2 * moe_intermediate][hidden]: gate rows, then up rows
+  const uint16_t *w_expert_down;     // [E][hidden][moe_intermediate]
+  const uint16_t *w_shared_gate, *w_shared_up, *w_shared_down, *w_shared_router;  // shared expert, optional
+  const uint32_t *expert_ids;        // [top_k] from the route kernel
+  const float *route_weights;        // [top_k]
+  float *gate_up_out;                // scratch: per expert gate then up rows (+ the shared expert's), fp32
+  float *shared_gate;                // scratch: 1 float
+  float *out_f32;                    // [hidden] the MLP output
+  uint32_t *error_word;
+  uint32_t max_intermediate, max_rows_per_block;  // filled by the launcher
+};
+bool moe_supported(uint32_t hidden, uint32_t moe_intermediate, uint32_t shared_intermediate,
+                   uint32_t num_experts, uint32_t top_k, uint32_t sm_count);
+cudaError_t configure_moe_kernels();
+// Router logits with fp32 activations; uses the residual/norm fields, weight, rows, cols, out_f32 of p.
+cudaError_t launch_router_logits_f32(cudaStream_t stream, const ProjectionParams &p, uint32_t sm_count);
+cudaError_t launch_moe_route(cudaStream_t stream, const MoeRouteParams &p, bool pdl);
+// Two launches: gate/up of the chosen experts, then SwiGLU + down and the weighted sum.
+cudaError_t launch_moe_experts(cudaStream_t stream, const MoeExpertParams &p, uint32_t sm_count, bool pdl);
+
 // ---- greedy sampling ----
 // Reduces per-block (value, index) partials, writes the token slot at the
 // cursor and advances the cursor.  sample == 0: only advances the cursor.

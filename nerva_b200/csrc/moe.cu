@@ -1,0 +1,346 @@
+// Softmax top-k sparse MoE MLP of the resident decode step (Qwen3-MoE / Mixtral
+// style).  The reference runs the whole MLP of a layer in ONE thread block
+// (run_sparse_moe_mlp, hf_decode_sequence/device_ops.cuh:183-315); here it is
+//   moe_router_logits_kernel  residual add + RMSNorm + router mat-vec (small matrix)
+//   moe_route_kernel    softmax over the router logits, top-k by (weight
+//                       descending, index ascending), optional renormalisation
+//   moe_expert_kernel<kGateUp>  gate and up projections of the k chosen experts
+//                       (+ the shared expert) as ONE weight stream over a job list
+//                       built on the device from the routing result
+//   moe_expert_kernel<kDown>    SwiGLU + down projections of the same experts,
+//                       summed with the routing weights in rank order
+// Arithmetic follows the reference kernel: the mat-vecs read the UNROUNDED fp32
+// normalised hidden state and the unrounded fp32 SwiGLU output (unlike the dense
+// path, which rounds both to bf16), accumulate in fp32, and the expert outputs
+// are added as down += weight * y in rank order, then the shared expert scaled by
+// sigmoid(shared_router . x).
+#include "kernels.cuh"
+#include "row_stream.cuh"
+#include "step_device.cuh"
+
+namespace nb {
+namespace {
+
+constexpr uint32_t kMoeMaxTopK = 16;
+constexpr uint32_t kMoeMaxJobs = 2u * kMoeMaxTopK + 2u;
+constexpr uint32_t kRouteThreads = 256;
+
+// ---- routing ----
+__device__ __forceinline__ bool route_precedes(float w, uint32_t e, float best_w, uint32_t best_e) {
+  return w > best_w || (w == best_w && e < best_e);
+}
+
+// One block.  weights = softmax(logits) with the reference's guards (divide only
+// by a finite positive total); the k winners by (weight desc, index asc).
+__global__ void __launch_bounds__(kRouteThreads) moe_route_kernel(MoeRouteParams p) {
+  __shared__ float w_sh[256];
+  __shared__ float scratch[40];
+  __shared__ float red_w[kRouteThreads / 32];
+  __shared__ uint32_t red_e[kRouteThreads / 32];
+  __shared__ uint32_t chosen[kMoeMaxTopK];
+  __shared__ float chosen_w[kMoeMaxTopK];
+  pdl_trigger();
+  pdl_wait();
+  const uint32_t e = threadIdx.x;
+  const float logit = e < p.num_experts ? p.logits[e] : -INFINITY;
+  // maximum
+  float m = logit;
+  m = warp_max(m);
+  if ((threadIdx.x & 31u) == 0) red_w[threadIdx.x >> 5] = m;
+  __syncthreads();
+  m = -INFINITY;
+  for (uint32_t i = 0; i < kRouteThreads / 32; ++i) m = fmaxf(m, red_w[i]);
+  __syncthreads();
+  const float ex = e < p.num_experts ? expf(logit - m) : 0.0f;
+  const float total = block_sum(ex, scratch);
+  float w = ex;
+  if (total > 0.0f && isfinite(total)) w = ex / total;
+  w_sh[e] = e < p.num_experts ? w : -INFINITY;
+  __syncthreads();
+  for (uint32_t rank = 0; rank < p.top_k; ++rank) {
+    float bw = -INFINITY;
+    uint32_t be = 0xffffffffu;
+    if (e < p.num_experts) {
+      bool taken = false;
+      for (uint32_t prev = 0; prev < rank; ++prev) taken = taken || chosen[prev] == e;
+      if (!taken) {
+        bw = w_sh[e];
+        be = e;
+      }
+    }
+    for (int offset = 16; offset > 0; offset >>= 1) {
+      const float ow = __shfl_xor_sync(0xffffffffu, bw, offset);
+      const uint32_t oe = __shfl_xor_sync(0xffffffffu, be, offset);
+      if (oe != 0xffffffffu && (be == 0xffffffffu || route_precedes(ow, oe, bw, be))) {
+        bw = ow;
+        be = oe;
+      }
+    }
+    if ((threadIdx.x & 31u) == 0) {
+      red_w[threadIdx.x >> 5] = bw;
+      red_e[threadIdx.x >> 5] = be;
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+      bw = -INFINITY;
+      be = 0xffffffffu;
+      for (uint32_t i = 0; i < kRouteThreads / 32; ++i) {
+        if (red_e[i] != 0xffffffffu && (be == 0xffffffffu || route_precedes(red_w[i], red_e[i], bw, be))) {
+          bw = red_w[i];
+          be = red_e[i];
+        }
+      }
+      chosen[rank] = be;
+      chosen_w[rank] = bw;
+    }
+    __syncthreads();
+  }
+  if (threadIdx.x == 0) {
+    float sum = 0.0f;
+    for (uint32_t rank = 0; rank < p.top_k; ++rank) sum += chosen_w[rank];
+    for (uint32_t rank = 0; rank < p.top_k; ++rank) {
+      float out = chosen_w[rank];
+      if (p.norm_topk_prob != 0 && sum > 0.0f) out /= sum;
+      p.expert_ids[rank] = chosen[rank] == 0xffffffffu ? 0u : chosen[rank];
+      p.weights[rank] = out;
+    }
+  }
+}
+
+// ---- expert projections ----
+enum MoePhase : uint32_t { kGateUp = 0, kDown = 1 };
+
+struct MoeShared {
+  StreamShared stream;
+  JobDesc jobs[kMoeMaxJobs];
+  float scratch[40];
+  uint32_t ids[kMoeMaxTopK];
+  float weights[kMoeMaxTopK + 1];  // [top_k] = the shared expert's gate
+};
+
+__host__ __device__ inline uint32_t round128u(uint32_t v) { return (v + 127u) & ~127u; }
+
+// fp32 twin of add_norm_to_smem: x = (r * scale) * w, unrounded.
+__device__ void add_norm_to_smem_f32(float *x, const float *a, const float *b, const uint16_t *bias,
+                                     const uint16_t *w, float eps, uint32_t cols, float *scratch) {
+  float sumsq = 0.0f;
+  for (uint32_t i = threadIdx.x; i < cols; i += blockDim.x) {
+    float r = b != nullptr ? __ldcg(b + i) : __ldcg(a + i);
+    if (bias != nullptr) r += bf16_bits_to_f32(bias[i]);
+    if (b != nullptr) r += __ldcg(a + i);
+    x[i] = r;
+    sumsq += r * r;
+  }
+  const float total = block_sum(sumsq, scratch);
+  const float scale = rsqrtf(total / static_cast<float>(cols) + eps);
+  for (uint32_t i = threadIdx.x; i < cols; i += blockDim.x) x[i] = x[i] * scale * bf16_bits_to_f32(w[i]);
+  __syncthreads();
+}
+
+// Router logits: logits[e] = W_router[e] . x with x the unrounded fp32 normalised hidden state
+// (residual add + RMSNorm in front, block 0 stores the new residual).  The matrix is small
+// (experts x hidden), so plain 16-byte loads, one warp per row.
+__global__ void __launch_bounds__(256) moe_router_logits_kernel(ProjectionParams p) {
+  extern __shared__ __align__(16) float xr[];  // [cols]
+  __shared__ float scratch[40];
+  pdl_trigger();
+  pdl_wait();
+  if (blockIdx.x == 0 && p.resid_out != nullptr) {
+    for (uint32_t i = threadIdx.x; i < p.cols; i += blockDim.x) {
+      float r = p.add_b != nullptr ? __ldcg(p.add_b + i) : __ldcg(p.add_a + i);
+      if (p.add_bias != nullptr) r += bf16_bits_to_f32(p.add_bias[i]);
+      if (p.add_b != nullptr) r += __ldcg(p.add_a + i);
+      p.resid_out[i] = r;
+    }
+  }
+  add_norm_to_smem_f32(xr, p.add_a, p.add_b, p.add_bias, p.norm_weight, p.eps, p.cols, scratch);
+  const uint32_t lane = threadIdx.x & 31u, warp = threadIdx.x >> 5, warps = blockDim.x >> 5;
+  for (uint32_t row = blockIdx.x * warps + warp; row < p.rows; row += gridDim.x * warps) {
+    const uint4 *w = reinterpret_cast<const uint4 *>(p.weight + static_cast<uint64_t>(row) * p.cols);
+    float acc = 0.0f;
+    for (uint32_t i = lane; i < p.cols / 8u; i += 32u) {
+      const uint4 wv = w[i];
+      const float4 xa = *reinterpret_cast<const float4 *>(xr + 8u * i);
+      const float4 xb = *reinterpret_cast<const float4 *>(xr + 8u * i + 4u);
+      acc = dot8_f32(wv, xa, xb, acc);
+    }
+    acc = warp_sum(acc);
+    if (lane == 0) p.out_f32[row] = acc;
+  }
+}
+
+// Shared memory: ring | x (fp32, max(hidden, largest intermediate)) | MoeShared | row totals | acc.
+template <uint32_t PHASE>
+__global__ void __launch_bounds__(kStreamThreads, 1) moe_expert_kernel(MoeExpertParams p) {
+  extern __shared__ __align__(128) uint8_t smem[];
+  const uint32_t x_elems = p.hidden > p.max_intermediate ? p.hidden : p.max_intermediate;
+  float *x = reinterpret_cast<float *>(smem + kRingBytes);
+  MoeShared &sh = *reinterpret_cast<MoeShared *>(smem + kRingBytes + round128u(x_elems * 4u));
+  float *row_total = reinterpret_cast<float *>(smem + kRingBytes + round128u(x_elems * 4u) +
+                                               round128u(sizeof(MoeShared)));
+  float *acc = row_total + p.max_rows_per_block;
+  const uint32_t experts = p.top_k + (p.shared_intermediate != 0 ? 1u : 0u);
+  const uint32_t job_count = PHASE == kGateUp ? 2u * experts : experts;
+  pdl_trigger();
+  // The job list depends on the routing result of this step.
+  pdl_wait();
+  if (threadIdx.x < p.top_k) {
+    sh.ids[threadIdx.x] = p.expert_ids[threadIdx.x];
+    sh.weights[threadIdx.x] = p.route_weights[threadIdx.x];
+  }
+  __syncthreads();
+  if (threadIdx.x < job_count) {
+    const uint32_t j = threadIdx.x;
+    const uint32_t r = PHASE == kGateUp ? j / 2u : j;
+    const bool is_shared = r >= p.top_k;
+    const uint64_t mi = p.moe_intermediate, h = p.hidden;
+    JobDesc d{};
+    d.unit = 1;
+    if (PHASE == kGateUp) {
+      d.cols = p.hidden;
+      if (is_shared) {
+        d.rows = p.shared_intermediate;
+        d.weight = (j & 1u) == 0 ? p.w_shared_gate : p.w_shared_up;
+      } else {
+        d.rows = p.moe_intermediate;
+        d.weight = p.w_expert_gate_up + static_cast<uint64_t>(sh.ids[r]) * 2u * mi * h + ((j & 1u) != 0 ? mi * h : 0u);
+      }
+    } else {
+      d.rows = p.hidden;
+      if (is_shared) {
+        d.cols = p.shared_intermediate;
+        d.weight = p.w_shared_down;
+      } else {
+        d.cols = p.moe_intermediate;
+        d.weight = p.w_expert_down + static_cast<uint64_t>(sh.ids[r]) * h * mi;
+      }
+    }
+    sh.jobs[j] = d;
+  }
+  __syncthreads();
+  RowStream rs;
+  stream_init(rs, smem, sh.stream, sh.jobs, job_count);
+  stream_fill(rs);
+  for (uint32_t i = threadIdx.x; i < p.max_rows_per_block; i += blockDim.x) {
+    row_total[i] = 0.0f;
+    acc[i] = 0.0f;
+  }
+
+  if (PHASE == kGateUp) {
+    add_norm_to_smem_f32(x, p.add_a, p.add_b, p.add_bias, p.norm_weight, p.eps, p.hidden, sh.scratch);
+    if (blockIdx.x == 0 && p.shared_intermediate != 0) {
+      // gate of the shared expert: sigmoid(shared_router . x)
+      float dot = 0.0f;
+      for (uint32_t i = threadIdx.x; i < p.hidden; i += blockDim.x) dot += bf16_bits_to_f32(p.w_shared_router[i]) * x[i];
+      const float total = block_sum(dot, sh.scratch);
+      if (threadIdx.x == 0) *p.shared_gate = 1.0f / (1.0f + expf(-total));
+    }
+  } else if (p.shared_intermediate != 0 && threadIdx.x == 0) {
+    sh.weights[p.top_k] = __ldcg(p.shared_gate);
+  }
+  __syncthreads();
+
+  uint64_t out_offset = 0;  // kGateUp: where job j's rows go in gate_up_out
+  for (uint32_t j = 0; j < job_count; ++j) {
+    const JobDesc &job = sh.jobs[j];
+    uint32_t row_begin, row_end;
+    block_row_range(job.rows, 1, blockIdx.x, gridDim.x, &row_begin, &row_end);
+    const uint32_t rows_local = row_end - row_begin;
+    if (PHASE == kDown) {
+      // x = silu(gate) * up of expert j, unrounded
+      const float *gate = p.gate_up_out + out_offset;
+      const float *up = gate + job.cols;
+      for (uint32_t i = threadIdx.x; i < job.cols; i += blockDim.x) x[i] = silu(__ldcg(gate + i)) * __ldcg(up + i);
+      __syncthreads();
+    }
+    stream_consume<true>(rs, sh.stream, j, x, row_total, p.error_word);
+    __syncthreads();
+    if (PHASE == kGateUp) {
+      for (uint32_t r = threadIdx.x; r < rows_local; r += blockDim.x) {
+        p.gate_up_out[out_offset + row_begin + r] = stream_row_total(sh.stream, row_total, r);
+        row_total[r] = 0.0f;
+      }
+      out_offset += job.rows;
+    } else {
+      const float weight = sh.weights[j];
+      for (uint32_t r = threadIdx.x; r < rows_local; r += blockDim.x) {
+        acc[r] += weight * stream_row_total(sh.stream, row_total, r);
+        row_total[r] = 0.0f;
+      }
+      out_offset += 2u * job.cols;
+    }
+    __syncthreads();
+  }
+  if (PHASE == kDown) {
+    uint32_t row_begin, row_end;
+    block_row_range(p.hidden, 1, blockIdx.x, gridDim.x, &row_begin, &row_end);
+    for (uint32_t r = threadIdx.x; r < row_end - row_begin; r += blockDim.x) p.out_f32[row_begin + r] = acc[r];
+  }
+  stream_drain(rs);
+}
+
+uint32_t moe_blocks(const MoeExpertParams &p, uint32_t sm_count) {
+  uint32_t rows = p.hidden < p.moe_intermediate ? p.hidden : p.moe_intermediate;
+  if (p.shared_intermediate != 0 && p.shared_intermediate < rows) rows = p.shared_intermediate;
+  uint32_t blocks = rows < sm_count ? rows : sm_count;
+  return blocks == 0 ? 1u : blocks;
+}
+
+uint32_t moe_smem_bytes(const MoeExpertParams &p) {
+  const uint32_t x_elems = p.hidden > p.max_intermediate ? p.hidden : p.max_intermediate;
+  return kRingBytes + round128u(x_elems * 4u) + round128u(sizeof(MoeShared)) + p.max_rows_per_block * 8u + 128u;
+}
+
+}  // namespace
+
+bool moe_supported(uint32_t hidden, uint32_t moe_intermediate, uint32_t shared_intermediate,
+                   uint32_t num_experts, uint32_t top_k, uint32_t sm_count) {
+  if (num_experts == 0 || num_experts > 256 || top_k == 0 || top_k > kMoeMaxTopK || top_k > num_experts) return false;
+  if (hidden % 8u != 0 || moe_intermediate % 8u != 0 || shared_intermediate % 8u != 0) return false;
+  if (hidden * 4u > 48u * 1024u) return false;  // the router kernel keeps the fp32 hidden state in 48 KB
+  MoeExpertParams p{};
+  p.hidden = hidden;
+  p.moe_intermediate = moe_intermediate;
+  p.shared_intermediate = shared_intermediate;
+  p.max_intermediate = moe_intermediate > shared_intermediate ? moe_intermediate : shared_intermediate;
+  const uint32_t blocks = moe_blocks(p, sm_count);
+  const uint32_t widest = hidden > p.max_intermediate ? hidden : p.max_intermediate;
+  p.max_rows_per_block = (widest + blocks - 1u) / blocks;
+  return moe_smem_bytes(p) <= 227u * 1024u;
+}
+
+cudaError_t configure_moe_kernels() {
+  cudaError_t err = cudaFuncSetAttribute(moe_expert_kernel<kGateUp>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         227 * 1024);
+  if (err == cudaSuccess)
+    err = cudaFuncSetAttribute(moe_expert_kernel<kDown>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
+  return err;
+}
+
+cudaError_t launch_router_logits_f32(cudaStream_t stream, const ProjectionParams &p, uint32_t sm_count) {
+  if (p.cols % 8u != 0 || p.cols * 4u > 48u * 1024u || p.rows == 0) return cudaErrorNotSupported;
+  uint32_t blocks = (p.rows + 7u) / 8u;
+  if (blocks > sm_count) blocks = sm_count;
+  return launch_with_pdl(moe_router_logits_kernel, dim3(blocks), dim3(256), p.cols * 4u, stream, p.pdl != 0, p);
+}
+
+cudaError_t launch_moe_route(cudaStream_t stream, const MoeRouteParams &p, bool pdl) {
+  if (p.num_experts == 0 || p.num_experts > 256 || p.top_k == 0 || p.top_k > kMoeMaxTopK) return cudaErrorInvalidValue;
+  return launch_with_pdl(moe_route_kernel, dim3(1), dim3(kRouteThreads), 0, stream, pdl, p);
+}
+
+cudaError_t launch_moe_experts(cudaStream_t stream, const MoeExpertParams &params, uint32_t sm_count, bool pdl) {
+  MoeExpertParams p = params;
+  p.max_intermediate = p.moe_intermediate > p.shared_intermediate ? p.moe_intermediate : p.shared_intermediate;
+  const uint32_t blocks = moe_blocks(p, sm_count);
+  const uint32_t widest = p.hidden > p.max_intermediate ? p.hidden : p.max_intermediate;
+  p.max_rows_per_block = (widest + blocks - 1u) / blocks;
+  const uint32_t smem = moe_smem_bytes(p);
+  if (smem > 227u * 1024u) return cudaErrorNotSupported;
+  cudaError_t err = launch_with_pdl(moe_expert_kernel<kGateUp>, dim3(blocks), dim3(kStreamThreads), smem, stream,
+                                    pdl, p);
+  if (err != cudaSuccess) return err;
+  return launch_with_pdl(moe_expert_kernel<kDown>, dim3(blocks), dim3(kStreamThreads), smem, stream, pdl, p);
+}
+
+}  // namespace nb

@@ -203,13 +203,40 @@ __device__ __forceinline__ float dot8(const uint4 &w, const uint4 &x, float acc)
   return acc;
 }
 
+// dot of 8 bf16 weights with 8 fp32 activations (the sparse-MoE path of the
+// reference feeds unrounded activations to its mat-vec).
+__device__ __forceinline__ float dot8_f32(const uint4 &w, const float4 &xa, const float4 &xb, float acc) {
+  acc = fmaf(bf16x2_lo(w.x), xa.x, acc);
+  acc = fmaf(bf16x2_hi(w.x), xa.y, acc);
+  acc = fmaf(bf16x2_lo(w.y), xa.z, acc);
+  acc = fmaf(bf16x2_hi(w.y), xa.w, acc);
+  acc = fmaf(bf16x2_lo(w.z), xb.x, acc);
+  acc = fmaf(bf16x2_hi(w.z), xb.y, acc);
+  acc = fmaf(bf16x2_lo(w.w), xb.z, acc);
+  acc = fmaf(bf16x2_hi(w.w), xb.w, acc);
+  return acc;
+}
+// One 16-byte piece of weights at `wp` times the matching activations: bf16 at
+// byte offset `off` of xp, or (XF32) fp32 at byte offset 2 * off.
+template <bool XF32>
+__device__ __forceinline__ float dot_piece(const uint8_t *wp, const uint8_t *xp, uint32_t off, float acc) {
+  if (XF32) {
+    const float4 xa = *reinterpret_cast<const float4 *>(xp + 2u * off);
+    const float4 xb = *reinterpret_cast<const float4 *>(xp + 2u * off + 16u);
+    return dot8_f32(lds128(wp + off), xa, xb, acc);
+  }
+  return dot8(lds128(wp + off), lds128(xp + off), acc);
+}
+
 // Consumes job `index` (jobs are consumed in order, each exactly once, by every
 // warp of the block).  `x` is the bf16 activation vector in shared memory;
 // row_total[r] (shared, one float per block-local row, zeroed by the caller
 // before the block's previous synchronisation) receives the total of every row
 // that lies wholly inside this warp's range; partial rows go to sh.edge.
+// XF32: `x` points at fp32 activations instead of bf16 ones.
+template <bool XF32 = false>
 __device__ __forceinline__ void stream_consume(RowStream &rs, StreamShared &sh, uint32_t index,
-                                               const uint16_t *x, float *row_total,
+                                               const void *x, float *row_total,
                                                uint32_t *error_word) {
   const uint32_t lane = threadIdx.x & 31u, warp = threadIdx.x >> 5;
   const WarpJob job = warp_job(rs.jobs[index]);
@@ -234,8 +261,18 @@ __device__ __forceinline__ void stream_consume(RowStream &rs, StreamShared &sh, 
       report_error(error_word, kErrTmaWaitTimeout);
     }
     const uint8_t *wp = rs.ring + slot * kChunkBytes + lane * 16u;
-    const uint8_t *xp = reinterpret_cast<const uint8_t *>(x) + (pos - (row_end - job.row_bytes)) + lane * 16u;
-    if (len == kChunkBytes) {
+    const uint8_t *xp = reinterpret_cast<const uint8_t *>(x) +
+                        (XF32 ? 2u : 1u) * ((pos - (row_end - job.row_bytes)) + lane * 16u);
+    if (XF32) {
+      uint32_t off = 0;
+      for (; off + 4u * kSweepBytes <= len; off += 4u * kSweepBytes) {
+        acc[0] = dot_piece<true>(wp, xp, off, acc[0]);
+        acc[1] = dot_piece<true>(wp, xp, off + kSweepBytes, acc[1]);
+        acc[2] = dot_piece<true>(wp, xp, off + 2u * kSweepBytes, acc[2]);
+        acc[3] = dot_piece<true>(wp, xp, off + 3u * kSweepBytes, acc[3]);
+      }
+      for (; off + lane * 16u < len; off += kSweepBytes) acc[0] = dot_piece<true>(wp, xp, off, acc[0]);
+    } else if (len == kChunkBytes) {
 #pragma unroll
       for (uint32_t i = 0; i < kChunkBytes / kSweepBytes; i += 4) {
         const uint4 w0 = lds128(wp + (i + 0) * kSweepBytes), x0 = lds128(xp + (i + 0) * kSweepBytes);

@@ -74,10 +74,11 @@ bool valid_layer(const NervaCudaHfDecodeChainLayer &layer, bool require_sources)
   return true;
 }
 
-// What this library's kernels run: full attention, no query gate, dense SwiGLU.
+// What this library's kernels run: full attention, no query gate, dense SwiGLU or
+// softmax top-k sparse MoE (whose shape limits are checked once the device is known).
 bool layer_supported(const NervaCudaHfDecodeChainLayer &layer) {
   return layer.attention_kind == NERVA_ATTENTION_KIND_FULL && layer.w_q_gate == nullptr &&
-         layer.mlp_kind == NERVA_MLP_KIND_DENSE;
+         (layer.mlp_kind == NERVA_MLP_KIND_DENSE || layer.mlp_kind == NERVA_MLP_KIND_SPARSE_MOE);
 }
 
 static bool sampler_valid(const NervaCudaHfDecodeSamplerConfig &s) {
@@ -250,6 +251,16 @@ bool plan_state(Session *s, StaticArena &arena, void *base) {
   ok = ok && carve(arena, base, static_cast<uint64_t>(s->max_context), &s->device_prompt);
   ok = ok && carve(arena, base, uint64_t{4}, &s->device_cursor);
   ok = ok && carve(arena, base, uint64_t{4}, &s->device_error);
+  uint64_t moe_scratch = 0;
+  for (const LayerLayout &L : s->layout.layers) {
+    if (L.mlp_kind == NERVA_MLP_KIND_SPARSE_MOE)
+      moe_scratch = std::max<uint64_t>(moe_scratch, 2ull * L.top_k * L.moe_intermediate + 2ull * L.shared_intermediate);
+  }
+  ok = ok && carve(arena, base, uint64_t{256}, &s->router_logits);
+  ok = ok && carve(arena, base, uint64_t{16}, &s->route_ids);
+  ok = ok && carve(arena, base, uint64_t{16}, &s->route_weights);
+  ok = ok && carve(arena, base, uint64_t{4}, &s->shared_gate);
+  ok = ok && carve(arena, base, moe_scratch + 4u, &s->moe_gate_up);
   s->timeline_nodes = 5u * d.layers + 1u;
   ok = ok && carve(arena, base, static_cast<uint64_t>(s->timeline_nodes) * kTimelineSlots, &s->timeline);
   return ok;
@@ -347,8 +358,8 @@ cudaError_t setup_step_kernel(Session *s) {
                                    max_rows_per_block(2u * d.intermediate, 2, s->sm_count)),
                           std::max(max_rows_per_block(d.hidden, 1, s->sm_count),
                                    max_rows_per_block(d.vocab, 1, s->sm_count)));
-  s->step_kernel_ok = step_kernel_supported(d.hidden, d.heads, d.kv_heads, d.head_dim, d.intermediate,
-                                            s->x_elems, s->row_elems);
+  s->step_kernel_ok = !s->has_moe && step_kernel_supported(d.hidden, d.heads, d.kv_heads, d.head_dim,
+                                                           d.intermediate, s->x_elems, s->row_elems);
   if (!s->step_kernel_ok) return cudaSuccess;
   cudaError_t err = configure_step_kernel();
   if (err != cudaSuccess) return err;
@@ -442,6 +453,12 @@ cudaError_t enqueue_step_kernel(Session *s, uint32_t splits, uint32_t sample) {
   p.row_elems = s->row_elems;
   p.phase_cycles = s->phase_profile ? s->phase_cycles : nullptr;
   return launch_step_kernel(s->stream, p, s->sm_count);
+}
+
+// Router logits of a sparse-MoE layer.  The expert kernels follow the reference's MoE arithmetic
+// (unrounded fp32 activations); the router mat-vec does too, through the fp32 router kernel.
+static cudaError_t launch_moe_router_logits(Session *s, const ProjectionParams &p) {
+  return launch_router_logits_f32(s->stream, p, s->sm_count);
 }
 
 // Records the next profile event; the interval that ends here gets `bucket`.
@@ -622,6 +639,66 @@ cudaError_t enqueue_step(Session *s, uint32_t splits, uint32_t sample, uint64_t 
     n += 1;
     profile_mark(s, prof, kBucketO);
     if (err != cudaSuccess) break;
+
+    if (L.mlp_kind == NERVA_MLP_KIND_SPARSE_MOE) {
+      // router logits (residual add + RMSNorm in front; block 0 stores the new residual)
+      p = ProjectionParams{};
+      p.error_word = s->device_error;
+      p.pdl = s->use_pdl ? 1u : 0u;
+      p.eps = s->rms_eps;
+      p.weight = arena_at(s, L.w_router);
+      p.rows = L.num_experts;
+      p.cols = d.hidden;
+      p.prologue = kPrologueAddNorm;
+      p.x_bf16 = s->x_scratch;
+      p.add_a = s->h_a;
+      p.add_b = s->o_out;
+      p.add_bias = arena_at(s, L.o_bias);
+      p.norm_weight = arena_at(s, L.rms_mlp);
+      p.resid_out = s->h_b;
+      p.epilogue = kEpilogueStore;
+      p.out_f32 = s->router_logits;
+      err = launch_moe_router_logits(s, p);
+      n += 1;
+      if (err != cudaSuccess) break;
+      MoeRouteParams rp{};
+      rp.logits = s->router_logits;
+      rp.num_experts = L.num_experts;
+      rp.top_k = L.top_k;
+      rp.norm_topk_prob = L.norm_topk_prob;
+      rp.expert_ids = s->route_ids;
+      rp.weights = s->route_weights;
+      err = launch_moe_route(s->stream, rp, s->use_pdl);
+      n += 1;
+      profile_mark(s, prof, kBucketGateUp);
+      if (err != cudaSuccess) break;
+      MoeExpertParams ep{};
+      ep.add_a = s->h_a;
+      ep.add_b = s->o_out;
+      ep.add_bias = arena_at(s, L.o_bias);
+      ep.norm_weight = arena_at(s, L.rms_mlp);
+      ep.eps = s->rms_eps;
+      ep.hidden = d.hidden;
+      ep.moe_intermediate = L.moe_intermediate;
+      ep.shared_intermediate = L.shared_intermediate;
+      ep.top_k = L.top_k;
+      ep.w_expert_gate_up = arena_at(s, L.w_expert_gate_up);
+      ep.w_expert_down = arena_at(s, L.w_expert_down);
+      ep.w_shared_gate = arena_at(s, L.w_shared_gate);
+      ep.w_shared_up = arena_at(s, L.w_shared_up);
+      ep.w_shared_down = arena_at(s, L.w_shared_down);
+      ep.w_shared_router = arena_at(s, L.w_shared_router);
+      ep.expert_ids = s->route_ids;
+      ep.route_weights = s->route_weights;
+      ep.gate_up_out = s->moe_gate_up;
+      ep.shared_gate = s->shared_gate;
+      ep.out_f32 = s->down;
+      ep.error_word = s->device_error;
+      err = launch_moe_experts(s->stream, ep, s->sm_count, s->use_pdl);
+      n += 2;
+      profile_mark(s, prof, kBucketDown);
+      continue;
+    }
 
     // gate/up + SwiGLU
     p = ProjectionParams{};
@@ -979,6 +1056,19 @@ cudaError_t upload_from_pointers(Session *s, const NervaCudaHfDecodeSequenceSess
     for (const Item &it : items) {
       if (err == cudaSuccess) err = copy_tensor(s, it.off, it.src, it.n, c);
     }
+    if (L.mlp_kind == NERVA_MLP_KIND_SPARSE_MOE) {
+      const uint64_t mi = L.moe_intermediate, e = L.num_experts, si = L.shared_expert_intermediate;
+      const Item moe[] = {{o.w_router, L.w_router, e * hidden},
+                          {o.w_expert_gate_up, L.w_expert_gate_up, e * 2u * mi * hidden},
+                          {o.w_expert_down, L.w_expert_down, e * hidden * mi},
+                          {o.w_shared_gate, L.w_shared_expert_gate, si * hidden},
+                          {o.w_shared_up, L.w_shared_expert_up, si * hidden},
+                          {o.w_shared_down, L.w_shared_expert_down, hidden * si},
+                          {o.w_shared_router, L.w_shared_expert_router, hidden}};
+      for (const Item &it : moe) {
+        if (err == cudaSuccess && it.off != kMissingOffset) err = copy_tensor(s, it.off, it.src, it.n, c);
+      }
+    }
   }
   if (err == cudaSuccess) err = copy_tensor(s, s->layout.final_norm, r->final_norm_weight, hidden, c);
   if (err == cudaSuccess) err = copy_tensor(s, s->layout.lm_head, r->lm_head, d.vocab * hidden, c);
@@ -1314,7 +1404,18 @@ static int create_session(const NervaCudaHfDecodeSequenceSessionCreateRequest *r
   err = configure_projection_kernels();
   if (err == cudaSuccess) err = configure_attention_kernels();
   if (err == cudaSuccess) err = configure_fused_attention_kernel();
+  if (err == cudaSuccess) err = configure_moe_kernels();
   if (err != cudaSuccess) return create_fail(s, out, err, kStageSetDevice);
+  for (const LayerLayout &L : s->layout.layers) {
+    if (L.mlp_kind != NERVA_MLP_KIND_SPARSE_MOE) continue;
+    s->has_moe = true;
+    if (shard != nullptr || !moe_supported(d.hidden, L.moe_intermediate, L.shared_intermediate, L.num_experts, L.top_k,
+                                           s->sm_count)) {
+      set_last_error("sparse MoE layer not supported: needs hidden and intermediate sizes that are multiples of 8, "
+                     "at most 256 experts and 16 per token, no tensor parallel");
+      return create_fail(s, out, cudaErrorNotSupported, kStageInvalidRequest);
+    }
+  }
 
   // shared weights: one allocation
   s->weights = std::make_shared<SharedWeights>();
@@ -1347,7 +1448,7 @@ static int create_session(const NervaCudaHfDecodeSequenceSessionCreateRequest *r
     err = launch_pack_qkv(s->stream, arena_at(s, L.w_q), arena_at(s, L.w_k), arena_at(s, L.w_v),
                           s->weights->qkv_packed + l * qkv_rows * d.hidden, ah * d.hidden,
                           kvh * d.hidden);
-    if (err == cudaSuccess)
+    if (err == cudaSuccess && L.mlp_kind == NERVA_MLP_KIND_DENSE)
       err = launch_pack_gate_up(s->stream, arena_at(s, L.w_gate), arena_at(s, L.w_up),
                                 s->weights->gate_up_packed + static_cast<uint64_t>(l) * 2u * d.intermediate * d.hidden,
                                 d.intermediate, d.hidden);

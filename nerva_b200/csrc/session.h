@@ -157,6 +157,10 @@ struct NervaCudaHfDecodeSequenceSession {
   unsigned long long *timeline = nullptr;
   uint32_t timeline_nodes = 0;
   bool timeline_on = false;
+  // sparse MoE layers: routing scratch
+  bool has_moe = false;
+  float *router_logits = nullptr, *route_weights = nullptr, *shared_gate = nullptr, *moe_gate_up = nullptr;
+  uint32_t *route_ids = nullptr;
   // tensor parallel (nerva_b200_session_create_sharded)
   uint32_t tp_world = 1, tp_rank = 0;
   void *comm_block = nullptr;  // this rank's exchange buffer (own allocation, exported to the peers)

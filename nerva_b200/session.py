@@ -60,6 +60,8 @@ _LAYER_TENSORS = {
     "w_o": "w_o", "q_norm": "q_norm_weight", "k_norm": "k_norm_weight", "q_bias": "q_bias", "k_bias": "k_bias",
     "v_bias": "v_bias", "o_bias": "o_bias", "w_gate": "w_gate", "w_up": "w_up", "w_down": "w_down",
     "w_router": "w_router", "w_expert_gate_up": "w_expert_gate_up", "w_expert_down": "w_expert_down",
+    "w_shared_expert_gate": "w_shared_expert_gate", "w_shared_expert_up": "w_shared_expert_up",
+    "w_shared_expert_down": "w_shared_expert_down", "w_shared_expert_router": "w_shared_expert_router",
 }
 
 

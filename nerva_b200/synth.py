@@ -26,6 +26,7 @@ L_WQ, L_WK, L_WV, L_WO, L_WGATE, L_WUP, L_WDOWN = 0, 1, 2, 3, 4, 5, 6
 L_ROUTER, L_EXPERT_GATE_UP, L_EXPERT_DOWN = 7, 8, 9
 L_SHARED_GATE, L_SHARED_UP, L_SHARED_DOWN = 10, 11, 12
 L_Q_A, L_Q_B, L_KV_A, L_KV_B, L_K, L_V, L_Q = 13, 14, 15, 16, 17, 18, 19
+L_SHARED_ROUTER = 20
 
 BF16_ONE = 0x3F80
 
@@ -191,6 +192,12 @@ def dense_checkpoint(cfg: DecoderConfig, seed: int = 0, std: float = 0.02, fill=
             entry["w_router"] = gen(seed, tid(L_ROUTER), e * cfg.hidden, std)
             entry["w_expert_gate_up"] = gen(seed, tid(L_EXPERT_GATE_UP), e * 2 * mi * cfg.hidden, std)
             entry["w_expert_down"] = gen(seed, tid(L_EXPERT_DOWN), e * cfg.hidden * mi, std)
+            if cfg.shared_intermediate:
+                si = cfg.shared_intermediate
+                entry["w_shared_expert_gate"] = gen(seed, tid(L_SHARED_GATE), si * cfg.hidden, std)
+                entry["w_shared_expert_up"] = gen(seed, tid(L_SHARED_UP), si * cfg.hidden, std)
+                entry["w_shared_expert_down"] = gen(seed, tid(L_SHARED_DOWN), cfg.hidden * si, std)
+                entry["w_shared_expert_router"] = gen(seed, tid(L_SHARED_ROUTER), cfg.hidden, std)
         ck.layers.append(entry)
     return ck
 

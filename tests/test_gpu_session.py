@@ -192,3 +192,4 @@ def test_qwen3_8b_shapes_logits(built_lib, oracle_mod, layers):
             break
     else:
         assert np.abs(got - ref_logits[-1]).max() <= bound
+
