@@ -645,6 +645,54 @@ typedef struct NervaCudaDeepSeekRouterRouteResult {
 int nerva_cuda_deepseek_router_route(const NervaCudaDeepSeekRouterRouteRequest *request,
                                      NervaCudaDeepSeekRouterRouteResult *out);
 
+/* nerva_cuda_api.h:1540-1555 — DeepSeek multi-head latent attention decode of one token in
+ * absorbed form.  fp32 host pointers: q_nope [heads][nope], q_pe [heads][rope],
+ * kv_c [tokens][kv_lora_rank], k_pe [tokens][rope], w_uk [kv_lora_rank][heads][nope],
+ * w_uv [kv_lora_rank][heads][v_head_dim], output [heads][v_head_dim]. */
+typedef struct NervaCudaDeepSeekMlaDecodeRequest {
+  uint32_t heads;
+  uint32_t tokens;
+  uint32_t kv_lora_rank;
+  uint32_t qk_nope_head_dim;
+  uint32_t qk_rope_head_dim;
+  uint32_t v_head_dim;
+  float softmax_scale;
+  const float *q_nope;
+  const float *q_pe;
+  const float *kv_c;
+  const float *k_pe;
+  const float *w_uk;
+  const float *w_uv;
+  float *output;
+} NervaCudaDeepSeekMlaDecodeRequest;
+
+/* nerva_cuda_api.h:1557-1577 */
+typedef struct NervaCudaDeepSeekMlaDecodeResult {
+  int32_t status;
+  int32_t cuda_error;
+  int32_t device_count;
+  int32_t decode_error;
+  uint32_t heads;
+  uint32_t tokens;
+  uint32_t kv_lora_rank;
+  uint32_t qk_nope_head_dim;
+  uint32_t qk_rope_head_dim;
+  uint32_t v_head_dim;
+  float softmax_scale;
+  uint64_t output_hash;
+  uint64_t device_arena_bytes;
+  uint64_t pinned_host_bytes;
+  uint64_t h2d_bytes;
+  uint64_t d2h_bytes;
+  uint64_t kernel_launches;
+  uint64_t sync_calls;
+  uint64_t hot_path_allocations;
+} NervaCudaDeepSeekMlaDecodeResult;
+
+/* nerva_cuda_api.h:2262 */
+int nerva_cuda_deepseek_mla_decode(const NervaCudaDeepSeekMlaDecodeRequest *request,
+                                   NervaCudaDeepSeekMlaDecodeResult *out);
+
 /* ---- additive entry points (no counterpart in the reference) ---- */
 
 /* Step engine of a session: 0 = one kernel per operator captured in a CUDA

@@ -103,6 +103,8 @@ def lib() -> C.CDLL:
         "nerva_cuda_projection_bench": [P(ProjectionBenchRequest), P(ProjectionBenchResult)],
         "nerva_cuda_deepseek_router_route": [P(structs["NervaCudaDeepSeekRouterRouteRequest"]),
                                              P(structs["NervaCudaDeepSeekRouterRouteResult"])],
+        "nerva_cuda_deepseek_mla_decode": [P(structs["NervaCudaDeepSeekMlaDecodeRequest"]),
+                                           P(structs["NervaCudaDeepSeekMlaDecodeResult"])],
         "nerva_b200_session_set_engine": [vp, C.c_uint32],
         "nerva_b200_session_read_logits": [vp, vp, C.c_uint32],
         "nerva_b200_session_set_kv_block_table": [vp, vp, C.c_uint32],

@@ -97,6 +97,23 @@ def deepseek_router_route(kind: int, logits, top_k: int, bias=None, num_groups: 
     return rc, ids, weights, out
 
 
+def deepseek_mla_decode(q_nope, q_pe, kv_c, k_pe, w_uk, w_uv, heads: int, tokens: int, kv_lora_rank: int,
+                        qk_nope_head_dim: int, qk_rope_head_dim: int, v_head_dim: int, softmax_scale: float):
+    """Absorbed multi-head latent attention decode of one token (fp32 host arrays).
+    Returns (return code, out [heads * v_head_dim], result struct)."""
+    arrays = [np.ascontiguousarray(a, dtype=np.float32) for a in (q_nope, q_pe, kv_c, k_pe, w_uk, w_uv)]
+    out_values = np.zeros(heads * v_head_dim, dtype=np.float32)
+    req = ffi.structs["NervaCudaDeepSeekMlaDecodeRequest"](
+        heads=heads, tokens=tokens, kv_lora_rank=kv_lora_rank, qk_nope_head_dim=qk_nope_head_dim,
+        qk_rope_head_dim=qk_rope_head_dim, v_head_dim=v_head_dim, softmax_scale=softmax_scale,
+        q_nope=arrays[0].ctypes.data, q_pe=arrays[1].ctypes.data, kv_c=arrays[2].ctypes.data,
+        k_pe=arrays[3].ctypes.data, w_uk=arrays[4].ctypes.data, w_uv=arrays[5].ctypes.data,
+        output=out_values.ctypes.data)
+    out = ffi.structs["NervaCudaDeepSeekMlaDecodeResult"]()
+    rc = ffi.lib().nerva_cuda_deepseek_mla_decode(C.byref(req), C.byref(out))
+    return rc, out_values, out
+
+
 def synth_normal_bf16(seed: int, tensor_id: int, count: int, std: float) -> np.ndarray:
     """Multi-threaded native twin of nerva_b200.synth.normal_bf16 (same bits)."""
     out = np.empty(count, dtype=np.uint16)

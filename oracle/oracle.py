@@ -319,3 +319,18 @@ def route_v4_hash(logits, table, route_token, top_k, norm_topk_prob, scaling, re
     library = ref_router_lib() if ref else lib()
     return _route(_router_fn(library, "ref" if ref else "oracle", "hash"), "hash", logits, None, top_k,
                   norm_topk_prob, scaling, table=table, route_token=route_token)
+
+
+# ---- DeepSeek MLA decode (oracle/nerva_oracle_mla.c) ----
+
+def mla_decode(q_nope, q_pe, kv_c, k_pe, w_uk, w_uv, heads, tokens, kv_lora_rank, qk_nope_head_dim,
+               qk_rope_head_dim, v_head_dim, softmax_scale):
+    """Absorbed multi-head latent attention for one token; returns (status, out [heads * v_head_dim])."""
+    arrays = [np.ascontiguousarray(a, dtype=np.float32) for a in (q_nope, q_pe, kv_c, k_pe, w_uk, w_uv)]
+    out = np.zeros(heads * v_head_dim, dtype=np.float32)
+    fn = lib().oracle_mla_decode
+    fn.restype = C.c_int
+    fn.argtypes = [_f32p] * 7 + [C.c_uint32] * 6 + [C.c_float]
+    rc = fn(*[_pf(a) for a in arrays], _pf(out), heads, tokens, kv_lora_rank, qk_nope_head_dim, qk_rope_head_dim,
+            v_head_dim, softmax_scale)
+    return rc, out
