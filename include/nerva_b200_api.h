@@ -693,6 +693,51 @@ typedef struct NervaCudaDeepSeekMlaDecodeResult {
 int nerva_cuda_deepseek_mla_decode(const NervaCudaDeepSeekMlaDecodeRequest *request,
                                    NervaCudaDeepSeekMlaDecodeResult *out);
 
+/* nerva_cuda_api.h:2023-2037 — expert MLP of one token over already routed experts.  fp32 host
+ * pointers: input [hidden], w_gate / w_up [num_experts][intermediate][hidden],
+ * w_down [num_experts][hidden][intermediate], output [hidden]. */
+typedef struct NervaCudaDeepSeekMoeForwardRequest {
+  uint32_t hidden_size;
+  uint32_t intermediate_size;
+  uint32_t num_experts;
+  uint32_t top_k;
+  uint32_t clamp_swiglu;
+  float swiglu_limit;
+  const float *input;
+  const uint32_t *expert_ids;
+  const float *expert_weights;
+  const float *w_gate;
+  const float *w_up;
+  const float *w_down;
+  float *output;
+} NervaCudaDeepSeekMoeForwardRequest;
+
+/* nerva_cuda_api.h:2039-2058 */
+typedef struct NervaCudaDeepSeekMoeForwardResult {
+  int32_t status;
+  int32_t cuda_error;
+  int32_t device_count;
+  int32_t moe_error;
+  uint32_t hidden_size;
+  uint32_t intermediate_size;
+  uint32_t num_experts;
+  uint32_t top_k;
+  uint32_t clamp_swiglu;
+  float swiglu_limit;
+  uint64_t output_hash;
+  uint64_t device_arena_bytes;
+  uint64_t pinned_host_bytes;
+  uint64_t h2d_bytes;
+  uint64_t d2h_bytes;
+  uint64_t kernel_launches;
+  uint64_t sync_calls;
+  uint64_t hot_path_allocations;
+} NervaCudaDeepSeekMoeForwardResult;
+
+/* nerva_cuda_api.h:2302 */
+int nerva_cuda_deepseek_moe_forward(const NervaCudaDeepSeekMoeForwardRequest *request,
+                                    NervaCudaDeepSeekMoeForwardResult *out);
+
 /* ---- additive entry points (no counterpart in the reference) ---- */
 
 /* Step engine of a session: 0 = one kernel per operator captured in a CUDA

@@ -105,6 +105,8 @@ def lib() -> C.CDLL:
                                              P(structs["NervaCudaDeepSeekRouterRouteResult"])],
         "nerva_cuda_deepseek_mla_decode": [P(structs["NervaCudaDeepSeekMlaDecodeRequest"]),
                                            P(structs["NervaCudaDeepSeekMlaDecodeResult"])],
+        "nerva_cuda_deepseek_moe_forward": [P(structs["NervaCudaDeepSeekMoeForwardRequest"]),
+                                            P(structs["NervaCudaDeepSeekMoeForwardResult"])],
         "nerva_b200_session_set_engine": [vp, C.c_uint32],
         "nerva_b200_session_read_logits": [vp, vp, C.c_uint32],
         "nerva_b200_session_set_kv_block_table": [vp, vp, C.c_uint32],

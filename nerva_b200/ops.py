@@ -114,6 +114,23 @@ def deepseek_mla_decode(q_nope, q_pe, kv_c, k_pe, w_uk, w_uv, heads: int, tokens
     return rc, out_values, out
 
 
+def deepseek_moe_forward(x, expert_ids, expert_weights, w_gate, w_up, w_down, hidden: int, intermediate: int,
+                         num_experts: int, clamp_swiglu: bool = False, swiglu_limit: float = 0.0):
+    """fp32 expert MLP of one token over already routed experts.  Returns (return code, out, result)."""
+    x, w_gate, w_up, w_down, ew = [np.ascontiguousarray(a, dtype=np.float32)
+                                   for a in (x, w_gate, w_up, w_down, expert_weights)]
+    ids = np.ascontiguousarray(expert_ids, dtype=np.uint32)
+    out_values = np.zeros(hidden, dtype=np.float32)
+    req = ffi.structs["NervaCudaDeepSeekMoeForwardRequest"](
+        hidden_size=hidden, intermediate_size=intermediate, num_experts=num_experts, top_k=ids.size,
+        clamp_swiglu=int(clamp_swiglu), swiglu_limit=swiglu_limit, input=x.ctypes.data, expert_ids=ids.ctypes.data,
+        expert_weights=ew.ctypes.data, w_gate=w_gate.ctypes.data, w_up=w_up.ctypes.data, w_down=w_down.ctypes.data,
+        output=out_values.ctypes.data)
+    out = ffi.structs["NervaCudaDeepSeekMoeForwardResult"]()
+    rc = ffi.lib().nerva_cuda_deepseek_moe_forward(C.byref(req), C.byref(out))
+    return rc, out_values, out
+
+
 def synth_normal_bf16(seed: int, tensor_id: int, count: int, std: float) -> np.ndarray:
     """Multi-threaded native twin of nerva_b200.synth.normal_bf16 (same bits)."""
     out = np.empty(count, dtype=np.uint16)

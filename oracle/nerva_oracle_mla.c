@@ -70,3 +70,44 @@ int oracle_mla_decode(const float *q_nope, const float *q_pe, const float *kv_c,
   free(latent);
   return status;
 }
+
+/* DeepSeek expert MLP of one token, fp32 (native/cuda/deepseek/nerva_cuda_deepseek_moe.cu:456-510;
+ * SwiGLU with the optional clamp of :118-127: gate = min(gate, limit), up clamped to +-limit).
+ * Experts are added in rank order: out += weight[rank] * W_down[e] . act.  Returns 0, -1, or -2 when
+ * an expert id is out of range. */
+static float mlp_dot(const float *a, const float *b, uint32_t n) {
+  float sum = 0.0f;
+  for (uint32_t i = 0; i < n; ++i) sum += a[i] * b[i];
+  return sum;
+}
+
+int oracle_moe_forward(const float *input, const uint32_t *expert_ids, const float *expert_weights,
+                       const float *w_gate, const float *w_up, const float *w_down, float *output,
+                       uint32_t hidden, uint32_t intermediate, uint32_t num_experts, uint32_t top_k,
+                       uint32_t clamp_swiglu, float swiglu_limit) {
+  if (hidden == 0 || intermediate == 0 || num_experts == 0 || top_k == 0) return -1;
+  float *act = (float *)malloc(sizeof(float) * intermediate);
+  if (!act) return -1;
+  for (uint32_t i = 0; i < hidden; ++i) output[i] = 0.0f;
+  for (uint32_t rank = 0; rank < top_k; ++rank) {
+    const uint32_t e = expert_ids[rank];
+    if (e >= num_experts) {
+      free(act);
+      return -2;
+    }
+    const uint64_t base = (uint64_t)e * intermediate * hidden;
+    for (uint32_t row = 0; row < intermediate; ++row) {
+      float gate = mlp_dot(w_gate + base + (uint64_t)row * hidden, input, hidden);
+      float up = mlp_dot(w_up + base + (uint64_t)row * hidden, input, hidden);
+      if (clamp_swiglu != 0) {
+        gate = fminf(gate, swiglu_limit);
+        up = fminf(fmaxf(up, -swiglu_limit), swiglu_limit);
+      }
+      act[row] = gate / (1.0f + expf(-gate)) * up;
+    }
+    for (uint32_t i = 0; i < hidden; ++i)
+      output[i] += expert_weights[rank] * mlp_dot(w_down + base + (uint64_t)i * intermediate, act, intermediate);
+  }
+  free(act);
+  return 0;
+}

@@ -334,3 +334,18 @@ def mla_decode(q_nope, q_pe, kv_c, k_pe, w_uk, w_uv, heads, tokens, kv_lora_rank
     rc = fn(*[_pf(a) for a in arrays], _pf(out), heads, tokens, kv_lora_rank, qk_nope_head_dim, qk_rope_head_dim,
             v_head_dim, softmax_scale)
     return rc, out
+
+
+def moe_forward(x, expert_ids, expert_weights, w_gate, w_up, w_down, hidden, intermediate, num_experts,
+                clamp_swiglu=False, swiglu_limit=0.0):
+    """fp32 expert MLP of one token; returns (status, out [hidden])."""
+    x, w_gate, w_up, w_down, ew = [np.ascontiguousarray(a, dtype=np.float32)
+                                   for a in (x, w_gate, w_up, w_down, expert_weights)]
+    ids = np.ascontiguousarray(expert_ids, dtype=np.uint32)
+    out = np.zeros(hidden, dtype=np.float32)
+    fn = lib().oracle_moe_forward
+    fn.restype = C.c_int
+    fn.argtypes = [_f32p, _u32p, _f32p, _f32p, _f32p, _f32p, _f32p] + [C.c_uint32] * 5 + [C.c_float]
+    rc = fn(_pf(x), _pu(ids), _pf(ew), _pf(w_gate), _pf(w_up), _pf(w_down), _pf(out), hidden, intermediate,
+            num_experts, ids.size, int(clamp_swiglu), swiglu_limit)
+    return rc, out
