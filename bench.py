@@ -311,7 +311,7 @@ def run_ours(args, cfg, rank: int, world: int) -> dict:
 
 
 def run_operator_workloads(kind: str) -> None:
-    """Per-operator measurements of BASELINE configs 3 and 4 through the per-op C ABI (host buffers in,
+    """Per-operator sweeps (isolated projection shapes, long-context attention) through the per-op C ABI (host buffers in,
     device time per launch out, L2 flushed between launches).  One JSON line per case."""
     from nerva_b200 import build, ops, synth
     build.build()

@@ -251,7 +251,8 @@ class Decoder:
 # ---- DeepSeek expert routers (oracle/nerva_oracle_router.c) and the reference's own header ----
 
 _REF_ROUTER_PATH = os.path.join(_HERE, "_ref", "libnerva_ref_router.so")
-_REFERENCE_HEADER = "/root/reference/native/cuda/deepseek/deepseek_router.cuh"
+_REFERENCE_ROOT = os.environ.get("NERVA_REFERENCE_ROOT", "/root/reference")
+_REFERENCE_HEADER = os.path.join(_REFERENCE_ROOT, "native/cuda/deepseek/deepseek_router.cuh")
 _ref_router = None
 
 
@@ -260,7 +261,7 @@ def build_ref(force: bool = False):
     checkout exists.  Returns the library path, or None when neither checkout nor a prebuilt
     library is there."""
     if os.path.exists(_REFERENCE_HEADER) and (force or not os.path.exists(_REF_ROUTER_PATH)):
-        subprocess.run(["make", "-C", _HERE, "ref"], check=True, capture_output=True)
+        subprocess.run(["make", "-C", _HERE, "ref", f"REFERENCE_ROOT={_REFERENCE_ROOT}"], check=True, capture_output=True)
     return _REF_ROUTER_PATH if os.path.exists(_REF_ROUTER_PATH) else None
 
 
