@@ -862,6 +862,14 @@ int nerva_b200_gqa_decode_attention_static_scratch(
  * non-finite values skipped).  Host pointers. */
 int nerva_b200_greedy_argmax(const float *logits, uint32_t count, uint32_t *token);
 
+/* One token from f32 host logits at `position` with the decode step's sampler: arg-max when
+ * temperature is 0 or top_k is 1, Gumbel-max when top_k is 0 and top_p >= 0.999999, else the
+ * top-k / top-p draw, all seeded by (seed, position) as the reference's final-head sampler
+ * (native/cuda/hf_decode_sequence/sampler.cu:66-408) seeds them.  temperature must be finite
+ * and >= 0, top_p in (0, 1]; -1 otherwise. */
+int nerva_b200_sample_token(const float *logits, uint32_t count, uint32_t position, float temperature,
+                            float top_p, uint32_t top_k, uint64_t seed, uint32_t *token);
+
 /* Fills host memory with the synthetic checkpoint generator of
  * include/nerva_synth.h (multi-threaded; same bits as the header). */
 void nerva_b200_synth_normal_bf16(uint64_t seed, uint64_t tensor_id, uint64_t count, float std,

@@ -221,6 +221,16 @@ struct TpSample {
 cudaError_t launch_sample_greedy(cudaStream_t stream, const StepState &st, const float *best_value,
                                  const uint32_t *best_index, uint32_t partials, uint32_t sample,
                                  bool pdl = false, const TpSample *tp = nullptr);
+// ---- temperature / top-k / top-p sampling ----
+// Read from device memory at every step, so that a captured graph does not depend on the values.
+struct SamplerParams {
+  float temperature, top_p;
+  uint32_t top_k, reserved;
+  uint64_t seed;
+};
+// One block over the fp32 logits: writes the token slot at the cursor and advances the cursor.
+cudaError_t launch_sample_general(cudaStream_t stream, const StepState &st, const float *logits,
+                                  const SamplerParams *params, bool pdl = false);
 // Stand-alone argmax over logits (used by the per-op entry point).
 cudaError_t launch_argmax(cudaStream_t stream, const float *logits, uint32_t count,
                           uint32_t *token_out);

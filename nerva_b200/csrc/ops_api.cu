@@ -369,6 +369,52 @@ extern "C" int nerva_b200_greedy_argmax(const float *logits, uint32_t count, uin
   return 0;
 }
 
+// One token from host logits at `position` with the step's temperature / top-k / top-p sampler
+// (the configuration is normalised and the arg-max cases are taken as in the session).
+extern "C" int nerva_b200_sample_token(const float *logits, uint32_t count, uint32_t position, float temperature,
+                                       float top_p, uint32_t top_k, uint64_t seed, uint32_t *token) {
+  set_last_error("");
+  if (logits == nullptr || token == nullptr || count == 0 || position == UINT32_MAX || !isfinite(temperature) ||
+      temperature < 0.0f || !isfinite(top_p) || top_p <= 0.0f || top_p > 1.0f)
+    return -1;
+  DeviceBuffers buf;
+  float *d_logits = nullptr;
+  uint32_t *d_word = nullptr;
+  SamplerParams *d_params = nullptr;
+  NervaCudaSyntheticTokenSlot *d_slots = nullptr;
+  cudaError_t err = buf.alloc(&d_logits, static_cast<uint64_t>(count));
+  if (err == cudaSuccess) err = buf.alloc(&d_word, uint64_t{2});
+  if (err == cudaSuccess) err = buf.alloc(&d_params, uint64_t{1});
+  if (err == cudaSuccess) err = buf.alloc(&d_slots, static_cast<uint64_t>(position) + 1u);
+  if (err == cudaSuccess) err = cudaMemcpy(d_logits, logits, static_cast<uint64_t>(count) * 4u, cudaMemcpyHostToDevice);
+  if (err == cudaSuccess) err = cudaMemcpy(d_word, &position, 4, cudaMemcpyHostToDevice);
+  if (err != cudaSuccess) {
+    set_last_error(cudaGetErrorString(err));
+    return -1;
+  }
+  if (!(temperature > 0.0f) || top_k == 1) {
+    err = launch_argmax(nullptr, d_logits, count, d_word + 1);
+    if (err == cudaSuccess) err = cudaMemcpy(token, d_word + 1, 4, cudaMemcpyDeviceToHost);
+  } else {
+    const SamplerParams params{temperature, top_p, top_k, 0u, seed};
+    StepState st{};
+    st.cursor = d_word;
+    st.slots = d_slots;
+    st.max_context = position + 1u;
+    st.vocab = count;
+    err = cudaMemcpy(d_params, &params, sizeof(params), cudaMemcpyHostToDevice);
+    if (err == cudaSuccess) err = launch_sample_general(nullptr, st, d_logits, d_params, false);
+    NervaCudaSyntheticTokenSlot slot{};
+    if (err == cudaSuccess) err = cudaMemcpy(&slot, d_slots + position, sizeof(slot), cudaMemcpyDeviceToHost);
+    if (err == cudaSuccess) *token = slot.token;
+  }
+  if (err != cudaSuccess) {
+    set_last_error(cudaGetErrorString(err));
+    return -1;
+  }
+  return 0;
+}
+
 // A rectangular block of a row-major tensor with `full_cols` columns: the shard
 // generator of the tensor-parallel tests and bench (same bits as the whole tensor).
 extern "C" void nerva_b200_synth_normal_bf16_block(uint64_t seed, uint64_t tensor_id, uint64_t full_cols,

@@ -251,6 +251,7 @@ bool plan_state(Session *s, StaticArena &arena, void *base) {
   ok = ok && carve(arena, base, static_cast<uint64_t>(s->max_context), &s->device_prompt);
   ok = ok && carve(arena, base, uint64_t{4}, &s->device_cursor);
   ok = ok && carve(arena, base, uint64_t{4}, &s->device_error);
+  ok = ok && carve(arena, base, uint64_t{1}, &s->device_sampler);
   uint64_t moe_scratch = 0;
   for (const LayerLayout &L : s->layout.layers) {
     if (L.mlp_kind == NERVA_MLP_KIND_SPARSE_MOE)
@@ -510,6 +511,7 @@ cudaError_t enqueue_step(Session *s, uint32_t splits, uint32_t sample, uint64_t 
   };
   if (s->engine == 1 && prof == nullptr) {
     if (launches != nullptr) *launches = 1;
+    if (sample == 2) return cudaErrorNotSupported;  // the one-kernel engine only has the arg-max sampler
     return enqueue_step_kernel(s, splits, sample);
   }
   profile_mark(s, prof, kBucketEmbed);
@@ -784,8 +786,11 @@ cudaError_t enqueue_step(Session *s, uint32_t splits, uint32_t sample, uint64_t 
         exchange.arrivals[q] = comm_at<unsigned long long>(s->comm_peers[q], comm.arrivals_s);
       }
     }
-    err = launch_sample_greedy(s->stream, st, s->best_value, s->best_index, partials, sample, s->use_pdl,
-                               tp ? &exchange : nullptr);
+    if (sample == 2)
+      err = launch_sample_general(s->stream, st, s->logits, s->device_sampler, s->use_pdl);
+    else
+      err = launch_sample_greedy(s->stream, st, s->best_value, s->best_index, partials, sample, s->use_pdl,
+                                 tp ? &exchange : nullptr);
     n += 1;
     profile_mark(s, prof, kBucketSampling);
   }
@@ -948,8 +953,31 @@ cudaError_t reset_request_state(Session *s, const uint32_t *prompt, uint32_t cou
   if (err == cudaSuccess)
     err = cudaMemcpyAsync(s->device_prompt, prompt, bytes, cudaMemcpyHostToDevice, s->stream);
   out->h2d_bytes = bytes;
+  if (err == cudaSuccess && s->sample_kind == 2) {
+    err = cudaMemcpyAsync(s->device_sampler, &s->host_sampler, sizeof(SamplerParams), cudaMemcpyHostToDevice,
+                          s->stream);
+    out->h2d_bytes += sizeof(SamplerParams);
+  }
   s->logits_valid = false;
   return err;
+}
+
+// Makes `config` the sampler of the request that is starting: normalised as the reference
+// does (hf_decode_sequence/sampler.cu:420-432), arg-max when temperature is 0 or top_k is 1.
+// The graphs read temperature, top-k, top-p and seed from device memory, so one captured
+// graph serves every non-greedy configuration.
+bool activate_sampler(Session *s, const NervaCudaHfDecodeSamplerConfig &config) {
+  if (sampler_greedy(config)) {
+    s->sample_kind = 1;
+    return true;
+  }
+  if (s->tp_world > 1 || s->engine != 0) {
+    set_last_error("temperature / top-k / top-p sampling needs engine 0 on one GPU");
+    return false;
+  }
+  s->sample_kind = 2;
+  s->host_sampler = SamplerParams{config.temperature, config.top_p, config.top_k, 0u, config.seed};
+  return true;
 }
 
 }  // namespace
@@ -1604,8 +1632,7 @@ extern "C" int nerva_cuda_hf_decode_sequence_session_start(
     if (request->prompt_tokens[i] >= s->dims.embed_vocab) return -1;
   }
   fill_header(s, out, 0, request->prompt_tokens[request->prompt_token_count - 1u]);
-  if (!sampler_greedy(request->sampler)) {
-    set_last_error("only greedy sampling is implemented");
+  if (!activate_sampler(s, request->sampler)) {
     out->cuda_error = static_cast<int32_t>(cudaErrorNotSupported);
     return -1;
   }
@@ -1617,7 +1644,7 @@ extern "C" int nerva_cuda_hf_decode_sequence_session_start(
   const uint32_t splits = splits_for(s, s->prompt_count);
   GraphEntry *quiet = nullptr, *sampled = nullptr;
   if (err == cudaSuccess && s->prompt_count > 1) err = ensure_graph(s, splits, 0, &quiet, out);
-  if (err == cudaSuccess) err = ensure_graph(s, splits, 1, &sampled, out);
+  if (err == cudaSuccess) err = ensure_graph(s, splits, s->sample_kind, &sampled, out);
   if (err == cudaSuccess) err = cudaEventRecord(s->ev_start, s->stream);
   for (uint32_t i = 0; err == cudaSuccess && i + 1 < s->prompt_count; ++i) {
     err = replay(s, quiet);
@@ -1683,7 +1710,7 @@ extern "C" int nerva_cuda_hf_decode_sequence_session_advance(
 
   cudaError_t err = cudaSuccess;
   GraphEntry *graph = nullptr;
-  if (run_count != 0) err = ensure_graph(s, splits_for(s, target), 1, &graph, out);
+  if (run_count != 0) err = ensure_graph(s, splits_for(s, target), s->sample_kind, &graph, out);
   if (err == cudaSuccess && run_count != 0) err = cudaEventRecord(s->ev_start, s->stream);
   for (uint32_t step = 0; err == cudaSuccess && step < run_count; ++step) {
     err = replay(s, graph);  // the hot loop: one graph launch per token, nothing else
@@ -1768,8 +1795,7 @@ extern "C" int nerva_cuda_hf_decode_sequence_session_run(
     if (request->prompt_tokens[i] >= s->dims.embed_vocab) return -1;
   }
   fill_header(s, out, request->steps, request->seed_token);
-  if (!sampler_greedy(request->sampler)) {
-    set_last_error("only greedy sampling is implemented");
+  if (!activate_sampler(s, request->sampler)) {
     out->cuda_error = static_cast<int32_t>(cudaErrorNotSupported);
     return -1;
   }
@@ -1779,7 +1805,7 @@ extern "C" int nerva_cuda_hf_decode_sequence_session_run(
   // One sampling graph replayed for every position, prompt included; samples at
   // prompt positions are never read (session_api_lifecycle.inc.cu:849-920).
   GraphEntry *graph = nullptr;
-  if (err == cudaSuccess) err = ensure_graph(s, splits_for(s, context_steps), 1, &graph, out);
+  if (err == cudaSuccess) err = ensure_graph(s, splits_for(s, context_steps), s->sample_kind, &graph, out);
   if (err == cudaSuccess) err = cudaEventRecord(s->ev_start, s->stream);
   for (uint32_t step = 0; err == cudaSuccess && step < context_steps; ++step) {
     err = replay(s, graph);
@@ -1885,6 +1911,8 @@ extern "C" int nerva_cuda_hf_decode_sequence_session_fork_shared_weights(
   s->observed = parent->observed;
   s->cursor = parent->cursor;
   s->logits_valid = parent->logits_valid;
+  s->sample_kind = parent->sample_kind;  // the parameters themselves came with the state block
+  s->host_sampler = parent->host_sampler;
   out->device_count = 1;
   out->dtype = s->dims.dtype;
   out->hidden = s->dims.hidden;

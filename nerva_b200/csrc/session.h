@@ -186,5 +186,9 @@ struct NervaCudaHfDecodeSequenceSession {
   uint32_t prompt_count = 0, has_eos = 0, eos_token = 0, seed_token = 0;
   uint32_t observed = 0, cursor = 0;
   bool logits_valid = false;
+  // Sampler of the active request: 1 = arg-max, 2 = temperature / top-k / top-p from device_sampler.
+  uint32_t sample_kind = 1;
+  nb::SamplerParams host_sampler{};
+  nb::SamplerParams *device_sampler = nullptr;
   uint64_t hot_path_allocations = 0;
 };

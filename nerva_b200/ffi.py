@@ -126,6 +126,8 @@ def lib() -> C.CDLL:
         "nerva_b200_gqa_decode_attention_static_scratch": [vp, vp, vp, vp, vp, C.c_uint32, C.c_uint32,
                                                            C.c_uint32, C.c_uint32, C.c_uint32, vp],
         "nerva_b200_greedy_argmax": [vp, C.c_uint32, P(C.c_uint32)],
+        "nerva_b200_sample_token": [vp, C.c_uint32, C.c_uint32, C.c_float, C.c_float, C.c_uint32, C.c_uint64,
+                                    P(C.c_uint32)],
         "nerva_b200_synth_normal_bf16": [C.c_uint64, C.c_uint64, C.c_uint64, C.c_float, vp],
         "nerva_b200_synth_normal_bf16_block": [C.c_uint64] * 7 + [C.c_float, vp],
     }

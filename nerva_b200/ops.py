@@ -63,6 +63,15 @@ def greedy_argmax(logits: np.ndarray) -> int:
     return token.value
 
 
+def sample_token(logits: np.ndarray, position: int, temperature: float, top_p: float, top_k: int, seed: int) -> int:
+    """One token with the decode step's seeded temperature / top-k / top-p sampler."""
+    logits = np.ascontiguousarray(logits, dtype=np.float32)
+    token = C.c_uint32(0)
+    _check(ffi.lib().nerva_b200_sample_token(logits.ctypes.data, logits.size, position, temperature, top_p, top_k,
+                                             seed, C.byref(token)), "sample_token")
+    return token.value
+
+
 def projection_bench(rows: int, cols: int, iterations: int = 20, warmup: int = 5, block_tokens: int = 0,
                      dtype: int = 1):
     req = ffi.ProjectionBenchRequest(dtype=dtype, rows=rows, cols=cols, iterations=iterations,

@@ -55,6 +55,11 @@ def greedy_sampler() -> "ffi.SamplerConfig":
     return ffi.SamplerConfig(temperature=0.0, top_p=1.0, top_k=0, reserved=0, seed=0)
 
 
+def sampler_config(temperature: float = 0.7, top_p: float = 0.9, top_k: int = 0, seed: int = 0) -> "ffi.SamplerConfig":
+    """Sampler of a request; the defaults are the reference's (hf_decode_sequence/sampler.cu:411-419)."""
+    return ffi.SamplerConfig(temperature=temperature, top_p=top_p, top_k=top_k, reserved=0, seed=seed)
+
+
 _LAYER_TENSORS = {
     "rms_attn": "rms_attn_weight", "rms_mlp": "rms_mlp_weight", "w_q": "w_q", "w_k": "w_k", "w_v": "w_v",
     "w_o": "w_o", "q_norm": "q_norm_weight", "k_norm": "k_norm_weight", "q_bias": "q_bias", "k_bias": "k_bias",
@@ -189,13 +194,14 @@ class CudaHfDecodeSequenceSession:
                                                                                  C.byref(handle))
         return self._from_handle(self, handle, res, _status(rc, res.status, res.cuda_error, res.device_count))
 
-    def run(self, prompt_tokens, steps: int, eos_token=None) -> Summary:
+    def run(self, prompt_tokens, steps: int, eos_token=None, sampler=None) -> Summary:
         prompt = np.ascontiguousarray(prompt_tokens, dtype=np.uint32)
         tokens = np.zeros(max(steps, 1), dtype=np.uint32)
         req = ffi.RunRequest(session=self._handle, steps=steps, seed_token=int(prompt[-1]) if prompt.size else 0,
                              prompt_tokens=_ptr(prompt), prompt_token_count=prompt.size,
                              has_eos_token=int(eos_token is not None), eos_token=eos_token or 0,
-                             output_tokens=_ptr(tokens), output_token_capacity=steps, sampler=greedy_sampler())
+                             output_tokens=_ptr(tokens), output_token_capacity=steps,
+                             sampler=sampler or greedy_sampler())
         out = ffi.SequenceResult()
         rc = ffi.lib().nerva_cuda_hf_decode_sequence_session_run(C.byref(req), C.byref(out))
         return Summary(_status(rc, out.status, out.cuda_error, out.device_count),

@@ -253,14 +253,17 @@ class Decoder:
 _REF_ROUTER_PATH = os.path.join(_HERE, "_ref", "libnerva_ref_router.so")
 _REFERENCE_ROOT = os.environ.get("NERVA_REFERENCE_ROOT", "/root/reference")
 _REFERENCE_HEADER = os.path.join(_REFERENCE_ROOT, "native/cuda/deepseek/deepseek_router.cuh")
+_REF_SAMPLER_PATH = os.path.join(_HERE, "_ref", "libnerva_ref_sampler.so")
 _ref_router = None
+_ref_sampler = None
 
 
 def build_ref(force: bool = False):
     """Compiles the reference's router header for the host (oracle/_ref/), where the reference
     checkout exists.  Returns the library path, or None when neither checkout nor a prebuilt
     library is there."""
-    if os.path.exists(_REFERENCE_HEADER) and (force or not os.path.exists(_REF_ROUTER_PATH)):
+    if os.path.exists(_REFERENCE_HEADER) and (force or not os.path.exists(_REF_ROUTER_PATH)
+                                              or not os.path.exists(_REF_SAMPLER_PATH)):
         subprocess.run(["make", "-C", _HERE, "ref", f"REFERENCE_ROOT={_REFERENCE_ROOT}"], check=True, capture_output=True)
     return _REF_ROUTER_PATH if os.path.exists(_REF_ROUTER_PATH) else None
 
@@ -350,3 +353,47 @@ def moe_forward(x, expert_ids, expert_weights, w_gate, w_up, w_down, hidden, int
     rc = fn(_pf(x), _pu(ids), _pf(ew), _pf(w_gate), _pf(w_up), _pf(w_down), _pf(out), hidden, intermediate,
             num_experts, ids.size, int(clamp_swiglu), swiglu_limit)
     return rc, out
+
+
+def sampler_uniform(seed: int, position: int, token: int, salt: int) -> float:
+    fn = lib().oracle_sampler_uniform
+    fn.restype = C.c_float
+    fn.argtypes = [C.c_uint64, C.c_uint32, C.c_uint32, C.c_uint32]
+    return fn(seed, position, token, salt)
+
+
+def sample_token(logits, position: int, temperature: float, top_p: float, top_k: int, seed: int):
+    """Restated sampler: returns (token, margin), margin being the relative distance of the
+    closest comparison the choice depended on (inf for arg-max)."""
+    logits = np.ascontiguousarray(logits, dtype=np.float32)
+    fn = lib().oracle_sample_token
+    fn.restype = C.c_uint32
+    fn.argtypes = [_f32p, C.c_uint32, C.c_uint32, C.c_float, C.c_float, C.c_uint32, C.c_uint64, _f32p]
+    margin = C.c_float(0.0)
+    token = fn(_pf(logits), logits.size, position, temperature, top_p, top_k, seed, C.byref(margin))
+    return token, margin.value
+
+
+def ref_sampler_lib():
+    """The reference's sampler kernel behind a host wrapper (needs a GPU to run), or None."""
+    global _ref_sampler
+    if _ref_sampler is None:
+        build_ref()
+        if not os.path.exists(_REF_SAMPLER_PATH):
+            return None
+        _ref_sampler = C.CDLL(_REF_SAMPLER_PATH)
+        _ref_sampler.ref_sample_token.restype = C.c_int
+        _ref_sampler.ref_sample_token.argtypes = [_f32p, C.c_uint32, C.c_uint32, C.c_float, C.c_float, C.c_uint32,
+                                                  C.c_uint64, _u32p]
+    return _ref_sampler
+
+
+def ref_sample_token(logits, position: int, temperature: float, top_p: float, top_k: int, seed: int) -> int:
+    """One token from the reference's own kernel on the current CUDA device."""
+    logits = np.ascontiguousarray(logits, dtype=np.float32)
+    token = C.c_uint32(0)
+    rc = ref_sampler_lib().ref_sample_token(_pf(logits), logits.size, position, temperature, top_p, top_k, seed,
+                                            C.cast(C.byref(token), _u32p))
+    if rc != 0:
+        raise RuntimeError(f"reference sampler failed with CUDA error {rc}")
+    return token.value
