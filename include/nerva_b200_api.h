@@ -488,6 +488,53 @@ typedef struct NervaCudaHfDecodeSequenceSessionAdvanceRequest {
   uint32_t output_token_capacity;
 } NervaCudaHfDecodeSequenceSessionAdvanceRequest;
 
+/* nerva_cuda_api.h:936-943.  `sessions` is an array of session_count handles;
+ * output_tokens[i] receives the token of sessions[i] when that session took part. */
+typedef struct NervaCudaHfDecodeSequenceBatchAdvanceRequest {
+  NervaCudaHfDecodeSequenceSession **sessions;
+  uint32_t session_count;
+  uint32_t target_block_tokens;
+  uint32_t min_block_tokens;
+  uint32_t *output_tokens;
+  uint32_t output_token_capacity;
+} NervaCudaHfDecodeSequenceBatchAdvanceRequest;
+
+/* nerva_cuda_api.h:945-976.  reason: 0 ready, 1 invalid request, 2 no sessions,
+ * 3 no ready sessions, 4 shared weights unproven (no descriptor hash), 5 fewer compatible
+ * ready sessions than min_block_tokens (hf_decode_sequence/session_prelude.inc.cu:56-64). */
+typedef struct NervaCudaHfDecodeSequenceBatchAdvanceResult {
+  int32_t status;
+  int32_t cuda_error;
+  int32_t device_count;
+  uint32_t reason;
+  uint32_t exact;
+  uint32_t requested_session_count;
+  uint32_t eligible_session_count;
+  uint32_t block_tokens;
+  uint32_t target_block_tokens;
+  uint32_t min_block_tokens;
+  uint32_t dtype;
+  uint32_t layer_count;
+  uint32_t observed_tokens;
+  uint32_t last_token;
+  uint64_t observed_token_hash;
+  uint64_t d2h_bytes;
+  uint64_t projection_elapsed_ns;
+  uint64_t qkv_elapsed_ns;
+  uint64_t attention_output_elapsed_ns;
+  uint64_t gate_up_elapsed_ns;
+  uint64_t down_elapsed_ns;
+  uint64_t lm_head_elapsed_ns;
+  uint64_t pack_kernel_launches;
+  uint64_t projection_kernel_launches;
+  uint64_t scatter_kernel_launches;
+  uint64_t dependency_kernel_launches;
+  uint64_t experimental_rt_selector_launches;
+  uint64_t sampling_kernel_launches;
+  uint64_t sync_calls;
+  uint64_t hot_path_allocations;
+} NervaCudaHfDecodeSequenceBatchAdvanceResult;
+
 /* nerva_cuda_api.h:1075-1082 */
 typedef struct NervaCudaProjectionBenchRequest {
   uint32_t dtype;
@@ -585,6 +632,16 @@ int nerva_cuda_hf_decode_sequence_session_start(
 int nerva_cuda_hf_decode_sequence_session_advance(
     const NervaCudaHfDecodeSequenceSessionAdvanceRequest *request,
     NervaCudaHfDecodeSequenceResult *out);
+/* nerva_cuda_api.h:2209.  Advances by one token every started, unfinished session of the
+ * request that has caught up with its cursor and shares the first such session's weights
+ * (same descriptor hash and shape), up to target_block_tokens (at most 32) of them, provided
+ * at least min_block_tokens qualify; otherwise status 0 with the reason and no session
+ * touched (hf_decode_sequence/session_api_batch_fork_destroy.inc.cu:1-309).  Tokens are
+ * the ones session_advance(1) would give.  Here the sessions' steps are replayed on their
+ * own streams side by side; the weights are streamed once per session, not once per block. */
+int nerva_cuda_hf_decode_sequence_batch_advance_one(
+    const NervaCudaHfDecodeSequenceBatchAdvanceRequest *request,
+    NervaCudaHfDecodeSequenceBatchAdvanceResult *out);
 /* nerva_cuda_api.h:2212 */
 int nerva_cuda_hf_decode_sequence_session_fork_shared_weights(
     const NervaCudaHfDecodeSequenceSessionForkSharedWeightsRequest *request,

@@ -82,6 +82,8 @@ struct ProjectionParams {
   float eps;
   float *resid_out;             // optional
   uint32_t epilogue;
+  const float *resid_in;        // kEpilogueStore, optional: out_f32[row] = y + resid_in[row], the residual
+                                // add done by the row's owner so that the next prologue reads one vector
   float *out_f32;
   uint16_t *out_bf16;
   float *best_value;     // [blocks] kEpilogueArgmax

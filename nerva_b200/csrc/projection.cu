@@ -75,10 +75,22 @@ __global__ void __launch_bounds__(kStreamThreads, 1) projection_stream_kernel(Pr
   block_row_range(p.rows, unit, blockIdx.x, gridDim.x, &row_begin, &row_end);
   const uint32_t rows_local = row_end - row_begin;
   for (uint32_t r = threadIdx.x; r < rows_local; r += blockDim.x) row_total[r] = 0.0f;
+  // A residual stream that arrives already summed needs one vector after the wait; the norm
+  // weights come in before it.
+  const bool norm_single = p.prologue == kPrologueAddNorm && p.add_b == nullptr && p.add_bias == nullptr &&
+                           p.resid_out == nullptr && !(TP && p.gather.world > 1) &&
+                           norm_single_eligible(p.add_a, p.norm_weight, p.cols);
+  NormWeightRegs norm_regs;
+  if (norm_single) norm_weights_preload(norm_regs, p.norm_weight, p.cols);
 
   // Everything above is independent of the previous kernel; its output is read below.
   pdl_wait();
   stamp(p.stamps, kStampAfterWait);
+  // kEpilogueStore with a fused residual add: this thread's row of the residual, fetched now so
+  // that its latency hides behind the weight stream instead of sitting at the kernel's tail.
+  float resid_first = 0.0f;
+  if (EPI == kEpilogueStore && p.resid_in != nullptr && threadIdx.x < rows_local)
+    resid_first = __ldcg(p.resid_in + row_begin + threadIdx.x);
   if (p.prologue == kProloguePlain) {
     const uint4 *src = reinterpret_cast<const uint4 *>(p.x_bf16);
     uint4 *dst = reinterpret_cast<uint4 *>(x);
@@ -87,6 +99,8 @@ __global__ void __launch_bounds__(kStreamThreads, 1) projection_stream_kernel(Pr
     if (TP && p.gather.world > 1 && p.add_b != nullptr) {
       // the partial sums of the ranks arrive over NVLink while this polls
       gather_prologue(p, x, sh.scratch);
+    } else if (norm_single) {
+      norm_single_to_smem(x, p.add_a, norm_regs, p.eps, p.cols, sh.scratch);
     } else {
       add_norm_to_smem(x, p.add_a, p.add_b, p.add_bias, p.norm_weight, p.eps, p.cols,
                        blockIdx.x == 0 ? p.resid_out : nullptr, sh.scratch);
@@ -113,7 +127,9 @@ __global__ void __launch_bounds__(kStreamThreads, 1) projection_stream_kernel(Pr
       }
     } else {
       for (uint32_t r = threadIdx.x; r < rows_local; r += blockDim.x) {
-        p.out_f32[row_begin + r] = stream_row_total(sh.stream, row_total, r);
+        float y = stream_row_total(sh.stream, row_total, r);
+        if (p.resid_in != nullptr) y += r == threadIdx.x ? resid_first : __ldcg(p.resid_in + row_begin + r);
+        p.out_f32[row_begin + r] = y;
       }
     }
   } else if (EPI == kEpilogueSwiglu) {
@@ -212,7 +228,8 @@ __global__ void projection_generic_kernel(ProjectionParams p, const uint16_t *x)
           p.out_bf16[r >> 1] = f32_to_bf16_bits(silu(gate) * v);
         }
       } else {
-        if (lane == 0) p.out_f32[r] = v;
+        if (lane == 0)
+          p.out_f32[r] = p.epilogue == kEpilogueStore && p.resid_in != nullptr ? v + p.resid_in[r] : v;
         if (p.epilogue == kEpilogueArgmax && isfinite(v) && candidate_better(v, r, best_v, best_i)) {
           best_v = v;
           best_i = r;

@@ -514,6 +514,11 @@ cudaError_t enqueue_step(Session *s, uint32_t splits, uint32_t sample, uint64_t 
     if (sample == 2) return cudaErrorNotSupported;  // the one-kernel engine only has the arg-max sampler
     return enqueue_step_kernel(s, splits, sample);
   }
+  // Dense single-GPU models without an O bias: O and down add the residual stream to their
+  // own output (row by row, by the row's owner), so the next prologue reads one summed vector.
+  // The sum is the same two-operand add the prologue would have done.
+  bool fused_resid = !tp && !s->has_moe;
+  for (const LayerLayout &L : s->layout.layers) fused_resid = fused_resid && arena_at(s, L.o_bias) == nullptr;
   profile_mark(s, prof, kBucketEmbed);
   cudaError_t err = launch_embed(s->stream, st, arena_at(s, s->layout.embeddings), d.hidden, s->h_b);
   n += 1;
@@ -531,13 +536,13 @@ cudaError_t enqueue_step(Session *s, uint32_t splits, uint32_t sample, uint64_t 
     p.prologue = kPrologueAddNorm;
     p.x_bf16 = s->x_scratch;
     p.add_a = s->h_b;
-    p.add_b = l == 0 ? nullptr : s->down;
+    p.add_b = l == 0 || fused_resid ? nullptr : s->down;
     if (tp && l != 0) {
       p.add_b = s->down;  // placeholder: the sum arrives in the exchange buffer
       p.gather = gather_from(comm.recv_d, l);  // down of layer l-1 was exchange number l
     }
     p.norm_weight = arena_at(s, L.rms_attn);
-    p.resid_out = s->h_a;
+    p.resid_out = fused_resid ? nullptr : s->h_a;
     p.epilogue = kEpilogueStore;
     p.out_f32 = s->qkv;
     p.stamps = stamps_for(5u * l);
@@ -635,6 +640,10 @@ cudaError_t enqueue_step(Session *s, uint32_t splits, uint32_t sample, uint64_t 
     p.x_bf16 = s->attn_bf16;
     p.epilogue = kEpilogueStore;
     p.out_f32 = s->o_out;
+    if (fused_resid) {
+      p.resid_in = s->h_b;  // the stream that entered the layer
+      p.out_f32 = s->h_a;   // the stream after attention
+    }
     if (tp) p.push = push_to(comm.recv_o, l + 1u);
     p.stamps = stamps_for(5u * l + 2u);
     err = launch_projection(s->stream, p, s->sm_count);
@@ -713,13 +722,13 @@ cudaError_t enqueue_step(Session *s, uint32_t splits, uint32_t sample, uint64_t 
     p.prologue = kPrologueAddNorm;
     p.x_bf16 = s->x_scratch;
     p.add_a = s->h_a;
-    p.add_b = s->o_out;
+    p.add_b = fused_resid ? nullptr : s->o_out;
     if (tp) {
       p.gather = gather_from(comm.recv_o, l + 1u);
     }
     p.add_bias = arena_at(s, L.o_bias);
     p.norm_weight = arena_at(s, L.rms_mlp);
-    p.resid_out = s->h_b;
+    p.resid_out = fused_resid ? nullptr : s->h_b;
     p.epilogue = kEpilogueSwiglu;
     p.out_bf16 = s->ff_bf16;
     p.stamps = stamps_for(5u * l + 3u);
@@ -740,6 +749,10 @@ cudaError_t enqueue_step(Session *s, uint32_t splits, uint32_t sample, uint64_t 
     p.x_bf16 = s->ff_bf16;
     p.epilogue = kEpilogueStore;
     p.out_f32 = s->down;
+    if (fused_resid) {
+      p.resid_in = s->h_a;
+      p.out_f32 = s->h_b;  // the stream that enters the next layer
+    }
     if (tp) p.push = push_to(comm.recv_d, l + 1u);
     p.stamps = stamps_for(5u * l + 4u);
     err = launch_projection(s->stream, p, s->sm_count);
@@ -758,12 +771,12 @@ cudaError_t enqueue_step(Session *s, uint32_t splits, uint32_t sample, uint64_t 
     p.prologue = kPrologueAddNorm;
     p.x_bf16 = s->x_scratch;
     p.add_a = s->h_b;
-    p.add_b = s->down;
+    p.add_b = fused_resid ? nullptr : s->down;
     if (tp) {
       p.gather = gather_from(comm.recv_d, d.layers);
     }
     p.norm_weight = arena_at(s, s->layout.final_norm);
-    p.resid_out = s->h_a;
+    p.resid_out = fused_resid ? nullptr : s->h_a;
     p.epilogue = kEpilogueArgmax;
     p.out_f32 = s->logits;
     p.best_value = s->best_value;
@@ -1849,6 +1862,158 @@ extern "C" int nerva_cuda_hf_decode_sequence_session_run(
 
 // Clones an active session's KV cache, token ring, cursor and request state;
 // the device weights are shared (session_api_batch_fork_destroy.inc.cu:311+).
+// One token for a block of sessions that share weights (reference:
+// hf_decode_sequence/session_api_batch_fork_destroy.inc.cu:1-309; selection, reasons, state
+// updates and result fields follow it).  The reference packs the sessions' activations and
+// runs each projection once per block; here every selected session replays its own captured
+// step on its own stream, all in flight together, which gives the same tokens and leaves the
+// weights to be streamed once per session.
+extern "C" int nerva_cuda_hf_decode_sequence_batch_advance_one(
+    const NervaCudaHfDecodeSequenceBatchAdvanceRequest *request,
+    NervaCudaHfDecodeSequenceBatchAdvanceResult *out) {
+  constexpr uint32_t kReady = 0, kInvalidRequest = 1, kNoSessions = 2, kNoReadySessions = 3,
+                     kSharedWeightsUnproven = 4, kInsufficientCompatibleReady = 5;
+  constexpr uint32_t kWorkspaceTokens = 32;  // hf_decode_sequence/types.cuh:63
+  if (out == nullptr) return -1;
+  memset(out, 0, sizeof(*out));
+  out->status = -1;
+  out->reason = kInvalidRequest;
+  if (request == nullptr) return -1;
+  out->requested_session_count = request->session_count;
+  out->target_block_tokens = request->target_block_tokens == 0 ? 1u : request->target_block_tokens;
+  out->min_block_tokens = request->min_block_tokens == 0 ? 1u : request->min_block_tokens;
+  if (request->session_count == 0) {
+    out->reason = kNoSessions;
+    out->status = 0;
+    return 0;
+  }
+  if (request->sessions == nullptr || request->output_tokens == nullptr ||
+      request->output_token_capacity < request->session_count)
+    return -1;
+  cudaError_t err = cudaGetDeviceCount(&out->device_count);
+  if (err != cudaSuccess) {
+    out->cuda_error = static_cast<int32_t>(err);
+    return -1;
+  }
+  auto ready = [](const Session *s) {
+    if (s == nullptr || !s->started || s->finished || s->prompt_count == 0 || s->cursor >= s->max_context)
+      return false;
+    // dense full-attention models whose heads span the hidden size (session_common.inc.cu:1078-1090),
+    // on the per-kernel engine of one GPU
+    if (s->dims.hidden < 128 || s->dims.heads * s->dims.head_dim != s->dims.hidden || s->has_moe ||
+        s->tp_world > 1 || s->engine != 0)
+      return false;
+    return s->prompt_count + s->observed == s->cursor + 1u;
+  };
+  auto same_model = [](const Session *a, const Session *b) {
+    return a->planned_weight_descriptor_hash != 0 &&
+           a->planned_weight_descriptor_hash == b->planned_weight_descriptor_hash &&
+           a->dims.dtype == b->dims.dtype && a->dims.hidden == b->dims.hidden && a->dims.heads == b->dims.heads &&
+           a->dims.kv_heads == b->dims.kv_heads && a->dims.head_dim == b->dims.head_dim &&
+           a->dims.intermediate == b->dims.intermediate && a->dims.vocab == b->dims.vocab &&
+           a->dims.layers == b->dims.layers && a->weights == b->weights;
+  };
+  uint32_t ready_count = 0;
+  bool any_hash = false;
+  for (uint32_t i = 0; i < request->session_count; ++i) {
+    const Session *s = request->sessions[i];
+    if (!ready(s)) continue;
+    ready_count += 1;
+    any_hash = any_hash || s->planned_weight_descriptor_hash != 0;
+  }
+  if (ready_count == 0 || !any_hash) {
+    out->reason = ready_count == 0 ? kNoReadySessions : kSharedWeightsUnproven;
+    out->status = 0;
+    return 0;
+  }
+  const Session *best = nullptr;
+  uint32_t best_count = 0;
+  for (uint32_t i = 0; i < request->session_count; ++i) {
+    const Session *candidate = request->sessions[i];
+    if (!ready(candidate) || candidate->planned_weight_descriptor_hash == 0) continue;
+    uint32_t compatible = 0;
+    for (uint32_t j = 0; j < request->session_count; ++j) {
+      if (ready(request->sessions[j]) && same_model(candidate, request->sessions[j])) compatible += 1;
+    }
+    if (compatible > best_count) {
+      best = candidate;
+      best_count = compatible;
+    }
+  }
+  out->eligible_session_count = best_count;
+  std::vector<uint32_t> selected;
+  const uint32_t max_block = std::min(out->target_block_tokens, kWorkspaceTokens);
+  for (uint32_t i = 0; best != nullptr && i < request->session_count && selected.size() < max_block; ++i) {
+    if (ready(request->sessions[i]) && same_model(best, request->sessions[i])) selected.push_back(i);
+  }
+  if (best == nullptr || best_count < out->min_block_tokens || selected.size() < out->min_block_tokens) {
+    out->reason = kInsufficientCompatibleReady;
+    out->status = 0;
+    return 0;
+  }
+  for (size_t a = 0; a < selected.size(); ++a) {  // a handle listed twice would be stepped twice
+    for (size_t b = a + 1; b < selected.size(); ++b) {
+      if (request->sessions[selected[a]] == request->sessions[selected[b]]) return -1;
+    }
+  }
+  out->reason = kReady;
+  out->exact = 1;
+  out->block_tokens = static_cast<uint32_t>(selected.size());
+  out->dtype = best->dims.dtype;
+  out->layer_count = best->dims.layers;
+
+  // Launch every session's step before waiting for any of them.
+  for (uint32_t index : selected) {
+    Session *s = request->sessions[index];
+    GraphEntry *graph = nullptr;
+    err = ensure_graph(s, splits_for(s, s->cursor + 1u), s->sample_kind, &graph, nullptr);
+    if (err == cudaSuccess) err = replay(s, graph);
+    const uint32_t slot = s->prompt_count - 1u + s->observed;
+    if (err == cudaSuccess)
+      err = cudaMemcpyAsync(s->host_slots + slot, s->device_slots + slot, sizeof(NervaCudaSyntheticTokenSlot),
+                            cudaMemcpyDeviceToHost, s->stream);
+    if (err == cudaSuccess)
+      err = cudaMemcpyAsync(s->host_error, s->device_error, sizeof(uint32_t), cudaMemcpyDeviceToHost, s->stream);
+    if (err != cudaSuccess) break;
+    out->d2h_bytes += sizeof(NervaCudaSyntheticTokenSlot);
+    out->projection_kernel_launches += 4ull * s->dims.layers + 1u;
+    out->sampling_kernel_launches += 1;
+  }
+  for (uint32_t index : selected) {  // also after a failed launch: nothing stays in flight
+    const cudaError_t sync = cudaStreamSynchronize(request->sessions[index]->stream);
+    out->sync_calls += 1;
+    if (err == cudaSuccess) err = sync;
+  }
+  if (err != cudaSuccess) {
+    set_last_error(cudaGetErrorString(err));
+    out->cuda_error = static_cast<int32_t>(err);
+    out->exact = 0;
+    return -1;
+  }
+  std::vector<uint32_t> observed;
+  for (uint32_t index : selected) {
+    Session *s = request->sessions[index];
+    out->hot_path_allocations += s->hot_path_allocations;
+    const uint32_t slot_start = s->prompt_count - 1u + s->observed;
+    const NervaCudaSyntheticTokenSlot &slot = s->host_slots[slot_start];
+    if (*s->host_error != 0 || !slots_valid(&slot, 1, slot_start)) {
+      out->status = -1;
+      return -1;
+    }
+    request->output_tokens[index] = slot.token;
+    observed.push_back(slot.token);
+    out->last_token = slot.token;
+    s->observed += 1;
+    s->cursor += 1;
+    s->logits_valid = true;
+    s->finished = (s->has_eos != 0 && slot.token == s->eos_token) || slot_start + 1u >= s->max_context;
+  }
+  out->observed_tokens = static_cast<uint32_t>(observed.size());
+  out->observed_token_hash = hash_tokens(observed.data(), out->observed_tokens);
+  out->status = out->observed_tokens == out->block_tokens ? 0 : -1;
+  return out->status == 0 ? 0 : -1;
+}
+
 extern "C" int nerva_cuda_hf_decode_sequence_session_fork_shared_weights(
     const NervaCudaHfDecodeSequenceSessionForkSharedWeightsRequest *request,
     NervaCudaHfDecodeSequenceSessionCreateResult *out,

@@ -87,6 +87,57 @@ __device__ __forceinline__ void add_norm_to_smem(uint16_t *x, const float *a, co
   }
 }
 
+// The same prologue for a residual stream that is already summed (the producer's epilogue
+// added its output to it): x = bf16(a * rsqrt(mean(a^2) + eps) * w).  The norm weights do not
+// depend on the previous kernel, so norm_weights_preload fetches them before the dependency
+// wait and the wait is followed by one 16-byte load per thread and iteration.
+struct NormWeightRegs {
+  uint2 w[kNormRegIters];
+};
+__device__ __forceinline__ bool norm_single_eligible(const float *a, const uint16_t *w, uint32_t cols) {
+  return cols % 4u == 0 && cols / 4u <= kNormRegIters * blockDim.x && (reinterpret_cast<uintptr_t>(a) & 15u) == 0 &&
+         (reinterpret_cast<uintptr_t>(w) & 7u) == 0;
+}
+__device__ __forceinline__ void norm_weights_preload(NormWeightRegs &regs, const uint16_t *w, uint32_t cols) {
+  const uint32_t vecs = cols / 4u;
+#pragma unroll
+  for (uint32_t k = 0; k < kNormRegIters; ++k) {
+    const uint32_t i = threadIdx.x + k * blockDim.x;
+    regs.w[k] = i < vecs ? reinterpret_cast<const uint2 *>(w)[i] : make_uint2(0u, 0u);
+  }
+}
+__device__ __forceinline__ void norm_single_to_smem(uint16_t *x, const float *a, const NormWeightRegs &regs,
+                                                    float eps, uint32_t cols, float *scratch) {
+  const uint32_t vecs = cols / 4u;
+  float4 r[kNormRegIters];
+  float sumsq = 0.0f;
+#pragma unroll
+  for (uint32_t k = 0; k < kNormRegIters; ++k) {
+    const uint32_t i = threadIdx.x + k * blockDim.x;
+    if (i < vecs) {
+      const float4 v = __ldcg(reinterpret_cast<const float4 *>(a) + i);
+      r[k] = v;
+      sumsq += v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w;
+    }
+  }
+  const float total = block_sum(sumsq, scratch);
+  const float scale = rsqrtf(total / static_cast<float>(cols) + eps);
+#pragma unroll
+  for (uint32_t k = 0; k < kNormRegIters; ++k) {
+    const uint32_t i = threadIdx.x + k * blockDim.x;
+    if (i < vecs) {
+      const float4 v = r[k];
+      const uint2 wb = regs.w[k];
+      uint2 out;
+      out.x = static_cast<uint32_t>(f32_to_bf16_bits(v.x * scale * bf16x2_lo(wb.x))) |
+              (static_cast<uint32_t>(f32_to_bf16_bits(v.y * scale * bf16x2_hi(wb.x))) << 16);
+      out.y = static_cast<uint32_t>(f32_to_bf16_bits(v.z * scale * bf16x2_lo(wb.y))) |
+              (static_cast<uint32_t>(f32_to_bf16_bits(v.w * scale * bf16x2_hi(wb.y))) << 16);
+      reinterpret_cast<uint2 *>(x)[i] = out;
+    }
+  }
+}
+
 // Tensor-parallel form of the same prologue: `b` is the sum over the ranks of
 // partial vectors that arrive from the other GPUs while this runs.  recv holds
 // [world][cols] 8-byte entries, value bits in the low word and a tag in the high

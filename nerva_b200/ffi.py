@@ -98,6 +98,9 @@ def lib() -> C.CDLL:
         "nerva_cuda_hf_decode_sequence_session_start": [P(StartRequest), P(SequenceResult)],
         "nerva_cuda_hf_decode_sequence_session_advance": [P(AdvanceRequest), P(SequenceResult)],
         "nerva_cuda_hf_decode_sequence_session_fork_shared_weights": [P(ForkRequest), P(CreateResult), P(vp)],
+        "nerva_cuda_hf_decode_sequence_batch_advance_one": [
+            P(structs["NervaCudaHfDecodeSequenceBatchAdvanceRequest"]),
+            P(structs["NervaCudaHfDecodeSequenceBatchAdvanceResult"])],
         "nerva_cuda_hf_decode_sequence_session_destroy": [vp, P(CreateResult)],
         "nerva_cuda_hf_decode_sequence_u16": [P(SequenceRequest), P(SequenceResult)],
         "nerva_cuda_projection_bench": [P(ProjectionBenchRequest), P(ProjectionBenchResult)],

@@ -194,6 +194,22 @@ class CudaHfDecodeSequenceSession:
                                                                                  C.byref(handle))
         return self._from_handle(self, handle, res, _status(rc, res.status, res.cuda_error, res.device_count))
 
+    @staticmethod
+    def batch_advance_one(sessions, target_block_tokens: int = 0, min_block_tokens: int = 0) -> Summary:
+        """One token for every ready session that shares weights with the others (reference:
+        CudaHfDecodeSequenceSession::batch_advance_one, decode/hf_sequence/session/request.rs:575-597).
+        tokens[i] is sessions[i]'s token, or 0xFFFFFFFF when that session did not take part."""
+        handles = (C.c_void_p * max(len(sessions), 1))(*[s.raw_handle() for s in sessions])
+        tokens = np.full(max(len(sessions), 1), 0xFFFFFFFF, dtype=np.uint32)
+        req = ffi.structs["NervaCudaHfDecodeSequenceBatchAdvanceRequest"](
+            sessions=C.cast(handles, C.c_void_p), session_count=len(sessions),
+            target_block_tokens=target_block_tokens, min_block_tokens=min_block_tokens,
+            output_tokens=_ptr(tokens), output_token_capacity=len(sessions))
+        out = ffi.structs["NervaCudaHfDecodeSequenceBatchAdvanceResult"]()
+        rc = ffi.lib().nerva_cuda_hf_decode_sequence_batch_advance_one(C.byref(req), C.byref(out))
+        return Summary(_status(rc, out.status, out.cuda_error, out.device_count), tokens[:len(sessions)].tolist(),
+                       out, ffi.last_error())
+
     def run(self, prompt_tokens, steps: int, eos_token=None, sampler=None) -> Summary:
         prompt = np.ascontiguousarray(prompt_tokens, dtype=np.uint32)
         tokens = np.zeros(max(steps, 1), dtype=np.uint32)
