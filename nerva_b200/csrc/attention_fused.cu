@@ -232,7 +232,28 @@ __global__ void fused_decode_attention_kernel(FusedAttentionParams p) {
         __syncwarp();
         const uint32_t left = hist - first < 32u ? hist - first : 32u;
         const uint8_t *v_tile = v_stage + tile * 32u * Layout::kRowV + lane * PER * 2u;
-        for (uint32_t t = 0; t < left; ++t) {
+        // Eight tokens' loads are issued before their multiply-adds (same order of additions as
+        // the one-token loop below, which takes the remainder).
+        uint32_t t = 0;
+        if (PER == 4) {
+          for (; t + 8u <= left; t += 8u) {
+            uint2 w[8];
+            float pt[8];
+#pragma unroll
+            for (uint32_t u = 0; u < 8u; ++u) {
+              w[u] = *reinterpret_cast<const uint2 *>(v_tile + (t + u) * Layout::kRowV);
+              pt[u] = p_sh[warp * 32u + t + u];
+            }
+#pragma unroll
+            for (uint32_t u = 0; u < 8u; ++u) {
+              acc[0] = fmaf(pt[u], bf16x2_lo(w[u].x), acc[0]);
+              acc[1 % PER] = fmaf(pt[u], bf16x2_hi(w[u].x), acc[1 % PER]);
+              acc[2 % PER] = fmaf(pt[u], bf16x2_lo(w[u].y), acc[2 % PER]);
+              acc[3 % PER] = fmaf(pt[u], bf16x2_hi(w[u].y), acc[3 % PER]);
+            }
+          }
+        }
+        for (; t < left; ++t) {
           const float pt = p_sh[warp * 32u + t];
           if (PER == 4) {
             const uint2 w = *reinterpret_cast<const uint2 *>(v_tile + t * Layout::kRowV);
@@ -285,34 +306,27 @@ __global__ void fused_decode_attention_kernel(FusedAttentionParams p) {
   stamp(p.stamps, kStampExit);  // partial written (a merging block stamps again at its end)
 
   // Publish the partials, then take a ticket: the block that draws the last
-  // ticket of its KV head sees every partial of the group's heads.
-  __threadfence();
+  // ticket of its KV head sees every partial of the group's heads.  The barrier
+  // orders every warp's partial stores before thread 0's release, and thread 0's
+  // acquire before every warp's loads after the second barrier, so one acq_rel
+  // atomic replaces a device-wide fence by every thread on each side.
   __syncthreads();
-  if (threadIdx.x == 0) ticket = atomicAdd(p.tickets + kvh, 1u);
+  if (threadIdx.x == 0) {
+    uint32_t drawn;
+    asm volatile("atom.acq_rel.gpu.global.add.u32 %0, [%1], 1;" : "=r"(drawn) : "l"(p.tickets + kvh) : "memory");
+    ticket = drawn;
+  }
   __syncthreads();
   if (ticket != S - 1u) return;
-  __threadfence();
   if (warp < group) {
+    // Every load of the merge is issued before anything is computed from them (every slot was
+    // written by this launch; an empty span holds zeros and gets weight 0): one round trip to L2.
     float ms[kFusedMaxSplits], ls[kFusedMaxSplits];
-    float m = -INFINITY;
+    float part[kFusedMaxSplits][PER];
 #pragma unroll
     for (uint32_t i = 0; i < kFusedMaxSplits; ++i) {
       ms[i] = i < S ? __ldcg(p.partial_m + h * S + i) : -INFINITY;
       ls[i] = i < S ? __ldcg(p.partial_l + h * S + i) : 0.0f;
-      if (ls[i] > 0.0f) m = fmaxf(m, ms[i]);
-    }
-    float l = 0.0f;
-#pragma unroll
-    for (uint32_t i = 0; i < kFusedMaxSplits; ++i) {
-      ms[i] = ls[i] > 0.0f ? exp2f(ms[i] - m) : 0.0f;  // weight of span i
-      l = fmaf(ls[i], ms[i], l);
-    }
-    const float inv = l > 0.0f ? 1.0f / l : 0.0f;
-    // All loads first (every slot was written by this launch; an empty span holds
-    // zeros and has weight 0), so they are in flight together.
-    float part[kFusedMaxSplits][PER];
-#pragma unroll
-    for (uint32_t i = 0; i < kFusedMaxSplits; ++i) {
       const float *src = p.partial_acc + (static_cast<uint64_t>(h) * S + (i < S ? i : 0u)) * D + lane * PER;
       if (PER == 4) {
         const float4 t4 = i < S ? __ldcg(reinterpret_cast<const float4 *>(src)) : make_float4(0.f, 0.f, 0.f, 0.f);
@@ -326,6 +340,18 @@ __global__ void fused_decode_attention_kernel(FusedAttentionParams p) {
         part[i][1 % PER] = t2.y;
       }
     }
+    float m = -INFINITY;
+#pragma unroll
+    for (uint32_t i = 0; i < kFusedMaxSplits; ++i) {
+      if (ls[i] > 0.0f) m = fmaxf(m, ms[i]);
+    }
+    float l = 0.0f;
+#pragma unroll
+    for (uint32_t i = 0; i < kFusedMaxSplits; ++i) {
+      ms[i] = ls[i] > 0.0f ? exp2f(ms[i] - m) : 0.0f;  // weight of span i
+      l = fmaf(ls[i], ms[i], l);
+    }
+    const float inv = l > 0.0f ? 1.0f / l : 0.0f;
     float a[PER];
 #pragma unroll
     for (uint32_t k = 0; k < PER; ++k) a[k] = 0.0f;

@@ -5,11 +5,14 @@
 1. tiny_qwen3.json — the CPU oracle (both numeric contracts) on the tiny
    Qwen3-architecture configuration: 64-token seeded prompt, 32 greedy tokens,
    plus a sample of logits per step.  The oracle itself is pinned by the
-   reference's known-answer tests (tests/test_oracle.py).
+   reference's known-answer tests (tests/test_cpu_oracle.py).
 2. abi_layout.txt — sizeof/offsetof of every ABI struct, measured by compiling
    a probe against the REFERENCE header (needs the reference checkout, only
    present on the build machine).  The test-suite compares this library's
    header against it.
+3. abi_prototypes.txt — return and parameter types, in order, of every
+   nerva_cuda_* function this library declares, as the REFERENCE header
+   declares them.
 """
 from __future__ import annotations
 
