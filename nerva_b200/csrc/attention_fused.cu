@@ -3,7 +3,7 @@
 // three launches on this (hf_decode_sequence/kernels.cu:434-492,
 // attention_kernels.cu:528-760, kernels.cu:494-555).
 //
-// Grid = kv_heads x splits blocks of (group + 1) warps.  A block serves the
+// Grid = kv_heads x splits blocks of (2 * group + 1) warps.  A block serves the
 // `group` query heads that share one KV head over one span of the context, so
 // every cached K/V byte is fetched once per block (not once per query head):
 //   * all threads copy the span's K and V rows into shared memory with 16-byte
@@ -11,9 +11,11 @@
 //     copy consecutive pieces of a row, so a request covers whole 128-byte
 //     lines.  These rows were written by earlier steps, so the copies are issued
 //     BEFORE the kernel waits for the QKV projection of this step;
-//   * warp w < group owns query head kv*group + w: q RMSNorm + RoPE, scores with
-//     one token per lane, base-2 online softmax, P.V with D/32 dims per lane;
-//   * warp `group` normalises and rotates the new K row, rounds K and V to bf16,
+//   * warps w and group + w (w < group) own query head kv*group + w: warp w does the
+//     q RMSNorm + RoPE and takes the first 32-token tile of every stage, warp
+//     group + w the second; scores with one token per lane, base-2 online softmax,
+//     P.V with D/32 dims per lane; the two softmax states are merged at the end;
+//   * warp 2*group normalises and rotates the new K row, rounds K and V to bf16,
 //     appends them to the page and hands them to the query warps (only in the
 //     block of the last span);
 //   * the partial (acc, m, l) of every (head, span) goes to global memory; the
@@ -46,9 +48,9 @@ struct FusedLayout {
   static constexpr uint32_t kRowV = D * 2u;
   static constexpr uint32_t kStageBytes = kChunkTokens * (kRowK + kRowV);
   static constexpr uint32_t kPieces = D * 2u / 16u;  // 16-byte pieces of one row
-  // stages | q [group][D] f32 | k_new [D] | v_new [D] | p [group][32]
+  // stages | q [group][D] f32 | k_new [D] | v_new [D] | p [2 * group][32]
   __host__ __device__ static constexpr uint32_t bytes(uint32_t group) {
-    return kStages * kStageBytes + (group * D + 2u * D + group * 32u) * 4u;
+    return kStages * kStageBytes + (group * D + 2u * D + 2u * group * 32u) * 4u;
   }
 };
 
@@ -127,7 +129,13 @@ __global__ void fused_decode_attention_kernel(FusedAttentionParams p) {
   // page-table and norm-weight loads are in flight while the rotation is computed.
   const uint32_t pages0 = chunk_begin < chunk_end ? chunk_pages(chunk_begin) : 0u;
   const uint32_t pages1 = chunk_begin + 1u < chunk_end ? chunk_pages(chunk_begin + 1u) : 0u;
-  const uint32_t h = kvh * group + warp;  // query head of this warp (warp < group)
+  // Warps 0 .. group-1 and group .. 2*group-1 serve the same query heads: the first set takes the
+  // first 32-token tile of every 64-token chunk, the second set the second tile, and the two
+  // partial softmax states are merged once at the end.  Warp 2*group prepares the new K/V row.
+  const uint32_t head_warps = 2u * group;
+  const uint32_t hw = warp < group ? warp : warp - group;  // head within the group (warp < head_warps)
+  const uint32_t my_tile = warp < group ? 0u : 1u;
+  const uint32_t h = kvh * group + hw;
   const float qscale = kAttnLog2e * rsqrtf(static_cast<float>(D));
   const uint16_t *norm_ptr = warp < group ? p.q_norm : p.k_norm;
   float norm_w[PER];
@@ -153,7 +161,7 @@ __global__ void fused_decode_attention_kernel(FusedAttentionParams p) {
     head_norm_rope_pre<PER>(v, p.q_norm != nullptr, norm_w, p.eps, rope);
 #pragma unroll
     for (uint32_t k = 0; k < PER; ++k) q_sh[warp * D + lane + 32u * k] = v[k] * qscale;
-  } else if (owns_current) {
+  } else if (warp == head_warps && owns_current) {
     float kn[PER], vn[PER];
 #pragma unroll
     for (uint32_t k = 0; k < PER; ++k) {
@@ -193,14 +201,13 @@ __global__ void fused_decode_attention_kernel(FusedAttentionParams p) {
       cp_async_wait<0>();
     }
     __syncthreads();  // every thread's copies of this stage (and q, k_new, v_new) are visible
-    if (warp < group) {
+    if (warp < head_warps) {
       const uint8_t *k_stage = smem + stage * Layout::kStageBytes;
       const uint8_t *v_stage = k_stage + kChunkTokens * Layout::kRowK;
-      const float *q = q_sh + warp * D;
-#pragma unroll 1
-      for (uint32_t tile = 0; tile < kChunkTokens / 32u; ++tile) {
-        const uint32_t first = chunk * kChunkTokens + tile * 32u;
-        if (first >= hist) break;
+      const float *q = q_sh + hw * D;
+      const uint32_t tile = my_tile;
+      const uint32_t first = chunk * kChunkTokens + tile * 32u;
+      if (first < hist) {
         const bool valid = first + lane < hist;
         float score = -INFINITY;
         if (valid) {
@@ -274,6 +281,30 @@ __global__ void fused_decode_attention_kernel(FusedAttentionParams p) {
     if (chunk + kStages < chunk_end) issue(chunk + kStages, stage, chunk_pages(chunk + kStages));
   }
   if (chunk_begin >= chunk_end) __syncthreads();  // q, k_new, v_new visible when no chunk ran
+
+  // The second warp set hands its softmax state to the first through the stage memory, which is
+  // idle now (every copy has landed and every warp is past its last read of it).
+  float *handoff = reinterpret_cast<float *>(smem);  // [group][32 lanes][PER acc | m | l]
+  if (warp >= group && warp < head_warps) {
+    float *dst = handoff + (hw * 32u + lane) * (PER + 2u);
+#pragma unroll
+    for (uint32_t i = 0; i < PER; ++i) dst[i] = acc[i];
+    dst[PER] = m_run;
+    dst[PER + 1u] = l_run;
+  }
+  __syncthreads();
+  if (warp < group) {
+    const float *src = handoff + (warp * 32u + lane) * (PER + 2u);
+    const float m1 = src[PER], l1 = src[PER + 1u];
+    if (l1 > 0.0f) {  // the second tiles held tokens
+      const float m = fmaxf(m_run, m1);
+      const float c0 = exp2f(m_run - m), c1 = exp2f(m1 - m);
+      l_run = l_run * c0 + l1 * c1;
+#pragma unroll
+      for (uint32_t i = 0; i < PER; ++i) acc[i] = acc[i] * c0 + src[i] * c1;
+      m_run = m;
+    }
+  }
 
   if (warp < group) {
     float m = m_run, l = l_run;
@@ -400,7 +431,7 @@ cudaError_t launch_fused_attention(cudaStream_t stream, const FusedAttentionPara
     return cudaErrorInvalidValue;
   const uint32_t group = p.heads / p.kv_heads;
   const uint32_t blocks = p.kv_heads * p.splits;
-  const uint32_t threads = (group + 1u) * 32u;
+  const uint32_t threads = (2u * group + 1u) * 32u;
   if (p.head_dim == 128) {
     return launch_with_pdl(fused_decode_attention_kernel<4>, dim3(blocks), dim3(threads),
                            FusedLayout<128>::bytes(group), stream, p.pdl != 0, p);
