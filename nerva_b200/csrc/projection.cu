@@ -52,6 +52,16 @@ __device__ __noinline__ void gather_prologue(const ProjectionParams &p, uint16_t
 
 // TP = true adds the tensor-parallel exchange (gather in the AddNorm prologue, push in the
 // Store epilogue); the single-GPU instantiations carry none of that code.
+// Ring slots a block fills before the dependency wait of a norm prologue; the rest follow the
+// prologue's activation loads.  Measured on Qwen3-8B: 3 (the whole ring) 337.8, 2: 343.4-347.6,
+// 1: 342.8 tok/s; holding a slot back ahead of the plain vector copy of O/down as well: 346.7.
+// The tensor-parallel gather prologue polls its entries behind the same queue: 435 -> 449 tok/s at 2 GPUs
+// (its held-back slot is issued by the first stream_fill of stream_consume).
+#ifndef NERVA_PREWAIT_SLOTS
+#define NERVA_PREWAIT_SLOTS (NERVA_STREAM_SLOTS - 1)
+#endif
+constexpr uint32_t kPrewaitSlots = NERVA_PREWAIT_SLOTS;
+
 template <uint32_t EPI, bool TP>
 __global__ void __launch_bounds__(kStreamThreads, 1) projection_stream_kernel(ProjectionParams p) {
   extern __shared__ __align__(128) uint8_t smem[];
@@ -66,20 +76,23 @@ __global__ void __launch_bounds__(kStreamThreads, 1) projection_stream_kernel(Pr
   if (threadIdx.x == 0) sh.job = JobDesc{p.weight, p.rows, p.cols, unit, 0};
   __syncthreads();
 
-  RowStream rs;
-  stream_init(rs, ring, sh.stream, &sh.job, 1);
-  // Weights do not depend on the activations: start streaming before the prologue.
-  stream_fill(rs);
-
-  uint32_t row_begin, row_end;
-  block_row_range(p.rows, unit, blockIdx.x, gridDim.x, &row_begin, &row_end);
-  const uint32_t rows_local = row_end - row_begin;
-  for (uint32_t r = threadIdx.x; r < rows_local; r += blockDim.x) row_total[r] = 0.0f;
   // A residual stream that arrives already summed needs one vector after the wait; the norm
   // weights come in before it.
   const bool norm_single = p.prologue == kPrologueAddNorm && p.add_b == nullptr && p.add_bias == nullptr &&
                            p.resid_out == nullptr && !(TP && p.gather.world > 1) &&
                            norm_single_eligible(p.add_a, p.norm_weight, p.cols);
+  RowStream rs;
+  stream_init(rs, ring, sh.stream, &sh.job, 1);
+  // Weights do not depend on the activations: start streaming before the prologue.  Ahead of a
+  // norm prologue the last ring slot is held back until the activation loads have been issued:
+  // they would otherwise queue behind a whole ring of bulk copies.
+  const bool gathers = TP && p.prologue == kPrologueAddNorm && p.gather.world > 1 && p.add_b != nullptr;
+  stream_fill(rs, norm_single || gathers ? kPrewaitSlots : kStreamSlots);
+
+  uint32_t row_begin, row_end;
+  block_row_range(p.rows, unit, blockIdx.x, gridDim.x, &row_begin, &row_end);
+  const uint32_t rows_local = row_end - row_begin;
+  for (uint32_t r = threadIdx.x; r < rows_local; r += blockDim.x) row_total[r] = 0.0f;
   NormWeightRegs norm_regs;
   if (norm_single) norm_weights_preload(norm_regs, p.norm_weight, p.cols);
 
@@ -100,7 +113,10 @@ __global__ void __launch_bounds__(kStreamThreads, 1) projection_stream_kernel(Pr
       // the partial sums of the ranks arrive over NVLink while this polls
       gather_prologue(p, x, sh.scratch);
     } else if (norm_single) {
-      norm_single_to_smem(x, p.add_a, norm_regs, p.eps, p.cols, sh.scratch);
+      NormValueRegs loaded;
+      norm_single_load(loaded, p.add_a, p.cols);
+      stream_fill(rs);  // the slot held back above, now behind the activation loads
+      norm_single_finish(x, loaded, norm_regs, p.eps, p.cols, sh.scratch);
     } else {
       add_norm_to_smem(x, p.add_a, p.add_b, p.add_bias, p.norm_weight, p.eps, p.cols,
                        blockIdx.x == 0 ? p.resid_out : nullptr, sh.scratch);

@@ -167,10 +167,10 @@ __device__ inline void stream_init(RowStream &rs, uint8_t *ring_base, StreamShar
   __syncwarp();
 }
 
-// Issues chunks, crossing into later jobs, while ring slots are free.
-__device__ __forceinline__ void stream_fill(RowStream &rs) {
+// Issues chunks, crossing into later jobs, while ring slots are free (at most `depth` in flight).
+__device__ __forceinline__ void stream_fill(RowStream &rs, uint32_t depth = kStreamSlots) {
   if (rs.dead) return;
-  while (rs.issue_job < rs.job_count && rs.issued - rs.consumed < kStreamSlots) {
+  while (rs.issue_job < rs.job_count && rs.issued - rs.consumed < depth) {
     if (rs.issue_cursor.pos >= rs.issue.end) {
       rs.issue_job += 1;
       if (rs.issue_job < rs.job_count) {

@@ -106,17 +106,30 @@ __device__ __forceinline__ void norm_weights_preload(NormWeightRegs &regs, const
     regs.w[k] = i < vecs ? reinterpret_cast<const uint2 *>(w)[i] : make_uint2(0u, 0u);
   }
 }
-__device__ __forceinline__ void norm_single_to_smem(uint16_t *x, const float *a, const NormWeightRegs &regs,
-                                                    float eps, uint32_t cols, float *scratch) {
+// Two halves, so that the caller can issue other memory traffic (the rest of its weight ring)
+// behind the activation loads instead of in front of them: norm_single_load issues the loads,
+// norm_single_finish consumes them.
+struct NormValueRegs {
+  float4 v[kNormRegIters];
+};
+__device__ __forceinline__ void norm_single_load(NormValueRegs &r, const float *a, uint32_t cols) {
   const uint32_t vecs = cols / 4u;
-  float4 r[kNormRegIters];
+#pragma unroll
+  for (uint32_t k = 0; k < kNormRegIters; ++k) {
+    const uint32_t i = threadIdx.x + k * blockDim.x;
+    r.v[k] = i < vecs ? __ldcg(reinterpret_cast<const float4 *>(a) + i) : make_float4(0.f, 0.f, 0.f, 0.f);
+  }
+}
+__device__ __forceinline__ void norm_single_finish(uint16_t *x, const NormValueRegs &loaded, const NormWeightRegs &regs,
+                                                   float eps, uint32_t cols, float *scratch) {
+  const uint32_t vecs = cols / 4u;
+  const float4 *r = loaded.v;
   float sumsq = 0.0f;
 #pragma unroll
   for (uint32_t k = 0; k < kNormRegIters; ++k) {
     const uint32_t i = threadIdx.x + k * blockDim.x;
     if (i < vecs) {
-      const float4 v = __ldcg(reinterpret_cast<const float4 *>(a) + i);
-      r[k] = v;
+      const float4 v = r[k];
       sumsq += v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w;
     }
   }
