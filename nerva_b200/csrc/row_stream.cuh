@@ -190,6 +190,20 @@ __device__ __forceinline__ void stream_fill(RowStream &rs, uint32_t depth = kStr
   }
 }
 
+// Asks L2 for the `bytes` that follow the chunks already issued (the warp's own span of the
+// current job only): the ring cannot hold more, but HBM can keep working while the block is
+// busy with its prologue.
+__device__ __forceinline__ void stream_prefetch_l2(const RowStream &rs, uint32_t bytes) {
+  if (rs.dead || bytes == 0 || rs.issue_job >= rs.job_count || (threadIdx.x & 31u) != 0) return;
+  const uint32_t pos = rs.issue_cursor.pos;
+  if (pos >= rs.issue.end) return;
+  uint32_t size = rs.issue.end - pos;
+  if (size > bytes) size = bytes;
+  size &= ~15u;
+  if (size == 0) return;
+  asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(rs.issue.base + pos), "r"(size) : "memory");
+}
+
 // dot of 8 bf16 weights with 8 bf16 activations, fp32.
 __device__ __forceinline__ float dot8(const uint4 &w, const uint4 &x, float acc) {
   acc = fmaf(bf16x2_lo(w.x), bf16x2_lo(x.x), acc);
