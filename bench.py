@@ -36,8 +36,8 @@ import numpy as np  # noqa: E402
 METRIC = "Qwen3-8B-arch BF16 batch-1 decode tok/s"
 # DRAM bytes (read + write) of the projection kernel's launches of one Qwen3-8B token, from the ncu
 # capture summarised in profiles/projection_stream_kernel_qwen3_8b_shapes.md:
-# 36 x (QKV 50.41 + O 33.63 + gate/up 205.35 + down 103.97 MB) + lm_head 1248.37 MB.
-NCU_PROJECTION_TRAFFIC_PER_TOKEN = 36 * (50.41e6 + 33.63e6 + 205.35e6 + 103.97e6) + 1248.37e6
+# 36 x (QKV 50.41 + O 33.63 + gate/up 205.18 + down 104.43 MB) + lm_head 1248.89 MB.
+NCU_PROJECTION_TRAFFIC_PER_TOKEN = 36 * (50.41e6 + 33.63e6 + 205.18e6 + 104.43e6) + 1248.89e6
 UNIT = "tok/s"
 
 
