@@ -86,6 +86,14 @@ extern "C" int nerva_b200_gqa_decode_attention_static_scratch(
     set_last_error("invalid argument");
     return -1;
   }
+  // The tiled kernels fetch K and V in 16-byte pieces: a view that starts in the middle of such a
+  // piece would fault the device instead of failing the call, so it is refused here.
+  if (reinterpret_cast<uintptr_t>(key_pages) % 16u != 0 || reinterpret_cast<uintptr_t>(value_pages) % 16u != 0 ||
+      reinterpret_cast<uintptr_t>(q) % 16u != 0 || reinterpret_cast<uintptr_t>(out) % 4u != 0 ||
+      reinterpret_cast<uintptr_t>(page_table) % 4u != 0) {
+    set_last_error("misaligned buffer: q, key_pages and value_pages must start on a 16-byte boundary");
+    return -1;
+  }
   const DeviceSetup *setup = nullptr;
   cudaError_t err = setup_current_device(&setup);
   if (err != cudaSuccess) {

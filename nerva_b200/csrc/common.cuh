@@ -159,13 +159,23 @@ __device__ __forceinline__ void pdl_trigger() {
   asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
 }
 
-// ---- counters written by other GPUs (tensor-parallel exchange) ----
+// ---- waits on other GPUs (tensor-parallel exchange) ----
+// A wait on a peer gives up after kPeerWaitCycleLimit SM cycles (about a second: ranks are separate
+// processes, so the limit has to cover launch skew between them) and records kErrPeerWaitTimeout.
+// The error word stays set until the next request starts, and every later wait of the session
+// looks at it first: once one exchange has failed, the steps already queued behind it run through
+// without waiting again, so a rank that died costs the others one limit, not one per exchange.
+constexpr long long kPeerWaitCycleLimit = kWaitCycleLimit;
+__device__ __forceinline__ bool step_already_failed(const uint32_t *error_word) {
+  return error_word != nullptr && *reinterpret_cast<const volatile uint32_t *>(error_word) != 0u;
+}
+
 __device__ __forceinline__ unsigned long long ld_acquire_sys(const unsigned long long *p) {
   unsigned long long v;
   asm volatile("ld.acquire.sys.global.u64 %0, [%1];" : "=l"(v) : "l"(p) : "memory");
   return v;
 }
-// Bounded wait until *counter >= expected (a few seconds); false on timeout.
+// Bounded wait until *counter >= expected; false on timeout.
 __device__ __forceinline__ bool wait_counter_bounded(const unsigned long long *counter,
                                                      unsigned long long expected) {
   if (ld_acquire_sys(counter) >= expected) return true;
@@ -175,7 +185,7 @@ __device__ __forceinline__ bool wait_counter_bounded(const unsigned long long *c
     for (uint32_t spin = 0; spin < 32; ++spin) {
       if (ld_acquire_sys(counter) >= expected) return true;
     }
-    if (clock64() - start > 4 * kWaitCycleLimit) return false;  // another process: allow host jitter
+    if (clock64() - start > kPeerWaitCycleLimit) return false;
   }
 }
 

@@ -17,7 +17,7 @@ constexpr uint32_t kCompletionDeviceComplete = 1;
 // Token of the position being decoded: a prompt id, or the token the previous
 // step wrote to the ring (hf_decode_sequence/kernels.cu:195-206).
 __device__ __forceinline__ uint32_t current_token(const StepState &st, uint32_t position) {
-  return position < st.prompt_count ? st.prompt[position] : st.slots[position - 1].token;
+  return position < *st.prompt_count ? st.prompt[position] : st.slots[position - 1].token;
 }
 
 __global__ void embed_kernel(StepState st, const uint16_t *embeddings, uint32_t hidden,
@@ -174,9 +174,12 @@ __global__ void sample_greedy_kernel(StepState st, const float *best_value,
       const unsigned long long expected = *tp.epoch + 1ull;
       bv = -INFINITY;
       bi = kNoIndex;
+      bool failed = step_already_failed(st.error_word);  // an earlier exchange gave up: do not wait again
       for (uint32_t q = 0; q < tp.world; ++q) {
+        if (failed) continue;
         if (!wait_counter_bounded(tp.arrivals[tp.rank] + q, expected)) {
           report_error(st.error_word, kErrPeerWaitTimeout);
+          failed = true;
           continue;
         }
         const unsigned long long cand = ld_acquire_sys(tp.recv[tp.rank] + q);

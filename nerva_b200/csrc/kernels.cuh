@@ -65,6 +65,7 @@ struct TpPush {
 struct TpGather {
   uint32_t world;                         // world <= 1: off
   const unsigned long long *recv;         // this rank's receive buffer of the phase
+  unsigned long long *reduced;            // this rank's [cols] tagged sums of the phase (world > 2)
   const unsigned long long *epoch;
   uint32_t per_epoch, offset;
 };
@@ -106,7 +107,7 @@ cudaError_t configure_projection_kernels();
 struct StepState {
   uint32_t *cursor;                       // device step cursor (= position of the token being run)
   const uint32_t *prompt;                 // device prompt ids
-  uint32_t prompt_count;
+  const uint32_t *prompt_count;           // device word: a captured step serves every prompt length
   NervaCudaSyntheticTokenSlot *slots;     // device token ring
   uint32_t max_context;
   uint32_t vocab;

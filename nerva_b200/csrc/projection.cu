@@ -39,15 +39,20 @@ __device__ __noinline__ void gather_prologue(const ProjectionParams &p, uint16_t
   const uint32_t tag = static_cast<uint32_t>(*p.gather.epoch) * p.gather.per_epoch + p.gather.offset;
   float *resid = blockIdx.x == 0 ? p.resid_out : nullptr;
   if (p.gather.world == 2) {
+    // two partials: every block adds them itself (one round trip)
     gather_norm_to_smem<2>(x, p.add_a, p.gather.recv, tag, p.add_bias, p.norm_weight, p.eps, p.cols, resid,
                            scratch, p.error_word);
-  } else if (p.gather.world == 4) {
-    gather_norm_to_smem<4>(x, p.add_a, p.gather.recv, tag, p.add_bias, p.norm_weight, p.eps, p.cols, resid,
-                           scratch, p.error_word);
-  } else {
-    gather_norm_to_smem<8>(x, p.add_a, p.gather.recv, tag, p.add_bias, p.norm_weight, p.eps, p.cols, resid,
-                           scratch, p.error_word);
+    return;
   }
+  // four or eight partials: each block adds the ranks for its slice of the vector only, then every
+  // block gathers the sums (reading all partials in every block costs more than the extra hop)
+  if (p.gather.world == 4) {
+    reduce_partials_slice<4>(p.gather.recv, p.gather.reduced, tag, p.cols, p.error_word);
+  } else {
+    reduce_partials_slice<8>(p.gather.recv, p.gather.reduced, tag, p.cols, p.error_word);
+  }
+  gather_norm_to_smem<1>(x, p.add_a, p.gather.reduced, tag, p.add_bias, p.norm_weight, p.eps, p.cols, resid,
+                         scratch, p.error_word);
 }
 
 // TP = true adds the tensor-parallel exchange (gather in the AddNorm prologue, push in the

@@ -270,7 +270,7 @@ bool plan_state(Session *s, StaticArena &arena, void *base) {
 // Exchange buffer of a tensor-parallel rank (its own allocation, shared with the
 // other ranks through an inter-process handle).  Offsets are the same on every rank.
 struct CommLayout {
-  uint64_t recv_o, recv_d, arrivals_s, candidates, epoch, bytes;
+  uint64_t recv_o, recv_d, reduced_o, reduced_d, arrivals_s, candidates, epoch, bytes;
 };
 CommLayout comm_layout(uint32_t world, uint32_t hidden) {
   CommLayout c{};
@@ -282,6 +282,8 @@ CommLayout comm_layout(uint32_t world, uint32_t hidden) {
   };
   c.recv_o = take(static_cast<uint64_t>(world) * hidden * 8u);  // tagged 8-byte entries
   c.recv_d = take(static_cast<uint64_t>(world) * hidden * 8u);
+  c.reduced_o = take(static_cast<uint64_t>(hidden) * 8u);  // local sums over the ranks (world > 2)
+  c.reduced_d = take(static_cast<uint64_t>(hidden) * 8u);
   c.arrivals_s = take(world * 8u);
   c.candidates = take(world * 8u);
   c.epoch = take(8u);
@@ -329,7 +331,7 @@ StepState step_state(Session *s) {
   StepState st;
   st.cursor = s->device_cursor;
   st.prompt = s->device_prompt;
-  st.prompt_count = s->prompt_count;
+  st.prompt_count = s->device_cursor + 1;  // word 1 of the cursor block, written by reset_request_state
   st.slots = s->device_slots;
   st.max_context = s->max_context;
   st.vocab = s->dims.embed_vocab;  // token ids index the (whole) embedding table
@@ -501,6 +503,7 @@ cudaError_t enqueue_step(Session *s, uint32_t splits, uint32_t sample, uint64_t 
     TpGather gather{};
     gather.world = s->tp_world;
     gather.recv = comm_at<unsigned long long>(s->comm_block, recv);
+    gather.reduced = comm_at<unsigned long long>(s->comm_block, recv == comm.recv_o ? comm.reduced_o : comm.reduced_d);
     gather.epoch = comm_at<unsigned long long>(s->comm_block, comm.epoch);
     gather.per_epoch = d.layers;
     gather.offset = exchange;
@@ -811,14 +814,15 @@ cudaError_t enqueue_step(Session *s, uint32_t splits, uint32_t sample, uint64_t 
   return err;
 }
 
-// Graph cache: one instantiated graph per (prompt length, attention split
-// count, sampling on/off, engine), like the reference's cached graph key
-// (hf_decode_sequence/session_graph_result.inc.cu:87-209).
+// Graph cache: one instantiated graph per (attention split bucket, sampler kind, engine) —
+// the role of the reference's cached graph key (hf_decode_sequence/session_graph_result.inc.cu:87-209).
+// Prompt length, cursor and sampler parameters are read from device memory by the kernels, so a
+// session that serves prompts of many lengths keeps a handful of graphs (split buckets x 3 sampler
+// kinds x 2 engines at most), never one per request.
 cudaError_t ensure_graph(Session *s, uint32_t splits, uint32_t sample, GraphEntry **out,
                          NervaCudaHfDecodeSequenceResult *res) {
   for (GraphEntry &g : s->graphs) {
-    if (g.prompt_count == s->prompt_count && g.splits == splits && g.sample == sample &&
-        g.engine == s->engine) {
+    if (g.splits == splits && g.sample == sample && g.engine == s->engine) {
       *out = &g;
       if (res != nullptr) {
         res->graph_cache_hits += 1;
@@ -828,7 +832,6 @@ cudaError_t ensure_graph(Session *s, uint32_t splits, uint32_t sample, GraphEntr
     }
   }
   GraphEntry entry;
-  entry.prompt_count = s->prompt_count;
   entry.splits = splits;
   entry.sample = sample;
   entry.engine = s->engine;
@@ -878,6 +881,20 @@ cudaError_t ensure_graph(Session *s, uint32_t splits, uint32_t sample, GraphEntr
 cudaError_t replay(Session *s, GraphEntry *g) {
   if (g->exec != nullptr) return cudaGraphLaunch(g->exec, s->stream);
   return enqueue_step(s, g->splits, g->sample, nullptr);
+}
+
+// Tensor-parallel sessions: a failed exchange (a peer that died or fell behind its wait limit)
+// sets the device error word.  Every kPeerCheckInterval replays a copy of that word to pinned
+// host memory is queued, and the replay loops stop queueing once a copy shows a failure.  The
+// host never waits for the copy, so the value it sees is up to one interval old; the kernels of
+// the steps queued meanwhile skip their waits (common.cuh: step_already_failed).
+constexpr uint32_t kPeerCheckInterval = 16;
+bool peer_failure_seen(Session *s, uint32_t step) {
+  if (s->tp_world <= 1) return false;
+  if (*reinterpret_cast<volatile uint32_t *>(s->host_error) != 0) return true;
+  if (step % kPeerCheckInterval == kPeerCheckInterval - 1u)
+    cudaMemcpyAsync(s->host_error, s->device_error, sizeof(uint32_t), cudaMemcpyDeviceToHost, s->stream);
+  return false;
 }
 
 uint32_t splits_for(Session *s, uint32_t target_context) {
@@ -965,13 +982,16 @@ cudaError_t reset_request_state(Session *s, const uint32_t *prompt, uint32_t cou
   const uint64_t bytes = static_cast<uint64_t>(count) * sizeof(uint32_t);
   if (err == cudaSuccess)
     err = cudaMemcpyAsync(s->device_prompt, prompt, bytes, cudaMemcpyHostToDevice, s->stream);
-  out->h2d_bytes = bytes;
+  if (err == cudaSuccess)  // pageable source: staged before the call returns
+    err = cudaMemcpyAsync(s->device_cursor + 1, &count, sizeof(uint32_t), cudaMemcpyHostToDevice, s->stream);
+  out->h2d_bytes = bytes + sizeof(uint32_t);
   if (err == cudaSuccess && s->sample_kind == 2) {
     err = cudaMemcpyAsync(s->device_sampler, &s->host_sampler, sizeof(SamplerParams), cudaMemcpyHostToDevice,
                           s->stream);
     out->h2d_bytes += sizeof(SamplerParams);
   }
   s->logits_valid = false;
+  *s->host_error = 0;  // nothing of this session is in flight when a request starts
   return err;
 }
 
@@ -1238,7 +1258,8 @@ int create_fail(Session *s, NervaCudaHfDecodeSequenceSessionCreateResult *out, c
   out->status = -1;
   out->cuda_error = static_cast<int32_t>(err);
   out->failure_stage = stage;
-  if (err != cudaSuccess) set_last_error(cudaGetErrorString(err));
+  // a more specific text set just before the failure (file errors, layout errors) is kept
+  if (err != cudaSuccess && g_last_error.empty()) set_last_error(cudaGetErrorString(err));
   destroy_session(s);
   return -1;
 }
@@ -1660,6 +1681,7 @@ extern "C" int nerva_cuda_hf_decode_sequence_session_start(
   if (err == cudaSuccess) err = ensure_graph(s, splits, s->sample_kind, &sampled, out);
   if (err == cudaSuccess) err = cudaEventRecord(s->ev_start, s->stream);
   for (uint32_t i = 0; err == cudaSuccess && i + 1 < s->prompt_count; ++i) {
+    if (peer_failure_seen(s, i)) break;
     err = replay(s, quiet);
     out->graph_replays += 1;
     out->graph_launches += 1;
@@ -1726,6 +1748,7 @@ extern "C" int nerva_cuda_hf_decode_sequence_session_advance(
   if (run_count != 0) err = ensure_graph(s, splits_for(s, target), s->sample_kind, &graph, out);
   if (err == cudaSuccess && run_count != 0) err = cudaEventRecord(s->ev_start, s->stream);
   for (uint32_t step = 0; err == cudaSuccess && step < run_count; ++step) {
+    if (peer_failure_seen(s, step)) break;
     err = replay(s, graph);  // the hot loop: one graph launch per token, nothing else
     if (err != cudaSuccess) break;
     out->graph_replays += 1;
@@ -1821,6 +1844,7 @@ extern "C" int nerva_cuda_hf_decode_sequence_session_run(
   if (err == cudaSuccess) err = ensure_graph(s, splits_for(s, context_steps), s->sample_kind, &graph, out);
   if (err == cudaSuccess) err = cudaEventRecord(s->ev_start, s->stream);
   for (uint32_t step = 0; err == cudaSuccess && step < context_steps; ++step) {
+    if (peer_failure_seen(s, step)) break;
     err = replay(s, graph);
     if (err == cudaSuccess) {
       out->graph_replays += 1;
@@ -2027,7 +2051,16 @@ extern "C" int nerva_cuda_hf_decode_sequence_session_fork_shared_weights(
     out->failure_stage = kStageInvalidRequest;
     return -1;
   }
+  set_last_error("");
   Session *parent = request->parent;
+  if (parent->tp_world > 1) {
+    // A tensor-parallel rank's step needs the exchange buffers of all ranks; a fork would need
+    // its own set on every rank, which this entry point cannot arrange.
+    out->cuda_error = static_cast<int32_t>(cudaErrorNotSupported);
+    out->failure_stage = kStageInvalidRequest;
+    set_last_error("a tensor-parallel session cannot be forked");
+    return -1;
+  }
   Session *s = new (std::nothrow) Session();
   if (s == nullptr) {
     out->cuda_error = static_cast<int32_t>(cudaErrorMemoryAllocation);
@@ -2043,6 +2076,7 @@ extern "C" int nerva_cuda_hf_decode_sequence_session_fork_shared_weights(
   s->detailed_profile = request->detailed_profile;
   s->layout = parent->layout;
   s->layer_meta = parent->layer_meta;
+  s->has_moe = parent->has_moe;
   s->resident_weight_bytes = parent->resident_weight_bytes;
   s->planned_weight_blocks = parent->planned_weight_blocks;
   s->planned_gpu_resident_blocks = parent->planned_gpu_resident_blocks;

@@ -88,7 +88,7 @@ struct StepProfile {
 };
 
 struct GraphEntry {
-  uint32_t prompt_count = 0, splits = 0, sample = 0, engine = 0;
+  uint32_t splits = 0, sample = 0, engine = 0;
   cudaGraph_t graph = nullptr;
   cudaGraphExec_t exec = nullptr;  // null: the step is launched directly (capture was refused)
   uint64_t nodes = 0;

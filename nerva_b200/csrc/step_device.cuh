@@ -156,8 +156,8 @@ __device__ __forceinline__ void norm_single_finish(uint16_t *x, const NormValueR
 // [world][cols] 8-byte entries, value bits in the low word and a tag in the high
 // word; a writer stores an entry with ONE 8-byte store, so an entry whose tag is
 // the expected one carries its value (no fence, no separate flag).  Each thread
-// polls exactly the entries it needs (bounded; on expiry the error word is set
-// and the step fails) and adds the partials in rank order, so every rank
+// polls exactly the entries it needs (bounded, see kPeerWaitCycleLimit; on expiry the error
+// word is set and the step fails) and adds the partials in rank order, so every rank
 // computes the same r bit for bit.  cols % 4 == 0 and cols <= 4 * kNormRegIters *
 // blockDim.x.
 constexpr uint32_t kMaxGatherWorld = 8;
@@ -185,7 +185,7 @@ __device__ __forceinline__ void gather_norm_to_smem(uint16_t *x, const float *a,
   uint2 wk[kNormRegIters];
   float sumsq = 0.0f;
   const long long start = clock64();
-  bool gave_up = false;
+  bool gave_up = step_already_failed(error_word);
 #pragma unroll
   for (uint32_t k0 = 0; k0 < kNormRegIters; k0 += BATCH) {
     if (k0 * blockDim.x >= vecs) break;
@@ -229,7 +229,7 @@ __device__ __forceinline__ void gather_norm_to_smem(uint16_t *x, const float *a,
         }
       }
       if (ok || gave_up) break;
-      if ((++polls & 63u) == 0 && clock64() - start > 4 * kWaitCycleLimit) {
+      if ((++polls & 63u) == 0 && clock64() - start > kPeerWaitCycleLimit) {
         gave_up = true;
         report_error(error_word, kErrPeerWaitTimeout);
       }
@@ -286,6 +286,71 @@ __device__ __forceinline__ void gather_norm_to_smem(uint16_t *x, const float *a,
               (static_cast<uint32_t>(f32_to_bf16_bits(v.w * scale * bf16x2_hi(wb.y))) << 16);
       reinterpret_cast<uint2 *>(x)[i] = out;
     }
+  }
+}
+
+// First stage of the tensor-parallel gather when every block would otherwise read all
+// WORLD partial vectors: block b adds the ranks' partials (in rank order) for ITS slice of
+// the vector only, and publishes the sums as tagged 8-byte entries in `reduced` (local
+// memory, same layout as one rank's slot).  Every block then gathers the whole vector from
+// `reduced` with gather_norm_to_smem<1>.  Blocks of one launch wait on each other's slices
+// here: the launch must fit the device in one wave (one block per SM), and the waits are
+// bounded like all others.
+template <uint32_t WORLD>
+__device__ __forceinline__ void reduce_partials_slice(const unsigned long long *recv,
+                                                      unsigned long long *reduced, uint32_t tag,
+                                                      uint32_t cols, uint32_t *error_word) {
+  const uint32_t groups = cols / 4u;
+  const uint32_t begin = static_cast<uint32_t>(static_cast<uint64_t>(groups) * blockIdx.x / gridDim.x);
+  const uint32_t end = static_cast<uint32_t>(static_cast<uint64_t>(groups) * (blockIdx.x + 1u) / gridDim.x);
+  const long long start = clock64();
+  bool gave_up = step_already_failed(error_word);
+  for (uint32_t g = begin + threadIdx.x; g < end; g += blockDim.x) {
+    ulonglong2 lo[WORLD], hi[WORLD];
+    uint32_t polls = 0;
+    for (;;) {
+#pragma unroll
+      for (uint32_t q = 0; q < WORLD; ++q) {
+        const ulonglong2 *src = reinterpret_cast<const ulonglong2 *>(recv + static_cast<uint64_t>(q) * cols + 4u * g);
+        lo[q] = ld_volatile_16(src);
+        hi[q] = ld_volatile_16(src + 1);
+      }
+      bool ok = true;
+#pragma unroll
+      for (uint32_t q = 0; q < WORLD; ++q) {
+        ok = ok && static_cast<uint32_t>(lo[q].x >> 32) == tag && static_cast<uint32_t>(lo[q].y >> 32) == tag &&
+             static_cast<uint32_t>(hi[q].x >> 32) == tag && static_cast<uint32_t>(hi[q].y >> 32) == tag;
+      }
+      if (ok || gave_up) break;
+      if ((++polls & 63u) == 0 && clock64() - start > kPeerWaitCycleLimit) {
+        gave_up = true;
+        report_error(error_word, kErrPeerWaitTimeout);
+      }
+    }
+    float4 t = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+#pragma unroll
+    for (uint32_t q = 0; q < WORLD; ++q) {
+      const float4 u = make_float4(__uint_as_float(static_cast<uint32_t>(lo[q].x)),
+                                   __uint_as_float(static_cast<uint32_t>(lo[q].y)),
+                                   __uint_as_float(static_cast<uint32_t>(hi[q].x)),
+                                   __uint_as_float(static_cast<uint32_t>(hi[q].y)));
+      if (q == 0) {
+        t = u;
+      } else {
+        t.x += u.x;
+        t.y += u.y;
+        t.z += u.z;
+        t.w += u.w;
+      }
+    }
+    const unsigned long long high = static_cast<unsigned long long>(tag) << 32;
+    unsigned long long *dst = reduced + 4u * g;
+    asm volatile("st.volatile.global.v2.u64 [%0], {%1, %2};" ::"l"(dst), "l"(high | __float_as_uint(t.x)),
+                 "l"(high | __float_as_uint(t.y))
+                 : "memory");
+    asm volatile("st.volatile.global.v2.u64 [%0], {%1, %2};" ::"l"(dst + 2), "l"(high | __float_as_uint(t.z)),
+                 "l"(high | __float_as_uint(t.w))
+                 : "memory");
   }
 }
 

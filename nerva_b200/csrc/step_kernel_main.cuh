@@ -35,7 +35,7 @@ __global__ void __launch_bounds__(kStreamThreads, 1) decode_step_kernel(StepKern
   __syncthreads();
   stream_fill(rs);
 
-  uint32_t token = position < p.st.prompt_count ? p.st.prompt[position] : p.st.slots[position - 1].token;
+  uint32_t token = position < *p.st.prompt_count ? p.st.prompt[position] : p.st.slots[position - 1].token;
   if (token >= p.st.vocab) {
     if (blockIdx.x == 0 && threadIdx.x == 0) report_error(p.st.error_word, kErrTokenOutOfRange);
     token = 0;

@@ -88,7 +88,18 @@ def lib() -> C.CDLL:
         raise RuntimeError(
             f"{LIB_PATH} is missing: build it with `python -m nerva_b200.build` (nvcc, sm_100a). "
             "There is no CPU fallback.")
-    L = C.CDLL(LIB_PATH)
+    _lib = _bind(C.CDLL(LIB_PATH), reference_abi_only=False)
+    return _lib
+
+
+def load_abi_library(path: str) -> C.CDLL:
+    """Another shared library that exports the reference's C ABI (the nerva_cuda_* entry points
+    with the structs of include/nerva_b200_api.h), bound with the same signatures.  The session
+    classes accept it through their `library` argument; the nerva_b200_* additions are not bound."""
+    return _bind(C.CDLL(path), reference_abi_only=True)
+
+
+def _bind(L: C.CDLL, reference_abi_only: bool) -> C.CDLL:
     P = C.POINTER
     vp = C.c_void_p
     sigs = {
@@ -134,6 +145,15 @@ def lib() -> C.CDLL:
         "nerva_b200_synth_normal_bf16": [C.c_uint64, C.c_uint64, C.c_uint64, C.c_float, vp],
         "nerva_b200_synth_normal_bf16_block": [C.c_uint64] * 7 + [C.c_float, vp],
     }
+    if reference_abi_only:
+        # another implementation of the reference's C ABI (same structs, same prototypes): bind the
+        # nerva_cuda_* entry points it exports and nothing else
+        for name, argtypes in sigs.items():
+            if name.startswith("nerva_cuda_") and hasattr(L, name):
+                fn = getattr(L, name)
+                fn.argtypes = argtypes
+                fn.restype = C.c_int
+        return L
     for name, argtypes in sigs.items():
         fn = getattr(L, name)
         fn.argtypes = argtypes
@@ -165,7 +185,6 @@ def lib() -> C.CDLL:
         fn.argtypes = argtypes
     L.nerva_b200_last_error.restype = C.c_char_p
     L.nerva_b200_last_error.argtypes = []
-    _lib = L
     return L
 
 

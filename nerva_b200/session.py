@@ -126,8 +126,12 @@ class CudaHfDecodeSequenceSession:
     """Owns one native session handle (create ... destroy)."""
 
     def __init__(self, checkpoint, max_context_tokens: int, use_descriptors: bool = False, dtype: int = DTYPE_BF16,
-                 engine: int = 0):
+                 engine: int = 0, library=None):
+        """library: a handle from ffi.load_abi_library for another implementation of the same C ABI
+        (default: this package's libnerva_b200.so)."""
         cfg = checkpoint.config
+        self._lib = library if library is not None else ffi.lib()
+        self._own_library = library is None
         self.config = cfg
         self._keep = [checkpoint]
         layers = chain_layers(checkpoint)
@@ -158,27 +162,32 @@ class CudaHfDecodeSequenceSession:
             info = ffi.structs["NervaB200ShardInfo"](rank=self.shard.rank, world=self.shard.world,
                                                      full_vocab=self.shard.full_vocab,
                                                      vocab_offset=self.shard.vocab_offset)
-            rc = ffi.lib().nerva_b200_session_create_sharded(C.byref(req), C.byref(info),
+            rc = self._lib.nerva_b200_session_create_sharded(C.byref(req), C.byref(info),
                                                              C.byref(self.create_result), C.byref(self._handle))
         else:
-            rc = ffi.lib().nerva_cuda_hf_decode_sequence_session_create(C.byref(req), C.byref(self.create_result),
+            rc = self._lib.nerva_cuda_hf_decode_sequence_session_create(C.byref(req), C.byref(self.create_result),
                                                                         C.byref(self._handle))
         r = self.create_result
         self.status = _status(rc, r.status, r.cuda_error, r.device_count)
-        self.error = ffi.last_error()
+        self.error = self._last_error()
         if self.status == SmokeStatus.OK and engine:
             if ffi.lib().nerva_b200_session_set_engine(self._handle, engine) != 0:
                 raise RuntimeError("engine not available for this model")
 
+    def _last_error(self) -> str:
+        return ffi.last_error() if self._own_library else ""
+
     @classmethod
     def _from_handle(cls, parent, handle, result, status):
         self = cls.__new__(cls)
+        self._lib = parent._lib
+        self._own_library = parent._own_library
         self.config = parent.config
         self._keep = parent._keep
         self._handle = handle
         self.create_result = result
         self.status = status
-        self.error = ffi.last_error()
+        self.error = self._last_error()
         return self
 
     def create_summary(self):
@@ -190,7 +199,7 @@ class CudaHfDecodeSequenceSession:
     def fork_shared_weights(self) -> "CudaHfDecodeSequenceSession":
         req = ffi.ForkRequest(parent=self._handle, detailed_profile=0)
         handle, res = C.c_void_p(), ffi.CreateResult()
-        rc = ffi.lib().nerva_cuda_hf_decode_sequence_session_fork_shared_weights(C.byref(req), C.byref(res),
+        rc = self._lib.nerva_cuda_hf_decode_sequence_session_fork_shared_weights(C.byref(req), C.byref(res),
                                                                                  C.byref(handle))
         return self._from_handle(self, handle, res, _status(rc, res.status, res.cuda_error, res.device_count))
 
@@ -206,9 +215,10 @@ class CudaHfDecodeSequenceSession:
             target_block_tokens=target_block_tokens, min_block_tokens=min_block_tokens,
             output_tokens=_ptr(tokens), output_token_capacity=len(sessions))
         out = ffi.structs["NervaCudaHfDecodeSequenceBatchAdvanceResult"]()
-        rc = ffi.lib().nerva_cuda_hf_decode_sequence_batch_advance_one(C.byref(req), C.byref(out))
+        library = sessions[0]._lib if sessions else ffi.lib()
+        rc = library.nerva_cuda_hf_decode_sequence_batch_advance_one(C.byref(req), C.byref(out))
         return Summary(_status(rc, out.status, out.cuda_error, out.device_count), tokens[:len(sessions)].tolist(),
-                       out, ffi.last_error())
+                       out, sessions[0]._last_error() if sessions else ffi.last_error())
 
     def run(self, prompt_tokens, steps: int, eos_token=None, sampler=None) -> Summary:
         prompt = np.ascontiguousarray(prompt_tokens, dtype=np.uint32)
@@ -219,9 +229,9 @@ class CudaHfDecodeSequenceSession:
                              output_tokens=_ptr(tokens), output_token_capacity=steps,
                              sampler=sampler or greedy_sampler())
         out = ffi.SequenceResult()
-        rc = ffi.lib().nerva_cuda_hf_decode_sequence_session_run(C.byref(req), C.byref(out))
+        rc = self._lib.nerva_cuda_hf_decode_sequence_session_run(C.byref(req), C.byref(out))
         return Summary(_status(rc, out.status, out.cuda_error, out.device_count),
-                       tokens[:out.observed_tokens].tolist(), out, ffi.last_error())
+                       tokens[:out.observed_tokens].tolist(), out, self._last_error())
 
     def read_logits(self) -> np.ndarray:
         logits = np.empty(self.config.vocab, dtype=np.float32)
@@ -296,7 +306,7 @@ class CudaHfDecodeSequenceSession:
 
     def destroy(self) -> None:
         if self._handle:
-            ffi.lib().nerva_cuda_hf_decode_sequence_session_destroy(self._handle, None)
+            self._lib.nerva_cuda_hf_decode_sequence_session_destroy(self._handle, None)
             self._handle = C.c_void_p()
 
     def __del__(self):
@@ -321,8 +331,8 @@ class CudaHfDecodeSequenceLoop:
                                prompt_token_count=prompt.size, has_eos_token=int(eos_token is not None),
                                eos_token=eos_token or 0, sampler=sampler or greedy_sampler())
         out = ffi.SequenceResult()
-        rc = ffi.lib().nerva_cuda_hf_decode_sequence_session_start(C.byref(req), C.byref(out))
-        summary = Summary(_status(rc, out.status, out.cuda_error, out.device_count), [], out, ffi.last_error())
+        rc = session._lib.nerva_cuda_hf_decode_sequence_session_start(C.byref(req), C.byref(out))
+        summary = Summary(_status(rc, out.status, out.cuda_error, out.device_count), [], out, session._last_error())
         return summary, (cls(session, eos_token) if summary.status == SmokeStatus.OK else None)
 
     def advance(self, steps: int) -> Summary:
@@ -332,9 +342,10 @@ class CudaHfDecodeSequenceLoop:
         req = ffi.AdvanceRequest(session=self.session.raw_handle(), steps=steps, output_tokens=_ptr(tokens),
                                  output_token_capacity=steps)
         out = ffi.SequenceResult()
-        rc = ffi.lib().nerva_cuda_hf_decode_sequence_session_advance(C.byref(req), C.byref(out))
+        rc = self.session._lib.nerva_cuda_hf_decode_sequence_session_advance(C.byref(req), C.byref(out))
         got = tokens[:min(out.observed_tokens, steps)].tolist()
-        summary = Summary(_status(rc, out.status, out.cuda_error, out.device_count), got, out, ffi.last_error())
+        summary = Summary(_status(rc, out.status, out.cuda_error, out.device_count), got, out,
+                          self.session._last_error())
         self.finished = summary.status == SmokeStatus.OK and (
             len(got) < steps or (self.eos_token is not None and bool(got) and got[-1] == self.eos_token))
         return summary

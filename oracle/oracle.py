@@ -45,7 +45,10 @@ class OracleModel(C.Structure):
 
 def build(force: bool = False) -> str:
     """Compile the oracle with the Makefile beside this file."""
-    if force or not os.path.exists(_LIB_PATH):
+    # make decides what is stale (a source newer than the library)
+    if force:
+        subprocess.run(["make", "-C", _HERE, "-B"], check=True, capture_output=True)
+    else:
         subprocess.run(["make", "-C", _HERE], check=True, capture_output=True)
     return _LIB_PATH
 
@@ -99,6 +102,27 @@ def lib() -> C.CDLL:
 
 def _p16(a):
     return None if a is None else a.ctypes.data_as(_u16p)
+
+
+def synth_normal_bf16(seed: int, tensor_id: int, count: int, std: float) -> np.ndarray:
+    """Multi-threaded twin of nerva_b200.synth.normal_bf16 (same bits), inside the oracle library."""
+    out = np.empty(count, dtype=np.uint16)
+    fn = lib().oracle_synth_normal_bf16
+    fn.restype = None
+    fn.argtypes = [C.c_uint64, C.c_uint64, C.c_uint64, C.c_float, _u16p]
+    fn(seed, tensor_id, count, std, _p16(out))
+    return out
+
+
+def synth_normal_bf16_block(seed: int, tensor_id: int, full_cols: int, row_begin: int, rows: int, col_begin: int,
+                            cols: int, std: float) -> np.ndarray:
+    """A rows x cols block of the row-major synthetic tensor with `full_cols` columns, flattened."""
+    out = np.empty(rows * cols, dtype=np.uint16)
+    fn = lib().oracle_synth_normal_bf16_block
+    fn.restype = None
+    fn.argtypes = [C.c_uint64] * 7 + [C.c_float, _u16p]
+    fn(seed, tensor_id, full_cols, row_begin, rows, col_begin, cols, std, _p16(out))
+    return out
 
 
 def _pf(a):

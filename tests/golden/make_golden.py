@@ -10,6 +10,13 @@
    a probe against the REFERENCE header (needs the reference checkout, only
    present on the build machine).  The test-suite compares this library's
    header against it.
+4. qwen3_8b.json (only with the argument `qwen3_8b`; takes about an hour and 20 GB on 8 cores) —
+   the CPU oracle on the full 36-layer Qwen3-8B-architecture model with the 512-token seeded
+   prompt: per decoded position the token, the top-1 minus top-2 margin, the largest logit, the
+   top-8 candidates and 64 sampled logits (CUDA contract: 64 positions; CPU contract: 32), and a
+   depth sweep (models cut to 1, 2, 4, 8, 16, 36 layers, 16-token prompt): 1024 sampled logits
+   under the serial summation order, and the oracle's distance to itself when only the
+   summation order changes (8 interleaved partial sums).
 3. abi_prototypes.txt — return and parameter types, in order, of every
    nerva_cuda_* function this library declares, as the REFERENCE header
    declares them.
@@ -51,6 +58,90 @@ def tiny_golden() -> dict:
             "top1_minus_top2": [float(b - a) for a, b in top2],
             "max_logit": [float(v) for v in logits.max(axis=1)],
         }
+    return out
+
+
+QWEN_SAMPLE_INDICES = [int(i) for i in np.linspace(0, 151935, 64).astype(np.int64)]
+SWEEP_DEPTHS = [1, 2, 4, 8, 16, 36]
+SWEEP_PROMPT_TOKENS = 16
+SWEEP_SAMPLE_INDICES = [int(i) for i in np.linspace(0, 151935, 1024).astype(np.int64)]
+
+
+def _prefix_checkpoint(full, layers: int):
+    """The first `layers` layers of `full` as a checkpoint of its own (same tensors, no copy)."""
+    import dataclasses
+    cfg = dataclasses.replace(full.config, name=f"{full.config.name}-cut{layers}", layers=layers)
+    return synth.DenseCheckpoint(cfg, full.embeddings, full.final_norm, full.lm_head, full.layers[:layers])
+
+
+def _record_stream(dec, prompt, steps: int, log) -> dict:
+    """Greedy decode step by step, keeping per position what the GPU test compares against."""
+    out = {"tokens": [], "top1_minus_top2": [], "max_logit": [], "logit_samples": [], "top8_index": [],
+           "top8_value": []}
+    for i, token in enumerate(prompt[:-1]):
+        dec.step(int(token), want_logits=False)
+        if i % 64 == 0:
+            log(f"  prompt {i}/{len(prompt)}")
+    current = int(prompt[-1])
+    for step in range(steps):
+        logits = dec.step(current, want_logits=True)
+        order = np.argsort(-logits, kind="stable")[:8]
+        current = O.argmax(logits, dec.mode if dec.mode != O.MODE_CPU else O.MODE_CUDA)
+        out["tokens"].append(int(current))
+        out["top1_minus_top2"].append(float(logits[order[0]] - logits[order[1]]))
+        out["max_logit"].append(float(logits[order[0]]))
+        out["logit_samples"].append([float(v) for v in logits[QWEN_SAMPLE_INDICES]])
+        out["top8_index"].append([int(v) for v in order])
+        out["top8_value"].append([float(v) for v in logits[order]])
+        log(f"  token {step}: {current} margin {out['top1_minus_top2'][-1]:.4f}")
+    out["token_hash"] = O.hash_tokens(out["tokens"])
+    return out
+
+
+def qwen3_8b_golden(threads: int = 0) -> dict:
+    import time
+    t0 = time.time()
+
+    def log(text):
+        print(f"[{time.time() - t0:7.0f}s] {text}", flush=True)
+
+    if threads:
+        O.lib().oracle_set_threads(threads)
+    cfg = synth.QWEN3_8B
+    log("generating the checkpoint")
+    ck = synth.dense_checkpoint(cfg, fill=O.synth_normal_bf16)
+    prompt = synth.prompt_ids(cfg)
+    out = {"config": cfg.name, "prompt_tokens": int(prompt.size), "prompt_hash": O.hash_tokens(prompt),
+           "sample_indices": QWEN_SAMPLE_INDICES}
+    # depth sweep first: it is the cheap part
+    sweep_prompt = synth.prompt_ids(cfg, count=SWEEP_PROMPT_TOKENS)
+    sweep = {"depths": SWEEP_DEPTHS, "prompt_tokens": SWEEP_PROMPT_TOKENS, "sample_indices": SWEEP_SAMPLE_INDICES,
+             "serial_samples": [], "lanes8_samples": [], "self_distance": [], "serial_argmax": [],
+             "serial_margin": []}
+    for depth in SWEEP_DEPTHS:
+        cut = _prefix_checkpoint(ck, depth)
+        rows = []
+        for lanes in (1, 8):
+            O.set_sum_lanes(lanes)
+            dec = O.Decoder(cut, SWEEP_PROMPT_TOKENS, mode=O.MODE_CUDA)
+            for token in sweep_prompt[:-1]:
+                dec.step(int(token), want_logits=False)
+            rows.append(dec.step(int(sweep_prompt[-1]), want_logits=True))
+            dec.close()
+        O.set_sum_lanes(1)
+        top2 = np.sort(rows[0])[-2:]
+        sweep["serial_samples"].append([float(v) for v in rows[0][SWEEP_SAMPLE_INDICES]])
+        sweep["lanes8_samples"].append([float(v) for v in rows[1][SWEEP_SAMPLE_INDICES]])
+        sweep["self_distance"].append(float(np.abs(rows[0] - rows[1]).max()))
+        sweep["serial_argmax"].append(int(np.argmax(rows[0])))
+        sweep["serial_margin"].append(float(top2[1] - top2[0]))
+        log(f"depth {depth}: oracle self-distance {sweep['self_distance'][-1]:.4e}")
+    out["depth_sweep"] = sweep
+    for name, mode, steps in (("cuda", O.MODE_CUDA, 64), ("cpu", O.MODE_CPU, 32)):
+        log(f"contract {name}: {prompt.size}-token prompt, {steps} greedy tokens")
+        dec = O.Decoder(ck, cfg.prompt_tokens + steps, mode=mode)
+        out[name] = _record_stream(dec, prompt, steps, log)
+        dec.close()
     return out
 
 
@@ -104,6 +195,11 @@ def reference_prototypes() -> str:
 
 
 if __name__ == "__main__":
+    if len(sys.argv) > 1 and sys.argv[1] == "qwen3_8b":
+        golden = qwen3_8b_golden(int(sys.argv[2]) if len(sys.argv) > 2 else 0)
+        with open(os.path.join(HERE, "qwen3_8b.json"), "w") as f:
+            json.dump(golden, f, indent=None, separators=(",", ":"))
+        sys.exit(0)
     with open(os.path.join(HERE, "tiny_qwen3.json"), "w") as f:
         json.dump(tiny_golden(), f, indent=1)
     if os.path.exists(REFERENCE_HEADER):
