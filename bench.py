@@ -11,11 +11,18 @@ Workload (N = 1): Qwen3-8B architecture, random-init BF16 weights ~N(0, 0.02) se
   e2e       the same metric through the C ABI the way a streaming server calls it:
             one session_advance(steps=1) per token, host wall clock, device->host copy
             of the token slot and a stream synchronise inside every step
-  roofline  the projection kernel (all five shapes): algorithmic weight+vector bytes
-            per token / its summed device time per token, from an event-per-launch
-            pass run after the timed region
+  roofline  the projection kernel (all five shapes): algorithmic weight+vector bytes per
+            token / the time its launches are busy inside ordinary graph replays, net of
+            overlap with their neighbours (kernel-written %globaltimer stamps of a fork of
+            the session that shares the weights); `isolated_frac` is the same bytes over an
+            event-per-launch pass outside the graph
+  parity    the decoded tokens against the committed oracle stream of the same prompt
+            (tests/golden/qwen3_8b.json): first diverging step and the oracle's margin there
   cpu_baseline / --impl reference: the CPU restatement of the reference decoder on
-            the host cores (bounded sample)
+            the host cores (bounded sample at the same context)
+  gpu_baseline (N = 1): the reference's own CUDA library (cuBLASLt projections), built from
+            the reference checkout into oracle/_ref, decoding the same workload in a child
+            process after everything else has been measured
 """
 from __future__ import annotations
 
@@ -34,10 +41,13 @@ if ROOT not in sys.path:
 import numpy as np  # noqa: E402
 
 METRIC = "Qwen3-8B-arch BF16 batch-1 decode tok/s"
-# DRAM bytes (read + write) of the projection kernel's launches of one Qwen3-8B token, from the ncu
-# capture summarised in profiles/projection_stream_kernel_qwen3_8b_shapes.md:
-# 36 x (QKV 50.41 + O 33.63 + gate/up 205.18 + down 104.43 MB) + lm_head 1248.89 MB.
+# DRAM bytes (read + write) of the projection kernel's launches of one Qwen3-8B token.  NOT measured
+# by a bench run (a profiler cannot sit inside the timed region): taken from the ncu capture
+# summarised in profiles/projection_stream_kernel_qwen3_8b_shapes.md, per launch
+# QKV 50.41 + O 33.63 + gate/up 205.18 + down 104.43 MB, lm_head 1248.89 MB.
 NCU_PROJECTION_TRAFFIC_PER_TOKEN = 36 * (50.41e6 + 33.63e6 + 205.18e6 + 104.43e6) + 1248.89e6
+NCU_TRAFFIC_SOURCE = ("ncu dram__bytes_read.sum + dram__bytes_write.sum per launch, capture summarised in "
+                      "profiles/projection_stream_kernel_qwen3_8b_shapes.md (not re-measured by this run)")
 UNIT = "tok/s"
 
 
@@ -132,48 +142,194 @@ def config_block(cfg, gpus: int, extra: dict | None = None) -> dict:
     return block
 
 
-def cpu_decode_sample(ck, cfg, budget_s: float, max_tokens: int, prompt_len: int = 2):
-    """Times the CPU restatement of the reference decoder (oracle, CPU contract) on a
-    short prompt: returns (tok/s over the decode tokens, tokens timed, threads)."""
+def host_threads() -> int:
+    """All host cores, whatever OMP_NUM_THREADS says (torch.distributed.run exports 1)."""
+    return max(1, len(os.sched_getaffinity(0)) if hasattr(os, "sched_getaffinity") else (os.cpu_count() or 1))
+
+
+def cpu_decode_sample(ck, cfg, budget_s: float, max_tokens: int, warmup_tokens: int = 1):
+    """Times the CPU restatement of the reference decoder (oracle, CPU contract) at the workload's
+    context: the cache is positioned at the prompt length (patterned rows instead of a CPU prefill,
+    which alone would take minutes; a decode step costs the same whatever the cached values are),
+    then `warmup_tokens` untimed and up to `max_tokens` timed decode steps within `budget_s`.
+    Returns (tok/s, tokens timed, threads)."""
     from nerva_b200 import synth
     from oracle import oracle as O
-    dec = O.Decoder(ck, prompt_len + max_tokens + 1, mode=O.MODE_CPU)
-    prompt = synth.prompt_ids(cfg, count=prompt_len)
-    for t in prompt[:-1]:
-        dec.step(int(t), want_logits=False)
-    token = int(prompt[-1])
+    threads = host_threads()
+    O.lib().oracle_set_threads(threads)
+    dec = O.Decoder(ck, cfg.prompt_tokens + warmup_tokens + max_tokens + 1, mode=O.MODE_CPU)
+    dec.seek_for_timing(cfg.prompt_tokens)
+    token = int(synth.prompt_ids(cfg, count=1)[0])
+    for _ in range(warmup_tokens):
+        token = O.argmax(dec.step(token), O.MODE_CUDA)
     done, elapsed = 0, 0.0
     while done < max_tokens and (done == 0 or elapsed + elapsed / done < budget_s):
         t0 = time.perf_counter()
         logits = dec.step(token)
-        token = O.argmax(logits, O.MODE_CPU)
+        token = O.argmax(logits, O.MODE_CUDA)
         elapsed += time.perf_counter() - t0
         done += 1
-    threads = O.lib().oracle_get_threads()
     dec.close()
     return done / elapsed, done, threads
+
+
+def cpu_sample_text(cfg, done: int, requested: int, threads: int) -> str:
+    return (f"{done} of {requested} decode steps of the full {cfg.layers}-layer model at context "
+            f"{cfg.prompt_tokens} (cache positioned there with patterned rows instead of a CPU prefill), "
+            f"{threads} host threads, row-parallel mat-vec")
 
 
 def run_reference(args, cfg) -> dict:
     """The reference's own CPU implementation of the path (the C restatement of its
     Rust decoder; the Rust original cannot be compiled on this image), on all host
-    threads.  Each step is one decoded token of the same model; steps stop early
-    when the wall-clock budget is spent."""
-    from nerva_b200 import ops, synth
-    ck = synth.dense_checkpoint(cfg, fill=ops.synth_normal_bf16)
+    threads.  Each step is one decoded token of the same model at the same context; steps
+    stop early when the wall-clock budget is spent.  Weights come from the oracle's own
+    generator: this arm does not load the CUDA library."""
+    from nerva_b200 import synth
+    from oracle import oracle as O
+    O.lib().oracle_set_threads(host_threads())
+    ck = synth.dense_checkpoint(cfg, fill=O.synth_normal_bf16)
     budget = float(os.environ.get("NERVA_REFERENCE_BUDGET_S", "150"))
-    warm_rate, _, threads = cpu_decode_sample(ck, cfg, budget_s=0.0, max_tokens=max(1, min(args.warmup, 1)))
-    rate, done, threads = cpu_decode_sample(ck, cfg, budget_s=budget, max_tokens=args.steps)
-    sample = (f"{done} of {args.steps} requested decode steps of the full model after a 2-token prompt "
-              f"(stops at a {budget:.0f} s budget), {threads} threads")
+    rate, done, threads = cpu_decode_sample(ck, cfg, budget_s=budget, max_tokens=args.steps,
+                                            warmup_tokens=max(1, min(args.warmup, 2)))
+    sample = cpu_sample_text(cfg, done, args.steps, threads) + f"; stops at a {budget:.0f} s budget"
     return {
         "impl": "reference", "metric": METRIC, "value": rate, "unit": UNIT, "n_gpus": args.gpus,
-        "steps": done, "warmup": 1, "ms_per_step": 1000.0 / rate, "higher_is_better": True, "scaling": "weak",
-        "vs_baseline": None, "dtype": "bf16", "data": "synthetic", "config": config_block(cfg, 1),
+        "steps": done, "warmup": max(1, min(args.warmup, 2)), "ms_per_step": 1000.0 / rate, "higher_is_better": True,
+        "scaling": "strong", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+        "config": config_block(cfg, args.gpus),
         "cpu_baseline": {"value": rate, "unit": UNIT, "cores": threads, "kind": "port", "sample": sample},
         "e2e": {"value": rate, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
     }
+
+
+def golden_stream(cfg):
+    """The committed oracle stream of the headline workload, or None for other workloads."""
+    path = os.path.join(ROOT, "tests", "golden", "qwen3_8b.json")
+    if cfg.name != "qwen3-8b" or cfg.prompt_tokens != 512 or not os.path.exists(path):
+        return None
+    with open(path) as f:
+        return json.load(f)["cuda"]
+
+
+def parity_block(cfg, tokens) -> dict:
+    """Compares the decoded tokens (from the first generated one) with the oracle's stream."""
+    golden = golden_stream(cfg)
+    if golden is None:
+        return {"reference": None, "note": "no committed oracle stream for this workload"}
+    want = golden["tokens"]
+    n = min(len(tokens), len(want))
+    at = next((i for i in range(n) if int(tokens[i]) != int(want[i])), None)
+    return {
+        "reference": "tests/golden/qwen3_8b.json: CPU oracle, CUDA numeric contract, serial fp32 sums",
+        "tokens_compared": n, "tokens_identical": n if at is None else at,
+        "first_divergence_step": at,
+        "margin_at_divergence": None if at is None else golden["top1_minus_top2"][at],
+        "note": "after a divergence the two streams decode different sequences; a divergence is a tie when the "
+                "oracle's top-1 minus top-2 margin there is below twice its own distance to itself under another "
+                "fp32 summation order (0.185 at 36 layers)",
+    }
+
+
+def timeline_busy_us(session, loop, cfg, steps: int) -> dict:
+    """Per operator kind, the time its launches are busy inside ordinary graph replays, net of
+    overlap: launches are walked in launch order and each is charged from max(its first stamp, the
+    end of everything before it) to its last stamp.  Mean over `steps` replays, microseconds."""
+    kinds = ("qkv", "attention", "o", "gate_up", "down")
+    total = {k: 0.0 for k in kinds + ("lm_head",)}
+    span = 0.0
+    for _ in range(steps):
+        out = loop.advance(1)
+        if not out.tokens:
+            raise RuntimeError("timeline step failed: " + out.error)
+        t = session.read_timeline().astype(np.int64)
+        covered = None
+        first = None
+        for node in range(5 * cfg.layers + 1):
+            row = t[node]
+            begin, end = int(min(row[0], row[4])), int(max(row[3], row[7]))
+            if first is None:
+                first = begin
+            kind = "lm_head" if node == 5 * cfg.layers else kinds[node % 5]
+            lo = begin if covered is None else max(begin, covered)
+            if end > lo:
+                total[kind] += (end - lo) / 1e3
+            covered = end if covered is None else max(covered, end)
+        span += (covered - first) / 1e3
+    out = {k: v / steps for k, v in total.items()}
+    out["step_span"] = span / steps
+    return out
+
+
+def gpu_baseline_child(args, cfg) -> dict:
+    """Runs the reference's CUDA library on the same workload in a child process (its own CUDA
+    context, nothing of this library on its path) and returns its JSON line."""
+    lib_path = os.path.join(ROOT, "oracle", "_ref", "libnerva_ref_decode.so")
+    if not os.path.exists(lib_path):
+        return {"unavailable": "oracle/_ref/libnerva_ref_decode.so has not been built (needs the reference checkout)"}
+    cmd = [sys.executable, os.path.abspath(__file__), "--workload", "reference-gpu", "--steps", str(min(args.steps, 64)),
+           "--warmup", str(max(args.warmup, 3)), "--config", args.config]
+    if args.layers:
+        cmd += ["--layers", str(args.layers)]
+    if args.prompt_tokens:
+        cmd += ["--prompt-tokens", str(args.prompt_tokens)]
+    try:
+        done = subprocess.run(cmd, capture_output=True, text=True, timeout=float(os.environ.get("NERVA_GPU_BASELINE_S", "420")))
+    except subprocess.TimeoutExpired:
+        return {"unavailable": "the reference CUDA library did not finish within its time limit"}
+    for line in reversed(done.stdout.strip().splitlines()):
+        if line.startswith("{"):
+            return json.loads(line)
+    return {"unavailable": f"no result line (rc {done.returncode}): {done.stderr.strip()[-300:]}"}
+
+
+def run_reference_gpu(args, cfg) -> None:
+    """The reference's CUDA decode library (cuBLASLt projections, its own kernels around them) on
+    this workload: session_create with planned descriptors, session_start (its chunked cuBLAS
+    prefill), warm-up, then `steps` graph replays timed by its own start/stop events."""
+    from nerva_b200 import ffi, synth
+    from nerva_b200.session import CudaHfDecodeSequenceLoop, CudaHfDecodeSequenceSession, SmokeStatus
+    from oracle import oracle as O
+    O.lib().oracle_set_threads(host_threads())
+    library = ffi.load_abi_library(os.path.join(ROOT, "oracle", "_ref", "libnerva_ref_decode.so"))
+    ck = synth.dense_checkpoint(cfg, fill=O.synth_normal_bf16)
+    prompt = synth.prompt_ids(cfg)
+    warm = max(args.warmup, 3)
+    t0 = time.perf_counter()
+    session = CudaHfDecodeSequenceSession(ck, cfg.prompt_tokens + 1 + warm + args.steps + 4, use_descriptors=True,
+                                          library=library)
+    if session.status != SmokeStatus.OK:
+        print(json.dumps({"unavailable": f"reference session_create failed: cuda_error "
+                                         f"{session.create_result.cuda_error}, stage {session.create_result.failure_stage}"}))
+        return
+    create_s = time.perf_counter() - t0
+    t0 = time.perf_counter()
+    start, loop = CudaHfDecodeSequenceLoop.start(session, prompt)
+    if start.status != SmokeStatus.OK:
+        print(json.dumps({"unavailable": f"reference session_start failed: cuda_error {start.cuda_error}"}))
+        return
+    prefill_s = time.perf_counter() - t0
+    head = loop.advance(1).tokens
+    warm_out = loop.advance(warm)
+    timed = loop.advance(args.steps)
+    if timed.status != SmokeStatus.OK or timed.device_elapsed_ns == 0:
+        print(json.dumps({"unavailable": f"reference session_advance failed: cuda_error {timed.cuda_error}"}))
+        return
+    session.destroy()
+    rate = args.steps / (timed.device_elapsed_ns * 1e-9)
+    tokens = head + warm_out.tokens + timed.tokens
+    peaks = measured_peaks()
+    nbytes = cfg.projection_bytes_per_token()
+    print(json.dumps({
+        "impl": "reference CUDA library (oracle/_ref/libnerva_ref_decode.so: the reference's session and kernels, "
+                "cuBLASLt projections, built for sm_100)",
+        "value": rate, "unit": UNIT, "steps": args.steps, "warmup": warm,
+        "ms_per_step": 1e3 / rate, "graph_nodes": int(timed.graph_nodes),
+        "whole_step_frac": nbytes * rate / 1e9 / peaks["hbm_gbs"],
+        "setup_s": {"session_create_with_autotune": create_s, "prefill": prefill_s},
+        "parity": parity_block(cfg, tokens),
+    }), flush=True)
 
 
 def run_ours(args, cfg, rank: int, world: int) -> dict:
@@ -192,8 +348,8 @@ def run_ours(args, cfg, rank: int, world: int) -> dict:
     gen_s = time.perf_counter() - t0
     prompt = synth.prompt_ids(cfg)
     profile_steps = 4
-    timeline_steps = 10 if args.timeline else 0
-    max_context = cfg.prompt_tokens + 1 + args.warmup + 2 * args.steps + profile_steps + timeline_steps + 8
+    timeline_steps = 8
+    max_context = cfg.prompt_tokens + 1 + args.warmup + 2 * args.steps + profile_steps + 2 * timeline_steps + 8
     t0 = time.perf_counter()
     session = CudaHfDecodeSequenceSession(ck, max_context, engine=args.engine)
     if session.status != SmokeStatus.OK:
@@ -223,12 +379,28 @@ def run_ours(args, cfg, rank: int, world: int) -> dict:
     device_s = timed.device_elapsed_ns * 1e-9
     # end to end: one C-ABI call per token, host clock, D2H of the slot + synchronise each step
     t0 = time.perf_counter()
-    e2e_tokens = 0
+    e2e_stream = []
     for _ in range(args.steps):
         out = loop.advance(1)
-        e2e_tokens += len(out.tokens)
+        e2e_stream += out.tokens
     e2e_s = time.perf_counter() - t0
+    e2e_tokens = len(e2e_stream)
     clock_info = clocks.stop()
+    stream = first.tokens + warm.tokens + timed.tokens + e2e_stream
+
+    # In-step time of every operator: a fork of the session (shared weights, cloned state) created
+    # with the stamps switched on replays the same graph shape; the timed region above ran without them.
+    busy = None
+    if world == 1 and args.engine == 0:
+        os.environ["NERVA_B200_TIMELINE"] = "1"
+        fork = session.fork_shared_weights()
+        if not args.timeline:
+            del os.environ["NERVA_B200_TIMELINE"]
+        if fork.status == SmokeStatus.OK:
+            fork_loop = CudaHfDecodeSequenceLoop(fork)
+            fork_loop.advance(3)
+            busy = timeline_busy_us(fork, fork_loop, cfg, timeline_steps)
+            fork.destroy()
     timeline = None
     if args.timeline:
         # %globaltimer stamps written by the kernels themselves during ordinary graph replays
@@ -251,14 +423,22 @@ def run_ours(args, cfg, rank: int, world: int) -> dict:
 
     device_s = _max_over_ranks(device_s, world)
     e2e_s = _max_over_ranks(e2e_s, world)
-    proj_ns = sum(prof[k]["ns"] for k in ("qkv", "o", "gate_up", "down", "lm_head")) / profile_steps
-    proj_launches = sum(prof[k]["launches_per_step"] for k in ("qkv", "o", "gate_up", "down", "lm_head"))
+    proj_kinds = ("qkv", "o", "gate_up", "down", "lm_head")
+    isolated_ns = sum(prof[k]["ns"] for k in proj_kinds) / profile_steps
+    proj_launches = sum(prof[k]["launches_per_step"] for k in proj_kinds)
     # per GPU: this rank's weight slices + bf16 vectors
     bytes_per_token = ck.config.projection_bytes_per_token() + 2 * cfg.hidden * (3 * cfg.layers + 1)
     peaks = measured_peaks()
-    achieved = bytes_per_token / (proj_ns * 1e-9) / 1e9
+    step_us = 1e6 * device_s / args.steps
     kernel_name = "projection_stream_kernel (QKV, O, gate-up, down, lm_head)"
-    kernel_us = proj_ns / 1e3
+    if busy is not None:
+        kernel_us = sum(busy[k] for k in proj_kinds)
+        time_source = ("in-step: kernel-written %globaltimer stamps during ordinary graph replays of a fork of the "
+                       "session, launches charged net of overlap with their predecessors")
+    else:
+        kernel_us = isolated_ns / 1e3
+        time_source = "event-per-launch pass outside the graph (no in-step stamps on this configuration)"
+    achieved = bytes_per_token / (kernel_us * 1e-6) / 1e9
     if args.engine == 1:
         # one kernel per token: its launch duration is the event-timed step itself; its
         # algorithmic bytes add the KV rows read at the mean timed context and the KV row written
@@ -267,15 +447,17 @@ def run_ours(args, cfg, rank: int, world: int) -> dict:
         bytes_per_token = bytes_per_token + int(kv_bytes)
         proj_launches = 1
         kernel_name = "decode_step_kernel (whole step: projections + attention + sampling)"
-        kernel_us = 1e6 * device_s / args.steps
+        kernel_us = step_us
+        time_source = "the event-timed step (one launch per token)"
         achieved = bytes_per_token / (device_s / args.steps) / 1e9
     value = args.steps / device_s  # all ranks decode the same sequence together
     result = {
         "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
         "warmup": max(args.warmup, 3), "ms_per_step": 1000.0 * device_s / args.steps, "higher_is_better": True,
-        "scaling": "weak" if world == 1 else "strong", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
-        "config": config_block(cfg, world, {"timed_context": f"{cfg.prompt_tokens + 1 + max(args.warmup, 3)}.."
-                                                              f"{cfg.prompt_tokens + 1 + max(args.warmup, 3) + args.steps}"}),
+        "scaling": "strong", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+        "config": config_block(cfg, world),
+        "timed_context": f"{cfg.prompt_tokens + 1 + max(args.warmup, 3)}.."
+                         f"{cfg.prompt_tokens + 1 + max(args.warmup, 3) + args.steps}",
         "clocks": clock_info,
         "e2e": {"value": e2e_tokens / e2e_s, "unit": UNIT, "h2d_bytes_per_step": 0,
                 "d2h_bytes_per_step": 44,
@@ -288,25 +470,31 @@ def run_ours(args, cfg, rank: int, world: int) -> dict:
             "achieved": achieved, "peak": peaks["hbm_gbs"], "unit": "GB/s", "frac": achieved / peaks["hbm_gbs"],
             "peak_source": peaks["source"],
             "traffic": NCU_PROJECTION_TRAFFIC_PER_TOKEN if (world == 1 and cfg.name == "qwen3-8b") else None,
-            "traffic_unit": "DRAM bytes per token over the same launches as bytes_per_token (ncu, see profiles/)",
+            "traffic_source": NCU_TRAFFIC_SOURCE,
             "launches_per_token": proj_launches, "bytes_per_token": bytes_per_token,
-            "us_per_token": kernel_us, "engine": args.engine,
+            "us_per_token": kernel_us, "time_source": time_source, "engine": args.engine,
+            "isolated_frac": (bytes_per_token / (isolated_ns * 1e-9) / 1e9) / peaks["hbm_gbs"],
+            "isolated_us_per_token": isolated_ns / 1e3,
             "whole_step_frac": (bytes_per_token * args.steps / device_s / 1e9) / peaks["hbm_gbs"],
         },
+        "parity": parity_block(cfg, stream),
+        "in_step_us_per_token": busy,
         "profile_us_per_token": {k: v["ns"] / profile_steps / 1e3 for k, v in prof.items()},
-        "setup_s": {"generate_weights": gen_s, "session_create": create_s, "prefill_by_decode": prefill_s},
+        "setup_s": {"generate_weights": gen_s, "session_create": create_s, "prefill": prefill_s},
         "graph_nodes": int(timed.graph_nodes),
         "token_hash": f"{timed.observed_token_hash:016x}",
     }
     if timeline is not None:
         result["timeline"] = timeline
     if rank == 0 and world == 1 and not args.no_cpu_baseline:
+        from oracle import oracle as O
         rate, done, threads = cpu_decode_sample(ck, cfg, budget_s=float(os.environ.get("NERVA_CPU_BUDGET_S", "20")),
                                                 max_tokens=8)
-        result["cpu_baseline"] = {
-            "value": rate, "unit": UNIT, "cores": threads, "kind": "port",
-            "sample": f"{done} decode steps of the full model after a 2-token prompt (CPU restatement of the "
-                      f"reference decoder, row-parallel mat-vec)"}
+        result["cpu_baseline"] = {"value": rate, "unit": UNIT, "cores": threads, "kind": "port",
+                                  "sample": cpu_sample_text(cfg, done, 8, threads)}
+        del ck
+        if not args.no_gpu_baseline:
+            result["gpu_baseline"] = gpu_baseline_child(args, cfg)
     return result
 
 
@@ -329,7 +517,7 @@ def run_operator_workloads(kind: str) -> None:
                 print(json.dumps({"workload": "decode-linear", "shape": name, "N": rows, "K": cols, "M": m,
                                   "us": ns / 1e3, "algorithmic_bytes": nbytes, "GB/s": gbs,
                                   "frac_of_measured_hbm": gbs / peak["hbm_gbs"],
-                                  "note": "M > 1 re-streams the weights once per token (no skinny-GEMM kernel yet)"
+                                  "note": "block kernel on the tensor pipe (tcgen05), weights streamed once for the block"
                                   if m > 1 else "weight-streaming GEMV"}), flush=True)
         return
     heads, kv_heads, d = 32, 8, 128
@@ -377,12 +565,14 @@ def main() -> None:
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--config", default="qwen3-8b", choices=["qwen3-8b", "tiny"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-gpu-baseline", action="store_true",
+                    help="skip the child process that times the reference's own CUDA library on this workload")
     ap.add_argument("--engine", type=int, default=0, choices=[0, 1],
                     help="0: one kernel per operator in a CUDA graph; 1: the whole-step kernel")
     ap.add_argument("--layers", type=int, default=0,
                     help="cut the model to this many layers (profiler captures only; not a bench line)")
     ap.add_argument("--prompt-tokens", type=int, default=0, help="override the prompt length")
-    ap.add_argument("--workload", default="decode", choices=["decode", "linear", "attention"],
+    ap.add_argument("--workload", default="decode", choices=["decode", "linear", "attention", "reference-gpu"],
                     help="decode: the bench line; linear / attention: per-operator sweeps of the isolated "
                          "projection shapes and of long-context attention (one JSON line per case)")
     ap.add_argument("--timeline", action="store_true",
@@ -391,11 +581,15 @@ def main() -> None:
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
     local = int(os.environ.get("LOCAL_RANK", "0"))
-    if args.workload != "decode":
+    if args.workload in ("linear", "attention"):
         if rank == 0:
             run_operator_workloads(args.workload)
         return
     cfg = workload(args.config, args.layers, args.prompt_tokens)
+    if args.workload == "reference-gpu":
+        if rank == 0:
+            run_reference_gpu(args, cfg)
+        return
     if args.impl == "reference":
         if rank == 0:
             print(json.dumps(run_reference(args, cfg)), flush=True)

@@ -545,8 +545,10 @@ typedef struct NervaCudaProjectionBenchRequest {
   uint32_t block_tokens;
 } NervaCudaProjectionBenchRequest;
 
-/* nerva_cuda_api.h:1084-1144.  The `cublaslt_*` fields stay zero: this library
- * links no BLAS.  `custom_*` describe the hand-written projection kernel. */
+/* nerva_cuda_api.h:1084-1144.  The single-token `cublaslt_*` fields stay zero: this library
+ * links no BLAS.  `custom_*` describe the hand-written single-token projection kernel.  With
+ * block_tokens > 1 the `block_cublaslt_*` fields (the reference's block path) carry this
+ * library's block kernel on the tensor pipe, which streams the weights once for the block. */
 typedef struct NervaCudaProjectionBenchResult {
   int32_t status;
   int32_t cuda_error;
@@ -871,6 +873,12 @@ int nerva_b200_session_comm_handle(NervaCudaHfDecodeSequenceSession *session, ui
 /* handles: world x 64 bytes in rank order (the rank's own entry is ignored). */
 int nerva_b200_session_attach_peers(NervaCudaHfDecodeSequenceSession *session,
                                     const uint8_t *handles, uint32_t world);
+/* Diagnostic stand-in for attach_peers when no peer exists: every rank's exchange buffer is taken
+ * to be this rank's own, so this rank's partial sums arrive and nobody else's ever do.  The first
+ * exchange of a step then runs into its wait limit, sets the error word (code 6), and the call
+ * that queued the step fails with status -1; the context stays usable.  It lets a test exercise
+ * the bounded-wait path on one GPU without faulting or hanging anything. */
+int nerva_b200_session_attach_loopback(NervaCudaHfDecodeSequenceSession *session);
 
 /* Tuning aid of the per-operator engine: nanosecond stamps (%globaltimer) of the
  * last step, 8 per launch, launches ordered [layer][QKV, attention, O, gate/up,

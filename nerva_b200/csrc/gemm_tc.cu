@@ -1,0 +1,506 @@
+// Block projection on the tensor pipe: bf16 W[rows][cols] times a block of bf16 activation rows
+// X[tokens][cols], fp32 accumulate, for 2..256 tokens at once.  The weights are streamed from HBM
+// once for the whole block.  Replaces the reference's cublasLtMatmul of the packed block step and
+// of the chunked prefill (hf_decode_sequence/projection.cu:192-262 launch_lt_gemm_tokens_plan,
+// session_api_batch_fork_destroy.inc.cu:1-310, session_decode_prefill.inc.cu:1879-2245).
+//
+// Shape of the work.  The operands are swapped so that the weight rows are the M dimension of the
+// MMA: D[128 weight rows][N tokens] += W_tile[128][64] * X_tile[N][64]^T per 64-wide slice of the
+// inner dimension, `tcgen05.mma.cta_group::1.kind::f16` (M = 128, N = tokens rounded up to 16,
+// K = 16 per instruction) with both operands in shared memory and the fp32 accumulator in tensor
+// memory.  A 64-element slice of a row is 128 bytes, i.e. one 128-byte swizzle atom, so a weight
+// tile and an activation tile arrive by ONE 2-D `cp.async.bulk.tensor` each (SWIZZLE_128B) in the
+// canonical K-major layout the MMA descriptors describe.  No cluster, no multicast.
+//
+// Decomposition ("stream-K").  The sequence of (row tile, 64-wide slice) pairs is cut into one
+// contiguous, equally long run per thread block, so every SM streams the same number of weight
+// bytes whatever the shape (QKV has 48 row tiles, lm_head 1187).  A run that starts or ends in the
+// middle of a row tile leaves a partial accumulator: it goes to a workspace slot, the blocks that
+// share the tile take a ticket, and the last one adds the partials in ascending block order before
+// it runs the epilogue.  The partition depends on the shape only, so a token's result does not
+// depend on which other tokens share its block, and results are bit-stable run to run.
+//
+// Roles inside a block (192 threads): warp 0 issues the TMA copies into an mbarrier ring, warp 1
+// allocates tensor memory and issues the MMAs (one elected lane), warps 2..5 read the accumulator
+// with `tcgen05.ld` (each warp its own 32-lane quarter) and run the epilogue; two accumulator
+// buffers let the epilogue of one tile overlap the MMAs of the next.  Every wait is bounded; a
+// wait that gives up sets the error word and an abort flag that all roles poll, the block drains
+// and frees its tensor memory before it returns.
+#include <cuda.h>
+#include <cudaTypedefs.h>
+
+#include <mutex>
+
+#include "common.cuh"
+#include "kernels.cuh"
+
+namespace nb {
+namespace {
+
+constexpr uint32_t kTileRows = 128;   // MMA M
+constexpr uint32_t kSliceK = 64;      // bf16 elements per ring stage along the inner dimension (128 bytes)
+constexpr uint32_t kUmmaK = 16;       // inner elements per MMA instruction
+constexpr uint32_t kATileBytes = kTileRows * kSliceK * 2u;
+constexpr uint32_t kMaxStages = 8;
+constexpr uint32_t kGemmThreads = 192;
+constexpr uint32_t kEpilogueThreads = 128;
+constexpr uint32_t kTmemColumns = 512;  // two accumulator buffers of up to 256 fp32 columns
+constexpr uint32_t kAccStride = 256;
+constexpr uint32_t kGroup = 16;         // tokens per tcgen05.ld
+
+struct GemmShared {
+  uint64_t full[kMaxStages], empty[kMaxStages];
+  uint64_t acc_full[2], acc_empty[2];
+  uint32_t tmem_base;
+  uint32_t abort;
+  uint32_t ticket;
+};
+
+struct GemmKernelParams {
+  uint32_t rows, cols, tokens, n_pad;  // n_pad: tokens rounded up to 16 (the MMA N)
+  uint32_t stages;
+  uint32_t epilogue;
+  const float *resid_in;
+  float *out_f32;
+  uint16_t *out_bf16;
+  float *workspace;
+  uint32_t *tickets;
+  uint32_t *error_word;
+};
+
+// ---- static partition, computed identically by every role and by the fix-up ----
+struct Partition {
+  uint32_t tiles, slices, blocks;
+  uint64_t total;
+  __device__ __host__ uint64_t begin(uint32_t b) const { return total * b / blocks; }
+  __device__ __host__ uint64_t end(uint32_t b) const { return total * (b + 1ull) / blocks; }
+};
+__device__ __host__ inline Partition make_partition(uint32_t rows, uint32_t cols, uint32_t blocks) {
+  Partition p;
+  p.tiles = (rows + kTileRows - 1u) / kTileRows;
+  p.slices = cols / kSliceK;
+  p.total = static_cast<uint64_t>(p.tiles) * p.slices;
+  p.blocks = blocks;
+  return p;
+}
+// First / last block whose run touches tile t.
+__device__ inline uint32_t first_block_of_tile(const Partition &p, uint32_t t) {
+  const uint64_t at = static_cast<uint64_t>(t) * p.slices;
+  uint32_t b = static_cast<uint32_t>(at * p.blocks / p.total);
+  while (b + 1u < p.blocks && p.end(b) <= at) ++b;
+  while (b > 0 && p.end(b - 1u) > at) --b;
+  return b;
+}
+__device__ inline uint32_t last_block_of_tile(const Partition &p, uint32_t t) {
+  const uint64_t at = static_cast<uint64_t>(t + 1u) * p.slices - 1ull;
+  uint32_t b = static_cast<uint32_t>(at * p.blocks / p.total);
+  while (b + 1u < p.blocks && p.end(b) <= at) ++b;
+  while (b > 0 && p.begin(b) > at) --b;
+  return b;
+}
+// Workspace slot of block b's partial accumulator of tile t: slot 0 when the tile is where the
+// block's run begins, slot 1 when it is where the run ends in another tile.
+__device__ inline uint32_t partial_slot(const Partition &p, uint32_t b, uint32_t t) {
+  return 2u * b + (static_cast<uint32_t>(p.begin(b) / p.slices) == t ? 0u : 1u);
+}
+
+struct Segment {
+  uint32_t tile, slice_begin, slice_end;
+};
+// Walks the segments of this block's run.
+struct SegmentWalk {
+  uint64_t pos, end;
+  uint32_t slices;
+  __device__ bool next(Segment *s) {
+    if (pos >= end) return false;
+    s->tile = static_cast<uint32_t>(pos / slices);
+    s->slice_begin = static_cast<uint32_t>(pos % slices);
+    const uint64_t left = end - pos;
+    const uint32_t room = slices - s->slice_begin;
+    s->slice_end = s->slice_begin + (left < room ? static_cast<uint32_t>(left) : room);
+    pos += s->slice_end - s->slice_begin;
+    return true;
+  }
+};
+
+// ---- PTX wrappers ----
+__device__ __forceinline__ bool abortable_wait(uint64_t *bar, uint32_t parity, volatile uint32_t *abort,
+                                               uint32_t *error_word) {
+  if (mbar_try_wait(bar, parity)) return true;
+  const long long start = clock64();
+  for (;;) {
+#pragma unroll 1
+    for (uint32_t spin = 0; spin < 64; ++spin) {
+      if (mbar_try_wait(bar, parity)) return true;
+    }
+    if (*abort != 0u) return false;
+    if (clock64() - start > kWaitCycleLimit) {
+      *abort = 1u;
+      report_error(error_word, kErrTmaWaitTimeout);
+      return false;
+    }
+  }
+}
+__device__ __forceinline__ void mbar_arrive(uint64_t *bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_addr(bar)) : "memory");
+}
+__device__ __forceinline__ void tma_load_2d(void *dst, const CUtensorMap *map, uint32_t x, uint32_t y, uint64_t *bar,
+                                            uint64_t policy) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes.L2::cache_hint "
+      "[%0], [%1, {%2, %3}], [%4], %5;" ::"r"(smem_addr(dst)),
+      "l"(map), "r"(x), "r"(y), "r"(smem_addr(bar)), "l"(policy)
+      : "memory");
+}
+__device__ __forceinline__ uint64_t l2_evict_last_policy() {
+  uint64_t policy;
+  asm volatile("createpolicy.fractional.L2::evict_last.b64 %0, 1.0;" : "=l"(policy));
+  return policy;
+}
+__device__ __forceinline__ void tcgen05_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tcgen05_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tcgen05_commit(uint64_t *bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_addr(bar))
+               : "memory");
+}
+__device__ __forceinline__ void tcgen05_mma_f16(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc,
+                                                uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}" ::"r"(tmem_d),
+      "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+__device__ __forceinline__ void tmem_load16(uint32_t taddr, float *v) {
+  uint32_t r[16];
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+        "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+      : "r"(taddr));
+  asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+  for (uint32_t i = 0; i < 16; ++i) v[i] = __uint_as_float(r[i]);
+}
+__device__ __forceinline__ void epilogue_barrier() { asm volatile("bar.sync 1, 128;" ::: "memory"); }
+
+// Shared-memory matrix descriptor of a K-major tile whose rows are 128 bytes (one swizzle atom):
+// start address, 8-row groups 1024 bytes apart, SWIZZLE_128B, descriptor version 1.
+__device__ __forceinline__ uint64_t kmajor_sw128_desc(const void *tile) {
+  const uint64_t addr = smem_addr(tile);
+  return ((addr & 0x3ffffull) >> 4) | (1ull << 16) | (static_cast<uint64_t>(1024u >> 4) << 32) | (1ull << 46) |
+         (2ull << 61);
+}
+// Instruction descriptor: fp32 accumulator, bf16 A and B, both K-major, N = n, M = 128.
+__device__ __forceinline__ uint32_t instr_desc_bf16(uint32_t n) {
+  return (1u << 4) | (1u << 7) | (1u << 10) | ((n >> 3) << 17) | ((kTileRows >> 4) << 24);
+}
+
+__global__ void __launch_bounds__(kGemmThreads, 1)
+gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x,
+               GemmKernelParams p) {
+  extern __shared__ __align__(1024) uint8_t smem_raw[];
+  // the ring must start on a 1024-byte boundary (the swizzle pattern is a function of the address)
+  uint8_t *ring = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023u) & ~uintptr_t{1023});
+  const uint32_t x_tile_bytes = p.n_pad * kSliceK * 2u;
+  const uint32_t stage_bytes = kATileBytes + x_tile_bytes;
+  GemmShared &sh = *reinterpret_cast<GemmShared *>(ring + p.stages * stage_bytes);
+  const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31u;
+  volatile uint32_t *abort = &sh.abort;
+
+  pdl_trigger();
+  if (threadIdx.x == 0) {
+    for (uint32_t s = 0; s < p.stages; ++s) {
+      mbar_init(&sh.full[s], 1);
+      mbar_init(&sh.empty[s], 1);
+    }
+    for (uint32_t a = 0; a < 2; ++a) {
+      mbar_init(&sh.acc_full[a], 1);
+      mbar_init(&sh.acc_empty[a], kEpilogueThreads);
+    }
+    sh.abort = 0;
+    mbar_init_fence();
+  }
+  if (warp == 1) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_addr(&sh.tmem_base)),
+                 "r"(kTmemColumns)
+                 : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  tcgen05_fence_before();
+  __syncthreads();
+  tcgen05_fence_after();
+  const uint32_t tmem_base = sh.tmem_base;
+
+  const Partition part = make_partition(p.rows, p.cols, gridDim.x);
+  const uint64_t run_begin = part.begin(blockIdx.x), run_end = part.end(blockIdx.x);
+
+  if (warp == 0) {
+    // ---------------- producer ----------------
+    if (lane == 0) {
+      const uint64_t w_policy = l2_evict_first_policy();  // weights are read once
+      const uint64_t x_policy = l2_evict_last_policy();   // every block re-reads the activation block
+      SegmentWalk walk{run_begin, run_end, part.slices};
+      Segment seg;
+      uint32_t issued = 0;
+      // The weights do not depend on the previous kernel: the first ring-full of weight tiles is
+      // requested before the dependency wait, the activation tiles of the same stages after it.
+      const uint64_t run_len = run_end - run_begin;
+      const uint32_t head = run_len < p.stages ? static_cast<uint32_t>(run_len) : p.stages;
+      {
+        SegmentWalk w2 = walk;
+        Segment s2;
+        uint32_t i = 0;
+        while (i < head && w2.next(&s2)) {
+          for (uint32_t c = s2.slice_begin; c < s2.slice_end && i < head; ++c, ++i) {
+            uint8_t *stage = ring + i * stage_bytes;
+            mbar_arrive_expect_tx(&sh.full[i], stage_bytes);
+            tma_load_2d(stage, &map_w, c * kSliceK, s2.tile * kTileRows, &sh.full[i], w_policy);
+          }
+        }
+      }
+      pdl_wait();
+      bool ok = true;
+      while (ok && walk.next(&seg)) {
+        for (uint32_t c = seg.slice_begin; c < seg.slice_end; ++c, ++issued) {
+          const uint32_t s = issued % p.stages;
+          uint8_t *stage = ring + s * stage_bytes;
+          if (issued >= head) {
+            if (!abortable_wait(&sh.empty[s], ((issued / p.stages) & 1u) ^ 1u, abort, p.error_word)) {
+              ok = false;
+              break;
+            }
+            mbar_arrive_expect_tx(&sh.full[s], stage_bytes);
+            tma_load_2d(stage, &map_w, c * kSliceK, seg.tile * kTileRows, &sh.full[s], w_policy);
+          }
+          tma_load_2d(stage + kATileBytes, &map_x, c * kSliceK, 0, &sh.full[s], x_policy);
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ---------------- MMA issuer ----------------
+    pdl_wait();
+    if (lane == 0) {
+      const uint32_t idesc = instr_desc_bf16(p.n_pad);
+      SegmentWalk walk{run_begin, run_end, part.slices};
+      Segment seg;
+      uint32_t consumed = 0, segment_index = 0;
+      bool ok = true;
+      while (ok && walk.next(&seg)) {
+        const uint32_t acc = segment_index & 1u;
+        // the epilogue must have drained this accumulator buffer (two segments ago)
+        if (!abortable_wait(&sh.acc_empty[acc], ((segment_index >> 1) & 1u) ^ 1u, abort, p.error_word)) break;
+        tcgen05_fence_after();
+        const uint32_t tmem_d = tmem_base + acc * kAccStride;
+        for (uint32_t c = seg.slice_begin; c < seg.slice_end; ++c, ++consumed) {
+          const uint32_t s = consumed % p.stages;
+          if (!abortable_wait(&sh.full[s], (consumed / p.stages) & 1u, abort, p.error_word)) {
+            ok = false;
+            break;
+          }
+          tcgen05_fence_after();
+          const uint8_t *stage = ring + s * stage_bytes;
+          const uint64_t desc_a = kmajor_sw128_desc(stage);
+          const uint64_t desc_b = kmajor_sw128_desc(stage + kATileBytes);
+#pragma unroll
+          for (uint32_t k = 0; k < kSliceK / kUmmaK; ++k) {
+            // 16 bf16 = 32 bytes further along the row: +2 in the 16-byte units of the descriptor
+            tcgen05_mma_f16(tmem_d, desc_a + 2ull * k, desc_b + 2ull * k, idesc, (c != seg.slice_begin || k != 0) ? 1u : 0u);
+          }
+          tcgen05_commit(&sh.empty[s]);  // the stage is free once these MMAs have read it
+        }
+        if (ok) tcgen05_commit(&sh.acc_full[acc]);
+        ++segment_index;
+      }
+    }
+  } else {
+    // ---------------- epilogue (warps 2..5) ----------------
+    pdl_wait();
+    const uint32_t quarter = warp & 3u;                 // the TMEM lanes this warp may read
+    const uint32_t row_in_tile = quarter * 32u + lane;  // accumulator row = TMEM lane
+    const uint32_t et = threadIdx.x - 64u;              // 0..127
+    SegmentWalk walk{run_begin, run_end, part.slices};
+    Segment seg;
+    uint32_t segment_index = 0;
+    const uint64_t slot_floats = static_cast<uint64_t>(p.n_pad) * kTileRows;
+    while (walk.next(&seg)) {
+      const uint32_t acc = segment_index & 1u;
+      if (!abortable_wait(&sh.acc_full[acc], (segment_index >> 1) & 1u, abort, p.error_word)) break;
+      tcgen05_fence_after();
+      const uint32_t taddr = tmem_base + acc * kAccStride + ((quarter * 32u) << 16);
+      const bool whole = seg.slice_begin == 0 && seg.slice_end == part.slices;
+      bool finish = whole;
+      uint32_t b_lo = 0, b_hi = 0;
+      if (!whole) {
+        // partial accumulator -> workspace slot; the last block of the tile to arrive finishes it
+        float *slot = p.workspace + partial_slot(part, blockIdx.x, seg.tile) * slot_floats;
+        for (uint32_t g = 0; g < p.n_pad; g += kGroup) {
+          float v[kGroup];
+          tmem_load16(taddr + g, v);
+#pragma unroll
+          for (uint32_t j = 0; j < kGroup; ++j) slot[static_cast<uint64_t>(g + j) * kTileRows + row_in_tile] = v[j];
+        }
+        b_lo = first_block_of_tile(part, seg.tile);
+        b_hi = last_block_of_tile(part, seg.tile);
+        epilogue_barrier();
+        if (et == 0) {
+          uint32_t ticket;
+          asm volatile("atom.acq_rel.gpu.global.add.u32 %0, [%1], 1;" : "=r"(ticket) : "l"(p.tickets + seg.tile) : "memory");
+          if (ticket == b_hi - b_lo) p.tickets[seg.tile] = 0;  // last one in: leave the counter ready for the next launch
+          sh.ticket = ticket;
+        }
+        epilogue_barrier();
+        finish = sh.ticket == b_hi - b_lo;
+      }
+      if (finish) {
+        const uint32_t row = seg.tile * kTileRows + row_in_tile;
+        for (uint32_t g = 0; g < p.n_pad; g += kGroup) {
+          float v[kGroup];
+          if (whole) {
+            tmem_load16(taddr + g, v);
+          } else {
+            // partials in ascending block order; this block's own comes back from its slot as well,
+            // so the sum does not depend on which block happened to arrive last
+#pragma unroll
+            for (uint32_t j = 0; j < kGroup; ++j) v[j] = 0.0f;
+            for (uint32_t b = b_lo; b <= b_hi; ++b) {
+              const float *src = p.workspace + partial_slot(part, b, seg.tile) * slot_floats;
+#pragma unroll
+              for (uint32_t j = 0; j < kGroup; ++j) {
+                const float part_v = __ldcg(src + static_cast<uint64_t>(g + j) * kTileRows + row_in_tile);
+                v[j] = b == b_lo ? part_v : v[j] + part_v;
+              }
+            }
+          }
+          if (p.epilogue == kEpilogueSwiglu) {
+            // rows interleaved (gate, up): the neighbouring lane holds the other half of the pair
+#pragma unroll
+            for (uint32_t j = 0; j < kGroup; ++j) {
+              const float other = __shfl_xor_sync(0xffffffffu, v[j], 1);
+              const uint32_t m = g + j;
+              if ((lane & 1u) == 0 && row + 1u < p.rows && m < p.tokens)
+                p.out_bf16[static_cast<uint64_t>(m) * (p.rows / 2u) + row / 2u] = f32_to_bf16_bits(silu(v[j]) * other);
+            }
+          } else if (row < p.rows) {
+#pragma unroll
+            for (uint32_t j = 0; j < kGroup; ++j) {
+              const uint32_t m = g + j;
+              if (m < p.tokens) {
+                const uint64_t at = static_cast<uint64_t>(m) * p.rows + row;
+                p.out_f32[at] = p.resid_in != nullptr ? v[j] + __ldcg(p.resid_in + at) : v[j];
+              }
+            }
+          }
+        }
+      }
+      tcgen05_fence_before();
+      mbar_arrive(&sh.acc_empty[acc]);
+      ++segment_index;
+    }
+  }
+  // ---- teardown: nothing of this block may still be in flight when its memory is released ----
+  tcgen05_fence_before();
+  __syncthreads();
+  if (sh.abort != 0u && threadIdx.x == 0) {
+    // a wait gave up: give the copies that were issued one more bounded chance to land
+    for (uint32_t s = 0; s < p.stages; ++s) {
+      mbar_wait_bounded(&sh.full[s], 0);
+      mbar_wait_bounded(&sh.full[s], 1);
+    }
+  }
+  __syncthreads();
+  if (warp == 1) {
+    tcgen05_fence_after();
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(kTmemColumns) : "memory");
+  }
+}
+
+// ---- host side ----
+PFN_cuTensorMapEncodeTiled_v12000 tensor_map_encoder() {
+  static PFN_cuTensorMapEncodeTiled_v12000 fn = nullptr;
+  static std::once_flag once;
+  std::call_once(once, [] {
+    void *entry = nullptr;
+    cudaDriverEntryPointQueryResult status;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &entry, cudaEnableDefault, &status) == cudaSuccess &&
+        status == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<PFN_cuTensorMapEncodeTiled_v12000>(entry);
+  });
+  return fn;
+}
+
+// bf16 [outer][inner] row-major, boxes of 64 x box_outer elements, 128-byte swizzle; rows beyond
+// `outer` read as zero.
+bool make_map(CUtensorMap *map, const uint16_t *base, uint64_t inner, uint64_t outer, uint32_t box_outer) {
+  PFN_cuTensorMapEncodeTiled_v12000 encode = tensor_map_encoder();
+  if (encode == nullptr) return false;
+  const cuuint64_t dims[2] = {inner, outer};
+  const cuuint64_t strides[1] = {inner * 2u};
+  const cuuint32_t box[2] = {kSliceK, box_outer};
+  const cuuint32_t elem_strides[2] = {1, 1};
+  return encode(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<uint16_t *>(base), dims, strides, box,
+                elem_strides, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+uint32_t padded_tokens(uint32_t tokens) { return (tokens + 15u) & ~15u; }
+
+uint32_t stages_for(uint32_t n_pad) {
+  const uint32_t stage_bytes = kATileBytes + n_pad * kSliceK * 2u;
+  uint32_t stages = (200u * 1024u) / stage_bytes;
+  if (stages > kMaxStages) stages = kMaxStages;
+  return stages;
+}
+
+uint32_t gemm_smem_bytes(uint32_t n_pad, uint32_t stages) {
+  return 1024u + stages * (kATileBytes + n_pad * kSliceK * 2u) + static_cast<uint32_t>(sizeof(GemmShared)) + 64u;
+}
+
+uint32_t gemm_blocks(uint32_t rows, uint32_t cols, uint32_t sm_count) {
+  const Partition p = make_partition(rows, cols, 1);
+  return p.total < sm_count ? static_cast<uint32_t>(p.total) : sm_count;
+}
+
+}  // namespace
+
+bool gemm_tc_eligible(const GemmParams &g) {
+  return g.tokens >= 1 && g.tokens <= kGemmMaxTokens && g.cols % kSliceK == 0 && g.cols != 0 && g.rows != 0 &&
+         reinterpret_cast<uintptr_t>(g.weight) % 16u == 0 && reinterpret_cast<uintptr_t>(g.x) % 16u == 0 &&
+         (g.epilogue != kEpilogueSwiglu || g.rows % 2u == 0) &&
+         (g.epilogue == kEpilogueStore || g.epilogue == kEpilogueSwiglu);
+}
+
+uint64_t gemm_tc_workspace_bytes(uint32_t tokens, uint32_t sm_count) {
+  return 2ull * sm_count * padded_tokens(tokens) * kTileRows * sizeof(float);
+}
+
+uint32_t gemm_tc_ticket_count(uint32_t rows) { return (rows + kTileRows - 1u) / kTileRows; }
+
+cudaError_t configure_gemm_tc_kernel() {
+  return cudaFuncSetAttribute(gemm_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
+}
+
+cudaError_t launch_gemm_tc(cudaStream_t stream, const GemmParams &g, uint32_t sm_count) {
+  if (!gemm_tc_eligible(g) || g.workspace == nullptr || g.tickets == nullptr) return cudaErrorInvalidValue;
+  GemmKernelParams p{};
+  p.rows = g.rows;
+  p.cols = g.cols;
+  p.tokens = g.tokens;
+  p.n_pad = padded_tokens(g.tokens);
+  p.stages = stages_for(p.n_pad);
+  p.epilogue = g.epilogue;
+  p.resid_in = g.resid_in;
+  p.out_f32 = g.out_f32;
+  p.out_bf16 = g.out_bf16;
+  p.workspace = g.workspace;
+  p.tickets = g.tickets;
+  p.error_word = g.error_word;
+  CUtensorMap map_w, map_x;
+  if (!make_map(&map_w, g.weight, g.cols, g.rows, kTileRows) || !make_map(&map_x, g.x, g.cols, g.tokens, p.n_pad))
+    return cudaErrorNotSupported;
+  const uint32_t blocks = gemm_blocks(g.rows, g.cols, sm_count);
+  return launch_with_pdl(gemm_tc_kernel, dim3(blocks), dim3(kGemmThreads), gemm_smem_bytes(p.n_pad, p.stages), stream,
+                         g.pdl != 0, map_w, map_x, p);
+}
+
+}  // namespace nb

@@ -98,6 +98,29 @@ struct ProjectionParams {
 
 constexpr uint32_t kTimelineSlots = 8;
 
+// ---- block projection on the tensor pipe (gemm_tc.cu): 2..256 tokens, weights streamed once ----
+constexpr uint32_t kGemmMaxTokens = 256;
+struct GemmParams {
+  const uint16_t *weight;  // [rows][cols] bf16 row-major, cols a multiple of 64
+  uint32_t rows, cols;
+  const uint16_t *x;       // [tokens][cols] bf16
+  uint32_t tokens;
+  uint32_t epilogue;       // kEpilogueStore: out_f32[token][row] = y (+ resid_in[token][row])
+                           // kEpilogueSwiglu: rows interleaved (gate, up): out_bf16[token][row/2]
+  const float *resid_in;   // optional [tokens][rows]
+  float *out_f32;          // [tokens][rows]
+  uint16_t *out_bf16;      // [tokens][rows/2]
+  float *workspace;        // gemm_tc_workspace_bytes(tokens, sm_count)
+  uint32_t *tickets;       // gemm_tc_ticket_count(rows) words, zero before the first launch (left zero)
+  uint32_t *error_word;
+  uint32_t pdl;
+};
+bool gemm_tc_eligible(const GemmParams &g);
+uint64_t gemm_tc_workspace_bytes(uint32_t tokens, uint32_t sm_count);
+uint32_t gemm_tc_ticket_count(uint32_t rows);
+cudaError_t configure_gemm_tc_kernel();
+cudaError_t launch_gemm_tc(cudaStream_t stream, const GemmParams &g, uint32_t sm_count);
+
 // Number of blocks launch_projection will use (= number of arg-max partials).
 uint32_t projection_blocks(const ProjectionParams &p, uint32_t sm_count);
 cudaError_t launch_projection(cudaStream_t stream, const ProjectionParams &p, uint32_t sm_count);

@@ -4,6 +4,7 @@
 #include <math.h>
 #include <string.h>
 
+#include <string>
 #include <vector>
 
 #include "../../include/nerva_synth.h"
@@ -83,11 +84,36 @@ extern "C" int nerva_b200_projection(const uint16_t *weight, const uint16_t *x, 
   if (err == cudaSuccess) err = cudaMemcpy(d_w, weight, w_elems * 2u, cudaMemcpyHostToDevice);
   if (err == cudaSuccess)
     err = cudaMemcpy(d_x, x, static_cast<uint64_t>(tokens) * cols * 2u, cudaMemcpyHostToDevice);
+  // More than one token: the block kernel on the tensor pipe streams the weights once for all of them.
+  GemmParams g{};
+  g.weight = d_w;
+  g.rows = rows;
+  g.cols = cols;
+  g.x = d_x;
+  g.tokens = tokens;
+  g.epilogue = kEpilogueStore;
+  g.out_f32 = d_y;
+  const bool block = tokens > 1 && gemm_tc_eligible(g);
+  uint32_t *d_error = nullptr;
+  if (block) {
+    float *d_ws = nullptr;
+    uint32_t *d_tickets = nullptr;
+    if (err == cudaSuccess) err = configure_gemm_tc_kernel();
+    if (err == cudaSuccess) err = buf.alloc(&d_ws, gemm_tc_workspace_bytes(tokens, sms) / sizeof(float));
+    if (err == cudaSuccess) err = buf.alloc(&d_tickets, static_cast<uint64_t>(gemm_tc_ticket_count(rows)) + 1u);
+    if (err == cudaSuccess)
+      err = cudaMemset(d_tickets, 0, (static_cast<uint64_t>(gemm_tc_ticket_count(rows)) + 1u) * sizeof(uint32_t));
+    g.workspace = d_ws;
+    g.tickets = d_tickets;
+    d_error = d_tickets + gemm_tc_ticket_count(rows);
+    g.error_word = d_error;
+  }
   double total_ms = 0.0;
   for (uint32_t it = 0; err == cudaSuccess && it < warmup + iterations; ++it) {
     if (d_flush != nullptr) err = cudaMemsetAsync(d_flush, it & 0xff, kFlushBytes, nullptr);
     if (err == cudaSuccess) err = cudaEventRecord(t.a, nullptr);
-    for (uint32_t m = 0; err == cudaSuccess && m < tokens; ++m) {
+    if (block && err == cudaSuccess) err = launch_gemm_tc(nullptr, g, sms);
+    for (uint32_t m = 0; !block && err == cudaSuccess && m < tokens; ++m) {
       ProjectionParams p{};
       p.weight = d_w;
       p.rows = rows;
@@ -106,8 +132,15 @@ extern "C" int nerva_b200_projection(const uint16_t *weight, const uint16_t *x, 
   }
   if (err == cudaSuccess)
     err = cudaMemcpy(y, d_y, static_cast<uint64_t>(tokens) * rows * 4u, cudaMemcpyDeviceToHost);
+  uint32_t device_error = 0;
+  if (err == cudaSuccess && d_error != nullptr)
+    err = cudaMemcpy(&device_error, d_error, sizeof(uint32_t), cudaMemcpyDeviceToHost);
   if (err != cudaSuccess) {
     set_last_error(cudaGetErrorString(err));
+    return -1;
+  }
+  if (device_error != 0) {
+    set_last_error("block projection kernel gave up a bounded wait (device error code " + std::to_string(device_error) + ")");
     return -1;
   }
   if (avg_ns != nullptr) *avg_ns = iterations == 0 ? 0 : static_cast<uint64_t>(total_ms * 1.0e6 / iterations);
@@ -183,11 +216,11 @@ extern "C" int nerva_cuda_projection_bench(const NervaCudaProjectionBenchRequest
   p.x_bf16 = d_x;
   p.epilogue = kEpilogueStore;
   p.out_f32 = d_y;
-  // stream launches
+  // single-token kernel: stream launches
   for (uint32_t i = 0; err == cudaSuccess && i < request->warmup_iterations; ++i)
     err = launch_projection(stream, p, sms);
   if (err == cudaSuccess) err = cudaEventRecord(t.a, stream);
-  for (uint32_t i = 0; err == cudaSuccess && i < request->iterations * tokens; ++i) {
+  for (uint32_t i = 0; err == cudaSuccess && i < request->iterations; ++i) {
     err = launch_projection(stream, p, sms);
     out->kernel_launches += 1;
   }
@@ -197,39 +230,103 @@ extern "C" int nerva_cuda_projection_bench(const NervaCudaProjectionBenchRequest
   float ms = 0.0f;
   if (err == cudaSuccess) err = cudaEventElapsedTime(&ms, t.a, t.b);
   out->custom_total_ns = static_cast<uint64_t>(ms * 1.0e6f);
-  out->custom_avg_ns = out->custom_total_ns / (static_cast<uint64_t>(request->iterations) * tokens);
-  // graph replays
-  cudaGraph_t graph = nullptr;
-  cudaGraphExec_t exec = nullptr;
-  if (err == cudaSuccess) err = cudaStreamBeginCapture(stream, cudaStreamCaptureModeThreadLocal);
-  if (err == cudaSuccess) {
-    for (uint32_t m = 0; err == cudaSuccess && m < tokens; ++m) err = launch_projection(stream, p, sms);
-    const cudaError_t end_err = cudaStreamEndCapture(stream, &graph);
-    if (err == cudaSuccess) err = end_err;
-  }
-  if (err == cudaSuccess) err = cudaGraphInstantiate(&exec, graph, 0);
-  if (err == cudaSuccess) {
-    size_t nodes = 0;
-    cudaGraphGetNodes(graph, nullptr, &nodes);
-    out->custom_graph_nodes = nodes;
-    out->graph_captures = 1;
-  }
-  for (uint32_t i = 0; err == cudaSuccess && i < request->warmup_iterations; ++i)
-    err = cudaGraphLaunch(exec, stream);
-  if (err == cudaSuccess) err = cudaEventRecord(t.a, stream);
-  for (uint32_t i = 0; err == cudaSuccess && i < request->iterations; ++i) {
-    err = cudaGraphLaunch(exec, stream);
-    out->graph_replays += 1;
-  }
-  if (err == cudaSuccess) err = cudaEventRecord(t.b, stream);
-  if (err == cudaSuccess) err = cudaEventSynchronize(t.b);
-  out->sync_calls += 1;
-  if (err == cudaSuccess) err = cudaEventElapsedTime(&ms, t.a, t.b);
-  out->custom_graph_total_ns = static_cast<uint64_t>(ms * 1.0e6f);
-  out->custom_graph_avg_ns = out->custom_graph_total_ns / request->iterations;
+  out->custom_avg_ns = out->custom_total_ns / request->iterations;
+  // single-token kernel: graph replays
+  auto time_graph = [&](auto &&enqueue, uint64_t *total_ns, uint64_t *avg_ns, uint64_t *nodes_out) {
+    cudaGraph_t graph = nullptr;
+    cudaGraphExec_t exec = nullptr;
+    if (err == cudaSuccess) err = cudaStreamBeginCapture(stream, cudaStreamCaptureModeThreadLocal);
+    if (err == cudaSuccess) {
+      err = enqueue();
+      const cudaError_t end_err = cudaStreamEndCapture(stream, &graph);
+      if (err == cudaSuccess) err = end_err;
+    }
+    if (err == cudaSuccess) err = cudaGraphInstantiate(&exec, graph, 0);
+    if (err == cudaSuccess) {
+      size_t nodes = 0;
+      cudaGraphGetNodes(graph, nullptr, &nodes);
+      *nodes_out = nodes;
+      out->graph_captures += 1;
+    }
+    for (uint32_t i = 0; err == cudaSuccess && i < request->warmup_iterations; ++i) err = cudaGraphLaunch(exec, stream);
+    if (err == cudaSuccess) err = cudaEventRecord(t.a, stream);
+    for (uint32_t i = 0; err == cudaSuccess && i < request->iterations; ++i) {
+      err = cudaGraphLaunch(exec, stream);
+      out->graph_replays += 1;
+    }
+    if (err == cudaSuccess) err = cudaEventRecord(t.b, stream);
+    if (err == cudaSuccess) err = cudaEventSynchronize(t.b);
+    out->sync_calls += 1;
+    float graph_ms = 0.0f;
+    if (err == cudaSuccess) err = cudaEventElapsedTime(&graph_ms, t.a, t.b);
+    *total_ns = static_cast<uint64_t>(graph_ms * 1.0e6f);
+    *avg_ns = *total_ns / request->iterations;
+    if (exec != nullptr) cudaGraphExecDestroy(exec);
+    if (graph != nullptr) cudaGraphDestroy(graph);
+  };
+  time_graph([&] { return launch_projection(stream, p, sms); }, &out->custom_graph_total_ns,
+             &out->custom_graph_avg_ns, &out->custom_graph_nodes);
   if (out->custom_graph_avg_ns != 0) {
-    const uint64_t bytes = tokens * (out->matrix_bytes + out->input_bytes + out->output_bytes);
+    const uint64_t bytes = out->matrix_bytes + out->input_bytes + out->output_bytes;
     out->custom_effective_bandwidth_bps = bytes * 1000000000ull / out->custom_graph_avg_ns;
+  }
+  // block_tokens > 1: the block kernel on the tensor pipe (weights streamed once for the block), in
+  // the result fields the reference uses for its block path (nerva_cuda_projection_bench.cu:791-830).
+  uint16_t *d_xb = nullptr;
+  float *d_yb = nullptr;
+  std::vector<uint16_t> h_xb;
+  uint32_t *d_block_error = nullptr;
+  if (tokens > 1) {
+    h_xb.resize(static_cast<uint64_t>(tokens) * cols);
+    for (uint64_t i = 0; i < h_xb.size(); ++i) h_xb[i] = nerva_synth_f32_to_bf16(value_at(i));
+    float *d_ws = nullptr;
+    uint32_t *d_tickets = nullptr;
+    if (err == cudaSuccess) err = buf.alloc(&d_xb, h_xb.size());
+    if (err == cudaSuccess) err = buf.alloc(&d_yb, static_cast<uint64_t>(tokens) * rows);
+    if (err == cudaSuccess) err = buf.alloc(&d_ws, gemm_tc_workspace_bytes(tokens, sms) / sizeof(float));
+    if (err == cudaSuccess) err = buf.alloc(&d_tickets, static_cast<uint64_t>(gemm_tc_ticket_count(rows)) + 1u);
+    if (err == cudaSuccess)
+      err = cudaMemset(d_tickets, 0, (static_cast<uint64_t>(gemm_tc_ticket_count(rows)) + 1u) * sizeof(uint32_t));
+    if (err == cudaSuccess) err = cudaMemcpy(d_xb, h_xb.data(), h_xb.size() * 2u, cudaMemcpyHostToDevice);
+    if (err == cudaSuccess) err = configure_gemm_tc_kernel();
+    out->device_allocations += 4;
+    GemmParams g{};
+    g.weight = d_w;
+    g.rows = rows;
+    g.cols = cols;
+    g.x = d_xb;
+    g.tokens = tokens;
+    g.epilogue = kEpilogueStore;
+    g.out_f32 = d_yb;
+    g.workspace = d_ws;
+    g.tickets = d_tickets;
+    d_block_error = d_tickets + gemm_tc_ticket_count(rows);
+    g.error_word = d_block_error;
+    if (err == cudaSuccess && !gemm_tc_eligible(g)) err = cudaErrorNotSupported;
+    for (uint32_t i = 0; err == cudaSuccess && i < request->warmup_iterations; ++i) err = launch_gemm_tc(stream, g, sms);
+    if (err == cudaSuccess) err = cudaEventRecord(t.a, stream);
+    for (uint32_t i = 0; err == cudaSuccess && i < request->iterations; ++i) {
+      err = launch_gemm_tc(stream, g, sms);
+      out->kernel_launches += 1;
+    }
+    if (err == cudaSuccess) err = cudaEventRecord(t.b, stream);
+    if (err == cudaSuccess) err = cudaEventSynchronize(t.b);
+    out->sync_calls += 1;
+    if (err == cudaSuccess) err = cudaEventElapsedTime(&ms, t.a, t.b);
+    out->block_cublaslt_total_ns = static_cast<uint64_t>(ms * 1.0e6f);
+    out->block_cublaslt_avg_ns = out->block_cublaslt_total_ns / request->iterations;
+    out->block_cublaslt_per_token_ns = out->block_cublaslt_avg_ns / tokens;
+    time_graph([&] { return launch_gemm_tc(stream, g, sms); }, &out->block_cublaslt_graph_total_ns,
+               &out->block_cublaslt_graph_avg_ns, &out->block_cublaslt_graph_nodes);
+    out->block_cublaslt_graph_per_token_ns = out->block_cublaslt_graph_avg_ns / tokens;
+    if (out->block_cublaslt_per_token_ns != 0)
+      out->block_cublaslt_speedup_x1000 = out->custom_avg_ns * 1000ull / out->block_cublaslt_per_token_ns;
+    if (out->block_cublaslt_graph_per_token_ns != 0)
+      out->block_cublaslt_graph_speedup_x1000 = out->custom_graph_avg_ns * 1000ull / out->block_cublaslt_graph_per_token_ns;
+    if (out->block_cublaslt_graph_avg_ns != 0) {
+      const uint64_t bytes = out->matrix_bytes + tokens * (out->input_bytes + out->output_bytes);
+      out->block_cublaslt_effective_bandwidth_bps = bytes * 1000000000ull / out->block_cublaslt_graph_avg_ns;
+    }
   }
   // check against an fp64 host dot product of the same bf16 inputs on a row sample
   std::vector<float> h_y(rows);
@@ -248,10 +345,30 @@ extern "C" int nerva_cuda_projection_bench(const NervaCudaProjectionBenchRequest
       if (diff > 0.25f) out->mismatch_count += 1;  // the reference's tolerance (:843-845)
     }
   }
-  if (exec != nullptr) cudaGraphExecDestroy(exec);
-  if (graph != nullptr) cudaGraphDestroy(graph);
+  if (err == cudaSuccess && tokens > 1) {
+    // every token of the block on a sparser row sample, and the kernel's own error word
+    std::vector<float> h_yb(static_cast<uint64_t>(tokens) * rows);
+    uint32_t device_error = 0;
+    err = cudaMemcpy(h_yb.data(), d_yb, h_yb.size() * 4u, cudaMemcpyDeviceToHost);
+    if (err == cudaSuccess) err = cudaMemcpy(&device_error, d_block_error, sizeof(uint32_t), cudaMemcpyDeviceToHost);
+    if (device_error != 0) out->mismatch_count += 1;
+    const uint32_t stride = rows > 512 ? rows / 512 : 1;
+    for (uint32_t m = 0; err == cudaSuccess && m < tokens; ++m) {
+      for (uint32_t r = m % stride; r < rows; r += stride) {
+        double acc = 0.0;
+        for (uint32_t k = 0; k < cols; ++k) {
+          const float w = __builtin_bit_cast(float, static_cast<uint32_t>(h_w[static_cast<uint64_t>(r) * cols + k]) << 16);
+          const float xv = __builtin_bit_cast(float, static_cast<uint32_t>(h_xb[static_cast<uint64_t>(m) * cols + k]) << 16);
+          acc += static_cast<double>(w) * xv;
+        }
+        const float diff = fabsf(h_yb[static_cast<uint64_t>(m) * rows + r] - static_cast<float>(acc));
+        if (diff > out->max_abs_diff) out->max_abs_diff = diff;
+        if (!(diff <= 0.25f)) out->mismatch_count += 1;
+      }
+    }
+  }
   if (stream != nullptr) cudaStreamDestroy(stream);
-  out->device_frees = 3;
+  out->device_frees = out->device_allocations;
   out->selected_strategy = 1;        // custom kernel
   out->selected_graph_strategy = 1;
   out->hot_path_allocations = 0;

@@ -1593,6 +1593,13 @@ extern "C" int nerva_b200_session_attach_peers(Session *s, const uint8_t *handle
   return 0;
 }
 
+extern "C" int nerva_b200_session_attach_loopback(Session *s) {
+  if (s == nullptr || s->tp_world <= 1 || s->comm_block == nullptr || s->tp_attached) return -1;
+  for (uint32_t q = 0; q < s->tp_world; ++q) s->comm_peers[q] = s->comm_block;  // destroy skips own pointers
+  s->tp_attached = true;
+  return 0;
+}
+
 // session_api_batch_fork_destroy.inc.cu:716-732: `out` (nullable) receives the
 // session's identity one last time.
 extern "C" int nerva_cuda_hf_decode_sequence_session_destroy(

@@ -133,6 +133,7 @@ def _bind(L: C.CDLL, reference_abi_only: bool) -> C.CDLL:
                                               P(vp)],
         "nerva_b200_session_comm_handle": [vp, vp, C.c_uint32],
         "nerva_b200_session_attach_peers": [vp, vp, C.c_uint32],
+        "nerva_b200_session_attach_loopback": [vp],
         "nerva_b200_projection": [vp, vp, vp, C.c_uint32, C.c_uint32, C.c_uint32, C.c_uint32, C.c_uint32,
                                   P(C.c_uint64)],
         "nerva_b200_gqa_decode_attention": [vp, vp, vp, vp, vp, C.c_uint32, C.c_uint32, C.c_uint32, C.c_uint32,

@@ -100,25 +100,50 @@ def hash_weight_blocks(blocks) -> int:
     return h
 
 
-def weight_blocks(checkpoint, staged_every: int = 2):
-    """Descriptor table in upload order: embeddings, per-layer tensors in arena
-    order, final norm, lm_head; contiguous offsets over the resident weight bytes."""
+def _upload_order(checkpoint) -> list:
+    """Tensors in upload order: embeddings, per-layer tensors in arena order, final norm, lm_head."""
     tensors = [checkpoint.embeddings]
     order = ("rms_attn", "w_q", "q_norm", "w_k", "k_norm", "w_v", "w_o", "rms_mlp", "w_gate", "w_up", "w_down",
              "q_bias", "k_bias", "v_bias", "o_bias")
     for entry in checkpoint.layers:
         tensors += [entry[k] for k in order if k in entry]
     tensors += [checkpoint.final_norm, checkpoint.lm_head]
+    return tensors
+
+
+def write_weight_file(checkpoint, path: str, header_bytes: int = 0) -> None:
+    """Writes the checkpoint's tensors back to back in upload order behind `header_bytes` of
+    padding: a stand-in for the byte ranges of a safetensors shard that file-backed descriptors
+    point at (crates/nerva-runtime/src/engine/hf_cuda_decode/file_backed/*)."""
+    with open(path, "wb") as f:
+        f.write(b"\0" * header_bytes)
+        for t in _upload_order(checkpoint):
+            f.write(np.ascontiguousarray(t).tobytes())
+
+
+def weight_blocks(checkpoint, staged_every: int = 2, source_file: str | None = None, header_bytes: int = 0):
+    """Descriptor table in upload order with contiguous offsets over the resident weight bytes.
+    Blocks come from the host tensors, or (source_file) from byte ranges of a file laid out by
+    write_weight_file, which the library reads through its pinned staging buffer
+    (hf_decode_sequence/weights.cu:797-850).  Returns (array, objects to keep alive)."""
+    tensors = _upload_order(checkpoint)
     arr = (ffi.WeightBlock * len(tensors))()
+    path_bytes = source_file.encode() if source_file is not None else None
     offset = 0
     for i, t in enumerate(tensors):
-        arr[i].host_source = _ptr(t)
+        if path_bytes is None:
+            arr[i].host_source = _ptr(t)
+        else:
+            arr[i].source_file = path_bytes
+            arr[i].source_file_len = len(path_bytes)
+            arr[i].file_offset_begin = header_bytes + offset
         arr[i].block_id = i + 1
         arr[i].block_version = 1
         arr[i].offset_bytes = offset
         arr[i].bytes = t.size * 2
         arr[i].strategy = STRATEGY_GPU_STAGED if staged_every and i % staged_every == 1 else STRATEGY_GPU_RESIDENT
         offset += t.size * 2
+    arr._path_keepalive = path_bytes
     return arr
 
 
@@ -126,9 +151,10 @@ class CudaHfDecodeSequenceSession:
     """Owns one native session handle (create ... destroy)."""
 
     def __init__(self, checkpoint, max_context_tokens: int, use_descriptors: bool = False, dtype: int = DTYPE_BF16,
-                 engine: int = 0, library=None):
+                 engine: int = 0, library=None, weight_file: str | None = None, weight_file_header: int = 0):
         """library: a handle from ffi.load_abi_library for another implementation of the same C ABI
-        (default: this package's libnerva_b200.so)."""
+        (default: this package's libnerva_b200.so).  weight_file: upload through descriptors that
+        name byte ranges of this file (see write_weight_file) instead of host pointers."""
         cfg = checkpoint.config
         self._lib = library if library is not None else ffi.lib()
         self._own_library = library is None
@@ -141,8 +167,8 @@ class CudaHfDecodeSequenceSession:
             max_context_tokens=max_context_tokens, rms_eps=cfg.rms_eps, rope_theta=cfg.rope_theta,
             embeddings=_ptr(checkpoint.embeddings), layers=C.cast(layers, C.c_void_p),
             final_norm_weight=_ptr(checkpoint.final_norm), lm_head=_ptr(checkpoint.lm_head))
-        if use_descriptors:
-            blocks = weight_blocks(checkpoint)
+        if use_descriptors or weight_file is not None:
+            blocks = weight_blocks(checkpoint, source_file=weight_file, header_bytes=weight_file_header)
             self._keep.append(blocks)
             req.planned_weight_blocks = len(blocks)
             req.planned_weight_descriptor_count = len(blocks)
@@ -293,6 +319,11 @@ class CudaHfDecodeSequenceSession:
         buf = (C.c_uint8 * len(blob)).from_buffer_copy(blob)
         if ffi.lib().nerva_b200_session_attach_peers(self._handle, buf, len(handles)) != 0:
             raise RuntimeError("attach_peers failed: " + ffi.last_error())
+
+    def attach_loopback(self) -> None:
+        """Diagnostic: a tensor-parallel rank whose peers never answer (see the C header)."""
+        if ffi.lib().nerva_b200_session_attach_loopback(self._handle) != 0:
+            raise RuntimeError("attach_loopback failed")
 
     def read_timeline(self) -> np.ndarray:
         """%globaltimer stamps of the last step, shape [5 * layers + 1, 8] (launch order QKV, attention,

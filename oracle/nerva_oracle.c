@@ -17,7 +17,12 @@
 
 static int g_threads = 0;
 
-void oracle_set_threads(int threads) { g_threads = threads; }
+void oracle_set_threads(int threads) {
+  g_threads = threads;
+  if (threads > 0) {
+    omp_set_num_threads(threads); /* parallel regions without a num_threads clause (the synthetic fill) */
+  }
+}
 
 int oracle_get_threads(void) {
 #ifdef _OPENMP
@@ -548,6 +553,30 @@ void oracle_destroy(OracleCtx *ctx) {
 void oracle_reset(OracleCtx *ctx) { ctx->len = 0; }
 
 uint32_t oracle_position(const OracleCtx *ctx) { return ctx->len; }
+
+/* Timing aid of the CPU baseline: makes `position` the next position without running the
+ * prompt, the cache rows in between filled with a fixed pattern.  A decode step at context n
+ * does the same arithmetic whatever the cached values are, so the steps that follow cost what
+ * they cost after a real n-token prefill; their tokens mean nothing. */
+int oracle_seek_for_timing(OracleCtx *ctx, uint32_t position) {
+  if (ctx == NULL || position > ctx->max_context || position < ctx->len) {
+    return -1;
+  }
+  const OracleModel *m = &ctx->model;
+  const uint64_t kv_hidden = (uint64_t)m->kv_heads * m->head_dim;
+  for (uint32_t l = 0; l < m->layers; ++l) {
+    for (uint64_t t = ctx->len; t < position; ++t) {
+      float *k = ctx->keys + ((uint64_t)l * ctx->max_context + t) * kv_hidden;
+      float *v = ctx->values + ((uint64_t)l * ctx->max_context + t) * kv_hidden;
+      for (uint64_t i = 0; i < kv_hidden; ++i) {
+        k[i] = 0.03125f * (float)((t + i) % 7) - 0.09375f;
+        v[i] = 0.0625f * (float)((t + 3 * i) % 5) - 0.125f;
+      }
+    }
+  }
+  ctx->len = position;
+  return 0;
+}
 
 const float *oracle_hidden_state(const OracleCtx *ctx) { return ctx->hidden_f32; }
 

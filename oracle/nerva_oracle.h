@@ -102,6 +102,8 @@ OracleCtx *oracle_create(const OracleModel *model, uint32_t max_context, int mod
 void oracle_destroy(OracleCtx *ctx);
 void oracle_reset(OracleCtx *ctx);
 uint32_t oracle_position(const OracleCtx *ctx);
+/* Timing aid: jump to `position` with a patterned cache (see the definition). */
+int oracle_seek_for_timing(OracleCtx *ctx, uint32_t position);
 /* Runs one token at the current position through every layer and appends its
  * K/V.  logits (vocab floats) may be NULL to skip final norm + lm_head. */
 int oracle_step(OracleCtx *ctx, uint32_t token, float *logits);

@@ -251,6 +251,15 @@ class Decoder:
     def reset(self):
         lib().oracle_reset(self._ctx)
 
+    def seek_for_timing(self, position: int) -> None:
+        """Jump to `position` with a patterned cache: later steps cost what they cost after a real
+        prefill of that length, their tokens mean nothing (bounded CPU timing samples only)."""
+        fn = lib().oracle_seek_for_timing
+        fn.restype = C.c_int
+        fn.argtypes = [C.c_void_p, C.c_uint32]
+        if fn(self._ctx, position) != 0:
+            raise ValueError("seek rejected")
+
     def step(self, token: int, want_logits: bool = True):
         logits = np.empty(self.cfg.vocab, dtype=np.float32) if want_logits else None
         rc = lib().oracle_step(self._ctx, int(token), _pf(logits) if want_logits else None)

@@ -51,8 +51,9 @@ def test_projection_full_size_row_sample(built_lib, oracle_mod, rows, cols):
     assert np.array_equal(y2, y * 2.0)
 
 
-def test_projection_multiple_tokens(built_lib, oracle_mod):
-    rows, cols, tokens = 1024, 4096, 4
+def test_projection_multiple_tokens_odd_width(built_lib, oracle_mod):
+    """A width that is not a multiple of 64 keeps the token-by-token path."""
+    rows, cols, tokens = 1024, 4096 + 8, 4
     w, x = _weights(rows, cols), _acts(cols, tokens)
     y, _ = ops.projection(w, x, rows, cols, tokens=tokens)
     for m in range(tokens):

@@ -1,0 +1,92 @@
+"""The reference's own CUDA decode library (its session and projection-bench translation units
+compiled where they lie into oracle/_ref/libnerva_ref_decode.so, cuBLAS/cuBLASLt underneath) as a
+second oracle on the GPU: both libraries export the same C ABI, so the same session mirror drives
+both, and their greedy token streams are compared on the same seeded inputs.  This pins RoPE,
+q/k-norm, attention, SwiGLU and the residual/norm plumbing to output the reference itself produced.
+Skipped when that library has not been built (it needs the reference checkout at build time)."""
+import os
+
+import numpy as np
+import pytest
+
+from nerva_b200 import ffi, ops, synth
+from nerva_b200.session import CudaHfDecodeSequenceLoop, CudaHfDecodeSequenceSession, SmokeStatus
+from tests.conftest import ROOT, assert_stream_matches_or_ties
+
+pytestmark = pytest.mark.gpu
+
+REF_LIBRARY = os.path.join(ROOT, "oracle", "_ref", "libnerva_ref_decode.so")
+# A position where the oracle's two best logits are closer than this may legitimately fall either
+# way between two fp32 summation orders (the reference sums in cuBLAS order).
+TINY_TIE_BOUND = 2e-2
+
+
+@pytest.fixture(scope="module")
+def reference_library():
+    if not os.path.exists(REF_LIBRARY):
+        pytest.skip("oracle/_ref/libnerva_ref_decode.so has not been built")
+    return ffi.load_abi_library(REF_LIBRARY)
+
+
+def _decode(checkpoint, prompt, steps, library=None, stepwise=True):
+    s = CudaHfDecodeSequenceSession(checkpoint, len(prompt) + steps, library=library)
+    assert s.status == SmokeStatus.OK, (s.error, s.create_result.cuda_error, s.create_result.failure_stage)
+    if stepwise:
+        start, loop = CudaHfDecodeSequenceLoop.start(s, prompt)
+        assert start.status == SmokeStatus.OK, (start.error, start.cuda_error)
+        out = loop.advance(steps)
+    else:
+        out = s.run(prompt, steps)
+    assert out.status == SmokeStatus.OK, (out.error, out.cuda_error)
+    s.destroy()
+    return out
+
+
+@pytest.mark.parametrize("seed", [1, 2, 3])
+def test_tiny_model_tokens_equal_the_reference_cuda_path(built_lib, reference_library, oracle_mod, tiny_checkpoint,
+                                                         seed):
+    cfg = synth.TINY_QWEN3
+    prompt = synth.prompt_ids(cfg, seed=seed)
+    ours = _decode(tiny_checkpoint, prompt, cfg.decode_tokens)
+    theirs = _decode(tiny_checkpoint, prompt, cfg.decode_tokens, library=reference_library)
+    dec = oracle_mod.Decoder(tiny_checkpoint, cfg.prompt_tokens + cfg.decode_tokens, mode=oracle_mod.MODE_CUDA)
+    tokens, logits = dec.decode_greedy(prompt, cfg.decode_tokens, want_logits=True)
+    top2 = np.sort(logits, axis=1)[:, -2:]
+    margins = (top2[:, 1] - top2[:, 0]).tolist()
+    # the reference's CUDA path against the CPU restatement of its numeric contract: pins the oracle
+    assert_stream_matches_or_ties(theirs.tokens, tokens.tolist(), margins, TINY_TIE_BOUND, "reference vs oracle")
+    # this library against the reference's CUDA path: the parity claim itself
+    assert_stream_matches_or_ties(ours.tokens, theirs.tokens, margins, TINY_TIE_BOUND, "this library vs reference")
+    assert theirs.hot_path_allocations == 0 and ours.hot_path_allocations == 0
+
+
+def test_one_shot_run_equals_the_reference_cuda_path(built_lib, reference_library, tiny_checkpoint, tiny_golden):
+    """session_run pushes the prompt through the decode step in both libraries (the reference with
+    its monolithic attention path)."""
+    cfg = synth.TINY_QWEN3
+    prompt = np.array(tiny_golden["prompt"], dtype=np.uint32)
+    ours = _decode(tiny_checkpoint, prompt, cfg.decode_tokens, stepwise=False)
+    theirs = _decode(tiny_checkpoint, prompt, cfg.decode_tokens, library=reference_library, stepwise=False)
+    margins = tiny_golden["cuda"]["top1_minus_top2"]
+    assert_stream_matches_or_ties(theirs.tokens, tiny_golden["cuda"]["tokens"], margins, TINY_TIE_BOUND,
+                                  "reference vs golden")
+    assert_stream_matches_or_ties(ours.tokens, theirs.tokens, margins, TINY_TIE_BOUND, "this library vs reference")
+
+
+@pytest.mark.parametrize("layers", [1, 2])
+def test_qwen3_8b_layer_shapes_equal_the_reference_cuda_path(built_lib, reference_library, oracle_mod, layers):
+    """Full-width Qwen3-8B layers (hidden 4096, 32/8 heads of 128, intermediate 12288, vocabulary
+    151936), cut to one and two layers: this library, the reference's CUDA path and the oracle."""
+    import dataclasses
+    cfg = dataclasses.replace(synth.QWEN3_8B, layers=layers, prompt_tokens=24, decode_tokens=12)
+    ck = synth.dense_checkpoint(cfg, fill=ops.synth_normal_bf16)
+    prompt = synth.prompt_ids(cfg)
+    ours = _decode(ck, prompt, cfg.decode_tokens)
+    theirs = _decode(ck, prompt, cfg.decode_tokens, library=reference_library)
+    dec = oracle_mod.Decoder(ck, cfg.prompt_tokens + cfg.decode_tokens, mode=oracle_mod.MODE_CUDA)
+    tokens, logits = dec.decode_greedy(prompt, cfg.decode_tokens, want_logits=True)
+    top2 = np.sort(logits, axis=1)[:, -2:]
+    margins = (top2[:, 1] - top2[:, 0]).tolist()
+    bound = 4e-2  # twice the oracle's own distance to itself at two layers of this width
+    assert_stream_matches_or_ties(theirs.tokens, tokens.tolist(), margins, bound, "reference vs oracle")
+    assert_stream_matches_or_ties(ours.tokens, theirs.tokens, margins, bound, "this library vs reference")

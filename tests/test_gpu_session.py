@@ -193,3 +193,32 @@ def test_qwen3_8b_shapes_logits(built_lib, oracle_mod, layers):
     else:
         assert np.abs(got - ref_logits[-1]).max() <= bound
 
+
+
+def test_weights_uploaded_from_byte_ranges_of_a_file(built_lib, tiny_checkpoint, tiny_golden, tmp_path):
+    """Descriptors that name (file, offset, length) ranges — the file-backed load path
+    (reference: hf_decode_sequence/weights.cu:797-850) — give the same model as host pointers."""
+    from nerva_b200.session import write_weight_file
+    path = str(tmp_path / "weights.bin")
+    write_weight_file(tiny_checkpoint, path, header_bytes=4096)
+    prompt = np.array(tiny_golden["prompt"], dtype=np.uint32)
+    s = CudaHfDecodeSequenceSession(tiny_checkpoint, 128, weight_file=path, weight_file_header=4096)
+    assert s.status == SmokeStatus.OK, s.error
+    r = s.create_result
+    assert r.planned_weight_bytes == r.resident_weight_bytes
+    assert r.descriptor_gpu_resident_h2d_bytes + r.descriptor_gpu_staged_h2d_bytes == r.planned_weight_bytes
+    out = s.run(prompt, 8)
+    assert out.status == SmokeStatus.OK and out.tokens == tiny_golden["cuda"]["tokens"][:8]
+    s.destroy()
+
+
+def test_file_backed_upload_reports_what_went_wrong(built_lib, tiny_checkpoint, tmp_path):
+    from nerva_b200.session import write_weight_file
+    missing = CudaHfDecodeSequenceSession(tiny_checkpoint, 64, weight_file=str(tmp_path / "absent.bin"))
+    assert missing.status == SmokeStatus.FAILED and "cannot open weight file" in missing.error
+    path = str(tmp_path / "short.bin")
+    write_weight_file(tiny_checkpoint, path)
+    with open(path, "r+b") as f:
+        f.truncate(1 << 20)
+    short = CudaHfDecodeSequenceSession(tiny_checkpoint, 64, weight_file=path)
+    assert short.status == SmokeStatus.FAILED and "short read" in short.error

@@ -146,3 +146,31 @@ def test_tensor_parallel_on_qwen3_8b_layer_shapes(built_lib, oracle_mod, world):
     assert worst <= bound, (worst, bound)
     if worst <= LOGIT_ATOL / 4:  # far from any tie: the token streams must agree as well
         assert ranks[0]["tokens"] == ref_tokens.tolist()
+
+
+def test_a_rank_whose_peers_never_answer_fails_the_step_within_its_wait_limit(built_lib):
+    """One rank of a two-rank model with the other rank absent: the first exchange gives up after
+    its bounded wait (about a second), every later exchange of the queued steps sees the error word
+    and does not wait again, the call returns status -1, and the device stays usable."""
+    import time
+    from nerva_b200 import ops, synth
+    from nerva_b200.session import CudaHfDecodeSequenceLoop, CudaHfDecodeSequenceSession, SmokeStatus
+    cfg = synth.TINY_QWEN3
+    full = synth.dense_checkpoint(cfg, fill=ops.synth_normal_bf16)
+    shard = synth.shard_checkpoint(full, 0, 2)
+    s = CudaHfDecodeSequenceSession(shard, 64)
+    assert s.status == SmokeStatus.OK, s.error
+    s.attach_loopback()
+    t0 = time.perf_counter()
+    start, loop = CudaHfDecodeSequenceLoop.start(s, synth.prompt_ids(cfg, count=24))
+    elapsed = time.perf_counter() - t0
+    assert start.status == SmokeStatus.FAILED
+    assert "error code 6" in start.error  # kErrPeerWaitTimeout
+    assert elapsed < 10.0, elapsed  # one wait limit, not one per exchange (24 tokens x 4 layers x 2 exchanges)
+    s.destroy()
+    # the context is intact: an ordinary session decodes afterwards
+    t = CudaHfDecodeSequenceSession(full, 64)
+    assert t.status == SmokeStatus.OK, t.error
+    out = t.run(synth.prompt_ids(cfg, count=8), 4)
+    assert out.status == SmokeStatus.OK and len(out.tokens) == 4
+    t.destroy()

@@ -1,4 +1,4 @@
-"""The allocation-free attention entry point against the allocating one, through the C ABI.
+"""The allocation-free attention entry point against the allocating one and the CPU oracle, through the C ABI.
 
 Collected last on purpose (the file name sorts after the other test files): the
 entry point keeps its split partials in one device array that every call shares,
@@ -45,13 +45,48 @@ def _static_scratch(q, k, v, table, batch, context, heads, kv_heads, head_dim):
 CASES = [(2, 2048, 32, 8, 128), (1, 769, 8, 2, 64)]
 
 
-def test_static_scratch_attention_matches_allocating_entry_point(built_lib):
+def _oracle(oracle_mod, q, k, v, table, batch, context, heads, kv_heads, head_dim):
+    pages = (context + 15) // 16
+    seq = pages * 16 * kv_heads * head_dim
+    rows = [oracle_mod.attention_paged(q[b * heads * head_dim:(b + 1) * heads * head_dim], k[b * seq:(b + 1) * seq],
+                                       v[b * seq:(b + 1) * seq], table[b], context, heads, kv_heads, head_dim)
+            for b in range(batch)]
+    return np.stack(rows)
+
+
+def test_static_scratch_attention_matches_allocating_entry_point(built_lib, oracle_mod):
     for seed, (batch, context, heads, kv_heads, head_dim) in enumerate(CASES):
         q, k, v, table = _inputs(batch, context, heads, kv_heads, head_dim, seed)
         got = _static_scratch(q, k, v, table, batch, context, heads, kv_heads, head_dim)
         want, _ = ops.gqa_decode_attention(q, k, v, table, batch, context, heads, kv_heads, head_dim)
         assert np.isfinite(got).all()
         assert np.abs(got - want).max() <= ATTN_ATOL
+        assert np.abs(got - _oracle(oracle_mod, q, k, v, table, batch, context, heads, kv_heads, head_dim)).max() \
+            <= ATTN_ATOL
+
+
+def test_static_scratch_attention_lowers_the_split_count_to_fit(built_lib, oracle_mod):
+    """32 query heads on one KV head at a long context: the split count the kernels would pick
+    (256) needs more than the fixed array holds (252 splits of 32 x 130 floats), so the entry
+    point lowers it; the result must not change."""
+    batch, context, heads, kv_heads, head_dim = 1, 33000, 32, 1, 128
+    q, k, v, table = _inputs(batch, context, heads, kv_heads, head_dim, 7)
+    got = _static_scratch(q, k, v, table, batch, context, heads, kv_heads, head_dim)
+    want = _oracle(oracle_mod, q, k, v, table, batch, context, heads, kv_heads, head_dim)
+    assert np.isfinite(got).all()
+    assert np.abs(got - want).max() <= ATTN_ATOL
+
+
+def test_static_scratch_attention_rejects_misaligned_views(built_lib):
+    import torch
+    # a K view that starts 2 bytes into a 16-byte piece: refused on the host, nothing is launched
+    buf = torch.zeros(1 << 16, dtype=torch.int16, device="cuda:0")
+    q = torch.zeros(8 * 64, dtype=torch.float32, device="cuda:0")
+    table = torch.zeros(4, dtype=torch.int32, device="cuda:0")
+    out = torch.zeros(8 * 64, dtype=torch.float32, device="cuda:0")
+    with pytest.raises(RuntimeError, match="misaligned buffer"):
+        ops.gqa_decode_attention_static_scratch(q.data_ptr(), buf.data_ptr() + 2, buf.data_ptr(), table.data_ptr(),
+                                                out.data_ptr(), 1, 48, 8, 2, 64)
 
 
 def test_static_scratch_attention_repeats_bit_exactly(built_lib):
