@@ -498,6 +498,59 @@ def run_ours(args, cfg, rank: int, world: int) -> dict:
     return result
 
 
+def run_batch_workload(args, cfg) -> None:
+    """32 forks of one session (shared weights, identical histories) advanced as packed blocks through
+    nerva_cuda_hf_decode_sequence_batch_advance_one, against the same forks advanced one after the
+    other with session_advance: the reference's shared-fork batch comparison
+    (docs/source/perf/qwen3_8b_shared_fork_batch_compare_32req_target32.json)."""
+    from nerva_b200 import build, ops, synth
+    from nerva_b200.session import CudaHfDecodeSequenceLoop, CudaHfDecodeSequenceSession, SmokeStatus
+    build.build()
+    ck = synth.dense_checkpoint(cfg, fill=ops.synth_normal_bf16)
+    prompt = synth.prompt_ids(cfg)
+    steps, forks = args.steps, 32
+    session = CudaHfDecodeSequenceSession(ck, cfg.prompt_tokens + 2 * steps + 16, use_descriptors=True)
+    if session.status != SmokeStatus.OK:
+        raise RuntimeError(f"session create failed: {session.error}")
+    start, loop = CudaHfDecodeSequenceLoop.start(session, prompt)
+    if start.status != SmokeStatus.OK:
+        raise RuntimeError(f"session start failed: {start.error}")
+    loop.advance(4)
+    block = [session] + [session.fork_shared_weights() for _ in range(forks - 1)]
+    lone = [session.fork_shared_weights() for _ in range(forks)]
+    for _ in range(2):   # warm-up block steps
+        CudaHfDecodeSequenceSession.batch_advance_one(block, forks, forks)
+    for s in lone:
+        CudaHfDecodeSequenceLoop(s).advance(2)
+    t0 = time.perf_counter()
+    block_tokens = []
+    for _ in range(steps):
+        out = CudaHfDecodeSequenceSession.batch_advance_one(block, forks, forks)
+        if out.status != SmokeStatus.OK or out.block_tokens != forks:
+            raise RuntimeError(f"block step failed: reason {out.reason} {out.error}")
+        block_tokens.append(out.tokens)
+    block_s = time.perf_counter() - t0
+    t0 = time.perf_counter()
+    lone_tokens = [CudaHfDecodeSequenceLoop(s).advance(steps).tokens for s in lone]
+    lone_s = time.perf_counter() - t0
+    same_within_block = all(len(set(row)) == 1 for row in block_tokens)
+    stream = [row[0] for row in block_tokens]
+    match = sum(1 for a, b in zip(stream, lone_tokens[0]) if a == b)
+    first_diff = next((i for i, (a, b) in enumerate(zip(stream, lone_tokens[0])) if a != b), None)
+    peaks = measured_peaks()
+    nbytes = cfg.projection_bytes_per_token()
+    print(json.dumps({
+        "workload": "shared-fork batch: 32 sessions, one token each per block step", "config": config_block(cfg, 1),
+        "block_tokens": forks, "steps": steps,
+        "block_tok_s": forks * steps / block_s, "sequential_tok_s": forks * steps / lone_s,
+        "speedup": lone_s / block_s, "ms_per_block_step": 1e3 * block_s / steps,
+        "weight_stream_frac_of_measured_hbm": nbytes / (block_s / steps) / 1e9 / peaks["hbm_gbs"],
+        "tokens_identical_within_block": same_within_block,
+        "token_match_with_sequential": {"compared": steps, "identical_prefix": steps if first_diff is None else first_diff},
+        "timing": "host wall clock around the C-ABI calls, token slots copied back every call",
+    }), flush=True)
+
+
 def run_operator_workloads(kind: str) -> None:
     """Per-operator sweeps (isolated projection shapes, long-context attention) through the per-op C ABI (host buffers in,
     device time per launch out, L2 flushed between launches).  One JSON line per case."""
@@ -511,12 +564,20 @@ def run_operator_workloads(kind: str) -> None:
             w = ops.synth_normal_bf16(0, 77, rows * cols, 0.02)
             for m in (1, 4, 16, 64):
                 x = ops.synth_normal_bf16(0, synth.T_ACTIVATION, m * cols, 1.0)
-                _, ns = ops.projection(w, x, rows, cols, tokens=m, warmup=3, iterations=10)
+                _, alone_ns = ops.projection(w, x, rows, cols, tokens=m, warmup=3, iterations=10)
+                # sustained: copies of the matrix that together exceed the 126 MB L2, launched back to back
+                copies = max(2, -(-320_000_000 // (2 * rows * cols)))
+                y, ns = ops.projection_sustained(w, x, rows, cols, tokens=m, copies=copies, warmup=2 * copies,
+                                                 iterations=8 * copies)
                 nbytes = 2 * rows * cols + 2 * m * cols + 4 * m * rows
                 gbs = nbytes / ns
                 print(json.dumps({"workload": "decode-linear", "shape": name, "N": rows, "K": cols, "M": m,
                                   "us": ns / 1e3, "algorithmic_bytes": nbytes, "GB/s": gbs,
                                   "frac_of_measured_hbm": gbs / peak["hbm_gbs"],
+                                  "timing": f"{8 * copies} launches back to back over {copies} copies of the matrix "
+                                            f"(larger than L2 together), programmatic dependent launch",
+                                  "single_launch_us": alone_ns / 1e3,
+                                  "single_launch_frac": nbytes / alone_ns / peak["hbm_gbs"],
                                   "note": "block kernel on the tensor pipe (tcgen05), weights streamed once for the block"
                                   if m > 1 else "weight-streaming GEMV"}), flush=True)
         return
@@ -572,7 +633,7 @@ def main() -> None:
     ap.add_argument("--layers", type=int, default=0,
                     help="cut the model to this many layers (profiler captures only; not a bench line)")
     ap.add_argument("--prompt-tokens", type=int, default=0, help="override the prompt length")
-    ap.add_argument("--workload", default="decode", choices=["decode", "linear", "attention", "reference-gpu"],
+    ap.add_argument("--workload", default="decode", choices=["decode", "linear", "attention", "reference-gpu", "batch"],
                     help="decode: the bench line; linear / attention: per-operator sweeps of the isolated "
                          "projection shapes and of long-context attention (one JSON line per case)")
     ap.add_argument("--timeline", action="store_true",
@@ -589,6 +650,10 @@ def main() -> None:
     if args.workload == "reference-gpu":
         if rank == 0:
             run_reference_gpu(args, cfg)
+        return
+    if args.workload == "batch":
+        if rank == 0:
+            run_batch_workload(args, cfg)
         return
     if args.impl == "reference":
         if rank == 0:

@@ -896,6 +896,13 @@ int nerva_b200_session_read_timeline(NervaCudaHfDecodeSequenceSession *session, 
 int nerva_b200_projection(const uint16_t *weight, const uint16_t *x, float *y, uint32_t rows,
                           uint32_t cols, uint32_t tokens, uint32_t warmup, uint32_t iterations,
                           uint64_t *avg_ns);
+/* Sustained form of the same measurement (no counterpart in the reference): `copies` device copies
+ * of the matrix, together larger than the L2, are projected back to back, each launch allowed to
+ * start while its predecessor drains, as the projections of consecutive layers follow each other
+ * inside a decode step.  avg_ns: time per launch over `iterations` launches after `warmup`. */
+int nerva_b200_projection_sustained(const uint16_t *weight, const uint16_t *x, float *y, uint32_t rows,
+                                    uint32_t cols, uint32_t tokens, uint32_t copies, uint32_t warmup,
+                                    uint32_t iterations, uint64_t *avg_ns);
 
 /* Isolated GQA paged decode attention for `batch` sequences of `context`
  * tokens each: q f32 [batch][heads*head_dim]; K/V pages bf16

@@ -54,7 +54,8 @@ struct FusedLayout {
   }
 };
 
-template <uint32_t PER>
+// ROWS: block-step form (one set of blocks per activation row, fields taken from p.rows[blockIdx.y]).
+template <uint32_t PER, bool ROWS>
 __global__ void fused_decode_attention_kernel(FusedAttentionParams p) {
   constexpr uint32_t D = PER * 32u;
   using Layout = FusedLayout<D>;
@@ -68,20 +69,40 @@ __global__ void fused_decode_attention_kernel(FusedAttentionParams p) {
 
   pdl_trigger();
   stamp(p.stamps, kStampEntry);
-  // The cursor only changes in the last kernel of a step, which has completed.
-  const uint32_t position = *p.cursor;
+  uint32_t position;
+  if (ROWS) {
+    const FusedAttentionRow r = p.rows[blockIdx.y];
+    position = r.position;
+    p.max_context = r.max_context;
+    p.page_count = r.page_count;
+    p.qkv = r.qkv;
+    p.key_pages = r.key_pages + p.layer * r.kv_layer_elems;
+    p.value_pages = r.value_pages + p.layer * r.kv_layer_elems;
+    p.page_table = r.page_table;
+    p.partial_acc = r.partial_acc;
+    p.partial_m = r.partial_m;
+    p.partial_l = r.partial_l;
+    p.tickets = r.tickets;
+    p.out_bf16 = r.out_bf16;
+    p.error_word = r.error_word;
+  } else {
+    // The cursor only changes in the last kernel of a step, which has completed.
+    position = *p.cursor;
+  }
   if (position >= p.max_context) return;
+  const bool cached_only = ROWS && p.cached_only != 0;
   const uint32_t lane = threadIdx.x & 31u, warp = threadIdx.x >> 5;
   const uint32_t S = p.splits;
   const uint32_t kvh = blockIdx.x / S, s = blockIdx.x - kvh * S;
   const uint32_t kv_hidden = p.kv_heads * D, attention_hidden = p.heads * D;
-  const uint32_t hist = position;  // cached tokens 0 .. position-1; the new one comes from qkv
+  // cached tokens 0 .. position-1, the new one comes from qkv; cached_only: 0 .. position, all cached
+  const uint32_t hist = cached_only ? position + 1u : position;
   const uint32_t chunks_total = (hist + kChunkTokens - 1u) / kChunkTokens;
   const uint32_t chunks_per_split = (chunks_total + S - 1u) / S;
   const uint32_t chunk_begin = s * chunks_per_split;
   uint32_t chunk_end = chunk_begin + chunks_per_split;
   if (chunk_end > chunks_total) chunk_end = chunks_total;
-  const bool owns_current = s + 1u == S;
+  const bool owns_current = !cached_only && s + 1u == S;
 
   // Copies the cached rows of one 64-token chunk into a stage (one commit group).
   // A warp copies whole tokens: half of its lanes (or a quarter, for D = 64) take
@@ -127,6 +148,9 @@ __global__ void fused_decode_attention_kernel(FusedAttentionParams p) {
   };
   // Everything that depends only on the position happens before the wait; the
   // page-table and norm-weight loads are in flight while the rotation is computed.
+  // cached_only: the newest cached rows come from the kernel just before this one, so nothing may
+  // be fetched ahead of the dependency wait.
+  if (cached_only) pdl_wait();
   const uint32_t pages0 = chunk_begin < chunk_end ? chunk_pages(chunk_begin) : 0u;
   const uint32_t pages1 = chunk_begin + 1u < chunk_end ? chunk_pages(chunk_begin + 1u) : 0u;
   // Warps 0 .. group-1 and group .. 2*group-1 serve the same query heads: the first set takes the
@@ -416,12 +440,15 @@ uint32_t fused_attention_splits(uint32_t target_context) {
 }
 
 cudaError_t configure_fused_attention_kernel() {
-  cudaError_t err = cudaFuncSetAttribute(fused_decode_attention_kernel<4>,
-                                         cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                         static_cast<int>(FusedLayout<128>::bytes(kFusedMaxGroup)));
-  if (err == cudaSuccess)
-    err = cudaFuncSetAttribute(fused_decode_attention_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                               static_cast<int>(FusedLayout<64>::bytes(kFusedMaxGroup)));
+  cudaError_t err = cudaSuccess;
+  auto set = [&](void (*kernel)(FusedAttentionParams), uint32_t bytes) {
+    if (err == cudaSuccess)
+      err = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(bytes));
+  };
+  set(fused_decode_attention_kernel<4, false>, FusedLayout<128>::bytes(kFusedMaxGroup));
+  set(fused_decode_attention_kernel<4, true>, FusedLayout<128>::bytes(kFusedMaxGroup));
+  set(fused_decode_attention_kernel<2, false>, FusedLayout<64>::bytes(kFusedMaxGroup));
+  set(fused_decode_attention_kernel<2, true>, FusedLayout<64>::bytes(kFusedMaxGroup));
   return err;
 }
 
@@ -432,11 +459,20 @@ cudaError_t launch_fused_attention(cudaStream_t stream, const FusedAttentionPara
   const uint32_t group = p.heads / p.kv_heads;
   const uint32_t blocks = p.kv_heads * p.splits;
   const uint32_t threads = (2u * group + 1u) * 32u;
+  if (p.rows != nullptr) {
+    if (p.row_count == 0 || p.row_count > 65535u) return cudaErrorInvalidValue;
+    const dim3 grid(blocks, p.row_count);
+    if (p.head_dim == 128)
+      return launch_with_pdl(fused_decode_attention_kernel<4, true>, grid, dim3(threads),
+                             FusedLayout<128>::bytes(group), stream, p.pdl != 0, p);
+    return launch_with_pdl(fused_decode_attention_kernel<2, true>, grid, dim3(threads), FusedLayout<64>::bytes(group),
+                           stream, p.pdl != 0, p);
+  }
   if (p.head_dim == 128) {
-    return launch_with_pdl(fused_decode_attention_kernel<4>, dim3(blocks), dim3(threads),
+    return launch_with_pdl(fused_decode_attention_kernel<4, false>, dim3(blocks), dim3(threads),
                            FusedLayout<128>::bytes(group), stream, p.pdl != 0, p);
   }
-  return launch_with_pdl(fused_decode_attention_kernel<2>, dim3(blocks), dim3(threads),
+  return launch_with_pdl(fused_decode_attention_kernel<2, false>, dim3(blocks), dim3(threads),
                          FusedLayout<64>::bytes(group), stream, p.pdl != 0, p);
 }
 

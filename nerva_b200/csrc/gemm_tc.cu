@@ -463,6 +463,8 @@ uint32_t gemm_blocks(uint32_t rows, uint32_t cols, uint32_t sm_count) {
 
 }  // namespace
 
+bool tensor_map_available() { return tensor_map_encoder() != nullptr; }
+
 bool gemm_tc_eligible(const GemmParams &g) {
   return g.tokens >= 1 && g.tokens <= kGemmMaxTokens && g.cols % kSliceK == 0 && g.cols != 0 && g.rows != 0 &&
          reinterpret_cast<uintptr_t>(g.weight) % 16u == 0 && reinterpret_cast<uintptr_t>(g.x) % 16u == 0 &&

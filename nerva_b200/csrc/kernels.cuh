@@ -118,6 +118,7 @@ struct GemmParams {
 bool gemm_tc_eligible(const GemmParams &g);
 uint64_t gemm_tc_workspace_bytes(uint32_t tokens, uint32_t sm_count);
 uint32_t gemm_tc_ticket_count(uint32_t rows);
+bool tensor_map_available();  // the driver exposes the tensor-map encoder the block kernel needs
 cudaError_t configure_gemm_tc_kernel();
 cudaError_t launch_gemm_tc(cudaStream_t stream, const GemmParams &g, uint32_t sm_count);
 
@@ -176,6 +177,21 @@ uint32_t attention_default_splits(uint32_t context, uint32_t batch, uint32_t kv_
                                   uint32_t sm_count);
 
 // ---- fused decode attention of the session (one launch per layer) ----
+// One activation row of a block step (several tokens through the layer together): the
+// per-row replacements of the single-session fields of FusedAttentionParams.
+struct FusedAttentionRow {
+  uint32_t position;       // position of this row's token
+  uint32_t max_context, page_count, reserved;
+  const float *qkv;        // this row's projection output
+  uint16_t *key_pages, *value_pages;  // layer 0 of the row's session; the kernel adds layer * kv_layer_elems
+  uint64_t kv_layer_elems;
+  const uint32_t *page_table;
+  float *partial_acc, *partial_m, *partial_l;
+  uint32_t *tickets;
+  uint16_t *out_bf16;
+  uint32_t *error_word;
+};
+
 struct FusedAttentionParams {
   const uint32_t *cursor;  // position of the token being decoded
   uint32_t max_context;
@@ -193,6 +209,12 @@ struct FusedAttentionParams {
   uint32_t *error_word;
   uint32_t pdl;
   unsigned long long *stamps;  // optional timeline stamps
+  // Block step: rows != nullptr launches one set of blocks per row (grid.y = row_count); the row
+  // supplies position, qkv, pages, partials, tickets and output.  cached_only: the row's own K/V
+  // are already in the cache (published by an earlier kernel of the chunk), so the kernel attends
+  // over positions 0..position and appends nothing.
+  const FusedAttentionRow *rows;
+  uint32_t row_count, layer, cached_only;
 };
 bool fused_attention_supported(uint32_t heads, uint32_t kv_heads, uint32_t head_dim);
 uint32_t fused_attention_splits(uint32_t target_context);

@@ -147,6 +147,98 @@ extern "C" int nerva_b200_projection(const uint16_t *weight, const uint16_t *x, 
   return 0;
 }
 
+// Sustained form of the same measurement: `copies` device copies of the matrix (together larger
+// than the L2, so no launch finds its weights cached) are projected back to back, each launch
+// allowed to start while its predecessor drains (programmatic dependent launch), the way the
+// projections of consecutive layers follow each other inside a decode step.  avg_ns is the time
+// per launch over `iterations` launches after `warmup`; y receives the last launch's output.
+extern "C" int nerva_b200_projection_sustained(const uint16_t *weight, const uint16_t *x, float *y, uint32_t rows,
+                                               uint32_t cols, uint32_t tokens, uint32_t copies, uint32_t warmup,
+                                               uint32_t iterations, uint64_t *avg_ns) {
+  set_last_error("");
+  if (weight == nullptr || x == nullptr || y == nullptr || rows == 0 || cols == 0 || tokens == 0 || copies == 0 ||
+      iterations == 0)
+    return -1;
+  uint32_t sms = 0;
+  cudaError_t err = device_sm_count(&sms, nullptr, nullptr, nullptr);
+  if (err == cudaSuccess) err = configure_projection_kernels();
+  if (err == cudaSuccess) err = configure_gemm_tc_kernel();
+  DeviceBuffers buf;
+  Timing t;
+  const uint64_t w_elems = static_cast<uint64_t>(rows) * cols;
+  std::vector<uint16_t *> d_w(copies, nullptr);
+  uint16_t *d_x = nullptr;
+  float *d_y = nullptr, *d_ws = nullptr;
+  uint32_t *d_tickets = nullptr;
+  for (uint32_t c = 0; err == cudaSuccess && c < copies; ++c) {
+    err = buf.alloc(&d_w[c], w_elems);
+    if (err == cudaSuccess) err = cudaMemcpy(d_w[c], weight, w_elems * 2u, cudaMemcpyHostToDevice);
+  }
+  if (err == cudaSuccess) err = buf.alloc(&d_x, static_cast<uint64_t>(tokens) * cols);
+  if (err == cudaSuccess) err = buf.alloc(&d_y, static_cast<uint64_t>(tokens) * rows);
+  if (err == cudaSuccess) err = buf.alloc(&d_ws, gemm_tc_workspace_bytes(tokens, sms) / sizeof(float));
+  if (err == cudaSuccess) err = buf.alloc(&d_tickets, static_cast<uint64_t>(gemm_tc_ticket_count(rows)) + 1u);
+  if (err == cudaSuccess)
+    err = cudaMemset(d_tickets, 0, (static_cast<uint64_t>(gemm_tc_ticket_count(rows)) + 1u) * sizeof(uint32_t));
+  if (err == cudaSuccess) err = cudaMemcpy(d_x, x, static_cast<uint64_t>(tokens) * cols * 2u, cudaMemcpyHostToDevice);
+  if (err == cudaSuccess) err = t.init();
+  cudaStream_t stream = nullptr;
+  if (err == cudaSuccess) err = cudaStreamCreateWithFlags(&stream, cudaStreamNonBlocking);
+  uint32_t *d_error = d_tickets != nullptr ? d_tickets + gemm_tc_ticket_count(rows) : nullptr;
+  GemmParams g{};
+  g.rows = rows;
+  g.cols = cols;
+  g.x = d_x;
+  g.tokens = tokens;
+  g.epilogue = kEpilogueStore;
+  g.out_f32 = d_y;
+  g.workspace = d_ws;
+  g.tickets = d_tickets;
+  g.error_word = d_error;
+  g.pdl = 1;
+  g.weight = d_w.empty() ? nullptr : d_w[0];
+  const bool block = tokens > 1 && err == cudaSuccess && gemm_tc_eligible(g);
+  if (tokens > 1 && err == cudaSuccess && !block) err = cudaErrorNotSupported;
+  auto launch = [&](uint32_t i) {
+    if (block) {
+      g.weight = d_w[i % copies];
+      return launch_gemm_tc(stream, g, sms);
+    }
+    ProjectionParams p{};
+    p.weight = d_w[i % copies];
+    p.rows = rows;
+    p.cols = cols;
+    p.prologue = kProloguePlain;
+    p.x_bf16 = d_x;
+    p.epilogue = kEpilogueStore;
+    p.out_f32 = d_y;
+    p.error_word = d_error;
+    p.pdl = 1;
+    return launch_projection(stream, p, sms);
+  };
+  for (uint32_t i = 0; err == cudaSuccess && i < warmup; ++i) err = launch(i);
+  if (err == cudaSuccess) err = cudaEventRecord(t.a, stream);
+  for (uint32_t i = 0; err == cudaSuccess && i < iterations; ++i) err = launch(warmup + i);
+  if (err == cudaSuccess) err = cudaEventRecord(t.b, stream);
+  if (err == cudaSuccess) err = cudaEventSynchronize(t.b);
+  float ms = 0.0f;
+  if (err == cudaSuccess) err = cudaEventElapsedTime(&ms, t.a, t.b);
+  if (err == cudaSuccess) err = cudaMemcpy(y, d_y, static_cast<uint64_t>(tokens) * rows * 4u, cudaMemcpyDeviceToHost);
+  uint32_t device_error = 0;
+  if (err == cudaSuccess) err = cudaMemcpy(&device_error, d_error, sizeof(uint32_t), cudaMemcpyDeviceToHost);
+  if (stream != nullptr) cudaStreamDestroy(stream);
+  if (err != cudaSuccess) {
+    set_last_error(cudaGetErrorString(err));
+    return -1;
+  }
+  if (device_error != 0) {
+    set_last_error("projection kernel gave up a bounded wait (device error code " + std::to_string(device_error) + ")");
+    return -1;
+  }
+  if (avg_ns != nullptr) *avg_ns = static_cast<uint64_t>(static_cast<double>(ms) * 1.0e6 / iterations);
+  return 0;
+}
+
 // Reference: native/cuda/nerva_cuda_projection_bench.cu.  Same deterministic
 // inputs (((17 i + 13) mod 127) - 63) / 128 for the matrix and the vector
 // (:38-41,84-101).  `custom_*` time this library's projection kernel as single

@@ -478,8 +478,10 @@ static void profile_mark(Session *s, StepProfile *prof, uint32_t bucket) {
   prof->used += 1;
 }
 
+// head_only: the residual stream after the last layer is already in s->h_b (the chunked prefill
+// left it there): only the final norm, lm_head and the sampler are enqueued.
 cudaError_t enqueue_step(Session *s, uint32_t splits, uint32_t sample, uint64_t *launches,
-                         StepProfile *prof = nullptr) {
+                         StepProfile *prof = nullptr, bool head_only = false) {
   const ModelDims &d = s->dims;
   const StepState st = step_state(s);
   const uint64_t ah = d.attention_hidden(), kvh = d.kv_hidden();
@@ -523,10 +525,13 @@ cudaError_t enqueue_step(Session *s, uint32_t splits, uint32_t sample, uint64_t 
   bool fused_resid = !tp && !s->has_moe;
   for (const LayerLayout &L : s->layout.layers) fused_resid = fused_resid && arena_at(s, L.o_bias) == nullptr;
   profile_mark(s, prof, kBucketEmbed);
-  cudaError_t err = launch_embed(s->stream, st, arena_at(s, s->layout.embeddings), d.hidden, s->h_b);
-  n += 1;
+  cudaError_t err = cudaSuccess;
+  if (!head_only) {
+    err = launch_embed(s->stream, st, arena_at(s, s->layout.embeddings), d.hidden, s->h_b);
+    n += 1;
+  }
   profile_mark(s, prof, kBucketEmbed);
-  for (uint32_t l = 0; err == cudaSuccess && l < d.layers; ++l) {
+  for (uint32_t l = 0; !head_only && err == cudaSuccess && l < d.layers; ++l) {
     const LayerLayout &L = s->layout.layers[l];
     ProjectionParams p{};
     p.error_word = s->device_error;
@@ -1497,6 +1502,10 @@ static int create_session(const NervaCudaHfDecodeSequenceSessionCreateRequest *r
     err = allocate_comm(s);
     if (err != cudaSuccess) return create_fail(s, out, err, kStageDeviceScratchAlloc);
   }
+  if (block_step_supported(s)) {
+    err = allocate_block_workspace(s);
+    if (err != cudaSuccess) return create_fail(s, out, err, kStageDeviceScratchAlloc);
+  }
 
   UploadCounters counters;
   err = declared_plan ? upload_from_descriptors(s, request, &counters)
@@ -1528,7 +1537,8 @@ static int create_session(const NervaCudaHfDecodeSequenceSessionCreateRequest *r
   out->device_arena_bytes = device_footprint(s);
   out->pinned_host_bytes = s->slots_bytes;
   out->head_threads = 128;
-  out->prefill_chunk_tokens = 1;  // the prompt is pushed through the decode step token by token
+  // chunk of the block prefill; 1 when the prompt is pushed through the decode step token by token
+  out->prefill_chunk_tokens = s->weights->block_ws.block != nullptr ? s->weights->block_ws.max_rows : 1;
   out->hot_path_allocations = 0;
   out->status = 0;
   *session_out = s;
@@ -1680,9 +1690,28 @@ extern "C" int nerva_cuda_hf_decode_sequence_session_start(
   s->prompt_count = request->prompt_token_count;
   s->started = false;
   cudaError_t err = reset_request_state(s, request->prompt_tokens, request->prompt_token_count, out);
+  const uint32_t splits = splits_for(s, s->prompt_count);
+  // NERVA_B200_PREFILL=decode keeps the token-by-token prefill on models that have the block path
+  // (comparison runs); read per call.
+  const char *prefill_env = getenv("NERVA_B200_PREFILL");
+  const bool chunked = s->weights->block_ws.block != nullptr && s->engine == 0 && s->prompt_count > 1 &&
+                       !(prefill_env != nullptr && prefill_env[0] == 'd');
+  if (chunked) {
+    // Chunked prefill: up to block_ws.max_rows prompt positions through every layer at a time
+    // (block projections on the tensor pipe, paged K/V published per chunk), then the head for the
+    // last position (session_decode_prefill.inc.cu:1879-2245 is the reference's counterpart).
+    if (err == cudaSuccess) err = cudaEventRecord(s->ev_start, s->stream);
+    uint64_t launches = 0;
+    if (err == cudaSuccess) err = enqueue_chunked_prefill(s, s->prompt_count, s->sample_kind, &launches);
+    const uint32_t last = s->prompt_count - 1u;
+    if (err == cudaSuccess)  // the head samples at the cursor: the last prompt position
+      err = cudaMemcpyAsync(s->device_cursor, &last, sizeof(uint32_t), cudaMemcpyHostToDevice, s->stream);
+    uint64_t head_launches = 0;
+    if (err == cudaSuccess) err = enqueue_step(s, splits, s->sample_kind, &head_launches, nullptr, true);
+    out->kernel_launches += launches + head_launches;
+  } else {
   // Prefill by decode: prompt_count - 1 steps without sampling, then one with
   // (the reference's serial prefill, session_decode_prefill.inc.cu:2245-2297).
-  const uint32_t splits = splits_for(s, s->prompt_count);
   GraphEntry *quiet = nullptr, *sampled = nullptr;
   if (err == cudaSuccess && s->prompt_count > 1) err = ensure_graph(s, splits, 0, &quiet, out);
   if (err == cudaSuccess) err = ensure_graph(s, splits, s->sample_kind, &sampled, out);
@@ -1699,6 +1728,7 @@ extern "C" int nerva_cuda_hf_decode_sequence_session_start(
     out->graph_replays += 1;
     out->graph_launches += 1;
     out->kernel_launches += sampled->nodes;
+  }
   }
   if (err == cudaSuccess) err = cudaEventRecord(s->ev_stop, s->stream);
   if (err == cudaSuccess)
@@ -1845,12 +1875,29 @@ extern "C" int nerva_cuda_hf_decode_sequence_session_run(
   s->prompt_count = request->prompt_token_count;
   s->started = false;
   cudaError_t err = reset_request_state(s, request->prompt_tokens, request->prompt_token_count, out);
-  // One sampling graph replayed for every position, prompt included; samples at
-  // prompt positions are never read (session_api_lifecycle.inc.cu:849-920).
   GraphEntry *graph = nullptr;
+  const char *prefill_env = getenv("NERVA_B200_PREFILL");
+  const bool chunked = s->weights->block_ws.block != nullptr && s->engine == 0 && s->prompt_count > 1 &&
+                       !(prefill_env != nullptr && prefill_env[0] == 'd');
   if (err == cudaSuccess) err = ensure_graph(s, splits_for(s, context_steps), s->sample_kind, &graph, out);
   if (err == cudaSuccess) err = cudaEventRecord(s->ev_start, s->stream);
-  for (uint32_t step = 0; err == cudaSuccess && step < context_steps; ++step) {
+  uint32_t first_step = 0;
+  if (chunked) {
+    // The prompt goes through the chunked prefill, exactly as session_start runs it, so that
+    // run == start + advance bit for bit; the decode steps follow.
+    uint64_t launches = 0, head_launches = 0;
+    if (err == cudaSuccess) err = enqueue_chunked_prefill(s, s->prompt_count, s->sample_kind, &launches);
+    const uint32_t last = s->prompt_count - 1u;
+    if (err == cudaSuccess)
+      err = cudaMemcpyAsync(s->device_cursor, &last, sizeof(uint32_t), cudaMemcpyHostToDevice, s->stream);
+    if (err == cudaSuccess)
+      err = enqueue_step(s, splits_for(s, s->prompt_count), s->sample_kind, &head_launches, nullptr, true);
+    out->kernel_launches += launches + head_launches;
+    first_step = s->prompt_count;
+  }
+  // One sampling graph replayed for every (remaining) position; samples at prompt positions are
+  // never read (session_api_lifecycle.inc.cu:849-920).
+  for (uint32_t step = first_step; err == cudaSuccess && step < context_steps; ++step) {
     if (peer_failure_seen(s, step)) break;
     err = replay(s, graph);
     if (err == cudaSuccess) {
@@ -1895,10 +1942,7 @@ extern "C" int nerva_cuda_hf_decode_sequence_session_run(
 // the device weights are shared (session_api_batch_fork_destroy.inc.cu:311+).
 // One token for a block of sessions that share weights (reference:
 // hf_decode_sequence/session_api_batch_fork_destroy.inc.cu:1-309; selection, reasons, state
-// updates and result fields follow it).  The reference packs the sessions' activations and
-// runs each projection once per block; here every selected session replays its own captured
-// step on its own stream, all in flight together, which gives the same tokens and leaves the
-// weights to be streamed once per session.
+// updates and result fields follow it).
 extern "C" int nerva_cuda_hf_decode_sequence_batch_advance_one(
     const NervaCudaHfDecodeSequenceBatchAdvanceRequest *request,
     NervaCudaHfDecodeSequenceBatchAdvanceResult *out) {
@@ -1993,6 +2037,40 @@ extern "C" int nerva_cuda_hf_decode_sequence_batch_advance_one(
   out->dtype = best->dims.dtype;
   out->layer_count = best->dims.layers;
 
+  // Packed block step: the selected sessions' tokens go through every projection together, so the
+  // weights are streamed once for the block (the reference: one cublasLtMatmul per projection,
+  // session_api_batch_fork_destroy.inc.cu:1-310).  Models without the block path (sparse MoE,
+  // biases, odd widths) and blocks of one replay the sessions' own captured steps side by side.
+  bool packed = selected.size() >= 2 && selected.size() <= kBlockSampleRows;
+  for (uint32_t index : selected) {
+    const Session *s = request->sessions[index];
+    packed = packed && s->weights->block_ws.block != nullptr && s->sample_kind == 1 && s->engine == 0;
+  }
+  if (packed) {
+    std::vector<Session *> block;
+    for (uint32_t index : selected) block.push_back(request->sessions[index]);
+    cudaStream_t stream = block[0]->stream;
+    for (Session *s : block) {  // idle sessions: this only orders their earlier work before the block's
+      if (err == cudaSuccess) err = cudaStreamSynchronize(s->stream);
+      out->sync_calls += 1;
+    }
+    uint64_t launches = 0;
+    if (err == cudaSuccess) err = enqueue_block_decode(block.data(), static_cast<uint32_t>(block.size()), stream, &launches);
+    for (Session *s : block) {
+      const uint32_t slot = s->prompt_count - 1u + s->observed;
+      if (err == cudaSuccess)
+        err = cudaMemcpyAsync(s->host_slots + slot, s->device_slots + slot, sizeof(NervaCudaSyntheticTokenSlot),
+                              cudaMemcpyDeviceToHost, stream);
+      if (err == cudaSuccess)
+        err = cudaMemcpyAsync(s->host_error, s->device_error, sizeof(uint32_t), cudaMemcpyDeviceToHost, stream);
+      out->d2h_bytes += sizeof(NervaCudaSyntheticTokenSlot);
+      out->sampling_kernel_launches += 1;
+    }
+    out->projection_kernel_launches += 4ull * block[0]->dims.layers + 1u;
+    const cudaError_t sync = cudaStreamSynchronize(stream);
+    out->sync_calls += 1;
+    if (err == cudaSuccess) err = sync;
+  } else {
   // Launch every session's step before waiting for any of them.
   for (uint32_t index : selected) {
     Session *s = request->sessions[index];
@@ -2014,6 +2092,7 @@ extern "C" int nerva_cuda_hf_decode_sequence_batch_advance_one(
     const cudaError_t sync = cudaStreamSynchronize(request->sessions[index]->stream);
     out->sync_calls += 1;
     if (err == cudaSuccess) err = sync;
+  }
   }
   if (err != cudaSuccess) {
     set_last_error(cudaGetErrorString(err));

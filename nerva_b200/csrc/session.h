@@ -63,6 +63,41 @@ uint64_t hash_tokens(const uint32_t *tokens, uint32_t count);
 uint64_t hash_weight_descriptors(const NervaCudaHfDecodeSequenceWeightBlock *blocks, uint32_t count);
 void set_last_error(const std::string &text);
 
+// One token of a block step: where its id comes from and where errors go.
+struct BlockTokenRow {
+  const uint32_t *prompt;
+  const uint32_t *prompt_count;
+  const NervaCudaSyntheticTokenSlot *slots;
+  uint32_t position, vocab;
+  uint32_t *error_word;
+};
+
+// Scratch of the block steps (several tokens through every layer together: the packed step of
+// batch_advance_one and the chunked prefill of session_start).  One per weight set, allocated at
+// create and shared by the forks; a block step runs on one stream at a time.
+struct BlockWorkspace {
+  void *block = nullptr;
+  uint64_t bytes = 0;
+  uint32_t max_rows = 0, sample_rows = 0;
+  uint16_t *x_bf16 = nullptr;   // [max_rows][x_elems] normalised activations, the B operand of the next GEMM
+  float *qkv = nullptr;         // [max_rows][A + 2 KV]
+  uint16_t *attn = nullptr;     // [max_rows][A]
+  float *h_a = nullptr, *h_b = nullptr;  // [max_rows][hidden] residual stream, ping-pong
+  uint16_t *ff = nullptr;       // [max_rows][intermediate]
+  float *logits = nullptr;      // [sample_rows][vocab]
+  float *partial_acc = nullptr, *partial_m = nullptr, *partial_l = nullptr;  // split attention, per row
+  uint32_t *attn_tickets = nullptr;  // [max_rows][kv_heads]
+  float *gemm_workspace = nullptr;
+  uint32_t *gemm_tickets = nullptr;
+  float *best_value = nullptr;  // [sample_rows][kBlockArgmaxChunks]
+  uint32_t *best_index = nullptr;
+  FusedAttentionRow *attn_rows = nullptr;  // [max_rows] device copies of the row descriptors
+  BlockTokenRow *token_rows = nullptr;
+};
+constexpr uint32_t kBlockArgmaxChunks = 64;
+constexpr uint32_t kBlockMaxRows = 256;       // one MMA N
+constexpr uint32_t kBlockSampleRows = 32;     // sessions per packed decode step (hf_decode_sequence/types.cuh:63)
+
 // Device weights shared between a session and its forks.
 struct SharedWeights {
   void *block = nullptr;  // one allocation
@@ -70,8 +105,10 @@ struct SharedWeights {
   uint16_t *arena = nullptr;          // upload arena (reference layout)
   uint16_t *qkv_packed = nullptr;     // [layers][(A + 2 KV) x H]
   uint16_t *gate_up_packed = nullptr; // [layers][2 I x H], rows interleaved gate/up
+  BlockWorkspace block_ws;            // empty when the model has no block-step path
   ~SharedWeights() {
     if (block != nullptr) cudaFree(block);
+    if (block_ws.block != nullptr) cudaFree(block_ws.block);
   }
 };
 
@@ -102,6 +139,23 @@ bool step_kernel_supported(uint32_t hidden, uint32_t heads, uint32_t kv_heads, u
                            uint32_t intermediate, uint32_t x_elems, uint32_t row_elems);
 cudaError_t configure_step_kernel();
 cudaError_t launch_step_kernel(cudaStream_t stream, const StepKernelParams &p, uint32_t blocks);
+
+// ---- block steps (block_step.cu) ----
+// True when every layer is dense SwiGLU without biases, the fused attention kernel serves the head
+// shape and every projection width is a multiple of 64: the shapes the block kernels run.
+bool block_step_supported(const NervaCudaHfDecodeSequenceSession *s);
+// Allocates s->weights->block_ws (at create).
+cudaError_t allocate_block_workspace(NervaCudaHfDecodeSequenceSession *s);
+// One token for each of `count` sessions that share weights, on `stream`: the weights are streamed
+// once for the block.  Every session must be idle, positioned at its next token, and its stream
+// synchronised.  Enqueues only; the caller copies the token slots back and synchronises.
+cudaError_t enqueue_block_decode(NervaCudaHfDecodeSequenceSession *const *sessions, uint32_t count,
+                                 cudaStream_t stream, uint64_t *launches);
+// Prompt positions [0, prompt_count) of one session through every layer in chunks of up to
+// kBlockMaxRows tokens, writing the same paged bf16 K/V the decode step reads, then the final
+// norm, lm_head and the sampler for the last position.  Leaves the cursor at prompt_count.
+cudaError_t enqueue_chunked_prefill(NervaCudaHfDecodeSequenceSession *s, uint32_t prompt_count, uint32_t sample_kind,
+                                    uint64_t *launches);
 
 }  // namespace nb
 

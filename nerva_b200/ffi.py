@@ -136,6 +136,8 @@ def _bind(L: C.CDLL, reference_abi_only: bool) -> C.CDLL:
         "nerva_b200_session_attach_loopback": [vp],
         "nerva_b200_projection": [vp, vp, vp, C.c_uint32, C.c_uint32, C.c_uint32, C.c_uint32, C.c_uint32,
                                   P(C.c_uint64)],
+        "nerva_b200_projection_sustained": [vp, vp, vp, C.c_uint32, C.c_uint32, C.c_uint32, C.c_uint32, C.c_uint32,
+                                            C.c_uint32, P(C.c_uint64)],
         "nerva_b200_gqa_decode_attention": [vp, vp, vp, vp, vp, C.c_uint32, C.c_uint32, C.c_uint32, C.c_uint32,
                                             C.c_uint32, C.c_uint32, C.c_uint32, P(C.c_uint64)],
         "nerva_b200_gqa_decode_attention_static_scratch": [vp, vp, vp, vp, vp, C.c_uint32, C.c_uint32,

@@ -26,6 +26,20 @@ def projection(weight_bits: np.ndarray, x_bits: np.ndarray, rows: int, cols: int
     return y, ns.value
 
 
+def projection_sustained(weight_bits: np.ndarray, x_bits: np.ndarray, rows: int, cols: int, tokens: int = 1,
+                         copies: int = 2, warmup: int = 4, iterations: int = 20):
+    """The same projection over `copies` device copies of the matrix (together larger than the L2),
+    launched back to back with programmatic dependent launch.  Returns (y, ns per launch)."""
+    w = np.ascontiguousarray(weight_bits, dtype=np.uint16)
+    x = np.ascontiguousarray(x_bits, dtype=np.uint16)
+    assert w.size == rows * cols and x.size == tokens * cols
+    y = np.empty((tokens, rows), dtype=np.float32)
+    ns = C.c_uint64(0)
+    _check(ffi.lib().nerva_b200_projection_sustained(w.ctypes.data, x.ctypes.data, y.ctypes.data, rows, cols, tokens,
+                                                     copies, warmup, iterations, C.byref(ns)), "projection_sustained")
+    return y, ns.value
+
+
 def gqa_decode_attention(q: np.ndarray, key_pages: np.ndarray, value_pages: np.ndarray, page_table: np.ndarray,
                          batch: int, context: int, heads: int, kv_heads: int, head_dim: int,
                          warmup: int = 0, iterations: int = 1):
