@@ -518,9 +518,19 @@ def run_batch_workload(args, cfg) -> None:
     loop.advance(4)
     block = [session] + [session.fork_shared_weights() for _ in range(forks - 1)]
     lone = [session.fork_shared_weights() for _ in range(forks)]
-    for _ in range(2):   # warm-up block steps
-        CudaHfDecodeSequenceSession.batch_advance_one(block, forks, forks)
-    for s in lone:
+    # warm-up: two block steps and two lone steps, with the logits of the first compared
+    warm_block, warm_lone = [], []
+    logit_gap = None
+    for i in range(2):
+        out = CudaHfDecodeSequenceSession.batch_advance_one(block, forks, forks)
+        warm_block.append(out.tokens[0])
+        warm_lone.append(CudaHfDecodeSequenceLoop(lone[0]).advance(1).tokens[0])
+        if i == 0:
+            a, b = block[0].read_logits(), lone[0].read_logits()
+            top2 = np.sort(b)[-2:]
+            logit_gap = {"max_abs_logit_difference": float(np.abs(a - b).max()),
+                         "lone_top1_minus_top2": float(top2[1] - top2[0])}
+    for s in lone[1:]:
         CudaHfDecodeSequenceLoop(s).advance(2)
     t0 = time.perf_counter()
     block_tokens = []
@@ -546,12 +556,15 @@ def run_batch_workload(args, cfg) -> None:
         "speedup": lone_s / block_s, "ms_per_block_step": 1e3 * block_s / steps,
         "weight_stream_frac_of_measured_hbm": nbytes / (block_s / steps) / 1e9 / peaks["hbm_gbs"],
         "tokens_identical_within_block": same_within_block,
-        "token_match_with_sequential": {"compared": steps, "identical_prefix": steps if first_diff is None else first_diff},
+        "token_match_with_sequential": {"compared": steps, "identical_prefix": steps if first_diff is None else first_diff,
+                                        "warm_up_block_tokens": warm_block, "warm_up_lone_tokens": warm_lone,
+                                        "first_step": logit_gap},
         "timing": "host wall clock around the C-ABI calls, token slots copied back every call",
     }), flush=True)
 
 
-def run_operator_workloads(kind: str) -> None:
+def run_operator_workloads(kind: str, only_shape: str = "", only_tokens: int = 0, only_batch: int = 0,
+                           only_context: int = 0) -> None:
     """Per-operator sweeps (isolated projection shapes, long-context attention) through the per-op C ABI (host buffers in,
     device time per launch out, L2 flushed between launches).  One JSON line per case."""
     from nerva_b200 import build, ops, synth
@@ -561,8 +574,12 @@ def run_operator_workloads(kind: str) -> None:
         shapes = [("qkv", 6144, 4096), ("o", 4096, 4096), ("gate_up", 24576, 4096), ("down", 4096, 12288),
                   ("lm_head", 151936, 4096)]
         for name, rows, cols in shapes:
+            if only_shape and name != only_shape:
+                continue
             w = ops.synth_normal_bf16(0, 77, rows * cols, 0.02)
             for m in (1, 4, 16, 64):
+                if only_tokens and m != only_tokens:
+                    continue
                 x = ops.synth_normal_bf16(0, synth.T_ACTIVATION, m * cols, 1.0)
                 _, alone_ns = ops.projection(w, x, rows, cols, tokens=m, warmup=3, iterations=10)
                 # sustained: copies of the matrix that together exceed the 126 MB L2, launched back to back
@@ -581,24 +598,53 @@ def run_operator_workloads(kind: str) -> None:
                                   "note": "block kernel on the tensor pipe (tcgen05), weights streamed once for the block"
                                   if m > 1 else "weight-streaming GEMV"}), flush=True)
         return
-    heads, kv_heads, d = 32, 8, 128
+    run_attention_workload(1, 0, only_batch, only_context)
+
+
+def run_attention_workload(world: int, rank: int, only_batch: int = 0, only_context: int = 0) -> None:
+    """Long-context GQA decode attention on the Qwen3-8B layer shape (32 query / 8 KV heads of 128),
+    bf16 K/V in 16-token pages placed by a seeded permutation.  With world > 1 the KV heads are
+    sharded the way the tensor-parallel session shards them: every rank owns 8 / world KV heads
+    (their pages and page table) and the 32 / world query heads that read them.  Attention needs
+    no exchange, and none follows it: a rank's output slice is exactly the input columns of its
+    shard of the O projection.  The time of a case is the slowest rank's."""
+    from nerva_b200 import build, ops, synth
+    build.build()
+    peak = measured_peaks()
+    heads, kv_heads, d = 32 // world, 8 // world, 128
     for batch in (1, 8):
         for context in (8192, 32768, 131072):
+            if (only_batch and batch != only_batch) or (only_context and context != only_context):
+                continue
             pages = (context + 15) // 16
             n = batch * pages * 16 * kv_heads * d
-            k = ops.synth_normal_bf16(0, synth.layer_tensor_id(0, synth.L_K), n, 1.0)
-            v = ops.synth_normal_bf16(0, synth.layer_tensor_id(0, synth.L_V), n, 1.0)
+            k = ops.synth_normal_bf16(rank, synth.layer_tensor_id(0, synth.L_K), n, 1.0)
+            v = ops.synth_normal_bf16(rank, synth.layer_tensor_id(0, synth.L_V), n, 1.0)
             table = np.stack([synth.permutation(b, synth.T_PAGE_TABLE, pages) for b in range(batch)])
-            q = synth.normal_f32(0, synth.layer_tensor_id(0, synth.L_Q), batch * heads * d, 1.0)
-            _, ns = ops.gqa_decode_attention(q, k, v, table, batch, context, heads, kv_heads, d, warmup=3,
-                                             iterations=10)
-            nbytes = batch * (4096 * context + pages * 4 + heads * d * 4 * 2)
-            gbs = nbytes / ns
-            print(json.dumps({"workload": "long-context GQA decode attention", "batch": batch, "context": context,
-                              "heads": heads, "kv_heads": kv_heads, "head_dim": d, "us": ns / 1e3,
-                              "algorithmic_bytes": nbytes, "GB/s": gbs,
-                              "frac_of_measured_hbm": gbs / peak["hbm_gbs"],
-                              "pages": "16-token pages placed by a seeded Fisher-Yates permutation"}), flush=True)
+            q = synth.normal_f32(rank, synth.layer_tensor_id(0, synth.L_Q), batch * heads * d, 1.0)
+            _, alone_ns = ops.gqa_decode_attention(q, k, v, table, batch, context, heads, kv_heads, d, warmup=3,
+                                                   iterations=10)
+            # sustained: the caches of several layers (together larger than the L2), one launch after the other
+            copies = max(2, min(36, -(-320_000_000 // (4 * n))))
+            out, ns = ops.gqa_decode_attention_sustained(q, k, v, table, batch, context, heads, kv_heads, d,
+                                                         copies=copies, warmup=copies, iterations=4 * copies)
+            total_ns = _max_over_ranks(float(ns), world)
+            # whole job: all KV heads of all ranks
+            nbytes = world * batch * (2 * context * kv_heads * d * 2 + pages * 4 + heads * d * 4 * 2)
+            gbs = nbytes / total_ns
+            if rank == 0:
+                print(json.dumps({"workload": "long-context GQA decode attention", "n_gpus": world, "batch": batch,
+                                  "context": context, "heads": 32, "kv_heads": 8, "head_dim": d,
+                                  "us": total_ns / 1e3, "algorithmic_bytes": nbytes,
+                                  "GB/s": gbs, "frac_of_measured_hbm_per_gpu": gbs / world / peak["hbm_gbs"],
+                                  "sharding": "none" if world == 1 else f"{kv_heads} KV heads per rank, no exchange "
+                                                                         f"(slowest rank's time)",
+                                  "pages": "16-token pages placed by a seeded Fisher-Yates permutation",
+                                  "timing": f"{4 * copies} launches back to back over the caches of {copies} layers "
+                                            f"(larger than L2 together)",
+                                  "single_launch_us": _max_over_ranks(float(alone_ns), world) / 1e3,
+                                  "single_launch_note": "one launch timed alone, 192 MB written to flush L2 before it"}),
+                      flush=True)
 
 
 def _barrier_fn(world: int):
@@ -636,15 +682,29 @@ def main() -> None:
     ap.add_argument("--workload", default="decode", choices=["decode", "linear", "attention", "reference-gpu", "batch"],
                     help="decode: the bench line; linear / attention: per-operator sweeps of the isolated "
                          "projection shapes and of long-context attention (one JSON line per case)")
+    ap.add_argument("--shape", default="", help="linear sweep: only this projection (qkv, o, gate_up, down, lm_head)")
+    ap.add_argument("--tokens", type=int, default=0, help="linear sweep: only this block size")
+    ap.add_argument("--batch", type=int, default=0, help="attention sweep: only this batch size")
+    ap.add_argument("--context", type=int, default=0, help="attention sweep: only this context length")
     ap.add_argument("--timeline", action="store_true",
                     help="add the in-graph timeline (kernel-written %%globaltimer stamps, mean over layers)")
     args = ap.parse_args()
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
     local = int(os.environ.get("LOCAL_RANK", "0"))
+    if args.workload == "attention" and world > 1:
+        visible = os.environ.get("CUDA_VISIBLE_DEVICES", "")
+        from nerva_b200 import tp
+        tp.select_device(local)
+        import torch.distributed as dist
+        dist.init_process_group("gloo")  # carries the host-side max over ranks only
+        run_attention_workload(world, rank, args.batch, args.context)
+        dist.barrier()
+        dist.destroy_process_group()
+        return
     if args.workload in ("linear", "attention"):
         if rank == 0:
-            run_operator_workloads(args.workload)
+            run_operator_workloads(args.workload, args.shape, args.tokens, args.batch, args.context)
         return
     cfg = workload(args.config, args.layers, args.prompt_tokens)
     if args.workload == "reference-gpu":

@@ -913,6 +913,15 @@ int nerva_b200_gqa_decode_attention(const float *q, const uint16_t *key_pages,
                                     float *out, uint32_t batch, uint32_t context, uint32_t heads,
                                     uint32_t kv_heads, uint32_t head_dim, uint32_t warmup,
                                     uint32_t iterations, uint64_t *avg_ns);
+/* Sustained form (no counterpart in the reference): `copies` device copies of the K and V pages —
+ * the caches of that many layers, together larger than the L2 — are attended over back to back on
+ * one stream, as the attention launches of the layers of a decode step follow each other.
+ * avg_ns: time per launch (attention + merge) over `iterations` launches after `warmup`. */
+int nerva_b200_gqa_decode_attention_sustained(const float *q, const uint16_t *key_pages,
+                                              const uint16_t *value_pages, const uint32_t *page_table,
+                                              float *out, uint32_t batch, uint32_t context, uint32_t heads,
+                                              uint32_t kv_heads, uint32_t head_dim, uint32_t copies,
+                                              uint32_t warmup, uint32_t iterations, uint64_t *avg_ns);
 
 /* The same attention with DEVICE pointers (layouts as above) and no allocation:
  * the split partials live in a fixed 4 MiB device array inside the library, so

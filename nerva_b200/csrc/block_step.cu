@@ -285,7 +285,7 @@ cudaError_t enqueue_block_layers(const BlockPlan &b, uint64_t *launches) {
       err = launch_with_pdl(block_norm_kernel, dim3(b.rows), dim3(kNormThreads), 0, b.stream, b.pdl, ws.h_a,
                             arena_at(s, L.rms_mlp), s->rms_eps, d.hidden, ws.x_bf16, d.hidden);
     if (err == cudaSuccess)
-      err = block_gemm(b, s->weights->gate_up_packed + static_cast<uint64_t>(l) * 2u * d.intermediate * d.hidden,
+      err = block_gemm(b, s->weights->gate_up_packed + gate_up_packed_offset(s, l),
                        2u * d.intermediate, d.hidden, ws.x_bf16, d.hidden, kEpilogueSwiglu, nullptr, nullptr, ws.ff);
     // h_b = h_a + down(ff)
     if (err == cudaSuccess)
@@ -295,6 +295,16 @@ cudaError_t enqueue_block_layers(const BlockPlan &b, uint64_t *launches) {
   }
   if (launches != nullptr) *launches += n;
   return err;
+}
+
+// Attention spans per KV head in a block step.  A single token wants many short spans (latency);
+// a block of rows already fills the machine with rows x kv_heads blocks per span, so it takes as
+// few spans as keep about six blocks per SM in flight, and never more than the context needs.
+uint32_t block_attention_splits(const Session *s, uint32_t rows, uint32_t longest_context) {
+  const uint32_t by_context = fused_attention_splits(longest_context);
+  uint32_t by_machine = (6u * s->sm_count) / (rows * s->dims.kv_heads);
+  if (by_machine < 1u) by_machine = 1u;
+  return by_context < by_machine ? by_context : by_machine;
 }
 
 FusedAttentionRow attention_row(Session *s, const BlockWorkspace &ws, uint32_t row, uint32_t position) {
@@ -344,7 +354,7 @@ cudaError_t upload_rows(const BlockWorkspace &ws, const std::vector<FusedAttenti
 
 bool block_step_supported(const NervaCudaHfDecodeSequenceSession *s) {
   const ModelDims &d = s->dims;
-  if (s->tp_world > 1 || s->has_moe || !s->fused_attention || d.dtype != NERVA_DTYPE_BF16) return false;
+  if (s->tp_world > 1 || s->has_moe || d.mla() || !s->fused_attention || d.dtype != NERVA_DTYPE_BF16) return false;
   const uint64_t ah = d.attention_hidden();
   if (d.hidden % 64u != 0 || ah % 64u != 0 || d.intermediate % 64u != 0) return false;
   if (d.hidden % 4u != 0 || d.hidden / 4u > kNormRegIters * kNormThreads) return false;  // block_norm_kernel's reach
@@ -396,7 +406,7 @@ cudaError_t enqueue_block_decode(NervaCudaHfDecodeSequenceSession *const *sessio
   }
   cudaError_t err = upload_rows(ws, attn, tokens, stream);
   if (err != cudaSuccess) return err;
-  BlockPlan b{model, stream, count, fused_attention_splits(longest), false, model->use_pdl};
+  BlockPlan b{model, stream, count, block_attention_splits(model, count, longest), false, model->use_pdl};
   uint64_t n = 0;
   err = enqueue_block_layers(b, &n);
   // final norm, lm_head, arg-max: per row
@@ -449,7 +459,7 @@ cudaError_t enqueue_chunked_prefill(NervaCudaHfDecodeSequenceSession *s, uint32_
     }
     err = upload_rows(ws, attn, tokens, s->stream);
     if (err != cudaSuccess) break;
-    BlockPlan b{s, s->stream, rows, fused_attention_splits(begin + rows), true, s->use_pdl};
+    BlockPlan b{s, s->stream, rows, block_attention_splits(s, rows, begin + rows), true, s->use_pdl};
     err = enqueue_block_layers(b, launches);
     if (err == cudaSuccess && begin + rows == prompt_count) {
       // the last position's residual stream becomes the session's own, where the head expects it

@@ -162,9 +162,10 @@ __device__ __forceinline__ void pdl_trigger() {
 // ---- waits on other GPUs (tensor-parallel exchange) ----
 // A wait on a peer gives up after kPeerWaitCycleLimit SM cycles (about a second: ranks are separate
 // processes, so the limit has to cover launch skew between them) and records kErrPeerWaitTimeout.
-// The error word stays set until the next request starts, and every later wait of the session
-// looks at it first: once one exchange has failed, the steps already queued behind it run through
-// without waiting again, so a rank that died costs the others one limit, not one per exchange.
+// The error word stays set until the next request starts, and a wait whose first poll misses
+// looks at it before it looks at the clock: once one exchange has failed, the steps already
+// queued behind it run through without waiting again, so a rank that died costs the others one
+// limit, not one per exchange.  A wait whose data is already there never reads the word.
 constexpr long long kPeerWaitCycleLimit = kWaitCycleLimit;
 __device__ __forceinline__ bool step_already_failed(const uint32_t *error_word) {
   return error_word != nullptr && *reinterpret_cast<const volatile uint32_t *>(error_word) != 0u;

@@ -15,10 +15,13 @@
 // Decomposition ("stream-K").  The sequence of (row tile, 64-wide slice) pairs is cut into one
 // contiguous, equally long run per thread block, so every SM streams the same number of weight
 // bytes whatever the shape (QKV has 48 row tiles, lm_head 1187).  A run that starts or ends in the
-// middle of a row tile leaves a partial accumulator: it goes to a workspace slot, the blocks that
-// share the tile take a ticket, and the last one adds the partials in ascending block order before
-// it runs the epilogue.  The partition depends on the shape only, so a token's result does not
-// depend on which other tokens share its block, and results are bit-stable run to run.
+// middle of a row tile leaves a partial accumulator in a workspace slot; a small second launch
+// (gemm_fixup_kernel, one block per split tile and 16 tokens) adds the partials of every split tile
+// in ascending block order and runs the epilogue for it.  Summing inside the projection kernel by
+// the last block to arrive was measured first: that one block reads every partial of its tile with
+// 128 threads while the rest of the grid has left, 10 to 27 us for a 64-token block.  The partition
+// depends on the shape only, so a token's result does not depend on which other tokens share its
+// block, and results are bit-stable run to run.
 //
 // Roles inside a block (192 threads): warp 0 issues the TMA copies into an mbarrier ring, warp 1
 // allocates tensor memory and issues the MMAs (one elected lane), warps 2..5 read the accumulator
@@ -44,21 +47,25 @@ constexpr uint32_t kATileBytes = kTileRows * kSliceK * 2u;
 constexpr uint32_t kMaxStages = 8;
 constexpr uint32_t kGemmThreads = 192;
 constexpr uint32_t kEpilogueThreads = 128;
-constexpr uint32_t kTmemColumns = 512;  // two accumulator buffers of up to 256 fp32 columns
-constexpr uint32_t kAccStride = 256;
 constexpr uint32_t kGroup = 16;         // tokens per tcgen05.ld
+// Blocks of up to kSmallBlockTokens tokens run two thread blocks per SM (half the shared memory and
+// a quarter of the tensor memory each): while one block of a launch drains its last tile, writes
+// its results and leaves, the block that takes its place — of this launch or, with programmatic
+// dependent launch, of the next one — is already filling its ring, so the SM keeps weights in
+// flight across the hand-over.  Larger blocks (prefill chunks) take the SM alone.
+constexpr uint32_t kSmallBlockTokens = 64;
 
 struct GemmShared {
   uint64_t full[kMaxStages], empty[kMaxStages];
   uint64_t acc_full[2], acc_empty[2];
   uint32_t tmem_base;
   uint32_t abort;
-  uint32_t ticket;
 };
 
 struct GemmKernelParams {
   uint32_t rows, cols, tokens, n_pad;  // n_pad: tokens rounded up to 16 (the MMA N)
   uint32_t stages;
+  uint32_t tmem_columns;  // allocation: two accumulator buffers of tmem_columns / 2 fp32 columns
   uint32_t epilogue;
   const float *resid_in;
   float *out_f32;
@@ -66,7 +73,19 @@ struct GemmKernelParams {
   float *workspace;
   uint32_t *tickets;
   uint32_t *error_word;
+  unsigned long long *stamps;
 };
+
+// Timeline stamp by an arbitrary thread of the first or the last block (common.cuh stamp() is thread 0 only).
+__device__ __forceinline__ void stamp_any(unsigned long long *stamps, uint32_t slot) {
+  if (stamps == nullptr) return;
+  const uint32_t last = gridDim.x - 1u;
+  if (blockIdx.x != 0 && blockIdx.x != last) return;
+  unsigned long long now;
+  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(now));
+  if (blockIdx.x == 0) stamps[slot] = now;
+  if (blockIdx.x == last) stamps[4u + slot] = now;
+}
 
 // ---- static partition, computed identically by every role and by the fix-up ----
 struct Partition {
@@ -83,19 +102,12 @@ __device__ __host__ inline Partition make_partition(uint32_t rows, uint32_t cols
   p.blocks = blocks;
   return p;
 }
-// First / last block whose run touches tile t.
+// First block whose run touches tile t.
 __device__ inline uint32_t first_block_of_tile(const Partition &p, uint32_t t) {
   const uint64_t at = static_cast<uint64_t>(t) * p.slices;
   uint32_t b = static_cast<uint32_t>(at * p.blocks / p.total);
   while (b + 1u < p.blocks && p.end(b) <= at) ++b;
   while (b > 0 && p.end(b - 1u) > at) --b;
-  return b;
-}
-__device__ inline uint32_t last_block_of_tile(const Partition &p, uint32_t t) {
-  const uint64_t at = static_cast<uint64_t>(t + 1u) * p.slices - 1ull;
-  uint32_t b = static_cast<uint32_t>(at * p.blocks / p.total);
-  while (b + 1u < p.blocks && p.end(b) <= at) ++b;
-  while (b > 0 && p.begin(b) > at) --b;
   return b;
 }
 // Workspace slot of block b's partial accumulator of tile t: slot 0 when the tile is where the
@@ -182,7 +194,6 @@ __device__ __forceinline__ void tmem_load16(uint32_t taddr, float *v) {
 #pragma unroll
   for (uint32_t i = 0; i < 16; ++i) v[i] = __uint_as_float(r[i]);
 }
-__device__ __forceinline__ void epilogue_barrier() { asm volatile("bar.sync 1, 128;" ::: "memory"); }
 
 // Shared-memory matrix descriptor of a K-major tile whose rows are 128 bytes (one swizzle atom):
 // start address, 8-row groups 1024 bytes apart, SWIZZLE_128B, descriptor version 1.
@@ -196,7 +207,83 @@ __device__ __forceinline__ uint32_t instr_desc_bf16(uint32_t n) {
   return (1u << 4) | (1u << 7) | (1u << 10) | ((n >> 3) << 17) | ((kTileRows >> 4) << 24);
 }
 
-__global__ void __launch_bounds__(kGemmThreads, 1)
+// Epilogue of 16 tokens (g .. g + 15) of accumulator row `row`, values in v.  Called by all 32 lanes
+// of a warp whose lanes hold 32 consecutive rows.
+__device__ __forceinline__ void tile_epilogue(const GemmKernelParams &p, const float (&v)[kGroup], uint32_t row,
+                                              uint32_t g, uint32_t lane) {
+  if (p.epilogue == kEpilogueSwiglu) {
+    // rows interleaved (gate, up): the neighbouring lane holds the other half of the pair
+#pragma unroll
+    for (uint32_t j = 0; j < kGroup; ++j) {
+      const float other = __shfl_xor_sync(0xffffffffu, v[j], 1);
+      const uint32_t m = g + j;
+      if ((lane & 1u) == 0 && row + 1u < p.rows && m < p.tokens)
+        p.out_bf16[static_cast<uint64_t>(m) * (p.rows / 2u) + row / 2u] = f32_to_bf16_bits(silu(v[j]) * other);
+    }
+  } else if (row < p.rows) {
+#pragma unroll
+    for (uint32_t j = 0; j < kGroup; ++j) {
+      const uint32_t m = g + j;
+      if (m < p.tokens) {
+        const uint64_t at = static_cast<uint64_t>(m) * p.rows + row;
+        p.out_f32[at] = p.resid_in != nullptr ? v[j] + __ldcg(p.resid_in + at) : v[j];
+      }
+    }
+  }
+}
+
+// Finishes the row tiles that more than one block of gemm_tc_kernel contributed to.  Grid
+// (blocks of the projection launch, n_pad / 16); block b is responsible for the tile its run began
+// in when that tile is split and b is the last block to touch it; it adds the partials in
+// ascending block order (bit-stable) and runs the epilogue.  Other blocks leave at once.
+__global__ void __launch_bounds__(kEpilogueThreads) gemm_fixup_kernel(GemmKernelParams p, uint32_t gemm_blocks) {
+  pdl_trigger();
+  const Partition part = make_partition(p.rows, p.cols, gemm_blocks);
+  const uint32_t b = blockIdx.x;
+  const uint64_t begin = part.begin(b), end = part.end(b);
+  const uint32_t tile = static_cast<uint32_t>(begin / part.slices);
+  const bool mine = begin % part.slices != 0 && end >= static_cast<uint64_t>(tile + 1u) * part.slices;
+  if (!mine) return;
+  pdl_wait();  // the partials come from the projection launch just before
+  const uint32_t b_lo = first_block_of_tile(part, tile);
+  const uint32_t row_in_tile = threadIdx.x, lane = threadIdx.x & 31u;
+  const uint32_t g = blockIdx.y * kGroup;
+  const uint64_t slot_floats = static_cast<uint64_t>(p.n_pad) * kTileRows;
+  float v[kGroup];
+  for (uint32_t q = b_lo; q <= b; q += 2u) {
+    // two contributors' loads in flight together
+    float4 x[2][kGroup / 4u];
+#pragma unroll
+    for (uint32_t u = 0; u < 2u; ++u) {
+      const uint32_t bb = q + u <= b ? q + u : b;
+      const float *src = p.workspace + partial_slot(part, bb, tile) * slot_floats +
+                         static_cast<uint64_t>(row_in_tile) * p.n_pad + g;
+#pragma unroll
+      for (uint32_t j = 0; j < kGroup / 4u; ++j) x[u][j] = __ldcg(reinterpret_cast<const float4 *>(src) + j);
+    }
+#pragma unroll
+    for (uint32_t u = 0; u < 2u; ++u) {
+      if (q + u > b) break;
+#pragma unroll
+      for (uint32_t j = 0; j < kGroup / 4u; ++j) {
+        if (q + u == b_lo) {
+          v[4u * j] = x[u][j].x;
+          v[4u * j + 1u] = x[u][j].y;
+          v[4u * j + 2u] = x[u][j].z;
+          v[4u * j + 3u] = x[u][j].w;
+        } else {
+          v[4u * j] += x[u][j].x;
+          v[4u * j + 1u] += x[u][j].y;
+          v[4u * j + 2u] += x[u][j].z;
+          v[4u * j + 3u] += x[u][j].w;
+        }
+      }
+    }
+  }
+  tile_epilogue(p, v, tile * kTileRows + row_in_tile, g, lane);
+}
+
+__global__ void __launch_bounds__(kGemmThreads, 2)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x,
                GemmKernelParams p) {
   extern __shared__ __align__(1024) uint8_t smem_raw[];
@@ -209,7 +296,15 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
   volatile uint32_t *abort = &sh.abort;
 
   pdl_trigger();
+  const Partition part = make_partition(p.rows, p.cols, gridDim.x);
+  const uint64_t run_begin = part.begin(blockIdx.x), run_end = part.end(blockIdx.x);
+  // The weights do not depend on the previous kernel: the first ring-full of weight tiles is
+  // requested by thread 0 as soon as its barriers exist — before the block's set-up barrier and
+  // before the dependency wait; the activation tiles of the same stages follow after that wait.
+  const uint64_t run_len = run_end - run_begin;
+  const uint32_t head = run_len < p.stages ? static_cast<uint32_t>(run_len) : p.stages;
   if (threadIdx.x == 0) {
+    stamp_any(p.stamps, kStampEntry);
     for (uint32_t s = 0; s < p.stages; ++s) {
       mbar_init(&sh.full[s], 1);
       mbar_init(&sh.empty[s], 1);
@@ -220,10 +315,20 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
     }
     sh.abort = 0;
     mbar_init_fence();
+    const uint64_t w_policy = l2_evict_first_policy();  // weights are read once
+    SegmentWalk walk{run_begin, run_end, part.slices};
+    Segment seg;
+    uint32_t i = 0;
+    while (i < head && walk.next(&seg)) {
+      for (uint32_t c = seg.slice_begin; c < seg.slice_end && i < head; ++c, ++i) {
+        mbar_arrive_expect_tx(&sh.full[i], stage_bytes);
+        tma_load_2d(ring + i * stage_bytes, &map_w, c * kSliceK, seg.tile * kTileRows, &sh.full[i], w_policy);
+      }
+    }
   }
   if (warp == 1) {
     asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_addr(&sh.tmem_base)),
-                 "r"(kTmemColumns)
+                 "r"(p.tmem_columns)
                  : "memory");
     asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
   }
@@ -231,9 +336,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
   __syncthreads();
   tcgen05_fence_after();
   const uint32_t tmem_base = sh.tmem_base;
-
-  const Partition part = make_partition(p.rows, p.cols, gridDim.x);
-  const uint64_t run_begin = part.begin(blockIdx.x), run_end = part.end(blockIdx.x);
+  const uint32_t acc_stride = p.tmem_columns / 2u;
 
   if (warp == 0) {
     // ---------------- producer ----------------
@@ -243,22 +346,6 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
       SegmentWalk walk{run_begin, run_end, part.slices};
       Segment seg;
       uint32_t issued = 0;
-      // The weights do not depend on the previous kernel: the first ring-full of weight tiles is
-      // requested before the dependency wait, the activation tiles of the same stages after it.
-      const uint64_t run_len = run_end - run_begin;
-      const uint32_t head = run_len < p.stages ? static_cast<uint32_t>(run_len) : p.stages;
-      {
-        SegmentWalk w2 = walk;
-        Segment s2;
-        uint32_t i = 0;
-        while (i < head && w2.next(&s2)) {
-          for (uint32_t c = s2.slice_begin; c < s2.slice_end && i < head; ++c, ++i) {
-            uint8_t *stage = ring + i * stage_bytes;
-            mbar_arrive_expect_tx(&sh.full[i], stage_bytes);
-            tma_load_2d(stage, &map_w, c * kSliceK, s2.tile * kTileRows, &sh.full[i], w_policy);
-          }
-        }
-      }
       pdl_wait();
       bool ok = true;
       while (ok && walk.next(&seg)) {
@@ -291,13 +378,14 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
         // the epilogue must have drained this accumulator buffer (two segments ago)
         if (!abortable_wait(&sh.acc_empty[acc], ((segment_index >> 1) & 1u) ^ 1u, abort, p.error_word)) break;
         tcgen05_fence_after();
-        const uint32_t tmem_d = tmem_base + acc * kAccStride;
+        const uint32_t tmem_d = tmem_base + acc * acc_stride;
         for (uint32_t c = seg.slice_begin; c < seg.slice_end; ++c, ++consumed) {
           const uint32_t s = consumed % p.stages;
           if (!abortable_wait(&sh.full[s], (consumed / p.stages) & 1u, abort, p.error_word)) {
             ok = false;
             break;
           }
+          if (consumed == 0) stamp_any(p.stamps, kStampAfterWait);
           tcgen05_fence_after();
           const uint8_t *stage = ring + s * stage_bytes;
           const uint64_t desc_a = kmajor_sw128_desc(stage);
@@ -312,13 +400,13 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
         if (ok) tcgen05_commit(&sh.acc_full[acc]);
         ++segment_index;
       }
+      stamp_any(p.stamps, kStampAfterPrologue);  // every MMA of this block issued and committed
     }
   } else {
     // ---------------- epilogue (warps 2..5) ----------------
     pdl_wait();
     const uint32_t quarter = warp & 3u;                 // the TMEM lanes this warp may read
     const uint32_t row_in_tile = quarter * 32u + lane;  // accumulator row = TMEM lane
-    const uint32_t et = threadIdx.x - 64u;              // 0..127
     SegmentWalk walk{run_begin, run_end, part.slices};
     Segment seg;
     uint32_t segment_index = 0;
@@ -327,70 +415,25 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
       const uint32_t acc = segment_index & 1u;
       if (!abortable_wait(&sh.acc_full[acc], (segment_index >> 1) & 1u, abort, p.error_word)) break;
       tcgen05_fence_after();
-      const uint32_t taddr = tmem_base + acc * kAccStride + ((quarter * 32u) << 16);
+      const uint32_t taddr = tmem_base + acc * acc_stride + ((quarter * 32u) << 16);
       const bool whole = seg.slice_begin == 0 && seg.slice_end == part.slices;
-      bool finish = whole;
-      uint32_t b_lo = 0, b_hi = 0;
       if (!whole) {
-        // partial accumulator -> workspace slot; the last block of the tile to arrive finishes it
-        float *slot = p.workspace + partial_slot(part, blockIdx.x, seg.tile) * slot_floats;
+        // partial accumulator -> this block's workspace slot, [row][token]; gemm_fixup_kernel finishes the tile
+        float *slot = p.workspace + partial_slot(part, blockIdx.x, seg.tile) * slot_floats +
+                      static_cast<uint64_t>(row_in_tile) * p.n_pad;
         for (uint32_t g = 0; g < p.n_pad; g += kGroup) {
           float v[kGroup];
           tmem_load16(taddr + g, v);
 #pragma unroll
-          for (uint32_t j = 0; j < kGroup; ++j) slot[static_cast<uint64_t>(g + j) * kTileRows + row_in_tile] = v[j];
+          for (uint32_t j = 0; j < kGroup; j += 4u)
+            *reinterpret_cast<float4 *>(slot + g + j) = make_float4(v[j], v[j + 1u], v[j + 2u], v[j + 3u]);
         }
-        b_lo = first_block_of_tile(part, seg.tile);
-        b_hi = last_block_of_tile(part, seg.tile);
-        epilogue_barrier();
-        if (et == 0) {
-          uint32_t ticket;
-          asm volatile("atom.acq_rel.gpu.global.add.u32 %0, [%1], 1;" : "=r"(ticket) : "l"(p.tickets + seg.tile) : "memory");
-          if (ticket == b_hi - b_lo) p.tickets[seg.tile] = 0;  // last one in: leave the counter ready for the next launch
-          sh.ticket = ticket;
-        }
-        epilogue_barrier();
-        finish = sh.ticket == b_hi - b_lo;
-      }
-      if (finish) {
+      } else {
         const uint32_t row = seg.tile * kTileRows + row_in_tile;
         for (uint32_t g = 0; g < p.n_pad; g += kGroup) {
           float v[kGroup];
-          if (whole) {
-            tmem_load16(taddr + g, v);
-          } else {
-            // partials in ascending block order; this block's own comes back from its slot as well,
-            // so the sum does not depend on which block happened to arrive last
-#pragma unroll
-            for (uint32_t j = 0; j < kGroup; ++j) v[j] = 0.0f;
-            for (uint32_t b = b_lo; b <= b_hi; ++b) {
-              const float *src = p.workspace + partial_slot(part, b, seg.tile) * slot_floats;
-#pragma unroll
-              for (uint32_t j = 0; j < kGroup; ++j) {
-                const float part_v = __ldcg(src + static_cast<uint64_t>(g + j) * kTileRows + row_in_tile);
-                v[j] = b == b_lo ? part_v : v[j] + part_v;
-              }
-            }
-          }
-          if (p.epilogue == kEpilogueSwiglu) {
-            // rows interleaved (gate, up): the neighbouring lane holds the other half of the pair
-#pragma unroll
-            for (uint32_t j = 0; j < kGroup; ++j) {
-              const float other = __shfl_xor_sync(0xffffffffu, v[j], 1);
-              const uint32_t m = g + j;
-              if ((lane & 1u) == 0 && row + 1u < p.rows && m < p.tokens)
-                p.out_bf16[static_cast<uint64_t>(m) * (p.rows / 2u) + row / 2u] = f32_to_bf16_bits(silu(v[j]) * other);
-            }
-          } else if (row < p.rows) {
-#pragma unroll
-            for (uint32_t j = 0; j < kGroup; ++j) {
-              const uint32_t m = g + j;
-              if (m < p.tokens) {
-                const uint64_t at = static_cast<uint64_t>(m) * p.rows + row;
-                p.out_f32[at] = p.resid_in != nullptr ? v[j] + __ldcg(p.resid_in + at) : v[j];
-              }
-            }
-          }
+          tmem_load16(taddr + g, v);
+          tile_epilogue(p, v, row, g, lane);
         }
       }
       tcgen05_fence_before();
@@ -411,7 +454,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
   __syncthreads();
   if (warp == 1) {
     tcgen05_fence_after();
-    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(kTmemColumns) : "memory");
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(p.tmem_columns) : "memory");
+    if (lane == 0) stamp_any(p.stamps, kStampExit);
   }
 }
 
@@ -445,25 +489,47 @@ bool make_map(CUtensorMap *map, const uint16_t *base, uint64_t inner, uint64_t o
 
 uint32_t padded_tokens(uint32_t tokens) { return (tokens + 15u) & ~15u; }
 
+bool two_blocks_per_sm(uint32_t n_pad) { return n_pad <= kSmallBlockTokens; }
+
 uint32_t stages_for(uint32_t n_pad) {
   const uint32_t stage_bytes = kATileBytes + n_pad * kSliceK * 2u;
-  uint32_t stages = (200u * 1024u) / stage_bytes;
+  const uint32_t budget = two_blocks_per_sm(n_pad) ? 108u * 1024u : 200u * 1024u;
+  uint32_t stages = budget / stage_bytes;
   if (stages > kMaxStages) stages = kMaxStages;
   return stages;
 }
+
+uint32_t tmem_columns_for(uint32_t n_pad) { return two_blocks_per_sm(n_pad) ? 128u : 512u; }
 
 uint32_t gemm_smem_bytes(uint32_t n_pad, uint32_t stages) {
   return 1024u + stages * (kATileBytes + n_pad * kSliceK * 2u) + static_cast<uint32_t>(sizeof(GemmShared)) + 64u;
 }
 
+// Two runs per SM whatever the block size, so that the split points — and with them the order in
+// which a row's partial sums are added — depend on the matrix shape alone: a token gets the same
+// bits in a block of 2 and in a block of 256.  Blocks too large for two per SM run the grid in two waves.
 uint32_t gemm_blocks(uint32_t rows, uint32_t cols, uint32_t sm_count) {
   const Partition p = make_partition(rows, cols, 1);
-  return p.total < sm_count ? static_cast<uint32_t>(p.total) : sm_count;
+  const uint32_t want = 2u * sm_count;
+  return p.total < want ? static_cast<uint32_t>(p.total) : want;
 }
 
 }  // namespace
 
 bool tensor_map_available() { return tensor_map_encoder() != nullptr; }
+
+bool encode_bf16_map_2d(void *map, const uint16_t *base, uint64_t inner, uint64_t outer, uint32_t box_inner,
+                        uint32_t box_outer) {
+  PFN_cuTensorMapEncodeTiled_v12000 encode = tensor_map_encoder();
+  if (encode == nullptr || box_inner != kSliceK) return false;
+  const cuuint64_t dims[2] = {inner, outer};
+  const cuuint64_t strides[1] = {inner * 2u};
+  const cuuint32_t box[2] = {box_inner, box_outer};
+  const cuuint32_t elem_strides[2] = {1, 1};
+  return encode(static_cast<CUtensorMap *>(map), CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<uint16_t *>(base), dims,
+                strides, box, elem_strides, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
 
 bool gemm_tc_eligible(const GemmParams &g) {
   return g.tokens >= 1 && g.tokens <= kGemmMaxTokens && g.cols % kSliceK == 0 && g.cols != 0 && g.rows != 0 &&
@@ -473,7 +539,8 @@ bool gemm_tc_eligible(const GemmParams &g) {
 }
 
 uint64_t gemm_tc_workspace_bytes(uint32_t tokens, uint32_t sm_count) {
-  return 2ull * sm_count * padded_tokens(tokens) * kTileRows * sizeof(float);
+  // two partial accumulators per thread block of the 2 x sm_count grid
+  return 2ull * (2ull * sm_count) * padded_tokens(tokens) * kTileRows * sizeof(float);
 }
 
 uint32_t gemm_tc_ticket_count(uint32_t rows) { return (rows + kTileRows - 1u) / kTileRows; }
@@ -483,13 +550,14 @@ cudaError_t configure_gemm_tc_kernel() {
 }
 
 cudaError_t launch_gemm_tc(cudaStream_t stream, const GemmParams &g, uint32_t sm_count) {
-  if (!gemm_tc_eligible(g) || g.workspace == nullptr || g.tickets == nullptr) return cudaErrorInvalidValue;
+  if (!gemm_tc_eligible(g) || g.workspace == nullptr) return cudaErrorInvalidValue;
   GemmKernelParams p{};
   p.rows = g.rows;
   p.cols = g.cols;
   p.tokens = g.tokens;
   p.n_pad = padded_tokens(g.tokens);
   p.stages = stages_for(p.n_pad);
+  p.tmem_columns = tmem_columns_for(p.n_pad);
   p.epilogue = g.epilogue;
   p.resid_in = g.resid_in;
   p.out_f32 = g.out_f32;
@@ -497,12 +565,22 @@ cudaError_t launch_gemm_tc(cudaStream_t stream, const GemmParams &g, uint32_t sm
   p.workspace = g.workspace;
   p.tickets = g.tickets;
   p.error_word = g.error_word;
+  p.stamps = g.stamps;
   CUtensorMap map_w, map_x;
   if (!make_map(&map_w, g.weight, g.cols, g.rows, kTileRows) || !make_map(&map_x, g.x, g.cols, g.tokens, p.n_pad))
     return cudaErrorNotSupported;
   const uint32_t blocks = gemm_blocks(g.rows, g.cols, sm_count);
-  return launch_with_pdl(gemm_tc_kernel, dim3(blocks), dim3(kGemmThreads), gemm_smem_bytes(p.n_pad, p.stages), stream,
-                         g.pdl != 0, map_w, map_x, p);
+  cudaError_t err = launch_with_pdl(gemm_tc_kernel, dim3(blocks), dim3(kGemmThreads), gemm_smem_bytes(p.n_pad, p.stages),
+                                    stream, g.pdl != 0, map_w, map_x, p);
+  if (err != cudaSuccess) return err;
+  // the fix-up launch follows only when some tile is shared between blocks (a block whose run
+  // begins inside a tile)
+  const Partition part = make_partition(g.rows, g.cols, blocks);
+  bool split = false;
+  for (uint32_t b = 0; b < blocks && !split; ++b) split = part.begin(b) % part.slices != 0;
+  if (!split) return cudaSuccess;
+  return launch_with_pdl(gemm_fixup_kernel, dim3(blocks, p.n_pad / kGroup), dim3(kEpilogueThreads), 0, stream, true, p,
+                         blocks);
 }
 
 }  // namespace nb

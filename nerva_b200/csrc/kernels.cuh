@@ -111,14 +111,21 @@ struct GemmParams {
   float *out_f32;          // [tokens][rows]
   uint16_t *out_bf16;      // [tokens][rows/2]
   float *workspace;        // gemm_tc_workspace_bytes(tokens, sm_count)
-  uint32_t *tickets;       // gemm_tc_ticket_count(rows) words, zero before the first launch (left zero)
+  uint32_t *tickets;       // unused (kept so that callers' buffer plans stay as they are)
   uint32_t *error_word;
   uint32_t pdl;
+  unsigned long long *stamps;  // optional kTimelineSlots stamps of the first and the last block: entry, first
+                               // tile ready for the MMA, last MMA committed, exit
 };
 bool gemm_tc_eligible(const GemmParams &g);
 uint64_t gemm_tc_workspace_bytes(uint32_t tokens, uint32_t sm_count);
 uint32_t gemm_tc_ticket_count(uint32_t rows);
-bool tensor_map_available();  // the driver exposes the tensor-map encoder the block kernel needs
+bool tensor_map_available();  // the driver exposes the tensor-map encoder the TMA kernels need
+// Encodes a CUtensorMap (128 bytes at `map`, 64-byte aligned) over a bf16 [outer][inner] row-major
+// tensor with boxes of box_inner x box_outer elements and the 128-byte swizzle (box_inner = 64);
+// elements outside the tensor read as zero.
+bool encode_bf16_map_2d(void *map, const uint16_t *base, uint64_t inner, uint64_t outer, uint32_t box_inner,
+                        uint32_t box_outer);
 cudaError_t configure_gemm_tc_kernel();
 cudaError_t launch_gemm_tc(cudaStream_t stream, const GemmParams &g, uint32_t sm_count);
 
@@ -221,6 +228,29 @@ uint32_t fused_attention_splits(uint32_t target_context);
 cudaError_t launch_fused_attention(cudaStream_t stream, const FusedAttentionParams &p);
 cudaError_t configure_fused_attention_kernel();
 
+// ---- DeepSeek multi-head latent attention of the session (mla_session.cu) ----
+struct MlaParams {
+  const uint32_t *cursor;  // position of the token being decoded
+  uint32_t max_context;
+  float *qkv;              // fused projection output: [heads][nope + rope] queries, then [rank + rope]; the
+                           // rotary parts of the queries are rotated in place
+  const uint16_t *w_kv_b;  // [heads][nope + v_dim][rank]: per head W_UK rows, then W_UV rows
+  const uint16_t *kv_a_norm;  // [rank]
+  uint16_t *cache;         // this layer's cache rows [pages][16][rank + rope] bf16
+  const uint32_t *page_table;
+  uint32_t page_count;
+  uint32_t heads, rank, nope, rope, v_dim;
+  float eps, rope_theta;
+  float *ql;               // scratch [heads][rank]
+  float *partial_acc, *partial_m, *partial_l;  // [heads][splits][rank], [heads][splits]
+  uint16_t *out_bf16;      // [heads * v_dim]
+  uint32_t *error_word;
+};
+bool mla_session_supported(uint32_t heads, uint32_t rank, uint32_t nope, uint32_t rope, uint32_t v_dim);
+uint32_t mla_attention_splits(uint32_t target_context);
+// Three launches: prepare (rotary, absorbed queries, cache append), split attention, merge + value projection.
+cudaError_t launch_mla_attention(cudaStream_t stream, const MlaParams &p, uint32_t splits, bool pdl);
+
 // ---- softmax top-k sparse MoE MLP (moe.cu) ----
 struct MoeRouteParams {
   const float *logits;   // [num_experts] router logits of this token
@@ -234,9 +264,13 @@ struct MoeExpertParams {
   const uint16_t *add_bias, *norm_weight;
   float eps;
   uint32_t hidden, moe_intermediate, shared_intermediate, top_k;
-  const uint16_t *w_expert_gate_up;  // [E][2 * moe_intermediate][hidden]: gate rows, then up rows
+  const uint16_t *w_expert_gate_up;  // expert e's gate matrix at e * expert_stride, its up matrix expert_up_offset
+                                     // further: [E][2 * mi][hidden] (stride 2 mi hidden, offset mi hidden), or all
+                                     // gate matrices then all up matrices (stride mi hidden, offset E mi hidden)
+  uint64_t expert_stride, expert_up_offset;
   const uint16_t *w_expert_down;     // [E][hidden][moe_intermediate]
-  const uint16_t *w_shared_gate, *w_shared_up, *w_shared_down, *w_shared_router;  // shared expert, optional
+  const uint16_t *w_shared_gate, *w_shared_up, *w_shared_down;  // shared expert, optional
+  const uint16_t *w_shared_router;   // its gate sigmoid(router . x); null: always on (scale 1)
   const uint32_t *expert_ids;        // [top_k] from the route kernel
   const float *route_weights;        // [top_k]
   float *gate_up_out;                // scratch: per expert gate then up rows (+ the shared expert's), fp32

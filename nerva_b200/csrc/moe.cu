@@ -203,7 +203,8 @@ __global__ void __launch_bounds__(kStreamThreads, 1) moe_expert_kernel(MoeExpert
         d.weight = (j & 1u) == 0 ? p.w_shared_gate : p.w_shared_up;
       } else {
         d.rows = p.moe_intermediate;
-        d.weight = p.w_expert_gate_up + static_cast<uint64_t>(sh.ids[r]) * 2u * mi * h + ((j & 1u) != 0 ? mi * h : 0u);
+        d.weight = p.w_expert_gate_up + static_cast<uint64_t>(sh.ids[r]) * p.expert_stride +
+                   ((j & 1u) != 0 ? p.expert_up_offset : 0u);
       }
     } else {
       d.rows = p.hidden;
@@ -229,11 +230,12 @@ __global__ void __launch_bounds__(kStreamThreads, 1) moe_expert_kernel(MoeExpert
   if (PHASE == kGateUp) {
     add_norm_to_smem_f32(x, p.add_a, p.add_b, p.add_bias, p.norm_weight, p.eps, p.hidden, sh.scratch);
     if (blockIdx.x == 0 && p.shared_intermediate != 0) {
-      // gate of the shared expert: sigmoid(shared_router . x)
+      // gate of the shared expert: sigmoid(shared_router . x), or 1 for shared experts that are always on
       float dot = 0.0f;
-      for (uint32_t i = threadIdx.x; i < p.hidden; i += blockDim.x) dot += bf16_bits_to_f32(p.w_shared_router[i]) * x[i];
+      for (uint32_t i = threadIdx.x; p.w_shared_router != nullptr && i < p.hidden; i += blockDim.x)
+        dot += bf16_bits_to_f32(p.w_shared_router[i]) * x[i];
       const float total = block_sum(dot, sh.scratch);
-      if (threadIdx.x == 0) *p.shared_gate = 1.0f / (1.0f + expf(-total));
+      if (threadIdx.x == 0) *p.shared_gate = p.w_shared_router != nullptr ? 1.0f / (1.0f + expf(-total)) : 1.0f;
     }
   } else if (p.shared_intermediate != 0 && threadIdx.x == 0) {
     sh.weights[p.top_k] = __ldcg(p.shared_gate);

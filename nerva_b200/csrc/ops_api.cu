@@ -2,6 +2,8 @@
 // entry point), isolated GQA decode attention, greedy arg-max, and the host
 // synthetic-checkpoint generator.  Host pointers in, host pointers out.
 #include <math.h>
+#include <stdio.h>
+#include <stdlib.h>
 #include <string.h>
 
 #include <string>
@@ -216,9 +218,20 @@ extern "C" int nerva_b200_projection_sustained(const uint16_t *weight, const uin
     p.pdl = 1;
     return launch_projection(stream, p, sms);
   };
+  // NERVA_B200_GEMM_TIMELINE=1 (tuning aid): kernel-written %globaltimer stamps of two consecutive
+  // block launches in the middle of the run go to stderr, in nanoseconds after the first stamp.
+  const char *timeline_env = getenv("NERVA_B200_GEMM_TIMELINE");
+  unsigned long long *d_stamps = nullptr;
+  if (block && timeline_env != nullptr && timeline_env[0] == '1' && err == cudaSuccess) {
+    err = buf.alloc(&d_stamps, uint64_t{2} * kTimelineSlots);
+    if (err == cudaSuccess) err = cudaMemset(d_stamps, 0, 2 * kTimelineSlots * sizeof(unsigned long long));
+  }
   for (uint32_t i = 0; err == cudaSuccess && i < warmup; ++i) err = launch(i);
   if (err == cudaSuccess) err = cudaEventRecord(t.a, stream);
-  for (uint32_t i = 0; err == cudaSuccess && i < iterations; ++i) err = launch(warmup + i);
+  for (uint32_t i = 0; err == cudaSuccess && i < iterations; ++i) {
+    if (d_stamps != nullptr) g.stamps = i == iterations / 2 ? d_stamps : (i == iterations / 2 + 1 ? d_stamps + kTimelineSlots : nullptr);
+    err = launch(warmup + i);
+  }
   if (err == cudaSuccess) err = cudaEventRecord(t.b, stream);
   if (err == cudaSuccess) err = cudaEventSynchronize(t.b);
   float ms = 0.0f;
@@ -226,6 +239,17 @@ extern "C" int nerva_b200_projection_sustained(const uint16_t *weight, const uin
   if (err == cudaSuccess) err = cudaMemcpy(y, d_y, static_cast<uint64_t>(tokens) * rows * 4u, cudaMemcpyDeviceToHost);
   uint32_t device_error = 0;
   if (err == cudaSuccess) err = cudaMemcpy(&device_error, d_error, sizeof(uint32_t), cudaMemcpyDeviceToHost);
+  if (err == cudaSuccess && d_stamps != nullptr) {
+    unsigned long long h[2 * kTimelineSlots] = {};
+    err = cudaMemcpy(h, d_stamps, sizeof(h), cudaMemcpyDeviceToHost);
+    const char *names[4] = {"entry", "first_tile_ready", "last_mma_committed", "exit"};
+    for (uint32_t launch_index = 0; launch_index < 2; ++launch_index)
+      for (uint32_t which = 0; which < 2; ++which)
+        for (uint32_t k = 0; k < 4; ++k)
+          fprintf(stderr, "gemm timeline rows=%u cols=%u tokens=%u launch %u %s block %s: %lld ns\n", rows, cols, tokens,
+                  launch_index, which == 0 ? "first" : "last", names[k],
+                  static_cast<long long>(h[launch_index * kTimelineSlots + which * 4 + k]) - static_cast<long long>(h[0]));
+  }
   if (stream != nullptr) cudaStreamDestroy(stream);
   if (err != cudaSuccess) {
     set_last_error(cudaGetErrorString(err));
@@ -471,6 +495,96 @@ extern "C" int nerva_cuda_projection_bench(const NervaCudaProjectionBenchRequest
   }
   out->status = out->mismatch_count == 0 ? 0 : -1;
   return out->status;
+}
+
+// Sustained form: `copies` device copies of the K and V pages (the caches of `copies` layers,
+// together larger than the L2) are attended over one after the other, back to back on one stream,
+// as the attention launches of the layers of a decode step follow each other.  avg_ns: time per
+// launch pair (attention + merge) over `iterations` after `warmup`; out: the last launch's output.
+extern "C" int nerva_b200_gqa_decode_attention_sustained(const float *q, const uint16_t *key_pages,
+                                                         const uint16_t *value_pages, const uint32_t *page_table,
+                                                         float *out, uint32_t batch, uint32_t context, uint32_t heads,
+                                                         uint32_t kv_heads, uint32_t head_dim, uint32_t copies,
+                                                         uint32_t warmup, uint32_t iterations, uint64_t *avg_ns) {
+  set_last_error("");
+  if (q == nullptr || key_pages == nullptr || value_pages == nullptr || page_table == nullptr || out == nullptr ||
+      batch == 0 || context == 0 || heads == 0 || kv_heads == 0 || heads % kv_heads != 0 || head_dim == 0 ||
+      head_dim > 256 || copies == 0 || iterations == 0)
+    return -1;
+  uint32_t sms = 0;
+  cudaError_t err = device_sm_count(&sms, nullptr, nullptr, nullptr);
+  if (err == cudaSuccess) err = configure_attention_kernels();
+  const uint32_t pages = (context + NERVA_KV_CACHE_BLOCK_TOKENS - 1) / NERVA_KV_CACHE_BLOCK_TOKENS;
+  const uint64_t kv_hidden = static_cast<uint64_t>(kv_heads) * head_dim;
+  const uint64_t kv_elems = static_cast<uint64_t>(batch) * pages * NERVA_KV_CACHE_BLOCK_TOKENS * kv_hidden;
+  const uint64_t q_elems = static_cast<uint64_t>(batch) * heads * head_dim;
+  const uint32_t splits = attention_default_splits(context, batch, kv_heads, sms);
+  DeviceBuffers buf;
+  Timing t;
+  float *d_q = nullptr, *d_out = nullptr, *d_acc = nullptr, *d_m = nullptr, *d_l = nullptr;
+  std::vector<uint16_t *> d_k(copies, nullptr), d_v(copies, nullptr);
+  uint32_t *d_table = nullptr, *d_err = nullptr;
+  if (err == cudaSuccess) err = buf.alloc(&d_q, q_elems);
+  if (err == cudaSuccess) err = buf.alloc(&d_out, q_elems);
+  for (uint32_t c = 0; err == cudaSuccess && c < copies; ++c) {
+    err = buf.alloc(&d_k[c], kv_elems);
+    if (err == cudaSuccess) err = buf.alloc(&d_v[c], kv_elems);
+    if (err == cudaSuccess) err = cudaMemcpy(d_k[c], key_pages, kv_elems * 2u, cudaMemcpyHostToDevice);
+    if (err == cudaSuccess) err = cudaMemcpy(d_v[c], value_pages, kv_elems * 2u, cudaMemcpyHostToDevice);
+  }
+  if (err == cudaSuccess) err = buf.alloc(&d_table, static_cast<uint64_t>(batch) * pages);
+  if (err == cudaSuccess) err = buf.alloc(&d_acc, q_elems * splits);
+  if (err == cudaSuccess) err = buf.alloc(&d_m, static_cast<uint64_t>(batch) * heads * splits);
+  if (err == cudaSuccess) err = buf.alloc(&d_l, static_cast<uint64_t>(batch) * heads * splits);
+  if (err == cudaSuccess) err = buf.alloc(&d_err, uint64_t{1});
+  if (err == cudaSuccess) err = t.init();
+  if (err == cudaSuccess) err = cudaMemset(d_err, 0, 4);
+  if (err == cudaSuccess) err = cudaMemcpy(d_q, q, q_elems * 4u, cudaMemcpyHostToDevice);
+  if (err == cudaSuccess)
+    err = cudaMemcpy(d_table, page_table, static_cast<uint64_t>(batch) * pages * 4u, cudaMemcpyHostToDevice);
+  cudaStream_t stream = nullptr;
+  if (err == cudaSuccess) err = cudaStreamCreateWithFlags(&stream, cudaStreamNonBlocking);
+  AttentionParams p{};
+  p.q = d_q;
+  p.page_table = d_table;
+  p.batch = batch;
+  p.heads = heads;
+  p.kv_heads = kv_heads;
+  p.head_dim = head_dim;
+  p.page_count = pages;
+  p.context = context;
+  p.splits = splits;
+  p.partial_acc = d_acc;
+  p.partial_m = d_m;
+  p.partial_l = d_l;
+  p.out_f32 = d_out;
+  p.error_word = d_err;
+  auto launch = [&](uint32_t i) {
+    p.key_pages = d_k[i % copies];
+    p.value_pages = d_v[i % copies];
+    return launch_attention(stream, p);
+  };
+  for (uint32_t i = 0; err == cudaSuccess && i < warmup; ++i) err = launch(i);
+  if (err == cudaSuccess) err = cudaEventRecord(t.a, stream);
+  for (uint32_t i = 0; err == cudaSuccess && i < iterations; ++i) err = launch(warmup + i);
+  if (err == cudaSuccess) err = cudaEventRecord(t.b, stream);
+  if (err == cudaSuccess) err = cudaEventSynchronize(t.b);
+  float ms = 0.0f;
+  if (err == cudaSuccess) err = cudaEventElapsedTime(&ms, t.a, t.b);
+  uint32_t device_error = 0;
+  if (err == cudaSuccess) err = cudaMemcpy(&device_error, d_err, 4, cudaMemcpyDeviceToHost);
+  if (err == cudaSuccess) err = cudaMemcpy(out, d_out, q_elems * 4u, cudaMemcpyDeviceToHost);
+  if (stream != nullptr) cudaStreamDestroy(stream);
+  if (err != cudaSuccess) {
+    set_last_error(cudaGetErrorString(err));
+    return -1;
+  }
+  if (device_error != 0) {
+    set_last_error("attention kernel reported device error code " + std::to_string(device_error));
+    return -1;
+  }
+  if (avg_ns != nullptr) *avg_ns = static_cast<uint64_t>(static_cast<double>(ms) * 1.0e6 / iterations);
+  return 0;
 }
 
 extern "C" int nerva_b200_gqa_decode_attention(const float *q, const uint16_t *key_pages,

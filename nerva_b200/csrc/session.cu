@@ -60,7 +60,7 @@ bool valid_layer(const NervaCudaHfDecodeChainLayer &layer, bool require_sources)
     return false;
   if (!require_sources) return true;
   if (layer.rms_attn_weight == nullptr || layer.rms_mlp_weight == nullptr) return false;
-  if (layer.attention_kind != NERVA_ATTENTION_KIND_FULL) return false;
+  if (layer.attention_kind != NERVA_ATTENTION_KIND_FULL) return false;  // latent-attention tensors only come by descriptor
   if (layer.w_q == nullptr || layer.w_k == nullptr || layer.w_v == nullptr || layer.w_o == nullptr)
     return false;
   if (dense) return layer.w_gate != nullptr && layer.w_up != nullptr && layer.w_down != nullptr;
@@ -77,8 +77,19 @@ bool valid_layer(const NervaCudaHfDecodeChainLayer &layer, bool require_sources)
 // What this library's kernels run: full attention, no query gate, dense SwiGLU or
 // softmax top-k sparse MoE (whose shape limits are checked once the device is known).
 bool layer_supported(const NervaCudaHfDecodeChainLayer &layer) {
-  return layer.attention_kind == NERVA_ATTENTION_KIND_FULL && layer.w_q_gate == nullptr &&
-         (layer.mlp_kind == NERVA_MLP_KIND_DENSE || layer.mlp_kind == NERVA_MLP_KIND_SPARSE_MOE);
+  const bool mlp_ok = layer.mlp_kind == NERVA_MLP_KIND_DENSE || layer.mlp_kind == NERVA_MLP_KIND_SPARSE_MOE;
+  if (layer.attention_kind == NERVA_ATTENTION_KIND_FULL) return layer.w_q_gate == nullptr && mlp_ok;
+  if (layer.attention_kind != NERVA_ATTENTION_KIND_DEEPSEEK_MLA) return false;
+  // Latent attention in its plain bf16 form: no query low-rank stage, no indexer, compressor,
+  // hyper-connection, FP8 storage or rotary scaling (the DeepSeek-V2-Lite shape).  The reference's
+  // own session runs the V3 form with a query low-rank stage and grouped-sigmoid routing; this
+  // degenerate form is an extension the reference rejects (session_decode_v3_projection.inc.cu:30-33).
+  return mlp_ok && layer.deepseek_q_lora_rank == 0 && layer.deepseek_storage == 1u && layer.deepseek_flags == 0 &&
+         layer.deepseek_hc_mult == 0 && layer.deepseek_o_lora_rank == 0 && layer.deepseek_compress_ratio <= 1 &&
+         layer.deepseek_rope_scaling_type == 0 && layer.deepseek_kv_lora_rank % 32u == 0 &&
+         layer.deepseek_kv_lora_rank <= 512u && layer.deepseek_qk_rope_head_dim % 2u == 0 &&
+         layer.deepseek_qk_rope_head_dim <= 64u && layer.deepseek_qk_nope_head_dim != 0 &&
+         layer.deepseek_qk_nope_head_dim <= 256u && layer.deepseek_v_head_dim != 0;
 }
 
 static bool sampler_valid(const NervaCudaHfDecodeSamplerConfig &s) {
@@ -119,6 +130,43 @@ ArenaLayout compute_arena_layout(const ModelDims &d, const NervaCudaHfDecodeChai
     l.num_experts = layer.num_experts;
     l.top_k = layer.experts_per_token;
     l.norm_topk_prob = layer.norm_topk_prob == 0 ? 0u : 1u;
+    l.attention_kind = layer.attention_kind;
+    if (layer.attention_kind == NERVA_ATTENTION_KIND_DEEPSEEK_MLA) {
+      // hf_decode_sequence/deepseek/weights_pack.inc.cu:156-186,261-322 (bf16 storage), with the query
+      // projection in the w_q slot because there is no low-rank stage in front of it
+      const uint64_t rank = layer.deepseek_kv_lora_rank, nope = layer.deepseek_qk_nope_head_dim;
+      const uint64_t rope = layer.deepseek_qk_rope_head_dim, vdim = layer.deepseek_v_head_dim;
+      const uint64_t heads = d.heads;
+      l.kv_lora_rank = static_cast<uint32_t>(rank);
+      l.qk_nope = static_cast<uint32_t>(nope);
+      l.qk_rope = static_cast<uint32_t>(rope);
+      l.rms_attn = push(c, hidden);
+      l.w_q = push(c, heads * (nope + rope) * hidden);
+      l.w_k = push(c, (rank + rope) * hidden);
+      l.k_norm = push(c, rank);
+      l.w_v = push(c, heads * (nope + vdim) * rank);
+      l.w_o = push(c, hidden * heads * vdim);
+      l.rms_mlp = push(c, hidden);
+      if (layer.mlp_kind == NERVA_MLP_KIND_SPARSE_MOE) {
+        const uint64_t mi = layer.moe_intermediate, e = layer.num_experts, si = layer.shared_expert_intermediate;
+        l.w_router = push(c, e * hidden);
+        if (si != 0) {
+          l.w_shared_gate = push(c, si * hidden);
+          l.w_shared_up = push(c, si * hidden);
+          l.w_shared_down = push(c, hidden * si);
+        }
+        l.w_expert_gate_up = push(c, e * mi * hidden);  // every expert's gate matrix ...
+        push(c, e * mi * hidden);                       // ... then every expert's up matrix
+        l.w_expert_down = push(c, e * hidden * mi);
+        l.expert_stride = mi * hidden;
+        l.expert_up_offset = e * mi * hidden;
+      } else {
+        l.w_gate = push(c, inter * hidden);
+        l.w_up = push(c, inter * hidden);
+        l.w_down = push(c, hidden * inter);
+      }
+      continue;
+    }
     l.rms_attn = push(c, hidden);
     l.w_q = push(c, ah * hidden);
     l.w_q_gate = push_optional(c, ah * hidden, layer.w_q_gate);
@@ -134,6 +182,8 @@ ArenaLayout compute_arena_layout(const ModelDims &d, const NervaCudaHfDecodeChai
       l.w_router = push(c, e * hidden);
       l.w_expert_gate_up = push(c, e * mi * 2u * hidden);
       l.w_expert_down = push(c, e * hidden * mi);
+      l.expert_stride = 2u * mi * hidden;
+      l.expert_up_offset = mi * hidden;
       if (si != 0) {
         l.w_shared_gate = push(c, si * hidden);
         l.w_shared_up = push(c, si * hidden);
@@ -202,11 +252,13 @@ bool carve(StaticArena &arena, void *base, uint64_t count, T **out) {
 // Carves the shared weight block.  base == nullptr: sizing pass.
 bool plan_weights(Session *s, StaticArena &arena, void *base, SharedWeights *w) {
   const ModelDims &d = s->dims;
-  const uint64_t qkv_rows = d.attention_hidden() + 2 * d.kv_hidden();
+  const uint64_t qkv_rows = d.qkv_rows();
+  uint64_t dense_layers = 0;
+  for (int32_t ordinal : s->dense_ordinal) dense_layers += ordinal >= 0 ? 1u : 0u;
   uint16_t *arena_ptr = nullptr, *qkv = nullptr, *gu = nullptr;
   bool ok = carve(arena, base, s->layout.elements, &arena_ptr);
   ok = ok && carve(arena, base, static_cast<uint64_t>(d.layers) * qkv_rows * d.hidden, &qkv);
-  ok = ok && carve(arena, base, static_cast<uint64_t>(d.layers) * 2u * d.intermediate * d.hidden, &gu);
+  ok = ok && carve(arena, base, std::max<uint64_t>(dense_layers, 1u) * 2u * d.intermediate * d.hidden, &gu);
   if (ok && w != nullptr) {
     w->arena = arena_ptr;
     w->qkv_packed = qkv;
@@ -220,22 +272,25 @@ bool plan_state(Session *s, StaticArena &arena, void *base) {
   const ModelDims &d = s->dims;
   const uint64_t ah = d.attention_hidden(), kvh = d.kv_hidden();
   s->kv_pages = (s->max_context + NERVA_KV_CACHE_BLOCK_TOKENS - 1) / NERVA_KV_CACHE_BLOCK_TOKENS;
-  s->kv_layer_elems = static_cast<uint64_t>(s->kv_pages) * NERVA_KV_CACHE_BLOCK_TOKENS * kvh;
+  // latent attention caches one row of (rank + rope) values per token in the K array; the V array is not used
+  s->kv_layer_elems = static_cast<uint64_t>(s->kv_pages) * NERVA_KV_CACHE_BLOCK_TOKENS * d.kv_row();
   s->max_splits = attention_default_splits(s->max_context, 1, d.kv_heads, s->sm_count);
   const uint64_t max_x = std::max<uint64_t>(std::max<uint64_t>(d.hidden, d.intermediate), ah);
   bool ok = carve(arena, base, d.layers * s->kv_layer_elems, &s->kv_keys);
-  ok = ok && carve(arena, base, d.layers * s->kv_layer_elems, &s->kv_values);
+  ok = ok && carve(arena, base, d.mla() ? uint64_t{16} : d.layers * s->kv_layer_elems, &s->kv_values);
   ok = ok && carve(arena, base, static_cast<uint64_t>(s->kv_pages), &s->page_table);
   ok = ok && carve(arena, base, static_cast<uint64_t>(d.hidden), &s->h_a);
   ok = ok && carve(arena, base, static_cast<uint64_t>(d.hidden), &s->h_b);
-  ok = ok && carve(arena, base, ah + 2 * kvh, &s->qkv);
+  ok = ok && carve(arena, base, std::max<uint64_t>(ah + 2 * kvh, d.qkv_rows()), &s->qkv);
+  ok = ok && carve(arena, base, std::max<uint64_t>(static_cast<uint64_t>(d.heads) * d.mla_rank, 4u), &s->mla_ql);
   ok = ok && carve(arena, base, static_cast<uint64_t>(d.hidden), &s->o_out);
   ok = ok && carve(arena, base, static_cast<uint64_t>(d.hidden), &s->down);
   ok = ok && carve(arena, base, static_cast<uint64_t>(d.vocab), &s->logits);
   const uint64_t split_slots = std::max<uint32_t>(s->max_splits, 16u);  // fused attention uses up to 16
   ok = ok && carve(arena, base, static_cast<uint64_t>(d.heads), &s->attn_tickets);
   s->x_elems = static_cast<uint32_t>(max_x);
-  ok = ok && carve(arena, base, static_cast<uint64_t>(d.heads) * split_slots * d.head_dim, &s->partial_acc);
+  ok = ok && carve(arena, base, static_cast<uint64_t>(d.heads) * split_slots * std::max(d.head_dim, d.mla_rank),
+                   &s->partial_acc);
   ok = ok && carve(arena, base, static_cast<uint64_t>(d.heads) * split_slots, &s->partial_m);
   ok = ok && carve(arena, base, static_cast<uint64_t>(d.heads) * split_slots, &s->partial_l);
   ok = ok && carve(arena, base, static_cast<uint64_t>(d.layers), &s->step_layers);
@@ -356,12 +411,12 @@ const uint16_t *arena_at(Session *s, uint64_t offset) {
 // and the projection job list (QKV, O, gate/up, down per layer, then lm_head).
 cudaError_t setup_step_kernel(Session *s) {
   const ModelDims &d = s->dims;
-  const uint32_t qkv_rows32 = static_cast<uint32_t>(d.attention_hidden() + 2 * d.kv_hidden());
+  const uint32_t qkv_rows32 = static_cast<uint32_t>(d.qkv_rows());
   s->row_elems = std::max(std::max(max_rows_per_block(qkv_rows32, 1, s->sm_count),
                                    max_rows_per_block(2u * d.intermediate, 2, s->sm_count)),
                           std::max(max_rows_per_block(d.hidden, 1, s->sm_count),
                                    max_rows_per_block(d.vocab, 1, s->sm_count)));
-  s->step_kernel_ok = !s->has_moe && step_kernel_supported(d.hidden, d.heads, d.kv_heads, d.head_dim,
+  s->step_kernel_ok = !s->has_moe && !d.mla() && step_kernel_supported(d.hidden, d.heads, d.kv_heads, d.head_dim,
                                                            d.intermediate, s->x_elems, s->row_elems);
   if (!s->step_kernel_ok) return cudaSuccess;
   cudaError_t err = configure_step_kernel();
@@ -370,7 +425,7 @@ cudaError_t setup_step_kernel(Session *s) {
   s->phase_profile = profile != nullptr && profile[0] == '1';
   err = cudaMemsetAsync(s->phase_cycles, 0, kPhaseCount * sizeof(unsigned long long), s->stream);
   if (err != cudaSuccess) return err;
-  const uint64_t ah = d.attention_hidden(), kvh = d.kv_hidden(), qkv_rows = ah + 2 * kvh;
+  const uint64_t ah = d.attention_hidden(), qkv_rows = d.qkv_rows();
   std::vector<StepLayerDev> layers(d.layers);
   std::vector<JobDesc> jobs(static_cast<size_t>(d.layers) * 4u + 1u);
   for (uint32_t l = 0; l < d.layers; ++l) {
@@ -389,7 +444,7 @@ cudaError_t setup_step_kernel(Session *s) {
     jobs[4 * l + 0] = JobDesc{s->weights->qkv_packed + static_cast<uint64_t>(l) * qkv_rows * d.hidden,
                               static_cast<uint32_t>(qkv_rows), d.hidden, 1, 0};
     jobs[4 * l + 1] = JobDesc{arena_at(s, L.w_o), d.hidden, static_cast<uint32_t>(ah), 1, 0};
-    jobs[4 * l + 2] = JobDesc{s->weights->gate_up_packed + static_cast<uint64_t>(l) * 2u * d.intermediate * d.hidden,
+    jobs[4 * l + 2] = JobDesc{s->weights->gate_up_packed + gate_up_packed_offset(s, l),
                               2u * d.intermediate, d.hidden, 2, 0};
     jobs[4 * l + 3] = JobDesc{arena_at(s, L.w_down), d.hidden, d.intermediate, 1, 0};
   }
@@ -484,8 +539,8 @@ cudaError_t enqueue_step(Session *s, uint32_t splits, uint32_t sample, uint64_t 
                          StepProfile *prof = nullptr, bool head_only = false) {
   const ModelDims &d = s->dims;
   const StepState st = step_state(s);
-  const uint64_t ah = d.attention_hidden(), kvh = d.kv_hidden();
-  const uint64_t qkv_rows = ah + 2 * kvh;
+  const uint64_t ah = d.attention_hidden();
+  const uint64_t qkv_rows = d.qkv_rows();
   uint64_t n = 0;
   // tensor parallel: where the partial sums of O and down travel (see kernels.cuh: TpPush)
   const bool tp = s->tp_world > 1;
@@ -559,6 +614,36 @@ cudaError_t enqueue_step(Session *s, uint32_t splits, uint32_t sample, uint64_t 
     profile_mark(s, prof, kBucketQkv);
     if (err != cudaSuccess) break;
 
+    if (d.mla()) {
+      // latent attention: rotary + absorbed queries + cache append, split attention over the latent
+      // cache, merge + value projection
+      MlaParams mp{};
+      mp.cursor = s->device_cursor;
+      mp.max_context = s->max_context;
+      mp.qkv = s->qkv;
+      mp.w_kv_b = arena_at(s, L.w_v);
+      mp.kv_a_norm = arena_at(s, L.k_norm);
+      mp.cache = s->kv_keys + l * s->kv_layer_elems;
+      mp.page_table = s->page_table;
+      mp.page_count = s->kv_pages;
+      mp.heads = d.heads;
+      mp.rank = d.mla_rank;
+      mp.nope = d.mla_nope;
+      mp.rope = d.mla_rope;
+      mp.v_dim = d.head_dim;
+      mp.eps = s->rms_eps;
+      mp.rope_theta = s->rope_theta;
+      mp.ql = s->mla_ql;
+      mp.partial_acc = s->partial_acc;
+      mp.partial_m = s->partial_m;
+      mp.partial_l = s->partial_l;
+      mp.out_bf16 = s->attn_bf16;
+      mp.error_word = s->device_error;
+      err = launch_mla_attention(s->stream, mp, splits, s->use_pdl);
+      n += 3;
+      profile_mark(s, prof, kBucketAttention);
+      if (err != cudaSuccess) break;
+    } else {
     QkvPrepareParams qp{};
     qp.qkv = s->qkv;
     qp.q_bias = arena_at(s, L.q_bias);
@@ -635,6 +720,7 @@ cudaError_t enqueue_step(Session *s, uint32_t splits, uint32_t sample, uint64_t 
     profile_mark(s, prof, kBucketAttention);
     if (err != cudaSuccess) break;
     }
+    }
 
     // O
     p = ProjectionParams{};
@@ -702,6 +788,8 @@ cudaError_t enqueue_step(Session *s, uint32_t splits, uint32_t sample, uint64_t 
       ep.shared_intermediate = L.shared_intermediate;
       ep.top_k = L.top_k;
       ep.w_expert_gate_up = arena_at(s, L.w_expert_gate_up);
+      ep.expert_stride = L.expert_stride;
+      ep.expert_up_offset = L.expert_up_offset;
       ep.w_expert_down = arena_at(s, L.w_expert_down);
       ep.w_shared_gate = arena_at(s, L.w_shared_gate);
       ep.w_shared_up = arena_at(s, L.w_shared_up);
@@ -724,7 +812,7 @@ cudaError_t enqueue_step(Session *s, uint32_t splits, uint32_t sample, uint64_t 
     p.error_word = s->device_error;
     p.pdl = s->use_pdl ? 1u : 0u;
     p.eps = s->rms_eps;
-    p.weight = s->weights->gate_up_packed + static_cast<uint64_t>(l) * 2u * d.intermediate * d.hidden;
+    p.weight = s->weights->gate_up_packed + gate_up_packed_offset(s, l);
     p.rows = 2u * d.intermediate;
     p.cols = d.hidden;
     p.prologue = kPrologueAddNorm;
@@ -904,6 +992,7 @@ bool peer_failure_seen(Session *s, uint32_t step) {
 
 uint32_t splits_for(Session *s, uint32_t target_context) {
   if (s->engine == 1) return step_kernel_splits(target_context);
+  if (s->dims.mla()) return mla_attention_splits(target_context);
   if (s->fused_attention) return fused_attention_splits(target_context);
   uint32_t want = attention_default_splits(target_context, 1, s->dims.kv_heads, s->sm_count);
   uint32_t bucket = 1;
@@ -937,7 +1026,7 @@ void fill_header(const Session *s, NervaCudaHfDecodeSequenceResult *out, uint32_
 }
 
 uint64_t resident_kv_bytes(const Session *s) {
-  return 2ull * s->dims.layers * s->kv_layer_elems * sizeof(uint16_t);
+  return (s->dims.mla() ? 1ull : 2ull) * s->dims.layers * s->kv_layer_elems * sizeof(uint16_t);
 }
 uint64_t device_footprint(const Session *s) {
   return s->state_bytes + (s->weights ? s->weights->block_bytes : 0);
@@ -1298,8 +1387,8 @@ cudaError_t allocate_state(Session *s, int32_t *stage) {
   // KV pages come out of the pool in FIFO order, which makes the initial
   // logical->physical table the identity, as the reference initialises it
   // (hf_decode_sequence/kernels.cu:732-739).
-  StaticArena page_space(2ull * s->dims.layers * s->kv_layer_elems * 2u);
-  const uint64_t page_bytes = NERVA_KV_CACHE_BLOCK_TOKENS * s->dims.kv_hidden() * 2u;
+  StaticArena page_space(2ull * s->dims.layers * s->kv_layer_elems * 2u + 64u);
+  const uint64_t page_bytes = NERVA_KV_CACHE_BLOCK_TOKENS * s->dims.kv_row() * 2u;
   if (!s->kv_pool.preallocate(page_space, s->kv_pages, NERVA_KV_CACHE_BLOCK_TOKENS, page_bytes, 16))
     return cudaErrorMemoryAllocation;
   std::vector<uint32_t> table(s->kv_pages);
@@ -1314,7 +1403,7 @@ cudaError_t allocate_state(Session *s, int32_t *stage) {
   if (err == cudaSuccess) err = cudaMemsetAsync(s->device_cursor, 0, sizeof(uint32_t), s->stream);
   if (err == cudaSuccess)
     err = cudaMemsetAsync(s->attn_tickets, 0, s->dims.heads * sizeof(uint32_t), s->stream);
-  s->fused_attention = fused_attention_supported(s->dims.heads, s->dims.kv_heads, s->dims.head_dim);
+  s->fused_attention = !s->dims.mla() && fused_attention_supported(s->dims.heads, s->dims.kv_heads, s->dims.head_dim);
   const char *timeline_env = getenv("NERVA_B200_TIMELINE");
   s->timeline_on = timeline_env != nullptr && timeline_env[0] == '1';
   if (err == cudaSuccess)
@@ -1401,6 +1490,28 @@ static int create_session(const NervaCudaHfDecodeSequenceSessionCreateRequest *r
     d.embed_vocab = shard->full_vocab;
     d.vocab_offset = shard->vocab_offset;
   }
+  // Latent attention: every layer or none, one shape, value width = head_dim; its tensors have no
+  // pointer fields in the layer struct, so they come through planned descriptors.
+  uint32_t mla_layers = 0;
+  for (uint32_t i = 0; i < request->layer_count; ++i) {
+    const NervaCudaHfDecodeChainLayer &layer = request->layers[i];
+    if (layer.attention_kind != NERVA_ATTENTION_KIND_DEEPSEEK_MLA) continue;
+    mla_layers += 1;
+    if (mla_layers == 1) {
+      d.mla_rank = layer.deepseek_kv_lora_rank;
+      d.mla_nope = layer.deepseek_qk_nope_head_dim;
+      d.mla_rope = layer.deepseek_qk_rope_head_dim;
+    }
+    if (layer.deepseek_kv_lora_rank != d.mla_rank || layer.deepseek_qk_nope_head_dim != d.mla_nope ||
+        layer.deepseek_qk_rope_head_dim != d.mla_rope || layer.deepseek_v_head_dim != d.head_dim || !declared_plan) {
+      out->failure_stage = kStageInvalidRequest;
+      return -1;
+    }
+  }
+  if (mla_layers != 0 && (mla_layers != request->layer_count || shard != nullptr)) {
+    out->failure_stage = kStageInvalidRequest;
+    return -1;
+  }
   ArenaLayout layout = compute_arena_layout(d, request->layers);
   const uint64_t resident_weight_bytes = layout.elements * 2u - static_cast<uint64_t>(d.hidden) * 4u;
   out->resident_weight_bytes = resident_weight_bytes;
@@ -1429,7 +1540,8 @@ static int create_session(const NervaCudaHfDecodeSequenceSessionCreateRequest *r
   if (!supported) {
     out->cuda_error = static_cast<int32_t>(cudaErrorNotSupported);
     out->failure_stage = kStageInvalidRequest;
-    set_last_error("model not supported: needs bf16, full attention, dense SwiGLU, head_dim <= 256");
+    set_last_error("model not supported: needs bf16, full attention or plain bf16 latent attention without a "
+                   "query low-rank stage, dense SwiGLU or softmax top-k sparse MoE, head_dim <= 256");
     return -1;
   }
 
@@ -1455,6 +1567,9 @@ static int create_session(const NervaCudaHfDecodeSequenceSessionCreateRequest *r
   s->planned_weight_descriptor_count = request->planned_weight_descriptor_count;
   s->planned_weight_descriptor_hash = declared_plan ? request->planned_weight_descriptor_hash : 0;
   s->layer_meta.assign(request->layers, request->layers + request->layer_count);
+  int32_t dense_count = 0;
+  for (const LayerLayout &L : s->layout.layers)
+    s->dense_ordinal.push_back(L.mlp_kind == NERVA_MLP_KIND_DENSE ? dense_count++ : -1);
   if (shard != nullptr) {
     s->tp_world = shard->world;
     s->tp_rank = shard->rank;
@@ -1473,6 +1588,11 @@ static int create_session(const NervaCudaHfDecodeSequenceSessionCreateRequest *r
   if (err == cudaSuccess) err = configure_fused_attention_kernel();
   if (err == cudaSuccess) err = configure_moe_kernels();
   if (err != cudaSuccess) return create_fail(s, out, err, kStageSetDevice);
+  if (d.mla() && !mla_session_supported(d.heads, d.mla_rank, d.mla_nope, d.mla_rope, d.head_dim)) {
+    set_last_error("latent attention shape not supported: needs at most 16 heads, latent rank 128, 256 or 512, "
+                   "rotary width a multiple of 8 up to 64");
+    return create_fail(s, out, cudaErrorNotSupported, kStageInvalidRequest);
+  }
   for (const LayerLayout &L : s->layout.layers) {
     if (L.mlp_kind != NERVA_MLP_KIND_SPARSE_MOE) continue;
     s->has_moe = true;
@@ -1513,16 +1633,24 @@ static int create_session(const NervaCudaHfDecodeSequenceSessionCreateRequest *r
   if (err != cudaSuccess) return create_fail(s, out, err, kStageDescriptorCopy);
   // packed replicas
   const uint64_t ah = d.attention_hidden(), kvh = d.kv_hidden();
-  const uint64_t qkv_rows = ah + 2 * kvh;
+  const uint64_t qkv_rows = d.qkv_rows();
   for (uint32_t l = 0; err == cudaSuccess && l < d.layers; ++l) {
     const LayerLayout &L = s->layout.layers[l];
-    err = launch_pack_qkv(s->stream, arena_at(s, L.w_q), arena_at(s, L.w_k), arena_at(s, L.w_v),
-                          s->weights->qkv_packed + l * qkv_rows * d.hidden, ah * d.hidden,
-                          kvh * d.hidden);
+    uint16_t *packed = s->weights->qkv_packed + l * qkv_rows * d.hidden;
+    if (d.mla()) {
+      // [query projection; latent + rotary-key projection]: one launch streams both
+      err = cudaMemcpyAsync(packed, arena_at(s, L.w_q), d.mla_q_rows() * d.hidden * 2u, cudaMemcpyDeviceToDevice,
+                            s->stream);
+      if (err == cudaSuccess)
+        err = cudaMemcpyAsync(packed + d.mla_q_rows() * d.hidden, arena_at(s, L.w_k), d.mla_width() * d.hidden * 2u,
+                              cudaMemcpyDeviceToDevice, s->stream);
+    } else {
+      err = launch_pack_qkv(s->stream, arena_at(s, L.w_q), arena_at(s, L.w_k), arena_at(s, L.w_v), packed,
+                            ah * d.hidden, kvh * d.hidden);
+    }
     if (err == cudaSuccess && L.mlp_kind == NERVA_MLP_KIND_DENSE)
       err = launch_pack_gate_up(s->stream, arena_at(s, L.w_gate), arena_at(s, L.w_up),
-                                s->weights->gate_up_packed + static_cast<uint64_t>(l) * 2u * d.intermediate * d.hidden,
-                                d.intermediate, d.hidden);
+                                s->weights->gate_up_packed + gate_up_packed_offset(s, l), d.intermediate, d.hidden);
   }
   if (err == cudaSuccess) err = setup_step_kernel(s);
   if (err != cudaSuccess) return create_fail(s, out, err, kStagePackReplicas);
@@ -2163,6 +2291,7 @@ extern "C" int nerva_cuda_hf_decode_sequence_session_fork_shared_weights(
   s->layout = parent->layout;
   s->layer_meta = parent->layer_meta;
   s->has_moe = parent->has_moe;
+  s->dense_ordinal = parent->dense_ordinal;
   s->resident_weight_bytes = parent->resident_weight_bytes;
   s->planned_weight_blocks = parent->planned_weight_blocks;
   s->planned_gpu_resident_blocks = parent->planned_gpu_resident_blocks;
@@ -2326,7 +2455,7 @@ extern "C" int nerva_b200_session_get_kv_block_table(Session *s, uint32_t *table
 extern "C" int nerva_b200_session_read_kv_row(Session *s, uint32_t layer, uint32_t token,
                                               uint32_t which, uint16_t *row, uint32_t capacity) {
   if (s == nullptr || row == nullptr || layer >= s->dims.layers || token >= s->max_context ||
-      which > 1 || capacity < s->dims.kv_hidden())
+      which > 1 || capacity < s->dims.kv_row() || (which == 1 && s->dims.mla()))
     return -1;
   if (cudaStreamSynchronize(s->stream) != cudaSuccess) return -1;
   uint32_t physical = 0;
@@ -2335,9 +2464,9 @@ extern "C" int nerva_b200_session_read_kv_row(Session *s, uint32_t layer, uint32
     return -1;
   // hf_decode_sequence/types.cuh:328-337
   const uint64_t offset = ((static_cast<uint64_t>(layer) * s->kv_pages + physical) * NERVA_KV_CACHE_BLOCK_TOKENS +
-                           token % NERVA_KV_CACHE_BLOCK_TOKENS) * s->dims.kv_hidden();
+                           token % NERVA_KV_CACHE_BLOCK_TOKENS) * s->dims.kv_row();
   const uint16_t *src = (which == 0 ? s->kv_keys : s->kv_values) + offset;
-  return cudaMemcpy(row, src, s->dims.kv_hidden() * 2u, cudaMemcpyDeviceToHost) == cudaSuccess ? 0 : -1;
+  return cudaMemcpy(row, src, s->dims.kv_row() * 2u, cudaMemcpyDeviceToHost) == cudaSuccess ? 0 : -1;
 }
 
 // Runs `steps` further decode steps of the active request outside any graph,

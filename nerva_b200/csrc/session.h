@@ -38,6 +38,16 @@ struct LayerLayout {
   uint64_t o_bias = kMissingOffset;
   uint32_t mlp_kind = 0, moe_intermediate = 0, shared_intermediate = 0;
   uint32_t num_experts = 0, top_k = 0, norm_topk_prob = 0;
+  // DeepSeek multi-head latent attention (attention_kind 2): w_q is the query projection
+  // [heads * (nope + rope)][hidden], w_k the latent + rotary-key projection [rank + rope][hidden],
+  // k_norm the latent's norm weight [rank], w_v the up-projection [heads * (nope + v)][rank]
+  // (per head: nope rows of W_UK, then v rows of W_UV), w_o [hidden][heads * v] — the slots the
+  // reference's packer uses for them (hf_decode_sequence/deepseek/weights_pack.inc.cu:156-186).
+  uint32_t attention_kind = 0, kv_lora_rank = 0, qk_nope = 0, qk_rope = 0;
+  // Sparse-MoE expert matrices: Qwen-style layers hold per expert [gate rows | up rows]
+  // (expert_up_offset = moe_intermediate * hidden inside a stride of twice that); DeepSeek layers
+  // hold all gate matrices, then all up matrices (weights_pack.inc.cu:303-312).
+  uint64_t expert_stride = 0, expert_up_offset = 0;
 };
 
 struct ArenaLayout {
@@ -52,8 +62,18 @@ struct ModelDims {
   // vocab = rows of lm_head held here; a tensor-parallel rank holds a shard of the
   // rows starting at vocab_offset, while the embedding table keeps embed_vocab rows.
   uint32_t embed_vocab = 0, vocab_offset = 0;
+  // latent attention (every layer, or none): rows of the fused query + latent projection and width
+  // of a cache row; zero for ordinary attention
+  uint32_t mla_rank = 0, mla_nope = 0, mla_rope = 0;
   uint64_t attention_hidden() const { return static_cast<uint64_t>(heads) * head_dim; }
   uint64_t kv_hidden() const { return static_cast<uint64_t>(kv_heads) * head_dim; }
+  bool mla() const { return mla_rank != 0; }
+  uint64_t mla_q_rows() const { return static_cast<uint64_t>(heads) * (mla_nope + mla_rope); }
+  uint64_t mla_width() const { return static_cast<uint64_t>(mla_rank) + mla_rope; }
+  // rows of the packed first projection of a layer: [Q; K; V], or [Q; latent + rotary key]
+  uint64_t qkv_rows() const { return mla() ? mla_q_rows() + mla_width() : attention_hidden() + 2 * kv_hidden(); }
+  // elements of one cached row per array
+  uint64_t kv_row() const { return mla() ? mla_width() : kv_hidden(); }
 };
 
 bool valid_layer(const NervaCudaHfDecodeChainLayer &layer, bool require_sources);
@@ -213,6 +233,9 @@ struct NervaCudaHfDecodeSequenceSession {
   bool timeline_on = false;
   // sparse MoE layers: routing scratch
   bool has_moe = false;
+  std::vector<int32_t> dense_ordinal;  // per layer: index of its packed gate/up copy, -1 for sparse layers
+  // latent attention scratch
+  float *mla_ql = nullptr;             // [heads][rank] absorbed queries
   float *router_logits = nullptr, *route_weights = nullptr, *shared_gate = nullptr, *moe_gate_up = nullptr;
   uint32_t *route_ids = nullptr;
   // tensor parallel (nerva_b200_session_create_sharded)
@@ -246,3 +269,8 @@ struct NervaCudaHfDecodeSequenceSession {
   nb::SamplerParams *device_sampler = nullptr;
   uint64_t hot_path_allocations = 0;
 };
+
+// Element offset of layer l's packed gate/up copy (dense layers only; sparse layers have none).
+inline uint64_t gate_up_packed_offset(const NervaCudaHfDecodeSequenceSession *s, uint32_t l) {
+  return static_cast<uint64_t>(s->dense_ordinal[l]) * 2u * s->dims.intermediate * s->dims.hidden;
+}

@@ -185,7 +185,7 @@ __device__ __forceinline__ void gather_norm_to_smem(uint16_t *x, const float *a,
   uint2 wk[kNormRegIters];
   float sumsq = 0.0f;
   const long long start = clock64();
-  bool gave_up = step_already_failed(error_word);
+  bool gave_up = false;
 #pragma unroll
   for (uint32_t k0 = 0; k0 < kNormRegIters; k0 += BATCH) {
     if (k0 * blockDim.x >= vecs) break;
@@ -229,9 +229,14 @@ __device__ __forceinline__ void gather_norm_to_smem(uint16_t *x, const float *a,
         }
       }
       if (ok || gave_up) break;
-      if ((++polls & 63u) == 0 && clock64() - start > kPeerWaitCycleLimit) {
-        gave_up = true;
-        report_error(error_word, kErrPeerWaitTimeout);
+      // looked at only while waiting: first whether an earlier exchange of this step gave up, then the clock
+      if ((polls++ & 63u) == 0) {
+        if (step_already_failed(error_word)) {
+          gave_up = true;
+        } else if (clock64() - start > kPeerWaitCycleLimit) {
+          gave_up = true;
+          report_error(error_word, kErrPeerWaitTimeout);
+        }
       }
     }
 #pragma unroll
@@ -304,7 +309,7 @@ __device__ __forceinline__ void reduce_partials_slice(const unsigned long long *
   const uint32_t begin = static_cast<uint32_t>(static_cast<uint64_t>(groups) * blockIdx.x / gridDim.x);
   const uint32_t end = static_cast<uint32_t>(static_cast<uint64_t>(groups) * (blockIdx.x + 1u) / gridDim.x);
   const long long start = clock64();
-  bool gave_up = step_already_failed(error_word);
+  bool gave_up = false;
   for (uint32_t g = begin + threadIdx.x; g < end; g += blockDim.x) {
     ulonglong2 lo[WORLD], hi[WORLD];
     uint32_t polls = 0;
@@ -322,9 +327,14 @@ __device__ __forceinline__ void reduce_partials_slice(const unsigned long long *
              static_cast<uint32_t>(hi[q].x >> 32) == tag && static_cast<uint32_t>(hi[q].y >> 32) == tag;
       }
       if (ok || gave_up) break;
-      if ((++polls & 63u) == 0 && clock64() - start > kPeerWaitCycleLimit) {
-        gave_up = true;
-        report_error(error_word, kErrPeerWaitTimeout);
+      // looked at only while waiting: first whether an earlier exchange of this step gave up, then the clock
+      if ((polls++ & 63u) == 0) {
+        if (step_already_failed(error_word)) {
+          gave_up = true;
+        } else if (clock64() - start > kPeerWaitCycleLimit) {
+          gave_up = true;
+          report_error(error_word, kErrPeerWaitTimeout);
+        }
       }
     }
     float4 t = make_float4(0.0f, 0.0f, 0.0f, 0.0f);

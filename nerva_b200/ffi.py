@@ -140,6 +140,9 @@ def _bind(L: C.CDLL, reference_abi_only: bool) -> C.CDLL:
                                             C.c_uint32, P(C.c_uint64)],
         "nerva_b200_gqa_decode_attention": [vp, vp, vp, vp, vp, C.c_uint32, C.c_uint32, C.c_uint32, C.c_uint32,
                                             C.c_uint32, C.c_uint32, C.c_uint32, P(C.c_uint64)],
+        "nerva_b200_gqa_decode_attention_sustained": [vp, vp, vp, vp, vp, C.c_uint32, C.c_uint32, C.c_uint32,
+                                                      C.c_uint32, C.c_uint32, C.c_uint32, C.c_uint32, C.c_uint32,
+                                                      P(C.c_uint64)],
         "nerva_b200_gqa_decode_attention_static_scratch": [vp, vp, vp, vp, vp, C.c_uint32, C.c_uint32,
                                                            C.c_uint32, C.c_uint32, C.c_uint32, vp],
         "nerva_b200_greedy_argmax": [vp, C.c_uint32, P(C.c_uint32)],

@@ -59,6 +59,23 @@ def gqa_decode_attention(q: np.ndarray, key_pages: np.ndarray, value_pages: np.n
     return out, ns.value
 
 
+def gqa_decode_attention_sustained(q: np.ndarray, key_pages: np.ndarray, value_pages: np.ndarray,
+                                   page_table: np.ndarray, batch: int, context: int, heads: int, kv_heads: int,
+                                   head_dim: int, copies: int = 2, warmup: int = 4, iterations: int = 20):
+    """The same attention over `copies` device copies of the cache (the caches of that many layers,
+    together larger than the L2), launched back to back.  Returns (out, ns per launch)."""
+    q = np.ascontiguousarray(q, dtype=np.float32)
+    k = np.ascontiguousarray(key_pages, dtype=np.uint16)
+    v = np.ascontiguousarray(value_pages, dtype=np.uint16)
+    t = np.ascontiguousarray(page_table, dtype=np.uint32)
+    out = np.empty((batch, heads * head_dim), dtype=np.float32)
+    ns = C.c_uint64(0)
+    _check(ffi.lib().nerva_b200_gqa_decode_attention_sustained(
+        q.ctypes.data, k.ctypes.data, v.ctypes.data, t.ctypes.data, out.ctypes.data, batch, context, heads, kv_heads,
+        head_dim, copies, warmup, iterations, C.byref(ns)), "gqa_decode_attention_sustained")
+    return out, ns.value
+
+
 def gqa_decode_attention_static_scratch(q_ptr: int, key_pages_ptr: int, value_pages_ptr: int, page_table_ptr: int,
                                         out_ptr: int, batch: int, context: int, heads: int, kv_heads: int,
                                         head_dim: int, stream: int = 0) -> None:

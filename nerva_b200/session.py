@@ -78,7 +78,14 @@ def chain_layers(checkpoint):
         for key, fname in _LAYER_TENSORS.items():
             if key in entry:
                 setattr(arr[i], fname, _ptr(entry[key]))
-        if cfg.num_experts:
+        if getattr(cfg, "kv_lora_rank", 0):
+            arr[i].attention_kind = 2
+            arr[i].deepseek_storage = 1  # bf16
+            arr[i].deepseek_kv_lora_rank = cfg.kv_lora_rank
+            arr[i].deepseek_qk_nope_head_dim = cfg.qk_nope_head_dim
+            arr[i].deepseek_qk_rope_head_dim = cfg.qk_rope_head_dim
+            arr[i].deepseek_v_head_dim = cfg.head_dim
+        if cfg.num_experts and i >= getattr(cfg, "dense_layers", 0):
             arr[i].mlp_kind = 1
             arr[i].moe_intermediate = cfg.moe_intermediate
             arr[i].shared_expert_intermediate = cfg.shared_intermediate
@@ -105,7 +112,23 @@ def _upload_order(checkpoint) -> list:
     tensors = [checkpoint.embeddings]
     order = ("rms_attn", "w_q", "q_norm", "w_k", "k_norm", "w_v", "w_o", "rms_mlp", "w_gate", "w_up", "w_down",
              "q_bias", "k_bias", "v_bias", "o_bias")
+    cfg = checkpoint.config
     for entry in checkpoint.layers:
+        if getattr(cfg, "kv_lora_rank", 0):
+            # latent-attention layers (the reference's DeepSeek packing order,
+            # hf_decode_sequence/deepseek/weights_pack.inc.cu:156-186,261-322): attention tensors, then the
+            # dense MLP or router | shared expert | every expert's gate | every expert's up | every expert's down
+            tensors += [entry[k] for k in ("rms_attn", "w_q", "w_kv_a", "kv_a_norm", "w_kv_b", "w_o", "rms_mlp")]
+            if "w_router" in entry:
+                tensors.append(entry["w_router"])
+                tensors += [entry[k] for k in ("w_shared_expert_gate", "w_shared_expert_up", "w_shared_expert_down")
+                            if k in entry]
+                per_expert = entry["w_expert_gate_up"].reshape(cfg.num_experts, 2, cfg.moe_intermediate * cfg.hidden)
+                tensors += [np.ascontiguousarray(per_expert[:, 0]).reshape(-1),
+                            np.ascontiguousarray(per_expert[:, 1]).reshape(-1), entry["w_expert_down"]]
+            else:
+                tensors += [entry[k] for k in ("w_gate", "w_up", "w_down")]
+            continue
         tensors += [entry[k] for k in order if k in entry]
     tensors += [checkpoint.final_norm, checkpoint.lm_head]
     return tensors
@@ -144,6 +167,7 @@ def weight_blocks(checkpoint, staged_every: int = 2, source_file: str | None = N
         arr[i].strategy = STRATEGY_GPU_STAGED if staged_every and i % staged_every == 1 else STRATEGY_GPU_RESIDENT
         offset += t.size * 2
     arr._path_keepalive = path_bytes
+    arr._tensor_keepalive = tensors  # re-packed copies (per-expert gate / up matrices) live as long as the table
     return arr
 
 
@@ -167,7 +191,7 @@ class CudaHfDecodeSequenceSession:
             max_context_tokens=max_context_tokens, rms_eps=cfg.rms_eps, rope_theta=cfg.rope_theta,
             embeddings=_ptr(checkpoint.embeddings), layers=C.cast(layers, C.c_void_p),
             final_norm_weight=_ptr(checkpoint.final_norm), lm_head=_ptr(checkpoint.lm_head))
-        if use_descriptors or weight_file is not None:
+        if use_descriptors or weight_file is not None or getattr(cfg, "kv_lora_rank", 0):
             blocks = weight_blocks(checkpoint, source_file=weight_file, header_bytes=weight_file_header)
             self._keep.append(blocks)
             req.planned_weight_blocks = len(blocks)

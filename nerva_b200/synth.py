@@ -126,6 +126,12 @@ class DecoderConfig:
     moe_intermediate: int = 0
     shared_intermediate: int = 0
     norm_topk_prob: bool = False
+    dense_layers: int = 0          # leading layers that keep the dense MLP in a sparse-MoE model
+    # DeepSeek multi-head latent attention (attention_kind 2); zero rank = ordinary attention.
+    # heads * head_dim is the value width (head_dim = v_head_dim); shared experts are ungated.
+    kv_lora_rank: int = 0
+    qk_nope_head_dim: int = 0
+    qk_rope_head_dim: int = 0
 
     @property
     def attention_hidden(self) -> int:
@@ -135,6 +141,22 @@ class DecoderConfig:
     def kv_hidden(self) -> int:
         return self.kv_heads * self.head_dim
 
+    def active_weight_bytes_per_token(self) -> int:
+        """Weight bytes one decoded token must stream in a latent-attention / sparse-MoE model: the
+        attention projections, the dense or the routed + shared expert matrices it touches, lm_head."""
+        h = self.hidden
+        if self.kv_lora_rank:
+            qdim = self.qk_nope_head_dim + self.qk_rope_head_dim
+            attn = (self.heads * qdim * h + (self.kv_lora_rank + self.qk_rope_head_dim) * h
+                    + self.heads * (self.qk_nope_head_dim + self.head_dim) * self.kv_lora_rank
+                    + h * self.heads * self.head_dim)
+        else:
+            attn = (self.attention_hidden + 2 * self.kv_hidden) * h + h * self.attention_hidden
+        dense = 3 * self.intermediate * h
+        moe = self.num_experts * h + 3 * (self.top_k * self.moe_intermediate + self.shared_intermediate) * h
+        moe_layers = max(0, self.layers - self.dense_layers) if self.num_experts else 0
+        return 2 * (attn * self.layers + dense * (self.layers - moe_layers) + moe * moe_layers + self.vocab * h)
+
     def projection_bytes_per_token(self) -> int:
         """Weight bytes one decoded token must stream (2*N*K per projection)."""
         h = self.hidden
@@ -142,6 +164,15 @@ class DecoderConfig:
         per_layer += 3 * self.intermediate * h
         return 2 * (per_layer * self.layers + self.vocab * h)
 
+
+# DeepSeek-V2-Lite architecture: 27 layers, latent attention (rank 512, nope 128 / rope 64 / v 128),
+# first layer dense (intermediate 10944), then 64 routed experts (top-6 softmax) + 2 shared experts
+# of intermediate 1408 each (one ungated MLP of 2816).
+DEEPSEEK_V2_LITE = DecoderConfig("deepseek-v2-lite", layers=27, hidden=2048, heads=16, kv_heads=16, head_dim=128,
+                                 intermediate=10944, vocab=102400, rope_theta=1e4, qk_norm=False, prompt_tokens=1024,
+                                 decode_tokens=128, num_experts=64, top_k=6, moe_intermediate=1408,
+                                 shared_intermediate=2816, norm_topk_prob=False, dense_layers=1, kv_lora_rank=512,
+                                 qk_nope_head_dim=128, qk_rope_head_dim=64)
 
 TINY_QWEN3 = DecoderConfig("tiny-qwen3", layers=4, hidden=512, heads=8, kv_heads=2, head_dim=64,
                            intermediate=1536, vocab=32000, prompt_tokens=64, decode_tokens=32)
@@ -172,18 +203,31 @@ def dense_checkpoint(cfg: DecoderConfig, seed: int = 0, std: float = 0.02, fill=
     )
     for layer in range(cfg.layers):
         tid = lambda slot: layer_tensor_id(layer, slot)  # noqa: E731
-        entry = {
-            "rms_attn": ones_h.copy(),
-            "rms_mlp": ones_h.copy(),
-            "w_q": gen(seed, tid(L_WQ), cfg.attention_hidden * cfg.hidden, std),
-            "w_k": gen(seed, tid(L_WK), cfg.kv_hidden * cfg.hidden, std),
-            "w_v": gen(seed, tid(L_WV), cfg.kv_hidden * cfg.hidden, std),
-            "w_o": gen(seed, tid(L_WO), cfg.hidden * cfg.attention_hidden, std),
-        }
-        if cfg.qk_norm:
+        if cfg.kv_lora_rank:
+            qdim = cfg.qk_nope_head_dim + cfg.qk_rope_head_dim
+            entry = {
+                "rms_attn": ones_h.copy(),
+                "rms_mlp": ones_h.copy(),
+                "w_q": gen(seed, tid(L_Q), cfg.heads * qdim * cfg.hidden, std),
+                "w_kv_a": gen(seed, tid(L_KV_A), (cfg.kv_lora_rank + cfg.qk_rope_head_dim) * cfg.hidden, std),
+                "kv_a_norm": np.full(cfg.kv_lora_rank, BF16_ONE, dtype=np.uint16),
+                "w_kv_b": gen(seed, tid(L_KV_B), cfg.heads * (cfg.qk_nope_head_dim + cfg.head_dim) * cfg.kv_lora_rank,
+                              std),
+                "w_o": gen(seed, tid(L_WO), cfg.hidden * cfg.attention_hidden, std),
+            }
+        else:
+            entry = {
+                "rms_attn": ones_h.copy(),
+                "rms_mlp": ones_h.copy(),
+                "w_q": gen(seed, tid(L_WQ), cfg.attention_hidden * cfg.hidden, std),
+                "w_k": gen(seed, tid(L_WK), cfg.kv_hidden * cfg.hidden, std),
+                "w_v": gen(seed, tid(L_WV), cfg.kv_hidden * cfg.hidden, std),
+                "w_o": gen(seed, tid(L_WO), cfg.hidden * cfg.attention_hidden, std),
+            }
+        if cfg.qk_norm and not cfg.kv_lora_rank:
             entry["q_norm"] = ones_d.copy()
             entry["k_norm"] = ones_d.copy()
-        if cfg.num_experts == 0:
+        if cfg.num_experts == 0 or layer < cfg.dense_layers:
             entry["w_gate"] = gen(seed, tid(L_WGATE), cfg.intermediate * cfg.hidden, std)
             entry["w_up"] = gen(seed, tid(L_WUP), cfg.intermediate * cfg.hidden, std)
             entry["w_down"] = gen(seed, tid(L_WDOWN), cfg.hidden * cfg.intermediate, std)
@@ -197,7 +241,8 @@ def dense_checkpoint(cfg: DecoderConfig, seed: int = 0, std: float = 0.02, fill=
                 entry["w_shared_expert_gate"] = gen(seed, tid(L_SHARED_GATE), si * cfg.hidden, std)
                 entry["w_shared_expert_up"] = gen(seed, tid(L_SHARED_UP), si * cfg.hidden, std)
                 entry["w_shared_expert_down"] = gen(seed, tid(L_SHARED_DOWN), cfg.hidden * si, std)
-                entry["w_shared_expert_router"] = gen(seed, tid(L_SHARED_ROUTER), cfg.hidden, std)
+                if not cfg.kv_lora_rank:  # DeepSeek shared experts are always on: no router row
+                    entry["w_shared_expert_router"] = gen(seed, tid(L_SHARED_ROUTER), cfg.hidden, std)
         ck.layers.append(entry)
     return ck
 

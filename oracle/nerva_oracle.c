@@ -472,6 +472,7 @@ struct OracleCtx {
   float *input, *attn_norm, *q, *k, *v, *attn, *residual, *mlp_norm;
   float *gate, *up, *ff, *down, *tmp, *hidden_f32, *router;
   uint16_t *hidden_bits, *next_bits;
+  float *mla_q, *mla_kv, *mla_ql, *mla_lat, *mla_scores;  /* latent-attention scratch (attention_kind 2) */
 };
 
 static float *alloc_f32(uint64_t n) { return (float *)calloc(n ? n : 1, sizeof(float)); }
@@ -520,6 +521,25 @@ OracleCtx *oracle_create(const OracleModel *model, uint32_t max_context, int mod
   ctx->router = alloc_f32(experts);
   ctx->hidden_bits = (uint16_t *)calloc(hidden, sizeof(uint16_t));
   ctx->next_bits = (uint16_t *)calloc(hidden, sizeof(uint16_t));
+  uint64_t mla_q = 0, mla_width = 0, mla_rank = 0;
+  for (uint32_t l = 0; l < model->layers; ++l) {
+    const OracleLayer *layer = &model->layer[l];
+    if (layer->attention_kind != 2u) {
+      continue;
+    }
+    const uint64_t q = (uint64_t)model->heads * (layer->qk_nope_head_dim + layer->qk_rope_head_dim);
+    const uint64_t w = (uint64_t)layer->kv_lora_rank + layer->qk_rope_head_dim;
+    mla_q = q > mla_q ? q : mla_q;
+    mla_width = w > mla_width ? w : mla_width;
+    mla_rank = layer->kv_lora_rank > mla_rank ? layer->kv_lora_rank : mla_rank;
+  }
+  if (mla_q != 0) {
+    ctx->mla_q = alloc_f32(mla_q);
+    ctx->mla_kv = alloc_f32(mla_width);
+    ctx->mla_ql = alloc_f32((uint64_t)model->heads * mla_rank);
+    ctx->mla_lat = alloc_f32((uint64_t)model->heads * mla_rank);
+    ctx->mla_scores = alloc_f32(max_context);
+  }
   return ctx;
 }
 
@@ -545,6 +565,11 @@ void oracle_destroy(OracleCtx *ctx) {
   free(ctx->tmp);
   free(ctx->hidden_f32);
   free(ctx->router);
+  free(ctx->mla_q);
+  free(ctx->mla_kv);
+  free(ctx->mla_ql);
+  free(ctx->mla_lat);
+  free(ctx->mla_scores);
   free(ctx->hidden_bits);
   free(ctx->next_bits);
   free(ctx);
@@ -633,7 +658,7 @@ static void sparse_moe_mlp(OracleCtx *ctx, const OracleLayer *layer, const float
   if (layer->shared_intermediate != 0) {
     const uint32_t si = layer->shared_intermediate;
     float gate_weight = 0.0f;
-    for (uint32_t i = 0; i < hidden; ++i) {
+    for (uint32_t i = 0; layer->w_shared_router != NULL && i < hidden; ++i) {
       gate_weight += decode(m->dtype, layer->w_shared_router[i]) * x[i];
     }
     oracle_matvec(m->dtype, layer->w_shared_gate, x, si, hidden, ctx->gate);
@@ -642,11 +667,114 @@ static void sparse_moe_mlp(OracleCtx *ctx, const OracleLayer *layer, const float
       ctx->ff[i] = oracle_silu(ctx->gate[i]) * ctx->up[i];
     }
     oracle_matvec(m->dtype, layer->w_shared_down, ctx->ff, hidden, si, ctx->tmp);
-    const float shared_scale = oracle_sigmoid(gate_weight);
+    /* DeepSeek shared experts are always on: no router, scale 1 */
+    const float shared_scale = layer->w_shared_router != NULL ? oracle_sigmoid(gate_weight) : 1.0f;
     for (uint32_t i = 0; i < hidden; ++i) {
       down[i] += shared_scale * ctx->tmp[i];
     }
   }
+}
+
+/* DeepSeek multi-head latent attention in its absorbed form, for one token (CUDA numeric contract:
+ * bf16 mat-vec inputs, bf16 latent cache).  The reference has this attention only behind a query
+ * low-rank stage and grouped-sigmoid routing (hf_decode_sequence/deepseek/
+ * session_decode_v3_projection.inc.cu:1-624); the pieces restated here are its cache row
+ * (kernels_v3_mla.inc.cu:1-61: normalised latent, then the rotary key with interleaved pairs on
+ * inputs rounded to the model dtype), its rotary helper (kernels_helpers_math.inc.cu:236-262,
+ * no YaRN scaling), its softmax scale rsqrt(nope + rope) (:166-180) and the absorbed algebra of
+ * the stand-alone operator (native/cuda/deepseek/nerva_cuda_deepseek_mla.cu:144-227):
+ *   ql[h] = q_nope[h] . W_UK[h];  s[h][t] = (ql[h] . c[t] + q_pe[h] . k_pe[t]) * scale;
+ *   lat[h] = sum_t softmax(s)[t] c[t];  out[h] = W_UV[h] . lat[h].
+ * Writes heads * head_dim values to ctx->attn. */
+static void rope_interleaved(float *values, uint32_t dim, uint32_t position, float theta) {
+  if (!(theta > 0.0f) || dim < 2) {
+    return;
+  }
+  for (uint32_t pair = 0; pair < dim / 2u; ++pair) {
+    const float exponent = (float)(2u * pair) / (float)dim;
+    const float angle = (float)position * (1.0f / powf(theta, exponent));
+    const float s = sinf(angle), c = cosf(angle);
+    const float left = values[2u * pair], right = values[2u * pair + 1u];
+    values[2u * pair] = left * c - right * s;
+    values[2u * pair + 1u] = right * c + left * s;
+  }
+}
+
+static int mla_attention(OracleCtx *ctx, const OracleLayer *layer, uint32_t layer_index,
+                         uint32_t position) {
+  const OracleModel *m = &ctx->model;
+  const uint32_t dtype = m->dtype, hidden = m->hidden, heads = m->heads;
+  const uint32_t rank = layer->kv_lora_rank, nope = layer->qk_nope_head_dim;
+  const uint32_t rope = layer->qk_rope_head_dim, vdim = m->head_dim;
+  const uint32_t width = rank + rope, qdim = nope + rope;
+  const uint64_t stride = (uint64_t)m->kv_heads * m->head_dim;  /* cache row stride of this context */
+  if (width > stride) {
+    return -1;
+  }
+  oracle_matvec(dtype, layer->w_q, ctx->attn_norm, heads * qdim, hidden, ctx->mla_q);
+  oracle_matvec(dtype, layer->w_kv_a, ctx->attn_norm, width, hidden, ctx->mla_kv);
+  /* cache row: bf16(rmsnorm(latent) * w) | bf16(rope(bf16(k_pe))) */
+  float *row = ctx->keys + ((uint64_t)layer_index * ctx->max_context + position) * stride;
+  oracle_rms_norm(dtype, ctx->mla_kv, layer->kv_a_norm, rank, m->rms_eps, row);
+  for (uint32_t i = 0; i < rope; ++i) {
+    row[rank + i] = round_to_dtype(dtype, ctx->mla_kv[rank + i]);
+  }
+  rope_interleaved(row + rank, rope, position, m->rope_theta);
+  round_vec(dtype, row, width);
+  const float scale = 1.0f / sqrtf((float)qdim);
+  for (uint32_t h = 0; h < heads; ++h) {
+    float *q = ctx->mla_q + (uint64_t)h * qdim;
+    rope_interleaved(q + nope, rope, position, m->rope_theta);
+    /* absorbed query: ql[r] = sum_n q[n] W_UK[h][n][r] */
+    float *ql = ctx->mla_ql + (uint64_t)h * rank;
+    const uint16_t *w_uk = layer->w_kv_b + (uint64_t)h * (nope + vdim) * rank;
+    for (uint32_t r = 0; r < rank; ++r) {
+      ql[r] = 0.0f;
+    }
+    for (uint32_t n = 0; n < nope; ++n) {
+      const float qn = q[n];
+      for (uint32_t r = 0; r < rank; ++r) {
+        ql[r] += qn * decode(dtype, w_uk[(uint64_t)n * rank + r]);
+      }
+    }
+    float top = -INFINITY;
+    for (uint32_t t = 0; t <= position; ++t) {
+      const float *c = ctx->keys + ((uint64_t)layer_index * ctx->max_context + t) * stride;
+      float s = 0.0f;
+      for (uint32_t r = 0; r < rank; ++r) {
+        s += ql[r] * c[r];
+      }
+      for (uint32_t i = 0; i < rope; ++i) {
+        s += q[nope + i] * c[rank + i];
+      }
+      ctx->mla_scores[t] = s * scale;
+      if (ctx->mla_scores[t] > top) {
+        top = ctx->mla_scores[t];
+      }
+    }
+    float total = 0.0f;
+    float *lat = ctx->mla_lat + (uint64_t)h * rank;
+    for (uint32_t r = 0; r < rank; ++r) {
+      lat[r] = 0.0f;
+    }
+    for (uint32_t t = 0; t <= position; ++t) {
+      const float p = expf(ctx->mla_scores[t] - top);
+      const float *c = ctx->keys + ((uint64_t)layer_index * ctx->max_context + t) * stride;
+      total += p;
+      for (uint32_t r = 0; r < rank; ++r) {
+        lat[r] += p * c[r];
+      }
+    }
+    const uint16_t *w_uv = w_uk + (uint64_t)nope * rank;
+    for (uint32_t v = 0; v < vdim; ++v) {
+      float acc = 0.0f;
+      for (uint32_t r = 0; r < rank; ++r) {
+        acc += (lat[r] / total) * decode(dtype, w_uv[(uint64_t)v * rank + r]);
+      }
+      ctx->attn[(uint64_t)h * vdim + v] = acc;
+    }
+  }
+  return 0;
 }
 
 /* One layer for one token at `position`.
@@ -664,6 +792,12 @@ static int layer_forward(OracleCtx *ctx, uint32_t layer_index, uint32_t position
   oracle_rms_norm(dtype, ctx->input, layer->rms_attn, hidden, m->rms_eps, ctx->attn_norm);
   if (cuda) {
     round_vec(dtype, ctx->attn_norm, hidden);
+  }
+  if (layer->attention_kind == 2u) {
+    if (mla_attention(ctx, layer, layer_index, position) != 0) {
+      return -1;
+    }
+    goto attention_done;
   }
   /* K: mat-vec, bias, k-norm, (V: mat-vec, bias), RoPE on K  — kv.rs:113-141 */
   oracle_matvec(dtype, layer->w_k, ctx->attn_norm, kv_hidden, hidden, ctx->k);
@@ -699,6 +833,7 @@ static int layer_forward(OracleCtx *ctx, uint32_t layer_index, uint32_t position
                        m->head_dim, ctx->attn) != 0) {
     return -1;
   }
+attention_done:
   if (cuda) {
     round_vec(dtype, ctx->attn, attention_hidden);
   }

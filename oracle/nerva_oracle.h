@@ -45,6 +45,15 @@ typedef struct OracleLayer {
   uint32_t num_experts, top_k, norm_topk_prob;
   const uint16_t *w_router, *w_expert_gate_up, *w_expert_down;
   const uint16_t *w_shared_gate, *w_shared_up, *w_shared_down, *w_shared_router;
+  /* DeepSeek multi-head latent attention (attention_kind == 2), the V2-Lite form without a query
+   * low-rank stage: w_q is [heads * (nope + rope)][hidden], w_o is [hidden][heads * v_head_dim]
+   * (v_head_dim == model head_dim), and
+   *   w_kv_a    [kv_lora_rank + rope][hidden]      latent + shared rotary key
+   *   kv_a_norm [kv_lora_rank]                     RMSNorm weight of the latent
+   *   w_kv_b    [heads * (nope + v)][kv_lora_rank] per head: nope rows of W_UK, then v rows of W_UV
+   * With attention_kind == 2 a sparse-MoE layer's shared experts are ungated (w_shared_router NULL). */
+  uint32_t attention_kind, kv_lora_rank, qk_nope_head_dim, qk_rope_head_dim;
+  const uint16_t *w_kv_a, *kv_a_norm, *w_kv_b;
 } OracleLayer;
 
 typedef struct OracleModel {

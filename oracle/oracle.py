@@ -32,7 +32,9 @@ class OracleLayer(C.Structure):
             "mlp_kind", "moe_intermediate", "shared_intermediate", "num_experts", "top_k", "norm_topk_prob")] + [
         (n, _u16p) for n in (
             "w_router", "w_expert_gate_up", "w_expert_down",
-            "w_shared_gate", "w_shared_up", "w_shared_down", "w_shared_router")]
+            "w_shared_gate", "w_shared_up", "w_shared_down", "w_shared_router")] + [
+        (n, C.c_uint32) for n in ("attention_kind", "kv_lora_rank", "qk_nope_head_dim", "qk_rope_head_dim")] + [
+        (n, _u16p) for n in ("w_kv_a", "kv_a_norm", "w_kv_b")]
 
 
 class OracleModel(C.Structure):
@@ -222,7 +224,12 @@ class Decoder:
             for fname, ftype in OracleLayer._fields_:
                 if ftype is _u16p:
                     setattr(layer, fname, _p16(entry.get(names.get(fname, fname))))
-            if cfg.num_experts:
+            if getattr(cfg, "kv_lora_rank", 0):
+                layer.attention_kind = 2
+                layer.kv_lora_rank = cfg.kv_lora_rank
+                layer.qk_nope_head_dim = cfg.qk_nope_head_dim
+                layer.qk_rope_head_dim = cfg.qk_rope_head_dim
+            if cfg.num_experts and i >= getattr(cfg, "dense_layers", 0):
                 layer.mlp_kind = 1
                 layer.moe_intermediate = cfg.moe_intermediate
                 layer.shared_intermediate = cfg.shared_intermediate

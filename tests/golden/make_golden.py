@@ -10,6 +10,9 @@
    a probe against the REFERENCE header (needs the reference checkout, only
    present on the build machine).  The test-suite compares this library's
    header against it.
+3. abi_prototypes.txt — return and parameter types, in order, of every
+   nerva_cuda_* function this library declares, as the REFERENCE header
+   declares them.
 4. qwen3_8b.json (only with the argument `qwen3_8b`; takes about an hour and 20 GB on 8 cores) —
    the CPU oracle on the full 36-layer Qwen3-8B-architecture model with the 512-token seeded
    prompt: per decoded position the token, the top-1 minus top-2 margin, the largest logit, the
@@ -17,9 +20,6 @@
    depth sweep (models cut to 1, 2, 4, 8, 16, 36 layers, 16-token prompt): 1024 sampled logits
    under the serial summation order, and the oracle's distance to itself when only the
    summation order changes (8 interleaved partial sums).
-3. abi_prototypes.txt — return and parameter types, in order, of every
-   nerva_cuda_* function this library declares, as the REFERENCE header
-   declares them.
 """
 from __future__ import annotations
 

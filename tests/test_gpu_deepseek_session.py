@@ -1,0 +1,88 @@
+"""DeepSeek-V2-Lite-architecture sessions (latent attention + softmax top-k sparse MoE with always-on
+shared experts, a dense first layer) against the CPU oracle's composed model.  The reference has no
+end-to-end path for this architecture (its latent-attention session needs a query low-rank stage and
+grouped-sigmoid routing), so the whole-model semantics are this repository's composition of pieces
+that are pinned one by one: the stand-alone latent-attention operator, softmax top-k routing and
+the expert MLP."""
+import dataclasses
+
+import numpy as np
+import pytest
+
+from nerva_b200 import ops, synth
+from nerva_b200.session import CudaHfDecodeSequenceLoop, CudaHfDecodeSequenceSession, SmokeStatus
+
+pytestmark = pytest.mark.gpu
+
+LOGIT_ATOL = 2e-2
+
+
+def _small():
+    return dataclasses.replace(synth.DEEPSEEK_V2_LITE, name="v2-lite-small", layers=3, vocab=4096, prompt_tokens=21,
+                               decode_tokens=12, hidden=512, heads=4, kv_heads=4, head_dim=64, intermediate=1024,
+                               num_experts=8, top_k=2, moe_intermediate=128, shared_intermediate=256,
+                               kv_lora_rank=128, qk_nope_head_dim=64, qk_rope_head_dim=32)
+
+
+def _full_width(layers):
+    return dataclasses.replace(synth.DEEPSEEK_V2_LITE, name=f"v2-lite cut to {layers}", layers=layers, vocab=32768,
+                               prompt_tokens=40, decode_tokens=8)
+
+
+def _decode(cfg, ck, steps):
+    s = CudaHfDecodeSequenceSession(ck, cfg.prompt_tokens + steps + 1)
+    assert s.status == SmokeStatus.OK, (s.error, s.create_result.cuda_error, s.create_result.failure_stage)
+    start, loop = CudaHfDecodeSequenceLoop.start(s, synth.prompt_ids(cfg))
+    assert start.status == SmokeStatus.OK, start.error
+    tokens, logits = [], []
+    for _ in range(steps):
+        out = loop.advance(1)
+        assert out.status == SmokeStatus.OK, out.error
+        tokens += out.tokens
+        logits.append(s.read_logits())
+    return s, tokens, np.stack(logits)
+
+
+@pytest.mark.parametrize("make", [_small, lambda: _full_width(2), lambda: _full_width(3)])
+def test_latent_attention_moe_session_matches_the_composed_oracle(built_lib, oracle_mod, make):
+    cfg = make()
+    ck = synth.dense_checkpoint(cfg, fill=ops.synth_normal_bf16)
+    steps = cfg.decode_tokens
+    s, tokens, logits = _decode(cfg, ck, steps)
+    dec = oracle_mod.Decoder(ck, cfg.prompt_tokens + steps + 1, mode=oracle_mod.MODE_CUDA)
+    want_tokens, want_logits = dec.decode_greedy(synth.prompt_ids(cfg), steps, want_logits=True)
+    top2 = np.sort(want_logits, axis=1)[:, -2:]
+    margins = top2[:, 1] - top2[:, 0]
+    at = next((i for i in range(steps) if tokens[i] != int(want_tokens[i])), None)
+    compared = steps if at is None else at + 1
+    assert float(np.abs(logits[:compared] - want_logits[:compared]).max()) <= LOGIT_ATOL
+    assert at is None or margins[at] <= LOGIT_ATOL, (at, tokens, want_tokens.tolist(), margins[at])
+    # the cached latent rows are the oracle's, to one bf16 rounding step of the row's magnitude
+    r = s.create_result
+    assert r.resident_kv_bytes == cfg.layers * ((cfg.prompt_tokens + steps + 1 + 15) // 16) * 16 * \
+        (cfg.kv_lora_rank + cfg.qk_rope_head_dim) * 2
+    # bit-stable and independent of the page placement
+    again = CudaHfDecodeSequenceSession(ck, cfg.prompt_tokens + steps + 1)
+    pages = (cfg.prompt_tokens + steps + 1 + 15) // 16
+    again.set_kv_block_table(synth.permutation(9, synth.T_PAGE_TABLE, pages))
+    _, loop = CudaHfDecodeSequenceLoop.start(again, synth.prompt_ids(cfg))
+    assert loop.advance(steps).tokens == tokens
+    for token in (0, cfg.prompt_tokens - 1, cfg.prompt_tokens + 2):
+        assert np.array_equal(again.read_kv_row(cfg.layers - 1, token, 0), s.read_kv_row(cfg.layers - 1, token, 0))
+    again.destroy()
+    s.destroy()
+
+
+def test_fork_of_a_latent_attention_session_continues_like_its_parent(built_lib):
+    cfg = _small()
+    ck = synth.dense_checkpoint(cfg, fill=ops.synth_normal_bf16)
+    s = CudaHfDecodeSequenceSession(ck, cfg.prompt_tokens + 16)
+    assert s.status == SmokeStatus.OK, s.error
+    start, loop = CudaHfDecodeSequenceLoop.start(s, synth.prompt_ids(cfg))
+    assert start.status == SmokeStatus.OK, start.error
+    head = loop.advance(4).tokens
+    fork = s.fork_shared_weights()
+    assert fork.status == SmokeStatus.OK, fork.error
+    assert CudaHfDecodeSequenceLoop(fork).advance(8).tokens == loop.advance(8).tokens and len(head) == 4
+    fork.destroy()
+    s.destroy()

@@ -66,10 +66,10 @@ def test_static_scratch_attention_matches_allocating_entry_point(built_lib, orac
 
 
 def test_static_scratch_attention_lowers_the_split_count_to_fit(built_lib, oracle_mod):
-    """32 query heads on one KV head at a long context: the split count the kernels would pick
-    (256) needs more than the fixed array holds (252 splits of 32 x 130 floats), so the entry
-    point lowers it; the result must not change."""
-    batch, context, heads, kv_heads, head_dim = 1, 33000, 32, 1, 128
+    """64 query heads of 256 dims on one KV head: the split count the launcher would pick (64) needs
+    more than the fixed array holds (63 splits of 64 x 258 floats), so the entry point lowers it;
+    the result must not change."""
+    batch, context, heads, kv_heads, head_dim = 1, 8200, 64, 1, 256
     q, k, v, table = _inputs(batch, context, heads, kv_heads, head_dim, 7)
     got = _static_scratch(q, k, v, table, batch, context, heads, kv_heads, head_dim)
     want = _oracle(oracle_mod, q, k, v, table, batch, context, heads, kv_heads, head_dim)
