@@ -235,3 +235,35 @@ def test_summation_order_probe_changes_logits_only_slightly_on_tiny(oracle_mod):
         oracle_mod.set_sum_lanes(1)
     d = float(np.abs(alt - ref).max())
     assert 0.0 < d < 2e-2
+
+
+# ---- the full-size fixture: its cheapest row is regenerated here ----
+
+def test_one_layer_cut_of_the_full_size_fixture_is_reproduced(oracle_mod):
+    """tests/golden/qwen3_8b.json takes an hour to make; its depth-1 row (one Qwen3-8B layer between
+    the full embedding table and lm_head, 16-token prompt) takes seconds, so it is recomputed and
+    compared bit for bit, under both summation orders: the committed file and this oracle agree."""
+    import dataclasses
+    import json
+    import os
+    path = os.path.join(os.path.dirname(__file__), "golden", "qwen3_8b.json")
+    with open(path) as f:
+        sweep = json.load(f)["depth_sweep"]
+    assert sweep["depths"][0] == 1
+    cfg = dataclasses.replace(synth.QWEN3_8B, layers=1, name="qwen3-8b cut to 1")
+    ck = synth.dense_checkpoint(cfg, fill=oracle_mod.synth_normal_bf16)
+    prompt = synth.prompt_ids(synth.QWEN3_8B, count=sweep["prompt_tokens"])
+    idx = sweep["sample_indices"]
+    try:
+        for lanes, key in ((1, "serial_samples"), (8, "lanes8_samples")):
+            oracle_mod.set_sum_lanes(lanes)
+            dec = oracle_mod.Decoder(ck, sweep["prompt_tokens"], mode=oracle_mod.MODE_CUDA)
+            for token in prompt[:-1]:
+                dec.step(int(token), want_logits=False)
+            logits = dec.step(int(prompt[-1]), want_logits=True)
+            dec.close()
+            assert np.array_equal(logits[idx], np.array(sweep[key][0], dtype=np.float32))
+            if lanes == 1:
+                assert int(np.argmax(logits)) == sweep["serial_argmax"][0]
+    finally:
+        oracle_mod.set_sum_lanes(1)
