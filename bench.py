@@ -563,6 +563,75 @@ def run_batch_workload(args, cfg) -> None:
     }), flush=True)
 
 
+def run_deepseek_workload(args) -> None:
+    """DeepSeek-V2-Lite architecture (latent attention + softmax top-6 of 64 experts + always-on shared
+    experts, dense first layer) on one GPU: batch-1 greedy decode after a 1024-token prompt.  The bytes
+    a token must stream are the matrices it touches (attention projections, router, 6 routed + the
+    shared expert matrices per sparse layer, lm_head), not the 31 GB that are resident."""
+    import dataclasses
+    from nerva_b200 import build, ops, synth
+    from nerva_b200.session import CudaHfDecodeSequenceLoop, CudaHfDecodeSequenceSession, SmokeStatus
+    build.build()
+    cfg = synth.DEEPSEEK_V2_LITE
+    if args.layers:
+        cfg = dataclasses.replace(cfg, layers=args.layers, name=f"{cfg.name} cut to {args.layers} layers")
+    if args.prompt_tokens:
+        cfg = dataclasses.replace(cfg, prompt_tokens=args.prompt_tokens)
+    t0 = time.perf_counter()
+    ck = synth.dense_checkpoint(cfg, fill=ops.synth_normal_bf16)
+    t1 = time.perf_counter()
+    session = CudaHfDecodeSequenceSession(ck, cfg.prompt_tokens + max(args.warmup, 3) + 2 * args.steps + 8)
+    if session.status != SmokeStatus.OK:
+        raise RuntimeError(f"session create failed: {session.error}")
+    t2 = time.perf_counter()
+    start, loop = CudaHfDecodeSequenceLoop.start(session, synth.prompt_ids(cfg))
+    if start.status != SmokeStatus.OK:
+        raise RuntimeError(f"session start failed: {start.error}")
+    t3 = time.perf_counter()
+    loop.advance(max(args.warmup, 3))
+    sampler = ClockSampler()
+    sampler.start()
+    timed = loop.advance(args.steps)
+    clocks = sampler.stop()
+    if timed.status != SmokeStatus.OK or len(timed.tokens) != args.steps:
+        raise RuntimeError(f"timed advance failed: {timed.error}")
+    device_s = timed.device_elapsed_ns * 1e-9
+    t4 = time.perf_counter()
+    e2e_tokens = []
+    for _ in range(args.steps):
+        out = loop.advance(1)
+        if out.status != SmokeStatus.OK:
+            raise RuntimeError(f"advance failed: {out.error}")
+        e2e_tokens += out.tokens
+    e2e_s = time.perf_counter() - t4
+    peaks = measured_peaks()
+    nbytes = cfg.active_weight_bytes_per_token()
+    r = session.create_result
+    print(json.dumps({
+        "metric": "DeepSeek-V2-Lite-arch BF16 batch-1 decode tok/s", "value": args.steps / device_s, "unit": "tok/s",
+        "n_gpus": 1, "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": 1e3 * device_s / args.steps,
+        "higher_is_better": True, "dtype": "bf16", "data": "synthetic",
+        "config": {"workload": f"{cfg.name}: {cfg.layers} layers, hidden {cfg.hidden}, {cfg.heads} heads, latent rank "
+                               f"{cfg.kv_lora_rank}, nope {cfg.qk_nope_head_dim} / rope {cfg.qk_rope_head_dim} / v "
+                               f"{cfg.head_dim}; {cfg.dense_layers} dense layer (intermediate {cfg.intermediate}), then "
+                               f"{cfg.num_experts} experts top-{cfg.top_k} softmax + shared {cfg.shared_intermediate}, "
+                               f"expert intermediate {cfg.moe_intermediate}; vocab {cfg.vocab}; batch 1, "
+                               f"{cfg.prompt_tokens}-token seeded prompt, greedy decode",
+                   "weights": "random-init bf16 ~N(0,0.02) seed 0, unit norm weights (synthetic)",
+                   "active_weight_bytes_per_token": nbytes, "resident_weight_bytes": int(r.resident_weight_bytes),
+                   "resident_kv_bytes": int(r.resident_kv_bytes)},
+        "clocks": clocks,
+        "e2e": {"value": args.steps / e2e_s, "unit": "tok/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 44},
+        "roofline": {"bound": "hbm", "kernel": "whole step (projection, latent attention and expert stream kernels)",
+                     "achieved": nbytes / device_s * args.steps / 1e9, "peak": peaks["hbm_gbs"], "unit": "GB/s",
+                     "frac": nbytes / device_s * args.steps / 1e9 / peaks["hbm_gbs"], "peak_source": peaks["source"],
+                     "traffic": None},
+        "token_hash": f"{timed.observed_token_hash:016x}",
+        "setup_s": {"generate_weights": t1 - t0, "session_create": t2 - t1, "prefill": t3 - t2},
+    }), flush=True)
+    session.destroy()
+
+
 def run_operator_workloads(kind: str, only_shape: str = "", only_tokens: int = 0, only_batch: int = 0,
                            only_context: int = 0) -> None:
     """Per-operator sweeps (isolated projection shapes, long-context attention) through the per-op C ABI (host buffers in,
@@ -679,7 +748,7 @@ def main() -> None:
     ap.add_argument("--layers", type=int, default=0,
                     help="cut the model to this many layers (profiler captures only; not a bench line)")
     ap.add_argument("--prompt-tokens", type=int, default=0, help="override the prompt length")
-    ap.add_argument("--workload", default="decode", choices=["decode", "linear", "attention", "reference-gpu", "batch"],
+    ap.add_argument("--workload", default="decode", choices=["decode", "linear", "attention", "reference-gpu", "batch", "deepseek"],
                     help="decode: the bench line; linear / attention: per-operator sweeps of the isolated "
                          "projection shapes and of long-context attention (one JSON line per case)")
     ap.add_argument("--shape", default="", help="linear sweep: only this projection (qkv, o, gate_up, down, lm_head)")
@@ -714,6 +783,10 @@ def main() -> None:
     if args.workload == "batch":
         if rank == 0:
             run_batch_workload(args, cfg)
+        return
+    if args.workload == "deepseek":
+        if rank == 0:
+            run_deepseek_workload(args)
         return
     if args.impl == "reference":
         if rank == 0:

@@ -862,6 +862,15 @@ typedef struct NervaB200ShardInfo {
   uint32_t world;        /* 2, 4 or 8 (any value in 2..8 that divides the head counts) */
   uint32_t full_vocab;   /* rows of the embedding table */
   uint32_t vocab_offset; /* first lm_head row of this rank */
+  uint32_t mode;         /* 0: tensor parallel (dense layers: heads, intermediate size and lm_head rows are
+                          * cut).  1: expert parallel (sparse-MoE models): every rank holds the whole model
+                          * except the routed experts, of which it holds num_experts / world consecutive
+                          * ones starting at rank * num_experts / world, and the shared expert, of which it
+                          * holds an equal slice of the intermediate dimension (the request's
+                          * shared_expert_intermediate is the slice's size, num_experts stays the layer's
+                          * total); full_vocab = vocab_size, vocab_offset = 0.  The ranks' partial MLP
+                          * outputs are exchanged like the tensor-parallel partial sums.  Needs an even
+                          * number of sparse layers. */
 } NervaB200ShardInfo;
 int nerva_b200_session_create_sharded(const NervaCudaHfDecodeSequenceSessionCreateRequest *request,
                                       const NervaB200ShardInfo *shard,

@@ -26,6 +26,7 @@
 #include <cuda.h>
 #include <cudaTypedefs.h>
 #include <math.h>
+#include <string.h>
 
 #include "common.cuh"
 #include "kernels.cuh"
@@ -95,10 +96,16 @@ __device__ __forceinline__ uint32_t swizzled(uint32_t row, uint32_t piece) {
   return row * 128u + ((piece ^ (row & 7u)) << 4);
 }
 
-template <uint32_t D>
-__global__ void __launch_bounds__(kAttnWarps * 32, kAttnBlocksPerSm)
-gqa_decode_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v,
-                  AttentionParams p) {
+// The K / V tensor-map pairs of the caches a row-form launch spans (kernel parameter space).
+struct RowCacheMaps {
+  CUtensorMap k[kAttentionRowCaches], v[kAttentionRowCaches];
+};
+
+// One block's work.  ROWS: sequence b is row b of a block step (p.rows[b]); the maps are that
+// row's cache, whose pages of layer p.layer start at row p.layer * pages * 16 of the 2-D view.
+template <uint32_t D, bool ROWS>
+__device__ __forceinline__ void gqa_decode_block(const CUtensorMap *map_k_all, const CUtensorMap *map_v_all,
+                                                 const AttentionParams &p) {
   using L = PagedLayout<D>;
   constexpr uint32_t kKSteps = D / 16u;   // mma k-steps of q.k
   constexpr uint32_t kNTiles = D / 8u;    // mma n-tiles of p.v
@@ -113,18 +120,36 @@ gqa_decode_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_consta
   const uint32_t G = p.heads / p.kv_heads;
   // q, the cache, the page table and the cursor are inputs that an earlier launch of this pair
   // never writes; only the partial buffers below are shared with the previous launch's merge
-  if (p.cursor != nullptr) pdl_wait();  // the cursor comes from the step's previous kernel
-  const uint32_t context = p.cursor != nullptr ? *p.cursor + 1u : p.context;
+  if (ROWS || p.cursor != nullptr) pdl_wait();  // the cursor, or the row's q and newest cache row, come from the previous kernel
+  const CUtensorMap *map_k = map_k_all, *map_v = map_v_all;
+  const float *q_row;
+  const uint32_t *table;
+  uint32_t context, page_count, y_base;
+  if (ROWS) {
+    const FusedAttentionRow &r = p.rows[b];
+    map_k += r.map_index;
+    map_v += r.map_index;
+    q_row = r.qkv;
+    table = r.page_table;
+    context = r.position + 1u;
+    page_count = r.page_count;
+    y_base = p.layer * r.page_count * kPageTokens;
+  } else {
+    q_row = p.q + static_cast<uint64_t>(b) * p.heads * D;
+    table = p.page_table + static_cast<uint64_t>(b) * p.page_count;
+    context = p.cursor != nullptr ? *p.cursor + 1u : p.context;
+    page_count = p.page_count;
+    y_base = b * p.page_count * kPageTokens;  // row of the [batch * pages * 16][kv_hidden] view
+  }
   const uint32_t pages_total = (context + kPageTokens - 1u) / kPageTokens;
   const uint32_t pages_per_split = (pages_total + p.splits - 1u) / p.splits;
   const uint32_t page_begin = split * pages_per_split;
   uint32_t page_end = page_begin + pages_per_split;
   if (page_end > pages_total) page_end = pages_total;
-  const uint32_t *table = p.page_table + static_cast<uint64_t>(b) * p.page_count;
 
   // q, pre-multiplied by log2(e)/sqrt(d) so that the softmax runs on exp2; rows beyond the group stay zero.
   const float qscale = kLog2e * rsqrtf(static_cast<float>(D));
-  const float *q_in = p.q + (static_cast<uint64_t>(b) * p.heads + kvh * G) * D;
+  const float *q_in = q_row + static_cast<uint64_t>(kvh) * G * D;
   for (uint32_t i = threadIdx.x; i < kMaxGroupHeads * D; i += blockDim.x) q_s[i] = i < G * D ? q_in[i] * qscale : 0.0f;
   if (lane == 0) {
     for (uint32_t s = 0; s < kAttnStages; ++s) mbar_init(&sh.full[warp][s], 1);
@@ -139,18 +164,18 @@ gqa_decode_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_consta
   auto issue = [&](uint32_t i) {  // lane 0 only
     const uint32_t logical = first + i * kAttnWarps;
     uint32_t phys = table[logical];
-    if (phys >= p.page_count) {
+    if (phys >= page_count) {
       report_error(p.error_word, kErrPageOutOfRange);
       phys = 0;
     }
     const uint32_t stage = i % kAttnStages;
     uint8_t *dst = ring + stage * L::kStageBytes;
-    const uint32_t y = (b * p.page_count + phys) * kPageTokens;  // row of the [batch * pages * 16][kv_hidden] view
+    const uint32_t y = y_base + phys * kPageTokens;
     mbar_arrive_expect_tx(&sh.full[warp][stage], L::kStageBytes);
 #pragma unroll
     for (uint32_t h = 0; h < L::kHalves; ++h) {
-      tma_load_box(dst + h * L::kBoxBytes, &map_k, kvh * D + h * 64u, y, &sh.full[warp][stage]);
-      tma_load_box(dst + (L::kHalves + h) * L::kBoxBytes, &map_v, kvh * D + h * 64u, y, &sh.full[warp][stage]);
+      tma_load_box(dst + h * L::kBoxBytes, map_k, kvh * D + h * 64u, y, &sh.full[warp][stage]);
+      tma_load_box(dst + (L::kHalves + h) * L::kBoxBytes, map_v, kvh * D + h * 64u, y, &sh.full[warp][stage]);
     }
   };
   if (lane == 0) {
@@ -319,6 +344,19 @@ gqa_decode_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_consta
   }
 }
 
+template <uint32_t D>
+__global__ void __launch_bounds__(kAttnWarps * 32, kAttnBlocksPerSm)
+gqa_decode_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v,
+                  AttentionParams p) {
+  gqa_decode_block<D, false>(&map_k, &map_v, p);
+}
+
+template <uint32_t D>
+__global__ void __launch_bounds__(kAttnWarps * 32, kAttnBlocksPerSm)
+gqa_decode_rows_kernel(const __grid_constant__ RowCacheMaps maps, AttentionParams p) {
+  gqa_decode_block<D, true>(maps.k, maps.v, p);
+}
+
 // Any head_dim <= 256 and any group size: one warp per query head, no split.
 __global__ void gqa_decode_generic_kernel(AttentionParams p) {
   const uint32_t head = blockIdx.x, b = blockIdx.y, lane = threadIdx.x;
@@ -420,6 +458,12 @@ cudaError_t configure_attention_kernels() {
   if (err == cudaSuccess)
     err = cudaFuncSetAttribute(gqa_decode_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                static_cast<int>(paged_smem_bytes<64>()));
+  if (err == cudaSuccess)
+    err = cudaFuncSetAttribute(gqa_decode_rows_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                               static_cast<int>(paged_smem_bytes<128>()));
+  if (err == cudaSuccess)
+    err = cudaFuncSetAttribute(gqa_decode_rows_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                               static_cast<int>(paged_smem_bytes<64>()));
   return err;
 }
 
@@ -481,6 +525,41 @@ cudaError_t launch_attention(cudaStream_t stream, const AttentionParams &p) {
   uint32_t threads = ((p.head_dim + 31u) / 32u) * 32u;
   if (threads > 256) threads = 256;
   return launch_with_pdl(gqa_merge_kernel, dim3(p.heads, p.batch), dim3(threads), 0, stream, paged, p);
+}
+
+bool attention_rows_supported(uint32_t heads, uint32_t kv_heads, uint32_t head_dim) {
+  return (head_dim == 128 || head_dim == 64) && kv_heads != 0 && heads % kv_heads == 0 &&
+         heads / kv_heads <= kMaxGroupHeads && tensor_map_available();
+}
+
+uint32_t attention_rows_splits(uint32_t longest_context, uint32_t rows, uint32_t kv_heads, uint32_t sm_count) {
+  const uint32_t splits = attention_default_splits(longest_context, rows, kv_heads, sm_count);
+  return splits > 16u ? 16u : splits;  // the block steps keep 16 partial slots per (row, head)
+}
+
+cudaError_t launch_attention_rows(cudaStream_t stream, const AttentionParams &p, const TensorMapStorage *k_maps,
+                                  const TensorMapStorage *v_maps, uint32_t caches) {
+  if (p.rows == nullptr || p.batch == 0 || p.splits == 0 || p.splits > 16u || caches == 0 ||
+      caches > kAttentionRowCaches || !attention_rows_supported(p.heads, p.kv_heads, p.head_dim))
+    return cudaErrorInvalidValue;
+  static_assert(sizeof(TensorMapStorage) == sizeof(CUtensorMap), "a tensor map is 128 bytes");
+  RowCacheMaps maps;
+  for (uint32_t i = 0; i < kAttentionRowCaches; ++i) {
+    const uint32_t from = i < caches ? i : 0;  // unused entries repeat the first pair
+    memcpy(&maps.k[i], &k_maps[from], sizeof(CUtensorMap));
+    memcpy(&maps.v[i], &v_maps[from], sizeof(CUtensorMap));
+  }
+  const dim3 grid(p.splits, p.kv_heads, p.batch);
+  cudaError_t err;
+  if (p.head_dim == 128)
+    err = launch_with_pdl(gqa_decode_rows_kernel<128>, grid, dim3(kAttnWarps * 32), paged_smem_bytes<128>(), stream,
+                          true, maps, p);
+  else
+    err = launch_with_pdl(gqa_decode_rows_kernel<64>, grid, dim3(kAttnWarps * 32), paged_smem_bytes<64>(), stream, true,
+                          maps, p);
+  if (err != cudaSuccess) return err;
+  uint32_t threads = ((p.head_dim + 31u) / 32u) * 32u;
+  return launch_with_pdl(gqa_merge_kernel, dim3(p.heads, p.batch), dim3(threads), 0, stream, true, p);
 }
 
 }  // namespace nb

@@ -11,6 +11,9 @@
 // the residual add in its epilogue -> RMSNorm -> gate/up block projection with SwiGLU in its
 // epilogue -> down block projection with the residual add.  The projections are the tcgen05 block
 // kernel (gemm_tc.cu); attention is the session's own fused kernel in its row form.
+#include <stdlib.h>
+#include <string.h>
+
 #include <algorithm>
 #include <vector>
 
@@ -62,22 +65,43 @@ __global__ void __launch_bounds__(kNormThreads) block_norm_kernel(const float *h
 // Prefill: K (k-norm + RoPE) and V of every row of the chunk, rounded to bf16, into the row's page.
 // One warp per (KV head, row); the same functions, in the same order, as the decode step's append
 // (attention_fused.cu), so the cached bits are those the decode step would have written.
+// Blocks beyond the KV heads (the grid has kv_heads + heads of them per row when prepare_q is set)
+// do the query side for the paged attention kernel: bias, q-norm and RoPE of one query head, written
+// back in place as fp32 (that kernel reads its queries ready-made).
 template <uint32_t PER>
 __global__ void block_kv_publish_kernel(const FusedAttentionRow *rows, uint32_t layer, uint32_t heads, uint32_t kv_heads,
                                         const uint16_t *k_bias, const uint16_t *v_bias, const uint16_t *k_norm,
-                                        float eps, float rope_theta) {
+                                        const uint16_t *q_bias, const uint16_t *q_norm, float eps, float rope_theta) {
   constexpr uint32_t D = PER * 32u;
   pdl_trigger();
   const FusedAttentionRow r = rows[blockIdx.y];
-  const uint32_t kvh = blockIdx.x, lane = threadIdx.x & 31u;
+  const uint32_t lane = threadIdx.x & 31u;
+  const bool query = blockIdx.x >= kv_heads;
+  const uint32_t kvh = blockIdx.x;
   const uint32_t attention_hidden = heads * D, kv_hidden = kv_heads * D;
+  const uint16_t *norm = query ? q_norm : k_norm;
   float norm_w[PER];
 #pragma unroll
-  for (uint32_t k = 0; k < PER; ++k) norm_w[k] = k_norm != nullptr ? bf16_bits_to_f32(k_norm[lane + 32u * k]) : 1.0f;
+  for (uint32_t k = 0; k < PER; ++k) norm_w[k] = norm != nullptr ? bf16_bits_to_f32(norm[lane + 32u * k]) : 1.0f;
   RopeFactors<PER> rope;
   rope_factors<PER>(rope, rope_theta, r.position);
   pdl_wait();
   if (r.position >= r.max_context) return;
+  if (query) {
+    const uint32_t h = blockIdx.x - kv_heads;
+    float *q = const_cast<float *>(r.qkv) + h * D;  // the row's projection output is scratch of the block step
+    float qn[PER];
+#pragma unroll
+    for (uint32_t k = 0; k < PER; ++k) {
+      const uint32_t e = lane + 32u * k;
+      qn[k] = __ldcg(q + e);
+      if (q_bias != nullptr) qn[k] += bf16_bits_to_f32(q_bias[h * D + e]);
+    }
+    head_norm_rope_pre<PER>(qn, q_norm != nullptr, norm_w, eps, rope);
+#pragma unroll
+    for (uint32_t k = 0; k < PER; ++k) q[lane + 32u * k] = qn[k];
+    return;
+  }
   float kn[PER], vn[PER];
 #pragma unroll
   for (uint32_t k = 0; k < PER; ++k) {
@@ -199,6 +223,10 @@ struct BlockPlan {
   uint32_t splits;       // attention spans per KV head (covers the longest row)
   bool publish;          // prefill: K/V of all rows published before attention (cached_only)
   bool pdl;
+  // Attention on the paged tensor-pipe kernel (attention.cu) instead of the fused kernel's row form:
+  // the tensor maps of the caches the rows live in (rows[r].map_index), or empty for the fused kernel.
+  std::vector<TensorMapStorage> k_maps, v_maps;
+  uint32_t longest = 0;  // longest context among the rows
 };
 
 cudaError_t block_gemm(const BlockPlan &b, const uint16_t *weight, uint32_t rows, uint32_t cols, const uint16_t *x,
@@ -244,19 +272,39 @@ cudaError_t enqueue_block_layers(const BlockPlan &b, uint64_t *launches) {
       err = block_gemm(b, s->weights->qkv_packed + static_cast<uint64_t>(l) * qkv_rows * d.hidden, qkv_rows, d.hidden,
                        ws.x_bf16, d.hidden, kEpilogueStore, nullptr, ws.qkv, nullptr);
     n += 2;
-    if (err == cudaSuccess && b.publish) {
-      const dim3 grid(d.kv_heads, b.rows);
+    const bool paged = !b.k_maps.empty();
+    if (err == cudaSuccess && (b.publish || paged)) {
+      const dim3 grid(d.kv_heads + (paged ? d.heads : 0u), b.rows);
       if (d.head_dim == 128)
         err = launch_with_pdl(block_kv_publish_kernel<4>, grid, dim3(32), 0, b.stream, b.pdl, ws.attn_rows, l, d.heads,
                               d.kv_heads, arena_at(s, L.k_bias), arena_at(s, L.v_bias), arena_at(s, L.k_norm),
-                              s->rms_eps, s->rope_theta);
+                              arena_at(s, L.q_bias), arena_at(s, L.q_norm), s->rms_eps, s->rope_theta);
       else
         err = launch_with_pdl(block_kv_publish_kernel<2>, grid, dim3(32), 0, b.stream, b.pdl, ws.attn_rows, l, d.heads,
                               d.kv_heads, arena_at(s, L.k_bias), arena_at(s, L.v_bias), arena_at(s, L.k_norm),
-                              s->rms_eps, s->rope_theta);
+                              arena_at(s, L.q_bias), arena_at(s, L.q_norm), s->rms_eps, s->rope_theta);
       n += 1;
     }
     if (err != cudaSuccess) break;
+    if (paged) {
+      // every row's K/V (its own newest row included) is in its cache and its queries are prepared
+      AttentionParams ap{};
+      ap.batch = b.rows;
+      ap.heads = d.heads;
+      ap.kv_heads = d.kv_heads;
+      ap.head_dim = d.head_dim;
+      ap.splits = attention_rows_splits(b.longest, b.rows, d.kv_heads, s->sm_count);
+      ap.partial_acc = ws.partial_acc;
+      ap.partial_m = ws.partial_m;
+      ap.partial_l = ws.partial_l;
+      ap.out_bf16 = ws.attn;
+      ap.error_word = s->device_error;
+      ap.rows = ws.attn_rows;
+      ap.layer = l;
+      err = launch_attention_rows(b.stream, ap, b.k_maps.data(), b.v_maps.data(), static_cast<uint32_t>(b.k_maps.size()));
+      n += 2;
+      if (err != cudaSuccess) break;
+    } else {
     FusedAttentionParams fp{};
     fp.max_context = s->max_context;
     fp.q_bias = arena_at(s, L.q_bias);
@@ -278,6 +326,7 @@ cudaError_t enqueue_block_layers(const BlockPlan &b, uint64_t *launches) {
     err = launch_fused_attention(b.stream, fp);
     n += 1;
     if (err != cudaSuccess) break;
+    }
     // h_a = h_b + O(attention)
     err = block_gemm(b, arena_at(s, L.w_o), d.hidden, ah, ws.attn, ah, kEpilogueStore, ws.h_b, ws.h_a, nullptr);
     // MLP half
@@ -385,6 +434,10 @@ cudaError_t allocate_block_workspace(NervaCudaHfDecodeSequenceSession *s) {
     err = cudaMemsetAsync(ws.gemm_tickets, 0, static_cast<uint64_t>(gemm_tc_ticket_count(max_out)) * sizeof(uint32_t),
                           s->stream);
   if (err == cudaSuccess) err = configure_gemm_tc_kernel();
+  // NERVA_B200_ROW_ATTENTION=fused keeps the fused kernel's row form (comparison and fallback)
+  const char *row_attention = getenv("NERVA_B200_ROW_ATTENTION");
+  ws.paged_rows = attention_rows_supported(d.heads, d.kv_heads, d.head_dim) &&
+                  !(row_attention != nullptr && strcmp(row_attention, "fused") == 0);
   return err;
 }
 
@@ -398,15 +451,25 @@ cudaError_t enqueue_block_decode(NervaCudaHfDecodeSequenceSession *const *sessio
   std::vector<FusedAttentionRow> attn(count);
   std::vector<BlockTokenRow> tokens(count);
   uint32_t longest = 0;
+  bool paged = ws.paged_rows && count <= kAttentionRowCaches;
   for (uint32_t r = 0; r < count; ++r) {
     Session *s = sessions[r];
     attn[r] = attention_row(s, ws, r, s->cursor);
+    attn[r].map_index = r;  // every session brings its own cache
     tokens[r] = token_row(s, s->cursor);
     longest = std::max(longest, s->cursor + 1u);
+    paged = paged && s->kv_maps;
   }
   cudaError_t err = upload_rows(ws, attn, tokens, stream);
   if (err != cudaSuccess) return err;
   BlockPlan b{model, stream, count, block_attention_splits(model, count, longest), false, model->use_pdl};
+  b.longest = longest;
+  if (paged) {
+    for (uint32_t r = 0; r < count; ++r) {
+      b.k_maps.push_back(sessions[r]->kv_map_k);
+      b.v_maps.push_back(sessions[r]->kv_map_v);
+    }
+  }
   uint64_t n = 0;
   err = enqueue_block_layers(b, &n);
   // final norm, lm_head, arg-max: per row
@@ -460,6 +523,11 @@ cudaError_t enqueue_chunked_prefill(NervaCudaHfDecodeSequenceSession *s, uint32_
     err = upload_rows(ws, attn, tokens, s->stream);
     if (err != cudaSuccess) break;
     BlockPlan b{s, s->stream, rows, block_attention_splits(s, rows, begin + rows), true, s->use_pdl};
+    b.longest = begin + rows;
+    if (ws.paged_rows && s->kv_maps) {
+      b.k_maps.push_back(s->kv_map_k);  // all rows of a chunk live in this session's cache (map_index 0)
+      b.v_maps.push_back(s->kv_map_v);
+    }
     err = enqueue_block_layers(b, launches);
     if (err == cudaSuccess && begin + rows == prompt_count) {
       // the last position's residual stream becomes the session's own, where the head expects it

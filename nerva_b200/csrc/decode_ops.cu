@@ -311,6 +311,42 @@ cudaError_t launch_sample_greedy(cudaStream_t stream, const StepState &st, const
                          best_index, partials, sample, exchange);
 }
 
+// A step that does not sample has no head projection, so nothing reads the last exchange of its
+// layers.  This kernel reads it instead: one block waits (bounded, like every peer wait) until all
+// ranks' entries of that exchange carry the step's tag.  With it every push of a step is followed
+// by a wait on the same exchange before the rank can push into that buffer again, which is what
+// keeps a rank that runs ahead from overwriting entries a slower rank is still polling.
+__global__ void __launch_bounds__(256) exchange_wait_kernel(TpGather g, uint32_t cols, uint32_t *error_word) {
+  pdl_trigger();
+  pdl_wait();
+  const uint32_t tag = static_cast<uint32_t>(*g.epoch) * g.per_epoch + g.offset;
+  const uint32_t total = g.world * cols;
+  const long long start = clock64();
+  bool gave_up = false;
+  for (uint32_t i = threadIdx.x; i < total && !gave_up; i += blockDim.x) {
+    uint32_t polls = 0;
+    for (;;) {
+      unsigned long long v;
+      asm volatile("ld.volatile.global.u64 %0, [%1];" : "=l"(v) : "l"(g.recv + i) : "memory");
+      if (static_cast<uint32_t>(v >> 32) == tag) break;
+      if ((polls++ & 63u) == 0) {
+        if (step_already_failed(error_word)) {
+          gave_up = true;
+        } else if (clock64() - start > kPeerWaitCycleLimit) {
+          gave_up = true;
+          report_error(error_word, kErrPeerWaitTimeout);
+        }
+        if (gave_up) break;
+      }
+    }
+  }
+}
+
+cudaError_t launch_exchange_wait(cudaStream_t stream, const TpGather &gather, uint32_t cols, uint32_t *error_word,
+                                 bool pdl) {
+  return launch_with_pdl(exchange_wait_kernel, dim3(1), dim3(256), 0, stream, pdl, gather, cols, error_word);
+}
+
 cudaError_t launch_argmax(cudaStream_t stream, const float *logits, uint32_t count,
                           uint32_t *token_out) {
   argmax_kernel<<<1, 1024, 0, stream>>>(logits, count, token_out);

@@ -232,55 +232,89 @@ __device__ __forceinline__ void tile_epilogue(const GemmKernelParams &p, const f
   }
 }
 
-// Finishes the row tiles that more than one block of gemm_tc_kernel contributed to.  Grid
-// (blocks of the projection launch, n_pad / 16); block b is responsible for the tile its run began
-// in when that tile is split and b is the last block to touch it; it adds the partials in
-// ascending block order (bit-stable) and runs the epilogue.  Other blocks leave at once.
-__global__ void __launch_bounds__(kEpilogueThreads) gemm_fixup_kernel(GemmKernelParams p, uint32_t gemm_blocks) {
-  pdl_trigger();
-  const Partition part = make_partition(p.rows, p.cols, gemm_blocks);
-  const uint32_t b = blockIdx.x;
-  const uint64_t begin = part.begin(b), end = part.end(b);
-  const uint32_t tile = static_cast<uint32_t>(begin / part.slices);
-  const bool mine = begin % part.slices != 0 && end >= static_cast<uint64_t>(tile + 1u) * part.slices;
-  if (!mine) return;
-  pdl_wait();  // the partials come from the projection launch just before
-  const uint32_t b_lo = first_block_of_tile(part, tile);
-  const uint32_t row_in_tile = threadIdx.x, lane = threadIdx.x & 31u;
-  const uint32_t g = blockIdx.y * kGroup;
-  const uint64_t slot_floats = static_cast<uint64_t>(p.n_pad) * kTileRows;
-  float v[kGroup];
-  for (uint32_t q = b_lo; q <= b; q += 2u) {
-    // two contributors' loads in flight together
-    float4 x[2][kGroup / 4u];
+// Finishes the row tiles that more than one block of gemm_tc_kernel contributed to.  Grid (row
+// tiles, n_pad / 16), block (128 rows, 4 groups of 4 tokens): a thread adds the partials of its four
+// values in ascending block order (bit-stable) with the loads of up to eight contributors in flight
+// together, and runs the epilogue.  Blocks of tiles that one projection block covered alone (it has
+// written them itself) leave at once.
+constexpr uint32_t kFixupMaxListed = 320;  // contributors whose slots are looked up once, in shared memory
+constexpr uint32_t kFixupBatch = 8;
+
+__device__ __forceinline__ void fixup_epilogue(const GemmKernelParams &p, const float4 &v, uint32_t row, uint32_t m0) {
+  const float vals[4] = {v.x, v.y, v.z, v.w};
+  if (p.epilogue == kEpilogueSwiglu) {
+    // rows interleaved (gate, up): the neighbouring lane holds the other half of the pair
 #pragma unroll
-    for (uint32_t u = 0; u < 2u; ++u) {
-      const uint32_t bb = q + u <= b ? q + u : b;
-      const float *src = p.workspace + partial_slot(part, bb, tile) * slot_floats +
-                         static_cast<uint64_t>(row_in_tile) * p.n_pad + g;
-#pragma unroll
-      for (uint32_t j = 0; j < kGroup / 4u; ++j) x[u][j] = __ldcg(reinterpret_cast<const float4 *>(src) + j);
+    for (uint32_t j = 0; j < 4u; ++j) {
+      const float other = __shfl_xor_sync(0xffffffffu, vals[j], 1);
+      const uint32_t m = m0 + j;
+      if ((threadIdx.x & 1u) == 0 && row + 1u < p.rows && m < p.tokens)
+        p.out_bf16[static_cast<uint64_t>(m) * (p.rows / 2u) + row / 2u] = f32_to_bf16_bits(silu(vals[j]) * other);
     }
+  } else if (row < p.rows) {
 #pragma unroll
-    for (uint32_t u = 0; u < 2u; ++u) {
-      if (q + u > b) break;
-#pragma unroll
-      for (uint32_t j = 0; j < kGroup / 4u; ++j) {
-        if (q + u == b_lo) {
-          v[4u * j] = x[u][j].x;
-          v[4u * j + 1u] = x[u][j].y;
-          v[4u * j + 2u] = x[u][j].z;
-          v[4u * j + 3u] = x[u][j].w;
-        } else {
-          v[4u * j] += x[u][j].x;
-          v[4u * j + 1u] += x[u][j].y;
-          v[4u * j + 2u] += x[u][j].z;
-          v[4u * j + 3u] += x[u][j].w;
-        }
+    for (uint32_t j = 0; j < 4u; ++j) {
+      const uint32_t m = m0 + j;
+      if (m < p.tokens) {
+        const uint64_t at = static_cast<uint64_t>(m) * p.rows + row;
+        p.out_f32[at] = p.resid_in != nullptr ? vals[j] + __ldcg(p.resid_in + at) : vals[j];
       }
     }
   }
-  tile_epilogue(p, v, tile * kTileRows + row_in_tile, g, lane);
+}
+
+__global__ void __launch_bounds__(4 * kTileRows) gemm_fixup_kernel(GemmKernelParams p, uint32_t gemm_blocks) {
+  __shared__ uint32_t range[2];
+  __shared__ uint32_t slots[kFixupMaxListed];
+  pdl_trigger();
+  const Partition part = make_partition(p.rows, p.cols, gemm_blocks);
+  const uint32_t tile = blockIdx.x;
+  const uint32_t tid = threadIdx.y * blockDim.x + threadIdx.x;
+  if (tid == 0) {
+    const uint64_t last_slice = static_cast<uint64_t>(tile + 1u) * part.slices - 1u;
+    uint32_t hi = static_cast<uint32_t>(last_slice * part.blocks / part.total);
+    while (hi + 1u < part.blocks && part.end(hi) <= last_slice) ++hi;
+    while (hi > 0 && part.begin(hi) > last_slice) --hi;
+    range[0] = first_block_of_tile(part, tile);
+    range[1] = hi;
+  }
+  __syncthreads();
+  const uint32_t lo = range[0], hi = range[1];
+  if (lo == hi) return;  // one block covered the tile: nothing to add
+  const uint32_t count = hi - lo + 1u;
+  const bool listed = count <= kFixupMaxListed;
+  if (listed) {
+    for (uint32_t i = tid; i < count; i += blockDim.x * blockDim.y) slots[i] = partial_slot(part, lo + i, tile);
+  }
+  __syncthreads();
+  pdl_wait();  // the partials come from the projection launch just before
+  const uint32_t row_in_tile = threadIdx.x;
+  const uint32_t m0 = blockIdx.y * kGroup + 4u * threadIdx.y;
+  const uint64_t slot_floats = static_cast<uint64_t>(p.n_pad) * kTileRows;
+  const float *base = p.workspace + static_cast<uint64_t>(row_in_tile) * p.n_pad + m0;
+  float4 v = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+  for (uint32_t q = 0; q < count; q += kFixupBatch) {
+    float4 x[kFixupBatch];
+#pragma unroll
+    for (uint32_t u = 0; u < kFixupBatch; ++u) {
+      const uint32_t i = q + u < count ? q + u : count - 1u;
+      const uint32_t slot = listed ? slots[i] : partial_slot(part, lo + i, tile);
+      x[u] = __ldcg(reinterpret_cast<const float4 *>(base + slot * slot_floats));
+    }
+#pragma unroll
+    for (uint32_t u = 0; u < kFixupBatch; ++u) {
+      if (q + u >= count) break;
+      if (q + u == 0) {
+        v = x[u];
+      } else {
+        v.x += x[u].x;
+        v.y += x[u].y;
+        v.z += x[u].z;
+        v.w += x[u].w;
+      }
+    }
+  }
+  fixup_epilogue(p, v, tile * kTileRows + row_in_tile, m0);
 }
 
 __global__ void __launch_bounds__(kGemmThreads, 2)
@@ -579,7 +613,7 @@ cudaError_t launch_gemm_tc(cudaStream_t stream, const GemmParams &g, uint32_t sm
   bool split = false;
   for (uint32_t b = 0; b < blocks && !split; ++b) split = part.begin(b) % part.slices != 0;
   if (!split) return cudaSuccess;
-  return launch_with_pdl(gemm_fixup_kernel, dim3(blocks, p.n_pad / kGroup), dim3(kEpilogueThreads), 0, stream, true, p,
+  return launch_with_pdl(gemm_fixup_kernel, dim3(part.tiles, p.n_pad / kGroup), dim3(kTileRows, 4), 0, stream, true, p,
                          blocks);
 }
 

@@ -177,8 +177,27 @@ struct AttentionParams {
   float *out_f32;              // [batch][heads*d] optional
   uint16_t *out_bf16;          // optional
   uint32_t *error_word;
+  // Row form (launch_attention_rows): sequence b of the batch is row b of a block step; its q
+  // (normalised, rotated, fp32, at the start of the row's projection output), cache, page table
+  // and context (position + 1) come from rows[b], q / key_pages / value_pages / page_table /
+  // cursor / context above are unused.  `layer` selects the layer inside the row's cache.
+  const struct FusedAttentionRow *rows;
+  uint32_t layer;
 };
 cudaError_t launch_attention(cudaStream_t stream, const AttentionParams &p);
+// 128 opaque bytes of a tensor map, encoded once per cache by encode_bf16_map_2d (gemm_tc.cu).
+struct alignas(64) TensorMapStorage {
+  unsigned char bytes[128];
+};
+// Caches one launch of the row form may span (rows[b].map_index selects the pair).
+constexpr uint32_t kAttentionRowCaches = 32;
+// The row form of the paged tensor-pipe kernel + its merge: head_dim 64 or 128, at most 8 query
+// heads per KV head, at most 16 spans (the block steps' partial buffers).  k_maps / v_maps: host
+// arrays of `caches` tensor maps over [layers * pages * 16][kv_hidden] bf16, boxes of 64 x 16.
+bool attention_rows_supported(uint32_t heads, uint32_t kv_heads, uint32_t head_dim);
+uint32_t attention_rows_splits(uint32_t longest_context, uint32_t rows, uint32_t kv_heads, uint32_t sm_count);
+cudaError_t launch_attention_rows(cudaStream_t stream, const AttentionParams &p, const TensorMapStorage *k_maps,
+                                  const TensorMapStorage *v_maps, uint32_t caches);
 cudaError_t configure_attention_kernels();
 uint32_t attention_default_splits(uint32_t context, uint32_t batch, uint32_t kv_heads,
                                   uint32_t sm_count);
@@ -188,7 +207,8 @@ uint32_t attention_default_splits(uint32_t context, uint32_t batch, uint32_t kv_
 // per-row replacements of the single-session fields of FusedAttentionParams.
 struct FusedAttentionRow {
   uint32_t position;       // position of this row's token
-  uint32_t max_context, page_count, reserved;
+  uint32_t max_context, page_count;
+  uint32_t map_index;      // row form of the paged tensor-pipe kernel: which cache of the launch is this row's
   const float *qkv;        // this row's projection output
   uint16_t *key_pages, *value_pages;  // layer 0 of the row's session; the kernel adds layer * kv_layer_elems
   uint64_t kv_layer_elems;
@@ -278,6 +298,14 @@ struct MoeExpertParams {
   float *out_f32;                    // [hidden] the MLP output
   uint32_t *error_word;
   uint32_t max_intermediate, max_rows_per_block;  // filled by the launcher
+  // Expert parallel: this rank holds experts [expert_base, expert_base + expert_local) of the layer
+  // (the matrices above are indexed by id - expert_base) and, of the shared expert, a slice of the
+  // intermediate dimension; chosen experts held elsewhere are skipped.  With push.world > 1 the
+  // partial MLP output goes, tagged, into every rank's receive buffer instead of out_f32, and the
+  // next norm prologue adds the ranks' partials in rank order (TpPush / TpGather).
+  // expert_local == 0 means all experts are here.
+  uint32_t expert_base, expert_local;
+  TpPush push;
 };
 bool moe_supported(uint32_t hidden, uint32_t moe_intermediate, uint32_t shared_intermediate,
                    uint32_t num_experts, uint32_t top_k, uint32_t sm_count);
@@ -303,6 +331,10 @@ struct TpSample {
 cudaError_t launch_sample_greedy(cudaStream_t stream, const StepState &st, const float *best_value,
                                  const uint32_t *best_index, uint32_t partials, uint32_t sample,
                                  bool pdl = false, const TpSample *tp = nullptr);
+// Waits (bounded) until every rank's entries of one exchange have arrived; closes a step that does
+// not sample, whose last exchange no projection reads.
+cudaError_t launch_exchange_wait(cudaStream_t stream, const TpGather &gather, uint32_t cols, uint32_t *error_word,
+                                 bool pdl);
 // ---- temperature / top-k / top-p sampling ----
 // Read from device memory at every step, so that a captured graph does not depend on the values.
 struct SamplerParams {

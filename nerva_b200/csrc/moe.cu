@@ -114,8 +114,9 @@ struct MoeShared {
   StreamShared stream;
   JobDesc jobs[kMoeMaxJobs];
   float scratch[40];
-  uint32_t ids[kMoeMaxTopK];
-  float weights[kMoeMaxTopK + 1];  // [top_k] = the shared expert's gate
+  uint32_t ids[kMoeMaxTopK];       // the chosen experts held by this rank, as local indices, in routing order
+  float weights[kMoeMaxTopK + 1];  // their routing weights; [routed] = the shared expert's gate
+  uint32_t routed;                 // how many of the top_k experts are held here
 };
 
 __host__ __device__ inline uint32_t round128u(uint32_t v) { return (v + 127u) & ~127u; }
@@ -179,20 +180,30 @@ __global__ void __launch_bounds__(kStreamThreads, 1) moe_expert_kernel(MoeExpert
   float *row_total = reinterpret_cast<float *>(smem + kRingBytes + round128u(x_elems * 4u) +
                                                round128u(sizeof(MoeShared)));
   float *acc = row_total + p.max_rows_per_block;
-  const uint32_t experts = p.top_k + (p.shared_intermediate != 0 ? 1u : 0u);
-  const uint32_t job_count = PHASE == kGateUp ? 2u * experts : experts;
   pdl_trigger();
   // The job list depends on the routing result of this step.
   pdl_wait();
-  if (threadIdx.x < p.top_k) {
-    sh.ids[threadIdx.x] = p.expert_ids[threadIdx.x];
-    sh.weights[threadIdx.x] = p.route_weights[threadIdx.x];
+  if (threadIdx.x == 0) {
+    // routing order is kept; under expert parallel only the experts held here stay in the list
+    uint32_t routed = 0;
+    for (uint32_t r = 0; r < p.top_k; ++r) {
+      const uint32_t local = p.expert_ids[r] - p.expert_base;  // wraps to a large value below the base
+      if (p.expert_local == 0 || local < p.expert_local) {
+        sh.ids[routed] = local;
+        sh.weights[routed] = p.route_weights[r];
+        routed += 1;
+      }
+    }
+    sh.routed = routed;
   }
   __syncthreads();
+  const uint32_t routed = sh.routed;
+  const uint32_t experts = routed + (p.shared_intermediate != 0 ? 1u : 0u);
+  const uint32_t job_count = PHASE == kGateUp ? 2u * experts : experts;
   if (threadIdx.x < job_count) {
     const uint32_t j = threadIdx.x;
     const uint32_t r = PHASE == kGateUp ? j / 2u : j;
-    const bool is_shared = r >= p.top_k;
+    const bool is_shared = r >= routed;
     const uint64_t mi = p.moe_intermediate, h = p.hidden;
     JobDesc d{};
     d.unit = 1;
@@ -238,7 +249,7 @@ __global__ void __launch_bounds__(kStreamThreads, 1) moe_expert_kernel(MoeExpert
       if (threadIdx.x == 0) *p.shared_gate = p.w_shared_router != nullptr ? 1.0f / (1.0f + expf(-total)) : 1.0f;
     }
   } else if (p.shared_intermediate != 0 && threadIdx.x == 0) {
-    sh.weights[p.top_k] = __ldcg(p.shared_gate);
+    sh.weights[routed] = __ldcg(p.shared_gate);
   }
   __syncthreads();
 
@@ -276,7 +287,20 @@ __global__ void __launch_bounds__(kStreamThreads, 1) moe_expert_kernel(MoeExpert
   if (PHASE == kDown) {
     uint32_t row_begin, row_end;
     block_row_range(p.hidden, 1, blockIdx.x, gridDim.x, &row_begin, &row_end);
-    for (uint32_t r = threadIdx.x; r < row_end - row_begin; r += blockDim.x) p.out_f32[row_begin + r] = acc[r];
+    if (p.push.world > 1) {
+      // expert parallel: this rank's partial sum travels to every rank (projection.cu: the Store epilogue's push)
+      const unsigned long long tag =
+          static_cast<unsigned long long>(static_cast<uint32_t>(*p.push.epoch) * p.push.per_epoch + p.push.offset) << 32;
+      for (uint32_t r = threadIdx.x; r < row_end - row_begin; r += blockDim.x) {
+        const unsigned long long entry = tag | __float_as_uint(acc[r]);
+        const uint64_t at = static_cast<uint64_t>(p.push.rank) * p.hidden + row_begin + r;
+        for (uint32_t q = 0; q < p.push.world; ++q) {
+          asm volatile("st.volatile.global.u64 [%0], %1;" ::"l"(p.push.recv[q] + at), "l"(entry) : "memory");
+        }
+      }
+    } else {
+      for (uint32_t r = threadIdx.x; r < row_end - row_begin; r += blockDim.x) p.out_f32[row_begin + r] = acc[r];
+    }
   }
   stream_drain(rs);
 }

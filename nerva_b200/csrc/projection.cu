@@ -58,10 +58,12 @@ __device__ __noinline__ void gather_prologue(const ProjectionParams &p, uint16_t
 // TP = true adds the tensor-parallel exchange (gather in the AddNorm prologue, push in the
 // Store epilogue); the single-GPU instantiations carry none of that code.
 // Ring slots a block fills before the dependency wait of a norm prologue; the rest follow the
-// prologue's activation loads.  Measured on Qwen3-8B: 3 (the whole ring) 337.8, 2: 343.4-347.6,
-// 1: 342.8 tok/s; holding a slot back ahead of the plain vector copy of O/down as well: 346.7.
-// The tensor-parallel gather prologue polls its entries behind the same queue: 435 -> 449 tok/s at 2 GPUs
-// (its held-back slot is issued by the first stream_fill of stream_consume).
+// prologue's activation loads, which would otherwise queue behind a whole ring of bulk copies
+// although they are on the critical path and the ring is not.  Holding back one slot of three
+// measured best on the Qwen3-8B shapes (whole ring first: 2-3 % slower per token; two held back:
+// about 1 % slower; holding a slot back ahead of the plain vector copy of O/down too: no gain).
+// The tensor-parallel gather prologue polls its entries behind the same queue and gains the same
+// way (its held-back slot is issued by the first stream_fill of stream_consume).
 #ifndef NERVA_PREWAIT_SLOTS
 #define NERVA_PREWAIT_SLOTS (NERVA_STREAM_SLOTS - 1)
 #endif
@@ -115,8 +117,8 @@ __global__ void __launch_bounds__(kStreamThreads, 1) projection_stream_kernel(Pr
     uint4 *dst = reinterpret_cast<uint4 *>(x);
     for (uint32_t i = threadIdx.x; i < p.cols / 8u; i += blockDim.x) dst[i] = src[i];
     // The ring is full and the block is about to synchronise: let HBM bring the next bytes of every
-    // warp's span as far as L2 meanwhile (16 and 32 KiB per warp: 347-349 -> 350.5 tok/s; 64 KiB: 343.6;
-    // the same behind a norm prologue: no change).
+    // warp's span as far as L2 meanwhile (16 and 32 KiB per warp measured about 1 % faster per token,
+    // 64 KiB slower than none; the same behind a norm prologue: no change).
     stream_prefetch_l2(rs, kPlainL2PrefetchBytes);
   } else {
     if (TP && p.gather.world > 1 && p.add_b != nullptr) {

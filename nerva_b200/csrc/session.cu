@@ -148,8 +148,11 @@ ArenaLayout compute_arena_layout(const ModelDims &d, const NervaCudaHfDecodeChai
       l.w_o = push(c, hidden * heads * vdim);
       l.rms_mlp = push(c, hidden);
       if (layer.mlp_kind == NERVA_MLP_KIND_SPARSE_MOE) {
-        const uint64_t mi = layer.moe_intermediate, e = layer.num_experts, si = layer.shared_expert_intermediate;
-        l.w_router = push(c, e * hidden);
+        const uint64_t mi = layer.moe_intermediate, si = layer.shared_expert_intermediate;
+        const uint64_t e = layer.num_experts / d.ep_world;  // the experts held here
+        l.expert_local = static_cast<uint32_t>(e);
+        l.expert_base = static_cast<uint32_t>(e) * d.ep_rank;
+        l.w_router = push(c, static_cast<uint64_t>(layer.num_experts) * hidden);
         if (si != 0) {
           l.w_shared_gate = push(c, si * hidden);
           l.w_shared_up = push(c, si * hidden);
@@ -177,9 +180,11 @@ ArenaLayout compute_arena_layout(const ModelDims &d, const NervaCudaHfDecodeChai
     l.w_o = push(c, hidden * ah);
     l.rms_mlp = push(c, hidden);
     if (layer.mlp_kind == NERVA_MLP_KIND_SPARSE_MOE) {
-      const uint64_t mi = layer.moe_intermediate, e = layer.num_experts;
+      const uint64_t mi = layer.moe_intermediate, e = layer.num_experts / d.ep_world;
       const uint64_t si = layer.shared_expert_intermediate;
-      l.w_router = push(c, e * hidden);
+      l.expert_local = static_cast<uint32_t>(e);
+      l.expert_base = static_cast<uint32_t>(e) * d.ep_rank;
+      l.w_router = push(c, static_cast<uint64_t>(layer.num_experts) * hidden);
       l.w_expert_gate_up = push(c, e * mi * 2u * hidden);
       l.w_expert_down = push(c, e * hidden * mi);
       l.expert_stride = 2u * mi * hidden;
@@ -543,9 +548,19 @@ cudaError_t enqueue_step(Session *s, uint32_t splits, uint32_t sample, uint64_t 
   const uint64_t qkv_rows = d.qkv_rows();
   uint64_t n = 0;
   // tensor parallel: where the partial sums of O and down travel (see kernels.cuh: TpPush)
-  const bool tp = s->tp_world > 1;
-  if (tp && (!s->tp_attached || s->engine != 0)) return cudaErrorNotReady;
+  // expert parallel uses the same exchange buffers for the sparse MLPs' partial outputs; every
+  // other operator runs whole on every rank
+  const bool ep_on = s->tp_world > 1 && d.ep_world > 1;
+  const bool tp = s->tp_world > 1 && !ep_on;
+  if ((tp || ep_on) && (!s->tp_attached || s->engine != 0)) return cudaErrorNotReady;
   const CommLayout comm = comm_layout(s->tp_world, d.hidden);
+  // sparse layer number `ordinal` (counted from 0) exchanges through recv_d when even, recv_o when odd
+  auto ep_buffer = [&](uint32_t layer) {
+    uint32_t ordinal = 0;
+    for (uint32_t i = 0; i < layer; ++i) ordinal += s->layout.layers[i].mlp_kind == NERVA_MLP_KIND_SPARSE_MOE ? 1u : 0u;
+    return ordinal % 2u == 0 ? comm.recv_d : comm.recv_o;
+  };
+  auto sparse_layer = [&](uint32_t layer) { return s->layout.layers[layer].mlp_kind == NERVA_MLP_KIND_SPARSE_MOE; };
   auto push_to = [&](uint64_t recv, uint32_t exchange) {
     TpPush push{};
     push.world = s->tp_world;
@@ -603,6 +618,10 @@ cudaError_t enqueue_step(Session *s, uint32_t splits, uint32_t sample, uint64_t 
     if (tp && l != 0) {
       p.add_b = s->down;  // placeholder: the sum arrives in the exchange buffer
       p.gather = gather_from(comm.recv_d, l);  // down of layer l-1 was exchange number l
+    }
+    if (ep_on && l != 0 && sparse_layer(l - 1u)) {
+      p.add_b = s->down;  // placeholder: the ranks' partial MLP outputs arrive in the exchange buffer
+      p.gather = gather_from(ep_buffer(l - 1u), l);
     }
     p.norm_weight = arena_at(s, L.rms_attn);
     p.resid_out = fused_resid ? nullptr : s->h_a;
@@ -801,6 +820,9 @@ cudaError_t enqueue_step(Session *s, uint32_t splits, uint32_t sample, uint64_t 
       ep.shared_gate = s->shared_gate;
       ep.out_f32 = s->down;
       ep.error_word = s->device_error;
+      ep.expert_base = L.expert_base;
+      ep.expert_local = L.expert_local;
+      if (ep_on) ep.push = push_to(ep_buffer(l), l + 1u);
       err = launch_moe_experts(s->stream, ep, s->sm_count, s->use_pdl);
       n += 2;
       profile_mark(s, prof, kBucketDown);
@@ -871,6 +893,7 @@ cudaError_t enqueue_step(Session *s, uint32_t splits, uint32_t sample, uint64_t 
     if (tp) {
       p.gather = gather_from(comm.recv_d, d.layers);
     }
+    if (ep_on && sparse_layer(d.layers - 1u)) p.gather = gather_from(ep_buffer(d.layers - 1u), d.layers);
     p.norm_weight = arena_at(s, s->layout.final_norm);
     p.resid_out = fused_resid ? nullptr : s->h_a;
     p.epilogue = kEpilogueArgmax;
@@ -883,8 +906,24 @@ cudaError_t enqueue_step(Session *s, uint32_t splits, uint32_t sample, uint64_t 
     n += 1;
     profile_mark(s, prof, kBucketLmHead);
   }
+  if (err == cudaSuccess && sample == 0 && !head_only) {
+    // no head projection in this step: the last exchange of the layers is read here instead
+    if (tp) {
+      err = launch_exchange_wait(s->stream, gather_from(comm.recv_d, d.layers), d.hidden, s->device_error, s->use_pdl);
+      n += 1;
+    } else if (ep_on && sparse_layer(d.layers - 1u)) {
+      err = launch_exchange_wait(s->stream, gather_from(ep_buffer(d.layers - 1u), d.layers), d.hidden, s->device_error,
+                                 s->use_pdl);
+      n += 1;
+    }
+  }
   if (err == cudaSuccess) {
     TpSample exchange{};
+    if (ep_on) {
+      // every rank holds the whole head and samples alone; the step counter still advances
+      exchange.world = 1;
+      exchange.epoch = comm_at<unsigned long long>(s->comm_block, comm.epoch);
+    }
     if (tp) {
       exchange.world = s->tp_world;
       exchange.rank = s->tp_rank;
@@ -899,7 +938,7 @@ cudaError_t enqueue_step(Session *s, uint32_t splits, uint32_t sample, uint64_t 
       err = launch_sample_general(s->stream, st, s->logits, s->device_sampler, s->use_pdl);
     else
       err = launch_sample_greedy(s->stream, st, s->best_value, s->best_index, partials, sample, s->use_pdl,
-                                 tp ? &exchange : nullptr);
+                                 tp || ep_on ? &exchange : nullptr);
     n += 1;
     profile_mark(s, prof, kBucketSampling);
   }
@@ -1404,6 +1443,11 @@ cudaError_t allocate_state(Session *s, int32_t *stage) {
   if (err == cudaSuccess)
     err = cudaMemsetAsync(s->attn_tickets, 0, s->dims.heads * sizeof(uint32_t), s->stream);
   s->fused_attention = !s->dims.mla() && fused_attention_supported(s->dims.heads, s->dims.kv_heads, s->dims.head_dim);
+  if (!s->dims.mla() && attention_rows_supported(s->dims.heads, s->dims.kv_heads, s->dims.head_dim)) {
+    const uint64_t rows = static_cast<uint64_t>(s->dims.layers) * s->kv_pages * NERVA_KV_CACHE_BLOCK_TOKENS;
+    s->kv_maps = encode_bf16_map_2d(&s->kv_map_k, s->kv_keys, s->dims.kv_hidden(), rows, 64, NERVA_KV_CACHE_BLOCK_TOKENS) &&
+                 encode_bf16_map_2d(&s->kv_map_v, s->kv_values, s->dims.kv_hidden(), rows, 64, NERVA_KV_CACHE_BLOCK_TOKENS);
+  }
   const char *timeline_env = getenv("NERVA_B200_TIMELINE");
   s->timeline_on = timeline_env != nullptr && timeline_env[0] == '1';
   if (err == cudaSuccess)
@@ -1482,13 +1526,33 @@ static int create_session(const NervaCudaHfDecodeSequenceSessionCreateRequest *r
     // KV heads, intermediate size and lm_head rows); the embedding table is whole.
     if ((shard->world != 2 && shard->world != 4 && shard->world != 8) || shard->rank >= shard->world ||
         shard->full_vocab < request->vocab_size ||
-        static_cast<uint64_t>(shard->vocab_offset) + request->vocab_size > shard->full_vocab ||
-        request->planned_weight_blocks != 0) {
+        static_cast<uint64_t>(shard->vocab_offset) + request->vocab_size > shard->full_vocab || shard->mode > 1u ||
+        (shard->mode == 0u && request->planned_weight_blocks != 0)) {
       out->failure_stage = kStageInvalidRequest;
       return -1;
     }
     d.embed_vocab = shard->full_vocab;
     d.vocab_offset = shard->vocab_offset;
+    if (shard->mode == 1u) {
+      // An expert-parallel rank: the whole model except the routed experts (num_experts / world of
+      // every sparse layer) and the shared expert (a slice of its intermediate dimension).  The
+      // exchange alternates between two receive buffers from one sparse layer to the next, which
+      // closes over a step boundary only for an even number of sparse layers.
+      uint32_t sparse = 0;
+      bool ok = shard->full_vocab == request->vocab_size && shard->vocab_offset == 0;
+      for (uint32_t i = 0; ok && i < request->layer_count; ++i) {
+        const NervaCudaHfDecodeChainLayer &layer = request->layers[i];
+        if (layer.mlp_kind != NERVA_MLP_KIND_SPARSE_MOE) continue;
+        sparse += 1;
+        ok = layer.num_experts % shard->world == 0;
+      }
+      if (!ok || sparse == 0 || sparse % 2u != 0) {
+        out->failure_stage = kStageInvalidRequest;
+        return -1;
+      }
+      d.ep_world = shard->world;
+      d.ep_rank = shard->rank;
+    }
   }
   // Latent attention: every layer or none, one shape, value width = head_dim; its tensors have no
   // pointer fields in the layer struct, so they come through planned descriptors.
@@ -1508,7 +1572,7 @@ static int create_session(const NervaCudaHfDecodeSequenceSessionCreateRequest *r
       return -1;
     }
   }
-  if (mla_layers != 0 && (mla_layers != request->layer_count || shard != nullptr)) {
+  if (mla_layers != 0 && (mla_layers != request->layer_count || (shard != nullptr && shard->mode != 1u))) {
     out->failure_stage = kStageInvalidRequest;
     return -1;
   }
@@ -1596,10 +1660,10 @@ static int create_session(const NervaCudaHfDecodeSequenceSessionCreateRequest *r
   for (const LayerLayout &L : s->layout.layers) {
     if (L.mlp_kind != NERVA_MLP_KIND_SPARSE_MOE) continue;
     s->has_moe = true;
-    if (shard != nullptr || !moe_supported(d.hidden, L.moe_intermediate, L.shared_intermediate, L.num_experts, L.top_k,
+    if ((shard != nullptr && shard->mode != 1u) || !moe_supported(d.hidden, L.moe_intermediate, L.shared_intermediate, L.num_experts, L.top_k,
                                            s->sm_count)) {
       set_last_error("sparse MoE layer not supported: needs hidden and intermediate sizes that are multiples of 8, "
-                     "at most 256 experts and 16 per token, no tensor parallel");
+                     "at most 256 experts and 16 per token; several GPUs only as expert parallel");
       return create_fail(s, out, cudaErrorNotSupported, kStageInvalidRequest);
     }
   }

@@ -48,6 +48,8 @@ struct LayerLayout {
   // (expert_up_offset = moe_intermediate * hidden inside a stride of twice that); DeepSeek layers
   // hold all gate matrices, then all up matrices (weights_pack.inc.cu:303-312).
   uint64_t expert_stride = 0, expert_up_offset = 0;
+  // expert parallel: the experts whose matrices this arena holds (all of them otherwise)
+  uint32_t expert_base = 0, expert_local = 0;
 };
 
 struct ArenaLayout {
@@ -65,6 +67,8 @@ struct ModelDims {
   // latent attention (every layer, or none): rows of the fused query + latent projection and width
   // of a cache row; zero for ordinary attention
   uint32_t mla_rank = 0, mla_nope = 0, mla_rope = 0;
+  // expert parallel (ep_world > 1): this rank's arena holds num_experts / ep_world routed experts per layer
+  uint32_t ep_world = 1, ep_rank = 0;
   uint64_t attention_hidden() const { return static_cast<uint64_t>(heads) * head_dim; }
   uint64_t kv_hidden() const { return static_cast<uint64_t>(kv_heads) * head_dim; }
   bool mla() const { return mla_rank != 0; }
@@ -112,6 +116,7 @@ struct BlockWorkspace {
   float *best_value = nullptr;  // [sample_rows][kBlockArgmaxChunks]
   uint32_t *best_index = nullptr;
   FusedAttentionRow *attn_rows = nullptr;  // [max_rows] device copies of the row descriptors
+  bool paged_rows = false;      // the rows' attention runs on the paged tensor-pipe kernel (attention.cu)
   BlockTokenRow *token_rows = nullptr;
 };
 constexpr uint32_t kBlockArgmaxChunks = 64;
@@ -207,6 +212,10 @@ struct NervaCudaHfDecodeSequenceSession {
   uint64_t state_bytes = 0;
   uint16_t *kv_keys = nullptr, *kv_values = nullptr;  // [layers][pages][16][kv_hidden]
   uint64_t kv_layer_elems = 0;
+  // the two arrays as 2-D tensor maps [layers * pages * 16][kv_hidden] (boxes of 64 dims x one page),
+  // encoded once when the state is allocated; read by the row form of the paged attention kernel
+  nb::TensorMapStorage kv_map_k{}, kv_map_v{};
+  bool kv_maps = false;
   uint32_t kv_pages = 0;
   uint32_t *page_table = nullptr;
   float *h_a = nullptr, *h_b = nullptr, *qkv = nullptr, *o_out = nullptr, *down = nullptr;

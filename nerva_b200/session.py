@@ -123,7 +123,8 @@ def _upload_order(checkpoint) -> list:
                 tensors.append(entry["w_router"])
                 tensors += [entry[k] for k in ("w_shared_expert_gate", "w_shared_expert_up", "w_shared_expert_down")
                             if k in entry]
-                per_expert = entry["w_expert_gate_up"].reshape(cfg.num_experts, 2, cfg.moe_intermediate * cfg.hidden)
+                # -1: an expert-parallel rank holds fewer experts than the router has rows
+                per_expert = entry["w_expert_gate_up"].reshape(-1, 2, cfg.moe_intermediate * cfg.hidden)
                 tensors += [np.ascontiguousarray(per_expert[:, 0]).reshape(-1),
                             np.ascontiguousarray(per_expert[:, 1]).reshape(-1), entry["w_expert_down"]]
             else:
@@ -208,10 +209,12 @@ class CudaHfDecodeSequenceSession:
         self.create_result = ffi.CreateResult()
         self.shard = getattr(checkpoint, "shard", None)
         if self.shard is not None:
-            # a tensor-parallel rank: `checkpoint` holds this rank's slices (nerva_b200.synth.shard_checkpoint)
+            # a tensor- or expert-parallel rank: `checkpoint` holds this rank's slices (nerva_b200.synth.shard_checkpoint,
+            # expert_shard_checkpoint)
             info = ffi.structs["NervaB200ShardInfo"](rank=self.shard.rank, world=self.shard.world,
                                                      full_vocab=self.shard.full_vocab,
-                                                     vocab_offset=self.shard.vocab_offset)
+                                                     vocab_offset=self.shard.vocab_offset,
+                                                     mode=getattr(self.shard, "mode", 0))
             rc = self._lib.nerva_b200_session_create_sharded(C.byref(req), C.byref(info),
                                                              C.byref(self.create_result), C.byref(self._handle))
         else:

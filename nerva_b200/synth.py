@@ -189,12 +189,41 @@ class DenseCheckpoint:
     layers: list = field(default_factory=list)  # dict name -> uint16 array
 
 
+def _attention_tensors(cfg: DecoderConfig, layer: int, seed: int, std: float, gen) -> dict:
+    """Norm weights and attention projections of one layer (latent attention or Q/K/V/O)."""
+    tid = lambda slot: layer_tensor_id(layer, slot)  # noqa: E731
+    ones_h = np.full(cfg.hidden, BF16_ONE, dtype=np.uint16)
+    if cfg.kv_lora_rank:
+        qdim = cfg.qk_nope_head_dim + cfg.qk_rope_head_dim
+        return {
+            "rms_attn": ones_h.copy(),
+            "rms_mlp": ones_h.copy(),
+            "w_q": gen(seed, tid(L_Q), cfg.heads * qdim * cfg.hidden, std),
+            "w_kv_a": gen(seed, tid(L_KV_A), (cfg.kv_lora_rank + cfg.qk_rope_head_dim) * cfg.hidden, std),
+            "kv_a_norm": np.full(cfg.kv_lora_rank, BF16_ONE, dtype=np.uint16),
+            "w_kv_b": gen(seed, tid(L_KV_B), cfg.heads * (cfg.qk_nope_head_dim + cfg.head_dim) * cfg.kv_lora_rank, std),
+            "w_o": gen(seed, tid(L_WO), cfg.hidden * cfg.attention_hidden, std),
+        }
+    entry = {
+        "rms_attn": ones_h.copy(),
+        "rms_mlp": ones_h.copy(),
+        "w_q": gen(seed, tid(L_WQ), cfg.attention_hidden * cfg.hidden, std),
+        "w_k": gen(seed, tid(L_WK), cfg.kv_hidden * cfg.hidden, std),
+        "w_v": gen(seed, tid(L_WV), cfg.kv_hidden * cfg.hidden, std),
+        "w_o": gen(seed, tid(L_WO), cfg.hidden * cfg.attention_hidden, std),
+    }
+    if cfg.qk_norm:
+        ones_d = np.full(cfg.head_dim, BF16_ONE, dtype=np.uint16)
+        entry["q_norm"] = ones_d.copy()
+        entry["k_norm"] = ones_d.copy()
+    return entry
+
+
 def dense_checkpoint(cfg: DecoderConfig, seed: int = 0, std: float = 0.02, fill=None) -> DenseCheckpoint:
     """Random-init BF16 checkpoint.  `fill(seed, tensor_id, count, std)` may be a
     native generator (same bits, multi-threaded) for the full-size models."""
     gen = fill or normal_bf16
     ones_h = np.full(cfg.hidden, BF16_ONE, dtype=np.uint16)
-    ones_d = np.full(cfg.head_dim, BF16_ONE, dtype=np.uint16)
     ck = DenseCheckpoint(
         cfg,
         embeddings=gen(seed, T_EMBEDDINGS, cfg.vocab * cfg.hidden, std),
@@ -203,30 +232,7 @@ def dense_checkpoint(cfg: DecoderConfig, seed: int = 0, std: float = 0.02, fill=
     )
     for layer in range(cfg.layers):
         tid = lambda slot: layer_tensor_id(layer, slot)  # noqa: E731
-        if cfg.kv_lora_rank:
-            qdim = cfg.qk_nope_head_dim + cfg.qk_rope_head_dim
-            entry = {
-                "rms_attn": ones_h.copy(),
-                "rms_mlp": ones_h.copy(),
-                "w_q": gen(seed, tid(L_Q), cfg.heads * qdim * cfg.hidden, std),
-                "w_kv_a": gen(seed, tid(L_KV_A), (cfg.kv_lora_rank + cfg.qk_rope_head_dim) * cfg.hidden, std),
-                "kv_a_norm": np.full(cfg.kv_lora_rank, BF16_ONE, dtype=np.uint16),
-                "w_kv_b": gen(seed, tid(L_KV_B), cfg.heads * (cfg.qk_nope_head_dim + cfg.head_dim) * cfg.kv_lora_rank,
-                              std),
-                "w_o": gen(seed, tid(L_WO), cfg.hidden * cfg.attention_hidden, std),
-            }
-        else:
-            entry = {
-                "rms_attn": ones_h.copy(),
-                "rms_mlp": ones_h.copy(),
-                "w_q": gen(seed, tid(L_WQ), cfg.attention_hidden * cfg.hidden, std),
-                "w_k": gen(seed, tid(L_WK), cfg.kv_hidden * cfg.hidden, std),
-                "w_v": gen(seed, tid(L_WV), cfg.kv_hidden * cfg.hidden, std),
-                "w_o": gen(seed, tid(L_WO), cfg.hidden * cfg.attention_hidden, std),
-            }
-        if cfg.qk_norm and not cfg.kv_lora_rank:
-            entry["q_norm"] = ones_d.copy()
-            entry["k_norm"] = ones_d.copy()
+        entry = _attention_tensors(cfg, layer, seed, std, gen)
         if cfg.num_experts == 0 or layer < cfg.dense_layers:
             entry["w_gate"] = gen(seed, tid(L_WGATE), cfg.intermediate * cfg.hidden, std)
             entry["w_up"] = gen(seed, tid(L_WUP), cfg.intermediate * cfg.hidden, std)
@@ -253,6 +259,7 @@ class ShardInfo:
     world: int
     full_vocab: int
     vocab_offset: int
+    mode: int = 0  # 0: tensor parallel, 1: expert parallel
 
 
 def shard_config(cfg: DecoderConfig, world: int) -> DecoderConfig:
@@ -345,6 +352,96 @@ def shard_checkpoint(full: DenseCheckpoint, rank: int, world: int) -> DenseCheck
             if name in entry:
                 out[name] = np.ascontiguousarray(entry[name][rank * width:(rank + 1) * width])
         ck.layers.append(out)
+    return ck
+
+
+def expert_shard_config(cfg: DecoderConfig, world: int) -> DecoderConfig:
+    """Dimensions one expert-parallel rank holds: everything except the routed experts (num_experts /
+    world consecutive ones per sparse layer; num_experts itself stays the layer's total, the router
+    is whole) and the shared expert, of which it holds a 1 / world slice of the intermediate size."""
+    import dataclasses
+    if not cfg.num_experts:
+        raise ValueError("expert parallel needs sparse layers")
+    if cfg.num_experts % world or cfg.shared_intermediate % (8 * world):
+        raise ValueError(f"{cfg.num_experts} experts / shared intermediate {cfg.shared_intermediate} do not split "
+                         f"over {world} ranks")
+    if (cfg.layers - cfg.dense_layers) % 2:
+        raise ValueError("expert parallel needs an even number of sparse layers")
+    return dataclasses.replace(cfg, name=f"{cfg.name} experts 1/{world}",
+                               shared_intermediate=cfg.shared_intermediate // world)
+
+
+def _expert_slices(entry: dict, cfg: DecoderConfig, rank: int, world: int, cut) -> dict:
+    """The sparse-MLP tensors of one layer as rank `rank` holds them.  cut(name, full_cols, row_begin,
+    rows, col_begin, cols) returns that block of the full tensor `name` seen as a matrix."""
+    h, mi, si = cfg.hidden, cfg.moe_intermediate, cfg.shared_intermediate
+    local_e, local_si = cfg.num_experts // world, si // world
+    out = {"w_router": entry["w_router"] if entry is not None else None}
+    out["w_expert_gate_up"] = cut("w_expert_gate_up", 2 * mi * h, rank * local_e, local_e, 0, 2 * mi * h)
+    out["w_expert_down"] = cut("w_expert_down", h * mi, rank * local_e, local_e, 0, h * mi)
+    if si:
+        out["w_shared_expert_gate"] = cut("w_shared_expert_gate", h, rank * local_si, local_si, 0, h)
+        out["w_shared_expert_up"] = cut("w_shared_expert_up", h, rank * local_si, local_si, 0, h)
+        out["w_shared_expert_down"] = cut("w_shared_expert_down", si, 0, h, rank * local_si, local_si)
+    return out
+
+
+def expert_shard_checkpoint(full: DenseCheckpoint, rank: int, world: int) -> DenseCheckpoint:
+    """Rank `rank`'s part of a sparse-MoE checkpoint under expert parallel, cut out of the full
+    checkpoint: dense tensors are shared with it (no copy), expert tensors are slices."""
+    cfg = full.config
+    local = expert_shard_config(cfg, world)
+    ck = DenseCheckpoint(local, embeddings=full.embeddings, final_norm=full.final_norm, lm_head=full.lm_head)
+    ck.shard = ShardInfo(rank, world, cfg.vocab, 0, mode=1)
+    for entry in full.layers:
+        if "w_router" not in entry:
+            ck.layers.append(entry)
+            continue
+
+        def cut(name, full_cols, row_begin, rows, col_begin, cols, entry=entry):
+            m = entry[name].reshape(-1, full_cols)[row_begin:row_begin + rows, col_begin:col_begin + cols]
+            return np.ascontiguousarray(m).reshape(-1)
+
+        out = {k: v for k, v in entry.items() if not k.startswith("w_expert") and not k.startswith("w_shared_expert")}
+        out.update({k: v for k, v in _expert_slices(entry, cfg, rank, world, cut).items() if v is not None})
+        if "w_shared_expert_router" in entry:
+            out["w_shared_expert_router"] = entry["w_shared_expert_router"]
+        ck.layers.append(out)
+    return ck
+
+
+def expert_checkpoint_shard(cfg: DecoderConfig, rank: int, world: int, seed: int = 0, std: float = 0.02,
+                            block_fill=None, fill=None) -> DenseCheckpoint:
+    """The same part generated directly (the full model's expert tensors never exist in memory),
+    with the same bits as the slices of dense_checkpoint(cfg)."""
+    local = expert_shard_config(cfg, world)
+    block = block_fill or _numpy_block
+    gen = fill or normal_bf16
+    h = cfg.hidden
+    ck = DenseCheckpoint(local, embeddings=gen(seed, T_EMBEDDINGS, cfg.vocab * h, std),
+                         final_norm=np.full(h, BF16_ONE, dtype=np.uint16),
+                         lm_head=gen(seed, T_LM_HEAD, cfg.vocab * h, std))
+    ck.shard = ShardInfo(rank, world, cfg.vocab, 0, mode=1)
+    names = {"w_expert_gate_up": L_EXPERT_GATE_UP, "w_expert_down": L_EXPERT_DOWN, "w_shared_expert_gate": L_SHARED_GATE,
+             "w_shared_expert_up": L_SHARED_UP, "w_shared_expert_down": L_SHARED_DOWN}
+    for layer in range(cfg.layers):
+        tid = lambda slot: layer_tensor_id(layer, slot)  # noqa: E731
+        entry = _attention_tensors(cfg, layer, seed, std, gen)
+        if layer < cfg.dense_layers:
+            entry["w_gate"] = gen(seed, tid(L_WGATE), cfg.intermediate * h, std)
+            entry["w_up"] = gen(seed, tid(L_WUP), cfg.intermediate * h, std)
+            entry["w_down"] = gen(seed, tid(L_WDOWN), h * cfg.intermediate, std)
+            ck.layers.append(entry)
+            continue
+
+        def cut(name, full_cols, row_begin, rows, col_begin, cols, layer=layer):
+            return block(seed, layer_tensor_id(layer, names[name]), full_cols, row_begin, rows, col_begin, cols, std)
+
+        entry["w_router"] = gen(seed, tid(L_ROUTER), cfg.num_experts * h, std)
+        entry.update({k: v for k, v in _expert_slices(None, cfg, rank, world, cut).items() if v is not None})
+        if cfg.shared_intermediate and not cfg.kv_lora_rank:
+            entry["w_shared_expert_router"] = gen(seed, tid(L_SHARED_ROUTER), h, std)
+        ck.layers.append(entry)
     return ck
 
 

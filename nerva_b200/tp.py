@@ -32,9 +32,17 @@ def connect(session: CudaHfDecodeSequenceSession, group=None) -> None:
 
 def create_session(cfg: synth.DecoderConfig, max_context_tokens: int, rank: int, world: int, full_checkpoint=None,
                    group=None) -> CudaHfDecodeSequenceSession:
-    """Creates this rank's shard of `cfg` (cut from full_checkpoint when given, else generated
-    directly with the native generator) and connects it to the other ranks."""
-    if full_checkpoint is not None:
+    """Creates this rank's part of `cfg` (cut from full_checkpoint when given, else generated
+    directly with the native generator) and connects it to the other ranks.  Dense models are
+    cut tensor-parallel; models with sparse-MoE layers expert-parallel (every rank holds the
+    whole model except its share of the routed and shared experts)."""
+    if cfg.num_experts:
+        if full_checkpoint is not None:
+            shard = synth.expert_shard_checkpoint(full_checkpoint, rank, world)
+        else:
+            shard = synth.expert_checkpoint_shard(cfg, rank, world, block_fill=ops.synth_normal_bf16_block,
+                                                  fill=ops.synth_normal_bf16)
+    elif full_checkpoint is not None:
         shard = synth.shard_checkpoint(full_checkpoint, rank, world)
     else:
         shard = synth.dense_checkpoint_shard(cfg, rank, world, block_fill=ops.synth_normal_bf16_block,

@@ -291,8 +291,10 @@ class Decoder:
 # ---- DeepSeek expert routers (oracle/nerva_oracle_router.c) and the reference's own header ----
 
 _REF_ROUTER_PATH = os.path.join(_HERE, "_ref", "libnerva_ref_router.so")
-_REFERENCE_ROOT = os.environ.get("NERVA_REFERENCE_ROOT", "/root/reference")
-_REFERENCE_HEADER = os.path.join(_REFERENCE_ROOT, "native/cuda/deepseek/deepseek_router.cuh")
+# the reference checkout: NERVA_REFERENCE_ROOT, else a directory `reference` beside this repository
+REFERENCE_ROOT = os.environ.get("NERVA_REFERENCE_ROOT",
+                                 os.path.abspath(os.path.join(_HERE, "..", "..", "reference")))
+_REFERENCE_HEADER = os.path.join(REFERENCE_ROOT, "native/cuda/deepseek/deepseek_router.cuh")
 _REF_SAMPLER_PATH = os.path.join(_HERE, "_ref", "libnerva_ref_sampler.so")
 _ref_router = None
 _ref_sampler = None
@@ -304,7 +306,7 @@ def build_ref(force: bool = False):
     library is there."""
     if os.path.exists(_REFERENCE_HEADER) and (force or not os.path.exists(_REF_ROUTER_PATH)
                                               or not os.path.exists(_REF_SAMPLER_PATH)):
-        subprocess.run(["make", "-C", _HERE, "ref", f"REFERENCE_ROOT={_REFERENCE_ROOT}"], check=True, capture_output=True)
+        subprocess.run(["make", "-C", _HERE, "ref", f"REFERENCE_ROOT={REFERENCE_ROOT}"], check=True, capture_output=True)
     return _REF_ROUTER_PATH if os.path.exists(_REF_ROUTER_PATH) else None
 
 

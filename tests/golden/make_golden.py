@@ -38,7 +38,7 @@ sys.path.insert(0, ROOT)
 from nerva_b200 import ffi, synth  # noqa: E402
 from oracle import oracle as O  # noqa: E402
 
-REFERENCE_HEADER = os.path.join(os.environ.get("NERVA_REFERENCE_ROOT", "/root/reference"), "native/cuda/nerva_cuda_api.h")
+REFERENCE_HEADER = os.path.join(O.REFERENCE_ROOT, "native/cuda/nerva_cuda_api.h")
 SAMPLE_INDICES = [0, 1, 2, 3, 101, 1009, 4099, 8191, 12345, 16000, 20011, 25000, 29999, 31000, 31998, 31999]
 
 

@@ -138,3 +138,118 @@ def test_handles_reach_every_rank_in_rank_order():
         assert p.exitcode == 0
     expected = [bytes([0]) * 64, bytes([1]) * 64]
     assert results[0] == expected and results[1] == expected
+
+
+# ---- expert-parallel host logic ----
+
+def _sparse_config():
+    import dataclasses
+    from nerva_b200 import synth
+    return dataclasses.replace(synth.DEEPSEEK_V2_LITE, name="v2-lite-small", layers=3, vocab=512, prompt_tokens=8,
+                               decode_tokens=4, hidden=256, heads=4, kv_heads=4, head_dim=32, intermediate=512,
+                               num_experts=8, top_k=3, moe_intermediate=64, shared_intermediate=128,
+                               kv_lora_rank=128, qk_nope_head_dim=32, qk_rope_head_dim=16)
+
+
+def _f32(bits):
+    import numpy as np
+    return (bits.astype(np.uint32) << 16).view(np.float32)
+
+
+def _expert_mlp(x, gate, up, down):
+    """down . (silu(gate . x) * (up . x)) in float64 from bf16 matrices."""
+    import numpy as np
+    g = _f32(gate).astype(np.float64) @ x
+    u = _f32(up).astype(np.float64) @ x
+    return _f32(down).astype(np.float64) @ (g / (1.0 + np.exp(-g)) * u)
+
+
+def _partial_sparse_mlp(entry, cfg, x, ids, weights, expert_base, expert_local, shared_intermediate):
+    """What one rank adds to the MLP output: the chosen experts it holds (the kernel's rule: id -
+    expert_base below expert_local, matrices indexed by that difference) and its slice of the shared expert."""
+    import numpy as np
+    h, mi = cfg.hidden, cfg.moe_intermediate
+    gate_up = entry["w_expert_gate_up"].reshape(-1, 2, mi, h)
+    down = entry["w_expert_down"].reshape(-1, h, mi)
+    out = np.zeros(h)
+    for e, w in zip(ids, weights):
+        local = int(e) - expert_base
+        if 0 <= local < expert_local:
+            out += float(w) * _expert_mlp(x, gate_up[local, 0], gate_up[local, 1], down[local])
+    si = shared_intermediate
+    out += _expert_mlp(x, entry["w_shared_expert_gate"].reshape(si, h), entry["w_shared_expert_up"].reshape(si, h),
+                       entry["w_shared_expert_down"].reshape(h, si))
+    return out
+
+
+def _expert_rank_main(rank: int, world: int, port: int, results) -> None:
+    sys.path.insert(0, ROOT)
+    import numpy as np
+    import torch
+    import torch.distributed as dist
+    from nerva_b200 import synth
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), RANK=str(rank), WORLD_SIZE=str(world))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        cfg = _sparse_config()
+        shard = synth.expert_checkpoint_shard(cfg, rank, world)  # generated directly: no full model on this rank
+        local_e = cfg.num_experts // world
+        x = synth.normal_f32(0, 77, cfg.hidden, 1.0).astype(np.float64)
+        ids, weights = [6, 1, 3], [0.5, 0.3, 0.2]
+        part = _partial_sparse_mlp(shard.layers[1], cfg, x, ids, weights, rank * local_e, local_e,
+                                   shard.config.shared_intermediate)
+        total = torch.from_numpy(part.copy())
+        dist.all_reduce(total)  # the sum the gather prologue forms from the ranks' partial outputs
+        results[rank] = total.numpy()
+    finally:
+        dist.destroy_process_group()
+
+
+def test_expert_parallel_partial_outputs_add_up_to_the_whole_mlp():
+    import numpy as np
+    import torch.multiprocessing as mp
+    from nerva_b200 import synth
+    world, port = 2, _free_port()
+    ctx = mp.get_context("spawn")
+    results = ctx.Manager().dict()
+    procs = [ctx.Process(target=_expert_rank_main, args=(r, world, port, results)) for r in range(world)]
+    for p in procs:
+        p.start()
+    for p in procs:
+        p.join(180)
+        assert p.exitcode == 0
+    cfg = _sparse_config()
+    full = synth.dense_checkpoint(cfg)
+    x = synth.normal_f32(0, 77, cfg.hidden, 1.0).astype(np.float64)
+    whole = _partial_sparse_mlp(full.layers[1], cfg, x, [6, 1, 3], [0.5, 0.3, 0.2], 0, cfg.num_experts,
+                                cfg.shared_intermediate)
+    assert np.abs(results[0] - whole).max() < 1e-9 * max(1.0, np.abs(whole).max()) + 1e-12
+    assert np.array_equal(results[0], results[1])
+
+
+def test_expert_shards_partition_the_experts_and_keep_everything_else_whole():
+    import numpy as np
+    from nerva_b200 import synth
+    cfg = _sparse_config()
+    full = synth.dense_checkpoint(cfg)
+    for world in (2, 4):
+        shards = [synth.expert_shard_checkpoint(full, r, world) for r in range(world)]
+        for r, s in enumerate(shards):
+            direct = synth.expert_checkpoint_shard(cfg, r, world)
+            assert s.shard.mode == 1 and s.shard.vocab_offset == 0 and s.config.num_experts == cfg.num_experts
+            assert s.config.shared_intermediate == cfg.shared_intermediate // world
+            assert s.lm_head is full.lm_head and s.layers[0] is full.layers[0]  # dense parts are shared, not copied
+            for a, b in zip(s.layers, direct.layers):
+                assert set(a) == set(b)
+                assert all(np.array_equal(a[k], b[k]) for k in a)
+        sparse = full.layers[1]
+        for name in ("w_expert_gate_up", "w_expert_down", "w_shared_expert_gate", "w_shared_expert_up"):
+            assert np.array_equal(np.concatenate([s.layers[1][name] for s in shards]), sparse[name])
+        si, h = cfg.shared_intermediate, cfg.hidden
+        parts = [s.layers[1]["w_shared_expert_down"].reshape(h, si // world) for s in shards]
+        assert np.array_equal(np.concatenate(parts, axis=1).reshape(-1), sparse["w_shared_expert_down"])
+    with pytest.raises(ValueError):
+        synth.expert_shard_config(cfg, 3)
+    import dataclasses
+    with pytest.raises(ValueError):  # an odd number of sparse layers: the exchange buffers would not alternate
+        synth.expert_shard_config(dataclasses.replace(cfg, layers=4), 2)

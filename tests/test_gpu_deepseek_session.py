@@ -43,6 +43,18 @@ def _decode(cfg, ck, steps):
     return s, tokens, np.stack(logits)
 
 
+def _first_step_self_distance(oracle_mod, ck, cfg, first_logits) -> float:
+    """The oracle against itself with 8 interleaved partial sums per row instead of serial sums, on
+    the first decoded position (both runs have seen the same prompt, so the histories are equal)."""
+    oracle_mod.set_sum_lanes(8)
+    try:
+        dec = oracle_mod.Decoder(ck, cfg.prompt_tokens + 2, mode=oracle_mod.MODE_CUDA)
+        _, alt = dec.decode_greedy(synth.prompt_ids(cfg), 1, want_logits=True)
+    finally:
+        oracle_mod.set_sum_lanes(1)
+    return float(np.abs(alt[0] - first_logits).max())
+
+
 @pytest.mark.parametrize("make", [_small, lambda: _full_width(2), lambda: _full_width(3)])
 def test_latent_attention_moe_session_matches_the_composed_oracle(built_lib, oracle_mod, make):
     cfg = make()
@@ -55,9 +67,14 @@ def test_latent_attention_moe_session_matches_the_composed_oracle(built_lib, ora
     margins = top2[:, 1] - top2[:, 0]
     at = next((i for i in range(steps) if tokens[i] != int(want_tokens[i])), None)
     compared = steps if at is None else at + 1
-    assert float(np.abs(logits[:compared] - want_logits[:compared]).max()) <= LOGIT_ATOL
-    assert at is None or margins[at] <= LOGIT_ATOL, (at, tokens, want_tokens.tolist(), margins[at])
-    # the cached latent rows are the oracle's, to one bf16 rounding step of the row's magnitude
+    # the stated bound, or twice the oracle's own distance to itself under another fp32 summation
+    # order where that is larger (full-width layers: about 1e-2 per layer pair, as for the dense model)
+    floor = _first_step_self_distance(oracle_mod, ck, cfg, want_logits[0])
+    bound = max(LOGIT_ATOL, 2.0 * floor)
+    worst = float(np.abs(logits[:compared] - want_logits[:compared]).max())
+    assert worst <= bound, (worst, bound, floor)
+    assert at is None or margins[at] <= bound, (at, tokens, want_tokens.tolist(), margins[at])
+    # the cache holds one latent row per token and layer, nothing else
     r = s.create_result
     assert r.resident_kv_bytes == cfg.layers * ((cfg.prompt_tokens + steps + 1 + 15) // 16) * 16 * \
         (cfg.kv_lora_rank + cfg.qk_rope_head_dim) * 2

@@ -123,12 +123,11 @@ def _qwen_golden():
 
 
 def _write_report(name: str, report: dict) -> None:
-    """Keeps the measured distances beside the run when a scratch folder for GPU runs exists."""
+    """Keeps the measured distances as a file when NERVA_REPORT_DIR names a folder for them."""
     import json
     import os
-    from tests.conftest import ROOT
-    out_dir = os.path.join(ROOT, "gpurun_out")
-    if os.path.isdir(out_dir):
+    out_dir = os.environ.get("NERVA_REPORT_DIR", "")
+    if out_dir and os.path.isdir(out_dir):
         with open(os.path.join(out_dir, name), "w") as f:
             json.dump(report, f, indent=1)
 
