@@ -580,7 +580,7 @@ def run_deepseek_workload(args) -> None:
     t0 = time.perf_counter()
     ck = synth.dense_checkpoint(cfg, fill=ops.synth_normal_bf16)
     t1 = time.perf_counter()
-    session = CudaHfDecodeSequenceSession(ck, cfg.prompt_tokens + max(args.warmup, 3) + 2 * args.steps + 8)
+    session = CudaHfDecodeSequenceSession(ck, cfg.prompt_tokens + max(args.warmup, 3) + 2 * args.steps + 16)
     if session.status != SmokeStatus.OK:
         raise RuntimeError(f"session create failed: {session.error}")
     t2 = time.perf_counter()
@@ -604,6 +604,9 @@ def run_deepseek_workload(args) -> None:
             raise RuntimeError(f"advance failed: {out.error}")
         e2e_tokens += out.tokens
     e2e_s = time.perf_counter() - t4
+    # where the step's time goes: events between launch groups, un-captured (includes event overhead)
+    profile = session.profile_steps(4)
+    profile_us = {name: entry["ns"] / 4 / 1e3 for name, entry in profile.items()}
     peaks = measured_peaks()
     nbytes = cfg.active_weight_bytes_per_token()
     r = session.create_result
@@ -627,6 +630,10 @@ def run_deepseek_workload(args) -> None:
                      "frac": nbytes / device_s * args.steps / 1e9 / peaks["hbm_gbs"], "peak_source": peaks["source"],
                      "traffic": None},
         "token_hash": f"{timed.observed_token_hash:016x}",
+        "profile_us_per_token": profile_us,
+        "profile_note": "event-per-launch pass outside the graph: qkv = first projection, attention = the three "
+                        "latent-attention kernels, o = output projection, gate_up = dense gate/up or router + "
+                        "routing, down = dense down or the two expert-stream kernels",
         "setup_s": {"generate_weights": t1 - t0, "session_create": t2 - t1, "prefill": t3 - t2},
     }), flush=True)
     session.destroy()

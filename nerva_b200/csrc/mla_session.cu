@@ -4,14 +4,14 @@
 // session_decode_v3_projection.inc.cu:1-624; kernels_v3_mla.inc.cu:1-61 cache row, :196-236 absorbed
 // query, :465 attention tile, :890 value projection) with the whole layer's attention of a batch-1
 // step in ONE thread block.  Here, after the fused [query; latent + rotary key] projection:
-//   mla_prepare_kernel    block h < heads: rotary part of query head h in place, and its absorbed
-//                         query ql[h] = q_nope[h] . W_UK[h] (128 x 512 mat-vec);
-//                         block `heads`: cache row of the new token — bf16(RMSNorm(latent) * w) and
+//   mla_prepare_kernel    blocks (head h, 64-wide slice): rotary part of query head h in place, and the
+//                         slice of its absorbed query ql[h] = q_nope[h] . W_UK[h] (128 x 512 mat-vec);
+//                         last block: cache row of the new token — bf16(RMSNorm(latent) * w) and
 //                         bf16(rope(bf16(k_pe))), interleaved rotary pairs — appended to its page
 //   mla_attention_kernel  grid = splits: the block's span of cached rows goes through shared memory
 //                         once for ALL heads (the latent cache is shared between heads), one warp
 //                         per head: s = (ql . c + q_pe . k_pe) * scale, online softmax, acc += p c
-//   mla_output_kernel     block h: merges the spans, then out[h] = W_UV[h] . lat[h] -> bf16
+//   mla_output_kernel     blocks (head h, 8 output rows): merge of the spans, then out[h] = W_UV[h] . lat[h] -> bf16
 // Cache rows are (rank + rope) bf16 values in the session's K pages, addressed through the page
 // table like every other cache row (hf_decode_sequence/types.cuh:328-337).
 #include <math.h>
@@ -40,33 +40,47 @@ __device__ __forceinline__ void rope_pair(float &left, float &right, uint32_t pa
   right = r * c + l * s;
 }
 
+constexpr uint32_t kMlaPrepareSlice = 64;  // absorbed-query elements per block
+
+// Grid: heads * (rank / 64) blocks for the absorbed queries, one more for the cache row.
 __global__ void __launch_bounds__(256) mla_prepare_kernel(MlaParams p) {
   __shared__ float q_nope[kMlaMaxNope];
+  __shared__ float part[4][kMlaPrepareSlice];
   __shared__ float scratch[40];
   pdl_trigger();
   pdl_wait();  // the fused projection of this step
   const uint32_t position = *p.cursor;
   if (position >= p.max_context) return;
   const uint32_t qdim = p.nope + p.rope, width = p.rank + p.rope;
-  if (blockIdx.x < p.heads) {
-    const uint32_t h = blockIdx.x;
+  const uint32_t slices = p.rank / kMlaPrepareSlice;
+  if (blockIdx.x < p.heads * slices) {
+    const uint32_t h = blockIdx.x / slices, slice = blockIdx.x % slices;
     float *q = p.qkv + static_cast<uint64_t>(h) * qdim;
     for (uint32_t i = threadIdx.x; i < p.nope; i += blockDim.x) q_nope[i] = q[i];
-    if (p.rope_theta > 0.0f && threadIdx.x < p.rope / 2u) {
+    if (slice == 0 && p.rope_theta > 0.0f && threadIdx.x < p.rope / 2u) {
+      // the head's rotary part, in place, by one of the head's blocks (the others read q_nope only)
       float l = q[p.nope + 2u * threadIdx.x], r = q[p.nope + 2u * threadIdx.x + 1u];
       rope_pair(l, r, threadIdx.x, p.rope, position, p.rope_theta);
       q[p.nope + 2u * threadIdx.x] = l;
       q[p.nope + 2u * threadIdx.x + 1u] = r;
     }
     __syncthreads();
-    // ql[r] = sum_n q_nope[n] W_UK[h][n][r]: consecutive threads take consecutive r, so every row of
-    // W_UK is read in whole lines
+    // ql[r] = sum_n q_nope[n] W_UK[h][n][r] for 64 consecutive r: thread (r, quarter) adds a quarter
+    // of the n range (64 consecutive threads read one 128-byte piece of a W_UK row, all of a
+    // thread's loads are independent), the quarters are added in order
     const uint16_t *w_uk = p.w_kv_b + static_cast<uint64_t>(h) * (p.nope + p.v_dim) * p.rank;
-    for (uint32_t r = threadIdx.x; r < p.rank; r += blockDim.x) {
-      float acc = 0.0f;
-      for (uint32_t n = 0; n < p.nope; ++n) acc = fmaf(q_nope[n], bf16_bits_to_f32(w_uk[static_cast<uint64_t>(n) * p.rank + r]), acc);
-      p.ql[static_cast<uint64_t>(h) * p.rank + r] = acc;
-    }
+    const uint32_t r_local = threadIdx.x & (kMlaPrepareSlice - 1u), quarter = threadIdx.x / kMlaPrepareSlice;
+    const uint32_t r = slice * kMlaPrepareSlice + r_local;
+    const uint32_t per = (p.nope + 3u) / 4u;
+    const uint32_t n_begin = quarter * per, n_end = n_begin + per < p.nope ? n_begin + per : p.nope;
+    float acc = 0.0f;
+#pragma unroll 8
+    for (uint32_t n = n_begin; n < n_end; ++n)
+      acc = fmaf(q_nope[n], bf16_bits_to_f32(w_uk[static_cast<uint64_t>(n) * p.rank + r]), acc);
+    part[quarter][r_local] = acc;
+    __syncthreads();
+    if (quarter == 0)
+      p.ql[static_cast<uint64_t>(h) * p.rank + r] = ((part[0][r_local] + part[1][r_local]) + part[2][r_local]) + part[3][r_local];
     return;
   }
   // the new token's cache row
@@ -202,10 +216,12 @@ __global__ void __launch_bounds__(256) mla_output_kernel(MlaParams p, uint32_t s
     lat[r] = a;
   }
   __syncthreads();
-  // out[v] = sum_r lat[r] W_UV[h][v][r]: one warp per output row, 16-byte loads along r
+  // out[v] = sum_r lat[r] W_UV[h][v][r]: one warp per output row, 16-byte loads along r; block
+  // (h, y) takes rows y * warps .. of the head (the merge above is repeated by the head's blocks:
+  // it reads a few KB that stay in L2, the value projection reads the weights)
   const uint16_t *w_uv = p.w_kv_b + (static_cast<uint64_t>(h) * (p.nope + p.v_dim) + p.nope) * p.rank;
   const uint32_t lane = threadIdx.x & 31u, warp = threadIdx.x >> 5, warps = blockDim.x >> 5;
-  for (uint32_t v = warp; v < p.v_dim; v += warps) {
+  for (uint32_t v = blockIdx.y * warps + warp; v < p.v_dim; v += gridDim.y * warps) {
     const uint4 *row = reinterpret_cast<const uint4 *>(w_uv + static_cast<uint64_t>(v) * p.rank);
     float acc = 0.0f;
     for (uint32_t i = lane; i < p.rank / 8u; i += 32u) {
@@ -242,7 +258,8 @@ uint32_t mla_attention_splits(uint32_t target_context) {
 cudaError_t launch_mla_attention(cudaStream_t stream, const MlaParams &p, uint32_t splits, bool pdl) {
   if (!mla_session_supported(p.heads, p.rank, p.nope, p.rope, p.v_dim) || splits == 0 || splits > kMlaMaxSplits)
     return cudaErrorInvalidValue;
-  cudaError_t err = launch_with_pdl(mla_prepare_kernel, dim3(p.heads + 1u), dim3(256), 0, stream, pdl, p);
+  cudaError_t err = launch_with_pdl(mla_prepare_kernel, dim3(p.heads * (p.rank / kMlaPrepareSlice) + 1u), dim3(256), 0,
+                                    stream, pdl, p);
   if (err != cudaSuccess) return err;
   const uint32_t smem = kMlaTile * ((p.rank + p.rope) * 2u + 16u);
   const dim3 grid(splits), block(512);
@@ -259,7 +276,7 @@ cudaError_t launch_mla_attention(cudaStream_t stream, const MlaParams &p, uint32
       return cudaErrorNotSupported;  // latent ranks 128, 256 and 512
   }
   if (err != cudaSuccess) return err;
-  return launch_with_pdl(mla_output_kernel, dim3(p.heads), dim3(256), 0, stream, pdl, p, splits);
+  return launch_with_pdl(mla_output_kernel, dim3(p.heads, (p.v_dim + 7u) / 8u), dim3(256), 0, stream, pdl, p, splits);
 }
 
 }  // namespace nb
