@@ -563,11 +563,13 @@ def run_batch_workload(args, cfg) -> None:
     }), flush=True)
 
 
-def run_deepseek_workload(args) -> None:
+def run_deepseek_workload(args, rank: int = 0, world: int = 1) -> None:
     """DeepSeek-V2-Lite architecture (latent attention + softmax top-6 of 64 experts + always-on shared
-    experts, dense first layer) on one GPU: batch-1 greedy decode after a 1024-token prompt.  The bytes
-    a token must stream are the matrices it touches (attention projections, router, 6 routed + the
-    shared expert matrices per sparse layer, lm_head), not the 31 GB that are resident."""
+    experts, dense first layer): batch-1 greedy decode after a 1024-token prompt, on one GPU or
+    expert-parallel over `world` GPUs (every rank holds 64 / world routed experts and 1 / world of the
+    shared expert of each sparse layer, everything else whole).  The bytes a token must stream are the
+    matrices it touches (attention projections, router, 6 routed + the shared expert matrices per sparse
+    layer, lm_head), not the 31 GB that are resident."""
     import dataclasses
     from nerva_b200 import build, ops, synth
     from nerva_b200.session import CudaHfDecodeSequenceLoop, CudaHfDecodeSequenceSession, SmokeStatus
@@ -577,10 +579,16 @@ def run_deepseek_workload(args) -> None:
         cfg = dataclasses.replace(cfg, layers=args.layers, name=f"{cfg.name} cut to {args.layers} layers")
     if args.prompt_tokens:
         cfg = dataclasses.replace(cfg, prompt_tokens=args.prompt_tokens)
+    max_context = cfg.prompt_tokens + max(args.warmup, 3) + 2 * args.steps + 16
     t0 = time.perf_counter()
-    ck = synth.dense_checkpoint(cfg, fill=ops.synth_normal_bf16)
-    t1 = time.perf_counter()
-    session = CudaHfDecodeSequenceSession(ck, cfg.prompt_tokens + max(args.warmup, 3) + 2 * args.steps + 16)
+    if world > 1:
+        from nerva_b200 import tp
+        t1 = t0
+        session = tp.create_session(cfg, max_context, rank, world)  # generates this rank's part and connects the ranks
+    else:
+        ck = synth.dense_checkpoint(cfg, fill=ops.synth_normal_bf16)
+        t1 = time.perf_counter()
+        session = CudaHfDecodeSequenceSession(ck, max_context)
     if session.status != SmokeStatus.OK:
         raise RuntimeError(f"session create failed: {session.error}")
     t2 = time.perf_counter()
@@ -589,13 +597,16 @@ def run_deepseek_workload(args) -> None:
         raise RuntimeError(f"session start failed: {start.error}")
     t3 = time.perf_counter()
     loop.advance(max(args.warmup, 3))
-    sampler = ClockSampler()
+    sync = _barrier_fn(world)
+    sampler = ClockSampler(int(os.environ.get("NERVA_GPU_INDEX", "0")))
+    sync()
     sampler.start()
     timed = loop.advance(args.steps)
     clocks = sampler.stop()
+    sync()
     if timed.status != SmokeStatus.OK or len(timed.tokens) != args.steps:
         raise RuntimeError(f"timed advance failed: {timed.error}")
-    device_s = timed.device_elapsed_ns * 1e-9
+    device_s = _max_over_ranks(timed.device_elapsed_ns * 1e-9, world)
     t4 = time.perf_counter()
     e2e_tokens = []
     for _ in range(args.steps):
@@ -603,17 +614,23 @@ def run_deepseek_workload(args) -> None:
         if out.status != SmokeStatus.OK:
             raise RuntimeError(f"advance failed: {out.error}")
         e2e_tokens += out.tokens
-    e2e_s = time.perf_counter() - t4
+    e2e_s = _max_over_ranks(time.perf_counter() - t4, world)
     # where the step's time goes: events between launch groups, un-captured (includes event overhead)
-    profile = session.profile_steps(4)
-    profile_us = {name: entry["ns"] / 4 / 1e3 for name, entry in profile.items()}
+    profile_us = None
+    if world == 1:
+        profile = session.profile_steps(4)
+        profile_us = {name: entry["ns"] / 4 / 1e3 for name, entry in profile.items()}
     peaks = measured_peaks()
     nbytes = cfg.active_weight_bytes_per_token()
     r = session.create_result
+    sync()
+    if rank != 0:
+        session.destroy()
+        return
     print(json.dumps({
         "metric": "DeepSeek-V2-Lite-arch BF16 batch-1 decode tok/s", "value": args.steps / device_s, "unit": "tok/s",
-        "n_gpus": 1, "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": 1e3 * device_s / args.steps,
-        "higher_is_better": True, "dtype": "bf16", "data": "synthetic",
+        "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": 1e3 * device_s / args.steps,
+        "higher_is_better": True, "scaling": "strong", "dtype": "bf16", "data": "synthetic",
         "config": {"workload": f"{cfg.name}: {cfg.layers} layers, hidden {cfg.hidden}, {cfg.heads} heads, latent rank "
                                f"{cfg.kv_lora_rank}, nope {cfg.qk_nope_head_dim} / rope {cfg.qk_rope_head_dim} / v "
                                f"{cfg.head_dim}; {cfg.dense_layers} dense layer (intermediate {cfg.intermediate}), then "
@@ -621,6 +638,9 @@ def run_deepseek_workload(args) -> None:
                                f"expert intermediate {cfg.moe_intermediate}; vocab {cfg.vocab}; batch 1, "
                                f"{cfg.prompt_tokens}-token seeded prompt, greedy decode",
                    "weights": "random-init bf16 ~N(0,0.02) seed 0, unit norm weights (synthetic)",
+                   "parallelism": "single GPU" if world == 1 else
+                                  f"ep{world}: routed experts and the shared expert's intermediate divided over the ranks, "
+                                  f"everything else whole on every rank; partial MLP outputs exchanged over NVLink peer memory",
                    "active_weight_bytes_per_token": nbytes, "resident_weight_bytes": int(r.resident_weight_bytes),
                    "resident_kv_bytes": int(r.resident_kv_bytes)},
         "clocks": clocks,
@@ -792,7 +812,16 @@ def main() -> None:
             run_batch_workload(args, cfg)
         return
     if args.workload == "deepseek":
-        if rank == 0:
+        if world > 1:
+            from nerva_b200 import tp
+            tp.select_device(local)
+            os.environ["NERVA_GPU_INDEX"] = str(local)
+            import torch.distributed as dist
+            dist.init_process_group("gloo")
+            run_deepseek_workload(args, rank, world)
+            dist.barrier()
+            dist.destroy_process_group()
+        else:
             run_deepseek_workload(args)
         return
     if args.impl == "reference":

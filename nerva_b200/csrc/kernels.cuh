@@ -296,6 +296,8 @@ struct MoeExpertParams {
   float *gate_up_out;                // scratch: per expert gate then up rows (+ the shared expert's), fp32
   float *shared_gate;                // scratch: 1 float
   float *out_f32;                    // [hidden] the MLP output
+  float *partial;                    // scratch: [17][hidden] per-expert contributions before they are added
+  uint32_t *ticket;                  // scratch: one counter, zero between launches
   uint32_t *error_word;
   uint32_t max_intermediate, max_rows_per_block;  // filled by the launcher
   // Expert parallel: this rank holds experts [expert_base, expert_base + expert_local) of the layer
@@ -313,6 +315,10 @@ cudaError_t configure_moe_kernels();
 // Router logits with fp32 activations; uses the residual/norm fields, weight, rows, cols, out_f32 of p.
 cudaError_t launch_router_logits_f32(cudaStream_t stream, const ProjectionParams &p, uint32_t sm_count);
 cudaError_t launch_moe_route(cudaStream_t stream, const MoeRouteParams &p, bool pdl);
+// Both in one launch (route.logits must be p.out_f32, route.num_experts == p.rows); `ticket`: one
+// device counter, zero between launches.
+cudaError_t launch_moe_router_route(cudaStream_t stream, const ProjectionParams &p, const MoeRouteParams &route,
+                                    uint32_t *ticket, uint32_t sm_count);
 // Two launches: gate/up of the chosen experts, then SwiGLU + down and the weighted sum.
 cudaError_t launch_moe_experts(cudaStream_t stream, const MoeExpertParams &p, uint32_t sm_count, bool pdl);
 

@@ -24,7 +24,7 @@ namespace {
 
 constexpr uint32_t kMlaMaxRank = 512, kMlaMaxRope = 64, kMlaMaxNope = 256;
 constexpr uint32_t kMlaTile = 32;       // cached rows per shared-memory tile
-constexpr uint32_t kMlaMaxSplits = 16;
+constexpr uint32_t kMlaMaxSplits = 64;
 constexpr float kLog2e = 1.4426950408889634f;
 
 // Interleaved rotary pair (2i, 2i + 1) of a `dim`-wide vector at `position`:
@@ -195,23 +195,37 @@ __global__ void __launch_bounds__(256) mla_output_kernel(MlaParams p, uint32_t s
   const uint32_t position = *p.cursor;
   if (position >= p.max_context) return;
   const uint32_t h = blockIdx.x;
-  if (threadIdx.x == 0) {
+  if (threadIdx.x < 32u) {
+    // one lane per span (two when there are more than 32): the (m, l) pairs become normalised weights
+    const uint32_t lane = threadIdx.x;
     float m = -INFINITY;
-    for (uint32_t s = 0; s < splits; ++s)
+    for (uint32_t s = lane; s < splits; s += 32u)
       if (__ldcg(p.partial_l + h * splits + s) > 0.0f) m = fmaxf(m, __ldcg(p.partial_m + h * splits + s));
+    m = warp_max(m);
     float l = 0.0f;
-    for (uint32_t s = 0; s < splits; ++s) {
+    for (uint32_t s = lane; s < splits; s += 32u) {
       const float ls = __ldcg(p.partial_l + h * splits + s);
-      weight[s] = ls > 0.0f ? exp2f(__ldcg(p.partial_m + h * splits + s) - m) : 0.0f;
-      l = fmaf(ls, weight[s], l);
+      const float w = ls > 0.0f ? exp2f(__ldcg(p.partial_m + h * splits + s) - m) : 0.0f;
+      weight[s] = w;
+      l = fmaf(ls, w, l);
     }
+    l = warp_sum(l);
     const float inv = l > 0.0f ? 1.0f / l : 0.0f;
-    for (uint32_t s = 0; s < splits; ++s) weight[s] *= inv;
+    __syncwarp();
+    for (uint32_t s = lane; s < splits; s += 32u) weight[s] *= inv;
   }
   __syncthreads();
   for (uint32_t r = threadIdx.x; r < p.rank; r += blockDim.x) {
     float a = 0.0f;
-    for (uint32_t s = 0; s < splits; ++s)
+    uint32_t s = 0;
+    for (; s + 8u <= splits; s += 8u) {
+      float v[8];
+#pragma unroll
+      for (uint32_t u = 0; u < 8u; ++u) v[u] = __ldcg(p.partial_acc + (static_cast<uint64_t>(h) * splits + s + u) * p.rank + r);
+#pragma unroll
+      for (uint32_t u = 0; u < 8u; ++u) a = fmaf(v[u], weight[s + u], a);
+    }
+    for (; s < splits; ++s)
       a = fmaf(__ldcg(p.partial_acc + (static_cast<uint64_t>(h) * splits + s) * p.rank + r), weight[s], a);
     lat[r] = a;
   }

@@ -50,7 +50,8 @@ struct JobDesc {
   const uint16_t *weight;  // [rows][cols] bf16 row-major, 16-byte aligned, cols % 8 == 0
   uint32_t rows, cols;
   uint32_t unit;           // rows are dealt to blocks in multiples of `unit` (2 keeps gate/up pairs together)
-  uint32_t reserved;
+  uint32_t whole;          // non-zero: the job belongs to this block alone (its list was built per block):
+                           // all `rows` are this block's, nothing is dealt
 };
 
 // Rows [begin, end) of block `block` out of `blocks`, in units of `unit` rows.
@@ -74,8 +75,8 @@ struct WarpJob {
 };
 
 __device__ __forceinline__ WarpJob warp_job(const JobDesc &d) {
-  uint32_t row_begin, row_end;
-  block_row_range(d.rows, d.unit, blockIdx.x, gridDim.x, &row_begin, &row_end);
+  uint32_t row_begin = 0, row_end = d.rows;
+  if (d.whole == 0) block_row_range(d.rows, d.unit, blockIdx.x, gridDim.x, &row_begin, &row_end);
   WarpJob j;
   j.row_bytes = d.cols * 2u;
   j.base = reinterpret_cast<const uint8_t *>(d.weight) + static_cast<uint64_t>(row_begin) * j.row_bytes;

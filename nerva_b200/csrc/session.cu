@@ -291,7 +291,8 @@ bool plan_state(Session *s, StaticArena &arena, void *base) {
   ok = ok && carve(arena, base, static_cast<uint64_t>(d.hidden), &s->o_out);
   ok = ok && carve(arena, base, static_cast<uint64_t>(d.hidden), &s->down);
   ok = ok && carve(arena, base, static_cast<uint64_t>(d.vocab), &s->logits);
-  const uint64_t split_slots = std::max<uint32_t>(s->max_splits, 16u);  // fused attention uses up to 16
+  // fused attention uses up to 16 spans, latent attention up to 64
+  const uint64_t split_slots = std::max<uint32_t>(s->max_splits, d.mla() ? 64u : 16u);
   ok = ok && carve(arena, base, static_cast<uint64_t>(d.heads), &s->attn_tickets);
   s->x_elems = static_cast<uint32_t>(max_x);
   ok = ok && carve(arena, base, static_cast<uint64_t>(d.heads) * split_slots * std::max(d.head_dim, d.mla_rank),
@@ -322,6 +323,8 @@ bool plan_state(Session *s, StaticArena &arena, void *base) {
   ok = ok && carve(arena, base, uint64_t{16}, &s->route_weights);
   ok = ok && carve(arena, base, uint64_t{4}, &s->shared_gate);
   ok = ok && carve(arena, base, moe_scratch + 4u, &s->moe_gate_up);
+  ok = ok && carve(arena, base, moe_scratch != 0 ? uint64_t{17} * d.hidden : uint64_t{4}, &s->moe_partial);
+  ok = ok && carve(arena, base, uint64_t{4}, &s->moe_ticket);
   s->timeline_nodes = 5u * d.layers + 1u;
   ok = ok && carve(arena, base, static_cast<uint64_t>(s->timeline_nodes) * kTimelineSlots, &s->timeline);
   return ok;
@@ -520,9 +523,6 @@ cudaError_t enqueue_step_kernel(Session *s, uint32_t splits, uint32_t sample) {
 
 // Router logits of a sparse-MoE layer.  The expert kernels follow the reference's MoE arithmetic
 // (unrounded fp32 activations); the router mat-vec does too, through the fp32 router kernel.
-static cudaError_t launch_moe_router_logits(Session *s, const ProjectionParams &p) {
-  return launch_router_logits_f32(s->stream, p, s->sm_count);
-}
 
 // Records the next profile event; the interval that ends here gets `bucket`.
 static void profile_mark(Session *s, StepProfile *prof, uint32_t bucket) {
@@ -782,9 +782,6 @@ cudaError_t enqueue_step(Session *s, uint32_t splits, uint32_t sample, uint64_t 
       p.resid_out = s->h_b;
       p.epilogue = kEpilogueStore;
       p.out_f32 = s->router_logits;
-      err = launch_moe_router_logits(s, p);
-      n += 1;
-      if (err != cudaSuccess) break;
       MoeRouteParams rp{};
       rp.logits = s->router_logits;
       rp.num_experts = L.num_experts;
@@ -792,7 +789,8 @@ cudaError_t enqueue_step(Session *s, uint32_t splits, uint32_t sample, uint64_t 
       rp.norm_topk_prob = L.norm_topk_prob;
       rp.expert_ids = s->route_ids;
       rp.weights = s->route_weights;
-      err = launch_moe_route(s->stream, rp, s->use_pdl);
+      // logits and routing in one launch (word 1 of the counter block is this launch's ticket)
+      err = launch_moe_router_route(s->stream, p, rp, s->moe_ticket + 1, s->sm_count);
       n += 1;
       profile_mark(s, prof, kBucketGateUp);
       if (err != cudaSuccess) break;
@@ -819,6 +817,8 @@ cudaError_t enqueue_step(Session *s, uint32_t splits, uint32_t sample, uint64_t 
       ep.gate_up_out = s->moe_gate_up;
       ep.shared_gate = s->shared_gate;
       ep.out_f32 = s->down;
+      ep.partial = s->moe_partial;
+      ep.ticket = s->moe_ticket;
       ep.error_word = s->device_error;
       ep.expert_base = L.expert_base;
       ep.expert_local = L.expert_local;
@@ -1112,6 +1112,9 @@ cudaError_t reset_request_state(Session *s, const uint32_t *prompt, uint32_t cou
   cudaError_t err = cudaMemsetAsync(s->device_slots, 0, s->slots_bytes, s->stream);
   if (err == cudaSuccess) err = cudaMemsetAsync(s->device_cursor, 0, sizeof(uint32_t), s->stream);
   if (err == cudaSuccess) err = cudaMemsetAsync(s->device_error, 0, sizeof(uint32_t), s->stream);
+  // completion counters are zero between launches; a request that failed half-way may have left one mid-count
+  if (err == cudaSuccess) err = cudaMemsetAsync(s->moe_ticket, 0, 4 * sizeof(uint32_t), s->stream);
+  if (err == cudaSuccess) err = cudaMemsetAsync(s->attn_tickets, 0, s->dims.heads * sizeof(uint32_t), s->stream);
   const uint64_t bytes = static_cast<uint64_t>(count) * sizeof(uint32_t);
   if (err == cudaSuccess)
     err = cudaMemcpyAsync(s->device_prompt, prompt, bytes, cudaMemcpyHostToDevice, s->stream);
@@ -1442,6 +1445,7 @@ cudaError_t allocate_state(Session *s, int32_t *stage) {
   if (err == cudaSuccess) err = cudaMemsetAsync(s->device_cursor, 0, sizeof(uint32_t), s->stream);
   if (err == cudaSuccess)
     err = cudaMemsetAsync(s->attn_tickets, 0, s->dims.heads * sizeof(uint32_t), s->stream);
+  if (err == cudaSuccess) err = cudaMemsetAsync(s->moe_ticket, 0, 4 * sizeof(uint32_t), s->stream);
   s->fused_attention = !s->dims.mla() && fused_attention_supported(s->dims.heads, s->dims.kv_heads, s->dims.head_dim);
   if (!s->dims.mla() && attention_rows_supported(s->dims.heads, s->dims.kv_heads, s->dims.head_dim)) {
     const uint64_t rows = static_cast<uint64_t>(s->dims.layers) * s->kv_pages * NERVA_KV_CACHE_BLOCK_TOKENS;

@@ -247,6 +247,8 @@ struct NervaCudaHfDecodeSequenceSession {
   float *mla_ql = nullptr;             // [heads][rank] absorbed queries
   float *router_logits = nullptr, *route_weights = nullptr, *shared_gate = nullptr, *moe_gate_up = nullptr;
   uint32_t *route_ids = nullptr;
+  float *moe_partial = nullptr;        // [17][hidden] per-expert contributions of a sparse MLP (moe.cu)
+  uint32_t *moe_ticket = nullptr;      // completion counter of the expert down launch, zero between launches
   // tensor parallel (nerva_b200_session_create_sharded)
   uint32_t tp_world = 1, tp_rank = 0;
   void *comm_block = nullptr;  // this rank's exchange buffer (own allocation, exported to the peers)
