@@ -697,7 +697,8 @@ def run_operator_workloads(kind: str, only_shape: str = "", only_tokens: int = 0
     run_attention_workload(1, 0, only_batch, only_context)
 
 
-def run_attention_workload(world: int, rank: int, only_batch: int = 0, only_context: int = 0) -> None:
+def run_attention_workload(world: int, rank: int, only_batch: int = 0, only_context: int = 0,
+                           emulated: bool = False) -> None:
     """Long-context GQA decode attention on the Qwen3-8B layer shape (32 query / 8 KV heads of 128),
     bf16 K/V in 16-token pages placed by a seeded permutation.  With world > 1 the KV heads are
     sharded the way the tensor-parallel session shards them: every rank owns 8 / world KV heads
@@ -724,7 +725,8 @@ def run_attention_workload(world: int, rank: int, only_batch: int = 0, only_cont
             copies = max(2, min(36, -(-320_000_000 // (4 * n))))
             out, ns = ops.gqa_decode_attention_sustained(q, k, v, table, batch, context, heads, kv_heads, d,
                                                          copies=copies, warmup=copies, iterations=4 * copies)
-            total_ns = _max_over_ranks(float(ns), world)
+            # emulated: one rank's shard measured alone on this GPU (every rank does the same work)
+            total_ns = float(ns) if emulated else _max_over_ranks(float(ns), world)
             # whole job: all KV heads of all ranks
             nbytes = world * batch * (2 * context * kv_heads * d * 2 + pages * 4 + heads * d * 4 * 2)
             gbs = nbytes / total_ns
@@ -738,7 +740,9 @@ def run_attention_workload(world: int, rank: int, only_batch: int = 0, only_cont
                                   "pages": "16-token pages placed by a seeded Fisher-Yates permutation",
                                   "timing": f"{4 * copies} launches back to back over the caches of {copies} layers "
                                             f"(larger than L2 together)",
-                                  "single_launch_us": _max_over_ranks(float(alone_ns), world) / 1e3,
+                                  "single_launch_us": (float(alone_ns) if emulated else
+                                                       _max_over_ranks(float(alone_ns), world)) / 1e3,
+                                  "ranks_measured": "one rank's shard on one GPU" if emulated else "all",
                                   "single_launch_note": "one launch timed alone, 192 MB written to flush L2 before it"}),
                       flush=True)
 
@@ -782,6 +786,8 @@ def main() -> None:
     ap.add_argument("--tokens", type=int, default=0, help="linear sweep: only this block size")
     ap.add_argument("--batch", type=int, default=0, help="attention sweep: only this batch size")
     ap.add_argument("--context", type=int, default=0, help="attention sweep: only this context length")
+    ap.add_argument("--shard-of", type=int, default=0, choices=[0, 2, 4, 8],
+                    help="attention sweep on one GPU: measure one rank's shard of an N-way split by KV head")
     ap.add_argument("--timeline", action="store_true",
                     help="add the in-graph timeline (kernel-written %%globaltimer stamps, mean over layers)")
     args = ap.parse_args()
@@ -797,6 +803,9 @@ def main() -> None:
         run_attention_workload(world, rank, args.batch, args.context)
         dist.barrier()
         dist.destroy_process_group()
+        return
+    if args.workload == "attention" and args.shard_of and world == 1:
+        run_attention_workload(args.shard_of, 0, args.batch, args.context, emulated=True)
         return
     if args.workload in ("linear", "attention"):
         if rank == 0:

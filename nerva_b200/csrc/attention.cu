@@ -39,7 +39,7 @@ constexpr uint32_t kAttnBlocksPerSm = 2;
 constexpr uint32_t kAttnStages = 3;
 constexpr uint32_t kPageTokens = NERVA_KV_CACHE_BLOCK_TOKENS;  // 16: one page = the K dimension of one P.V mma
 constexpr uint32_t kMaxGroupHeads = 8;
-constexpr uint32_t kMaxSplits = 64;
+constexpr uint32_t kMaxSplits = 256;   // the merge kernel's weight table
 constexpr float kLog2e = 1.4426950408889634f;
 
 template <uint32_t D>
@@ -404,18 +404,22 @@ __global__ void gqa_decode_generic_kernel(AttentionParams p) {
   }
 }
 
-// out = sum_s acc_s 2^{m_s - M} / sum_s l_s 2^{m_s - M}; one block per (head, batch).  Warp 0
-// turns the (m, l) pairs of all spans into normalised weights in one round trip (a lane per span),
-// then every thread adds its dimension over the spans with all loads issued before the first use.
+// out = sum_s acc_s 2^{m_s - M} / sum_s l_s 2^{m_s - M}; one block per (head, batch), blockDim =
+// (dims rounded up to 32, groups).  Warp 0 turns the (m, l) pairs of all spans into normalised
+// weights in one round trip (a lane per span); then thread (i, g) adds dimension i over the spans
+// g, g + groups, ... with eight loads in flight, and the groups' sums are added in group order.
+constexpr uint32_t kMergeGroups = 8;
 __global__ void gqa_merge_kernel(AttentionParams p) {
   __shared__ float weight[256];  // launch_attention refuses more spans
+  __shared__ float part[kMergeGroups][256];
   pdl_trigger();
   pdl_wait();  // the partials come from the launch just before
   const uint32_t head = blockIdx.x, b = blockIdx.y;
   const uint32_t d = p.head_dim, S = p.splits;
   const uint64_t slot0 = (static_cast<uint64_t>(b) * p.heads + head) * S;
-  if (threadIdx.x < 32u) {
-    const uint32_t lane = threadIdx.x;
+  const uint32_t tid = threadIdx.y * blockDim.x + threadIdx.x;
+  if (tid < 32u) {
+    const uint32_t lane = tid;
     float m = -INFINITY;
     for (uint32_t s = lane; s < S; s += 32u)
       if (__ldcg(p.partial_l + slot0 + s) > 0.0f) m = fmaxf(m, __ldcg(p.partial_m + slot0 + s));
@@ -433,21 +437,37 @@ __global__ void gqa_merge_kernel(AttentionParams p) {
     for (uint32_t s = lane; s < S; s += 32u) weight[s] *= inv;
   }
   __syncthreads();
-  for (uint32_t i = threadIdx.x; i < d; i += blockDim.x) {
+  const uint32_t i = threadIdx.x, g = threadIdx.y, groups = blockDim.y;
+  if (i < d) {
     float a = 0.0f;
-    uint32_t s = 0;
-    for (; s + 8u <= S; s += 8u) {
+    uint32_t s = g;
+    for (; s + 7u * groups < S; s += 8u * groups) {
       float v[8];
 #pragma unroll
-      for (uint32_t u = 0; u < 8u; ++u) v[u] = __ldcg(p.partial_acc + (slot0 + s + u) * d + i);
+      for (uint32_t u = 0; u < 8u; ++u) v[u] = __ldcg(p.partial_acc + (slot0 + s + u * groups) * d + i);
 #pragma unroll
-      for (uint32_t u = 0; u < 8u; ++u) a = fmaf(v[u], weight[s + u], a);
+      for (uint32_t u = 0; u < 8u; ++u) a = fmaf(v[u], weight[s + u * groups], a);
     }
-    for (; s < S; ++s) a = fmaf(__ldcg(p.partial_acc + (slot0 + s) * d + i), weight[s], a);
+    for (; s < S; s += groups) a = fmaf(__ldcg(p.partial_acc + (slot0 + s) * d + i), weight[s], a);
+    part[g][i] = a;
+  }
+  __syncthreads();
+  if (g == 0 && i < d) {
+    float a = part[0][i];
+    for (uint32_t k = 1; k < groups; ++k) a += part[k][i];
     const uint64_t o = (static_cast<uint64_t>(b) * p.heads + head) * d + i;
     if (p.out_f32 != nullptr) p.out_f32[o] = a;
     if (p.out_bf16 != nullptr) p.out_bf16[o] = f32_to_bf16_bits(a);
   }
+}
+
+// Threads of the merge launch: one per dimension, and as many span groups as the spans can use.
+dim3 merge_block(uint32_t head_dim, uint32_t splits) {
+  uint32_t x = ((head_dim + 31u) / 32u) * 32u;
+  if (x > 256u) x = 256u;
+  uint32_t groups = splits >= 64u ? kMergeGroups : (splits >= 16u ? 4u : 1u);
+  while (x * groups > 1024u) groups /= 2u;
+  return dim3(x, groups);
 }
 
 }  // namespace
@@ -483,7 +503,8 @@ uint32_t attention_default_splits(uint32_t context, uint32_t batch, uint32_t kv_
     const uint64_t slots = static_cast<uint64_t>(sm_count) * kAttnBlocksPerSm;
     const uint64_t waves = (static_cast<uint64_t>(units) * s + slots - 1u) / slots;
     const uint64_t span = (pages + s - 1u) / s + 8u;  // + a fixed cost per block (set-up, merge) in page units
-    const uint64_t cost = waves * span;
+    // the second launch merges s spans per head: about a page's time per 16 spans on top of a fixed two
+    const uint64_t cost = waves * span + 2u + s / 16u;
     if (cost < best_cost) {
       best_cost = cost;
       best = s;
@@ -522,9 +543,7 @@ cudaError_t launch_attention(cudaStream_t stream, const AttentionParams &p) {
   }
   cudaError_t err = cudaGetLastError();
   if (err != cudaSuccess) return err;
-  uint32_t threads = ((p.head_dim + 31u) / 32u) * 32u;
-  if (threads > 256) threads = 256;
-  return launch_with_pdl(gqa_merge_kernel, dim3(p.heads, p.batch), dim3(threads), 0, stream, paged, p);
+  return launch_with_pdl(gqa_merge_kernel, dim3(p.heads, p.batch), merge_block(p.head_dim, p.splits), 0, stream, paged, p);
 }
 
 bool attention_rows_supported(uint32_t heads, uint32_t kv_heads, uint32_t head_dim) {
@@ -558,8 +577,7 @@ cudaError_t launch_attention_rows(cudaStream_t stream, const AttentionParams &p,
     err = launch_with_pdl(gqa_decode_rows_kernel<64>, grid, dim3(kAttnWarps * 32), paged_smem_bytes<64>(), stream, true,
                           maps, p);
   if (err != cudaSuccess) return err;
-  uint32_t threads = ((p.head_dim + 31u) / 32u) * 32u;
-  return launch_with_pdl(gqa_merge_kernel, dim3(p.heads, p.batch), dim3(threads), 0, stream, true, p);
+  return launch_with_pdl(gqa_merge_kernel, dim3(p.heads, p.batch), merge_block(p.head_dim, p.splits), 0, stream, true, p);
 }
 
 }  // namespace nb

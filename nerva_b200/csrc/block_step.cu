@@ -209,6 +209,7 @@ bool plan_workspace(const Session *s, BlockWorkspace *ws, StaticArena &arena, vo
   ok = ok && carve(arena, base, sample * kBlockArgmaxChunks, &ws->best_index);
   ok = ok && carve(arena, base, rows, &ws->attn_rows);
   ok = ok && carve(arena, base, rows, &ws->token_rows);
+  ok = ok && carve(arena, base, sample, &ws->sample_rows_dev);
   return ok;
 }
 
@@ -483,9 +484,12 @@ cudaError_t enqueue_block_decode(NervaCudaHfDecodeSequenceSession *const *sessio
     err = launch_with_pdl(block_argmax_partials_kernel, dim3(kBlockArgmaxChunks, count), dim3(256), 0, stream, b.pdl,
                           ws.logits, d.vocab, ws.best_value, ws.best_index);
   n += 3;
-  for (uint32_t r = 0; err == cudaSuccess && r < count; ++r) {
+  // every row's token into its own session's ring, and its logits into the session's own buffer
+  // (nerva_b200_session_read_logits), in one launch
+  std::vector<BlockSampleRow> sample(count);
+  for (uint32_t r = 0; r < count; ++r) {
     Session *s = sessions[r];
-    StepState st{};
+    StepState &st = sample[r].state;
     st.cursor = s->device_cursor;
     st.prompt = s->device_prompt;
     st.prompt_count = s->device_cursor + 1;
@@ -493,14 +497,15 @@ cudaError_t enqueue_block_decode(NervaCudaHfDecodeSequenceSession *const *sessio
     st.max_context = s->max_context;
     st.vocab = d.embed_vocab;
     st.error_word = s->device_error;
-    // the session keeps its own copy of the logits it sampled from (nerva_b200_session_read_logits)
-    err = cudaMemcpyAsync(s->logits, ws.logits + static_cast<uint64_t>(r) * d.vocab,
-                          static_cast<uint64_t>(d.vocab) * sizeof(float), cudaMemcpyDeviceToDevice, stream);
-    if (err == cudaSuccess)
-      err = launch_sample_greedy(stream, st, ws.best_value + r * kBlockArgmaxChunks,
-                                 ws.best_index + r * kBlockArgmaxChunks, kBlockArgmaxChunks, 1, false, nullptr);
-    n += 1;
+    sample[r].logits = s->logits;
   }
+  if (err == cudaSuccess)  // pageable source: staged before the call returns
+    err = cudaMemcpyAsync(ws.sample_rows_dev, sample.data(), sample.size() * sizeof(BlockSampleRow),
+                          cudaMemcpyHostToDevice, stream);
+  if (err == cudaSuccess)
+    err = launch_block_sample(stream, ws.sample_rows_dev, count, ws.best_value, ws.best_index, kBlockArgmaxChunks,
+                              ws.logits, d.vocab, false);
+  n += 1;
   if (launches != nullptr) *launches += n;
   return err;
 }

@@ -121,12 +121,11 @@ __device__ __forceinline__ bool candidate_better(float v, uint32_t i, float best
 // ranks' candidates of this step and applies the same tie rule, so all ranks
 // write the same token.  Quiet steps exchange an empty candidate to keep the
 // counters equal to the number of completed steps.
-__global__ void sample_greedy_kernel(StepState st, const float *best_value,
-                                     const uint32_t *best_index, uint32_t partials,
-                                     uint32_t sample, TpSample tp) {
+__device__ __forceinline__ void sample_greedy_block(const StepState &st, const float *best_value,
+                                                    const uint32_t *best_index, uint32_t partials,
+                                                    uint32_t sample, const TpSample &tp) {
   __shared__ float sv[32];
   __shared__ uint32_t si[32];
-  pdl_wait();  // the arg-max partials come from the lm_head projection
   const uint32_t position = *st.cursor;
   if (position >= st.max_context) return;
   float bv = -INFINITY;
@@ -203,6 +202,42 @@ __global__ void sample_greedy_kernel(StepState st, const float *best_value,
     }
     *st.cursor = position + 1;
     if (tp.epoch != nullptr) *tp.epoch += 1ull;
+  }
+}
+
+__global__ void sample_greedy_kernel(StepState st, const float *best_value,
+                                     const uint32_t *best_index, uint32_t partials,
+                                     uint32_t sample, TpSample tp) {
+  pdl_wait();  // the arg-max partials come from the lm_head projection
+  sample_greedy_block(st, best_value, best_index, partials, sample, tp);
+}
+
+// The rows of a packed step, one block each: row r's token goes to its own session's ring at that
+// session's cursor (rows[r].state), from the row's `partials` arg-max candidates; blocks with
+// blockIdx.y > 0 copy a slice of the row's logits into the session's own logits buffer instead.
+__global__ void block_sample_kernel(const BlockSampleRow *rows, const float *best_value, const uint32_t *best_index,
+                                    uint32_t partials, const float *logits, uint32_t vocab) {
+  pdl_wait();
+  const BlockSampleRow row = rows[blockIdx.x];
+  if (blockIdx.y == 0) {
+    TpSample none{};
+    sample_greedy_block(row.state, best_value + blockIdx.x * partials, best_index + blockIdx.x * partials, partials, 1u,
+                        none);
+    return;
+  }
+  if (row.logits == nullptr) return;
+  const uint32_t slices = gridDim.y - 1u, slice = blockIdx.y - 1u;
+  const float *src = logits + static_cast<uint64_t>(blockIdx.x) * vocab;
+  if (vocab % 4u == 0) {  // rows start on 16-byte boundaries
+    const uint32_t quads = vocab / 4u;
+    const uint32_t begin = static_cast<uint32_t>(static_cast<uint64_t>(quads) * slice / slices);
+    const uint32_t end = static_cast<uint32_t>(static_cast<uint64_t>(quads) * (slice + 1u) / slices);
+    for (uint32_t i = begin + threadIdx.x; i < end; i += blockDim.x)
+      reinterpret_cast<float4 *>(row.logits)[i] = __ldcg(reinterpret_cast<const float4 *>(src) + i);
+  } else {
+    const uint32_t begin = static_cast<uint32_t>(static_cast<uint64_t>(vocab) * slice / slices);
+    const uint32_t end = static_cast<uint32_t>(static_cast<uint64_t>(vocab) * (slice + 1u) / slices);
+    for (uint32_t i = begin + threadIdx.x; i < end; i += blockDim.x) row.logits[i] = __ldcg(src + i);
   }
 }
 
@@ -345,6 +380,13 @@ __global__ void __launch_bounds__(256) exchange_wait_kernel(TpGather g, uint32_t
 cudaError_t launch_exchange_wait(cudaStream_t stream, const TpGather &gather, uint32_t cols, uint32_t *error_word,
                                  bool pdl) {
   return launch_with_pdl(exchange_wait_kernel, dim3(1), dim3(256), 0, stream, pdl, gather, cols, error_word);
+}
+
+cudaError_t launch_block_sample(cudaStream_t stream, const BlockSampleRow *rows, uint32_t count, const float *best_value,
+                                const uint32_t *best_index, uint32_t partials, const float *logits, uint32_t vocab,
+                                bool pdl) {
+  return launch_with_pdl(block_sample_kernel, dim3(count, 9u), dim3(256), 0, stream, pdl, rows, best_value, best_index,
+                         partials, logits, vocab);
 }
 
 cudaError_t launch_argmax(cudaStream_t stream, const float *logits, uint32_t count,

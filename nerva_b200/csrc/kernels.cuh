@@ -68,6 +68,7 @@ struct TpGather {
   unsigned long long *reduced;            // this rank's [cols] tagged sums of the phase (world > 2)
   const unsigned long long *epoch;
   uint32_t per_epoch, offset;
+  uint32_t two_stage;                     // world == 2 only: take the two-stage gather of the larger worlds
 };
 
 struct ProjectionParams {
@@ -337,6 +338,17 @@ struct TpSample {
 cudaError_t launch_sample_greedy(cudaStream_t stream, const StepState &st, const float *best_value,
                                  const uint32_t *best_index, uint32_t partials, uint32_t sample,
                                  bool pdl = false, const TpSample *tp = nullptr);
+// One row of a packed step for the batched sampler: the row's session (cursor, token ring, ...) and
+// where that session keeps the logits it sampled from (nullable).
+struct BlockSampleRow {
+  StepState state;
+  float *logits;
+};
+// Arg-max of every row (from `partials` candidates per row) into the row's own session, and the
+// rows' logits into the sessions' own buffers, in one launch.
+cudaError_t launch_block_sample(cudaStream_t stream, const BlockSampleRow *rows, uint32_t count, const float *best_value,
+                                const uint32_t *best_index, uint32_t partials, const float *logits, uint32_t vocab,
+                                bool pdl);
 // Waits (bounded) until every rank's entries of one exchange have arrived; closes a step that does
 // not sample, whose last exchange no projection reads.
 cudaError_t launch_exchange_wait(cudaStream_t stream, const TpGather &gather, uint32_t cols, uint32_t *error_word,

@@ -38,7 +38,7 @@ __host__ __device__ inline uint32_t round128(uint32_t v) { return (v + 127u) & ~
 __device__ __noinline__ void gather_prologue(const ProjectionParams &p, uint16_t *x, float *scratch) {
   const uint32_t tag = static_cast<uint32_t>(*p.gather.epoch) * p.gather.per_epoch + p.gather.offset;
   float *resid = blockIdx.x == 0 ? p.resid_out : nullptr;
-  if (p.gather.world == 2) {
+  if (p.gather.world == 2 && p.gather.two_stage == 0) {
     // two partials: every block adds them itself (one round trip)
     gather_norm_to_smem<2>(x, p.add_a, p.gather.recv, tag, p.add_bias, p.norm_weight, p.eps, p.cols, resid,
                            scratch, p.error_word);
@@ -46,7 +46,9 @@ __device__ __noinline__ void gather_prologue(const ProjectionParams &p, uint16_t
   }
   // four or eight partials: each block adds the ranks for its slice of the vector only, then every
   // block gathers the sums (reading all partials in every block costs more than the extra hop)
-  if (p.gather.world == 4) {
+  if (p.gather.world == 2) {
+    reduce_partials_slice<2>(p.gather.recv, p.gather.reduced, tag, p.cols, p.error_word);
+  } else if (p.gather.world == 4) {
     reduce_partials_slice<4>(p.gather.recv, p.gather.reduced, tag, p.cols, p.error_word);
   } else {
     reduce_partials_slice<8>(p.gather.recv, p.gather.reduced, tag, p.cols, p.error_word);

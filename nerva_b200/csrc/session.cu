@@ -579,6 +579,7 @@ cudaError_t enqueue_step(Session *s, uint32_t splits, uint32_t sample, uint64_t 
     gather.epoch = comm_at<unsigned long long>(s->comm_block, comm.epoch);
     gather.per_epoch = d.layers;
     gather.offset = exchange;
+    gather.two_stage = s->tp_two_stage ? 1u : 0u;
     return gather;
   };
   auto stamps_for = [s](uint32_t node) -> unsigned long long * {
@@ -1641,6 +1642,10 @@ static int create_session(const NervaCudaHfDecodeSequenceSessionCreateRequest *r
   if (shard != nullptr) {
     s->tp_world = shard->world;
     s->tp_rank = shard->rank;
+    // NERVA_B200_TWO_STAGE_GATHER=1: two ranks take the gather of four and eight (each block adds the
+    // ranks for its slice, then every block reads the sums), so that path can run where two GPUs are
+    const char *two_stage = getenv("NERVA_B200_TWO_STAGE_GATHER");
+    s->tp_two_stage = two_stage != nullptr && two_stage[0] == '1';
   }
 
   int device = 0;

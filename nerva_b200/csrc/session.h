@@ -118,6 +118,7 @@ struct BlockWorkspace {
   FusedAttentionRow *attn_rows = nullptr;  // [max_rows] device copies of the row descriptors
   bool paged_rows = false;      // the rows' attention runs on the paged tensor-pipe kernel (attention.cu)
   BlockTokenRow *token_rows = nullptr;
+  BlockSampleRow *sample_rows_dev = nullptr;  // [sample_rows] device copies of the sampler's row descriptors
 };
 constexpr uint32_t kBlockArgmaxChunks = 64;
 constexpr uint32_t kBlockMaxRows = 256;       // one MMA N
@@ -251,6 +252,7 @@ struct NervaCudaHfDecodeSequenceSession {
   uint32_t *moe_ticket = nullptr;      // completion counter of the expert down launch, zero between launches
   // tensor parallel (nerva_b200_session_create_sharded)
   uint32_t tp_world = 1, tp_rank = 0;
+  bool tp_two_stage = false;   // two ranks only: use the two-stage gather of the larger worlds
   void *comm_block = nullptr;  // this rank's exchange buffer (own allocation, exported to the peers)
   uint64_t comm_bytes = 0;
   void *comm_peers[nb::kMaxTpWorld] = {};  // every rank's exchange buffer as mapped here
