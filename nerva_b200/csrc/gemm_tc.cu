@@ -103,16 +103,24 @@ __device__ __host__ inline Partition make_partition(uint32_t rows, uint32_t cols
   return p;
 }
 // First block whose run touches tile t.
-__device__ inline uint32_t first_block_of_tile(const Partition &p, uint32_t t) {
+__device__ __host__ inline uint32_t first_block_of_tile(const Partition &p, uint32_t t) {
   const uint64_t at = static_cast<uint64_t>(t) * p.slices;
   uint32_t b = static_cast<uint32_t>(at * p.blocks / p.total);
   while (b + 1u < p.blocks && p.end(b) <= at) ++b;
   while (b > 0 && p.end(b - 1u) > at) --b;
   return b;
 }
+// Last block whose run touches tile t.
+__device__ __host__ inline uint32_t last_block_of_tile(const Partition &p, uint32_t t) {
+  const uint64_t last_slice = static_cast<uint64_t>(t + 1u) * p.slices - 1u;
+  uint32_t hi = static_cast<uint32_t>(last_slice * p.blocks / p.total);
+  while (hi + 1u < p.blocks && p.end(hi) <= last_slice) ++hi;
+  while (hi > 0 && p.begin(hi) > last_slice) --hi;
+  return hi;
+}
 // Workspace slot of block b's partial accumulator of tile t: slot 0 when the tile is where the
 // block's run begins, slot 1 when it is where the run ends in another tile.
-__device__ inline uint32_t partial_slot(const Partition &p, uint32_t b, uint32_t t) {
+__device__ __host__ inline uint32_t partial_slot(const Partition &p, uint32_t b, uint32_t t) {
   return 2u * b + (static_cast<uint32_t>(p.begin(b) / p.slices) == t ? 0u : 1u);
 }
 
@@ -271,12 +279,8 @@ __global__ void __launch_bounds__(4 * kTileRows) gemm_fixup_kernel(GemmKernelPar
   const uint32_t tile = blockIdx.x;
   const uint32_t tid = threadIdx.y * blockDim.x + threadIdx.x;
   if (tid == 0) {
-    const uint64_t last_slice = static_cast<uint64_t>(tile + 1u) * part.slices - 1u;
-    uint32_t hi = static_cast<uint32_t>(last_slice * part.blocks / part.total);
-    while (hi + 1u < part.blocks && part.end(hi) <= last_slice) ++hi;
-    while (hi > 0 && part.begin(hi) > last_slice) --hi;
     range[0] = first_block_of_tile(part, tile);
-    range[1] = hi;
+    range[1] = last_block_of_tile(part, tile);
   }
   __syncthreads();
   const uint32_t lo = range[0], hi = range[1];
@@ -291,7 +295,7 @@ __global__ void __launch_bounds__(4 * kTileRows) gemm_fixup_kernel(GemmKernelPar
   const uint32_t row_in_tile = threadIdx.x;
   const uint32_t m0 = blockIdx.y * kGroup + 4u * threadIdx.y;
   const uint64_t slot_floats = static_cast<uint64_t>(p.n_pad) * kTileRows;
-  const float *base = p.workspace + static_cast<uint64_t>(row_in_tile) * p.n_pad + m0;
+  const float *base = p.workspace + static_cast<uint64_t>(m0) * kTileRows + row_in_tile;
   float4 v = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
   for (uint32_t q = 0; q < count; q += kFixupBatch) {
     float4 x[kFixupBatch];
@@ -299,7 +303,8 @@ __global__ void __launch_bounds__(4 * kTileRows) gemm_fixup_kernel(GemmKernelPar
     for (uint32_t u = 0; u < kFixupBatch; ++u) {
       const uint32_t i = q + u < count ? q + u : count - 1u;
       const uint32_t slot = listed ? slots[i] : partial_slot(part, lo + i, tile);
-      x[u] = __ldcg(reinterpret_cast<const float4 *>(base + slot * slot_floats));
+      const float *src = base + slot * slot_floats;  // four tokens of this row: 128 rows apart
+      x[u] = make_float4(__ldcg(src), __ldcg(src + kTileRows), __ldcg(src + 2u * kTileRows), __ldcg(src + 3u * kTileRows));
     }
 #pragma unroll
     for (uint32_t u = 0; u < kFixupBatch; ++u) {
@@ -452,15 +457,14 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
       const uint32_t taddr = tmem_base + acc * acc_stride + ((quarter * 32u) << 16);
       const bool whole = seg.slice_begin == 0 && seg.slice_end == part.slices;
       if (!whole) {
-        // partial accumulator -> this block's workspace slot, [row][token]; gemm_fixup_kernel finishes the tile
-        float *slot = p.workspace + partial_slot(part, blockIdx.x, seg.tile) * slot_floats +
-                      static_cast<uint64_t>(row_in_tile) * p.n_pad;
+        // partial accumulator -> this block's workspace slot, [token][row] (a warp's 32 rows of one token
+        // are one 128-byte line); gemm_fixup_kernel, or the caller's next kernel, finishes the tile
+        float *slot = p.workspace + partial_slot(part, blockIdx.x, seg.tile) * slot_floats + row_in_tile;
         for (uint32_t g = 0; g < p.n_pad; g += kGroup) {
           float v[kGroup];
           tmem_load16(taddr + g, v);
 #pragma unroll
-          for (uint32_t j = 0; j < kGroup; j += 4u)
-            *reinterpret_cast<float4 *>(slot + g + j) = make_float4(v[j], v[j + 1u], v[j + 2u], v[j + 3u]);
+          for (uint32_t j = 0; j < kGroup; ++j) slot[static_cast<uint64_t>(g + j) * kTileRows] = v[j];
         }
       } else {
         const uint32_t row = seg.tile * kTileRows + row_in_tile;
@@ -545,6 +549,11 @@ uint32_t gemm_smem_bytes(uint32_t n_pad, uint32_t stages) {
 uint32_t gemm_blocks(uint32_t rows, uint32_t cols, uint32_t sm_count) {
   const Partition p = make_partition(rows, cols, 1);
   const uint32_t want = 2u * sm_count;
+  // Between one and two row tiles per SM (gate/up of the 8B shapes: 192 tiles): one block per tile.
+  // Nothing is split, so no fix-up launch follows; the SMs that hold two blocks stream twice the
+  // bytes of the others, which the memory system evens out better than a second launch costs
+  // (gate/up at 64 tokens: 0.52 -> 0.79 of the measured HBM peak).
+  if (p.tiles >= sm_count && p.tiles <= want) return p.tiles;
   return p.total < want ? static_cast<uint32_t>(p.total) : want;
 }
 

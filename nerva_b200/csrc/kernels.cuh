@@ -4,6 +4,8 @@
 #pragma once
 
 #include <cuda_runtime.h>
+
+#include <vector>
 #include <stdint.h>
 
 #include "../../include/nerva_b200_api.h"
