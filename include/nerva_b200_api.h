@@ -939,8 +939,8 @@ int nerva_b200_gqa_decode_attention_sustained(const float *q, const uint16_t *ke
  * the limit in nerva_b200_last_error()).  `stream` is a cudaStream_t (NULL: the
  * default stream); the call returns once the stream has finished the work.
  * Calls on one device share the array, so overlapping calls race: serialise
- * them.  The first call on each device performs the set-up and should be made
- * before any stream capture begins.  No counterpart in the reference: it is
+ * them.  The first call on each device also performs the set-up (the address
+ * of the array, the kernels' attributes).  No counterpart in the reference: it is
  * for callers whose arena already owns the device memory, or whose decode loop
  * must report zero hot-path allocations. */
 int nerva_b200_gqa_decode_attention_static_scratch(
