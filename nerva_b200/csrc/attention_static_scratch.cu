@@ -20,7 +20,6 @@
 //    one device (two streams, two threads) race on the array: serialise them.
 //  * The first call on each device does the set-up (address of the array, SM
 //    count, shared-memory attributes of the kernels) with that device current.
-//    Make that first call before any stream capture begins.
 //  * The call returns after `stream` has finished the work, because it reads the
 //    kernel's error word back.
 #include <mutex>
