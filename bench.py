@@ -69,24 +69,39 @@ class ClockSampler:
 
     def __init__(self, gpu_index: int = 0):
         self.gpu_index = gpu_index
-        self.lines: list[str] = []
+        self.lines: list[tuple[float, str]] = []
         self.proc = None
         self.thread = None
+        self.begin = None
 
-    def start(self):
+    def start(self, wait_s: float = 8.0):
+        """Starts the sampling process and waits until its first sample has arrived (nvidia-smi takes a
+        while to come up on a machine with many GPUs), so that a short timed region is not over before
+        the first sample; the region itself begins at mark()."""
         try:
             self.proc = subprocess.Popen(
                 ["nvidia-smi", f"--id={self.gpu_index}", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits",
-                 "-lms", "100"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+                 "-lms", "50"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
         except OSError:
             self.proc = None
             return
         self.thread = threading.Thread(target=self._pump, daemon=True)
         self.thread.start()
+        deadline = time.perf_counter() + wait_s
+        while not self.lines and time.perf_counter() < deadline and self.proc.poll() is None:
+            time.sleep(0.01)
+        self.mark()
+
+    def mark(self):
+        """The load to be sampled starts now: earlier samples are dropped from the report."""
+        self.begin = time.perf_counter()
 
     def _pump(self):
         for line in self.proc.stdout:
-            self.lines.append(line.strip())
+            self.lines.append((time.perf_counter(), line.strip()))
+
+    def samples_since_mark(self) -> int:
+        return sum(1 for t, _ in self.lines if self.begin is None or t >= self.begin)
 
     def stop(self) -> dict:
         if self.proc is None:
@@ -98,7 +113,9 @@ class ClockSampler:
             self.proc.kill()
         sm, sm_max, reasons = [], [], set()
         names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
-        for line in self.lines:
+        for stamp, line in self.lines:
+            if self.begin is not None and stamp < self.begin:
+                continue
             parts = [p.strip() for p in line.split(",")]
             if len(parts) < 9:
                 continue
@@ -112,6 +129,20 @@ class ClockSampler:
                     reasons.add(name)
         return {"sm_mhz": float(np.median(sm)) if sm else None, "sm_max_mhz": max(sm_max) if sm_max else None,
                 "samples": len(sm), "reasons": sorted(reasons)}
+
+
+MAX_EXTRA_CLOCK_STEPS = 512
+
+
+def extra_clock_steps(timed_s: float, steps: int) -> int:
+    """Untimed steps to run behind the timed and the end-to-end region (each `steps` long, about
+    timed_s) so that the clock sampler, which reports every 50 ms, sees this load for about 0.35 s."""
+    if timed_s <= 0 or steps <= 0:
+        return 0
+    missing = 0.35 - 2.0 * timed_s
+    if missing <= 0:
+        return 0
+    return min(MAX_EXTRA_CLOCK_STEPS, int(missing / (timed_s / steps)) + 1)
 
 
 def workload(name: str, layers: int = 0, prompt_tokens: int = 0):
@@ -349,7 +380,8 @@ def run_ours(args, cfg, rank: int, world: int) -> dict:
     prompt = synth.prompt_ids(cfg)
     profile_steps = 4
     timeline_steps = 8
-    max_context = cfg.prompt_tokens + 1 + args.warmup + 2 * args.steps + profile_steps + 2 * timeline_steps + 8
+    max_context = (cfg.prompt_tokens + 1 + args.warmup + 2 * args.steps + profile_steps + 2 * timeline_steps + 8 +
+                   MAX_EXTRA_CLOCK_STEPS)
     t0 = time.perf_counter()
     session = CudaHfDecodeSequenceSession(ck, max_context, engine=args.engine)
     if session.status != SmokeStatus.OK:
@@ -372,6 +404,7 @@ def run_ours(args, cfg, rank: int, world: int) -> dict:
     clocks = ClockSampler(int(os.environ.get("NERVA_GPU_INDEX", "0")))
     clocks.start()
     sync()
+    clocks.mark()
     timed = loop.advance(args.steps)             # K graph replays, timed by CUDA events on the session stream
     sync()
     if timed.status != SmokeStatus.OK or len(timed.tokens) != args.steps:
@@ -385,6 +418,13 @@ def run_ours(args, cfg, rank: int, world: int) -> dict:
         e2e_stream += out.tokens
     e2e_s = time.perf_counter() - t0
     e2e_tokens = len(e2e_stream)
+    # a timed region of a fraction of a second may end before the sampler has seen it: the same step keeps
+    # running, untimed, until a few samples of the clocks under this load exist
+    # (a number of steps every rank computes alike from the slowest rank's time: the ranks step together)
+    agreed_s = _max_over_ranks(device_s, world)
+    extra = extra_clock_steps(agreed_s, args.steps)
+    if extra:
+        loop.advance(extra)
     clock_info = clocks.stop()
     stream = first.tokens + warm.tokens + timed.tokens + e2e_stream
 
@@ -579,7 +619,7 @@ def run_deepseek_workload(args, rank: int = 0, world: int = 1) -> None:
         cfg = dataclasses.replace(cfg, layers=args.layers, name=f"{cfg.name} cut to {args.layers} layers")
     if args.prompt_tokens:
         cfg = dataclasses.replace(cfg, prompt_tokens=args.prompt_tokens)
-    max_context = cfg.prompt_tokens + max(args.warmup, 3) + 2 * args.steps + 16
+    max_context = cfg.prompt_tokens + max(args.warmup, 3) + 2 * args.steps + 16 + MAX_EXTRA_CLOCK_STEPS
     t0 = time.perf_counter()
     if world > 1:
         from nerva_b200 import tp
@@ -599,10 +639,10 @@ def run_deepseek_workload(args, rank: int = 0, world: int = 1) -> None:
     loop.advance(max(args.warmup, 3))
     sync = _barrier_fn(world)
     sampler = ClockSampler(int(os.environ.get("NERVA_GPU_INDEX", "0")))
-    sync()
     sampler.start()
+    sync()
+    sampler.mark()
     timed = loop.advance(args.steps)
-    clocks = sampler.stop()
     sync()
     if timed.status != SmokeStatus.OK or len(timed.tokens) != args.steps:
         raise RuntimeError(f"timed advance failed: {timed.error}")
@@ -615,6 +655,10 @@ def run_deepseek_workload(args, rank: int = 0, world: int = 1) -> None:
             raise RuntimeError(f"advance failed: {out.error}")
         e2e_tokens += out.tokens
     e2e_s = _max_over_ranks(time.perf_counter() - t4, world)
+    extra = extra_clock_steps(device_s, args.steps)  # as in the dense bench: a few clock samples under this load
+    if extra:
+        loop.advance(extra)
+    clocks = sampler.stop()
     # where the step's time goes: events between launch groups, un-captured (includes event overhead)
     profile_us = None
     if world == 1:
