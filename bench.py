@@ -263,6 +263,55 @@ def parity_block(cfg, tokens) -> dict:
     }
 
 
+def teacher_forced_parity(session, cfg, positions: int = 64) -> dict | None:
+    """The session against the committed oracle stream position by position: it decodes freely until
+    its token differs from the oracle's, then the request is restarted on the prompt plus the oracle's
+    own tokens, so that every position is compared on the oracle's history.  A differing token is a
+    near tie when the oracle's top-1 minus top-2 margin there is below the bound (twice the oracle's
+    own distance to itself under another fp32 summation order, twice over) and the token is among the
+    oracle's eight best."""
+    from nerva_b200 import synth
+    from nerva_b200.session import CudaHfDecodeSequenceLoop, SmokeStatus
+    path = os.path.join(ROOT, "tests", "golden", "qwen3_8b.json")
+    if cfg.name != "qwen3-8b" or cfg.prompt_tokens != 512 or not os.path.exists(path):
+        return None
+    with open(path) as f:
+        golden = json.load(f)
+    g = golden["cuda"]
+    sweep = golden["depth_sweep"]
+    self_distance = sweep["self_distance"][sweep["depths"].index(cfg.layers)] if cfg.layers in sweep["depths"] else None
+    if self_distance is None:
+        return None
+    bound = max(2e-2, 2.0 * self_distance)
+    idx = golden["sample_indices"]
+    prompt = synth.prompt_ids(cfg)
+    positions = min(positions, len(g["tokens"]))
+    start, loop = CudaHfDecodeSequenceLoop.start(session, prompt)
+    if start.status != SmokeStatus.OK:
+        return {"error": start.error}
+    equal, ties, outside, worst = 0, [], [], 0.0
+    for i in range(positions):
+        out = loop.advance(1)
+        if out.status != SmokeStatus.OK or not out.tokens:
+            return {"error": out.error}
+        logits = session.read_logits()
+        want = np.array(g["logit_samples"][i] + g["top8_value"][i], dtype=np.float32)
+        got = np.concatenate([logits[idx], logits[g["top8_index"][i]]])
+        worst = max(worst, float(np.abs(got - want).max()))
+        if out.tokens[0] == g["tokens"][i]:
+            equal += 1
+            continue
+        entry = {"position": i, "oracle_margin": g["top1_minus_top2"][i]}
+        (ties if g["top1_minus_top2"][i] <= 2.0 * bound and out.tokens[0] in g["top8_index"][i] else outside).append(entry)
+        if i + 1 < positions:
+            restarted = np.concatenate([prompt, np.array(g["tokens"][:i + 1], dtype=np.uint32)])
+            start, loop = CudaHfDecodeSequenceLoop.start(session, restarted)
+            if start.status != SmokeStatus.OK:
+                return {"error": start.error}
+    return {"positions": positions, "tokens_equal": equal, "near_ties": ties, "outside_the_tie_rule": outside,
+            "max_abs_logit_error_on_samples": worst, "logit_bound": bound, "oracle_self_distance": self_distance}
+
+
 def timeline_busy_us(session, loop, cfg, steps: int) -> dict:
     """Per operator kind, the time its launches are busy inside ordinary graph replays, net of
     overlap: launches are walked in launch order and each is charged from max(its first stamp, the
@@ -459,6 +508,8 @@ def run_ours(args, cfg, rank: int, world: int) -> dict:
                                            for i, name in enumerate(("qkv", "attention", "o", "gate_up", "down"))}}
     # per-kernel pass: events between launch groups, un-captured
     prof = session.profile_steps(profile_steps)
+    # parity on the oracle's history, position by position (restarts the session's request: last use of it)
+    forced_parity = teacher_forced_parity(session, cfg) if world == 1 and args.engine == 0 else None
     session.destroy()
 
     device_s = _max_over_ranks(device_s, world)
@@ -517,7 +568,7 @@ def run_ours(args, cfg, rank: int, world: int) -> dict:
             "isolated_us_per_token": isolated_ns / 1e3,
             "whole_step_frac": (bytes_per_token * args.steps / device_s / 1e9) / peaks["hbm_gbs"],
         },
-        "parity": parity_block(cfg, stream),
+        "parity": dict(parity_block(cfg, stream), teacher_forced=forced_parity),
         "in_step_us_per_token": busy,
         "profile_us_per_token": {k: v["ns"] / profile_steps / 1e3 for k, v in prof.items()},
         "setup_s": {"generate_weights": gen_s, "session_create": create_s, "prefill": prefill_s},
