@@ -128,7 +128,9 @@ struct MoeShared {
 };
 __host__ __device__ inline uint32_t round128u(uint32_t v) { return (v + 127u) & ~127u; }
 
-// fp32 twin of add_norm_to_smem: x = (r * scale) * w, unrounded.
+// fp32 twin of add_norm_to_smem: x = (r * scale) * w, unrounded.  PLANAR: element i goes to
+// xf32_index(i, cols), the layout the fp32 path of the weight stream reads (row_stream.cuh).
+template <bool PLANAR>
 __device__ void add_norm_to_smem_f32(float *x, const float *a, const float *b, const uint16_t *bias,
                                      const uint16_t *w, float eps, uint32_t cols, float *scratch) {
   float sumsq = 0.0f;
@@ -136,12 +138,15 @@ __device__ void add_norm_to_smem_f32(float *x, const float *a, const float *b, c
     float r = b != nullptr ? __ldcg(b + i) : __ldcg(a + i);
     if (bias != nullptr) r += bf16_bits_to_f32(bias[i]);
     if (b != nullptr) r += __ldcg(a + i);
-    x[i] = r;
+    x[PLANAR ? xf32_index(i, cols) : i] = r;
     sumsq += r * r;
   }
   const float total = block_sum(sumsq, scratch);
   const float scale = rsqrtf(total / static_cast<float>(cols) + eps);
-  for (uint32_t i = threadIdx.x; i < cols; i += blockDim.x) x[i] = x[i] * scale * bf16_bits_to_f32(w[i]);
+  for (uint32_t i = threadIdx.x; i < cols; i += blockDim.x) {
+    const uint32_t at = PLANAR ? xf32_index(i, cols) : i;
+    x[at] = x[at] * scale * bf16_bits_to_f32(w[i]);
+  }
   __syncthreads();
 }
 
@@ -161,7 +166,7 @@ __global__ void __launch_bounds__(256) moe_router_logits_kernel(ProjectionParams
       p.resid_out[i] = r;
     }
   }
-  add_norm_to_smem_f32(xr, p.add_a, p.add_b, p.add_bias, p.norm_weight, p.eps, p.cols, scratch);
+  add_norm_to_smem_f32<false>(xr, p.add_a, p.add_b, p.add_bias, p.norm_weight, p.eps, p.cols, scratch);
   const uint32_t lane = threadIdx.x & 31u, warp = threadIdx.x >> 5, warps = blockDim.x >> 5;
   for (uint32_t row = blockIdx.x * warps + warp; row < p.rows; row += gridDim.x * warps) {
     const uint4 *w = reinterpret_cast<const uint4 *>(p.weight + static_cast<uint64_t>(row) * p.cols);
@@ -195,7 +200,7 @@ __global__ void __launch_bounds__(kRouteThreads) moe_router_route_kernel(Project
       p.resid_out[i] = r;
     }
   }
-  add_norm_to_smem_f32(xr, p.add_a, p.add_b, p.add_bias, p.norm_weight, p.eps, p.cols, scratch);
+  add_norm_to_smem_f32<false>(xr, p.add_a, p.add_b, p.add_bias, p.norm_weight, p.eps, p.cols, scratch);
   for (uint32_t row = blockIdx.x; row < p.rows; row += gridDim.x) {
     const uint4 *w = reinterpret_cast<const uint4 *>(p.weight + static_cast<uint64_t>(row) * p.cols);
     float acc = 0.0f;
@@ -339,12 +344,12 @@ __global__ void __launch_bounds__(kStreamThreads, 1) moe_expert_kernel(MoeExpert
   for (uint32_t i = threadIdx.x; i < p.max_rows_per_block; i += blockDim.x) row_total[i] = 0.0f;
 
   if (PHASE == kGateUp) {
-    add_norm_to_smem_f32(x, p.add_a, p.add_b, p.add_bias, p.norm_weight, p.eps, p.hidden, sh.scratch);
+    add_norm_to_smem_f32<true>(x, p.add_a, p.add_b, p.add_bias, p.norm_weight, p.eps, p.hidden, sh.scratch);
     if (blockIdx.x == 0 && p.shared_intermediate != 0) {
       // gate of the shared expert: sigmoid(shared_router . x), or 1 for shared experts that are always on
       float dot = 0.0f;
       for (uint32_t i = threadIdx.x; p.w_shared_router != nullptr && i < p.hidden; i += blockDim.x)
-        dot += bf16_bits_to_f32(p.w_shared_router[i]) * x[i];
+        dot += bf16_bits_to_f32(p.w_shared_router[i]) * x[xf32_index(i, p.hidden)];
       const float sum = block_sum(dot, sh.scratch);
       if (threadIdx.x == 0) *p.shared_gate = p.w_shared_router != nullptr ? 1.0f / (1.0f + expf(-sum)) : 1.0f;
     }
@@ -366,7 +371,8 @@ __global__ void __launch_bounds__(kStreamThreads, 1) moe_expert_kernel(MoeExpert
       // x = silu(gate) * up of expert g, unrounded
       const float *gate = p.gate_up_out + place;
       const float *up = gate + job.cols;
-      for (uint32_t i = threadIdx.x; i < job.cols; i += blockDim.x) x[i] = silu(__ldcg(gate + i)) * __ldcg(up + i);
+      for (uint32_t i = threadIdx.x; i < job.cols; i += blockDim.x)
+        x[xf32_index(i, job.cols)] = silu(__ldcg(gate + i)) * __ldcg(up + i);
       __syncthreads();
     }
     stream_consume<true>(rs, sh.stream, j, x, row_total, p.error_word);

@@ -231,15 +231,19 @@ __device__ __forceinline__ float dot8_f32(const uint4 &w, const float4 &xa, cons
   acc = fmaf(bf16x2_hi(w.w), xb.w, acc);
   return acc;
 }
-// One 16-byte piece of weights at `wp` times the matching activations: bf16 at
-// byte offset `off` of xp, or (XF32) fp32 at byte offset 2 * off.
+// fp32 activations (XF32) sit in shared memory in two planes, so that the lanes of a warp read
+// consecutive 16-byte pieces (a plain [cols] array would put a lane's two float4 32 bytes from the
+// next lane's: a two-way bank conflict on every load): element i of a `cols`-wide vector is at
+// xf32_index(i, cols) — the first four of every eight elements in plane A, the last four in plane B.
+__host__ __device__ inline uint32_t xf32_index(uint32_t i, uint32_t cols) {
+  return ((i & 4u) != 0 ? cols / 2u : 0u) + ((i >> 3) << 2) + (i & 3u);
+}
+// One 16-byte piece of weights at `wp + off` times the matching activations: bf16 at byte offset
+// `off` of xp, or (XF32) the piece's two float4 at index off / 16 of the planes xa and xb.
 template <bool XF32>
-__device__ __forceinline__ float dot_piece(const uint8_t *wp, const uint8_t *xp, uint32_t off, float acc) {
-  if (XF32) {
-    const float4 xa = *reinterpret_cast<const float4 *>(xp + 2u * off);
-    const float4 xb = *reinterpret_cast<const float4 *>(xp + 2u * off + 16u);
-    return dot8_f32(lds128(wp + off), xa, xb, acc);
-  }
+__device__ __forceinline__ float dot_piece(const uint8_t *wp, const uint8_t *xp, const float4 *xa, const float4 *xb,
+                                           uint32_t off, float acc) {
+  if (XF32) return dot8_f32(lds128(wp + off), xa[off / 16u], xb[off / 16u], acc);
   return dot8(lds128(wp + off), lds128(xp + off), acc);
 }
 
@@ -276,17 +280,39 @@ __device__ __forceinline__ void stream_consume(RowStream &rs, StreamShared &sh, 
       report_error(error_word, kErrTmaWaitTimeout);
     }
     const uint8_t *wp = rs.ring + slot * kChunkBytes + lane * 16u;
-    const uint8_t *xp = reinterpret_cast<const uint8_t *>(x) +
-                        (XF32 ? 2u : 1u) * ((pos - (row_end - job.row_bytes)) + lane * 16u);
+    const uint32_t row_offset = pos - (row_end - job.row_bytes);  // bytes into the row
+    const uint8_t *xp = reinterpret_cast<const uint8_t *>(x) + row_offset + lane * 16u;
     if (XF32) {
+      // planes A and B of the fp32 vector (xf32_index), at this lane's first piece of the chunk
+      const float4 *xa = reinterpret_cast<const float4 *>(x) + row_offset / 16u + lane;
+      const float4 *xb = xa + job.row_bytes / 16u;
       uint32_t off = 0;
-      for (; off + 4u * kSweepBytes <= len; off += 4u * kSweepBytes) {
-        acc[0] = dot_piece<true>(wp, xp, off, acc[0]);
-        acc[1] = dot_piece<true>(wp, xp, off + kSweepBytes, acc[1]);
-        acc[2] = dot_piece<true>(wp, xp, off + 2u * kSweepBytes, acc[2]);
-        acc[3] = dot_piece<true>(wp, xp, off + 3u * kSweepBytes, acc[3]);
+      if (len == kChunkBytes) {
+#pragma unroll
+        for (uint32_t i = 0; i < kChunkBytes / kSweepBytes; i += 4) {
+          acc[0] = dot_piece<true>(wp, xp, xa, xb, (i + 0) * kSweepBytes, acc[0]);
+          acc[1] = dot_piece<true>(wp, xp, xa, xb, (i + 1) * kSweepBytes, acc[1]);
+          acc[2] = dot_piece<true>(wp, xp, xa, xb, (i + 2) * kSweepBytes, acc[2]);
+          acc[3] = dot_piece<true>(wp, xp, xa, xb, (i + 3) * kSweepBytes, acc[3]);
+        }
+        off = kChunkBytes;
+      } else if (len == kChunkBytes / 2u) {
+#pragma unroll
+        for (uint32_t i = 0; i < kChunkBytes / kSweepBytes / 2u; i += 4) {
+          acc[0] = dot_piece<true>(wp, xp, xa, xb, (i + 0) * kSweepBytes, acc[0]);
+          acc[1] = dot_piece<true>(wp, xp, xa, xb, (i + 1) * kSweepBytes, acc[1]);
+          acc[2] = dot_piece<true>(wp, xp, xa, xb, (i + 2) * kSweepBytes, acc[2]);
+          acc[3] = dot_piece<true>(wp, xp, xa, xb, (i + 3) * kSweepBytes, acc[3]);
+        }
+        off = kChunkBytes / 2u;
       }
-      for (; off + lane * 16u < len; off += kSweepBytes) acc[0] = dot_piece<true>(wp, xp, off, acc[0]);
+      for (; off + 4u * kSweepBytes <= len; off += 4u * kSweepBytes) {
+        acc[0] = dot_piece<true>(wp, xp, xa, xb, off, acc[0]);
+        acc[1] = dot_piece<true>(wp, xp, xa, xb, off + kSweepBytes, acc[1]);
+        acc[2] = dot_piece<true>(wp, xp, xa, xb, off + 2u * kSweepBytes, acc[2]);
+        acc[3] = dot_piece<true>(wp, xp, xa, xb, off + 3u * kSweepBytes, acc[3]);
+      }
+      for (; off + lane * 16u < len; off += kSweepBytes) acc[0] = dot_piece<true>(wp, xp, xa, xb, off, acc[0]);
     } else if (len == kChunkBytes) {
 #pragma unroll
       for (uint32_t i = 0; i < kChunkBytes / kSweepBytes; i += 4) {
