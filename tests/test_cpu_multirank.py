@@ -253,3 +253,15 @@ def test_expert_shards_partition_the_experts_and_keep_everything_else_whole():
     import dataclasses
     with pytest.raises(ValueError):  # an odd number of sparse layers: the exchange buffers would not alternate
         synth.expert_shard_config(dataclasses.replace(cfg, layers=4), 2)
+
+
+def test_extra_clock_steps_are_a_function_of_the_agreed_time_only():
+    """The untimed steps that keep the load up for the clock sampler are computed from the slowest
+    rank's time, which every rank holds after the max over ranks: equal inputs, equal step counts
+    (ranks that stepped a different number of times would leave each other waiting in an exchange)."""
+    sys.path.insert(0, ROOT)
+    import bench
+    assert bench.extra_clock_steps(0.5, 128) == 0            # the timed and the end-to-end region cover 0.35 s
+    assert bench.extra_clock_steps(0.104, 64) == int((0.35 - 0.208) / (0.104 / 64)) + 1
+    assert bench.extra_clock_steps(1e-4, 4) == bench.MAX_EXTRA_CLOCK_STEPS
+    assert bench.extra_clock_steps(0.0, 8) == 0 and bench.extra_clock_steps(0.1, 0) == 0
