@@ -15,9 +15,11 @@
 // Decomposition ("stream-K").  The sequence of (row tile, 64-wide slice) pairs is cut into one
 // contiguous, equally long run per thread block, so every SM streams the same number of weight
 // bytes whatever the shape (QKV has 48 row tiles, lm_head 1187).  A run that starts or ends in the
-// middle of a row tile leaves a partial accumulator in a workspace slot; a small second launch
-// (gemm_fixup_kernel, one block per split tile and 16 tokens) adds the partials of every split tile
-// in ascending block order and runs the epilogue for it.  Summing inside the projection kernel by
+// middle of a row tile leaves a partial accumulator in a workspace slot (fp32, token-major: a warp's
+// 32 rows of one token are one line); a small second launch (gemm_fixup_kernel, one block per split
+// tile and 16 tokens) adds the partials of every split tile in ascending block order and runs the
+// epilogue for it.  A matrix with between one and two row tiles per SM gets one block per tile
+// instead: nothing is split and no second launch follows.  Summing inside the projection kernel by
 // the last block to arrive was measured first: that one block reads every partial of its tile with
 // 128 threads while the rest of the grid has left, 10 to 27 us for a 64-token block.  The partition
 // depends on the shape only, so a token's result does not depend on which other tokens share its
