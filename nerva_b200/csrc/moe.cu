@@ -14,6 +14,17 @@
 // path, which rounds both to bf16), accumulate in fp32, and the expert outputs
 // are added as down += weight * y in rank order, then the shared expert scaled by
 // sigmoid(shared_router . x).
+//
+// Shape of the expert kernels' weight stream (row_stream.cuh, set for this file only): 16 warps per
+// block, each with a ring of two 4 KB slots, where the dense projections run 8 warps with three 8 KB
+// slots.  An expert's rows are short (4 KB for gate/up at hidden 2048, 2.8 KB for down at
+// intermediate 1408) and the fp32 activations cost two shared loads per weight load, so these
+// kernels are bound by the instruction latency of a warp, not by the bytes in flight: twice the
+// warps hide twice the latency (DeepSeek-V2-Lite step 3.23 -> 2.94 ms; 12, 20 and 24 warps and a
+// third slot measured slower).
+#define NERVA_STREAM_WARPS 16
+#define NERVA_CHUNK_BYTES 4096
+#define NERVA_STREAM_SLOTS 2
 #include "kernels.cuh"
 #include "row_stream.cuh"
 #include "step_device.cuh"

@@ -99,23 +99,30 @@ __device__ __forceinline__ WarpJob warp_job(const JobDesc &d) {
 struct StreamCursor {
   uint32_t pos;      // byte offset of the next chunk
   uint32_t row_end;  // end byte of the row that contains pos
+  uint32_t row;      // block-local index of that row
 };
 __device__ __forceinline__ StreamCursor cursor_at_start(const WarpJob &j) {
   StreamCursor c;
   c.pos = j.begin;
-  c.row_end = (j.begin / j.row_bytes + 1u) * j.row_bytes;
+  c.row = j.begin / j.row_bytes;
+  c.row_end = (c.row + 1u) * j.row_bytes;
   return c;
 }
-// Length of the chunk at the cursor; advances the cursor.
+// Length of the chunk at the cursor, its position, the end of its row and the row's index;
+// advances the cursor.
 __device__ __forceinline__ uint32_t cursor_next(const WarpJob &j, StreamCursor &c, uint32_t *pos,
-                                                uint32_t *row_end) {
+                                                uint32_t *row_end, uint32_t *row = nullptr) {
   uint32_t len = kChunkBytes;
   if (c.row_end - c.pos < len) len = c.row_end - c.pos;
   if (j.end - c.pos < len) len = j.end - c.pos;
   *pos = c.pos;
   *row_end = c.row_end;
+  if (row != nullptr) *row = c.row;
   c.pos += len;
-  if (c.pos == c.row_end) c.row_end += j.row_bytes;
+  if (c.pos == c.row_end) {
+    c.row_end += j.row_bytes;
+    c.row += 1u;
+  }
   return len;
 }
 
@@ -218,6 +225,26 @@ __device__ __forceinline__ float dot8(const uint4 &w, const uint4 &x, float acc)
   return acc;
 }
 
+// Packed fp32 multiply-add (two lanes per instruction).
+__device__ __forceinline__ float2 fma2(float a0, float a1, float b0, float b1, float2 c) {
+  uint64_t a, b, cc, d;
+  asm("mov.b64 %0, {%1, %2};" : "=l"(a) : "f"(a0), "f"(a1));
+  asm("mov.b64 %0, {%1, %2};" : "=l"(b) : "f"(b0), "f"(b1));
+  asm("mov.b64 %0, {%1, %2};" : "=l"(cc) : "f"(c.x), "f"(c.y));
+  asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(d) : "l"(a), "l"(b), "l"(cc));
+  float2 r;
+  asm("mov.b64 {%0, %1}, %2;" : "=f"(r.x), "=f"(r.y) : "l"(d));
+  return r;
+}
+// dot of 8 bf16 weights with 8 fp32 activations, even elements into acc.x and odd ones into acc.y.
+__device__ __forceinline__ float2 dot8_f32x2(const uint4 &w, const float4 &xa, const float4 &xb, float2 acc) {
+  acc = fma2(bf16x2_lo(w.x), bf16x2_hi(w.x), xa.x, xa.y, acc);
+  acc = fma2(bf16x2_lo(w.y), bf16x2_hi(w.y), xa.z, xa.w, acc);
+  acc = fma2(bf16x2_lo(w.z), bf16x2_hi(w.z), xb.x, xb.y, acc);
+  acc = fma2(bf16x2_lo(w.w), bf16x2_hi(w.w), xb.z, xb.w, acc);
+  return acc;
+}
+
 // dot of 8 bf16 weights with 8 fp32 activations (the sparse-MoE path of the
 // reference feeds unrounded activations to its mat-vec).
 __device__ __forceinline__ float dot8_f32(const uint4 &w, const float4 &xa, const float4 &xb, float acc) {
@@ -246,6 +273,10 @@ __device__ __forceinline__ float dot_piece(const uint8_t *wp, const uint8_t *xp,
   if (XF32) return dot8_f32(lds128(wp + off), xa[off / 16u], xb[off / 16u], acc);
   return dot8(lds128(wp + off), lds128(xp + off), acc);
 }
+__device__ __forceinline__ float2 dot_piece_x2(const uint8_t *wp, const float4 *xa, const float4 *xb, uint32_t off,
+                                               float2 acc) {
+  return dot8_f32x2(lds128(wp + off), xa[off / 16u], xb[off / 16u], acc);
+}
 
 // Consumes job `index` (jobs are consumed in order, each exactly once, by every
 // warp of the block).  `x` is the bf16 activation vector in shared memory;
@@ -268,8 +299,8 @@ __device__ __forceinline__ void stream_consume(RowStream &rs, StreamShared &sh, 
   uint32_t edges = 0;
   bool row_from_start = job.begin % job.row_bytes == 0;  // this warp has seen the current row from byte 0
   while (cur.pos < job.end) {
-    uint32_t pos, row_end;
-    const uint32_t len = cursor_next(job, cur, &pos, &row_end);
+    uint32_t pos, row_end, row;
+    const uint32_t len = cursor_next(job, cur, &pos, &row_end, &row);
     stream_fill(rs);
     const uint32_t slot = rs.consumed % kStreamSlots;
     const uint32_t parity = (rs.consumed / kStreamSlots) & 1u;
@@ -286,33 +317,38 @@ __device__ __forceinline__ void stream_consume(RowStream &rs, StreamShared &sh, 
       // planes A and B of the fp32 vector (xf32_index), at this lane's first piece of the chunk
       const float4 *xa = reinterpret_cast<const float4 *>(x) + row_offset / 16u + lane;
       const float4 *xb = xa + job.row_bytes / 16u;
+      // packed multiply-adds: every accumulator splits into an even and an odd half for the chunk
+      float2 a2[4] = {make_float2(acc[0], 0.0f), make_float2(acc[1], 0.0f), make_float2(acc[2], 0.0f),
+                      make_float2(acc[3], 0.0f)};
       uint32_t off = 0;
       if (len == kChunkBytes) {
 #pragma unroll
         for (uint32_t i = 0; i < kChunkBytes / kSweepBytes; i += 4) {
-          acc[0] = dot_piece<true>(wp, xp, xa, xb, (i + 0) * kSweepBytes, acc[0]);
-          acc[1] = dot_piece<true>(wp, xp, xa, xb, (i + 1) * kSweepBytes, acc[1]);
-          acc[2] = dot_piece<true>(wp, xp, xa, xb, (i + 2) * kSweepBytes, acc[2]);
-          acc[3] = dot_piece<true>(wp, xp, xa, xb, (i + 3) * kSweepBytes, acc[3]);
+          a2[0] = dot_piece_x2(wp, xa, xb, (i + 0) * kSweepBytes, a2[0]);
+          a2[1] = dot_piece_x2(wp, xa, xb, (i + 1) * kSweepBytes, a2[1]);
+          a2[2] = dot_piece_x2(wp, xa, xb, (i + 2) * kSweepBytes, a2[2]);
+          a2[3] = dot_piece_x2(wp, xa, xb, (i + 3) * kSweepBytes, a2[3]);
         }
         off = kChunkBytes;
       } else if (len == kChunkBytes / 2u) {
 #pragma unroll
         for (uint32_t i = 0; i < kChunkBytes / kSweepBytes / 2u; i += 4) {
-          acc[0] = dot_piece<true>(wp, xp, xa, xb, (i + 0) * kSweepBytes, acc[0]);
-          acc[1] = dot_piece<true>(wp, xp, xa, xb, (i + 1) * kSweepBytes, acc[1]);
-          acc[2] = dot_piece<true>(wp, xp, xa, xb, (i + 2) * kSweepBytes, acc[2]);
-          acc[3] = dot_piece<true>(wp, xp, xa, xb, (i + 3) * kSweepBytes, acc[3]);
+          a2[0] = dot_piece_x2(wp, xa, xb, (i + 0) * kSweepBytes, a2[0]);
+          a2[1] = dot_piece_x2(wp, xa, xb, (i + 1) * kSweepBytes, a2[1]);
+          a2[2] = dot_piece_x2(wp, xa, xb, (i + 2) * kSweepBytes, a2[2]);
+          a2[3] = dot_piece_x2(wp, xa, xb, (i + 3) * kSweepBytes, a2[3]);
         }
         off = kChunkBytes / 2u;
       }
       for (; off + 4u * kSweepBytes <= len; off += 4u * kSweepBytes) {
-        acc[0] = dot_piece<true>(wp, xp, xa, xb, off, acc[0]);
-        acc[1] = dot_piece<true>(wp, xp, xa, xb, off + kSweepBytes, acc[1]);
-        acc[2] = dot_piece<true>(wp, xp, xa, xb, off + 2u * kSweepBytes, acc[2]);
-        acc[3] = dot_piece<true>(wp, xp, xa, xb, off + 3u * kSweepBytes, acc[3]);
+        a2[0] = dot_piece_x2(wp, xa, xb, off, a2[0]);
+        a2[1] = dot_piece_x2(wp, xa, xb, off + kSweepBytes, a2[1]);
+        a2[2] = dot_piece_x2(wp, xa, xb, off + 2u * kSweepBytes, a2[2]);
+        a2[3] = dot_piece_x2(wp, xa, xb, off + 3u * kSweepBytes, a2[3]);
       }
-      for (; off + lane * 16u < len; off += kSweepBytes) acc[0] = dot_piece<true>(wp, xp, xa, xb, off, acc[0]);
+      for (; off + lane * 16u < len; off += kSweepBytes) a2[0] = dot_piece_x2(wp, xa, xb, off, a2[0]);
+#pragma unroll
+      for (uint32_t i = 0; i < 4; ++i) acc[i] = a2[i].x + a2[i].y;
     } else if (len == kChunkBytes) {
 #pragma unroll
       for (uint32_t i = 0; i < kChunkBytes / kSweepBytes; i += 4) {
@@ -346,7 +382,6 @@ __device__ __forceinline__ void stream_consume(RowStream &rs, StreamShared &sh, 
     const bool range_done = pos + len == job.end;
     if (row_done || range_done) {
       const float total = warp_sum((acc[0] + acc[1]) + (acc[2] + acc[3]));
-      const uint32_t row = (row_end - job.row_bytes) / job.row_bytes;
       if (lane == 0) {
         if (row_done && row_from_start) {
           row_total[row] = total;
