@@ -747,8 +747,8 @@ def run_deepseek_workload(args, rank: int = 0, world: int = 1) -> None:
         "token_hash": f"{timed.observed_token_hash:016x}",
         "profile_us_per_token": profile_us,
         "profile_note": "event-per-launch pass outside the graph: qkv = first projection, attention = the three "
-                        "latent-attention kernels, o = output projection, gate_up = dense gate/up or router + "
-                        "routing, down = dense down or the two expert-stream kernels",
+                        "latent-attention kernels, o = output projection, gate_up = dense gate/up, down = dense down "
+                        "or the two expert-stream kernels (routing + gate/up, down)",
         "setup_s": {"generate_weights": t1 - t0, "session_create": t2 - t1, "prefill": t3 - t2},
     }), flush=True)
     session.destroy()

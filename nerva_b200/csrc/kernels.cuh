@@ -275,12 +275,6 @@ uint32_t mla_attention_splits(uint32_t target_context);
 cudaError_t launch_mla_attention(cudaStream_t stream, const MlaParams &p, uint32_t splits, bool pdl);
 
 // ---- softmax top-k sparse MoE MLP (moe.cu) ----
-struct MoeRouteParams {
-  const float *logits;   // [num_experts] router logits of this token
-  uint32_t num_experts, top_k, norm_topk_prob;
-  uint32_t *expert_ids;  // [top_k]
-  float *weights;        // [top_k]
-};
 struct MoeExpertParams {
   // residual add + RMSNorm prologue (as ProjectionParams), fp32 result
   const float *add_a, *add_b;
@@ -294,8 +288,14 @@ struct MoeExpertParams {
   const uint16_t *w_expert_down;     // [E][hidden][moe_intermediate]
   const uint16_t *w_shared_gate, *w_shared_up, *w_shared_down;  // shared expert, optional
   const uint16_t *w_shared_router;   // its gate sigmoid(router . x); null: always on (scale 1)
-  const uint32_t *expert_ids;        // [top_k] from the route kernel
-  const float *route_weights;        // [top_k]
+  // Routing happens inside the gate/up launch: router logits W_router . x for all experts, softmax,
+  // top-k, optional renormalisation; block 0 stores the new residual stream (resid_out, optional)
+  // and the result, which the down launch reads.
+  const uint16_t *w_router;          // [num_experts][hidden]
+  uint32_t num_experts, norm_topk_prob;
+  float *resid_out;
+  uint32_t *expert_ids;              // [top_k] scratch: the routing result
+  float *route_weights;              // [top_k]
   float *gate_up_out;                // scratch: per expert gate then up rows (+ the shared expert's), fp32
   float *shared_gate;                // scratch: 1 float
   float *out_f32;                    // [hidden] the MLP output
@@ -315,14 +315,7 @@ struct MoeExpertParams {
 bool moe_supported(uint32_t hidden, uint32_t moe_intermediate, uint32_t shared_intermediate,
                    uint32_t num_experts, uint32_t top_k, uint32_t sm_count);
 cudaError_t configure_moe_kernels();
-// Router logits with fp32 activations; uses the residual/norm fields, weight, rows, cols, out_f32 of p.
-cudaError_t launch_router_logits_f32(cudaStream_t stream, const ProjectionParams &p, uint32_t sm_count);
-cudaError_t launch_moe_route(cudaStream_t stream, const MoeRouteParams &p, bool pdl);
-// Both in one launch (route.logits must be p.out_f32, route.num_experts == p.rows); `ticket`: one
-// device counter, zero between launches.
-cudaError_t launch_moe_router_route(cudaStream_t stream, const ProjectionParams &p, const MoeRouteParams &route,
-                                    uint32_t *ticket, uint32_t sm_count);
-// Two launches: gate/up of the chosen experts, then SwiGLU + down and the weighted sum.
+// Two launches: routing + gate/up of the chosen experts, then SwiGLU + down and the weighted sum.
 cudaError_t launch_moe_experts(cudaStream_t stream, const MoeExpertParams &p, uint32_t sm_count, bool pdl);
 
 // ---- greedy sampling ----

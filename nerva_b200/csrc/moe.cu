@@ -1,12 +1,11 @@
 // Softmax top-k sparse MoE MLP of the resident decode step (Qwen3-MoE / Mixtral
 // style).  The reference runs the whole MLP of a layer in ONE thread block
-// (run_sparse_moe_mlp, hf_decode_sequence/device_ops.cuh:183-315); here it is
-//   moe_router_logits_kernel  residual add + RMSNorm + router mat-vec (small matrix)
-//   moe_route_kernel    softmax over the router logits, top-k by (weight
-//                       descending, index ascending), optional renormalisation
-//   moe_expert_kernel<kGateUp>  gate and up projections of the k chosen experts
-//                       (+ the shared expert) as ONE weight stream over a job list
-//                       built on the device from the routing result
+// (run_sparse_moe_mlp, hf_decode_sequence/device_ops.cuh:183-315); here it is two launches:
+//   moe_expert_kernel<kGateUp>  residual add + RMSNorm, the router mat-vec, softmax over the
+//                       router logits and top-k by (weight descending, index ascending) with
+//                       optional renormalisation — by every block for itself —, then the gate
+//                       and up projections of the k chosen experts (+ the shared expert) as
+//                       ONE weight stream over a job list built from the routing result
 //   moe_expert_kernel<kDown>    SwiGLU + down projections of the same experts,
 //                       summed with the routing weights in rank order
 // Arithmetic follows the reference kernel: the mat-vecs read the UNROUNDED fp32
@@ -41,35 +40,39 @@ __device__ __forceinline__ bool route_precedes(float w, uint32_t e, float best_w
   return w > best_w || (w == best_w && e < best_e);
 }
 
-// One block.  weights = softmax(logits) with the reference's guards (divide only
-// by a finite positive total); the k winners by (weight desc, index asc).
-__device__ __forceinline__ void moe_route_block(const MoeRouteParams &p) {
+// One block of THREADS threads, all of which call.  `logit` is the router logit of expert
+// threadIdx.x (anything for threads beyond num_experts).  weights = softmax(logits) with the
+// reference's guards (divide only by a finite positive total); the k winners by (weight desc,
+// index asc) go to ids_out / weights_out (shared or global memory), written by thread 0.
+template <uint32_t THREADS>
+__device__ __forceinline__ void moe_route_block(float logit, uint32_t num_experts, uint32_t top_k, uint32_t norm_topk_prob,
+                                                uint32_t *ids_out, float *weights_out) {
   __shared__ float w_sh[256];
   __shared__ float scratch[40];
-  __shared__ float red_w[kRouteThreads / 32];
-  __shared__ uint32_t red_e[kRouteThreads / 32];
+  __shared__ float red_w[THREADS / 32];
+  __shared__ uint32_t red_e[THREADS / 32];
   __shared__ uint32_t chosen[kMoeMaxTopK];
   __shared__ float chosen_w[kMoeMaxTopK];
   const uint32_t e = threadIdx.x;
-  const float logit = e < p.num_experts ? __ldcg(p.logits + e) : -INFINITY;
+  if (e >= num_experts) logit = -INFINITY;
   // maximum
   float m = logit;
   m = warp_max(m);
   if ((threadIdx.x & 31u) == 0) red_w[threadIdx.x >> 5] = m;
   __syncthreads();
   m = -INFINITY;
-  for (uint32_t i = 0; i < kRouteThreads / 32; ++i) m = fmaxf(m, red_w[i]);
+  for (uint32_t i = 0; i < THREADS / 32; ++i) m = fmaxf(m, red_w[i]);
   __syncthreads();
-  const float ex = e < p.num_experts ? expf(logit - m) : 0.0f;
+  const float ex = e < num_experts ? expf(logit - m) : 0.0f;
   const float total = block_sum(ex, scratch);
   float w = ex;
   if (total > 0.0f && isfinite(total)) w = ex / total;
-  w_sh[e] = e < p.num_experts ? w : -INFINITY;
+  if (e < 256u) w_sh[e] = e < num_experts ? w : -INFINITY;
   __syncthreads();
-  for (uint32_t rank = 0; rank < p.top_k; ++rank) {
+  for (uint32_t rank = 0; rank < top_k; ++rank) {
     float bw = -INFINITY;
     uint32_t be = 0xffffffffu;
-    if (e < p.num_experts) {
+    if (e < num_experts) {
       bool taken = false;
       for (uint32_t prev = 0; prev < rank; ++prev) taken = taken || chosen[prev] == e;
       if (!taken) {
@@ -93,7 +96,7 @@ __device__ __forceinline__ void moe_route_block(const MoeRouteParams &p) {
     if (threadIdx.x == 0) {
       bw = -INFINITY;
       be = 0xffffffffu;
-      for (uint32_t i = 0; i < kRouteThreads / 32; ++i) {
+      for (uint32_t i = 0; i < THREADS / 32; ++i) {
         if (red_e[i] != 0xffffffffu && (be == 0xffffffffu || route_precedes(red_w[i], red_e[i], bw, be))) {
           bw = red_w[i];
           be = red_e[i];
@@ -106,19 +109,15 @@ __device__ __forceinline__ void moe_route_block(const MoeRouteParams &p) {
   }
   if (threadIdx.x == 0) {
     float sum = 0.0f;
-    for (uint32_t rank = 0; rank < p.top_k; ++rank) sum += chosen_w[rank];
-    for (uint32_t rank = 0; rank < p.top_k; ++rank) {
+    for (uint32_t rank = 0; rank < top_k; ++rank) sum += chosen_w[rank];
+    for (uint32_t rank = 0; rank < top_k; ++rank) {
       float out = chosen_w[rank];
-      if (p.norm_topk_prob != 0 && sum > 0.0f) out /= sum;
-      p.expert_ids[rank] = chosen[rank] == 0xffffffffu ? 0u : chosen[rank];
-      p.weights[rank] = out;
+      if (norm_topk_prob != 0 && sum > 0.0f) out /= sum;
+      ids_out[rank] = chosen[rank] == 0xffffffffu ? 0u : chosen[rank];
+      weights_out[rank] = out;
     }
   }
-}
-__global__ void __launch_bounds__(kRouteThreads) moe_route_kernel(MoeRouteParams p) {
-  pdl_trigger();
-  pdl_wait();
-  moe_route_block(p);
+  __syncthreads();
 }
 
 // ---- expert projections ----
@@ -134,6 +133,9 @@ struct MoeShared {
   uint32_t ids[kMoeMaxTopK];       // the chosen experts held by this rank, as local indices, in routing order
   float weights[kMoeMaxTopK + 1];  // their routing weights; [routed] = the shared expert's gate
   uint32_t routed;                 // how many of the top_k experts are held here
+  uint32_t route_ids[kMoeMaxTopK]; // kGateUp: the routing result of this block's own routing
+  float route_weights[kMoeMaxTopK];
+  float logits[256];               // kGateUp: router logits
   uint32_t pieces;
   uint32_t ticket;
 };
@@ -159,81 +161,6 @@ __device__ void add_norm_to_smem_f32(float *x, const float *a, const float *b, c
     x[at] = x[at] * scale * bf16_bits_to_f32(w[i]);
   }
   __syncthreads();
-}
-
-// Router logits: logits[e] = W_router[e] . x with x the unrounded fp32 normalised hidden state
-// (residual add + RMSNorm in front, block 0 stores the new residual).  The matrix is small
-// (experts x hidden), so plain 16-byte loads, one warp per row.
-__global__ void __launch_bounds__(256) moe_router_logits_kernel(ProjectionParams p) {
-  extern __shared__ __align__(16) float xr[];  // [cols]
-  __shared__ float scratch[40];
-  pdl_trigger();
-  pdl_wait();
-  if (blockIdx.x == 0 && p.resid_out != nullptr) {
-    for (uint32_t i = threadIdx.x; i < p.cols; i += blockDim.x) {
-      float r = p.add_b != nullptr ? __ldcg(p.add_b + i) : __ldcg(p.add_a + i);
-      if (p.add_bias != nullptr) r += bf16_bits_to_f32(p.add_bias[i]);
-      if (p.add_b != nullptr) r += __ldcg(p.add_a + i);
-      p.resid_out[i] = r;
-    }
-  }
-  add_norm_to_smem_f32<false>(xr, p.add_a, p.add_b, p.add_bias, p.norm_weight, p.eps, p.cols, scratch);
-  const uint32_t lane = threadIdx.x & 31u, warp = threadIdx.x >> 5, warps = blockDim.x >> 5;
-  for (uint32_t row = blockIdx.x * warps + warp; row < p.rows; row += gridDim.x * warps) {
-    const uint4 *w = reinterpret_cast<const uint4 *>(p.weight + static_cast<uint64_t>(row) * p.cols);
-    float acc = 0.0f;
-    for (uint32_t i = lane; i < p.cols / 8u; i += 32u) {
-      const uint4 wv = w[i];
-      const float4 xa = *reinterpret_cast<const float4 *>(xr + 8u * i);
-      const float4 xb = *reinterpret_cast<const float4 *>(xr + 8u * i + 4u);
-      acc = dot8_f32(wv, xa, xb, acc);
-    }
-    acc = warp_sum(acc);
-    if (lane == 0) p.out_f32[row] = acc;
-  }
-}
-
-// Router logits and routing in one launch: block e computes logit e (every block normalises the
-// hidden state for itself; the eight warps split the row), and the block that draws the last
-// ticket — it sees every logit — runs the routing.  Block 0 stores the new residual.
-__global__ void __launch_bounds__(kRouteThreads) moe_router_route_kernel(ProjectionParams p, MoeRouteParams route,
-                                                                          uint32_t *ticket) {
-  extern __shared__ __align__(16) float xr[];  // [cols]
-  __shared__ float scratch[40];
-  __shared__ uint32_t drawn_sh;
-  pdl_trigger();
-  pdl_wait();
-  if (blockIdx.x == 0 && p.resid_out != nullptr) {
-    for (uint32_t i = threadIdx.x; i < p.cols; i += blockDim.x) {
-      float r = p.add_b != nullptr ? __ldcg(p.add_b + i) : __ldcg(p.add_a + i);
-      if (p.add_bias != nullptr) r += bf16_bits_to_f32(p.add_bias[i]);
-      if (p.add_b != nullptr) r += __ldcg(p.add_a + i);
-      p.resid_out[i] = r;
-    }
-  }
-  add_norm_to_smem_f32<false>(xr, p.add_a, p.add_b, p.add_bias, p.norm_weight, p.eps, p.cols, scratch);
-  for (uint32_t row = blockIdx.x; row < p.rows; row += gridDim.x) {
-    const uint4 *w = reinterpret_cast<const uint4 *>(p.weight + static_cast<uint64_t>(row) * p.cols);
-    float acc = 0.0f;
-    for (uint32_t i = threadIdx.x; i < p.cols / 8u; i += blockDim.x) {
-      const uint4 wv = w[i];
-      const float4 xa = *reinterpret_cast<const float4 *>(xr + 8u * i);
-      const float4 xb = *reinterpret_cast<const float4 *>(xr + 8u * i + 4u);
-      acc = dot8_f32(wv, xa, xb, 0.0f) + acc;
-    }
-    const float total = block_sum(acc, scratch);
-    if (threadIdx.x == 0) p.out_f32[row] = total;
-  }
-  __syncthreads();
-  if (threadIdx.x == 0) {
-    uint32_t drawn;
-    asm volatile("atom.acq_rel.gpu.global.add.u32 %0, [%1], 1;" : "=r"(drawn) : "l"(ticket) : "memory");
-    drawn_sh = drawn;
-  }
-  __syncthreads();
-  if (drawn_sh != gridDim.x - 1u) return;
-  moe_route_block(route);
-  if (threadIdx.x == 0) *ticket = 0;  // ready for the next launch
 }
 
 // Matrix `g` of a phase.  kGateUp: gate then up matrix of every chosen expert held here (routing
@@ -290,16 +217,52 @@ __global__ void __launch_bounds__(kStreamThreads, 1) moe_expert_kernel(MoeExpert
   float *row_total = reinterpret_cast<float *>(smem + kRingBytes + round128u(x_elems * 4u) +
                                                round128u(sizeof(MoeShared)));
   pdl_trigger();
-  // The list depends on the routing result of this step.
+  // Everything depends on the previous kernel: the hidden state, and through it the routing.
   pdl_wait();
+  const uint32_t *route_ids = p.expert_ids;
+  const float *route_weights = p.route_weights;
+  if (PHASE == kGateUp) {
+    // Routing.  Every block normalises the hidden state for itself (it needs it for its rows
+    // anyway), computes all router logits from it (one warp per expert row; the matrix is small and
+    // comes from L2 after the first block has read it) and routes: the same arithmetic in the same
+    // order in every block, so all blocks agree.  Block 0 stores the new residual and the routing
+    // result for the down launch.
+    if (blockIdx.x == 0 && p.resid_out != nullptr) {
+      for (uint32_t i = threadIdx.x; i < p.hidden; i += blockDim.x) {
+        float r = p.add_b != nullptr ? __ldcg(p.add_b + i) : __ldcg(p.add_a + i);
+        if (p.add_bias != nullptr) r += bf16_bits_to_f32(p.add_bias[i]);
+        if (p.add_b != nullptr) r += __ldcg(p.add_a + i);
+        p.resid_out[i] = r;
+      }
+    }
+    add_norm_to_smem_f32<true>(x, p.add_a, p.add_b, p.add_bias, p.norm_weight, p.eps, p.hidden, sh.scratch);
+    const uint32_t lane = threadIdx.x & 31u, warp = threadIdx.x >> 5;
+    const float4 *xa = reinterpret_cast<const float4 *>(x), *xb = xa + p.hidden / 8u;
+    for (uint32_t row = warp; row < p.num_experts; row += kStreamWarps) {
+      const uint4 *w = reinterpret_cast<const uint4 *>(p.w_router + static_cast<uint64_t>(row) * p.hidden);
+      float acc = 0.0f;
+      for (uint32_t i = lane; i < p.hidden / 8u; i += 32u) acc = dot8_f32(__ldg(w + i), xa[i], xb[i], acc);
+      acc = warp_sum(acc);
+      if (lane == 0) sh.logits[row] = acc;
+    }
+    __syncthreads();
+    moe_route_block<kStreamThreads>(sh.logits[threadIdx.x < 256u ? threadIdx.x : 0u], p.num_experts, p.top_k,
+                                    p.norm_topk_prob, sh.route_ids, sh.route_weights);
+    route_ids = sh.route_ids;
+    route_weights = sh.route_weights;
+    if (blockIdx.x == 0 && threadIdx.x < p.top_k) {
+      p.expert_ids[threadIdx.x] = sh.route_ids[threadIdx.x];
+      p.route_weights[threadIdx.x] = sh.route_weights[threadIdx.x];
+    }
+  }
   if (threadIdx.x == 0) {
     // routing order is kept; under expert parallel only the experts held here stay in the list
     uint32_t routed = 0;
     for (uint32_t r = 0; r < p.top_k; ++r) {
-      const uint32_t local = p.expert_ids[r] - p.expert_base;  // wraps to a large value below the base
+      const uint32_t local = route_ids[r] - p.expert_base;  // wraps to a large value below the base
       if (p.expert_local == 0 || local < p.expert_local) {
         sh.ids[routed] = local;
-        sh.weights[routed] = p.route_weights[r];
+        sh.weights[routed] = route_weights[r];
         routed += 1;
       }
     }
@@ -355,7 +318,6 @@ __global__ void __launch_bounds__(kStreamThreads, 1) moe_expert_kernel(MoeExpert
   for (uint32_t i = threadIdx.x; i < p.max_rows_per_block; i += blockDim.x) row_total[i] = 0.0f;
 
   if (PHASE == kGateUp) {
-    add_norm_to_smem_f32<true>(x, p.add_a, p.add_b, p.add_bias, p.norm_weight, p.eps, p.hidden, sh.scratch);
     if (blockIdx.x == 0 && p.shared_intermediate != 0) {
       // gate of the shared expert: sigmoid(shared_router . x), or 1 for shared experts that are always on
       float dot = 0.0f;
@@ -470,7 +432,6 @@ bool moe_supported(uint32_t hidden, uint32_t moe_intermediate, uint32_t shared_i
                    uint32_t num_experts, uint32_t top_k, uint32_t sm_count) {
   if (num_experts == 0 || num_experts > 256 || top_k == 0 || top_k > kMoeMaxTopK || top_k > num_experts) return false;
   if (hidden % 8u != 0 || moe_intermediate % 8u != 0 || shared_intermediate % 8u != 0) return false;
-  if (hidden * 4u > 48u * 1024u) return false;  // the router kernel keeps the fp32 hidden state in 48 KB
   MoeExpertParams p{};
   p.hidden = hidden;
   p.moe_intermediate = moe_intermediate;
@@ -478,38 +439,25 @@ bool moe_supported(uint32_t hidden, uint32_t moe_intermediate, uint32_t shared_i
   p.max_intermediate = moe_intermediate > shared_intermediate ? moe_intermediate : shared_intermediate;
   p.top_k = top_k;
   p.max_rows_per_block = moe_max_rows(p, moe_blocks(p, sm_count));
-  return moe_smem_bytes(p) <= 227u * 1024u;
+  return moe_smem_bytes(p) <= 227u * 1024u - 2048u;
 }
+
+// Dynamic shared memory a block may ask for: the 227 KB of an SM less the kernels' static arrays
+// (the routing scratch).
+constexpr uint32_t kMoeStaticSmemAllowance = 2048;
+constexpr uint32_t kMoeMaxDynamicSmem = 227u * 1024u - kMoeStaticSmemAllowance;
 
 cudaError_t configure_moe_kernels() {
-  cudaError_t err = cudaFuncSetAttribute(moe_expert_kernel<kGateUp>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                         227 * 1024);
+  cudaFuncAttributes attr{};
+  cudaError_t err = cudaFuncGetAttributes(&attr, moe_expert_kernel<kGateUp>);
+  if (err == cudaSuccess && attr.sharedSizeBytes > kMoeStaticSmemAllowance) err = cudaErrorInvalidConfiguration;
   if (err == cudaSuccess)
-    err = cudaFuncSetAttribute(moe_expert_kernel<kDown>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
+    err = cudaFuncSetAttribute(moe_expert_kernel<kGateUp>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                               kMoeMaxDynamicSmem);
+  if (err == cudaSuccess)
+    err = cudaFuncSetAttribute(moe_expert_kernel<kDown>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                               kMoeMaxDynamicSmem);
   return err;
-}
-
-cudaError_t launch_router_logits_f32(cudaStream_t stream, const ProjectionParams &p, uint32_t sm_count) {
-  if (p.cols % 8u != 0 || p.cols * 4u > 48u * 1024u || p.rows == 0) return cudaErrorNotSupported;
-  uint32_t blocks = (p.rows + 7u) / 8u;
-  if (blocks > sm_count) blocks = sm_count;
-  return launch_with_pdl(moe_router_logits_kernel, dim3(blocks), dim3(256), p.cols * 4u, stream, p.pdl != 0, p);
-}
-
-cudaError_t launch_moe_router_route(cudaStream_t stream, const ProjectionParams &p, const MoeRouteParams &route,
-                                    uint32_t *ticket, uint32_t sm_count) {
-  if (p.cols % 8u != 0 || p.cols * 4u > 48u * 1024u || p.rows == 0 || ticket == nullptr) return cudaErrorNotSupported;
-  if (route.num_experts == 0 || route.num_experts > 256 || route.top_k == 0 || route.top_k > kMoeMaxTopK ||
-      route.num_experts != p.rows)
-    return cudaErrorInvalidValue;
-  const uint32_t blocks = p.rows < sm_count ? p.rows : sm_count;
-  return launch_with_pdl(moe_router_route_kernel, dim3(blocks), dim3(kRouteThreads), p.cols * 4u, stream, p.pdl != 0,
-                         p, route, ticket);
-}
-
-cudaError_t launch_moe_route(cudaStream_t stream, const MoeRouteParams &p, bool pdl) {
-  if (p.num_experts == 0 || p.num_experts > 256 || p.top_k == 0 || p.top_k > kMoeMaxTopK) return cudaErrorInvalidValue;
-  return launch_with_pdl(moe_route_kernel, dim3(1), dim3(kRouteThreads), 0, stream, pdl, p);
 }
 
 cudaError_t launch_moe_experts(cudaStream_t stream, const MoeExpertParams &params, uint32_t sm_count, bool pdl) {
@@ -518,7 +466,9 @@ cudaError_t launch_moe_experts(cudaStream_t stream, const MoeExpertParams &param
   const uint32_t blocks = moe_blocks(p, sm_count);
   p.max_rows_per_block = moe_max_rows(p, blocks);
   const uint32_t smem = moe_smem_bytes(p);
-  if (smem > 227u * 1024u || p.partial == nullptr || p.ticket == nullptr) return cudaErrorNotSupported;
+  if (smem > kMoeMaxDynamicSmem || p.partial == nullptr || p.ticket == nullptr || p.w_router == nullptr ||
+      p.num_experts == 0 || p.num_experts > 256 || p.top_k == 0 || p.top_k > kMoeMaxTopK || p.hidden % 8u != 0)
+    return cudaErrorNotSupported;
   cudaError_t err = launch_with_pdl(moe_expert_kernel<kGateUp>, dim3(blocks), dim3(kStreamThreads), smem, stream,
                                     pdl, p);
   if (err != cudaSuccess) return err;

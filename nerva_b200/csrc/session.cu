@@ -766,35 +766,6 @@ cudaError_t enqueue_step(Session *s, uint32_t splits, uint32_t sample, uint64_t 
     if (err != cudaSuccess) break;
 
     if (L.mlp_kind == NERVA_MLP_KIND_SPARSE_MOE) {
-      // router logits (residual add + RMSNorm in front; block 0 stores the new residual)
-      p = ProjectionParams{};
-      p.error_word = s->device_error;
-      p.pdl = s->use_pdl ? 1u : 0u;
-      p.eps = s->rms_eps;
-      p.weight = arena_at(s, L.w_router);
-      p.rows = L.num_experts;
-      p.cols = d.hidden;
-      p.prologue = kPrologueAddNorm;
-      p.x_bf16 = s->x_scratch;
-      p.add_a = s->h_a;
-      p.add_b = s->o_out;
-      p.add_bias = arena_at(s, L.o_bias);
-      p.norm_weight = arena_at(s, L.rms_mlp);
-      p.resid_out = s->h_b;
-      p.epilogue = kEpilogueStore;
-      p.out_f32 = s->router_logits;
-      MoeRouteParams rp{};
-      rp.logits = s->router_logits;
-      rp.num_experts = L.num_experts;
-      rp.top_k = L.top_k;
-      rp.norm_topk_prob = L.norm_topk_prob;
-      rp.expert_ids = s->route_ids;
-      rp.weights = s->route_weights;
-      // logits and routing in one launch (word 1 of the counter block is this launch's ticket)
-      err = launch_moe_router_route(s->stream, p, rp, s->moe_ticket + 1, s->sm_count);
-      n += 1;
-      profile_mark(s, prof, kBucketGateUp);
-      if (err != cudaSuccess) break;
       MoeExpertParams ep{};
       ep.add_a = s->h_a;
       ep.add_b = s->o_out;
@@ -813,6 +784,10 @@ cudaError_t enqueue_step(Session *s, uint32_t splits, uint32_t sample, uint64_t 
       ep.w_shared_up = arena_at(s, L.w_shared_up);
       ep.w_shared_down = arena_at(s, L.w_shared_down);
       ep.w_shared_router = arena_at(s, L.w_shared_router);
+      ep.w_router = arena_at(s, L.w_router);
+      ep.num_experts = L.num_experts;
+      ep.norm_topk_prob = L.norm_topk_prob;
+      ep.resid_out = s->h_b;
       ep.expert_ids = s->route_ids;
       ep.route_weights = s->route_weights;
       ep.gate_up_out = s->moe_gate_up;
@@ -824,6 +799,7 @@ cudaError_t enqueue_step(Session *s, uint32_t splits, uint32_t sample, uint64_t 
       ep.expert_base = L.expert_base;
       ep.expert_local = L.expert_local;
       if (ep_on) ep.push = push_to(ep_buffer(l), l + 1u);
+      // routing + gate/up, then down: two launches
       err = launch_moe_experts(s->stream, ep, s->sm_count, s->use_pdl);
       n += 2;
       profile_mark(s, prof, kBucketDown);
