@@ -30,6 +30,7 @@
 
 #include "common.cuh"
 #include "kernels.cuh"
+#include "mma_bf16.cuh"
 
 namespace nb {
 namespace {
@@ -67,29 +68,6 @@ __device__ __forceinline__ void tma_load_box(void *dst, const CUtensorMap *map, 
           "r"(smem_addr(dst)),
       "l"(map), "r"(x), "r"(y), "r"(smem_addr(bar))
       : "memory");
-}
-__device__ __forceinline__ void ldmatrix_x4(uint32_t (&r)[4], uint32_t addr) {
-  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0, %1, %2, %3}, [%4];"
-               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
-               : "r"(addr));
-}
-__device__ __forceinline__ void ldmatrix_x4_trans(uint32_t (&r)[4], uint32_t addr) {
-  asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0, %1, %2, %3}, [%4];"
-               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
-               : "r"(addr));
-}
-__device__ __forceinline__ void mma_bf16(float (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
-  asm volatile(
-      "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, {%0, %1, %2, %3};"
-      : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
-      : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
-}
-// Two fp32 values -> one register of two bf16 roundings (low half first), and what the rounding lost.
-__device__ __forceinline__ uint32_t pack_bf16_hi(float x, float y) {
-  return static_cast<uint32_t>(f32_to_bf16_bits(x)) | (static_cast<uint32_t>(f32_to_bf16_bits(y)) << 16);
-}
-__device__ __forceinline__ uint32_t pack_bf16_lo(float x, float y) {
-  return pack_bf16_hi(x - bf16_round(x), y - bf16_round(y));
 }
 // Byte offset of 16-byte piece `piece` of row `row` inside a 128-byte-swizzled 16 x 128 B box.
 __device__ __forceinline__ uint32_t swizzled(uint32_t row, uint32_t piece) {

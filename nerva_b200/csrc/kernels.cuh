@@ -273,6 +273,7 @@ bool mla_session_supported(uint32_t heads, uint32_t rank, uint32_t nope, uint32_
 uint32_t mla_attention_splits(uint32_t target_context);
 // Three launches: prepare (rotary, absorbed queries, cache append), split attention, merge + value projection.
 cudaError_t launch_mla_attention(cudaStream_t stream, const MlaParams &p, uint32_t splits, bool pdl);
+cudaError_t configure_mla_kernels();  // once per device before the first launch
 
 // ---- softmax top-k sparse MoE MLP (moe.cu) ----
 struct MoeExpertParams {

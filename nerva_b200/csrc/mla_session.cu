@@ -18,6 +18,7 @@
 
 #include "common.cuh"
 #include "kernels.cuh"
+#include "mma_bf16.cuh"
 
 namespace nb {
 namespace {
@@ -106,17 +107,48 @@ __global__ void __launch_bounds__(256) mla_prepare_kernel(MlaParams p) {
   }
 }
 
-// Shared memory: one tile of kMlaTile cache rows, bf16, rows padded by 16 bytes.
-template <uint32_t RANK_PER_LANE>
+// Split attention over the latent cache on the tensor pipe.  The heads are the M dimension of the
+// MMA (at most 16 of them: one m16n8k16 tile), so a block of 16 warps handles all heads of its span
+// of cached rows, one tile of 32 rows at a time:
+//   scores   S[16 heads][32 rows] = Q . C^T over the rank + rope features: warp (n-tile of 8 rows,
+//            quarter of the feature range); the four quarters are added in order through shared memory
+//   softmax  warp h owns head h (one lane per row): running maximum and sum, p = exp2(s - m)
+//   values   acc[16 heads][rank] += P . C: warp w owns rank / 16 consecutive features of all heads,
+//            the C fragments come out of shared memory transposed (ldmatrix.trans)
+// Q and P are fp32 values split into a bf16 rounding and what it lost (two MMAs each), the cache
+// rows are bf16 as stored, accumulation is fp32.
+// Shared memory: tile of kMlaTile cache rows | Q roundings | Q remainders (16 rows each, the tile's
+// row stride: width * 2 + 16 bytes, which keeps fragment loads free of bank conflicts when
+// width * 2 is a multiple of 128) | score quarters | P roundings, remainders | per-head rescale.
+constexpr uint32_t kMlaHeadsTile = 16;   // MMA M
+constexpr uint32_t kMlaPStride = kMlaTile + 8u;  // bf16 elements per row of P (80 bytes: conflict-free A loads)
+
+__host__ __device__ inline uint32_t mla_row_bytes(uint32_t rank, uint32_t rope) { return (rank + rope) * 2u + 16u; }
+__host__ __device__ inline uint32_t mla_attention_smem(uint32_t rank, uint32_t rope) {
+  return (kMlaTile + 2u * kMlaHeadsTile) * mla_row_bytes(rank, rope) + 4u * kMlaHeadsTile * kMlaTile * 4u +
+         2u * kMlaHeadsTile * kMlaPStride * 2u + kMlaHeadsTile * 4u;
+}
+
+template <uint32_t NT>  // n-tiles of 8 features per warp in the value product: rank / 128
 __global__ void __launch_bounds__(512) mla_attention_kernel(MlaParams p) {
-  constexpr uint32_t RANK = RANK_PER_LANE * 32u;
-  extern __shared__ __align__(16) uint8_t tile[];
+  constexpr uint32_t RANK = NT * 128u;
+  extern __shared__ __align__(16) uint8_t smem[];
   pdl_trigger();
   pdl_wait();
   const uint32_t position = *p.cursor;
   if (position >= p.max_context) return;
-  const uint32_t lane = threadIdx.x & 31u, h = threadIdx.x >> 5;  // one warp per head
-  const uint32_t width = RANK + p.rope, row_bytes = width * 2u + 16u;
+  const uint32_t lane = threadIdx.x & 31u, warp = threadIdx.x >> 5;
+  const uint32_t g = lane >> 2, t = lane & 3u;
+  const uint32_t width = RANK + p.rope, row_bytes = mla_row_bytes(RANK, p.rope);
+  const uint32_t k_steps = (width + 15u) / 16u;
+  uint8_t *tile = smem;
+  uint8_t *q_hi = tile + kMlaTile * row_bytes;
+  uint8_t *q_lo = q_hi + kMlaHeadsTile * row_bytes;
+  float *s_part = reinterpret_cast<float *>(q_lo + kMlaHeadsTile * row_bytes);  // [4][16][32]
+  uint16_t *p_hi = reinterpret_cast<uint16_t *>(s_part + 4u * kMlaHeadsTile * kMlaTile);
+  uint16_t *p_lo = p_hi + kMlaHeadsTile * kMlaPStride;
+  float *rescale = reinterpret_cast<float *>(p_lo + kMlaHeadsTile * kMlaPStride);
+
   const uint32_t context = position + 1u;  // the new token's row was appended by the prepare kernel
   const uint32_t split = blockIdx.x, S = gridDim.x;
   const uint32_t tiles_total = (context + kMlaTile - 1u) / kMlaTile;
@@ -125,69 +157,164 @@ __global__ void __launch_bounds__(512) mla_attention_kernel(MlaParams p) {
   uint32_t tile_end = tile_begin + tiles_per_split;
   if (tile_end > tiles_total) tile_end = tiles_total;
 
-  // this head's absorbed query and rotary query, pre-multiplied by scale * log2(e)
-  const float qscale = kLog2e * rsqrtf(static_cast<float>(p.nope + p.rope));
-  float ql[RANK_PER_LANE], qr[2] = {0.0f, 0.0f};
-  if (h < p.heads) {
-#pragma unroll
-    for (uint32_t j = 0; j < RANK_PER_LANE; ++j) ql[j] = __ldcg(p.ql + static_cast<uint64_t>(h) * RANK + lane + 32u * j) * qscale;
-    const float *q_pe = p.qkv + static_cast<uint64_t>(h) * (p.nope + p.rope) + p.nope;
-    if (lane < p.rope) qr[0] = __ldcg(q_pe + lane) * qscale;
-    if (lane + 32u < p.rope) qr[1] = __ldcg(q_pe + lane + 32u) * qscale;
+  // Q[h] = [absorbed query | rotary query] * scale * log2(e), rows of absent heads and the row
+  // padding zero
+  if (tile_begin < tile_end) {
+    const float qscale = kLog2e * rsqrtf(static_cast<float>(p.nope + p.rope));
+    const uint32_t padded = row_bytes / 2u;
+    for (uint32_t i = threadIdx.x; i < kMlaHeadsTile * padded; i += blockDim.x) {
+      const uint32_t h = i / padded, k = i % padded;
+      float v = 0.0f;
+      if (h < p.heads && k < RANK) v = __ldcg(p.ql + static_cast<uint64_t>(h) * RANK + k) * qscale;
+      else if (h < p.heads && k < width)
+        v = __ldcg(p.qkv + static_cast<uint64_t>(h) * (p.nope + p.rope) + p.nope + (k - RANK)) * qscale;
+      const uint16_t hi = f32_to_bf16_bits(v);
+      reinterpret_cast<uint16_t *>(q_hi + h * row_bytes)[k] = hi;
+      reinterpret_cast<uint16_t *>(q_lo + h * row_bytes)[k] = f32_to_bf16_bits(v - bf16_bits_to_f32(hi));
+    }
   }
-  float m_run = -INFINITY, l_run = 0.0f, acc[RANK_PER_LANE];
+  // warp h keeps head h's running maximum and sum; every warp its features of all heads
+  float m_run = -INFINITY, l_run = 0.0f;
+  float acc[NT][4];
 #pragma unroll
-  for (uint32_t j = 0; j < RANK_PER_LANE; ++j) acc[j] = 0.0f;
+  for (uint32_t i = 0; i < NT; ++i) acc[i][0] = acc[i][1] = acc[i][2] = acc[i][3] = 0.0f;
 
-  for (uint32_t t = tile_begin; t < tile_end; ++t) {
-    const uint32_t token0 = t * kMlaTile;
+  for (uint32_t tl = tile_begin; tl < tile_end; ++tl) {
+    const uint32_t token0 = tl * kMlaTile;
     const uint32_t valid = context - token0 < kMlaTile ? context - token0 : kMlaTile;
     __syncthreads();  // the previous tile has been consumed
-    // copy the tile's rows (16-byte pieces; a row is `width * 2` bytes, a multiple of 16)
-    const uint32_t pieces = width / 8u;
-    for (uint32_t i = threadIdx.x; i < valid * pieces; i += blockDim.x) {
+    // the tile's rows in 16-byte pieces (a row is width * 2 bytes, a multiple of 16, then 16 bytes
+    // of padding); rows beyond the context and the padding are zero
+    const uint32_t pieces = row_bytes / 16u;
+    for (uint32_t i = threadIdx.x; i < kMlaTile * pieces; i += blockDim.x) {
       const uint32_t r = i / pieces, piece = i % pieces;
-      const uint32_t token = token0 + r;
-      uint32_t page = p.page_table[token / NERVA_KV_CACHE_BLOCK_TOKENS];
-      if (page >= p.page_count) {
-        report_error(p.error_word, kErrPageOutOfRange);
-        page = 0;
+      uint4 v = make_uint4(0u, 0u, 0u, 0u);
+      if (r < valid && piece < width / 8u) {
+        const uint32_t token = token0 + r;
+        uint32_t page = p.page_table[token / NERVA_KV_CACHE_BLOCK_TOKENS];
+        if (page >= p.page_count) {
+          report_error(p.error_word, kErrPageOutOfRange);
+          page = 0;
+        }
+        const uint16_t *src = p.cache + (static_cast<uint64_t>(page) * NERVA_KV_CACHE_BLOCK_TOKENS +
+                                         token % NERVA_KV_CACHE_BLOCK_TOKENS) * width + piece * 8u;
+        v = __ldcg(reinterpret_cast<const uint4 *>(src));
       }
-      const uint16_t *src = p.cache + (static_cast<uint64_t>(page) * NERVA_KV_CACHE_BLOCK_TOKENS +
-                                       token % NERVA_KV_CACHE_BLOCK_TOKENS) * width + piece * 8u;
-      *reinterpret_cast<uint4 *>(tile + r * row_bytes + piece * 16u) = __ldcg(reinterpret_cast<const uint4 *>(src));
+      *reinterpret_cast<uint4 *>(tile + r * row_bytes + piece * 16u) = v;
     }
     __syncthreads();
-    if (h >= p.heads) continue;
-    for (uint32_t r = 0; r < valid; ++r) {
-      const uint16_t *c = reinterpret_cast<const uint16_t *>(tile + r * row_bytes);
-      float dot = 0.0f;
-#pragma unroll
-      for (uint32_t j = 0; j < RANK_PER_LANE; ++j) dot = fmaf(ql[j], bf16_bits_to_f32(c[lane + 32u * j]), dot);
-      if (lane < p.rope) dot = fmaf(qr[0], bf16_bits_to_f32(c[RANK + lane]), dot);
-      if (lane + 32u < p.rope) dot = fmaf(qr[1], bf16_bits_to_f32(c[RANK + lane + 32u]), dot);
-      const float s = warp_sum(dot);
-      const float m_new = fmaxf(m_run, s);
-      const float corr = exp2f(m_run - m_new);  // first row: exp2(-inf) = 0
+    {
+      // ---- scores: this warp's 8 rows, its quarter of the features ----
+      const uint32_t nt = warp & 3u, quarter = warp >> 2;
+      const uint32_t per = (k_steps + 3u) / 4u;
+      const uint32_t ks_begin = quarter * per;
+      const uint32_t ks_end = ks_begin + per < k_steps ? ks_begin + per : k_steps;
+      float c[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+      const uint8_t *b_row = tile + (nt * 8u + g) * row_bytes + 4u * t;
+      const uint8_t *a_row = q_hi + g * row_bytes + 4u * t;
+      const uint32_t lo_offset = kMlaHeadsTile * row_bytes;  // q_lo - q_hi
+      for (uint32_t ks = ks_begin; ks < ks_end; ++ks) {
+        const uint32_t at = ks * 32u;  // bytes into a row
+        const uint32_t b0 = *reinterpret_cast<const uint32_t *>(b_row + at);
+        const uint32_t b1 = *reinterpret_cast<const uint32_t *>(b_row + at + 16u);
+        uint32_t a[4];
+        a[0] = *reinterpret_cast<const uint32_t *>(a_row + at);
+        a[1] = *reinterpret_cast<const uint32_t *>(a_row + 8u * row_bytes + at);
+        a[2] = *reinterpret_cast<const uint32_t *>(a_row + at + 16u);
+        a[3] = *reinterpret_cast<const uint32_t *>(a_row + 8u * row_bytes + at + 16u);
+        mma_bf16(c, a, b0, b1);
+        a[0] = *reinterpret_cast<const uint32_t *>(a_row + lo_offset + at);
+        a[1] = *reinterpret_cast<const uint32_t *>(a_row + lo_offset + 8u * row_bytes + at);
+        a[2] = *reinterpret_cast<const uint32_t *>(a_row + lo_offset + at + 16u);
+        a[3] = *reinterpret_cast<const uint32_t *>(a_row + lo_offset + 8u * row_bytes + at + 16u);
+        mma_bf16(c, a, b0, b1);
+      }
+      float *out = s_part + quarter * kMlaHeadsTile * kMlaTile + nt * 8u + 2u * t;
+      *reinterpret_cast<float2 *>(out + g * kMlaTile) = make_float2(c[0], c[1]);
+      *reinterpret_cast<float2 *>(out + (g + 8u) * kMlaTile) = make_float2(c[2], c[3]);
+    }
+    __syncthreads();
+    {
+      // ---- softmax: head = warp, row = lane ----
+      const float *sp = s_part + warp * kMlaTile + lane;
+      float s = ((sp[0] + sp[kMlaHeadsTile * kMlaTile]) + sp[2u * kMlaHeadsTile * kMlaTile]) +
+                sp[3u * kMlaHeadsTile * kMlaTile];
+      if (lane >= valid) s = -INFINITY;
+      const float m_new = fmaxf(m_run, warp_max(s));
+      const float corr = exp2f(m_run - m_new);  // first tile: exp2(-inf) = 0
       const float pr = exp2f(s - m_new);
-      l_run = l_run * corr + pr;
+      l_run = l_run * corr + warp_sum(pr);
       m_run = m_new;
+      const uint16_t hi = f32_to_bf16_bits(pr);
+      p_hi[warp * kMlaPStride + lane] = hi;
+      p_lo[warp * kMlaPStride + lane] = f32_to_bf16_bits(pr - bf16_bits_to_f32(hi));
+      if (lane == 0) rescale[warp] = corr;
+    }
+    __syncthreads();
+    {
+      // ---- values: acc = acc * corr + P . C for this warp's features ----
+      const float corr_a = rescale[g], corr_b = rescale[g + 8u];
 #pragma unroll
-      for (uint32_t j = 0; j < RANK_PER_LANE; ++j) acc[j] = fmaf(pr, bf16_bits_to_f32(c[lane + 32u * j]), acc[j] * corr);
+      for (uint32_t i = 0; i < NT; ++i) {
+        acc[i][0] *= corr_a;
+        acc[i][1] *= corr_a;
+        acc[i][2] *= corr_b;
+        acc[i][3] *= corr_b;
+      }
+#pragma unroll
+      for (uint32_t ks = 0; ks < kMlaTile / 16u; ++ks) {
+        uint32_t a_hi[4], a_lo[4];
+        const uint32_t a0 = g * kMlaPStride + ks * 16u + 2u * t;
+        a_hi[0] = *reinterpret_cast<const uint32_t *>(p_hi + a0);
+        a_hi[1] = *reinterpret_cast<const uint32_t *>(p_hi + a0 + 8u * kMlaPStride);
+        a_hi[2] = *reinterpret_cast<const uint32_t *>(p_hi + a0 + 8u);
+        a_hi[3] = *reinterpret_cast<const uint32_t *>(p_hi + a0 + 8u * kMlaPStride + 8u);
+        a_lo[0] = *reinterpret_cast<const uint32_t *>(p_lo + a0);
+        a_lo[1] = *reinterpret_cast<const uint32_t *>(p_lo + a0 + 8u * kMlaPStride);
+        a_lo[2] = *reinterpret_cast<const uint32_t *>(p_lo + a0 + 8u);
+        a_lo[3] = *reinterpret_cast<const uint32_t *>(p_lo + a0 + 8u * kMlaPStride + 8u);
+        // four 8 x 8 matrices per load: (rows 0..7 | 8..15 of the k-step) x (features of n-tile i | i + 1)
+        const uint32_t row = ks * 16u + ((lane >> 3) & 1u) * 8u + (lane & 7u);
+        if constexpr (NT >= 2) {
+#pragma unroll
+          for (uint32_t i = 0; i < NT; i += 2) {
+            const uint32_t feature = (warp * NT + i + (lane >> 4)) * 8u;
+            uint32_t b[4];
+            ldmatrix_x4_trans(b, smem_addr(tile + row * row_bytes + feature * 2u));
+            mma_bf16(acc[i], a_hi, b[0], b[1]);
+            mma_bf16(acc[i], a_lo, b[0], b[1]);
+            mma_bf16(acc[i + 1], a_hi, b[2], b[3]);
+            mma_bf16(acc[i + 1], a_lo, b[2], b[3]);
+          }
+        } else {
+          // one n-tile per warp: lanes 16..31 repeat the addresses of lanes 0..15
+          const uint32_t feature = warp * 8u;
+          uint32_t b[4];
+          ldmatrix_x4_trans(b, smem_addr(tile + row * row_bytes + feature * 2u));
+          mma_bf16(acc[0], a_hi, b[0], b[1]);
+          mma_bf16(acc[0], a_lo, b[0], b[1]);
+        }
+      }
     }
   }
-  if (h < p.heads) {
-    const uint64_t slot = static_cast<uint64_t>(h) * S + split;
+  // partial results of the span: accumulator rows g and g + 8 are heads, columns features
 #pragma unroll
-    for (uint32_t j = 0; j < RANK_PER_LANE; ++j) p.partial_acc[slot * RANK + lane + 32u * j] = acc[j];
-    if (lane == 0) {
-      p.partial_m[slot] = m_run;
-      p.partial_l[slot] = l_run;
-    }
+  for (uint32_t i = 0; i < NT; ++i) {
+    const uint32_t feature = (warp * NT + i) * 8u + 2u * t;
+    if (g < p.heads)
+      *reinterpret_cast<float2 *>(p.partial_acc + (static_cast<uint64_t>(g) * S + split) * RANK + feature) =
+          make_float2(acc[i][0], acc[i][1]);
+    if (g + 8u < p.heads)
+      *reinterpret_cast<float2 *>(p.partial_acc + (static_cast<uint64_t>(g + 8u) * S + split) * RANK + feature) =
+          make_float2(acc[i][2], acc[i][3]);
+  }
+  if (warp < p.heads && lane == 0) {
+    p.partial_m[static_cast<uint64_t>(warp) * S + split] = m_run;
+    p.partial_l[static_cast<uint64_t>(warp) * S + split] = l_run;
   }
 }
 
-__global__ void __launch_bounds__(256) mla_output_kernel(MlaParams p, uint32_t splits) {
+__global__ void __launch_bounds__(256) mla_output_kernel(MlaParams p, uint32_t slots) {
   __shared__ float lat[kMlaMaxRank];
   __shared__ float weight[kMlaMaxSplits];
   pdl_trigger();
@@ -195,17 +322,25 @@ __global__ void __launch_bounds__(256) mla_output_kernel(MlaParams p, uint32_t s
   const uint32_t position = *p.cursor;
   if (position >= p.max_context) return;
   const uint32_t h = blockIdx.x;
+  uint32_t splits;  // spans that hold something; `slots` of them were launched and are the stride
+  {
+    // spans beyond the context's last tile hold nothing (the attention kernel's split arithmetic)
+    const uint32_t tiles_total = (position + 1u + kMlaTile - 1u) / kMlaTile;
+    const uint32_t tiles_per_split = (tiles_total + slots - 1u) / slots;
+    splits = (tiles_total + tiles_per_split - 1u) / tiles_per_split;
+    if (splits > slots) splits = slots;
+  }
   if (threadIdx.x < 32u) {
     // one lane per span (two when there are more than 32): the (m, l) pairs become normalised weights
     const uint32_t lane = threadIdx.x;
     float m = -INFINITY;
     for (uint32_t s = lane; s < splits; s += 32u)
-      if (__ldcg(p.partial_l + h * splits + s) > 0.0f) m = fmaxf(m, __ldcg(p.partial_m + h * splits + s));
+      if (__ldcg(p.partial_l + h * slots + s) > 0.0f) m = fmaxf(m, __ldcg(p.partial_m + h * slots + s));
     m = warp_max(m);
     float l = 0.0f;
     for (uint32_t s = lane; s < splits; s += 32u) {
-      const float ls = __ldcg(p.partial_l + h * splits + s);
-      const float w = ls > 0.0f ? exp2f(__ldcg(p.partial_m + h * splits + s) - m) : 0.0f;
+      const float ls = __ldcg(p.partial_l + h * slots + s);
+      const float w = ls > 0.0f ? exp2f(__ldcg(p.partial_m + h * slots + s) - m) : 0.0f;
       weight[s] = w;
       l = fmaf(ls, w, l);
     }
@@ -221,12 +356,12 @@ __global__ void __launch_bounds__(256) mla_output_kernel(MlaParams p, uint32_t s
     for (; s + 8u <= splits; s += 8u) {
       float v[8];
 #pragma unroll
-      for (uint32_t u = 0; u < 8u; ++u) v[u] = __ldcg(p.partial_acc + (static_cast<uint64_t>(h) * splits + s + u) * p.rank + r);
+      for (uint32_t u = 0; u < 8u; ++u) v[u] = __ldcg(p.partial_acc + (static_cast<uint64_t>(h) * slots + s + u) * p.rank + r);
 #pragma unroll
       for (uint32_t u = 0; u < 8u; ++u) a = fmaf(v[u], weight[s + u], a);
     }
     for (; s < splits; ++s)
-      a = fmaf(__ldcg(p.partial_acc + (static_cast<uint64_t>(h) * splits + s) * p.rank + r), weight[s], a);
+      a = fmaf(__ldcg(p.partial_acc + (static_cast<uint64_t>(h) * slots + s) * p.rank + r), weight[s], a);
     lat[r] = a;
   }
   __syncthreads();
@@ -257,6 +392,16 @@ __global__ void __launch_bounds__(256) mla_output_kernel(MlaParams p, uint32_t s
 
 }  // namespace
 
+cudaError_t configure_mla_kernels() {
+  const int bytes = static_cast<int>(mla_attention_smem(kMlaMaxRank, kMlaMaxRope));
+  cudaError_t err = cudaFuncSetAttribute(mla_attention_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
+  if (err == cudaSuccess)
+    err = cudaFuncSetAttribute(mla_attention_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
+  if (err == cudaSuccess)
+    err = cudaFuncSetAttribute(mla_attention_kernel<4>, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
+  return err;
+}
+
 bool mla_session_supported(uint32_t heads, uint32_t rank, uint32_t nope, uint32_t rope, uint32_t v_dim) {
   return heads != 0 && heads <= 16u && (rank == 128u || rank == 256u || rank == 512u) && nope != 0 &&
          nope <= kMlaMaxNope && rope % 8u == 0 && rope <= kMlaMaxRope && rope != 0 && v_dim != 0;
@@ -275,16 +420,16 @@ cudaError_t launch_mla_attention(cudaStream_t stream, const MlaParams &p, uint32
   cudaError_t err = launch_with_pdl(mla_prepare_kernel, dim3(p.heads * (p.rank / kMlaPrepareSlice) + 1u), dim3(256), 0,
                                     stream, pdl, p);
   if (err != cudaSuccess) return err;
-  const uint32_t smem = kMlaTile * ((p.rank + p.rope) * 2u + 16u);
+  const uint32_t smem = mla_attention_smem(p.rank, p.rope);
   const dim3 grid(splits), block(512);
-  switch (p.rank / 32u) {
+  switch (p.rank / 128u) {
 #define NERVA_MLA_CASE(N)                                                                            \
   case N:                                                                                            \
     err = launch_with_pdl(mla_attention_kernel<N>, grid, block, smem, stream, pdl, p);               \
     break;
+    NERVA_MLA_CASE(1)
+    NERVA_MLA_CASE(2)
     NERVA_MLA_CASE(4)
-    NERVA_MLA_CASE(8)
-    NERVA_MLA_CASE(16)
 #undef NERVA_MLA_CASE
     default:
       return cudaErrorNotSupported;  // latent ranks 128, 256 and 512

@@ -1636,6 +1636,7 @@ static int create_session(const NervaCudaHfDecodeSequenceSessionCreateRequest *r
   if (err == cudaSuccess) err = configure_attention_kernels();
   if (err == cudaSuccess) err = configure_fused_attention_kernel();
   if (err == cudaSuccess) err = configure_moe_kernels();
+  if (err == cudaSuccess) err = configure_mla_kernels();
   if (err != cudaSuccess) return create_fail(s, out, err, kStageSetDevice);
   if (d.mla() && !mla_session_supported(d.heads, d.mla_rank, d.mla_nope, d.mla_rope, d.head_dim)) {
     set_last_error("latent attention shape not supported: needs at most 16 heads, latent rank 128, 256 or 512, "
