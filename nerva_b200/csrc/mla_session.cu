@@ -161,16 +161,29 @@ __global__ void __launch_bounds__(512) mla_attention_kernel(MlaParams p) {
   // padding zero
   if (tile_begin < tile_end) {
     const float qscale = kLog2e * rsqrtf(static_cast<float>(p.nope + p.rope));
-    const uint32_t padded = row_bytes / 2u;
-    for (uint32_t i = threadIdx.x; i < kMlaHeadsTile * padded; i += blockDim.x) {
-      const uint32_t h = i / padded, k = i % padded;
-      float v = 0.0f;
-      if (h < p.heads && k < RANK) v = __ldcg(p.ql + static_cast<uint64_t>(h) * RANK + k) * qscale;
-      else if (h < p.heads && k < width)
-        v = __ldcg(p.qkv + static_cast<uint64_t>(h) * (p.nope + p.rope) + p.nope + (k - RANK)) * qscale;
-      const uint16_t hi = f32_to_bf16_bits(v);
-      reinterpret_cast<uint16_t *>(q_hi + h * row_bytes)[k] = hi;
-      reinterpret_cast<uint16_t *>(q_lo + h * row_bytes)[k] = f32_to_bf16_bits(v - bf16_bits_to_f32(hi));
+    const uint32_t padded = row_bytes / 2u, total = kMlaHeadsTile * padded;
+    constexpr uint32_t kBatch = 8;  // loads in flight per thread
+    for (uint32_t base = threadIdx.x; base < total; base += blockDim.x * kBatch) {
+      float v[kBatch];
+#pragma unroll
+      for (uint32_t u = 0; u < kBatch; ++u) {
+        const uint32_t i = base + u * blockDim.x;
+        const uint32_t h = i / padded, k = i % padded;
+        v[u] = 0.0f;
+        if (i < total && h < p.heads && k < RANK) v[u] = __ldcg(p.ql + static_cast<uint64_t>(h) * RANK + k);
+        else if (i < total && h < p.heads && k < width)
+          v[u] = __ldcg(p.qkv + static_cast<uint64_t>(h) * (p.nope + p.rope) + p.nope + (k - RANK));
+      }
+#pragma unroll
+      for (uint32_t u = 0; u < kBatch; ++u) {
+        const uint32_t i = base + u * blockDim.x;
+        if (i >= total) break;
+        const uint32_t h = i / padded, k = i % padded;
+        const float scaled = v[u] * qscale;
+        const uint16_t hi = f32_to_bf16_bits(scaled);
+        reinterpret_cast<uint16_t *>(q_hi + h * row_bytes)[k] = hi;
+        reinterpret_cast<uint16_t *>(q_lo + h * row_bytes)[k] = f32_to_bf16_bits(scaled - bf16_bits_to_f32(hi));
+      }
     }
   }
   // warp h keeps head h's running maximum and sum; every warp its features of all heads
@@ -186,21 +199,38 @@ __global__ void __launch_bounds__(512) mla_attention_kernel(MlaParams p) {
     // the tile's rows in 16-byte pieces (a row is width * 2 bytes, a multiple of 16, then 16 bytes
     // of padding); rows beyond the context and the padding are zero
     const uint32_t pieces = row_bytes / 16u;
-    for (uint32_t i = threadIdx.x; i < kMlaTile * pieces; i += blockDim.x) {
-      const uint32_t r = i / pieces, piece = i % pieces;
-      uint4 v = make_uint4(0u, 0u, 0u, 0u);
-      if (r < valid && piece < width / 8u) {
-        const uint32_t token = token0 + r;
-        uint32_t page = p.page_table[token / NERVA_KV_CACHE_BLOCK_TOKENS];
-        if (page >= p.page_count) {
-          report_error(p.error_word, kErrPageOutOfRange);
-          page = 0;
-        }
-        const uint16_t *src = p.cache + (static_cast<uint64_t>(page) * NERVA_KV_CACHE_BLOCK_TOKENS +
-                                         token % NERVA_KV_CACHE_BLOCK_TOKENS) * width + piece * 8u;
-        v = __ldcg(reinterpret_cast<const uint4 *>(src));
+    constexpr uint32_t kBatch = 5;  // 32 rows of rank 512 + rope 64 are 4.6 pieces per thread
+    for (uint32_t base = threadIdx.x; base < kMlaTile * pieces; base += blockDim.x * kBatch) {
+      uint32_t page[kBatch];
+      bool fetch[kBatch];
+      uint4 v[kBatch];
+#pragma unroll
+      for (uint32_t u = 0; u < kBatch; ++u) {
+        const uint32_t i = base + u * blockDim.x;
+        const uint32_t r = i / pieces, piece = i % pieces;
+        fetch[u] = i < kMlaTile * pieces && r < valid && piece < width / 8u;
+        page[u] = fetch[u] ? p.page_table[(token0 + r) / NERVA_KV_CACHE_BLOCK_TOKENS] : 0u;
       }
-      *reinterpret_cast<uint4 *>(tile + r * row_bytes + piece * 16u) = v;
+#pragma unroll
+      for (uint32_t u = 0; u < kBatch; ++u) {
+        const uint32_t i = base + u * blockDim.x;
+        const uint32_t r = i / pieces, piece = i % pieces;
+        v[u] = make_uint4(0u, 0u, 0u, 0u);
+        if (!fetch[u]) continue;
+        if (page[u] >= p.page_count) {
+          report_error(p.error_word, kErrPageOutOfRange);
+          page[u] = 0;
+        }
+        const uint16_t *src = p.cache + (static_cast<uint64_t>(page[u]) * NERVA_KV_CACHE_BLOCK_TOKENS +
+                                         (token0 + r) % NERVA_KV_CACHE_BLOCK_TOKENS) * width + piece * 8u;
+        v[u] = __ldcg(reinterpret_cast<const uint4 *>(src));
+      }
+#pragma unroll
+      for (uint32_t u = 0; u < kBatch; ++u) {
+        const uint32_t i = base + u * blockDim.x;
+        if (i >= kMlaTile * pieces) break;
+        *reinterpret_cast<uint4 *>(tile + (i / pieces) * row_bytes + (i % pieces) * 16u) = v[u];
+      }
     }
     __syncthreads();
     {

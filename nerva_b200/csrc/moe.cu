@@ -147,12 +147,27 @@ template <bool PLANAR>
 __device__ void add_norm_to_smem_f32(float *x, const float *a, const float *b, const uint16_t *bias,
                                      const uint16_t *w, float eps, uint32_t cols, float *scratch) {
   float sumsq = 0.0f;
-  for (uint32_t i = threadIdx.x; i < cols; i += blockDim.x) {
-    float r = b != nullptr ? __ldcg(b + i) : __ldcg(a + i);
-    if (bias != nullptr) r += bf16_bits_to_f32(bias[i]);
-    if (b != nullptr) r += __ldcg(a + i);
-    x[PLANAR ? xf32_index(i, cols) : i] = r;
-    sumsq += r * r;
+  constexpr uint32_t kBatch = 4;  // elements whose loads are in flight together
+  for (uint32_t base = threadIdx.x; base < cols; base += blockDim.x * kBatch) {
+    float va[kBatch], vb[kBatch], vbias[kBatch];
+#pragma unroll
+    for (uint32_t u = 0; u < kBatch; ++u) {
+      const uint32_t i = base + u * blockDim.x;
+      va[u] = i < cols ? __ldcg(a + i) : 0.0f;
+      vb[u] = i < cols && b != nullptr ? __ldcg(b + i) : 0.0f;
+      vbias[u] = i < cols && bias != nullptr ? bf16_bits_to_f32(bias[i]) : 0.0f;
+    }
+#pragma unroll
+    for (uint32_t u = 0; u < kBatch; ++u) {
+      const uint32_t i = base + u * blockDim.x;
+      if (i >= cols) break;
+      // the order of the sum: (b or a) + bias, then + a when there are two addends
+      float r = b != nullptr ? vb[u] : va[u];
+      if (bias != nullptr) r += vbias[u];
+      if (b != nullptr) r += va[u];
+      x[PLANAR ? xf32_index(i, cols) : i] = r;
+      sumsq += r * r;
+    }
   }
   const float total = block_sum(sumsq, scratch);
   const float scale = rsqrtf(total / static_cast<float>(cols) + eps);
@@ -241,7 +256,20 @@ __global__ void __launch_bounds__(kStreamThreads, 1) moe_expert_kernel(MoeExpert
     for (uint32_t row = warp; row < p.num_experts; row += kStreamWarps) {
       const uint4 *w = reinterpret_cast<const uint4 *>(p.w_router + static_cast<uint64_t>(row) * p.hidden);
       float acc = 0.0f;
-      for (uint32_t i = lane; i < p.hidden / 8u; i += 32u) acc = dot8_f32(__ldg(w + i), xa[i], xb[i], acc);
+      constexpr uint32_t kBatch = 8;  // loads in flight per lane: a 2048-wide row in one round trip
+      for (uint32_t base = lane; base < p.hidden / 8u; base += 32u * kBatch) {
+        uint4 wv[kBatch];
+#pragma unroll
+        for (uint32_t u = 0; u < kBatch; ++u) {
+          const uint32_t i = base + 32u * u;
+          wv[u] = i < p.hidden / 8u ? __ldg(w + i) : make_uint4(0u, 0u, 0u, 0u);
+        }
+#pragma unroll
+        for (uint32_t u = 0; u < kBatch; ++u) {
+          const uint32_t i = base + 32u * u;
+          if (i < p.hidden / 8u) acc = dot8_f32(wv[u], xa[i], xb[i], acc);
+        }
+      }
       acc = warp_sum(acc);
       if (lane == 0) sh.logits[row] = acc;
     }
