@@ -372,8 +372,21 @@ __global__ void __launch_bounds__(kStreamThreads, 1) moe_expert_kernel(MoeExpert
       // x = silu(gate) * up of expert g, unrounded
       const float *gate = p.gate_up_out + place;
       const float *up = gate + job.cols;
-      for (uint32_t i = threadIdx.x; i < job.cols; i += blockDim.x)
-        x[xf32_index(i, job.cols)] = silu(__ldcg(gate + i)) * __ldcg(up + i);
+      constexpr uint32_t kBatch = 4;  // elements whose loads are in flight together
+      for (uint32_t base = threadIdx.x; base < job.cols; base += blockDim.x * kBatch) {
+        float vg[kBatch], vu[kBatch];
+#pragma unroll
+        for (uint32_t u = 0; u < kBatch; ++u) {
+          const uint32_t i = base + u * blockDim.x;
+          vg[u] = i < job.cols ? __ldcg(gate + i) : 0.0f;
+          vu[u] = i < job.cols ? __ldcg(up + i) : 0.0f;
+        }
+#pragma unroll
+        for (uint32_t u = 0; u < kBatch; ++u) {
+          const uint32_t i = base + u * blockDim.x;
+          if (i < job.cols) x[xf32_index(i, job.cols)] = silu(vg[u]) * vu[u];
+        }
+      }
       __syncthreads();
     }
     stream_consume<true>(rs, sh.stream, j, x, row_total, p.error_word);
