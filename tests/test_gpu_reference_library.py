@@ -90,3 +90,24 @@ def test_qwen3_8b_layer_shapes_equal_the_reference_cuda_path(built_lib, referenc
     bound = 4e-2  # twice the oracle's own distance to itself at two layers of this width
     assert_stream_matches_or_ties(theirs.tokens, tokens.tolist(), margins, bound, "reference vs oracle")
     assert_stream_matches_or_ties(ours.tokens, theirs.tokens, margins, bound, "this library vs reference")
+
+
+@pytest.mark.parametrize("shared", [0, 128])
+def test_sparse_moe_tokens_equal_the_reference_cuda_path(built_lib, reference_library, oracle_mod, shared):
+    """Softmax top-k MoE layers (16 experts, top 4, renormalised weights, with and without a gated
+    shared expert): this library, the reference's CUDA path (its whole MoE MLP in one thread block,
+    hf_decode_sequence/device_ops.cuh:183-315) and the oracle.  Pins the routing order, the expert
+    matrix layout and the unrounded activations of the sparse path to output the reference produced."""
+    cfg = synth.DecoderConfig("tiny-moe", layers=2, hidden=512, heads=8, kv_heads=2, head_dim=64, intermediate=1024,
+                              vocab=4096, prompt_tokens=12, decode_tokens=12, num_experts=16, top_k=4,
+                              moe_intermediate=256, shared_intermediate=shared, norm_topk_prob=True)
+    ck = synth.dense_checkpoint(cfg, fill=ops.synth_normal_bf16)
+    prompt = synth.prompt_ids(cfg)
+    ours = _decode(ck, prompt, cfg.decode_tokens)
+    theirs = _decode(ck, prompt, cfg.decode_tokens, library=reference_library)
+    dec = oracle_mod.Decoder(ck, cfg.prompt_tokens + cfg.decode_tokens, mode=oracle_mod.MODE_CUDA)
+    tokens, logits = dec.decode_greedy(prompt, cfg.decode_tokens, want_logits=True)
+    top2 = np.sort(logits, axis=1)[:, -2:]
+    margins = (top2[:, 1] - top2[:, 0]).tolist()
+    assert_stream_matches_or_ties(theirs.tokens, tokens.tolist(), margins, TINY_TIE_BOUND, "reference vs oracle")
+    assert_stream_matches_or_ties(ours.tokens, theirs.tokens, margins, TINY_TIE_BOUND, "this library vs reference")
