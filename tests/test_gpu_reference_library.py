@@ -111,3 +111,4 @@ def test_sparse_moe_tokens_equal_the_reference_cuda_path(built_lib, reference_li
     margins = (top2[:, 1] - top2[:, 0]).tolist()
     assert_stream_matches_or_ties(theirs.tokens, tokens.tolist(), margins, TINY_TIE_BOUND, "reference vs oracle")
     assert_stream_matches_or_ties(ours.tokens, theirs.tokens, margins, TINY_TIE_BOUND, "this library vs reference")
+
