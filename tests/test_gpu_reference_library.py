@@ -112,3 +112,45 @@ def test_sparse_moe_tokens_equal_the_reference_cuda_path(built_lib, reference_li
     assert_stream_matches_or_ties(theirs.tokens, tokens.tolist(), margins, TINY_TIE_BOUND, "reference vs oracle")
     assert_stream_matches_or_ties(ours.tokens, theirs.tokens, margins, TINY_TIE_BOUND, "this library vs reference")
 
+
+def test_block_of_forks_equals_the_reference_cuda_path(built_lib, reference_library, oracle_mod, tiny_checkpoint):
+    """batch_advance_one over a parent and three forks in both libraries: the same selection result
+    (reason, exactness, block size, eligible and observed counts) every step, the same token for every
+    session of the block, and the same stream as the reference's packed path produced (its
+    cublasLt block projections, session_api_batch_fork_destroy.inc.cu)."""
+    cfg = synth.TINY_QWEN3
+    prompt = synth.prompt_ids(cfg)[:11]
+    steps = 6
+
+    def run(library):
+        # descriptors: the packed step only takes sessions whose shared weights are proven by a plan hash
+        parent = CudaHfDecodeSequenceSession(tiny_checkpoint, 96, use_descriptors=True, library=library)
+        assert parent.status == SmokeStatus.OK, parent.error
+        start, loop = CudaHfDecodeSequenceLoop.start(parent, prompt)
+        assert start.status == SmokeStatus.OK, start.error
+        stream = list(loop.advance(3).tokens)
+        forks = [parent.fork_shared_weights() for _ in range(3)]
+        assert all(f.status == SmokeStatus.OK for f in forks)
+        block = [parent] + forks
+        fields = []
+        for _ in range(steps):
+            out = CudaHfDecodeSequenceSession.batch_advance_one(block, target_block_tokens=8, min_block_tokens=2)
+            assert out.status == SmokeStatus.OK, out.error
+            assert out.reason == 0 and out.exact == 1 and out.block_tokens == 4, (out.reason, out.exact, out.block_tokens)
+            assert len(set(out.tokens)) == 1, out.tokens  # forks of one sequence decode the same token
+            stream.append(out.tokens[0])
+            fields.append((out.reason, out.exact, out.block_tokens, out.eligible_session_count, out.observed_tokens))
+        for s in forks:
+            s.destroy()
+        parent.destroy()
+        return stream, fields
+
+    ours, our_fields = run(None)
+    theirs, their_fields = run(reference_library)
+    assert our_fields == their_fields, (our_fields, their_fields)
+    dec = oracle_mod.Decoder(tiny_checkpoint, 96, mode=oracle_mod.MODE_CUDA)
+    tokens, logits = dec.decode_greedy(prompt, 3 + steps, want_logits=True)
+    top2 = np.sort(logits, axis=1)[:, -2:]
+    margins = (top2[:, 1] - top2[:, 0]).tolist()
+    assert_stream_matches_or_ties(theirs, tokens.tolist(), margins, TINY_TIE_BOUND, "reference block step vs oracle")
+    assert_stream_matches_or_ties(ours, theirs, margins, TINY_TIE_BOUND, "this library's block step vs the reference's")
