@@ -154,3 +154,26 @@ def test_block_of_forks_equals_the_reference_cuda_path(built_lib, reference_libr
     margins = (top2[:, 1] - top2[:, 0]).tolist()
     assert_stream_matches_or_ties(theirs, tokens.tolist(), margins, TINY_TIE_BOUND, "reference block step vs oracle")
     assert_stream_matches_or_ties(ours, theirs, margins, TINY_TIE_BOUND, "this library's block step vs the reference's")
+
+
+def test_file_backed_upload_equals_the_reference_cuda_path(built_lib, reference_library, tiny_checkpoint, tiny_golden,
+                                                           tmp_path):
+    """The same weight file and the same (file, offset, length) descriptors through both libraries'
+    pinned-staging upload (hf_decode_sequence/weights.cu:797-850): the same model in both."""
+    from nerva_b200.session import write_weight_file
+    path = str(tmp_path / "weights.bin")
+    write_weight_file(tiny_checkpoint, path, header_bytes=4096)
+    prompt = np.array(tiny_golden["prompt"], dtype=np.uint32)
+    streams = []
+    for library in (None, reference_library):
+        s = CudaHfDecodeSequenceSession(tiny_checkpoint, 128, weight_file=path, weight_file_header=4096,
+                                        library=library)
+        assert s.status == SmokeStatus.OK, (s.error, s.create_result.cuda_error, s.create_result.failure_stage)
+        out = s.run(prompt, 8)
+        assert out.status == SmokeStatus.OK, (out.error, out.cuda_error)
+        streams.append(out.tokens)
+        s.destroy()
+    margins = tiny_golden["cuda"]["top1_minus_top2"]
+    assert_stream_matches_or_ties(streams[1], tiny_golden["cuda"]["tokens"][:8], margins, TINY_TIE_BOUND,
+                                  "reference from the file vs golden")
+    assert_stream_matches_or_ties(streams[0], streams[1], margins, TINY_TIE_BOUND, "this library vs reference")
