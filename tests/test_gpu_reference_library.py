@@ -177,3 +177,31 @@ def test_file_backed_upload_equals_the_reference_cuda_path(built_lib, reference_
     assert_stream_matches_or_ties(streams[1], tiny_golden["cuda"]["tokens"][:8], margins, TINY_TIE_BOUND,
                                   "reference from the file vs golden")
     assert_stream_matches_or_ties(streams[0], streams[1], margins, TINY_TIE_BOUND, "this library vs reference")
+
+
+def test_fork_continues_like_its_parent_in_both_libraries(built_lib, reference_library, oracle_mod, tiny_checkpoint):
+    """session_fork_shared_weights in the middle of a sequence: the fork's tail and the parent's tail are
+    the same tokens, in the reference's library and in this one, and they are the oracle's."""
+    cfg = synth.TINY_QWEN3
+    prompt = synth.prompt_ids(cfg)[:17]
+    streams = []
+    for library in (None, reference_library):
+        parent = CudaHfDecodeSequenceSession(tiny_checkpoint, 96, use_descriptors=True, library=library)
+        assert parent.status == SmokeStatus.OK, parent.error
+        start, loop = CudaHfDecodeSequenceLoop.start(parent, prompt)
+        assert start.status == SmokeStatus.OK, start.error
+        head = list(loop.advance(4).tokens)
+        fork = parent.fork_shared_weights()
+        assert fork.status == SmokeStatus.OK, fork.error
+        fork_tail = list(CudaHfDecodeSequenceLoop(fork).advance(6).tokens)
+        parent_tail = list(loop.advance(6).tokens)
+        assert fork_tail == parent_tail, (fork_tail, parent_tail)
+        streams.append(head + parent_tail)
+        fork.destroy()
+        parent.destroy()
+    dec = oracle_mod.Decoder(tiny_checkpoint, 96, mode=oracle_mod.MODE_CUDA)
+    tokens, logits = dec.decode_greedy(prompt, 10, want_logits=True)
+    top2 = np.sort(logits, axis=1)[:, -2:]
+    margins = (top2[:, 1] - top2[:, 0]).tolist()
+    assert_stream_matches_or_ties(streams[1], tokens.tolist(), margins, TINY_TIE_BOUND, "reference vs oracle")
+    assert_stream_matches_or_ties(streams[0], streams[1], margins, TINY_TIE_BOUND, "this library vs reference")
