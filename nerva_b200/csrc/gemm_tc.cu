@@ -21,7 +21,7 @@
 // epilogue for it.  A matrix with between one and two row tiles per SM gets one block per tile
 // instead: nothing is split and no second launch follows.  Summing inside the projection kernel by
 // the last block to arrive was measured first: that one block reads every partial of its tile with
-// 128 threads while the rest of the grid has left, 10 to 27 us for a 64-token block.  The partition
+// 128 threads while the rest of the grid has left, which cost more than the launch.  The partition
 // depends on the shape only, so a token's result does not depend on which other tokens share its
 // block, and results are bit-stable run to run.
 //
@@ -553,8 +553,7 @@ uint32_t gemm_blocks(uint32_t rows, uint32_t cols, uint32_t sm_count) {
   const uint32_t want = 2u * sm_count;
   // Between one and two row tiles per SM (gate/up of the 8B shapes: 192 tiles): one block per tile.
   // Nothing is split, so no fix-up launch follows; the SMs that hold two blocks stream twice the
-  // bytes of the others, which the memory system evens out better than a second launch costs
-  // (gate/up at 64 tokens: 0.52 -> 0.79 of the measured HBM peak).
+  // bytes of the others, which the memory system evens out better than a second launch costs.
   if (p.tiles >= sm_count && p.tiles <= want) return p.tiles;
   return p.total < want ? static_cast<uint32_t>(p.total) : want;
 }

@@ -19,8 +19,7 @@
 // slots.  An expert's rows are short (4 KB for gate/up at hidden 2048, 2.8 KB for down at
 // intermediate 1408) and the fp32 activations cost two shared loads per weight load, so these
 // kernels are bound by the instruction latency of a warp, not by the bytes in flight: twice the
-// warps hide twice the latency (DeepSeek-V2-Lite step 3.23 -> 2.94 ms; 12, 20 and 24 warps and a
-// third slot measured slower).
+// warps hide twice the latency.
 #define NERVA_STREAM_WARPS 16
 #define NERVA_CHUNK_BYTES 4096
 #define NERVA_STREAM_SLOTS 2
