@@ -32,7 +32,6 @@ namespace {
 
 constexpr uint32_t kMoeMaxTopK = 16;
 constexpr uint32_t kMoeMaxJobs = 2u * kMoeMaxTopK + 2u;
-constexpr uint32_t kRouteThreads = 256;
 
 // ---- routing ----
 __device__ __forceinline__ bool route_precedes(float w, uint32_t e, float best_w, uint32_t best_e) {
